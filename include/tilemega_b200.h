@@ -1,0 +1,116 @@
+/* C ABI of libtilemega_b200.so: the serving-plan interface of TileMega
+ * (include/tilemega/Codegen/tasks/ServingAbi.h, version 1) implemented by a
+ * hand-written sm_100a persistent decode kernel.
+ *
+ * A TileMega plan library is one compiled model: tm_plan_query takes no
+ * argument. This library reads its model from the JSON sidecar
+ * "<path of this .so>.plan.json" (or the file named by TILEMEGA_PLAN_JSON), so
+ * one copy of the .so next to one sidecar is one plan library, loadable by the
+ * reference's python/tilemega/serving/plan.py:PlanLibrary unchanged.
+ *
+ * Conventions (ServingAbi.h:33-55; ServingRuntime.cuh:943-977): 0 = OK,
+ * -1 bad argument, -2 iteration / step-interval mismatch, -3 mode unavailable,
+ * -4 plan abandoned by its watchdog; CUDA error codes are passed through as
+ * positive integers. No exception crosses the boundary. The caller owns every
+ * external buffer; the plan owns and frees its internal ones. Launches are
+ * asynchronous on the caller's stream; synchronise before any tm_plan_read_*.
+ * One host thread per plan.
+ */
+#ifndef TILEMEGA_B200_H_
+#define TILEMEGA_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ServingAbi.h:11-15 */
+enum { TM_SERVING_ABI_VERSION = 1 };
+enum { TM_SERVING_PREFILL = 0, TM_SERVING_DECODE = 1, TM_SERVING_FORWARD = 2 };
+enum { TM_SERVING_L1 = 1, TM_SERVING_L2 = 2 };
+enum { TM_BUFFER_INTERNAL = 0, TM_BUFFER_EXTERNAL = 1 };
+enum { TM_DTYPE_BF16 = 0, TM_DTYPE_F32 = 1, TM_DTYPE_I32 = 2 };
+
+/* ServingAbi.h:17-23 */
+typedef struct {
+  uint32_t abi_version, phase;
+  int32_t batch_lo, batch_hi, seq, past_lo, past_hi, capacity;
+  int32_t grid, residency;
+  uint32_t modes;
+  uint32_t buffer_count;
+} tm_plan_info;
+
+/* ServingAbi.h:25-31 */
+typedef struct {
+  const char* name;
+  uint32_t role;
+  uint32_t dtype;
+  uint64_t elements_constant, elements_per_batch;
+  const char* pack_json;
+} tm_buffer_info;
+
+/* ---- required entry points ------------------------------------------- */
+
+/* ServingAbi.h:33. Static description of the plan; no GPU needed. */
+int tm_plan_query(tm_plan_info* out);
+/* ServingAbi.h:34. Buffer table entry `index`; strings live as long as the library. */
+int tm_plan_buffer(uint32_t index, tm_buffer_info* out);
+/* ServingAbi.h:35. external[i] = device pointer of every TM_BUFFER_EXTERNAL
+ * entry in table order, NULL for internal ones. NULL on any rejection. */
+void* tm_plan_create(int batch, void* const* external, int device);
+/* ServingAbi.h:36. past[s] = position decoded by step s. */
+int tm_plan_set_steps(void* plan, const int32_t* past, uint32_t count);
+/* ServingAbi.h:37-40. iteration = launches of this mode so far, gap-free. */
+int tm_plan_launch(void* plan, uint32_t step, uint32_t mode, uint64_t iteration, void* stream);
+/* ServingAbi.h:48. */
+void tm_plan_destroy(void* plan);
+
+/* ---- optional entry points the reference driver probes by name -------- */
+
+/* ServingAbi.h:41-42. One persistent launch for steps [first, first+steps). */
+int tm_plan_launch_steps(void* plan, uint32_t first_step, uint32_t steps, uint32_t mode,
+                         uint64_t base_iteration, void* stream);
+/* ServingAbi.h:43. Bit mask of modes that support tm_plan_launch_steps. */
+unsigned tm_plan_loop_modes(void* plan);
+/* ServingAbi.h:44-45. %globaltimer stamps: host[i] = start of step first+i
+ * (= end of step first+i-1); count+1 stamps exist for count steps. */
+int tm_plan_read_step_ns(void* plan, uint32_t first, uint32_t count, uint64_t* host);
+/* ServingAbi.h:46-47. Copy table entry `index` to the host. */
+int tm_plan_read_buffer(void* plan, uint32_t index, void* host, uint64_t bytes);
+/* include/tilemega/Codegen/tasks/ServingRuntime.cuh:1065-1075. Returns 1 and
+ * fills the 12-word record {fired, site, block, thread, waiter_stage,
+ * waiter_task, producer_stage, group, row, need, value, iteration} when a
+ * bounded device wait gave up; the kernel returns normally in that case. */
+int tm_plan_watchdog(void* plan, uint64_t* record12);
+/* python/tilemega/serving/plan.py:152-159. Positions below prompt_len keep the
+ * token state the caller wrote (teacher forcing through the decode plan). */
+int tm_plan_set_prompt_len(void* plan, int prompt_len);
+/* plan.py:75-77; this plan never uses programmatic dependent launch. */
+unsigned tm_plan_pdl_enabled(void* plan);
+/* plan.py:76. Dynamic shared memory of the persistent kernel. */
+uint64_t tm_plan_execution_smem(void* plan, unsigned mode);
+/* ServingAbi.h:49-55. Tensor-parallel extension: this plan is unsharded. */
+unsigned tm_plan_tp_world(void);
+unsigned long long tm_plan_tp_bytes(unsigned which);
+int tm_plan_bind_tp(void* plan, int rank, void* const* ar, void* const* x);
+
+/* ---- additions of this library (probed by name; absent in the reference) */
+
+/* Last error text of the calling thread's most recent failing call. */
+const char* tm_plan_last_error(void);
+/* Clear a fired watchdog so the plan can launch again (counters are rezeroed
+ * by every launch). */
+int tm_plan_clear_watchdog(void* plan);
+/* Bounded-wait self test: a two-CTA kernel whose producer withholds its arrival
+ * when `withhold` != 0; the waiter gives up after limit_us and the kernel
+ * returns normally. Returns 1 if the wait gave up, 0 if it was satisfied. */
+int tm_plan_watchdog_probe(void* plan, int withhold, uint32_t limit_us, void* stream);
+/* Algorithmic HBM bytes of one decode step: GEMV weights incl. lm_head plus
+ * 4*L*Hkv*D bytes per cached token (scripts/estimate_r16_mbu.py:15-38). */
+uint64_t tm_plan_step_bytes(void* plan, uint64_t cached_tokens_total);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TILEMEGA_B200_H_ */

@@ -1,0 +1,176 @@
+"""CPU oracle for the decode path: a functional restatement of the reference's
+PyTorch forward, python/tilemega/serving/export.py:18-172 (RMSNorm :18-27,
+rotate_half :30-32, SelfAttention.forward :69-100, MLP :115-116, Layer :134-140,
+Decoder.execute :165-172), with the KV cache held in 16-token blocks behind a
+block table instead of being passed in and out as whole tensors.
+
+TEST INFRASTRUCTURE ONLY. Nothing on the product path imports this file; only
+tests/, __graft_entry__.smoke() and bench.py's CPU-baseline legs may.
+
+Pinned: tests/golden/*.pt hold logits and greedy tokens produced by the
+reference module itself (tests/golden/make_golden.py imports it from the
+reference tree); tests/test_oracle_golden.py checks this restatement against
+them in fp32 and bf16.
+
+Every op is the same torch op on the same dtype as the reference, so in bf16 the
+rounding sites are the reference's: one rounding per linear output, RMSNorm
+`w * (x.float() * rsqrt(mean x^2 + eps)).to(dtype)`, RoPE product-product-sum,
+scores rounded then divided by sqrt(D), softmax in fp32 cast back, SwiGLU and
+residual adds in the model dtype.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+
+KV_BLOCK = 16
+
+
+def head_dim_of(config: dict) -> int:
+    return int(config.get("head_dim") or config["hidden_size"] // config["num_attention_heads"])
+
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    # export.py:24-27
+    value = x.float()
+    value = value * torch.rsqrt(value.square().mean(-1, keepdim=True) + eps)
+    return weight * value.to(x.dtype)
+
+
+def rotate_half(value: torch.Tensor) -> torch.Tensor:
+    # export.py:30-32
+    half = value.shape[-1] // 2
+    return torch.cat((-value[..., half:], value[..., :half]), dim=-1)
+
+
+def rope_tables(config: dict, capacity: int, dtype: torch.dtype) -> tuple[torch.Tensor, torch.Tensor]:
+    """cos/sin [capacity][D]: default RoPE, computed in fp32, stored in bf16 (the
+    reference hands bf16 tables to both the GPU plan and its module,
+    python/tilemega/serving/state.py:30-59), then cast to the compute dtype."""
+    dim = head_dim_of(config)
+    theta = float(config.get("rope_theta", 10000.0))
+    inv_freq = 1.0 / (theta ** (torch.arange(0, dim, 2, dtype=torch.int64).float() / dim))
+    angles = torch.arange(capacity, dtype=torch.float32)[:, None] * inv_freq[None, :]
+    table = torch.cat((angles, angles), dim=-1)
+    return table.cos().to(torch.bfloat16).to(dtype), table.sin().to(torch.bfloat16).to(dtype)
+
+
+class PagedKV:
+    """[L][2][num_blocks][Hkv][16][D] pool + int32 block table [B][max_blocks]."""
+
+    def __init__(self, config: dict, batch: int, capacity: int, dtype: torch.dtype,
+                 block_table: torch.Tensor | None = None, num_blocks: int | None = None):
+        self.max_blocks = capacity // KV_BLOCK
+        self.num_blocks = num_blocks or batch * self.max_blocks
+        self.table = (block_table.clone().to(torch.int64) if block_table is not None
+                      else torch.arange(batch * self.max_blocks).reshape(batch, self.max_blocks))
+        if int(self.table.max()) >= self.num_blocks or int(self.table.min()) < 0:
+            raise ValueError("block table entry outside the pool")
+        self.pool = torch.zeros((config["num_hidden_layers"], 2, self.num_blocks, config["num_key_value_heads"],
+                                 KV_BLOCK, head_dim_of(config)), dtype=dtype)
+
+    def rows(self, positions: torch.Tensor, b: int) -> tuple[torch.Tensor, torch.Tensor]:
+        """(pool block, row in block) of each position of sequence b."""
+        return self.table[b, positions // KV_BLOCK], positions % KV_BLOCK
+
+    def append(self, layer: int, b: int, start: int, k: torch.Tensor, v: torch.Tensor) -> None:
+        # k, v: [S][Hkv][D] for positions start .. start+S-1
+        positions = torch.arange(start, start + k.shape[0])
+        block, row = self.rows(positions, b)
+        self.pool[layer, 0, block, :, row] = k
+        self.pool[layer, 1, block, :, row] = v
+
+    def gather(self, layer: int, b: int, length: int) -> tuple[torch.Tensor, torch.Tensor]:
+        # -> [Hkv][length][D] in logical order
+        block, row = self.rows(torch.arange(length), b)
+        k = self.pool[layer, 0, block, :, row].transpose(0, 1)
+        v = self.pool[layer, 1, block, :, row].transpose(0, 1)
+        return k, v
+
+
+class OracleDecoder:
+    """forward(ids [B][S], start [B]) -> logits [B][S][V]; appends to the cache."""
+
+    def __init__(self, config: dict, weights: dict[str, torch.Tensor], dtype: torch.dtype = torch.float32,
+                 capacity: int = 256):
+        self.config = config
+        self.dtype = dtype
+        self.w = {name: tensor.to(dtype) for name, tensor in weights.items()}
+        if "lm_head.weight" not in self.w:
+            if not config.get("tie_word_embeddings", False):
+                raise KeyError("untied model without lm_head.weight")
+            self.w["lm_head.weight"] = self.w["model.embed_tokens.weight"]
+        self.eps = float(config.get("rms_norm_eps", 1e-5))
+        self.heads = config["num_attention_heads"]
+        self.kv_heads = config["num_key_value_heads"]
+        self.dim = head_dim_of(config)
+        self.cos, self.sin = rope_tables(config, capacity, dtype)
+
+    def attention(self, layer: int, x: torch.Tensor, start: list[int], kv: PagedKV) -> torch.Tensor:
+        # export.py:69-100, one sequence at a time because lengths differ
+        p = f"model.layers.{layer}.self_attn."
+        batch, seq, _ = x.shape
+        q = F.linear(x, self.w[p + "q_proj.weight"]).view(batch, seq, self.heads, self.dim)
+        k = F.linear(x, self.w[p + "k_proj.weight"]).view(batch, seq, self.kv_heads, self.dim)
+        v = F.linear(x, self.w[p + "v_proj.weight"]).view(batch, seq, self.kv_heads, self.dim)
+        context = torch.empty((batch, seq, self.heads * self.dim), dtype=x.dtype)
+        for b in range(batch):
+            positions = torch.arange(start[b], start[b] + seq)
+            cosine = self.cos.index_select(0, positions).view(seq, 1, self.dim)
+            sine = self.sin.index_select(0, positions).view(seq, 1, self.dim)
+            qb = q[b] * cosine + rotate_half(q[b]) * sine
+            kb = k[b] * cosine + rotate_half(k[b]) * sine
+            kv.append(layer, b, start[b], kb, v[b])
+            full_k, full_v = kv.gather(layer, b, start[b] + seq)
+            query = qb.transpose(0, 1)                                   # [Hq][S][D]
+            keys = torch.repeat_interleave(full_k, self.heads // self.kv_heads, dim=0)
+            values = torch.repeat_interleave(full_v, self.heads // self.kv_heads, dim=0)
+            score = torch.matmul(query, keys.transpose(-1, -2)) / math.sqrt(self.dim)
+            key_position = torch.arange(start[b] + seq)[None, :]
+            score = score.masked_fill(key_position > positions[:, None], float("-inf"))
+            probability = torch.softmax(score.float(), dim=-1).to(x.dtype)
+            context[b] = torch.matmul(probability, values).transpose(0, 1).reshape(seq, self.heads * self.dim)
+        return F.linear(context, self.w[p + "o_proj.weight"])
+
+    def mlp(self, layer: int, x: torch.Tensor) -> torch.Tensor:
+        # export.py:115-116
+        p = f"model.layers.{layer}.mlp."
+        return F.linear(F.silu(F.linear(x, self.w[p + "gate_proj.weight"])) * F.linear(x, self.w[p + "up_proj.weight"]),
+                        self.w[p + "down_proj.weight"])
+
+    @torch.inference_mode()
+    def forward(self, ids: torch.Tensor, start: list[int], kv: PagedKV,
+                last_only: bool = False) -> torch.Tensor:
+        # export.py:134-140,165-172
+        x = F.embedding(ids.long(), self.w["model.embed_tokens.weight"])
+        for layer in range(self.config["num_hidden_layers"]):
+            p = f"model.layers.{layer}."
+            x = x + self.attention(layer, rms_norm(x, self.w[p + "input_layernorm.weight"], self.eps), start, kv)
+            x = x + self.mlp(layer, rms_norm(x, self.w[p + "post_attention_layernorm.weight"], self.eps))
+        if last_only:
+            x = x[:, -1:]
+        return F.linear(rms_norm(x, self.w["model.norm.weight"], self.eps), self.w["lm_head.weight"])
+
+    @torch.inference_mode()
+    def greedy(self, prompt: torch.Tensor, new_tokens: int, kv: PagedKV, start: list[int] | None = None,
+               forced: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor]:
+        """Prefill `prompt` [B][P], then decode. Returns (tokens [B][new], logits
+        [new][B][V] as fp32). Ties go to the smaller index (torch.argmax on CPU
+        returns the first maximum). With `forced` [B][new] the history follows
+        `forced` instead of the oracle's own argmax (teacher forcing)."""
+        batch, length = prompt.shape
+        start = list(start) if start is not None else [0] * batch
+        logits = self.forward(prompt, start, kv, last_only=True)[:, -1].float()
+        tokens, history = [], []
+        for step in range(new_tokens):
+            history.append(logits)
+            chosen = logits.argmax(-1)
+            tokens.append(chosen)
+            if step + 1 == new_tokens:
+                break
+            feed = forced[:, step].long() if forced is not None else chosen
+            position = [s + length + step for s in start]
+            logits = self.forward(feed.view(batch, 1).to(torch.int32), position, kv)[:, -1].float()
+        return torch.stack(tokens, dim=1).to(torch.int32), torch.stack(history)

@@ -1,0 +1,1002 @@
+// Persistent decode megakernel for sm_100a.
+//
+// One launch runs `nsteps` decode steps of a Llama-shaped decoder. Every CTA
+// (one per SM) has one streaming warp and eight arithmetic warps:
+//
+//  * the streaming warp walks the CTA's share of the whole step -- every weight
+//    page of every GEMV stage and every KV block group of every attention stage,
+//    in program order -- and copies it into a shared-memory ring with
+//    cp.async.bulk. It never waits for a stage boundary, only for a free ring
+//    slot, so HBM keeps streaming while the arithmetic warps sit in a grid
+//    barrier or stage their activations.
+//  * the arithmetic warps walk the same list, wait for the stage's inputs (a
+//    grid-wide arrival counter with release/acquire), stage the activation rows
+//    in shared memory (RMSNorm fused), and consume ring slots: 128-bit
+//    shared-memory loads, fp32 FMA, the rounding sites of the reference's
+//    epilogues.
+//
+// Stage list per layer (reference: include/tilemega/Codegen/tasks/
+// Sm90DenseProgram.cuh:903-939): qkv (RMSNorm fused) -> RoPE + KV append +
+// split-KV attention (+ last-arriver merge) -> o (+residual) -> gate/up
+// (RMSNorm, SwiGLU) -> down (+residual); after the last layer lm_head
+// (RMSNorm, bf16 logits, argmax partials) and the argmax reduction that also
+// feeds the next step's embedding.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "params.h"
+#include "ptx.cuh"
+
+namespace tmb {
+
+// ---------------------------------------------------------------------------
+// shared memory map (bytes)
+// ---------------------------------------------------------------------------
+constexpr int kOffFull = 0;
+constexpr int kOffEmpty = 64;
+constexpr int kOffCtl = 128;      // int[32]: [0] abort seen, [1] last-arriver flag
+constexpr int kOffTok = 256;      // int[8]
+constexpr int kOffBestVal = 288;  // float[8]
+constexpr int kOffBestIdx = 320;  // int[8]
+constexpr int kOffWsum = 384;     // float[8][8]
+constexpr int kOffRed = 640;      // float[2][8 warps][8 rows][kMaxBatch]
+constexpr int kOffSc = 4736;      // float[8 warps][4][16]
+constexpr int kOffXs = 6784;      // activation rows / attention scratch
+
+__host__ __device__ inline int ring_offset(int xs_bytes) { return (kOffXs + xs_bytes + 1023) & ~1023; }
+
+struct Ctx {
+  const MegaParams& p;
+  unsigned char* smem;
+  int warp, lane, tid;
+  uint32_t slot, phase;              // ring cursor
+  int deal;                          // round-robin cursor of the task dealer
+  unsigned long long bar_target;     // arrivals that complete the previous stage
+  uint32_t task_seq;                 // tasks finished by this CTA (epilogue warp rotation)
+  __device__ Ctx(const MegaParams& q, unsigned char* s)
+      : p(q), smem(s), warp(threadIdx.x >> 5), lane(threadIdx.x & 31), tid(threadIdx.x), slot(0), phase(0),
+        deal(0), bar_target(q.bar_base), task_seq(0) {}
+  __device__ uint64_t* full(int i) const { return reinterpret_cast<uint64_t*>(smem + kOffFull) + i; }
+  __device__ uint64_t* empty(int i) const { return reinterpret_cast<uint64_t*>(smem + kOffEmpty) + i; }
+  __device__ volatile int* ctl() const { return reinterpret_cast<volatile int*>(smem + kOffCtl); }
+  __device__ int* tok() const { return reinterpret_cast<int*>(smem + kOffTok); }
+  __device__ float* best_val() const { return reinterpret_cast<float*>(smem + kOffBestVal); }
+  __device__ int* best_idx() const { return reinterpret_cast<int*>(smem + kOffBestIdx); }
+  __device__ float* wsum() const { return reinterpret_cast<float*>(smem + kOffWsum); }
+  __device__ float* red() const { return reinterpret_cast<float*>(smem + kOffRed); }
+  __device__ float* sc() const { return reinterpret_cast<float*>(smem + kOffSc); }
+  __device__ unsigned char* xs() const { return smem + kOffXs; }
+  __device__ unsigned char* ring(int i) const { return smem + ring_offset(p.xs_bytes) + i * kSlotBytes; }
+  __device__ void advance() {
+    if (++slot == uint32_t(p.nslots)) { slot = 0; phase ^= 1u; }
+  }
+  __device__ int first_task() const { return (int(blockIdx.x) + p.grid - deal) % p.grid; }
+  __device__ void dealt(int ntasks) { deal = (deal + ntasks) % p.grid; }
+};
+
+// ---------------------------------------------------------------------------
+// bounded waits: no spin in this kernel is unbounded. A wait that exceeds
+// watchdog_ns records who waited for what (the 12 words the reference's
+// tm_plan_watchdog reports, include/tilemega/Codegen/executor/Watchdog.cuh:13-44)
+// and raises status[0]; every other wait sees status[0] and falls through, and
+// every CTA leaves at its next stage boundary. Nothing traps.
+// ---------------------------------------------------------------------------
+__device__ __noinline__ bool wait_give_up(const MegaParams& p, unsigned long long& t0, int site,
+                                          unsigned long long need, unsigned long long value) {
+  if (ld_relaxed(p.status + kStFired) != 0) return true;
+  const unsigned long long now = global_timer();
+  if (t0 == 0) {
+    t0 = now;
+    return false;
+  }
+  if (now - t0 <= p.watchdog_ns) return false;
+  if (atomicCAS(p.status + kStFired, 0ull, 1ull) == 0ull) {
+    p.status[kStSite] = site;
+    p.status[kStBlock] = blockIdx.x;
+    p.status[kStThread] = threadIdx.x;
+    p.status[kStNeed] = need;
+    p.status[kStValue] = value;
+    __threadfence();
+  }
+  return true;
+}
+
+__device__ __forceinline__ void mbar_wait(const MegaParams& p, uint64_t* bar, uint32_t parity, int site) {
+  if (mbar_try_wait(bar, parity)) return;
+  unsigned long long t0 = 0;
+  uint32_t polls = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++polls & 127u) == 0 && wait_give_up(p, t0, site, parity, polls)) return;
+  }
+}
+
+// Arrive on the grid-wide counter: this CTA's stage outputs are in global memory.
+__device__ __forceinline__ void grid_arrive(Ctx& c) {
+  consumer_sync();
+  if (c.tid == 0) {
+    __threadfence();
+    red_release_add(c.p.bar, 1ull);
+  }
+  c.bar_target += (unsigned long long)c.p.grid;
+}
+
+// Wait until every CTA arrived for the previous stage. Returns false when the
+// launch is being abandoned (uniform over the arithmetic warps).
+__device__ __forceinline__ bool grid_wait(Ctx& c) {
+  if (c.tid == 0) {
+    unsigned long long t0 = 0;
+    uint32_t polls = 0;
+    unsigned long long seen;
+    while ((seen = ld_acquire(c.p.bar)) < c.bar_target) {
+      if ((++polls & 63u) == 0 && wait_give_up(c.p, t0, kSiteGrid, c.bar_target, seen)) break;
+    }
+    c.ctl()[0] = ld_relaxed(c.p.status + kStFired) != 0 ? 1 : 0;
+  }
+  consumer_sync();
+  return c.ctl()[0] == 0;
+}
+
+// ---------------------------------------------------------------------------
+// attention partition (identical on the streaming and the arithmetic side)
+// ---------------------------------------------------------------------------
+struct AttnTask {
+  int b, g, c;       // sequence, KV head, chunk
+  int pos;           // position of the new token (= number of cached tokens)
+  int ns, nch;       // slots of the sequence, chunks per KV head
+  int slot0, slot1;  // slot range of this chunk
+  int task0;         // first task of (b, g)
+};
+
+__device__ __forceinline__ int seq_pos(const MegaParams& p, int past, int b) {
+  int pos = past + (p.ctx_base ? __ldg(p.ctx_base + b) : 0);
+  return min(max(pos, 0), p.capacity - 1);
+}
+
+// slots-per-task and task count for one attention stage
+__device__ __forceinline__ void attn_shape(const MegaParams& p, int past, int nk, int& spt, int& ntasks) {
+  int total = 0;
+  for (int b = 0; b < p.batch; ++b) total += (seq_pos(p, past, b) / nk + 1) * p.kv_heads;
+  spt = max(1, (total + p.grid - 1) / p.grid);
+  ntasks = 0;
+  for (int b = 0; b < p.batch; ++b) {
+    const int ns = seq_pos(p, past, b) / nk + 1;
+    ntasks += p.kv_heads * ((ns + spt - 1) / spt);
+  }
+}
+
+__device__ __forceinline__ AttnTask attn_task(const MegaParams& p, int past, int nk, int spt, int t) {
+  AttnTask a;
+  int base = 0;
+  for (int b = 0;; ++b) {
+    const int pos = seq_pos(p, past, b);
+    const int ns = pos / nk + 1;
+    const int nch = (ns + spt - 1) / spt;
+    const int n = p.kv_heads * nch;
+    if (t < base + n || b == p.batch - 1) {
+      const int r = t - base;
+      a.b = b;
+      a.g = r / nch;
+      a.c = r % nch;
+      a.pos = pos;
+      a.ns = ns;
+      a.nch = nch;
+      a.slot0 = a.c * spt;
+      a.slot1 = min(ns, a.slot0 + spt);
+      a.task0 = base + a.g * nch;
+      return a;
+    }
+    base += n;
+  }
+}
+
+__device__ __forceinline__ int table_entry(const MegaParams& p, int b, int blk) {
+  int e = __ldg(p.block_table + (long long)b * p.max_blocks + min(blk, p.max_blocks - 1));
+  return min(max(e, 0), p.kv_max_entry);
+}
+
+// ---------------------------------------------------------------------------
+// streaming warp
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void stream_gemv(Ctx& c, const GemvGeo& geo, const void* weights, uint64_t policy) {
+  const uint32_t page_bytes = uint32_t(kTileN) * uint32_t(geo.tile_k) * 2u;
+  const int kt = geo.k / geo.tile_k;
+  for (int t = c.first_task(); t < geo.ntasks; t += c.p.grid) {
+    const int rt = t / geo.ksplit, ks = t - rt * geo.ksplit;
+    const unsigned char* src = static_cast<const unsigned char*>(weights) +
+                               (size_t(rt) * kt + size_t(ks) * geo.pages_per_task) * page_bytes;
+    for (int pg = 0; pg < geo.pages_per_task; ++pg) {
+      mbar_wait(c.p, c.empty(c.slot), c.phase ^ 1u, kSiteEmpty);
+      if (c.lane == 0) {
+        mbar_expect_tx(c.full(c.slot), page_bytes);
+        bulk_g2s_hint(c.ring(c.slot), src + size_t(pg) * page_bytes, page_bytes, c.full(c.slot), policy);
+      }
+      c.advance();
+    }
+  }
+  c.dealt(geo.ntasks);
+}
+
+template <int D>
+__device__ __forceinline__ void stream_attn(Ctx& c, const LayerPtrs& lp, int past) {
+  constexpr int NK = kAttnHalfBytes / (2 * D);   // keys per slot
+  constexpr int NB = NK / kKvBlock;              // KV blocks per slot
+  constexpr uint32_t BLKB = kKvBlock * D * 2;    // bytes of one block of one head
+  int spt, ntasks;
+  attn_shape(c.p, past, NK, spt, ntasks);
+  for (int t = c.first_task(); t < ntasks; t += c.p.grid) {
+    const AttnTask a = attn_task(c.p, past, NK, spt, t);
+    const int nblk = a.pos / kKvBlock + 1;
+    for (int s = a.slot0; s < a.slot1; ++s) {
+      mbar_wait(c.p, c.empty(c.slot), c.phase ^ 1u, kSiteEmpty);
+      const int nb = min(NB, nblk - s * NB);
+      if (c.lane == 0) mbar_expect_tx(c.full(c.slot), uint32_t(nb) * 2u * BLKB);
+      __syncwarp();
+      if (c.lane < nb) {
+        const long long e = table_entry(c.p, a.b, s * NB + c.lane);
+        const long long off = (e * c.p.kv_block_stride + (long long)a.g * c.p.kv_head_stride) * 2;
+        unsigned char* dst = c.ring(c.slot) + c.lane * BLKB;
+        bulk_g2s(dst, static_cast<const unsigned char*>(lp.k_pool) + off, BLKB, c.full(c.slot));
+        bulk_g2s(dst + kAttnHalfBytes, static_cast<const unsigned char*>(lp.v_pool) + off, BLKB,
+                 c.full(c.slot));
+      }
+      c.advance();
+    }
+  }
+  c.dealt(ntasks);
+}
+
+template <int D>
+__device__ void streamer_main(Ctx& c) {
+  const MegaParams& p = c.p;
+  const uint64_t policy = policy_evict_first();
+  const unsigned long long bars_per_step = 5ull * p.layers + 1ull;
+  for (int si = 0; si < p.nsteps; ++si) {
+    const int past = __ldg(p.past + p.first_step + si);
+    // KV rows appended by the previous step were written with ordinary stores by
+    // other CTAs: take the previous step's last grid barrier before any bulk
+    // (async-proxy) read of the pools, then order the proxies.
+    bool kv_ordered = si == 0;
+    for (int l = 0; l < p.layers; ++l) {
+      const LayerPtrs lp = p.layer[l];
+      stream_gemv(c, p.geo[kQkv], lp.qkv, policy);
+      if (!kv_ordered) {
+        const unsigned long long need = p.bar_base + bars_per_step * (unsigned long long)si * p.grid;
+        unsigned long long t0 = 0, seen;
+        uint32_t polls = 0;
+        while ((seen = ld_acquire(p.bar)) < need) {
+          if ((++polls & 63u) == 0 && wait_give_up(p, t0, kSiteGrid, need, seen)) break;
+        }
+        fence_proxy_async();
+        kv_ordered = true;
+      }
+      stream_attn<D>(c, lp, past);
+      stream_gemv(c, p.geo[kOProj], lp.o, policy);
+      stream_gemv(c, p.geo[kGateUp], lp.gate_up, policy);
+      stream_gemv(c, p.geo[kDown], lp.down, policy);
+      if (ld_relaxed(p.status + kStFired) != 0) return;
+    }
+    stream_gemv(c, p.geo[kHead], p.lm_head, policy);
+  }
+}
+
+// Before the CTA may retire, every bulk copy this warp issued must have landed:
+// slots below the cursor were last filled in the current lap, the others in the
+// previous one (a never-used barrier reports its "previous" phase complete).
+__device__ __forceinline__ void streamer_drain(Ctx& c) {
+  for (int i = 0; i < c.p.nslots; ++i) {
+    const uint32_t parity = uint32_t(i) < c.slot ? c.phase : (c.phase ^ 1u);
+    unsigned long long t0 = 0;
+    uint32_t polls = 0;
+    while (!mbar_try_wait(c.full(i), parity)) {
+      if ((++polls & 127u) == 0) {
+        // keep waiting past an abort: only the time limit ends this loop
+        const unsigned long long now = global_timer();
+        if (t0 == 0) t0 = now;
+        else if (now - t0 > c.p.watchdog_ns) break;
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// arithmetic warps: GEMV
+// ---------------------------------------------------------------------------
+struct GemvIo {
+  const void* src;     // bf16 [B][k] activation rows (global), or embedding table when embed != 0
+  const void* norm;    // bf16 [k] RMSNorm weight, or null
+  int embed;           // rows are table[tok[b]] and are also copied into x
+  int epilogue;
+  void* out;           // kEpiStore: bf16 [B][n]; kEpiResidual: x; kEpiSwiGLU: h [B][n/2]; kEpiHead: logits
+};
+
+// Stage the stage's B activation rows in shared memory; RMSNorm fused:
+// y = bf16(w * bf16(x * rsqrt(mean(x^2) + eps)))  (python/tilemega/serving/export.py:24-27).
+template <int B>
+__device__ __forceinline__ void stage_rows(Ctx& c, const GemvIo& io, int k) {
+  const MegaParams& p = c.p;
+  const int chunks = k >> 3;
+  uint4* xs4 = reinterpret_cast<uint4*>(c.xs());
+  float ss[B];
+#pragma unroll
+  for (int b = 0; b < B; ++b) {
+    const uint4* src;
+    if (io.embed) {
+      const int tok = min(max(c.tok()[b], 0), p.vocab - 1);
+      src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(io.src) + size_t(tok) * k);
+    } else {
+      src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(io.src) + size_t(b) * k);
+    }
+    const bool own = io.embed && (b % p.grid) == int(blockIdx.x);
+    uint4* xg = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.x) + size_t(b) * k);
+    float acc = 0.f;
+    for (int i = c.tid; i < chunks; i += kConsumerThreads) {
+      const uint4 v = io.embed ? __ldg(src + i) : __ldcg(src + i);
+      xs4[b * chunks + i] = v;
+      if (own) xg[i] = v;
+      if (io.norm) {
+        float f[8];
+        unpack8(v, f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc = fmaf(f[j], f[j], acc);
+      }
+    }
+    ss[b] = acc;
+  }
+  if (io.norm) {
+#pragma unroll
+    for (int b = 0; b < B; ++b) {
+      float v = ss[b];
+#pragma unroll
+      for (int m = 16; m; m >>= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
+      if (c.lane == 0) c.wsum()[b * 8 + c.warp] = v;
+    }
+    consumer_sync();
+    const uint4* nw = reinterpret_cast<const uint4*>(io.norm);
+#pragma unroll
+    for (int b = 0; b < B; ++b) {
+      float total = 0.f;
+#pragma unroll
+      for (int w = 0; w < kConsumerWarps; ++w) total += c.wsum()[b * 8 + w];
+      const float inv = 1.0f / sqrtf(total / float(k) + p.eps);
+      for (int i = c.tid; i < chunks; i += kConsumerThreads) {
+        float f[8], w[8];
+        unpack8(xs4[b * chunks + i], f);
+        unpack8(__ldg(nw + i), w);
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint32_t lo = bf16_bits(w[2 * j] * bf16_round(f[2 * j] * inv));
+          const uint32_t hi = bf16_bits(w[2 * j + 1] * bf16_round(f[2 * j + 1] * inv));
+          o[j] = lo | (hi << 16);
+        }
+        xs4[b * chunks + i] = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+    }
+  }
+  consumer_sync();
+}
+
+// One page = 8 weight rows x 2048 columns, 128-byte swizzled in 8x64 atoms:
+// element (r, col) sits at 1024*(col/64) + 128*r + 16*((col%64/8) ^ r) + 2*(col%8)
+// bytes (python/tilemega/serving/weights.py:239-240 with tn = 8). Warp w owns
+// columns [256w, 256w+256), lane l the 8 columns 8l.. of that segment.
+template <int B>
+__device__ __forceinline__ void gemv_page(const unsigned char* page, const unsigned char* xs, int k,
+                                          int col0, int warp, int lane, float (&acc)[kTileN][B]) {
+  float xv[B][8];
+#pragma unroll
+  for (int b = 0; b < B; ++b) {
+    const uint4 v = *reinterpret_cast<const uint4*>(xs + (size_t(b) * k + col0 + 256 * warp + 8 * lane) * 2);
+    unpack8(v, xv[b]);
+  }
+  const unsigned char* pg = page + 1024 * (4 * warp + (lane >> 3));
+  const int sw = lane & 7;
+#pragma unroll
+  for (int r = 0; r < kTileN; ++r) {
+    float w[8];
+    unpack8(*reinterpret_cast<const uint4*>(pg + 128 * r + 16 * (sw ^ r)), w);
+#pragma unroll
+    for (int b = 0; b < B; ++b)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[r][b] = fmaf(w[j], xv[b][j], acc[r][b]);
+  }
+}
+
+// Sum 8 per-lane values over the 32 lanes of a warp with 9 shuffles: three
+// halving exchanges (lane bits 4,3,2 select the row) then two full exchanges.
+// On return lane l holds the total of row (l >> 2) in v[0].
+__device__ __forceinline__ void warp_reduce_rows(float (&v)[kTileN], int lane) {
+  {
+    const bool up = lane & 16;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float send = up ? v[i] : v[i + 4];
+      const float recv = __shfl_xor_sync(0xffffffffu, send, 16);
+      v[i] = (up ? v[i + 4] : v[i]) + recv;
+    }
+  }
+  {
+    const bool up = lane & 8;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const float send = up ? v[i] : v[i + 2];
+      const float recv = __shfl_xor_sync(0xffffffffu, send, 8);
+      v[i] = (up ? v[i + 2] : v[i]) + recv;
+    }
+  }
+  {
+    const bool up = lane & 4;
+    const float send = up ? v[0] : v[1];
+    const float recv = __shfl_xor_sync(0xffffffffu, send, 4);
+    v[0] = (up ? v[1] : v[0]) + recv;
+  }
+  v[0] += __shfl_xor_sync(0xffffffffu, v[0], 2);
+  v[0] += __shfl_xor_sync(0xffffffffu, v[0], 1);
+}
+
+__device__ __forceinline__ float silu_bf16(float g) {
+  // silu on a bf16 value, result rounded to bf16
+  // (include/tilemega/Backend/ServingEpilogue.h:49-57).
+  return bf16_round(g / (1.0f + expf(-g)));
+}
+
+template <int B>
+__device__ void gemv_stage(Ctx& c, const GemvGeo& geo, const GemvIo& io) {
+  const MegaParams& p = c.p;
+  stage_rows<B>(c, io, geo.k);
+  if (io.epilogue == kEpiHead && c.tid < B) {
+    c.best_val()[c.tid] = -INFINITY;
+    c.best_idx()[c.tid] = 0x7fffffff;
+  }
+  float* red = c.red();
+  for (int t = c.first_task(); t < geo.ntasks; t += p.grid) {
+    const int rt = t / geo.ksplit, ks = t - rt * geo.ksplit;
+    float acc[kTileN][B];
+#pragma unroll
+    for (int r = 0; r < kTileN; ++r)
+#pragma unroll
+      for (int b = 0; b < B; ++b) acc[r][b] = 0.f;
+    // the warp that will run this task's epilogue fetches the residual now, so the
+    // L2 round trip overlaps the page arithmetic instead of delaying the next task
+    float residual = 0.f;
+    if (io.epilogue == kEpiResidual && c.warp == int(c.task_seq & 7) && c.lane < kTileN * B)
+      residual = bf16_from_bits(__ldcg(reinterpret_cast<const unsigned short*>(io.out) +
+                                       size_t(c.lane >> 3) * geo.n + rt * kTileN + (c.lane & 7)));
+    const int page0 = ks * geo.pages_per_task;
+    for (int pg = 0; pg < geo.pages_per_task; ++pg) {
+      mbar_wait(p, c.full(c.slot), c.phase, kSiteFull);
+      gemv_page<B>(c.ring(c.slot), c.xs(), geo.k, (page0 + pg) * geo.tile_k, c.warp, c.lane, acc);
+      __syncwarp();
+      if (c.lane == 0) mbar_arrive(c.empty(c.slot));
+      c.advance();
+    }
+    // lanes -> warps -> (k-splits) in a fixed order, so results are run-to-run identical
+    const int buf = c.task_seq & 1;
+#pragma unroll
+    for (int b = 0; b < B; ++b) {
+      float v[kTileN];
+#pragma unroll
+      for (int r = 0; r < kTileN; ++r) v[r] = acc[r][b];
+      warp_reduce_rows(v, c.lane);
+      if ((c.lane & 3) == 0) red[((buf * 8 + c.warp) * 8 + (c.lane >> 2)) * kMaxBatch + b] = v[0];
+    }
+    consumer_sync();
+    if (c.warp == int(c.task_seq & 7) && c.lane < kTileN * B) {
+      // lane = b*8 + r; kTileN*B <= 32 lanes take part, `mask` names exactly them
+      constexpr unsigned mask = kTileN * B >= 32 ? 0xffffffffu : ((1u << (kTileN * B)) - 1u);
+      const int r = c.lane & 7, b = c.lane >> 3;
+      const int row = rt * kTileN + r;
+      float v = 0.f;
+#pragma unroll
+      for (int w = 0; w < kConsumerWarps; ++w) v += red[((buf * 8 + w) * 8 + r) * kMaxBatch + b];
+      bool apply = true;
+      if (geo.ksplit > 1) {
+        p.gemv_part[(size_t(ks) * B + b) * geo.n + row] = v;
+        __threadfence();
+        __syncwarp(mask);
+        unsigned old = 0;
+        if (c.lane == 0) {
+          old = atomicAdd(p.gemv_cnt + rt, 1u);
+          if (old == unsigned(geo.ksplit - 1)) atomicExch(p.gemv_cnt + rt, 0u);
+        }
+        old = __shfl_sync(mask, old, 0);
+        apply = old == unsigned(geo.ksplit - 1);
+        if (apply) {
+          __threadfence();
+          v = 0.f;
+          for (int s = 0; s < geo.ksplit; ++s) v += __ldcg(p.gemv_part + (size_t(s) * B + b) * geo.n + row);
+        }
+      }
+      const float vb = bf16_round(v);
+      if (io.epilogue == kEpiSwiGLU) {
+        // rows 0..3 of the page are gate rows, rows 4..7 the matching up rows
+        const float up = __shfl_down_sync(mask, vb, 4);
+        if (apply && r < 4) {
+          __nv_bfloat16* h = static_cast<__nv_bfloat16*>(io.out);
+          h[size_t(b) * (geo.n >> 1) + rt * 4 + r] = __float2bfloat16_rn(silu_bf16(vb) * up);
+        }
+      } else if (io.epilogue == kEpiHead) {
+        if (apply && p.write_logits)
+          static_cast<__nv_bfloat16*>(io.out)[size_t(b) * geo.n + row] = __float2bfloat16_rn(v);
+        // ties -> smaller index (include/tilemega/Backend/Sm90DenseEpilogue.h:166-184)
+        float bv = row < p.vocab ? vb : -INFINITY;
+        int bi = row;
+#pragma unroll
+        for (int m = 1; m < 8; m <<= 1) {
+          const float ov = __shfl_xor_sync(mask, bv, m);
+          const int oi = __shfl_xor_sync(mask, bi, m);
+          if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if (apply && r == 0 && (bv > c.best_val()[b] || (bv == c.best_val()[b] && bi < c.best_idx()[b]))) {
+          c.best_val()[b] = bv;
+          c.best_idx()[b] = bi;
+        }
+      } else if (apply) {
+        __nv_bfloat16* out = static_cast<__nv_bfloat16*>(io.out) + size_t(b) * geo.n + row;
+        if (io.epilogue == kEpiResidual) {
+          // bf16(float(bf16(acc)) + float(residual)) (ServingEpilogue.h:38-43)
+          *out = __float2bfloat16_rn(vb + residual);
+        } else {
+          *out = __float2bfloat16_rn(v);
+        }
+      }
+    }
+    ++c.task_seq;
+  }
+  c.dealt(geo.ntasks);
+}
+
+// ---------------------------------------------------------------------------
+// arithmetic warps: RoPE + KV append + split-KV decode attention
+// ---------------------------------------------------------------------------
+template <int N, int LPK>
+__device__ __forceinline__ void subgroup_reduce_scatter(float (&v)[N], int hl) {
+  // Halving exchange over the LPK lanes of a sub-group: afterwards lane hl holds
+  // the totals of values [hl*N/LPK, (hl+1)*N/LPK) in v[0..N/LPK).
+  int n = N;
+#pragma unroll
+  for (int m = LPK / 2; m >= 1; m >>= 1) {
+    const bool up = hl & m;
+    const int half = n / 2;
+#pragma unroll
+    for (int i = 0; i < N / 2; ++i) {
+      if (i < half) {
+        const float send = up ? v[i] : v[i + half];
+        const float recv = __shfl_xor_sync(0xffffffffu, send, m);
+        v[i] = (up ? v[i + half] : v[i]) + recv;
+      }
+    }
+    n = half;
+  }
+}
+
+template <int B, int D, int GQ>
+__device__ void attn_stage(Ctx& c, const LayerPtrs& lp, int past) {
+  constexpr int NK = kAttnHalfBytes / (2 * D);  // keys per slot: 64 (D=128) / 128 (D=64)
+  constexpr int LPK = D / 8;                    // lanes that share one key row
+  constexpr int KPW = 32 / LPK;                 // sub-groups per warp
+  constexpr int KSG = NK / (kConsumerWarps * KPW);  // keys per sub-group per slot (= 4)
+  constexpr int NV = KSG * GQ;                  // scores per sub-group per slot (= 16)
+  constexpr int PW = D + 2;                     // floats per (chunk, head) partial: acc, m, l
+  static_assert(KSG == 4 && NV == 16, "attention slot geometry");
+  const MegaParams& p = c.p;
+  const int hl = c.lane % LPK, sg = c.lane / LPK;
+  const int sgi = c.warp * KPW + sg;
+  float* qs = reinterpret_cast<float*>(c.xs());                          // [GQ][D] scaled, roped q
+  __nv_bfloat16* knew = reinterpret_cast<__nv_bfloat16*>(qs + GQ * D);   // [D] roped new key
+  __nv_bfloat16* vnew = knew + D;                                        // [D] new value
+  float* scratch = reinterpret_cast<float*>(vnew + D);                   // [8 warps][GQ][PW]
+  float* sc = c.sc() + (c.warp * 4 + sg) * 16;
+  const int qkv_width = (p.heads + 2 * p.kv_heads) * D;
+  const __nv_bfloat16* cosb = static_cast<const __nv_bfloat16*>(p.rope_cos);
+  const __nv_bfloat16* sinb = static_cast<const __nv_bfloat16*>(p.rope_sin);
+
+  int spt, ntasks;
+  attn_shape(p, past, NK, spt, ntasks);
+  for (int t = c.first_task(); t < ntasks; t += p.grid) {
+    const AttnTask a = attn_task(p, past, NK, spt, t);
+    const bool tail = a.c == a.nch - 1;  // this chunk holds the new token
+    // ---- q (GQ heads) and the new k: RoPE with bf16 tables, each product and the
+    // sum rounded to bf16 (include/tilemega/Codegen/tasks/FusedAttentionTaskBody.h:141-151)
+    const unsigned short* row = reinterpret_cast<const unsigned short*>(p.qkv) + size_t(a.b) * qkv_width +
+                                size_t(a.g) * (GQ + 2) * D;
+    long long new_off = 0;
+    if (tail) {
+      const long long e = table_entry(p, a.b, a.pos / kKvBlock);
+      new_off = e * p.kv_block_stride + (long long)a.g * p.kv_head_stride + (a.pos % kKvBlock) * D;
+    }
+    for (int e = c.tid; e < (GQ + 2) * D; e += kConsumerThreads) {
+      const int hh = e / D, d = e - hh * D;
+      const float xv = bf16_from_bits(__ldcg(row + e));
+      if (hh == GQ + 1) {
+        if (tail) {
+          vnew[d] = __float2bfloat16_rn(xv);
+          static_cast<__nv_bfloat16*>(lp.v_pool)[new_off + d] = __float2bfloat16_rn(xv);
+        }
+        continue;
+      }
+      if (hh == GQ && !tail) continue;
+      const int d2 = d < D / 2 ? d + D / 2 : d - D / 2;
+      const float xp = bf16_from_bits(__ldcg(row + hh * D + d2));
+      const float cs = __bfloat162float(cosb[size_t(a.pos) * D + d]);
+      const float sn = __bfloat162float(sinb[size_t(a.pos) * D + d]);
+      const float rot = d < D / 2 ? -xp : xp;
+      const float o = bf16_round(bf16_round(xv * cs) + bf16_round(rot * sn));
+      if (hh < GQ) {
+        qs[hh * D + d] = o * p.qk_scale_log2;
+      } else {
+        knew[d] = __float2bfloat16_rn(o);
+        static_cast<__nv_bfloat16*>(lp.k_pool)[new_off + d] = __float2bfloat16_rn(o);
+      }
+    }
+    if (tail) fence_proxy_async();
+    consumer_sync();
+    float q[GQ][8];
+#pragma unroll
+    for (int h = 0; h < GQ; ++h)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) q[h][j] = qs[h * D + hl * 8 + j];
+    float m[GQ], l[GQ], acc[GQ][8];
+#pragma unroll
+    for (int h = 0; h < GQ; ++h) {
+      m[h] = -INFINITY;
+      l[h] = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[h][j] = 0.f;
+    }
+    for (int s = a.slot0; s < a.slot1; ++s) {
+      mbar_wait(p, c.full(c.slot), c.phase, kSiteFull);
+      unsigned char* kbase = c.ring(c.slot);
+      unsigned char* vbase = kbase + kAttnHalfBytes;
+      if (tail && s == a.ns - 1) {
+        // the cache row of the new token is being written this step: take it from
+        // this CTA's own copy instead of whatever the bulk copy saw
+        const int r = a.pos - s * NK;
+        if (c.tid < D / 8) {
+          reinterpret_cast<uint4*>(kbase + size_t(r) * D * 2)[c.tid] = reinterpret_cast<const uint4*>(knew)[c.tid];
+        } else if (c.tid < D / 4) {
+          reinterpret_cast<uint4*>(vbase + size_t(r) * D * 2)[c.tid - D / 8] =
+              reinterpret_cast<const uint4*>(vnew)[c.tid - D / 8];
+        }
+        fence_proxy_async();   // generic writes into a slot the bulk engine refills later
+        consumer_sync();
+      }
+      const int nkeys = min(NK, a.pos + 1 - s * NK);
+      const int key0 = sgi * KSG;
+      {
+        // every sub-group runs the dot products (the shuffles below are warp-wide);
+        // rows past nkeys hold stale bytes and are masked by selection afterwards
+        float sv[NV];
+#pragma unroll
+        for (int kk = 0; kk < KSG; ++kk) {
+          float kf[8];
+          unpack8(*reinterpret_cast<const uint4*>(kbase + size_t(key0 + kk) * D * 2 + hl * 16), kf);
+#pragma unroll
+          for (int h = 0; h < GQ; ++h) {
+            float d0 = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) d0 = fmaf(q[h][j], kf[j], d0);
+            sv[kk * GQ + h] = d0;
+          }
+        }
+        subgroup_reduce_scatter<NV, LPK>(sv, hl);
+        // lane hl now owns NV/LPK consecutive scores; share all 16 through shared memory
+#pragma unroll
+        for (int i = 0; i < NV / LPK; ++i) sc[hl * (NV / LPK) + i] = sv[i];
+      }
+      __syncwarp();
+      if (key0 < nkeys) {
+        float pr[KSG][GQ];
+#pragma unroll
+        for (int kk = 0; kk < KSG; ++kk) {
+          const float4 s4 = *reinterpret_cast<const float4*>(sc + kk * 4);
+          const bool valid = key0 + kk < nkeys;
+          pr[kk][0] = valid ? s4.x : -INFINITY;
+          pr[kk][1] = valid ? s4.y : -INFINITY;
+          pr[kk][2] = valid ? s4.z : -INFINITY;
+          pr[kk][3] = valid ? s4.w : -INFINITY;
+        }
+#pragma unroll
+        for (int h = 0; h < GQ; ++h) {
+          float mn = m[h];
+#pragma unroll
+          for (int kk = 0; kk < KSG; ++kk) mn = fmaxf(mn, pr[kk][h]);
+          // key0 < nkeys, so at least one score is finite and mn is finite
+          const float alpha = ex2(m[h] - mn);
+          m[h] = mn;
+          float sum = 0.f;
+#pragma unroll
+          for (int kk = 0; kk < KSG; ++kk) {
+            pr[kk][h] = ex2(pr[kk][h] - mn);
+            sum += pr[kk][h];
+          }
+          l[h] = fmaf(l[h], alpha, sum);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[h][j] *= alpha;
+        }
+#pragma unroll
+        for (int kk = 0; kk < KSG; ++kk) {
+          if (key0 + kk < nkeys) {
+            float vf[8];
+            unpack8(*reinterpret_cast<const uint4*>(vbase + size_t(key0 + kk) * D * 2 + hl * 16), vf);
+#pragma unroll
+            for (int h = 0; h < GQ; ++h)
+#pragma unroll
+              for (int j = 0; j < 8; ++j) acc[h][j] = fmaf(pr[kk][h], vf[j], acc[h][j]);
+          }
+        }
+      }
+      __syncwarp();
+      if (c.lane == 0) mbar_arrive(c.empty(c.slot));
+      c.advance();
+    }
+    // ---- merge the sub-groups of a warp with shuffles, then the warps through scratch
+#pragma unroll
+    for (int mask = LPK; mask < 32; mask <<= 1) {
+#pragma unroll
+      for (int h = 0; h < GQ; ++h) {
+        const float mo = __shfl_xor_sync(0xffffffffu, m[h], mask);
+        const float lo = __shfl_xor_sync(0xffffffffu, l[h], mask);
+        const float mx = fmaxf(m[h], mo);
+        const float ms = mx == -INFINITY ? 0.f : mx;
+        const float wa = ex2(m[h] - ms), wb = ex2(mo - ms);
+        l[h] = l[h] * wa + lo * wb;
+        m[h] = mx;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float ao = __shfl_xor_sync(0xffffffffu, acc[h][j], mask);
+          acc[h][j] = acc[h][j] * wa + ao * wb;
+        }
+      }
+    }
+    if (sg == 0) {
+#pragma unroll
+      for (int h = 0; h < GQ; ++h) {
+        float* dst = scratch + (c.warp * GQ + h) * PW;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) dst[hl * 8 + j] = acc[h][j];
+        if (hl == 0) {
+          dst[D] = m[h];
+          dst[D + 1] = l[h];
+        }
+      }
+    }
+    consumer_sync();
+    __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.attn) + size_t(a.b) * p.heads * D + size_t(a.g) * GQ * D;
+    float* part = p.attn_part + size_t(t) * GQ * PW;
+    for (int o = c.tid; o < GQ * D; o += kConsumerThreads) {
+      const int h = o / D, d = o - h * D;
+      float mx = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < kConsumerWarps; ++w) mx = fmaxf(mx, scratch[(w * GQ + h) * PW + D]);
+      const float ms = mx == -INFINITY ? 0.f : mx;
+      float ls = 0.f, as = 0.f;
+#pragma unroll
+      for (int w = 0; w < kConsumerWarps; ++w) {
+        const float* src = scratch + (w * GQ + h) * PW;
+        const float wgt = ex2(src[D] - ms);
+        ls = fmaf(src[D + 1], wgt, ls);
+        as = fmaf(src[d], wgt, as);
+      }
+      if (a.nch == 1) {
+        out[o] = __float2bfloat16_rn(as / ls);
+      } else {
+        part[h * PW + d] = as;
+        if (d == 0) {
+          part[h * PW + D] = mx;
+          part[h * PW + D + 1] = ls;
+        }
+      }
+    }
+    if (a.nch > 1) {
+      // last arriver of (sequence, KV head) merges the chunks in chunk order
+      // (include/tilemega/Backend/Sm90DenseAttentionBody.cuh:359-363,409-446)
+      __threadfence();
+      consumer_sync();
+      if (c.tid == 0) {
+        unsigned* cnt = p.attn_cnt + a.b * p.kv_heads + a.g;
+        const unsigned old = atomicAdd(cnt, 1u);
+        const int last = old == unsigned(a.nch - 1);
+        if (last) atomicExch(cnt, 0u);
+        c.ctl()[1] = last;
+      }
+      consumer_sync();
+      if (c.ctl()[1]) {
+        __threadfence();
+        const float* parts = p.attn_part + size_t(a.task0) * GQ * PW;
+        for (int o = c.tid; o < GQ * D; o += kConsumerThreads) {
+          const int h = o / D, d = o - h * D;
+          float mx = -INFINITY;
+          for (int ch = 0; ch < a.nch; ++ch) mx = fmaxf(mx, __ldcg(parts + (size_t(ch) * GQ + h) * PW + D));
+          float ls = 0.f, as = 0.f;
+          for (int ch = 0; ch < a.nch; ++ch) {
+            const float* src = parts + (size_t(ch) * GQ + h) * PW;
+            const float wgt = ex2(__ldcg(src + D) - mx);
+            ls = fmaf(__ldcg(src + D + 1), wgt, ls);
+            as = fmaf(__ldcg(src + d), wgt, as);
+          }
+          out[o] = __float2bfloat16_rn(as / ls);
+        }
+      }
+      consumer_sync();
+    }
+    ++c.task_seq;
+  }
+  c.dealt(ntasks);
+}
+
+// ---------------------------------------------------------------------------
+// arithmetic warps: one decode step after another
+// ---------------------------------------------------------------------------
+template <int B, int D, int GQ>
+__device__ void consumer_main(Ctx& c) {
+  const MegaParams& p = c.p;
+  for (int si = 0; si < p.nsteps; ++si) {
+    const int step = p.first_step + si;
+    const int past = __ldg(p.past + step);
+    if (si == 0) {
+      // the first step reads its token ids from the token state; later steps
+      // carry them over from the argmax reduction below
+      if (c.tid < B) c.tok()[c.tid] = __ldcg(p.tokens + size_t(c.tid) * p.capacity + seq_pos(p, past, c.tid));
+      consumer_sync();
+    }
+    if (blockIdx.x == 0 && c.tid == 0) p.step_ns[step] = global_timer();
+    for (int l = 0; l < p.layers; ++l) {
+      const LayerPtrs lp = p.layer[l];
+      GemvIo io;
+      // qkv: RMSNorm fused; layer 0 reads the embedding rows and seeds the residual stream
+      if (l > 0) {
+        if (!grid_wait(c)) return;
+      }
+      io = GemvIo{l == 0 ? p.embed : p.x, lp.norm1, l == 0, kEpiStore, p.qkv};
+      gemv_stage<B>(c, p.geo[kQkv], io);
+      grid_arrive(c);
+      if (!grid_wait(c)) return;
+      attn_stage<B, D, GQ>(c, lp, past);
+      grid_arrive(c);
+      if (!grid_wait(c)) return;
+      io = GemvIo{p.attn, nullptr, 0, kEpiResidual, p.x};
+      gemv_stage<B>(c, p.geo[kOProj], io);
+      grid_arrive(c);
+      if (!grid_wait(c)) return;
+      io = GemvIo{p.x, lp.norm2, 0, kEpiSwiGLU, p.h};
+      gemv_stage<B>(c, p.geo[kGateUp], io);
+      grid_arrive(c);
+      if (!grid_wait(c)) return;
+      io = GemvIo{p.h, nullptr, 0, kEpiResidual, p.x};
+      gemv_stage<B>(c, p.geo[kDown], io);
+      grid_arrive(c);
+    }
+    if (!grid_wait(c)) return;
+    GemvIo io{p.x, p.final_norm, 0, kEpiHead, p.logits};
+    gemv_stage<B>(c, p.geo[kHead], io);
+    consumer_sync();
+    if (c.tid < B) {
+      p.argmax_val[size_t(blockIdx.x) * B + c.tid] = c.best_val()[c.tid];
+      p.argmax_idx[size_t(blockIdx.x) * B + c.tid] = c.best_idx()[c.tid];
+    }
+    grid_arrive(c);
+    if (!grid_wait(c)) return;
+    // every CTA reduces the per-CTA candidates itself: it needs the token for the
+    // next step's embedding, and CTA 0 records it
+    // (include/tilemega/Backend/Sm90DenseHead.cuh:48-135; ties -> smaller index)
+    if (c.warp < B) {
+      const int b = c.warp;
+      float bv = -INFINITY;
+      int bi = 0x7fffffff;
+      for (int g = c.lane; g < p.grid; g += 32) {
+        const float v = __ldcg(p.argmax_val + size_t(g) * B + b);
+        const int i = __ldcg(p.argmax_idx + size_t(g) * B + b);
+        if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+      }
+#pragma unroll
+      for (int mk = 16; mk; mk >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, mk);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, mk);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+      }
+      if (c.lane == 0) {
+        const int pos = seq_pos(p, past, b);
+        int* slot = p.tokens + size_t(b) * p.capacity + min(pos + 1, p.capacity - 1);
+        int tok = min(max(bi, 0), p.vocab - 1);
+        if (pos + 1 < p.prompt_len) {
+          tok = __ldcg(slot);   // teacher-forced prompt position: the token state wins
+        } else if (blockIdx.x == 0 && pos + 1 < p.capacity) {
+          *slot = tok;
+        }
+        c.tok()[b] = tok;
+      }
+    }
+    if (blockIdx.x == 0 && c.tid == 0) p.step_ns[step + 1] = global_timer();
+    consumer_sync();
+  }
+}
+
+template <int B, int D, int GQ>
+__global__ void __launch_bounds__(kThreads, 1) decode_megakernel(const __grid_constant__ MegaParams p) {
+  extern __shared__ __align__(1024) unsigned char smem[];
+  Ctx c(p, smem);
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < p.nslots; ++i) {
+      mbar_init(c.full(i), 1);
+      mbar_init(c.empty(i), kConsumerWarps);
+    }
+    mbar_fence_init();
+    c.ctl()[0] = 0;
+    c.ctl()[1] = 0;
+  }
+  __syncthreads();
+  if (c.warp == kConsumerWarps) {
+    streamer_main<D>(c);
+    streamer_drain(c);
+  } else {
+    consumer_main<B, D, GQ>(c);
+  }
+}
+
+// A two-CTA toy that exercises the bounded-wait path without hanging anything:
+// CTA 1 waits for an arrival CTA 0 is told to withhold; the wait gives up after
+// watchdog_ns, records the site and both CTAs return normally.
+__global__ void watchdog_probe_kernel(MegaParams p, int withhold) {
+  if (threadIdx.x != 0) return;
+  if (blockIdx.x == 0) {
+    if (!withhold) red_release_add(p.bar, 1ull);
+    return;
+  }
+  unsigned long long t0 = 0, seen;
+  uint32_t polls = 0;
+  while ((seen = ld_acquire(p.bar)) < p.bar_base + 1) {
+    if ((++polls & 63u) == 0 && wait_give_up(p, t0, kSiteTest, p.bar_base + 1, seen)) break;
+  }
+}
+
+template <int B, int D, int GQ>
+static cudaError_t launch_instance(const MegaParams& p, size_t smem_bytes, cudaStream_t stream) {
+  auto kernel = decode_megakernel<B, D, GQ>;
+  cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem_bytes));
+  if (err != cudaSuccess) return err;
+  int resident = 0;
+  err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, kernel, kThreads, smem_bytes);
+  if (err != cudaSuccess) return err;
+  int device = 0, sms = 0;
+  cudaGetDevice(&device);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+  // liveness: every CTA of the grid must be resident at once
+  // (include/tilemega/Codegen/tasks/Sm90DenseRuntime.cuh:304-308)
+  if (resident < 1 || p.grid > sms * resident) return cudaErrorLaunchOutOfResources;
+  kernel<<<p.grid, kThreads, smem_bytes, stream>>>(p);
+  return cudaGetLastError();
+}
+
+template <int D, int GQ>
+static cudaError_t launch_batch(const MegaParams& p, size_t smem_bytes, cudaStream_t stream) {
+  switch (p.batch) {
+    case 1: return launch_instance<1, D, GQ>(p, smem_bytes, stream);
+    case 2: return launch_instance<2, D, GQ>(p, smem_bytes, stream);
+    case 3: return launch_instance<3, D, GQ>(p, smem_bytes, stream);
+    case 4: return launch_instance<4, D, GQ>(p, smem_bytes, stream);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+}  // namespace tmb
+
+extern "C" int tmb_smem_bytes(const tmb::MegaParams* p) {
+  return tmb::ring_offset(p->xs_bytes) + p->nslots * tmb::kSlotBytes;
+}
+
+extern "C" int tmb_launch_decode(const tmb::MegaParams* p, void* stream) {
+  const size_t smem_bytes = size_t(tmb_smem_bytes(p));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int gq = p->heads / p->kv_heads;
+  if (gq != 4) return int(cudaErrorInvalidValue);
+  if (p->head_dim == 128) return int(tmb::launch_batch<128, 4>(*p, smem_bytes, s));
+  if (p->head_dim == 64) return int(tmb::launch_batch<64, 4>(*p, smem_bytes, s));
+  return int(cudaErrorInvalidValue);
+}
+
+extern "C" int tmb_launch_watchdog_probe(const tmb::MegaParams* p, int withhold, void* stream) {
+  tmb::watchdog_probe_kernel<<<2, 32, 0, static_cast<cudaStream_t>(stream)>>>(*p, withhold);
+  return int(cudaGetLastError());
+}

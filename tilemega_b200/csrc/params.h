@@ -1,0 +1,105 @@
+// Structures shared by the host runtime and the persistent decode kernel.
+// Plain C++ (no CUDA types) so the host side can be unit-tested without a GPU.
+#pragma once
+#include <stdint.h>
+
+namespace tmb {
+
+constexpr int kConsumerWarps = 8;                       // warps that do arithmetic
+constexpr int kConsumerThreads = kConsumerWarps * 32;   // 256
+constexpr int kThreads = kConsumerThreads + 32;         // + one streaming warp
+constexpr int kSlotBytes = 32768;                       // one ring slot = one weight page / KV group
+constexpr int kMaxSlots = 6;
+constexpr int kTileN = 8;                               // weight rows per page (one 128B-swizzle atom)
+constexpr int kKvBlock = 16;                            // tokens per KV block
+constexpr int kMaxBatch = 8;                            // SIMT GEMV path
+constexpr int kAttnHalfBytes = kSlotBytes / 2;          // K part, then V part, of an attention slot
+
+enum StageKind : int { kQkv = 0, kOProj = 1, kGateUp = 2, kDown = 3, kHead = 4, kNumGemv = 5 };
+enum Epilogue : int { kEpiStore = 0, kEpiResidual = 1, kEpiSwiGLU = 2, kEpiHead = 3 };
+
+// Geometry of one GEMV stage. Weights are packed [N/8][K/tile_k][8*tile_k]
+// with the 8x64 128-byte XOR swizzle of the reference's tile_pages recipe
+// (python/tilemega/serving/weights.py:204-242), so one page is one contiguous
+// bulk copy.
+struct GemvGeo {
+  int n, k;            // output rows, reduction length
+  int tile_k;          // columns per page; multiple of 256*? (see kernel)
+  int ksplit;          // tasks per row tile; partial sums merged by the last arriver
+  int pages_per_task;  // k / tile_k / ksplit
+  int ntasks;          // (n / 8) * ksplit
+};
+
+struct LayerPtrs {
+  const void* qkv;       // packed pages, rows group-interleaved [Gq q heads][k][v] per KV head
+  const void* o;
+  const void* gate_up;   // packed pages, rows interleaved 4 gate / 4 up
+  const void* down;
+  const void* norm1;     // bf16 [H]
+  const void* norm2;     // bf16 [H]
+  void* k_pool;          // bf16, addressed by block table
+  void* v_pool;
+};
+
+// Status words written by the device (index into MegaParams::status).
+enum StatusWord : int {
+  kStFired = 0, kStSite, kStBlock, kStThread, kStStage, kStTask, kStProducer,
+  kStGroup, kStRow, kStNeed, kStValue, kStIteration, kStWords
+};
+enum WaitSite : int { kSiteGrid = 1, kSiteFull = 2, kSiteEmpty = 3, kSiteDrain = 4, kSiteTest = 5 };
+
+struct MegaParams {
+  // model
+  int batch, hidden, inter, heads, kv_heads, head_dim, layers, vocab;
+  float eps;
+  float qk_scale_log2;      // log2(e) / sqrt(head_dim)
+  // request state
+  int capacity, max_blocks; // tokens per sequence; block-table row length
+  int kv_max_entry;         // block-table entries are clamped to [0, kv_max_entry]
+  long long kv_block_stride, kv_head_stride;   // elements
+  int first_step, nsteps, prompt_len;
+  int write_logits;
+  int grid, nslots, xs_bytes;
+  unsigned long long bar_base;     // grid-barrier arrivals before this launch
+  unsigned long long watchdog_ns;  // per-wait limit
+  GemvGeo geo[kNumGemv];
+  // external buffers
+  int* tokens;                 // [B][capacity]
+  const void* rope_cos;        // bf16 [capacity][D]
+  const void* rope_sin;
+  const int* block_table;      // [B][max_blocks]
+  const int* ctx_base;         // [B] position offset of each sequence (may be null)
+  const int* past;             // [steps] position run by each step
+  const void* embed;           // bf16 [V][H]
+  const void* final_norm;      // bf16 [H]
+  const void* lm_head;         // packed pages [V/8][H/tile_k][8*tile_k]
+  const LayerPtrs* layer;      // [L]
+  // internal buffers
+  void* x;                     // bf16 [B][H] residual stream
+  void* qkv;                   // bf16 [B][(Hq+2Hkv)*D]
+  void* attn;                  // bf16 [B][Hq*D]
+  void* h;                     // bf16 [B][I]
+  void* logits;                // bf16 [B][V]
+  float* gemv_part;            // [ksplit_max][B][Nmax] partial sums
+  unsigned* gemv_cnt;          // [Nmax/8]
+  float* attn_part;            // [grid + B*Hkv][Gq][D+2]
+  unsigned* attn_cnt;          // [B*Hkv]
+  float* argmax_val;           // [grid][B]
+  int* argmax_idx;             // [grid][B]
+  unsigned long long* bar;     // grid barrier arrivals (monotonic)
+  unsigned long long* status;  // [kStWords]
+  unsigned long long* step_ns; // [capacity+1] %globaltimer stamps
+};
+
+// Per-step, per-sequence attention partition shared by the streaming warp and
+// the arithmetic warps (both must enumerate exactly the same slots).
+struct AttnSeq {
+  int pos;        // position of the new token
+  int nslots;     // ring slots covering positions [0, pos]
+  int nchunks;    // tasks per KV head
+  int task_base;  // first task index of this sequence
+};
+
+static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+}  // namespace tmb

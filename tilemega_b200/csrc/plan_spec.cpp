@@ -1,0 +1,172 @@
+#include "plan_spec.h"
+
+#include <algorithm>
+#include <stdexcept>
+
+namespace tmb {
+
+namespace {
+
+std::string Sources(std::initializer_list<std::string> names) {
+  std::string out = "[";
+  bool first = true;
+  for (const auto& name : names) {
+    if (!first) out += ',';
+    out += Json::Quote(name);
+    first = false;
+  }
+  return out + "]";
+}
+
+std::string Alias(const std::string& fqn) { return "{\"kind\":\"alias\",\"source\":" + Json::Quote(fqn) + "}"; }
+
+// The reference's tile_pages recipe (python/tilemega/serving/weights.py:204-242):
+// [N/tile_n][K/tile_k][tile_n*tile_k] with the 8x64 128-byte XOR swizzle.
+std::string Pages(const std::string& source, int tile_k) {
+  return "{\"kind\":\"tile_pages\",\"tile_n\":" + std::to_string(kTileN) + ",\"tile_k\":" + std::to_string(tile_k) +
+         ",\"source\":" + source + "}";
+}
+
+GemvGeo MakeGeo(const char* what, int n, int k, const Json& overrides) {
+  GemvGeo g{};
+  g.n = n;
+  g.k = k;
+  g.tile_k = 2048;
+  g.ksplit = 1;
+  if (overrides.has(what)) {
+    g.tile_k = int(overrides.at(what).integer("tile_k", g.tile_k));
+    g.ksplit = int(overrides.at(what).integer("ksplit", g.ksplit));
+  }
+  if (g.tile_k != 2048) throw std::invalid_argument(std::string(what) + ": tile_k must be 2048");
+  if (n <= 0 || n % kTileN) throw std::invalid_argument(std::string(what) + ": rows must be a multiple of 8");
+  if (k <= 0 || k % g.tile_k) throw std::invalid_argument(std::string(what) + ": K must be a multiple of tile_k");
+  const int kt = k / g.tile_k;
+  if (g.ksplit < 1 || kt % g.ksplit) throw std::invalid_argument(std::string(what) + ": ksplit must divide K/tile_k");
+  g.pages_per_task = kt / g.ksplit;
+  g.ntasks = (n / kTileN) * g.ksplit;
+  return g;
+}
+
+}  // namespace
+
+int PlanSpec::max_k() const { return std::max({hidden, inter, heads * head_dim}); }
+
+uint64_t PlanSpec::weight_bytes() const {
+  uint64_t total = 0;
+  for (int s = 0; s < kNumGemv; ++s) {
+    const uint64_t one = 2ull * uint64_t(geo[s].n) * uint64_t(geo[s].k);
+    total += s == kHead ? one : one * uint64_t(layers);
+  }
+  return total;
+}
+
+PlanSpec PlanSpec::FromJson(const Json& plan) {
+  PlanSpec s;
+  if (plan.str("phase", "decode") != "decode") throw std::invalid_argument("only decode plans are built");
+  const Json& model = plan.at("model");
+  s.hidden = int(model.integer("hidden_size", 0));
+  s.inter = int(model.integer("intermediate_size", 0));
+  s.heads = int(model.integer("num_attention_heads", 0));
+  s.kv_heads = int(model.integer("num_key_value_heads", 0));
+  s.layers = int(model.integer("num_hidden_layers", 0));
+  s.vocab = int(model.integer("vocab_size", 0));
+  s.head_dim = int(model.integer("head_dim", s.heads ? s.hidden / s.heads : 0));
+  s.eps = model.num("rms_norm_eps", 1e-5);
+  s.tied = model.flag("tie_word_embeddings", false);
+  if (s.hidden <= 0 || s.inter <= 0 || s.heads <= 0 || s.kv_heads <= 0 || s.layers <= 0 || s.vocab <= 0)
+    throw std::invalid_argument("model dimensions must be positive");
+  if (s.head_dim != 64 && s.head_dim != 128) throw std::invalid_argument("head_dim must be 64 or 128");
+  if (s.heads % s.kv_heads || s.heads / s.kv_heads != 4)
+    throw std::invalid_argument("query heads per KV head must be 4");
+  s.batch_lo = int(plan.integer("batch_lo", 1));
+  s.batch_hi = int(plan.integer("batch_hi", s.batch_lo));
+  s.capacity = int(plan.integer("capacity", 0));
+  if (s.batch_lo < 1 || s.batch_hi < s.batch_lo || s.batch_hi > 4)
+    throw std::invalid_argument("batch interval must lie in [1, 4]");
+  if (s.capacity < 2 || s.capacity % kKvBlock) throw std::invalid_argument("capacity must be a positive multiple of 16");
+  const Json empty;
+  const Json& kv = plan.has("kv") ? plan.at("kv") : empty;
+  const std::string layout = kv.str("layout", "contiguous");
+  if (layout != "contiguous" && layout != "paged") throw std::invalid_argument("kv.layout must be contiguous or paged");
+  s.paged = layout == "paged";
+  s.max_blocks = s.capacity / kKvBlock;
+  if (s.paged) {
+    s.num_blocks = int(kv.integer("num_blocks", 0));
+    if (s.num_blocks < 1) throw std::invalid_argument("kv.num_blocks must be positive for a paged plan");
+  }
+  s.grid = int(plan.integer("grid", 0));
+  s.slots = int(plan.integer("slots", 0));
+  s.write_logits = plan.flag("write_logits", true);
+  const Json& geometry = plan.has("geometry") ? plan.at("geometry") : empty;
+  s.geo[kQkv] = MakeGeo("qkv", s.qkv_rows(), s.hidden, geometry);
+  s.geo[kOProj] = MakeGeo("o", s.hidden, s.heads * s.head_dim, geometry);
+  s.geo[kGateUp] = MakeGeo("gate_up", 2 * s.inter, s.hidden, geometry);
+  s.geo[kDown] = MakeGeo("down", s.hidden, s.inter, geometry);
+  s.geo[kHead] = MakeGeo("lm_head", s.vocab, s.hidden, geometry);
+
+  auto add = [&](std::string name, uint32_t role, uint32_t dtype, uint64_t constant, uint64_t per_batch,
+                 std::string recipe) {
+    BufferSpec b;
+    b.name = std::move(name);
+    b.role = role;
+    b.dtype = dtype;
+    b.elements_constant = constant;
+    b.elements_per_batch = per_batch;
+    b.pack_json = std::move(recipe);
+    s.buffers.push_back(std::move(b));
+    return int(s.buffers.size()) - 1;
+  };
+  const uint64_t H = s.hidden, D = s.head_dim, V = s.vocab, I = s.inter;
+  s.tokens = add("serving.tokens", 1, 2, 0, s.capacity, "");
+  s.rope_cos = add("serving.rope_cos", 1, 0, uint64_t(s.capacity) * D, 0, "");
+  s.rope_sin = add("serving.rope_sin", 1, 0, uint64_t(s.capacity) * D, 0, "");
+  if (s.paged) {
+    s.block_table = add("serving.block_table", 1, 2, 0, s.max_blocks, "");
+    s.context_base = add("serving.context_base", 1, 2, 0, 1, "");
+  }
+  s.embed = add("model.embed_tokens.weight", 1, 0, V * H, 0, Alias("model.embed_tokens.weight"));
+  s.hidden_buf = add("serving.hidden", 0, 0, 0, H, "");
+  s.qkv_buf = add("serving.qkv", 0, 0, 0, uint64_t(s.qkv_rows()), "");
+  s.attn_buf = add("serving.attention", 0, 0, 0, uint64_t(s.heads) * D, "");
+  s.mlp_buf = add("serving.mlp", 0, 0, 0, I, "");
+  s.logits_buf = add("serving.logits", 0, 0, 0, V, "");
+  for (int l = 0; l < s.layers; ++l) {
+    const std::string p = "l" + std::to_string(l) + ".";
+    const std::string m = "model.layers." + std::to_string(l) + ".";
+    LayerBuffers lb{};
+    lb.norm1 = add(p + "norm1.weight", 1, 0, H, 0, Alias(m + "input_layernorm.weight"));
+    const std::string qkv_source =
+        "{\"kind\":\"qkv_group_interleave\",\"sources\":" +
+        Sources({m + "self_attn.q_proj.weight", m + "self_attn.k_proj.weight", m + "self_attn.v_proj.weight"}) +
+        ",\"hkv\":" + std::to_string(s.kv_heads) + ",\"qperkv\":" + std::to_string(s.heads / s.kv_heads) +
+        ",\"head_dim\":" + std::to_string(s.head_dim) + "}";
+    lb.qkv = add(p + "qkv.weight", 1, 0, uint64_t(s.geo[kQkv].n) * s.geo[kQkv].k, 0,
+                 Pages(qkv_source, s.geo[kQkv].tile_k));
+    if (s.paged) {
+      const uint64_t pool = uint64_t(s.num_blocks) * s.kv_heads * kKvBlock * D;
+      lb.k = add("kv_pool.k." + std::to_string(l), 1, 0, pool, 0, "");
+      lb.v = add("kv_pool.v." + std::to_string(l), 1, 0, pool, 0, "");
+    } else {
+      const uint64_t cache = uint64_t(s.kv_heads) * s.capacity * D;
+      lb.k = add("kv_cache.k." + std::to_string(l), 1, 0, 0, cache, "");
+      lb.v = add("kv_cache.v." + std::to_string(l), 1, 0, 0, cache, "");
+    }
+    lb.o = add(p + "o.weight", 1, 0, uint64_t(s.geo[kOProj].n) * s.geo[kOProj].k, 0,
+               Pages(Alias(m + "self_attn.o_proj.weight"), s.geo[kOProj].tile_k));
+    lb.norm2 = add(p + "norm2.weight", 1, 0, H, 0, Alias(m + "post_attention_layernorm.weight"));
+    const std::string gate_up_source = "{\"kind\":\"gate_up_interleave\",\"sources\":" +
+                                       Sources({m + "mlp.gate_proj.weight", m + "mlp.up_proj.weight"}) +
+                                       ",\"u\":4}";
+    lb.gate_up = add(p + "gate_up.weight", 1, 0, uint64_t(s.geo[kGateUp].n) * s.geo[kGateUp].k, 0,
+                     Pages(gate_up_source, s.geo[kGateUp].tile_k));
+    lb.down = add(p + "down.weight", 1, 0, uint64_t(s.geo[kDown].n) * s.geo[kDown].k, 0,
+                  Pages(Alias(m + "mlp.down_proj.weight"), s.geo[kDown].tile_k));
+    s.layer.push_back(lb);
+  }
+  s.final_norm = add("model.norm.weight", 1, 0, H, 0, Alias("model.norm.weight"));
+  s.lm_head = add("lm_head.weight", 1, 0, uint64_t(s.geo[kHead].n) * s.geo[kHead].k, 0,
+                  Pages(Alias("lm_head.weight"), s.geo[kHead].tile_k));
+  return s;
+}
+
+}  // namespace tmb

@@ -1,0 +1,60 @@
+// Host-side description of one plan: model dimensions, request geometry, the
+// buffer table with its packing recipes, and the GEMV page geometry. This is the
+// part of the reference's code generator output that the runtime needs
+// (lib/Frontend/ModelPlan.cpp:1005-1100 buffer names and recipes;
+// lib/Codegen/Codegen.cpp:2164-2615 tables), written by hand instead of emitted.
+#pragma once
+#include <stdint.h>
+
+#include <string>
+#include <vector>
+
+#include "json.h"
+#include "params.h"
+
+namespace tmb {
+
+struct BufferSpec {
+  std::string name;
+  uint32_t role = 0;   // 0 internal, 1 external
+  uint32_t dtype = 0;  // 0 bf16, 1 f32, 2 i32
+  uint64_t elements_constant = 0, elements_per_batch = 0;
+  std::string pack_json;
+};
+
+// Index of the buffers the runtime binds, into PlanSpec::buffers.
+struct LayerBuffers {
+  int norm1, qkv, k, v, o, norm2, gate_up, down;
+};
+
+struct PlanSpec {
+  // model
+  int hidden = 0, inter = 0, heads = 0, kv_heads = 0, head_dim = 0, layers = 0, vocab = 0;
+  double eps = 1e-5;
+  bool tied = false;
+  // request geometry
+  int batch_lo = 1, batch_hi = 1, capacity = 0;
+  bool paged = false;
+  int num_blocks = 0, max_blocks = 0;
+  // execution
+  int grid = 0, slots = 0;
+  bool write_logits = true;
+  GemvGeo geo[kNumGemv];
+  // buffer table
+  std::vector<BufferSpec> buffers;
+  int tokens = -1, rope_cos = -1, rope_sin = -1, block_table = -1, context_base = -1;
+  int embed = -1, final_norm = -1, lm_head = -1;
+  int hidden_buf = -1, qkv_buf = -1, attn_buf = -1, mlp_buf = -1, logits_buf = -1;
+  std::vector<LayerBuffers> layer;
+
+  // Throws std::invalid_argument with a precise message on any unsupported field.
+  static PlanSpec FromJson(const Json& plan);
+
+  int qkv_rows() const { return (heads + 2 * kv_heads) * head_dim; }
+  int max_k() const;
+  // algorithmic bytes of one decode step (weights of every GEMV + KV rows read)
+  uint64_t weight_bytes() const;
+  uint64_t kv_bytes_per_token() const { return 4ull * layers * kv_heads * head_dim; }
+};
+
+}  // namespace tmb

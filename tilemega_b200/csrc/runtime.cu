@@ -1,0 +1,494 @@
+// Host side of the tm_plan_* C ABI (include/tilemega_b200.h): reads the plan
+// sidecar, publishes the buffer table, owns the internal device buffers and
+// launches the persistent decode kernel. The reference's counterpart is
+// include/tilemega/Codegen/tasks/Sm90DenseRuntime.cuh:244-559.
+#include <cuda_runtime.h>
+#include <dlfcn.h>
+
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <fstream>
+#include <memory>
+#include <mutex>
+#include <sstream>
+#include <string>
+#include <vector>
+
+#include "../../include/tilemega_b200.h"
+#include "params.h"
+#include "plan_spec.h"
+
+extern "C" int tmb_smem_bytes(const tmb::MegaParams* p);
+extern "C" int tmb_launch_decode(const tmb::MegaParams* p, void* stream);
+extern "C" int tmb_launch_watchdog_probe(const tmb::MegaParams* p, int withhold, void* stream);
+
+namespace {
+
+thread_local std::string g_error;
+
+int Fail(int code, const std::string& message) {
+  g_error = message;
+  std::fprintf(stderr, "tilemega_b200: %s\n", message.c_str());
+  return code;
+}
+
+struct Library {
+  bool ok = false;
+  std::string error;
+  std::string sidecar;
+  tmb::PlanSpec spec;
+};
+
+std::string SidecarPath() {
+  if (const char* env = std::getenv("TILEMEGA_PLAN_JSON")) return env;
+  Dl_info info{};
+  if (dladdr(reinterpret_cast<const void*>(&tm_plan_query), &info) && info.dli_fname)
+    return std::string(info.dli_fname) + ".plan.json";
+  return "";
+}
+
+const Library& Lib() {
+  static Library lib;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    try {
+      lib.sidecar = SidecarPath();
+      std::ifstream in(lib.sidecar);
+      if (!in) throw std::invalid_argument("cannot read plan sidecar '" + lib.sidecar + "'");
+      std::stringstream text;
+      text << in.rdbuf();
+      lib.spec = tmb::PlanSpec::FromJson(tmb::Json::Parse(text.str()));
+      lib.ok = true;
+    } catch (const std::exception& e) {
+      lib.error = e.what();
+    }
+  });
+  return lib;
+}
+
+// Switch to the plan's device for one call and restore the caller's
+// (include/tilemega/Codegen/tasks/Sm90DenseRuntime.cuh:112-119).
+class DeviceScope {
+ public:
+  explicit DeviceScope(int device) {
+    cudaGetDevice(&previous_);
+    if (previous_ != device) cudaSetDevice(device);
+    device_ = device;
+  }
+  ~DeviceScope() {
+    if (previous_ != device_) cudaSetDevice(previous_);
+  }
+
+ private:
+  int previous_ = 0, device_ = 0;
+};
+
+constexpr uint32_t kMagic = 0x544d4232u;  // "TMB2"
+
+struct Plan {
+  uint32_t magic = kMagic;
+  int device = 0;
+  int batch = 0;
+  tmb::MegaParams params{};
+  std::vector<void*> buffer_ptr;      // per table entry
+  std::vector<uint64_t> buffer_bytes;
+  std::vector<void*> owned;           // cudaMalloc'd by the plan
+  int* past_dev = nullptr;
+  uint32_t step_count = 0;
+  uint64_t next_iteration[3] = {0, 0, 0};
+  int prompt_len = 0;
+  size_t smem_bytes = 0;
+  unsigned char* sync_block = nullptr;  // barrier + counters, rezeroed by every launch
+  size_t sync_bytes = 0;
+};
+
+Plan* AsPlan(void* handle) {
+  Plan* plan = static_cast<Plan*>(handle);
+  return plan && plan->magic == kMagic ? plan : nullptr;
+}
+
+uint64_t ElementBytes(uint32_t dtype) { return dtype == TM_DTYPE_BF16 ? 2 : 4; }
+
+cudaError_t Alloc(Plan& plan, void** out, size_t bytes) {
+  cudaError_t err = cudaMalloc(out, bytes ? bytes : 16);
+  if (err != cudaSuccess) return err;
+  plan.owned.push_back(*out);
+  return cudaMemset(*out, 0, bytes ? bytes : 16);
+}
+
+void Destroy(Plan* plan) {
+  DeviceScope scope(plan->device);
+  for (void* p : plan->owned) cudaFree(p);
+  plan->magic = 0;
+  delete plan;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* tm_plan_last_error(void) { return g_error.c_str(); }
+
+int tm_plan_query(tm_plan_info* out) {
+  if (!out) return Fail(-1, "tm_plan_query: null output");
+  const Library& lib = Lib();
+  if (!lib.ok) return Fail(-1, "tm_plan_query: " + lib.error);
+  const tmb::PlanSpec& s = lib.spec;
+  std::memset(out, 0, sizeof(*out));
+  out->abi_version = TM_SERVING_ABI_VERSION;
+  out->phase = TM_SERVING_DECODE;
+  out->batch_lo = s.batch_lo;
+  out->batch_hi = s.batch_hi;
+  out->seq = 1;
+  out->past_lo = 0;
+  out->past_hi = s.capacity - 1;
+  out->capacity = s.capacity;
+  out->grid = s.grid;  // 0: one CTA per SM of the device the plan is created on
+  out->residency = 1;
+  out->modes = TM_SERVING_L1 | TM_SERVING_L2;
+  out->buffer_count = uint32_t(s.buffers.size());
+  return 0;
+}
+
+int tm_plan_buffer(uint32_t index, tm_buffer_info* out) {
+  if (!out) return Fail(-1, "tm_plan_buffer: null output");
+  const Library& lib = Lib();
+  if (!lib.ok) return Fail(-1, "tm_plan_buffer: " + lib.error);
+  if (index >= lib.spec.buffers.size()) return Fail(-1, "tm_plan_buffer: index out of range");
+  const tmb::BufferSpec& b = lib.spec.buffers[index];
+  out->name = b.name.c_str();
+  out->role = b.role;
+  out->dtype = b.dtype;
+  out->elements_constant = b.elements_constant;
+  out->elements_per_batch = b.elements_per_batch;
+  out->pack_json = b.pack_json.empty() ? nullptr : b.pack_json.c_str();
+  return 0;
+}
+
+void* tm_plan_create(int batch, void* const* external, int device) {
+  const Library& lib = Lib();
+  if (!lib.ok) {
+    Fail(-1, "tm_plan_create: " + lib.error);
+    return nullptr;
+  }
+  const tmb::PlanSpec& s = lib.spec;
+  if (batch < s.batch_lo || batch > s.batch_hi || !external) {
+    Fail(-1, "tm_plan_create: batch outside the plan's interval or null buffer list");
+    return nullptr;
+  }
+  int device_count = 0;
+  if (cudaGetDeviceCount(&device_count) != cudaSuccess || device < 0 || device >= device_count) {
+    Fail(-1, "tm_plan_create: no such CUDA device (this library has no CPU path)");
+    return nullptr;
+  }
+  for (size_t i = 0; i < s.buffers.size(); ++i) {
+    if (s.buffers[i].role == TM_BUFFER_EXTERNAL && !external[i]) {
+      Fail(-1, "tm_plan_create: external buffer '" + s.buffers[i].name + "' is null");
+      return nullptr;
+    }
+    if (s.buffers[i].role == TM_BUFFER_EXTERNAL && (reinterpret_cast<uintptr_t>(external[i]) & 15u)) {
+      Fail(-1, "tm_plan_create: external buffer '" + s.buffers[i].name + "' is not 16-byte aligned");
+      return nullptr;
+    }
+  }
+  DeviceScope scope(device);
+  cudaDeviceProp prop{};
+  if (cudaGetDeviceProperties(&prop, device) != cudaSuccess || prop.major < 10) {
+    Fail(-1, "tm_plan_create: the kernels are built for sm_100a only");
+    return nullptr;
+  }
+  auto plan = std::unique_ptr<Plan, void (*)(Plan*)>(new Plan, Destroy);
+  plan->device = device;
+  plan->batch = batch;
+  plan->buffer_ptr.assign(s.buffers.size(), nullptr);
+  plan->buffer_bytes.assign(s.buffers.size(), 0);
+  auto fail = [&](const std::string& what, cudaError_t err) -> void* {
+    Fail(int(err), "tm_plan_create: " + what + ": " + cudaGetErrorString(err));
+    return nullptr;
+  };
+  for (size_t i = 0; i < s.buffers.size(); ++i) {
+    const tmb::BufferSpec& b = s.buffers[i];
+    plan->buffer_bytes[i] = (b.elements_constant + uint64_t(batch) * b.elements_per_batch) * ElementBytes(b.dtype);
+    if (b.role == TM_BUFFER_EXTERNAL) {
+      plan->buffer_ptr[i] = external[i];
+    } else {
+      cudaError_t err = Alloc(*plan, &plan->buffer_ptr[i], plan->buffer_bytes[i]);
+      if (err != cudaSuccess) return fail("allocating " + b.name, err);
+    }
+  }
+  tmb::MegaParams& p = plan->params;
+  p.batch = batch;
+  p.hidden = s.hidden;
+  p.inter = s.inter;
+  p.heads = s.heads;
+  p.kv_heads = s.kv_heads;
+  p.head_dim = s.head_dim;
+  p.layers = s.layers;
+  p.vocab = s.vocab;
+  p.eps = float(s.eps);
+  p.qk_scale_log2 = float(1.4426950408889634 / std::sqrt(double(s.head_dim)));
+  p.capacity = s.capacity;
+  p.max_blocks = s.max_blocks;
+  p.first_step = 0;
+  p.nsteps = 0;
+  p.prompt_len = 0;
+  p.write_logits = s.write_logits ? 1 : 0;
+  p.grid = s.grid > 0 ? std::min(s.grid, prop.multiProcessorCount) : prop.multiProcessorCount;
+  for (int g = 0; g < tmb::kNumGemv; ++g) p.geo[g] = s.geo[g];
+  p.bar_base = 0;
+  const char* watchdog = std::getenv("TILEMEGA_WATCHDOG_MS");
+  const double watchdog_ms = watchdog ? std::atof(watchdog) : 2000.0;
+  p.watchdog_ns = (unsigned long long)(std::max(watchdog_ms, 0.001) * 1e6);
+  // shared memory: activation rows (or the attention scratch, whichever is larger) + ring
+  const int attention_scratch = 4 * s.head_dim * 4 + 2 * s.head_dim * 2 + 8 * 4 * (s.head_dim + 2) * 4;
+  int xs = std::max(batch * s.max_k() * 2, attention_scratch);
+  xs = (xs + 127) & ~127;
+  p.xs_bytes = xs;
+  const int limit = int(prop.sharedMemPerBlockOptin);
+  p.nslots = tmb::kMaxSlots;
+  if (s.slots > 0) p.nslots = std::min(s.slots, tmb::kMaxSlots);
+  while (p.nslots > 0 && tmb_smem_bytes(&p) > limit) --p.nslots;
+  if (p.nslots < 2) {
+    Fail(-1, "tm_plan_create: activation rows leave no room for a two-slot ring in shared memory");
+    return nullptr;
+  }
+  plan->smem_bytes = size_t(tmb_smem_bytes(&p));
+  // request state
+  p.tokens = static_cast<int*>(plan->buffer_ptr[s.tokens]);
+  p.rope_cos = plan->buffer_ptr[s.rope_cos];
+  p.rope_sin = plan->buffer_ptr[s.rope_sin];
+  const uint64_t D = s.head_dim;
+  if (s.paged) {
+    p.block_table = static_cast<const int*>(plan->buffer_ptr[s.block_table]);
+    p.ctx_base = static_cast<const int*>(plan->buffer_ptr[s.context_base]);
+    p.kv_block_stride = (long long)(s.kv_heads * tmb::kKvBlock * D);
+    p.kv_head_stride = (long long)(tmb::kKvBlock * D);
+    p.kv_max_entry = s.num_blocks - 1;
+  } else {
+    // The reference's contiguous [B][Hkv][capacity][D] cache seen as blocks of
+    // 16 rows: entry (b, j) = b*Hkv*capacity/16 + j, heads capacity*D apart
+    // (python/tilemega/serving/state.py:86-98).
+    const int per_head = s.capacity / tmb::kKvBlock;
+    std::vector<int> table(size_t(batch) * s.max_blocks);
+    for (int b = 0; b < batch; ++b)
+      for (int j = 0; j < s.max_blocks; ++j) table[size_t(b) * s.max_blocks + j] = b * s.kv_heads * per_head + j;
+    void* dev = nullptr;
+    cudaError_t err = Alloc(*plan, &dev, table.size() * sizeof(int));
+    if (err == cudaSuccess) err = cudaMemcpy(dev, table.data(), table.size() * sizeof(int), cudaMemcpyHostToDevice);
+    if (err != cudaSuccess) return fail("block table", err);
+    p.block_table = static_cast<const int*>(dev);
+    p.ctx_base = nullptr;
+    p.kv_block_stride = (long long)(tmb::kKvBlock * D);
+    p.kv_head_stride = (long long)(uint64_t(s.capacity) * D);
+    p.kv_max_entry = ((batch - 1) * s.kv_heads + 1) * per_head - 1;
+  }
+  p.embed = plan->buffer_ptr[s.embed];
+  p.final_norm = plan->buffer_ptr[s.final_norm];
+  p.lm_head = plan->buffer_ptr[s.lm_head];
+  std::vector<tmb::LayerPtrs> layers(size_t(s.layers));
+  for (int l = 0; l < s.layers; ++l) {
+    const tmb::LayerBuffers& lb = s.layer[size_t(l)];
+    layers[size_t(l)] = tmb::LayerPtrs{plan->buffer_ptr[lb.qkv],   plan->buffer_ptr[lb.o],     plan->buffer_ptr[lb.gate_up],
+                                       plan->buffer_ptr[lb.down],  plan->buffer_ptr[lb.norm1], plan->buffer_ptr[lb.norm2],
+                                       plan->buffer_ptr[lb.k],     plan->buffer_ptr[lb.v]};
+  }
+  {
+    void* dev = nullptr;
+    cudaError_t err = Alloc(*plan, &dev, layers.size() * sizeof(tmb::LayerPtrs));
+    if (err == cudaSuccess)
+      err = cudaMemcpy(dev, layers.data(), layers.size() * sizeof(tmb::LayerPtrs), cudaMemcpyHostToDevice);
+    if (err != cudaSuccess) return fail("layer table", err);
+    p.layer = static_cast<const tmb::LayerPtrs*>(dev);
+  }
+  p.x = plan->buffer_ptr[s.hidden_buf];
+  p.qkv = plan->buffer_ptr[s.qkv_buf];
+  p.attn = plan->buffer_ptr[s.attn_buf];
+  p.h = plan->buffer_ptr[s.mlp_buf];
+  p.logits = plan->buffer_ptr[s.logits_buf];
+  // scratch
+  int ksplit_max = 1, n_max = 0;
+  for (int g = 0; g < tmb::kNumGemv; ++g) {
+    ksplit_max = std::max(ksplit_max, s.geo[g].ksplit);
+    n_max = std::max(n_max, s.geo[g].n);
+  }
+  struct Scratch {
+    void** out;
+    size_t bytes;
+  };
+  void *gemv_part = nullptr, *attn_part = nullptr, *argmax_val = nullptr, *argmax_idx = nullptr, *status = nullptr,
+       *step_ns = nullptr, *past = nullptr;
+  const size_t attn_tasks = size_t(p.grid) + size_t(batch) * s.kv_heads + 1;
+  const Scratch scratch[] = {
+      {&gemv_part, size_t(ksplit_max) * batch * n_max * sizeof(float)},
+      {&attn_part, attn_tasks * 4 * (s.head_dim + 2) * sizeof(float)},
+      {&argmax_val, size_t(p.grid) * batch * sizeof(float)},
+      {&argmax_idx, size_t(p.grid) * batch * sizeof(int)},
+      {&status, tmb::kStWords * sizeof(unsigned long long)},
+      {&step_ns, size_t(s.capacity + 2) * sizeof(unsigned long long)},
+      {&past, size_t(s.capacity) * sizeof(int)},
+  };
+  for (const Scratch& item : scratch) {
+    cudaError_t err = Alloc(*plan, item.out, item.bytes);
+    if (err != cudaSuccess) return fail("scratch", err);
+  }
+  // barrier word, then the GEMV and attention arrival counters: one block, rezeroed per launch
+  const size_t gemv_cnt = size_t(n_max / tmb::kTileN), attn_cnt = size_t(batch) * s.kv_heads;
+  plan->sync_bytes = 128 + (gemv_cnt + attn_cnt) * sizeof(unsigned);
+  {
+    void* dev = nullptr;
+    cudaError_t err = Alloc(*plan, &dev, plan->sync_bytes);
+    if (err != cudaSuccess) return fail("counters", err);
+    plan->sync_block = static_cast<unsigned char*>(dev);
+  }
+  p.bar = reinterpret_cast<unsigned long long*>(plan->sync_block);
+  p.gemv_cnt = reinterpret_cast<unsigned*>(plan->sync_block + 128);
+  p.attn_cnt = p.gemv_cnt + gemv_cnt;
+  p.gemv_part = static_cast<float*>(gemv_part);
+  p.attn_part = static_cast<float*>(attn_part);
+  p.argmax_val = static_cast<float*>(argmax_val);
+  p.argmax_idx = static_cast<int*>(argmax_idx);
+  p.status = static_cast<unsigned long long*>(status);
+  p.step_ns = static_cast<unsigned long long*>(step_ns);
+  plan->past_dev = static_cast<int*>(past);
+  p.past = plan->past_dev;
+  if (cudaDeviceSynchronize() != cudaSuccess) return fail("initialisation", cudaGetLastError());
+  return plan.release();
+}
+
+int tm_plan_set_steps(void* handle, const int32_t* past, uint32_t count) {
+  Plan* plan = AsPlan(handle);
+  if (!plan || !past || count == 0) return Fail(-1, "tm_plan_set_steps: bad argument");
+  const tmb::MegaParams& p = plan->params;
+  if (count > uint32_t(p.capacity)) return Fail(-2, "tm_plan_set_steps: more steps than the plan's capacity");
+  for (uint32_t i = 0; i < count; ++i)
+    if (past[i] < 0 || past[i] >= p.capacity) return Fail(-2, "tm_plan_set_steps: position outside [0, capacity)");
+  DeviceScope scope(plan->device);
+  cudaError_t err = cudaMemcpy(plan->past_dev, past, size_t(count) * sizeof(int32_t), cudaMemcpyHostToDevice);
+  if (err != cudaSuccess) return Fail(int(err), std::string("tm_plan_set_steps: ") + cudaGetErrorString(err));
+  plan->step_count = count;
+  return 0;
+}
+
+int tm_plan_set_prompt_len(void* handle, int prompt_len) {
+  Plan* plan = AsPlan(handle);
+  if (!plan || prompt_len < 0 || prompt_len > plan->params.capacity)
+    return Fail(-1, "tm_plan_set_prompt_len: bad argument");
+  plan->prompt_len = prompt_len;
+  return 0;
+}
+
+int tm_plan_launch_steps(void* handle, uint32_t first_step, uint32_t steps, uint32_t mode, uint64_t base_iteration,
+                         void* stream) {
+  Plan* plan = AsPlan(handle);
+  if (!plan || steps == 0) return Fail(-1, "tm_plan_launch_steps: bad argument");
+  if (mode != TM_SERVING_L1 && mode != TM_SERVING_L2) return Fail(-3, "tm_plan_launch_steps: unknown mode");
+  if (uint64_t(first_step) + steps > plan->step_count)
+    return Fail(-2, "tm_plan_launch_steps: steps outside the interval given to tm_plan_set_steps");
+  if (base_iteration != plan->next_iteration[mode])
+    return Fail(-2, "tm_plan_launch_steps: iteration is not the number of previous launches of this mode");
+  DeviceScope scope(plan->device);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t err = cudaMemsetAsync(plan->sync_block, 0, plan->sync_bytes, s);
+  if (err != cudaSuccess) return Fail(int(err), std::string("tm_plan_launch_steps: ") + cudaGetErrorString(err));
+  tmb::MegaParams p = plan->params;
+  p.first_step = int(first_step);
+  p.nsteps = int(steps);
+  p.prompt_len = plan->prompt_len;
+  const int status = tmb_launch_decode(&p, stream);
+  if (status != 0)
+    return Fail(status, std::string("tm_plan_launch_steps: ") + cudaGetErrorString(cudaError_t(status)));
+  plan->next_iteration[mode] += steps;
+  return 0;
+}
+
+int tm_plan_launch(void* handle, uint32_t step, uint32_t mode, uint64_t iteration, void* stream) {
+  return tm_plan_launch_steps(handle, step, 1, mode, iteration, stream);
+}
+
+unsigned tm_plan_loop_modes(void* handle) { return AsPlan(handle) ? (TM_SERVING_L1 | TM_SERVING_L2) : 0u; }
+
+int tm_plan_read_step_ns(void* handle, uint32_t first, uint32_t count, uint64_t* host) {
+  Plan* plan = AsPlan(handle);
+  if (!plan || !host || uint64_t(first) + count > uint64_t(plan->params.capacity) + 2)
+    return Fail(-1, "tm_plan_read_step_ns: bad argument");
+  DeviceScope scope(plan->device);
+  cudaError_t err =
+      cudaMemcpy(host, plan->params.step_ns + first, size_t(count) * sizeof(uint64_t), cudaMemcpyDeviceToHost);
+  return err == cudaSuccess ? 0 : Fail(int(err), std::string("tm_plan_read_step_ns: ") + cudaGetErrorString(err));
+}
+
+int tm_plan_read_buffer(void* handle, uint32_t index, void* host, uint64_t bytes) {
+  Plan* plan = AsPlan(handle);
+  if (!plan || !host || index >= plan->buffer_ptr.size() || bytes > plan->buffer_bytes[index])
+    return Fail(-1, "tm_plan_read_buffer: bad argument");
+  DeviceScope scope(plan->device);
+  cudaError_t err = cudaMemcpy(host, plan->buffer_ptr[index], size_t(bytes), cudaMemcpyDeviceToHost);
+  return err == cudaSuccess ? 0 : Fail(int(err), std::string("tm_plan_read_buffer: ") + cudaGetErrorString(err));
+}
+
+int tm_plan_watchdog(void* handle, uint64_t* record12) {
+  Plan* plan = AsPlan(handle);
+  if (!plan || !record12) return 0;
+  DeviceScope scope(plan->device);
+  unsigned long long words[tmb::kStWords] = {};
+  if (cudaMemcpy(words, plan->params.status, sizeof(words), cudaMemcpyDeviceToHost) != cudaSuccess) return 0;
+  for (int i = 0; i < 12; ++i) record12[i] = words[i];
+  return words[tmb::kStFired] ? 1 : 0;
+}
+
+int tm_plan_clear_watchdog(void* handle) {
+  Plan* plan = AsPlan(handle);
+  if (!plan) return Fail(-1, "tm_plan_clear_watchdog: bad plan");
+  DeviceScope scope(plan->device);
+  cudaError_t err = cudaMemset(plan->params.status, 0, tmb::kStWords * sizeof(unsigned long long));
+  return err == cudaSuccess ? 0 : Fail(int(err), cudaGetErrorString(err));
+}
+
+int tm_plan_watchdog_probe(void* handle, int withhold, uint32_t limit_us, void* stream) {
+  Plan* plan = AsPlan(handle);
+  if (!plan || limit_us == 0 || limit_us > 1000000u) return Fail(-1, "tm_plan_watchdog_probe: bad argument");
+  DeviceScope scope(plan->device);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t err = cudaMemsetAsync(plan->sync_block, 0, plan->sync_bytes, s);
+  if (err == cudaSuccess) err = cudaMemsetAsync(plan->params.status, 0, tmb::kStWords * sizeof(unsigned long long), s);
+  if (err != cudaSuccess) return Fail(int(err), cudaGetErrorString(err));
+  tmb::MegaParams p = plan->params;
+  p.watchdog_ns = (unsigned long long)limit_us * 1000ull;
+  const int status = tmb_launch_watchdog_probe(&p, withhold, stream);
+  if (status != 0) return Fail(status, cudaGetErrorString(cudaError_t(status)));
+  err = cudaStreamSynchronize(s);
+  if (err != cudaSuccess) return Fail(int(err), cudaGetErrorString(err));
+  uint64_t record[12];
+  const int fired = tm_plan_watchdog(handle, record);
+  tm_plan_clear_watchdog(handle);
+  return fired;
+}
+
+unsigned tm_plan_pdl_enabled(void*) { return 0; }
+
+uint64_t tm_plan_execution_smem(void* handle, unsigned) {
+  Plan* plan = AsPlan(handle);
+  return plan ? plan->smem_bytes : 0;
+}
+
+uint64_t tm_plan_step_bytes(void* handle, uint64_t cached_tokens_total) {
+  Plan* plan = AsPlan(handle);
+  if (!plan) return 0;
+  const tmb::PlanSpec& s = Lib().spec;
+  return s.weight_bytes() + s.kv_bytes_per_token() * cached_tokens_total;
+}
+
+unsigned tm_plan_tp_world(void) { return 1; }
+unsigned long long tm_plan_tp_bytes(unsigned) { return 0; }
+int tm_plan_bind_tp(void*, int, void* const*, void* const*) {
+  return Fail(-1, "tm_plan_bind_tp: this plan is not tensor parallel");
+}
+
+void tm_plan_destroy(void* handle) {
+  Plan* plan = AsPlan(handle);
+  if (plan) Destroy(plan);
+}
+
+}  // extern "C"

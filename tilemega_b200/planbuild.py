@@ -1,0 +1,66 @@
+"""Emit one plan library: a copy of libtilemega_b200.so next to its JSON sidecar.
+
+TileMega's compiler produces one shared object per (model, phase, batch
+interval) and `tm_plan_query` takes no argument (reference:
+include/tilemega/Codegen/tasks/ServingAbi.h:33). Here the kernels are generic
+over the model dimensions, so "compiling a plan" is writing the sidecar the
+library reads at load time; the copy gives each plan its own file identity, which
+is what `ctypes.CDLL` keys loaded libraries on.
+"""
+from __future__ import annotations
+
+import hashlib
+import json
+import shutil
+from pathlib import Path
+
+from .build import LIBRARY, build_library
+
+MODEL_KEYS = ("hidden_size", "intermediate_size", "num_attention_heads", "num_key_value_heads",
+              "head_dim", "num_hidden_layers", "vocab_size", "rms_norm_eps", "tie_word_embeddings",
+              "rope_theta", "architectures")
+
+
+def plan_document(config: dict, *, batch_lo: int = 1, batch_hi: int | None = None, capacity: int,
+                  kv_layout: str = "contiguous", num_blocks: int = 0, geometry: dict | None = None,
+                  grid: int = 0, slots: int = 0, write_logits: bool = True) -> dict:
+    """The sidecar for one decode plan; raises ValueError on shapes the kernels do not cover."""
+    model = {key: config[key] for key in MODEL_KEYS if key in config}
+    model.setdefault("head_dim", config["hidden_size"] // config["num_attention_heads"])
+    model.setdefault("rms_norm_eps", 1e-5)
+    batch_hi = batch_lo if batch_hi is None else batch_hi
+    if not 1 <= batch_lo <= batch_hi <= 4:
+        raise ValueError("batch interval must lie in [1, 4]")
+    if capacity < 16 or capacity % 16:
+        raise ValueError("capacity must be a positive multiple of the KV block (16)")
+    if kv_layout not in ("contiguous", "paged"):
+        raise ValueError("kv_layout must be 'contiguous' or 'paged'")
+    if kv_layout == "paged" and num_blocks < batch_hi * (capacity // 16):
+        raise ValueError("a paged plan needs num_blocks >= batch_hi * capacity / 16")
+    document = {
+        "execution": "megakernel", "pg": "ring", "arch": "sm_100a", "phase": "decode",
+        "model": model, "batch_lo": batch_lo, "batch_hi": batch_hi, "capacity": capacity,
+        "kv": {"layout": kv_layout, "block": 16, "num_blocks": num_blocks},
+        "geometry": geometry or {}, "grid": grid, "slots": slots, "write_logits": write_logits,
+    }
+    return document
+
+
+def emit_plan(config: dict, out_dir: str | Path, **options) -> Path:
+    """Write `<out_dir>/<digest>.so` + `.so.plan.json` and return the library path."""
+    document = plan_document(config, **options)
+    text = json.dumps(document, indent=1, sort_keys=True) + "\n"
+    digest = hashlib.sha256(text.encode()).hexdigest()[:16]
+    out_dir = Path(out_dir)
+    out_dir.mkdir(parents=True, exist_ok=True)
+    library = build_library()
+    target = out_dir / f"tilemega_b200_{digest}.so"
+    if not target.exists() or target.stat().st_mtime < library.stat().st_mtime:
+        tmp = target.with_suffix(".so.tmp")
+        shutil.copyfile(library, tmp)
+        tmp.replace(target)
+    Path(str(target) + ".plan.json").write_text(text)
+    return target
+
+
+__all__ = ["emit_plan", "plan_document", "LIBRARY"]

@@ -1,0 +1,163 @@
+"""Checkpoint tensors -> the packed device buffers a plan's table asks for.
+
+Same role as python/tilemega/serving/weights.py:99-313 of the reference: every
+weight buffer of a plan carries a `pack_json` recipe that names checkpoint
+tensors by their HF names; this module evaluates the recipe kinds the dense
+decode plan uses (alias, qkv_group_interleave, gate_up_interleave, tile_pages).
+"""
+from __future__ import annotations
+
+import json
+from pathlib import Path
+from typing import Callable, Mapping
+
+import torch
+
+from .plan import Buffer, PlanLibrary
+
+DTYPES = {0: torch.bfloat16, 1: torch.float32, 2: torch.int32}
+
+
+class Checkpoint:
+    """A directory of *.safetensors files keyed by tensor name (weights.py:17-49)."""
+
+    def __init__(self, model_dir: str | Path):
+        from safetensors import safe_open
+        self._open = safe_open
+        self.model_dir = Path(model_dir)
+        config = self.model_dir / "config.json"
+        self.tie_word_embeddings = bool(json.loads(config.read_text()).get(
+            "tie_word_embeddings", False)) if config.exists() else False
+        self.files: dict[str, Path] = {}
+        for path in sorted(self.model_dir.glob("*.safetensors")):
+            with safe_open(path, framework="pt", device="cpu") as stream:
+                for name in stream.keys():
+                    if name in self.files:
+                        raise ValueError(f"duplicate checkpoint tensor {name}")
+                    self.files[name] = path
+        if not self.files:
+            raise FileNotFoundError(f"no safetensors in {self.model_dir}")
+
+    def tensor(self, name: str) -> torch.Tensor:
+        if name == "lm_head.weight" and name not in self.files and self.tie_word_embeddings:
+            name = "model.embed_tokens.weight"
+        path = self.files.get(name)
+        if path is None:
+            raise KeyError(f"checkpoint has no {name}")
+        with self._open(path, framework="pt", device="cpu") as stream:
+            return stream.get_tensor(name)
+
+
+class TensorCheckpoint:
+    """An in-memory checkpoint (name -> tensor), e.g. seeded random weights."""
+
+    def __init__(self, tensors: Mapping[str, torch.Tensor], tie_word_embeddings: bool = False):
+        self.tensors = tensors
+        self.tie_word_embeddings = tie_word_embeddings
+
+    def tensor(self, name: str) -> torch.Tensor:
+        if name == "lm_head.weight" and name not in self.tensors and self.tie_word_embeddings:
+            name = "model.embed_tokens.weight"
+        if name not in self.tensors:
+            raise KeyError(f"checkpoint has no {name}")
+        return self.tensors[name]
+
+
+def tile_pages(weight: torch.Tensor, tile_n: int, tile_k: int) -> torch.Tensor:
+    """[N][K] -> [N/tn][K/tk][tn*tk] pages, each 8x64 atom 128-byte XOR swizzled.
+
+    Layout contract (reference weights.py:239-240, tk >= 64): element (row, col)
+    of a page sits at 512*(row//8 + (tn//8)*(col//64)) + 64*(row%8) +
+    8*((col%64//8) ^ (row%8)) + col%8. Built here as a reshape: the page is
+    [col//64][row//8][row%8][chunk][8] and the chunk axis is permuted by row%8.
+    """
+    if weight.ndim != 2 or tile_n <= 0 or tile_k <= 0 or tile_n % 8 or tile_k % 64:
+        raise ValueError("invalid tile_pages source or geometry")
+    n, k = weight.shape
+    nt, kt = -(-n // tile_n), -(-k // tile_k)
+    if (nt * tile_n, kt * tile_k) != (n, k):
+        padded = torch.zeros((nt * tile_n, kt * tile_k), dtype=weight.dtype, device=weight.device)
+        padded[:n, :k] = weight
+        weight = padded
+    # axes: nt, row-group, row-in-group, kt, column-block, chunk, element
+    view = weight.reshape(nt, tile_n // 8, 8, kt, tile_k // 64, 8, 8)
+    view = view.permute(0, 3, 4, 1, 2, 5, 6)  # nt, kt, cb, rg, r, chunk, e
+    rows = torch.arange(8, device=weight.device)
+    source_chunk = rows[:, None] ^ rows[None, :]  # physical chunk c' of row r holds logical chunk c' ^ r
+    swizzled = view[:, :, :, :, rows[:, None], source_chunk, :]
+    return swizzled.reshape(-1).contiguous()
+
+
+def _sources(recipe: Mapping[str, object], source: Callable[[str], torch.Tensor]) -> list[torch.Tensor]:
+    tensors = [source(str(name)) for name in recipe["sources"]]
+    if not all(item.ndim == 2 for item in tensors) or len({item.shape[1] for item in tensors}) != 1:
+        raise ValueError("packed GEMM sources must be matrices with one K")
+    return tensors
+
+
+def pack(recipe: Mapping[str, object], source: Callable[[str], torch.Tensor]) -> torch.Tensor:
+    kind = recipe["kind"]
+    if kind == "alias":
+        return source(str(recipe["source"]))
+    if kind == "tile_pages":
+        return tile_pages(pack(recipe["source"], source), int(recipe["tile_n"]), int(recipe["tile_k"]))
+    if kind == "qkv_group_interleave":
+        # rows per KV head: its query heads, then its key head, then its value head
+        # (reference weights.py:246-256)
+        q, k, v = _sources(recipe, source)
+        hkv, qperkv, dim = (int(recipe[key]) for key in ("hkv", "qperkv", "head_dim"))
+        if q.shape[0] != hkv * qperkv * dim or k.shape[0] != hkv * dim or v.shape[0] != hkv * dim:
+            raise ValueError("QKV recipe and checkpoint shapes disagree")
+        width = q.shape[1]
+        grouped = torch.cat((q.reshape(hkv, qperkv * dim, width), k.reshape(hkv, dim, width),
+                             v.reshape(hkv, dim, width)), dim=1)
+        return grouped.reshape(-1, width)
+    if kind == "gate_up_interleave":
+        # u gate rows, then the u matching up rows (reference weights.py:257-264)
+        gate, up = _sources(recipe, source)
+        unit = int(recipe["u"])
+        if gate.shape != up.shape or unit <= 0 or gate.shape[0] % unit:
+            raise ValueError("gate/up interleave shape mismatch")
+        width = gate.shape[1]
+        return torch.stack((gate.reshape(-1, unit, width), up.reshape(-1, unit, width)), dim=1).reshape(-1, width)
+    raise ValueError(f"unsupported packing recipe {kind}")
+
+
+def weight_recipes(*plans: PlanLibrary) -> dict[str, Buffer]:
+    result: dict[str, Buffer] = {}
+    for plan in plans:
+        for buffer in plan.buffers:
+            if not buffer.pack_json:
+                continue
+            prior = result.setdefault(buffer.name, buffer)
+            if (prior.pack_json, prior.dtype, prior.elements_constant) != (
+                    buffer.pack_json, buffer.dtype, buffer.elements_constant):
+                raise ValueError(f"plans disagree on weight {buffer.name}")
+    return result
+
+
+def load_weights(checkpoint: str | Path | Checkpoint | TensorCheckpoint, *plans: PlanLibrary,
+                 device: str | torch.device = "cuda") -> dict[str, torch.Tensor]:
+    """Pack every recipe buffer of the plans on `device` (bf16 unless the table says otherwise)."""
+    if isinstance(checkpoint, (str, Path)):
+        checkpoint = Checkpoint(checkpoint)
+    device = torch.device(device)
+    result: dict[str, torch.Tensor] = {}
+    packed: dict[str, torch.Tensor] = {}
+    for name, buffer in weight_recipes(*plans).items():
+        if buffer.pack_json not in packed:
+            recipe = json.loads(buffer.pack_json)
+            dtype = DTYPES[buffer.dtype]
+            staged: dict[str, torch.Tensor] = {}
+
+            def source(fqn: str) -> torch.Tensor:
+                if fqn not in staged:
+                    staged[fqn] = checkpoint.tensor(fqn).to(device=device, dtype=dtype).contiguous()
+                return staged[fqn]
+
+            packed[buffer.pack_json] = pack(recipe, source).contiguous()
+        tensor = packed[buffer.pack_json]
+        if tensor.numel() != buffer.elements_constant:
+            raise ValueError(f"{name} has {tensor.numel()} elements; plan expects {buffer.elements_constant}")
+        result[name] = tensor
+    return result

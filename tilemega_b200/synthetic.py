@@ -1,0 +1,85 @@
+"""Seeded synthetic workloads with the shapes of the benchmark configurations.
+
+No dataset or checkpoint is involved: weights are N(0, 0.02) draws from a seeded
+generator (norm weights 1), token ids and context lengths are seeded uniform
+draws. The draw order is fixed here so every consumer (GPU path, CPU oracle,
+fixture generator) sees the same tensors.
+"""
+from __future__ import annotations
+
+import torch
+
+LLAMA_3_2_1B = dict(architectures=["LlamaForCausalLM"], hidden_size=2048, intermediate_size=8192,
+                    num_attention_heads=32, num_key_value_heads=8, head_dim=64, num_hidden_layers=16,
+                    vocab_size=128256, rms_norm_eps=1e-5, tie_word_embeddings=True, rope_theta=500000.0)
+LLAMA_3_1_8B = dict(architectures=["LlamaForCausalLM"], hidden_size=4096, intermediate_size=14336,
+                    num_attention_heads=32, num_key_value_heads=8, head_dim=128, num_hidden_layers=32,
+                    vocab_size=128256, rms_norm_eps=1e-5, tie_word_embeddings=False, rope_theta=500000.0)
+# Two-layer models (under 150 MB of bf16 weights) with every structural feature of
+# the above: 4 query heads per KV head, head_dim 64 / 128, every K a multiple of 2048.
+TINY = dict(architectures=["LlamaForCausalLM"], hidden_size=2048, intermediate_size=2048,
+            num_attention_heads=32, num_key_value_heads=8, head_dim=64, num_hidden_layers=2,
+            vocab_size=1024, rms_norm_eps=1e-5, tie_word_embeddings=True, rope_theta=500000.0)
+TINY_D128 = dict(architectures=["LlamaForCausalLM"], hidden_size=2048, intermediate_size=4096,
+                 num_attention_heads=16, num_key_value_heads=4, head_dim=128, num_hidden_layers=2,
+                 vocab_size=2048, rms_norm_eps=1e-5, tie_word_embeddings=False, rope_theta=500000.0)
+
+
+def head_dim_of(config: dict) -> int:
+    return int(config.get("head_dim") or config["hidden_size"] // config["num_attention_heads"])
+
+
+def parameter_shapes(config: dict) -> list[tuple[str, tuple[int, ...]]]:
+    """HF tensor names and shapes in state-dict order (the draw order)."""
+    hidden, inter = config["hidden_size"], config["intermediate_size"]
+    dim = head_dim_of(config)
+    q, kv = config["num_attention_heads"] * dim, config["num_key_value_heads"] * dim
+    shapes: list[tuple[str, tuple[int, ...]]] = [("model.embed_tokens.weight", (config["vocab_size"], hidden))]
+    for layer in range(config["num_hidden_layers"]):
+        p = f"model.layers.{layer}."
+        shapes += [
+            (p + "input_layernorm.weight", (hidden,)),
+            (p + "self_attn.q_proj.weight", (q, hidden)),
+            (p + "self_attn.k_proj.weight", (kv, hidden)),
+            (p + "self_attn.v_proj.weight", (kv, hidden)),
+            (p + "self_attn.o_proj.weight", (hidden, q)),
+            (p + "post_attention_layernorm.weight", (hidden,)),
+            (p + "mlp.gate_proj.weight", (inter, hidden)),
+            (p + "mlp.up_proj.weight", (inter, hidden)),
+            (p + "mlp.down_proj.weight", (hidden, inter)),
+        ]
+    shapes.append(("model.norm.weight", (hidden,)))
+    if not config.get("tie_word_embeddings", False):
+        shapes.append(("lm_head.weight", (config["vocab_size"], hidden)))
+    return shapes
+
+
+def seeded_weights(config: dict, seed: int = 0, dtype: torch.dtype = torch.float32,
+                   device: str | torch.device = "cpu", std: float = 0.02) -> dict[str, torch.Tensor]:
+    """Every matrix N(0, std) from one generator seeded with `seed`; norm weights 1.
+
+    On the CPU the draws are fp32 and then cast, so a bf16 copy is exactly the
+    rounding of the fp32 copy. On a CUDA device the generator is the device's
+    (a different stream of numbers: use it for throughput runs, not for parity).
+    """
+    device = torch.device(device)
+    generator = torch.Generator(device=device).manual_seed(seed)
+    weights: dict[str, torch.Tensor] = {}
+    for name, shape in parameter_shapes(config):
+        if len(shape) == 1:
+            weights[name] = torch.ones(shape, dtype=dtype, device=device)
+        else:
+            draw = torch.randn(shape, generator=generator, dtype=torch.float32, device=device)
+            weights[name] = (draw * std).to(dtype)
+    return weights
+
+
+def seeded_tokens(batch: int, length: int, vocab: int, seed: int = 1) -> torch.Tensor:
+    generator = torch.Generator().manual_seed(seed)
+    return torch.randint(0, vocab, (batch, length), generator=generator, dtype=torch.int64).to(torch.int32)
+
+
+def seeded_contexts(batch: int, low: int, high: int, seed: int = 2) -> torch.Tensor:
+    """Per-sequence context lengths uniform in [low, high]."""
+    generator = torch.Generator().manual_seed(seed)
+    return torch.randint(low, high + 1, (batch,), generator=generator, dtype=torch.int64).to(torch.int32)
