@@ -94,9 +94,16 @@ class OracleDecoder:
     """forward(ids [B][S], start [B]) -> logits [B][S][V]; appends to the cache."""
 
     def __init__(self, config: dict, weights: dict[str, torch.Tensor], dtype: torch.dtype = torch.float32,
-                 capacity: int = 256):
+                 capacity: int = 256, attention_fp32: bool = False):
+        # attention_fp32 restates the numerics of the reference's *kernel* instead of
+        # its module: scores, softmax and the probability-value product stay in fp32
+        # and only the context is rounded to the model dtype
+        # (include/tilemega/Backend/Sm90DenseAttentionBody.cuh:248-302,371-403; the
+        # module rounds scores and probabilities to bf16, export.py:94-99). With
+        # dtype fp32 the two modes are the same computation.
         self.config = config
         self.dtype = dtype
+        self.attention_fp32 = attention_fp32
         self.w = {name: tensor.to(dtype) for name, tensor in weights.items()}
         if "lm_head.weight" not in self.w:
             if not config.get("tie_word_embeddings", False):
@@ -127,11 +134,17 @@ class OracleDecoder:
             query = qb.transpose(0, 1)                                   # [Hq][S][D]
             keys = torch.repeat_interleave(full_k, self.heads // self.kv_heads, dim=0)
             values = torch.repeat_interleave(full_v, self.heads // self.kv_heads, dim=0)
-            score = torch.matmul(query, keys.transpose(-1, -2)) / math.sqrt(self.dim)
             key_position = torch.arange(start[b] + seq)[None, :]
-            score = score.masked_fill(key_position > positions[:, None], float("-inf"))
-            probability = torch.softmax(score.float(), dim=-1).to(x.dtype)
-            context[b] = torch.matmul(probability, values).transpose(0, 1).reshape(seq, self.heads * self.dim)
+            if self.attention_fp32:
+                score = torch.matmul(query.float(), keys.float().transpose(-1, -2)) / math.sqrt(self.dim)
+                score = score.masked_fill(key_position > positions[:, None], float("-inf"))
+                attended = torch.matmul(torch.softmax(score, dim=-1), values.float()).to(x.dtype)
+            else:
+                score = torch.matmul(query, keys.transpose(-1, -2)) / math.sqrt(self.dim)
+                score = score.masked_fill(key_position > positions[:, None], float("-inf"))
+                probability = torch.softmax(score.float(), dim=-1).to(x.dtype)
+                attended = torch.matmul(probability, values)
+            context[b] = attended.transpose(0, 1).reshape(seq, self.heads * self.dim)
         return F.linear(context, self.w[p + "o_proj.weight"])
 
     def mlp(self, layer: int, x: torch.Tensor) -> torch.Tensor:
@@ -142,8 +155,10 @@ class OracleDecoder:
 
     @torch.inference_mode()
     def forward(self, ids: torch.Tensor, start: list[int], kv: PagedKV,
-                last_only: bool = False) -> torch.Tensor:
-        # export.py:134-140,165-172
+                last_only: bool = False, head_fp32: bool = False) -> torch.Tensor:
+        # export.py:134-140,165-172. head_fp32 returns the lm_head products of the
+        # same (model-dtype) normalised hidden state accumulated and kept in fp32,
+        # i.e. the logits before their final rounding to the model dtype.
         x = F.embedding(ids.long(), self.w["model.embed_tokens.weight"])
         for layer in range(self.config["num_hidden_layers"]):
             p = f"model.layers.{layer}."
@@ -151,26 +166,32 @@ class OracleDecoder:
             x = x + self.mlp(layer, rms_norm(x, self.w[p + "post_attention_layernorm.weight"], self.eps))
         if last_only:
             x = x[:, -1:]
-        return F.linear(rms_norm(x, self.w["model.norm.weight"], self.eps), self.w["lm_head.weight"])
+        normed = rms_norm(x, self.w["model.norm.weight"], self.eps)
+        if head_fp32:
+            return F.linear(normed.float(), self.w["lm_head.weight"].float())
+        return F.linear(normed, self.w["lm_head.weight"])
 
     @torch.inference_mode()
     def greedy(self, prompt: torch.Tensor, new_tokens: int, kv: PagedKV, start: list[int] | None = None,
-               forced: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor]:
+               forced: torch.Tensor | None = None, head_fp32: bool = False) -> tuple[torch.Tensor, torch.Tensor]:
         """Prefill `prompt` [B][P], then decode. Returns (tokens [B][new], logits
         [new][B][V] as fp32). Ties go to the smaller index (torch.argmax on CPU
         returns the first maximum). With `forced` [B][new] the history follows
-        `forced` instead of the oracle's own argmax (teacher forcing)."""
+        `forced` instead of the oracle's own argmax (teacher forcing). The argmax
+        always sees the logits rounded to the model dtype (the reference compares
+        rounded logits); head_fp32 only changes what is returned."""
         batch, length = prompt.shape
         start = list(start) if start is not None else [0] * batch
-        logits = self.forward(prompt, start, kv, last_only=True)[:, -1].float()
+        logits = self.forward(prompt, start, kv, last_only=True, head_fp32=head_fp32)[:, -1].float()
         tokens, history = [], []
         for step in range(new_tokens):
             history.append(logits)
-            chosen = logits.argmax(-1)
+            chosen = logits.to(self.dtype).float().argmax(-1)
             tokens.append(chosen)
             if step + 1 == new_tokens:
                 break
             feed = forced[:, step].long() if forced is not None else chosen
             position = [s + length + step for s in start]
-            logits = self.forward(feed.view(batch, 1).to(torch.int32), position, kv)[:, -1].float()
+            logits = self.forward(feed.view(batch, 1).to(torch.int32), position, kv,
+                                  head_fp32=head_fp32)[:, -1].float()
         return torch.stack(tokens, dim=1).to(torch.int32), torch.stack(history)

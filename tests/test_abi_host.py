@@ -1,0 +1,99 @@
+"""Host-side checks of the C ABI that need no GPU: the library loads, exports
+every declared symbol, publishes the buffer table of its sidecar, and refuses
+loudly to create a plan without a CUDA device."""
+import ctypes
+import json
+import re
+from pathlib import Path
+
+import pytest
+import torch
+
+from tilemega_b200 import synthetic
+from tilemega_b200.planbuild import emit_plan, plan_document
+from tilemega_b200.serving.plan import DECODE, PlanLibrary
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def declared_symbols():
+    header = (ROOT / "include" / "tilemega_b200.h").read_text()
+    header = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
+    return sorted(set(re.findall(r"\b(tm_plan_\w+)\s*\(", header)))
+
+
+def test_library_exports_every_declared_symbol(library):
+    lib = ctypes.CDLL(str(library))
+    names = declared_symbols()
+    assert len(names) >= 20
+    for name in names:
+        assert hasattr(lib, name), f"{name} is declared in include/tilemega_b200.h but not exported"
+
+
+def test_query_without_sidecar_fails(library, tmp_path, monkeypatch):
+    import shutil
+    orphan = tmp_path / "orphan.so"
+    shutil.copyfile(library, orphan)
+    with pytest.raises(RuntimeError):
+        PlanLibrary(orphan)
+
+
+def test_buffer_table_of_tiny_plan(plan_dir):
+    config = synthetic.TINY
+    so = emit_plan(config, plan_dir, batch_lo=1, batch_hi=4, capacity=64)
+    lib = PlanLibrary(so)
+    assert lib.info.abi_version == 1 and lib.info.phase == DECODE and lib.info.seq == 1
+    assert (lib.info.batch_lo, lib.info.batch_hi, lib.info.capacity) == (1, 4, 64)
+    assert (lib.info.past_lo, lib.info.past_hi) == (0, 63)
+    assert lib.info.modes == 3
+    table = {b.name: b for b in lib.buffers}
+    hidden, dim = config["hidden_size"], config["head_dim"]
+    assert table["serving.tokens"].elements_per_batch == 64 and table["serving.tokens"].dtype == 2
+    assert table["serving.rope_cos"].elements_constant == 64 * dim
+    assert table["kv_cache.k.1"].elements_per_batch == config["num_key_value_heads"] * 64 * dim
+    qkv = table["l0.qkv.weight"]
+    rows = (config["num_attention_heads"] + 2 * config["num_key_value_heads"]) * dim
+    assert qkv.elements_constant == rows * hidden and qkv.role == 1
+    recipe = json.loads(qkv.pack_json)
+    assert recipe["kind"] == "tile_pages" and (recipe["tile_n"], recipe["tile_k"]) == (8, 2048)
+    assert recipe["source"]["kind"] == "qkv_group_interleave" and recipe["source"]["qperkv"] == 4
+    assert recipe["source"]["sources"][1] == "model.layers.0.self_attn.k_proj.weight"
+    assert json.loads(table["l1.gate_up.weight"].pack_json)["source"]["u"] == 4
+    assert json.loads(table["lm_head.weight"].pack_json)["source"] == {"kind": "alias", "source": "lm_head.weight"}
+    assert table["serving.logits"].role == 0 and table["serving.logits"].elements_per_batch == config["vocab_size"]
+    # external pointers are mandatory and checked before anything touches a device
+    with pytest.raises(KeyError):
+        lib.create(1, {}, 0)
+    with pytest.raises(ValueError):
+        lib.create(5, {}, 0)
+
+
+def test_paged_plan_lists_block_table(plan_dir):
+    so = emit_plan(synthetic.TINY, plan_dir, batch_lo=2, batch_hi=2, capacity=64, kv_layout="paged", num_blocks=24)
+    lib = PlanLibrary(so)
+    table = {b.name: b for b in lib.buffers}
+    assert table["serving.block_table"].elements_per_batch == 4 and table["serving.block_table"].dtype == 2
+    assert table["serving.context_base"].elements_per_batch == 1
+    assert table["kv_pool.k.0"].elements_constant == 24 * 8 * 16 * 64 and "kv_cache.k.0" not in table
+
+
+@pytest.mark.skipif(torch.cuda.is_available(), reason="checks the no-GPU failure mode")
+def test_create_without_a_gpu_fails_loudly(plan_dir):
+    so = emit_plan(synthetic.TINY, plan_dir, batch_lo=1, batch_hi=1, capacity=32)
+    lib = PlanLibrary(so)
+    pointers = {b.name: 4096 for b in lib.buffers if b.role == 1}
+    with pytest.raises(RuntimeError, match="no such CUDA device|rejected"):
+        lib.create(1, pointers, 0)
+
+
+def test_unsupported_shapes_are_rejected(plan_dir):
+    bad = dict(synthetic.TINY, hidden_size=1024)
+    so = emit_plan(bad, plan_dir, batch_lo=1, batch_hi=1, capacity=32)
+    with pytest.raises(RuntimeError, match="K must be a multiple"):
+        PlanLibrary(so)
+    with pytest.raises(ValueError):
+        plan_document(synthetic.TINY, batch_lo=1, batch_hi=9, capacity=32)
+    with pytest.raises(ValueError):
+        plan_document(synthetic.TINY, batch_lo=1, capacity=40)
+    with pytest.raises(ValueError):
+        plan_document(synthetic.TINY, batch_lo=2, capacity=64, kv_layout="paged", num_blocks=4)

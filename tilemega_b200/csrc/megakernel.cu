@@ -54,9 +54,10 @@ struct Ctx {
   int deal;                          // round-robin cursor of the task dealer
   unsigned long long bar_target;     // arrivals that complete the previous stage
   uint32_t task_seq;                 // tasks finished by this CTA (epilogue warp rotation)
+  bool dead;                         // a bounded wait gave up: stop waiting, leave at the next boundary
   __device__ Ctx(const MegaParams& q, unsigned char* s)
       : p(q), smem(s), warp(threadIdx.x >> 5), lane(threadIdx.x & 31), tid(threadIdx.x), slot(0), phase(0),
-        deal(0), bar_target(q.bar_base), task_seq(0) {}
+        deal(0), bar_target(q.bar_base), task_seq(0), dead(false) {}
   __device__ uint64_t* full(int i) const { return reinterpret_cast<uint64_t*>(smem + kOffFull) + i; }
   __device__ uint64_t* empty(int i) const { return reinterpret_cast<uint64_t*>(smem + kOffEmpty) + i; }
   __device__ volatile int* ctl() const { return reinterpret_cast<volatile int*>(smem + kOffCtl); }
@@ -102,13 +103,19 @@ __device__ __noinline__ bool wait_give_up(const MegaParams& p, unsigned long lon
   return true;
 }
 
-__device__ __forceinline__ void mbar_wait(const MegaParams& p, uint64_t* bar, uint32_t parity, int site) {
-  if (mbar_try_wait(bar, parity)) return;
+// Returns false when the wait was abandoned; from then on this thread waits for nothing.
+__device__ __forceinline__ bool mbar_wait(Ctx& c, uint64_t* bar, uint32_t parity, int site) {
+  if (c.dead) return false;
+  if (mbar_try_wait(bar, parity)) return true;
   unsigned long long t0 = 0;
   uint32_t polls = 0;
   while (!mbar_try_wait(bar, parity)) {
-    if ((++polls & 127u) == 0 && wait_give_up(p, t0, site, parity, polls)) return;
+    if ((++polls & 127u) == 0 && wait_give_up(c.p, t0, site, parity, polls)) {
+      c.dead = true;
+      return false;
+    }
   }
+  return true;
 }
 
 // Arrive on the grid-wide counter: this CTA's stage outputs are in global memory.
@@ -198,6 +205,13 @@ __device__ __forceinline__ int table_entry(const MegaParams& p, int b, int blk) 
 // ---------------------------------------------------------------------------
 // streaming warp
 // ---------------------------------------------------------------------------
+// The whole warp takes the same decision, so no lane is left behind at a __syncwarp.
+__device__ __forceinline__ bool stream_wait_empty(Ctx& c) {
+  const bool ok = mbar_wait(c, c.empty(c.slot), c.phase ^ 1u, kSiteEmpty);
+  const bool all = __all_sync(0xffffffffu, ok);
+  if (!all) c.dead = true;
+  return all;
+}
 __device__ __forceinline__ void stream_gemv(Ctx& c, const GemvGeo& geo, const void* weights, uint64_t policy) {
   const uint32_t page_bytes = uint32_t(kTileN) * uint32_t(geo.tile_k) * 2u;
   const int kt = geo.k / geo.tile_k;
@@ -206,7 +220,7 @@ __device__ __forceinline__ void stream_gemv(Ctx& c, const GemvGeo& geo, const vo
     const unsigned char* src = static_cast<const unsigned char*>(weights) +
                                (size_t(rt) * kt + size_t(ks) * geo.pages_per_task) * page_bytes;
     for (int pg = 0; pg < geo.pages_per_task; ++pg) {
-      mbar_wait(c.p, c.empty(c.slot), c.phase ^ 1u, kSiteEmpty);
+      if (!stream_wait_empty(c)) return;
       if (c.lane == 0) {
         mbar_expect_tx(c.full(c.slot), page_bytes);
         bulk_g2s_hint(c.ring(c.slot), src + size_t(pg) * page_bytes, page_bytes, c.full(c.slot), policy);
@@ -228,7 +242,7 @@ __device__ __forceinline__ void stream_attn(Ctx& c, const LayerPtrs& lp, int pas
     const AttnTask a = attn_task(c.p, past, NK, spt, t);
     const int nblk = a.pos / kKvBlock + 1;
     for (int s = a.slot0; s < a.slot1; ++s) {
-      mbar_wait(c.p, c.empty(c.slot), c.phase ^ 1u, kSiteEmpty);
+      if (!stream_wait_empty(c)) return;
       const int nb = min(NB, nblk - s * NB);
       if (c.lane == 0) mbar_expect_tx(c.full(c.slot), uint32_t(nb) * 2u * BLKB);
       __syncwarp();
@@ -274,7 +288,7 @@ __device__ void streamer_main(Ctx& c) {
       stream_gemv(c, p.geo[kOProj], lp.o, policy);
       stream_gemv(c, p.geo[kGateUp], lp.gate_up, policy);
       stream_gemv(c, p.geo[kDown], lp.down, policy);
-      if (ld_relaxed(p.status + kStFired) != 0) return;
+      if (c.dead || ld_relaxed(p.status + kStFired) != 0) return;
     }
     stream_gemv(c, p.geo[kHead], p.lm_head, policy);
   }
@@ -465,7 +479,7 @@ __device__ void gemv_stage(Ctx& c, const GemvGeo& geo, const GemvIo& io) {
                                        size_t(c.lane >> 3) * geo.n + rt * kTileN + (c.lane & 7)));
     const int page0 = ks * geo.pages_per_task;
     for (int pg = 0; pg < geo.pages_per_task; ++pg) {
-      mbar_wait(p, c.full(c.slot), c.phase, kSiteFull);
+      mbar_wait(c, c.full(c.slot), c.phase, kSiteFull);
       gemv_page<B>(c.ring(c.slot), c.xs(), geo.k, (page0 + pg) * geo.tile_k, c.warp, c.lane, acc);
       __syncwarp();
       if (c.lane == 0) mbar_arrive(c.empty(c.slot));
@@ -517,8 +531,9 @@ __device__ void gemv_stage(Ctx& c, const GemvGeo& geo, const GemvIo& io) {
           h[size_t(b) * (geo.n >> 1) + rt * 4 + r] = __float2bfloat16_rn(silu_bf16(vb) * up);
         }
       } else if (io.epilogue == kEpiHead) {
-        if (apply && p.write_logits)
-          static_cast<__nv_bfloat16*>(io.out)[size_t(b) * geo.n + row] = __float2bfloat16_rn(v);
+        // the logits buffer keeps the fp32 accumulator; the argmax below compares the
+        // bf16-rounded value, as the reference's head epilogue does
+        if (apply && p.write_logits) static_cast<float*>(io.out)[size_t(b) * geo.n + row] = v;
         // ties -> smaller index (include/tilemega/Backend/Sm90DenseEpilogue.h:166-184)
         float bv = row < p.vocab ? vb : -INFINITY;
         int bi = row;
@@ -646,7 +661,7 @@ __device__ void attn_stage(Ctx& c, const LayerPtrs& lp, int past) {
       for (int j = 0; j < 8; ++j) acc[h][j] = 0.f;
     }
     for (int s = a.slot0; s < a.slot1; ++s) {
-      mbar_wait(p, c.full(c.slot), c.phase, kSiteFull);
+      mbar_wait(c, c.full(c.slot), c.phase, kSiteFull);
       unsigned char* kbase = c.ring(c.slot);
       unsigned char* vbase = kbase + kAttnHalfBytes;
       if (tail && s == a.ns - 1) {
@@ -952,32 +967,42 @@ __global__ void watchdog_probe_kernel(MegaParams p, int withhold) {
 }
 
 template <int B, int D, int GQ>
-static cudaError_t launch_instance(const MegaParams& p, size_t smem_bytes, cudaStream_t stream) {
+static cudaError_t run_instance(const MegaParams& p, size_t smem_bytes, cudaStream_t stream, bool prepare) {
   auto kernel = decode_megakernel<B, D, GQ>;
-  cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem_bytes));
-  if (err != cudaSuccess) return err;
-  int resident = 0;
-  err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, kernel, kThreads, smem_bytes);
-  if (err != cudaSuccess) return err;
-  int device = 0, sms = 0;
-  cudaGetDevice(&device);
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
-  // liveness: every CTA of the grid must be resident at once
-  // (include/tilemega/Codegen/tasks/Sm90DenseRuntime.cuh:304-308)
-  if (resident < 1 || p.grid > sms * resident) return cudaErrorLaunchOutOfResources;
+  if (prepare) {
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem_bytes));
+    if (err != cudaSuccess) return err;
+    int resident = 0;
+    err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, kernel, kThreads, smem_bytes);
+    if (err != cudaSuccess) return err;
+    int device = 0, sms = 0;
+    cudaGetDevice(&device);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    // liveness: every CTA of the grid must be resident at once
+    // (include/tilemega/Codegen/tasks/Sm90DenseRuntime.cuh:304-308)
+    return (resident < 1 || p.grid > sms * resident) ? cudaErrorLaunchOutOfResources : cudaSuccess;
+  }
   kernel<<<p.grid, kThreads, smem_bytes, stream>>>(p);
   return cudaGetLastError();
 }
 
 template <int D, int GQ>
-static cudaError_t launch_batch(const MegaParams& p, size_t smem_bytes, cudaStream_t stream) {
+static cudaError_t run_batch(const MegaParams& p, size_t smem_bytes, cudaStream_t stream, bool prepare) {
   switch (p.batch) {
-    case 1: return launch_instance<1, D, GQ>(p, smem_bytes, stream);
-    case 2: return launch_instance<2, D, GQ>(p, smem_bytes, stream);
-    case 3: return launch_instance<3, D, GQ>(p, smem_bytes, stream);
-    case 4: return launch_instance<4, D, GQ>(p, smem_bytes, stream);
+    case 1: return run_instance<1, D, GQ>(p, smem_bytes, stream, prepare);
+    case 2: return run_instance<2, D, GQ>(p, smem_bytes, stream, prepare);
+    case 3: return run_instance<3, D, GQ>(p, smem_bytes, stream, prepare);
+    case 4: return run_instance<4, D, GQ>(p, smem_bytes, stream, prepare);
     default: return cudaErrorInvalidValue;
   }
+}
+
+static cudaError_t run_decode(const MegaParams& p, cudaStream_t stream, bool prepare) {
+  const size_t smem_bytes = size_t(ring_offset(p.xs_bytes) + p.nslots * kSlotBytes);
+  if (p.kv_heads <= 0 || p.heads / p.kv_heads != 4) return cudaErrorInvalidValue;
+  if (p.head_dim == 128) return run_batch<128, 4>(p, smem_bytes, stream, prepare);
+  if (p.head_dim == 64) return run_batch<64, 4>(p, smem_bytes, stream, prepare);
+  return cudaErrorInvalidValue;
 }
 
 }  // namespace tmb
@@ -986,14 +1011,12 @@ extern "C" int tmb_smem_bytes(const tmb::MegaParams* p) {
   return tmb::ring_offset(p->xs_bytes) + p->nslots * tmb::kSlotBytes;
 }
 
+// Once per plan: opt in to the dynamic shared memory and prove that the whole
+// grid is co-resident (the kernel's grid barrier depends on it).
+extern "C" int tmb_prepare_decode(const tmb::MegaParams* p) { return int(tmb::run_decode(*p, nullptr, true)); }
+
 extern "C" int tmb_launch_decode(const tmb::MegaParams* p, void* stream) {
-  const size_t smem_bytes = size_t(tmb_smem_bytes(p));
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const int gq = p->heads / p->kv_heads;
-  if (gq != 4) return int(cudaErrorInvalidValue);
-  if (p->head_dim == 128) return int(tmb::launch_batch<128, 4>(*p, smem_bytes, s));
-  if (p->head_dim == 64) return int(tmb::launch_batch<64, 4>(*p, smem_bytes, s));
-  return int(cudaErrorInvalidValue);
+  return int(tmb::run_decode(*p, static_cast<cudaStream_t>(stream), false));
 }
 
 extern "C" int tmb_launch_watchdog_probe(const tmb::MegaParams* p, int withhold, void* stream) {

@@ -79,7 +79,7 @@ struct MegaParams {
   void* qkv;                   // bf16 [B][(Hq+2Hkv)*D]
   void* attn;                  // bf16 [B][Hq*D]
   void* h;                     // bf16 [B][I]
-  void* logits;                // bf16 [B][V]
+  void* logits;                // f32 [B][V]: head accumulators before the bf16 rounding
   float* gemv_part;            // [ksplit_max][B][Nmax] partial sums
   unsigned* gemv_cnt;          // [Nmax/8]
   float* attn_part;            // [grid + B*Hkv][Gq][D+2]

@@ -129,7 +129,7 @@ PlanSpec PlanSpec::FromJson(const Json& plan) {
   s.qkv_buf = add("serving.qkv", 0, 0, 0, uint64_t(s.qkv_rows()), "");
   s.attn_buf = add("serving.attention", 0, 0, 0, uint64_t(s.heads) * D, "");
   s.mlp_buf = add("serving.mlp", 0, 0, 0, I, "");
-  s.logits_buf = add("serving.logits", 0, 0, 0, V, "");
+  s.logits_buf = add("serving.logits", 0, 1, 0, V, "");  // fp32 accumulators of the head
   for (int l = 0; l < s.layers; ++l) {
     const std::string p = "l" + std::to_string(l) + ".";
     const std::string m = "model.layers." + std::to_string(l) + ".";

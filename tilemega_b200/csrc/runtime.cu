@@ -21,6 +21,7 @@
 #include "plan_spec.h"
 
 extern "C" int tmb_smem_bytes(const tmb::MegaParams* p);
+extern "C" int tmb_prepare_decode(const tmb::MegaParams* p);
 extern "C" int tmb_launch_decode(const tmb::MegaParams* p, void* stream);
 extern "C" int tmb_launch_watchdog_probe(const tmb::MegaParams* p, int withhold, void* stream);
 
@@ -353,6 +354,10 @@ void* tm_plan_create(int batch, void* const* external, int device) {
   p.step_ns = static_cast<unsigned long long*>(step_ns);
   plan->past_dev = static_cast<int*>(past);
   p.past = plan->past_dev;
+  {
+    const int status = tmb_prepare_decode(&p);
+    if (status != 0) return fail("the persistent grid does not fit the device", cudaError_t(status));
+  }
   if (cudaDeviceSynchronize() != cudaSuccess) return fail("initialisation", cudaGetLastError());
   return plan.release();
 }
