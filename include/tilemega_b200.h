@@ -106,6 +106,14 @@ int tm_plan_clear_watchdog(void* plan);
  * when `withhold` != 0; the waiter gives up after limit_us and the kernel
  * returns normally. Returns 1 if the wait gave up, 0 if it was satisfied. */
 int tm_plan_watchdog_probe(void* plan, int withhold, uint32_t limit_us, void* stream);
+/* Stage trace of one step (the reference's TILEMEGA_TRACE_STAGE build,
+ * include/tilemega/Codegen/tasks/ModelRuntime.h:758-766, as a run-time switch):
+ * step >= 0 records, for every CTA and stage of that step, four %globaltimer
+ * stamps {wait begin, inputs ready, rows staged, tasks done}; step < 0 turns it
+ * off. tm_plan_read_trace(plan, NULL, 0) returns the byte size, otherwise copies
+ * u64 [grid][5*layers+1][4]. A traced launch is for diagnosis, not for timing. */
+int tm_plan_trace_step(void* plan, int step);
+long long tm_plan_read_trace(void* plan, uint64_t* host, uint64_t bytes);
 /* Algorithmic HBM bytes of one decode step: GEMV weights incl. lm_head plus
  * 4*L*Hkv*D bytes per cached token (scripts/estimate_r16_mbu.py:15-38). */
 uint64_t tm_plan_step_bytes(void* plan, uint64_t cached_tokens_total);

@@ -21,10 +21,10 @@ from harness import GpuRun, bf16_ulp, bf16_weights
 pytestmark = pytest.mark.gpu
 
 
-def agreement(got, ref, what, ulps=1.0, exact_fraction=0.99):
+def agreement(got, ref, what, ulps=1.0, exact_fraction=0.99, floor=1e-6):
     got, ref = got.float(), ref.float()
     diff = (got - ref).abs()
-    within = diff <= ulps * bf16_ulp(ref) + 1e-6   # absolute floor: outputs that cancel to ~0
+    within = diff <= ulps * bf16_ulp(ref) + floor   # absolute floor: outputs that cancel to ~0
     exact = (diff == 0).float().mean().item()
     assert within.all(), f"{what}: {int((~within).sum())} elements differ by more than {ulps} ulp (max {diff.max().item()})"
     assert exact >= exact_fraction, f"{what}: only {exact:.4f} of the elements are bit-identical"
@@ -80,7 +80,9 @@ def test_every_stage_of_one_layer(base, batch, history, plan_dir):
     # stage 4: RMSNorm + gate/up + SwiGLU
     xm = rms_norm(x_mid, w[p + "post_attention_layernorm.weight"], eps)
     h_ref = F.silu(F.linear(xm, w[p + "mlp.gate_proj.weight"])) * F.linear(xm, w[p + "mlp.up_proj.weight"])
-    agreement(h_gpu, h_ref, "swiglu", ulps=2.0, exact_fraction=0.97)
+    # a product of two bf16 values that may each be one ulp off: the error scales with the
+    # factors (O(1) here), not with a product that happens to be small
+    agreement(h_gpu, h_ref, "swiglu", ulps=2.0, exact_fraction=0.97, floor=1e-3)
     # stage 5: down projection + residual (from the GPU's own activations)
     agreement(x_gpu, x_mid + F.linear(h_gpu, w[p + "mlp.down_proj.weight"]), "residual stream", ulps=2.0,
               exact_fraction=0.97)

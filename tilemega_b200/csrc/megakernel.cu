@@ -3,17 +3,19 @@
 // One launch runs `nsteps` decode steps of a Llama-shaped decoder. Every CTA
 // (one per SM) has one streaming warp and eight arithmetic warps:
 //
-//  * the streaming warp walks the CTA's share of the whole step -- every weight
-//    page of every GEMV stage and every KV block group of every attention stage,
-//    in program order -- and copies it into a shared-memory ring with
-//    cp.async.bulk. It never waits for a stage boundary, only for a free ring
-//    slot, so HBM keeps streaming while the arithmetic warps sit in a grid
-//    barrier or stage their activations.
-//  * the arithmetic warps walk the same list, wait for the stage's inputs (a
-//    grid-wide arrival counter with release/acquire), stage the activation rows
-//    in shared memory (RMSNorm fused), and consume ring slots: 128-bit
-//    shared-memory loads, fp32 FMA, the rounding sites of the reference's
-//    epilogues.
+//  * the streaming warp claims tasks of the current stage from a global counter
+//    (one atomicAdd per task, issued one task ahead), posts each task id into a
+//    small shared-memory FIFO and copies the task's data -- weight pages of a GEMV
+//    stage, KV block groups of an attention stage -- into a shared-memory ring
+//    with cp.async.bulk. It never waits for a stage boundary, only for a free ring
+//    slot, so HBM keeps streaming while the arithmetic warps sit in a grid barrier
+//    or stage their activations; and because tasks are claimed, not dealt, an SM
+//    that streams faster simply takes more of them and every stage ends together.
+//  * the arithmetic warps pop the FIFO, wait for the stage's inputs (a grid-wide
+//    arrival counter with release/acquire), stage the activation rows in shared
+//    memory (RMSNorm fused), and consume ring slots: 128-bit shared-memory loads,
+//    fp32 FMA, the rounding sites of the reference's epilogues. Results do not
+//    depend on which CTA ran a task, so the run-to-run bits are identical.
 //
 // Stage list per layer (reference: include/tilemega/Codegen/tasks/
 // Sm90DenseProgram.cuh:903-939): qkv (RMSNorm fused) -> RoPE + KV append +
@@ -28,38 +30,72 @@
 #include "params.h"
 #include "ptx.cuh"
 
+#ifndef TMB_SKIP
+#define TMB_SKIP 0   // bisecting hooks for the stage microbenchmark; 0 in the product
+#endif
+#ifndef TMB_PROFILE
+#define TMB_PROFILE 0   // cycle counters of the GEMV task loop for the stage microbenchmark
+#endif
+#if TMB_PROFILE
+__device__ long long g_prof[8];
+#define TMB_T(i) { long long now_ = clock64(); prof_[i] += now_ - last_; last_ = now_; }
+#else
+#define TMB_T(i)
+#endif
+#ifndef TMB_GEMV_MMA
+#define TMB_GEMV_MMA 1   // 1: weight pages through ldmatrix + mma.sync (bf16, fp32 accumulate); 0: fp32 FMA on CUDA cores
+#endif
+#ifndef TMB_MIXED_FMA
+#define TMB_MIXED_FMA 0
+#endif
+#ifndef TMB_GEMV_NOINLINE
+#define TMB_GEMV_NOINLINE 0
+#endif
+#if TMB_GEMV_NOINLINE
+#define TMB_GEMV_CALL __noinline__
+#else
+#define TMB_GEMV_CALL __forceinline__
+#endif
+
 namespace tmb {
 
 // ---------------------------------------------------------------------------
 // shared memory map (bytes)
 // ---------------------------------------------------------------------------
-constexpr int kOffFull = 0;
-constexpr int kOffEmpty = 64;
-constexpr int kOffCtl = 128;      // int[32]: [0] abort seen, [1] last-arriver flag
-constexpr int kOffTok = 256;      // int[8]
-constexpr int kOffBestVal = 288;  // float[8]
-constexpr int kOffBestIdx = 320;  // int[8]
-constexpr int kOffWsum = 384;     // float[8][8]
-constexpr int kOffRed = 640;      // float[2][8 warps][8 rows][kMaxBatch]
-constexpr int kOffSc = 4736;      // float[8 warps][4][16]
-constexpr int kOffXs = 6784;      // activation rows / attention scratch
+constexpr int kOffFull = 0;        // u64[8]  ring slot filled
+constexpr int kOffEmpty = 64;      // u64[8]  ring slot released by all arithmetic warps
+constexpr int kOffCtl = 128;       // int[8]: [0] abort seen, [1] last-arriver flag, [2] FIFO tail, [3] FIFO head, [4] popped task
+constexpr int kOffPFull = 192;     // u64[8]  all warps wrote their partial sums of a GEMV task
+constexpr int kOffTok = 256;       // int[8]
+constexpr int kOffFifo = 320;      // int[kFifo] task ids claimed by the streaming warp, -1 closes a stage
+constexpr int kOffBestVal = 448;   // float[8 warps][4]
+constexpr int kOffBestIdx = 576;   // int[8 warps][4]
+constexpr int kOffWsum = 704;      // float[4][8]
+constexpr int kOffSc = 832;        // float[8 warps][4][16]
+constexpr int kOffRed = 2880;      // float[kPartialRing][8 warps][8 rows][batch]: 2 KB per sequence of the batch
+constexpr int kFifo = 32;          // entries; the streaming warp keeps at most kFifo/2 unread
 
-__host__ __device__ inline int ring_offset(int xs_bytes) { return (kOffXs + xs_bytes + 1023) & ~1023; }
+__host__ __device__ inline int xs_offset(int batch) { return kOffRed + kPartialRing * 8 * 8 * 4 * batch; }   // activation rows / attention scratch
+__host__ __device__ inline int ring_offset(int xs_bytes, int batch) { return (xs_offset(batch) + xs_bytes + 1023) & ~1023; }
 
 struct Ctx {
   const MegaParams& p;
   unsigned char* smem;
   int warp, lane, tid;
   uint32_t slot, phase;              // ring cursor
-  int deal;                          // round-robin cursor of the task dealer
   unsigned long long bar_target;     // arrivals that complete the previous stage
   uint32_t task_seq;                 // tasks finished by this CTA (epilogue warp rotation)
   bool dead;                         // a bounded wait gave up: stop waiting, leave at the next boundary
+  uint32_t q_pos;                    // FIFO entries pushed (streaming warp) / popped (arithmetic warps)
+  uint32_t inst;                     // stage instances finished in this launch (index of the claim counter)
+  int pending;                       // streaming warp, lane 0: first task id claimed for the next stage
+  uint32_t gemv_seq;                 // GEMV tasks finished by this CTA (partial-sum ring cursor)
   __device__ Ctx(const MegaParams& q, unsigned char* s)
       : p(q), smem(s), warp(threadIdx.x >> 5), lane(threadIdx.x & 31), tid(threadIdx.x), slot(0), phase(0),
-        deal(0), bar_target(q.bar_base), task_seq(0), dead(false) {}
+        bar_target(q.bar_base), task_seq(0), dead(false), q_pos(0), inst(0), pending(0), gemv_seq(0) {}
   __device__ uint64_t* full(int i) const { return reinterpret_cast<uint64_t*>(smem + kOffFull) + i; }
   __device__ uint64_t* empty(int i) const { return reinterpret_cast<uint64_t*>(smem + kOffEmpty) + i; }
+  __device__ uint64_t* pfull(int i) const { return reinterpret_cast<uint64_t*>(smem + kOffPFull) + i; }
   __device__ volatile int* ctl() const { return reinterpret_cast<volatile int*>(smem + kOffCtl); }
   __device__ int* tok() const { return reinterpret_cast<int*>(smem + kOffTok); }
   __device__ float* best_val() const { return reinterpret_cast<float*>(smem + kOffBestVal); }
@@ -67,13 +103,12 @@ struct Ctx {
   __device__ float* wsum() const { return reinterpret_cast<float*>(smem + kOffWsum); }
   __device__ float* red() const { return reinterpret_cast<float*>(smem + kOffRed); }
   __device__ float* sc() const { return reinterpret_cast<float*>(smem + kOffSc); }
-  __device__ unsigned char* xs() const { return smem + kOffXs; }
-  __device__ unsigned char* ring(int i) const { return smem + ring_offset(p.xs_bytes) + i * kSlotBytes; }
+  __device__ unsigned char* xs() const { return smem + xs_offset(p.batch); }
+  __device__ unsigned char* ring(int i) const { return smem + ring_offset(p.xs_bytes, p.batch) + i * kSlotBytes; }
   __device__ void advance() {
     if (++slot == uint32_t(p.nslots)) { slot = 0; phase ^= 1u; }
   }
-  __device__ int first_task() const { return (int(blockIdx.x) + p.grid - deal) % p.grid; }
-  __device__ void dealt(int ntasks) { deal = (deal + ntasks) % p.grid; }
+  __device__ int* fifo() const { return reinterpret_cast<int*>(smem + kOffFifo); }
 };
 
 // ---------------------------------------------------------------------------
@@ -104,17 +139,38 @@ __device__ __noinline__ bool wait_give_up(const MegaParams& p, unsigned long lon
 }
 
 // Returns false when the wait was abandoned; from then on this thread waits for nothing.
+// For a single waiting thread (the streaming thread).
 __device__ __forceinline__ bool mbar_wait(Ctx& c, uint64_t* bar, uint32_t parity, int site) {
   if (c.dead) return false;
   if (mbar_try_wait(bar, parity)) return true;
   unsigned long long t0 = 0;
   uint32_t polls = 0;
   while (!mbar_try_wait(bar, parity)) {
-    if ((++polls & 127u) == 0 && wait_give_up(c.p, t0, site, parity, polls)) {
+    if ((++polls & 31u) == 0 && wait_give_up(c.p, t0, site, parity, polls)) {
       c.dead = true;
       return false;
     }
   }
+  return true;
+}
+
+// The same for a whole warp: only lane 0 polls (thirty-two lanes spinning on one
+// barrier word crowd the shared-memory pipeline that the other warps' loads and the
+// streaming thread's copies go through); afterwards every lane observes the
+// completed phase once itself, which is its acquire of the data behind it.
+__device__ __forceinline__ bool mbar_wait_warp(Ctx& c, uint64_t* bar, uint32_t parity, int site) {
+  if (c.dead) return false;
+  // the common case: already there. One decision for the warp (lanes polling at
+  // slightly different moments may see different answers).
+  if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity))) return true;
+  bool ok = true;
+  if (c.lane == 0) ok = mbar_wait(c, bar, parity, site);
+  ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+  if (!ok) {
+    c.dead = true;
+    return false;
+  }
+  mbar_try_wait(bar, parity);
   return true;
 }
 
@@ -142,6 +198,18 @@ __device__ __forceinline__ bool grid_wait(Ctx& c) {
   }
   consumer_sync();
   return c.ctl()[0] == 0;
+}
+
+// Optional stage trace (one chosen step): per CTA and stage, %globaltimer when the
+// CTA started waiting for the stage's inputs, when they were there, when its
+// activation rows were staged and when its last task was done. The reference's
+// counterpart is the TILEMEGA_TRACE_STAGE build
+// (include/tilemega/Codegen/tasks/ModelRuntime.h:758-766).
+__device__ __forceinline__ void trace_mark(const Ctx& c, bool on, int stage, int what) {
+  if (on && c.tid == 0) {
+    const int stages = 5 * c.p.layers + 1;
+    c.p.trace[(size_t(blockIdx.x) * stages + stage) * 4 + what] = global_timer();
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -203,32 +271,127 @@ __device__ __forceinline__ int table_entry(const MegaParams& p, int b, int blk) 
 }
 
 // ---------------------------------------------------------------------------
-// streaming warp
+// task FIFO between the streaming thread and the arithmetic warps. One 32-bit
+// word per entry carries both the task id (low 20 bits; 0xFFFFF closes a stage)
+// and the entry's sequence number (high 12 bits), so a reader needs exactly one
+// load and no ordering between two locations.
 // ---------------------------------------------------------------------------
-// The whole warp takes the same decision, so no lane is left behind at a __syncwarp.
-__device__ __forceinline__ bool stream_wait_empty(Ctx& c) {
-  const bool ok = mbar_wait(c, c.empty(c.slot), c.phase ^ 1u, kSiteEmpty);
-  const bool all = __all_sync(0xffffffffu, ok);
-  if (!all) c.dead = true;
-  return all;
-}
-__device__ __forceinline__ void stream_gemv(Ctx& c, const GemvGeo& geo, const void* weights, uint64_t policy) {
-  const uint32_t page_bytes = uint32_t(kTileN) * uint32_t(geo.tile_k) * 2u;
-  const int kt = geo.k / geo.tile_k;
-  for (int t = c.first_task(); t < geo.ntasks; t += c.p.grid) {
-    const int rt = t / geo.ksplit, ks = t - rt * geo.ksplit;
-    const unsigned char* src = static_cast<const unsigned char*>(weights) +
-                               (size_t(rt) * kt + size_t(ks) * geo.pages_per_task) * page_bytes;
-    for (int pg = 0; pg < geo.pages_per_task; ++pg) {
-      if (!stream_wait_empty(c)) return;
-      if (c.lane == 0) {
-        mbar_expect_tx(c.full(c.slot), page_bytes);
-        bulk_g2s_hint(c.ring(c.slot), src + size_t(pg) * page_bytes, page_bytes, c.full(c.slot), policy);
+constexpr uint32_t kFifoClose = 0xFFFFFu;
+
+__device__ __forceinline__ uint32_t fifo_word(uint32_t pos, uint32_t value) { return ((pos + 1u) << 20) | value; }
+
+// Streaming thread: append one entry (a task id, or -1 to close the stage).
+__device__ __forceinline__ void fifo_push(Ctx& c, int value) {
+  if (!c.dead) {
+    volatile int* head = c.ctl() + 3;
+    if (int(c.q_pos) - *head >= kFifo / 2) {
+      unsigned long long t0 = 0;
+      uint32_t polls = 0;
+      while (int(c.q_pos) - *head >= kFifo / 2) {
+        if ((++polls & 255u) == 0 && wait_give_up(c.p, t0, kSiteEmpty, c.q_pos, uint32_t(*head))) break;
       }
-      c.advance();
+    }
+    reinterpret_cast<volatile uint32_t*>(c.fifo())[c.q_pos & (kFifo - 1)] =
+        fifo_word(c.q_pos, value < 0 ? kFifoClose : uint32_t(value));
+  }
+  ++c.q_pos;
+}
+
+// Arithmetic thread: next entry of the FIFO; -1 closes the stage, -2 means the
+// launch is being abandoned (also treated as the end of the stage).
+__device__ __forceinline__ int fifo_pop(Ctx& c) {
+  const volatile uint32_t* slot = reinterpret_cast<volatile uint32_t*>(c.fifo()) + (c.q_pos & (kFifo - 1));
+  const uint32_t tag = (c.q_pos + 1u) & 0xFFFu;
+  uint32_t word = *slot;
+  if (!c.dead && (word >> 20) != tag) {
+    unsigned long long t0 = 0;
+    uint32_t polls = 0;
+    while (((word = *slot) >> 20) != tag) {
+      if ((++polls & 255u) == 0 && wait_give_up(c.p, t0, kSiteFull, c.q_pos, word)) {
+        c.dead = true;
+        break;
+      }
     }
   }
-  c.dealt(geo.ntasks);
+  if (c.dead) return -2;
+  ++c.q_pos;
+  if (c.tid == 0) c.ctl()[3] = int(c.q_pos);
+  const uint32_t value = word & kFifoClose;
+  return value == kFifoClose ? -1 : int(value);
+}
+
+// The same, decided once for all arithmetic warps (stages whose tasks contain
+// CTA-wide barriers must agree on every task, also while giving up).
+__device__ __forceinline__ int fifo_pop_uniform(Ctx& c) {
+  if (c.tid == 0) c.ctl()[4] = fifo_pop(c);
+  consumer_sync();
+  const int v = c.ctl()[4];
+  if (c.tid != 0 && v != -2) ++c.q_pos;
+  return v;
+}
+
+// ---------------------------------------------------------------------------
+// streaming warp: ONE thread runs it. A lone warp issues slowly next to eight
+// busy arithmetic warps, so every instruction on this path costs ring refill rate;
+// the loop is kept to a wait, a byte-count arrive and a bulk copy per slot.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ bool stream_wait_empty(Ctx& c) {
+  return mbar_wait(c, c.empty(c.slot), c.phase ^ 1u, kSiteEmpty);
+}
+
+// Claim the next task of stage instance `inst`. The value is not needed until the
+// current task's copies are issued, so the atomic's round trip overlaps them.
+__device__ __forceinline__ int claim(const Ctx& c, uint32_t inst) {
+  return int(atomicAdd(c.p.stage_cnt + inst, 1u));
+}
+
+// Close the stage: tell the arithmetic warps, and claim the first task of the next
+// stage right away.
+__device__ __forceinline__ void stream_close(Ctx& c) {
+  fifo_push(c, -1);
+  ++c.inst;
+  c.pending = claim(c, c.inst);
+}
+
+// One GEMV task: post its id, then copy its weight pages into the ring.
+__device__ __forceinline__ void stream_gemv_task(Ctx& c, const GemvGeo& geo, const unsigned char* weights, int t,
+                                                 uint32_t page_bytes, uint64_t policy) {
+  fifo_push(c, t);
+  // pages of a task are consecutive: task t = (row tile, k split) starts at page t * pages_per_task
+  const unsigned char* src = weights + size_t(t) * size_t(geo.pages_per_task) * page_bytes;
+  for (int pg = 0; pg < geo.pages_per_task; ++pg, src += page_bytes) {
+    if (!stream_wait_empty(c)) return;
+    if (c.p.diag & kDiagNoCopy) {
+      mbar_arrive(c.full(c.slot));   // diagnosis: arithmetic warps at their own speed on whatever is in the ring
+    } else {
+      mbar_expect_tx(c.full(c.slot), page_bytes);
+      bulk_g2s_hint(c.ring(c.slot), src, page_bytes, c.full(c.slot), policy);
+    }
+    c.advance();
+  }
+}
+
+// static_quarters/4 of a CTA's even share of a stage are dealt statically (task
+// cta + j*grid), so the first pages of the next stage are known without a round
+// trip and stream behind the current stage's last ones; the rest is claimed from
+// the stage's counter, so the stage still ends together on every SM.
+__device__ __forceinline__ int static_share(const MegaParams& p, int ntasks) {
+  return (ntasks / p.grid) * p.static_quarters / 4;
+}
+
+__device__ __forceinline__ void stream_gemv(Ctx& c, const GemvGeo& geo, const void* weights, uint64_t policy) {
+  const uint32_t page_bytes = uint32_t(kTileN) * uint32_t(geo.tile_k) * 2u;
+  const unsigned char* w = static_cast<const unsigned char*>(weights);
+  const int dealt = static_share(c.p, geo.ntasks);
+  for (int j = 0; j < dealt && !c.dead; ++j)
+    stream_gemv_task(c, geo, w, int(blockIdx.x) + j * c.p.grid, page_bytes, policy);
+  int t = dealt * c.p.grid + c.pending;
+  while (t < geo.ntasks && !c.dead) {
+    const int upcoming = claim(c, c.inst);
+    stream_gemv_task(c, geo, w, t, page_bytes, policy);
+    t = dealt * c.p.grid + upcoming;
+  }
+  stream_close(c);
 }
 
 template <int D>
@@ -238,26 +401,38 @@ __device__ __forceinline__ void stream_attn(Ctx& c, const LayerPtrs& lp, int pas
   constexpr uint32_t BLKB = kKvBlock * D * 2;    // bytes of one block of one head
   int spt, ntasks;
   attn_shape(c.p, past, NK, spt, ntasks);
-  for (int t = c.first_task(); t < ntasks; t += c.p.grid) {
+  int t = c.pending;
+  while (t < ntasks && !c.dead) {
+    const int upcoming = claim(c, c.inst);
+    fifo_push(c, t);
     const AttnTask a = attn_task(c.p, past, NK, spt, t);
     const int nblk = a.pos / kKvBlock + 1;
     for (int s = a.slot0; s < a.slot1; ++s) {
-      if (!stream_wait_empty(c)) return;
-      const int nb = min(NB, nblk - s * NB);
-      if (c.lane == 0) mbar_expect_tx(c.full(c.slot), uint32_t(nb) * 2u * BLKB);
-      __syncwarp();
-      if (c.lane < nb) {
-        const long long e = table_entry(c.p, a.b, s * NB + c.lane);
-        const long long off = (e * c.p.kv_block_stride + (long long)a.g * c.p.kv_head_stride) * 2;
-        unsigned char* dst = c.ring(c.slot) + c.lane * BLKB;
-        bulk_g2s(dst, static_cast<const unsigned char*>(lp.k_pool) + off, BLKB, c.full(c.slot));
-        bulk_g2s(dst + kAttnHalfBytes, static_cast<const unsigned char*>(lp.v_pool) + off, BLKB,
-                 c.full(c.slot));
+      const int nb = (c.p.diag & kDiagNoCopy) ? 0 : min(NB, nblk - s * NB);
+      // the block-table entries of the slot first (independent loads), then the copies
+      long long off[NB];
+#pragma unroll
+      for (int j = 0; j < NB; ++j) {
+        const long long e = table_entry(c.p, a.b, s * NB + min(j, max(nb - 1, 0)));
+        off[j] = (e * c.p.kv_block_stride + (long long)a.g * c.p.kv_head_stride) * 2;
+      }
+      if (!stream_wait_empty(c)) break;
+      if (nb) mbar_expect_tx(c.full(c.slot), uint32_t(nb) * 2u * BLKB);
+      else mbar_arrive(c.full(c.slot));
+      unsigned char* dst = c.ring(c.slot);
+#pragma unroll
+      for (int j = 0; j < NB; ++j) {
+        if (j < nb) {
+          bulk_g2s(dst + j * BLKB, static_cast<const unsigned char*>(lp.k_pool) + off[j], BLKB, c.full(c.slot));
+          bulk_g2s(dst + kAttnHalfBytes + j * BLKB, static_cast<const unsigned char*>(lp.v_pool) + off[j], BLKB,
+                   c.full(c.slot));
+        }
       }
       c.advance();
     }
+    t = upcoming;
   }
-  c.dealt(ntasks);
+  stream_close(c);
 }
 
 template <int D>
@@ -265,6 +440,8 @@ __device__ void streamer_main(Ctx& c) {
   const MegaParams& p = c.p;
   const uint64_t policy = policy_evict_first();
   const unsigned long long bars_per_step = 5ull * p.layers + 1ull;
+  const uint32_t norm_bytes = uint32_t(p.hidden) * 2u;
+  c.pending = claim(c, 0);
   for (int si = 0; si < p.nsteps; ++si) {
     const int past = __ldg(p.past + p.first_step + si);
     // KV rows appended by the previous step were written with ordinary stores by
@@ -273,6 +450,9 @@ __device__ void streamer_main(Ctx& c) {
     bool kv_ordered = si == 0;
     for (int l = 0; l < p.layers; ++l) {
       const LayerPtrs lp = p.layer[l];
+      // the RMSNorm weights are read by every CTA right after a barrier: have them in L2 by then
+      bulk_prefetch_l2(lp.norm1, norm_bytes);
+      bulk_prefetch_l2(lp.norm2, norm_bytes);
       stream_gemv(c, p.geo[kQkv], lp.qkv, policy);
       if (!kv_ordered) {
         const unsigned long long need = p.bar_base + bars_per_step * (unsigned long long)si * p.grid;
@@ -290,6 +470,7 @@ __device__ void streamer_main(Ctx& c) {
       stream_gemv(c, p.geo[kDown], lp.down, policy);
       if (c.dead || ld_relaxed(p.status + kStFired) != 0) return;
     }
+    bulk_prefetch_l2(p.final_norm, norm_bytes);
     stream_gemv(c, p.geo[kHead], p.lm_head, policy);
   }
 }
@@ -326,11 +507,15 @@ struct GemvIo {
 
 // Stage the stage's B activation rows in shared memory; RMSNorm fused:
 // y = bf16(w * bf16(x * rsqrt(mean(x^2) + eps)))  (python/tilemega/serving/export.py:24-27).
+// The norm weights travel in the same pass as the rows (into row B of the
+// staging area) so that their L2 round trip overlaps the rows'.
 template <int B>
 __device__ __forceinline__ void stage_rows(Ctx& c, const GemvIo& io, int k) {
   const MegaParams& p = c.p;
   const int chunks = k >> 3;
+  const int pitch = chunks + 1;   // rows are k + 8 elements apart: 16 bytes of padding keep ldmatrix row reads on distinct banks
   uint4* xs4 = reinterpret_cast<uint4*>(c.xs());
+  const uint4* nw = reinterpret_cast<const uint4*>(io.norm);
   float ss[B];
 #pragma unroll
   for (int b = 0; b < B; ++b) {
@@ -346,7 +531,8 @@ __device__ __forceinline__ void stage_rows(Ctx& c, const GemvIo& io, int k) {
     float acc = 0.f;
     for (int i = c.tid; i < chunks; i += kConsumerThreads) {
       const uint4 v = io.embed ? __ldg(src + i) : __ldcg(src + i);
-      xs4[b * chunks + i] = v;
+      if (b == 0 && io.norm) xs4[B * pitch + i] = __ldg(nw + i);
+      xs4[b * pitch + i] = v;
       if (own) xg[i] = v;
       if (io.norm) {
         float f[8];
@@ -366,7 +552,6 @@ __device__ __forceinline__ void stage_rows(Ctx& c, const GemvIo& io, int k) {
       if (c.lane == 0) c.wsum()[b * 8 + c.warp] = v;
     }
     consumer_sync();
-    const uint4* nw = reinterpret_cast<const uint4*>(io.norm);
 #pragma unroll
     for (int b = 0; b < B; ++b) {
       float total = 0.f;
@@ -375,8 +560,8 @@ __device__ __forceinline__ void stage_rows(Ctx& c, const GemvIo& io, int k) {
       const float inv = 1.0f / sqrtf(total / float(k) + p.eps);
       for (int i = c.tid; i < chunks; i += kConsumerThreads) {
         float f[8], w[8];
-        unpack8(xs4[b * chunks + i], f);
-        unpack8(__ldg(nw + i), w);
+        unpack8(xs4[b * pitch + i], f);
+        unpack8(xs4[B * pitch + i], w);   // written by this same thread above
         uint32_t o[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -384,7 +569,7 @@ __device__ __forceinline__ void stage_rows(Ctx& c, const GemvIo& io, int k) {
           const uint32_t hi = bf16_bits(w[2 * j + 1] * bf16_round(f[2 * j + 1] * inv));
           o[j] = lo | (hi << 16);
         }
-        xs4[b * chunks + i] = make_uint4(o[0], o[1], o[2], o[3]);
+        xs4[b * pitch + i] = make_uint4(o[0], o[1], o[2], o[3]);
       }
     }
   }
@@ -395,25 +580,61 @@ __device__ __forceinline__ void stage_rows(Ctx& c, const GemvIo& io, int k) {
 // element (r, col) sits at 1024*(col/64) + 128*r + 16*((col%64/8) ^ r) + 2*(col%8)
 // bytes (python/tilemega/serving/weights.py:239-240 with tn = 8). Warp w owns
 // columns [256w, 256w+256), lane l the 8 columns 8l.. of that segment.
+// CUDA-core form: lane l of warp w multiplies its 8 columns of each of the 8 rows.
 template <int B>
-__device__ __forceinline__ void gemv_page(const unsigned char* page, const unsigned char* xs, int k,
-                                          int col0, int warp, int lane, float (&acc)[kTileN][B]) {
-  float xv[B][8];
+__device__ __forceinline__ void gemv_page_fma(const unsigned char* page, const unsigned char* xs, int k, int col0,
+                                              int warp, int lane, float (&acc)[kTileN][B]) {
+  uint4 xv[B];
 #pragma unroll
-  for (int b = 0; b < B; ++b) {
-    const uint4 v = *reinterpret_cast<const uint4*>(xs + (size_t(b) * k + col0 + 256 * warp + 8 * lane) * 2);
-    unpack8(v, xv[b]);
-  }
+  for (int b = 0; b < B; ++b)
+    xv[b] = *reinterpret_cast<const uint4*>(xs + (size_t(b) * (k + 8) + col0 + 256 * warp + 8 * lane) * 2);
   const unsigned char* pg = page + 1024 * (4 * warp + (lane >> 3));
   const int sw = lane & 7;
 #pragma unroll
   for (int r = 0; r < kTileN; ++r) {
-    float w[8];
-    unpack8(*reinterpret_cast<const uint4*>(pg + 128 * r + 16 * (sw ^ r)), w);
+    const uint4 w = *reinterpret_cast<const uint4*>(pg + 128 * r + 16 * (sw ^ r));
 #pragma unroll
-    for (int b = 0; b < B; ++b)
+    for (int b = 0; b < B; ++b) {
+#if TMB_MIXED_FMA
+      fma_bf16x2(acc[r][b], w.x, xv[b].x);
+      fma_bf16x2(acc[r][b], w.y, xv[b].y);
+      fma_bf16x2(acc[r][b], w.z, xv[b].z);
+      fma_bf16x2(acc[r][b], w.w, xv[b].w);
+#else
+      float wf[8], xf[8];
+      unpack8(w, wf);
+      unpack8(xv[b], xf);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) acc[r][b] = fmaf(w[j], xv[b][j], acc[r][b]);
+      for (int j = 0; j < 8; ++j) acc[r][b] = fmaf(wf[j], xf[j], acc[r][b]);
+#endif
+    }
+  }
+}
+
+// Tensor-pipe form of the same page: D[batch row][weight row] += X * W^T with
+// mma.sync m16n8k16. The 8 weight rows of the page are the B operand's 8 columns
+// (an 8x64 swizzle atom of the page IS four ldmatrix tiles), the batch rows are the A
+// operand's rows 0..7 (rows past the batch alias row B-1 and their outputs are never
+// read; rows 8..15 are zero). The pipe converts bf16 to fp32 itself, so a page costs
+// a warp 16 ldmatrix + 16 mma instead of ~140 CUDA-core instructions, at any batch
+// up to 8. Four accumulator sets keep the dependent chains short.
+template <int B>
+__device__ __forceinline__ void gemv_page_mma(const unsigned char* page, const unsigned char* xs, int k, int col0,
+                                              int warp, int lane, float (&d)[4][4]) {
+  const int r = lane & 7, m = lane >> 3;                 // ldmatrix: row r of matrix m
+  const int brow = min(r, B - 1);
+  const uint32_t xa = smem_u32(xs) + uint32_t((size_t(brow) * (k + 8) + col0 + 256 * warp + 8 * m) * 2);
+  const uint32_t wa = smem_u32(page) + uint32_t(1024 * (4 * warp) + 128 * r);
+#pragma unroll
+  for (int cb = 0; cb < 4; ++cb) {
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      uint32_t w[4], x[4];
+      ldmatrix_x4(w, wa + 1024 * cb + 16 * ((4 * half + m) ^ r));
+      ldmatrix_x4(x, xa + 2 * (64 * cb + 32 * half));
+      mma_bf16_m16n8k16(d[2 * half], x[0], x[1], w[0], w[1]);
+      mma_bf16_m16n8k16(d[2 * half + 1], x[2], x[3], w[2], w[3]);
+    }
   }
 }
 
@@ -455,111 +676,184 @@ __device__ __forceinline__ float silu_bf16(float g) {
   return bf16_round(g / (1.0f + expf(-g)));
 }
 
+// Everything the epilogue of one GEMV task needs, kept by the warp that owns it.
+struct PendingEpilogue {
+  int task;         // -1: none
+  int buf;
+  uint32_t lap;
+  float residual;   // prefetched residual element of this lane (kEpiResidual)
+};
+
+// Epilogue of one task, run by one warp: sum the eight warps' partial sums in warp
+// order, then apply the stage's rounding sites. lane = b*8 + r.
 template <int B>
-__device__ void gemv_stage(Ctx& c, const GemvGeo& geo, const GemvIo& io) {
+__device__ __forceinline__ void gemv_epilogue(Ctx& c, const GemvGeo& geo, const GemvIo& io, const PendingEpilogue& e,
+                                              int lane, float& best_val, int& best_idx) {
+  const MegaParams& p = c.p;
+  const float* red = c.red();
+  mbar_wait_warp(c, c.pfull(e.buf), e.lap, kSiteFull);
+  if (lane < kTileN * B) {
+    // kTileN*B <= 32 lanes take part, `mask` names exactly them
+    constexpr unsigned mask = kTileN * B >= 32 ? 0xffffffffu : ((1u << (kTileN * B)) - 1u);
+    const int rt = e.task;
+    const int r = lane & 7, b = lane >> 3;
+    const int row = rt * kTileN + r;
+    float v = 0.f;
+#pragma unroll
+    for (int w = 0; w < kConsumerWarps; ++w) v += red[((e.buf * 8 + w) * 8 + r) * B + b];
+    constexpr bool apply = true;
+    const float vb = bf16_round(v);
+    if (io.epilogue == kEpiSwiGLU) {
+      // rows 0..3 of the page are gate rows, rows 4..7 the matching up rows
+      const float up = __shfl_down_sync(mask, vb, 4);
+      if (apply && r < 4) {
+        __nv_bfloat16* h = static_cast<__nv_bfloat16*>(io.out);
+        h[size_t(b) * (geo.n >> 1) + rt * 4 + r] = __float2bfloat16_rn(silu_bf16(vb) * up);
+      }
+    } else if (io.epilogue == kEpiHead) {
+      // the logits buffer keeps the fp32 accumulator; the argmax below compares the
+      // bf16-rounded value, as the reference's head epilogue does
+      if (apply && p.write_logits) static_cast<float*>(io.out)[size_t(b) * geo.n + row] = v;
+      // ties -> smaller index (include/tilemega/Backend/Sm90DenseEpilogue.h:166-184)
+      float bv = row < p.vocab ? vb : -INFINITY;
+      int bi = row;
+#pragma unroll
+      for (int m = 1; m < 8; m <<= 1) {
+        const float ov = __shfl_xor_sync(mask, bv, m);
+        const int oi = __shfl_xor_sync(mask, bi, m);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+      }
+      if (apply && (bv > best_val || (bv == best_val && bi < best_idx))) {
+        best_val = bv;   // lanes 8b..8b+7 all hold sequence b's candidate
+        best_idx = bi;
+      }
+    } else if (apply) {
+      __nv_bfloat16* out = static_cast<__nv_bfloat16*>(io.out) + size_t(b) * geo.n + row;
+      if (io.epilogue == kEpiResidual) {
+        // bf16(float(bf16(acc)) + float(residual)) (ServingEpilogue.h:38-43)
+        *out = __float2bfloat16_rn(vb + e.residual);
+      } else {
+        *out = __float2bfloat16_rn(v);
+      }
+    }
+  }
+}
+
+template <int B>
+__device__ TMB_GEMV_CALL void gemv_stage(Ctx& c, const GemvGeo& geo, const GemvIo& io, bool tr, int stage) {
   const MegaParams& p = c.p;
   stage_rows<B>(c, io, geo.k);
-  if (io.epilogue == kEpiHead && c.tid < B) {
-    c.best_val()[c.tid] = -INFINITY;
-    c.best_idx()[c.tid] = 0x7fffffff;
-  }
+  trace_mark(c, tr, stage, 2);
+  // per-warp running argmax (each warp runs every eighth epilogue); merged by the caller
+  float best_val = -INFINITY;
+  int best_idx = 0x7fffffff;
   float* red = c.red();
-  for (int t = c.first_task(); t < geo.ntasks; t += p.grid) {
-    const int rt = t / geo.ksplit, ks = t - rt * geo.ksplit;
+  uint32_t slot = c.slot, phase = c.phase, task_seq = c.task_seq, gemv_seq = c.gemv_seq;
+  const int warp = c.warp, lane = c.lane;
+  const uint32_t nslots = uint32_t(p.nslots);
+  unsigned char* const ring0 = c.ring(0);
+  const unsigned char* const xs = c.xs();
+  uint64_t* const full0 = c.full(0);
+  uint64_t* const empty0 = c.empty(0);
+  // Warp (n mod 8) owns the epilogue of this CTA's n-th task and runs it one task
+  // late, after its own pages of task n+1: by then the other warps' partial sums
+  // have long arrived, so no warp ever waits for another one here, and the cost of
+  // an epilogue is spread as one eighth per task instead of stalling every task.
+  // Warp (n mod 8) owns the epilogue of this CTA's n-th task and runs it one task
+  // late, after its own pages of task n+1: by then the other warps' partial sums
+  // have long arrived, so no warp ever waits for another one here, and the cost of
+  // an epilogue is spread as one eighth per task instead of stalling every task.
+  PendingEpilogue pending{-1, 0, 0u, 0.f};
+#if TMB_PROFILE
+  long long prof_[8] = {0, 0, 0, 0, 0, 0, 0, 0}, last_ = clock64();
+#endif
+  for (int t = fifo_pop(c); t >= 0; t = fifo_pop(c)) {
+    TMB_T(0)
+    const int rt = t;
+#if TMB_GEMV_MMA
+    float d[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) d[0][i] = d[1][i] = d[2][i] = d[3][i] = 0.f;
+#else
     float acc[kTileN][B];
 #pragma unroll
     for (int r = 0; r < kTileN; ++r)
 #pragma unroll
       for (int b = 0; b < B; ++b) acc[r][b] = 0.f;
-    // the warp that will run this task's epilogue fetches the residual now, so the
-    // L2 round trip overlaps the page arithmetic instead of delaying the next task
+#endif
+    const bool owner = warp == int(task_seq & 7);
+    // the owner fetches the residual now, so the L2 round trip overlaps the arithmetic
     float residual = 0.f;
-    if (io.epilogue == kEpiResidual && c.warp == int(c.task_seq & 7) && c.lane < kTileN * B)
+    if (io.epilogue == kEpiResidual && owner && lane < kTileN * B)
       residual = bf16_from_bits(__ldcg(reinterpret_cast<const unsigned short*>(io.out) +
-                                       size_t(c.lane >> 3) * geo.n + rt * kTileN + (c.lane & 7)));
-    const int page0 = ks * geo.pages_per_task;
+                                       size_t(lane >> 3) * geo.n + rt * kTileN + (lane & 7)));
     for (int pg = 0; pg < geo.pages_per_task; ++pg) {
-      mbar_wait(c, c.full(c.slot), c.phase, kSiteFull);
-      gemv_page<B>(c.ring(c.slot), c.xs(), geo.k, (page0 + pg) * geo.tile_k, c.warp, c.lane, acc);
+      TMB_T(1)
+      mbar_wait_warp(c, full0 + slot, phase, kSiteFull);
+      TMB_T(2)
+#if !(TMB_SKIP & 4)
+#if TMB_GEMV_MMA
+      gemv_page_mma<B>(ring0 + slot * kSlotBytes, xs, geo.k, pg * geo.tile_k, warp, lane, d);
+#else
+      gemv_page_fma<B>(ring0 + slot * kSlotBytes, xs, geo.k, pg * geo.tile_k, warp, lane, acc);
+#endif
+#endif
+      TMB_T(3)
       __syncwarp();
-      if (c.lane == 0) mbar_arrive(c.empty(c.slot));
-      c.advance();
+      if (lane == 0) mbar_arrive(empty0 + slot);
+      if (++slot == nslots) { slot = 0; phase ^= 1u; }
+      TMB_T(4)
     }
-    // lanes -> warps -> (k-splits) in a fixed order, so results are run-to-run identical
-    const int buf = c.task_seq & 1;
+    // lanes -> warps in a fixed order, so results are run-to-run identical. The warps
+    // hand their partial sums over through a small ring of buffers guarded by mbarriers.
+    const int buf = gemv_seq & (kPartialRing - 1);
+    const uint32_t lap = (gemv_seq / kPartialRing) & 1u;
+    // No wait before reusing buffer `buf`: its previous task lies kPartialRing tasks
+    // back, and no warp can be more than the data ring (at most kMaxSlots pages, so
+    // at most kMaxSlots tasks) ahead of the owner that reads it one task late.
+    TMB_T(5)
+#if TMB_GEMV_MMA
+    // lane holds D[batch row lane/4][weight rows 2*(lane%4), +1]
+    if ((lane >> 2) < B) {
+      float* dst = red + ((buf * 8 + warp) * 8 + 2 * (lane & 3)) * B + (lane >> 2);
+      dst[0] = (d[0][0] + d[1][0]) + (d[2][0] + d[3][0]);
+      dst[B] = (d[0][1] + d[1][1]) + (d[2][1] + d[3][1]);
+    }
+#else
 #pragma unroll
     for (int b = 0; b < B; ++b) {
       float v[kTileN];
 #pragma unroll
       for (int r = 0; r < kTileN; ++r) v[r] = acc[r][b];
-      warp_reduce_rows(v, c.lane);
-      if ((c.lane & 3) == 0) red[((buf * 8 + c.warp) * 8 + (c.lane >> 2)) * kMaxBatch + b] = v[0];
+      warp_reduce_rows(v, lane);
+      if ((lane & 3) == 0) red[((buf * 8 + warp) * 8 + (lane >> 2)) * B + b] = v[0];
     }
-    consumer_sync();
-    if (c.warp == int(c.task_seq & 7) && c.lane < kTileN * B) {
-      // lane = b*8 + r; kTileN*B <= 32 lanes take part, `mask` names exactly them
-      constexpr unsigned mask = kTileN * B >= 32 ? 0xffffffffu : ((1u << (kTileN * B)) - 1u);
-      const int r = c.lane & 7, b = c.lane >> 3;
-      const int row = rt * kTileN + r;
-      float v = 0.f;
-#pragma unroll
-      for (int w = 0; w < kConsumerWarps; ++w) v += red[((buf * 8 + w) * 8 + r) * kMaxBatch + b];
-      bool apply = true;
-      if (geo.ksplit > 1) {
-        p.gemv_part[(size_t(ks) * B + b) * geo.n + row] = v;
-        __threadfence();
-        __syncwarp(mask);
-        unsigned old = 0;
-        if (c.lane == 0) {
-          old = atomicAdd(p.gemv_cnt + rt, 1u);
-          if (old == unsigned(geo.ksplit - 1)) atomicExch(p.gemv_cnt + rt, 0u);
-        }
-        old = __shfl_sync(mask, old, 0);
-        apply = old == unsigned(geo.ksplit - 1);
-        if (apply) {
-          __threadfence();
-          v = 0.f;
-          for (int s = 0; s < geo.ksplit; ++s) v += __ldcg(p.gemv_part + (size_t(s) * B + b) * geo.n + row);
-        }
-      }
-      const float vb = bf16_round(v);
-      if (io.epilogue == kEpiSwiGLU) {
-        // rows 0..3 of the page are gate rows, rows 4..7 the matching up rows
-        const float up = __shfl_down_sync(mask, vb, 4);
-        if (apply && r < 4) {
-          __nv_bfloat16* h = static_cast<__nv_bfloat16*>(io.out);
-          h[size_t(b) * (geo.n >> 1) + rt * 4 + r] = __float2bfloat16_rn(silu_bf16(vb) * up);
-        }
-      } else if (io.epilogue == kEpiHead) {
-        // the logits buffer keeps the fp32 accumulator; the argmax below compares the
-        // bf16-rounded value, as the reference's head epilogue does
-        if (apply && p.write_logits) static_cast<float*>(io.out)[size_t(b) * geo.n + row] = v;
-        // ties -> smaller index (include/tilemega/Backend/Sm90DenseEpilogue.h:166-184)
-        float bv = row < p.vocab ? vb : -INFINITY;
-        int bi = row;
-#pragma unroll
-        for (int m = 1; m < 8; m <<= 1) {
-          const float ov = __shfl_xor_sync(mask, bv, m);
-          const int oi = __shfl_xor_sync(mask, bi, m);
-          if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
-        }
-        if (apply && r == 0 && (bv > c.best_val()[b] || (bv == c.best_val()[b] && bi < c.best_idx()[b]))) {
-          c.best_val()[b] = bv;
-          c.best_idx()[b] = bi;
-        }
-      } else if (apply) {
-        __nv_bfloat16* out = static_cast<__nv_bfloat16*>(io.out) + size_t(b) * geo.n + row;
-        if (io.epilogue == kEpiResidual) {
-          // bf16(float(bf16(acc)) + float(residual)) (ServingEpilogue.h:38-43)
-          *out = __float2bfloat16_rn(vb + residual);
-        } else {
-          *out = __float2bfloat16_rn(v);
-        }
-      }
+#endif
+    __syncwarp();
+    if (lane == 0) mbar_arrive(c.pfull(buf));
+    if (pending.task >= 0) {
+      gemv_epilogue<B>(c, geo, io, pending, lane, best_val, best_idx);
+      pending.task = -1;
     }
-    ++c.task_seq;
+    if (owner) pending = PendingEpilogue{t, buf, lap, residual};
+    ++task_seq;
+    ++gemv_seq;
+    TMB_T(6)
   }
-  c.dealt(geo.ntasks);
+#if TMB_PROFILE
+  if (blockIdx.x == 0 && threadIdx.x == 0)
+    for (int i = 0; i < 8; ++i) g_prof[i] = prof_[i];
+#endif
+  if (pending.task >= 0) gemv_epilogue<B>(c, geo, io, pending, lane, best_val, best_idx);
+  c.slot = slot;
+  c.phase = phase;
+  c.task_seq = task_seq;
+  c.gemv_seq = gemv_seq;
+  if (io.epilogue == kEpiHead && lane < kTileN * B && (lane & 7) == 0) {
+    c.best_val()[warp * kMaxBatch + (lane >> 3)] = best_val;
+    c.best_idx()[warp * kMaxBatch + (lane >> 3)] = best_idx;
+  }
+  trace_mark(c, tr, stage, 3);
 }
 
 // ---------------------------------------------------------------------------
@@ -587,7 +881,7 @@ __device__ __forceinline__ void subgroup_reduce_scatter(float (&v)[N], int hl) {
 }
 
 template <int B, int D, int GQ>
-__device__ void attn_stage(Ctx& c, const LayerPtrs& lp, int past) {
+__device__ void attn_stage(Ctx& c, const LayerPtrs& lp, int past, bool tr, int stage) {
   constexpr int NK = kAttnHalfBytes / (2 * D);  // keys per slot: 64 (D=128) / 128 (D=64)
   constexpr int LPK = D / 8;                    // lanes that share one key row
   constexpr int KPW = 32 / LPK;                 // sub-groups per warp
@@ -609,8 +903,9 @@ __device__ void attn_stage(Ctx& c, const LayerPtrs& lp, int past) {
 
   int spt, ntasks;
   attn_shape(p, past, NK, spt, ntasks);
-  for (int t = c.first_task(); t < ntasks; t += p.grid) {
-    const AttnTask a = attn_task(p, past, NK, spt, t);
+  trace_mark(c, tr, stage, 2);
+  for (int t = fifo_pop_uniform(c); t >= 0; t = fifo_pop_uniform(c)) {
+    const AttnTask a = attn_task(p, past, NK, spt, min(t, ntasks - 1));
     const bool tail = a.c == a.nch - 1;  // this chunk holds the new token
     // ---- q (GQ heads) and the new k: RoPE with bf16 tables, each product and the
     // sum rounded to bf16 (include/tilemega/Codegen/tasks/FusedAttentionTaskBody.h:141-151)
@@ -661,7 +956,7 @@ __device__ void attn_stage(Ctx& c, const LayerPtrs& lp, int past) {
       for (int j = 0; j < 8; ++j) acc[h][j] = 0.f;
     }
     for (int s = a.slot0; s < a.slot1; ++s) {
-      mbar_wait(c, c.full(c.slot), c.phase, kSiteFull);
+      mbar_wait_warp(c, c.full(c.slot), c.phase, kSiteFull);
       unsigned char* kbase = c.ring(c.slot);
       unsigned char* vbase = kbase + kAttnHalfBytes;
       if (tail && s == a.ns - 1) {
@@ -822,14 +1117,32 @@ __device__ void attn_stage(Ctx& c, const LayerPtrs& lp, int past) {
         const float* parts = p.attn_part + size_t(a.task0) * GQ * PW;
         for (int o = c.tid; o < GQ * D; o += kConsumerThreads) {
           const int h = o / D, d = o - h * D;
-          float mx = -INFINITY;
-          for (int ch = 0; ch < a.nch; ++ch) mx = fmaxf(mx, __ldcg(parts + (size_t(ch) * GQ + h) * PW + D));
-          float ls = 0.f, as = 0.f;
-          for (int ch = 0; ch < a.nch; ++ch) {
-            const float* src = parts + (size_t(ch) * GQ + h) * PW;
-            const float wgt = ex2(__ldcg(src + D) - mx);
-            ls = fmaf(__ldcg(src + D + 1), wgt, ls);
-            as = fmaf(__ldcg(src + d), wgt, as);
+          // chunks in ascending order, eight at a time so that their loads are in
+          // flight together (one L2 round trip per batch instead of one per chunk)
+          float mx = -INFINITY, ls = 0.f, as = 0.f;
+          for (int c0 = 0; c0 < a.nch; c0 += 8) {
+            float mc[8], lc[8], ac[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const bool live = c0 + j < a.nch;
+              const float* src = parts + (size_t(live ? c0 + j : c0) * GQ + h) * PW;
+              mc[j] = live ? __ldcg(src + D) : -INFINITY;
+              lc[j] = live ? __ldcg(src + D + 1) : 0.f;
+              ac[j] = live ? __ldcg(src + d) : 0.f;
+            }
+            float mb = mx;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) mb = fmaxf(mb, mc[j]);
+            const float rescale = ex2(mx - mb);   // mb is finite: chunk c0 exists and holds a valid key
+            ls *= rescale;
+            as *= rescale;
+            mx = mb;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float wgt = ex2(mc[j] - mb);
+              ls = fmaf(lc[j], wgt, ls);
+              as = fmaf(ac[j], wgt, as);
+            }
           }
           out[o] = __float2bfloat16_rn(as / ls);
         }
@@ -838,7 +1151,7 @@ __device__ void attn_stage(Ctx& c, const LayerPtrs& lp, int past) {
     }
     ++c.task_seq;
   }
-  c.dealt(ntasks);
+  trace_mark(c, tr, stage, 3);
 }
 
 // ---------------------------------------------------------------------------
@@ -857,39 +1170,63 @@ __device__ void consumer_main(Ctx& c) {
       consumer_sync();
     }
     if (blockIdx.x == 0 && c.tid == 0) p.step_ns[step] = global_timer();
+    const bool tr = p.trace != nullptr && step == p.trace_step;
+    int stage = 0;
+    LayerPtrs lp = p.layer[0];
     for (int l = 0; l < p.layers; ++l) {
-      const LayerPtrs lp = p.layer[l];
+      // the next layer's pointer record is fetched a whole layer ahead of its use
+      const LayerPtrs upcoming = p.layer[min(l + 1, p.layers - 1)];
       GemvIo io;
       // qkv: RMSNorm fused; layer 0 reads the embedding rows and seeds the residual stream
+      trace_mark(c, tr, stage, 0);
       if (l > 0) {
         if (!grid_wait(c)) return;
       }
+      trace_mark(c, tr, stage, 1);
       io = GemvIo{l == 0 ? p.embed : p.x, lp.norm1, l == 0, kEpiStore, p.qkv};
-      gemv_stage<B>(c, p.geo[kQkv], io);
+      gemv_stage<B>(c, p.geo[kQkv], io, tr, stage++);
       grid_arrive(c);
+      trace_mark(c, tr, stage, 0);
       if (!grid_wait(c)) return;
-      attn_stage<B, D, GQ>(c, lp, past);
+      trace_mark(c, tr, stage, 1);
+      attn_stage<B, D, GQ>(c, lp, past, tr, stage++);
       grid_arrive(c);
+      trace_mark(c, tr, stage, 0);
       if (!grid_wait(c)) return;
+      trace_mark(c, tr, stage, 1);
       io = GemvIo{p.attn, nullptr, 0, kEpiResidual, p.x};
-      gemv_stage<B>(c, p.geo[kOProj], io);
+      gemv_stage<B>(c, p.geo[kOProj], io, tr, stage++);
       grid_arrive(c);
+      trace_mark(c, tr, stage, 0);
       if (!grid_wait(c)) return;
+      trace_mark(c, tr, stage, 1);
       io = GemvIo{p.x, lp.norm2, 0, kEpiSwiGLU, p.h};
-      gemv_stage<B>(c, p.geo[kGateUp], io);
+      gemv_stage<B>(c, p.geo[kGateUp], io, tr, stage++);
       grid_arrive(c);
+      trace_mark(c, tr, stage, 0);
       if (!grid_wait(c)) return;
+      trace_mark(c, tr, stage, 1);
       io = GemvIo{p.h, nullptr, 0, kEpiResidual, p.x};
-      gemv_stage<B>(c, p.geo[kDown], io);
+      gemv_stage<B>(c, p.geo[kDown], io, tr, stage++);
       grid_arrive(c);
+      lp = upcoming;
     }
+    trace_mark(c, tr, stage, 0);
     if (!grid_wait(c)) return;
+    trace_mark(c, tr, stage, 1);
     GemvIo io{p.x, p.final_norm, 0, kEpiHead, p.logits};
-    gemv_stage<B>(c, p.geo[kHead], io);
+    gemv_stage<B>(c, p.geo[kHead], io, tr, stage);
     consumer_sync();
     if (c.tid < B) {
-      p.argmax_val[size_t(blockIdx.x) * B + c.tid] = c.best_val()[c.tid];
-      p.argmax_idx[size_t(blockIdx.x) * B + c.tid] = c.best_idx()[c.tid];
+      float bv = -INFINITY;
+      int bi = 0x7fffffff;
+      for (int w = 0; w < kConsumerWarps; ++w) {
+        const float v = c.best_val()[w * kMaxBatch + c.tid];
+        const int i = c.best_idx()[w * kMaxBatch + c.tid];
+        if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+      }
+      p.argmax_val[size_t(blockIdx.x) * B + c.tid] = bv;
+      p.argmax_idx[size_t(blockIdx.x) * B + c.tid] = bi;
     }
     grid_arrive(c);
     if (!grid_wait(c)) return;
@@ -937,14 +1274,19 @@ __global__ void __launch_bounds__(kThreads, 1) decode_megakernel(const __grid_co
       mbar_init(c.full(i), 1);
       mbar_init(c.empty(i), kConsumerWarps);
     }
+    for (int i = 0; i < kPartialRing; ++i) {
+      mbar_init(c.pfull(i), kConsumerWarps);
+    }
     mbar_fence_init();
-    c.ctl()[0] = 0;
-    c.ctl()[1] = 0;
+    for (int i = 0; i < 8; ++i) c.ctl()[i] = 0;
+    for (int i = 0; i < kFifo; ++i) c.fifo()[i] = 0;   // sequence tag 0 never matches
   }
   __syncthreads();
-  if (c.warp == kConsumerWarps) {
-    streamer_main<D>(c);
-    streamer_drain(c);
+  if (c.warp >= kConsumerWarps) {
+    if (c.lane == 0) {
+      streamer_main<D>(c);
+      streamer_drain(c);
+    }
   } else {
     consumer_main<B, D, GQ>(c);
   }
@@ -998,7 +1340,7 @@ static cudaError_t run_batch(const MegaParams& p, size_t smem_bytes, cudaStream_
 }
 
 static cudaError_t run_decode(const MegaParams& p, cudaStream_t stream, bool prepare) {
-  const size_t smem_bytes = size_t(ring_offset(p.xs_bytes) + p.nslots * kSlotBytes);
+  const size_t smem_bytes = size_t(ring_offset(p.xs_bytes, p.batch) + p.nslots * kSlotBytes);
   if (p.kv_heads <= 0 || p.heads / p.kv_heads != 4) return cudaErrorInvalidValue;
   if (p.head_dim == 128) return run_batch<128, 4>(p, smem_bytes, stream, prepare);
   if (p.head_dim == 64) return run_batch<64, 4>(p, smem_bytes, stream, prepare);
@@ -1008,7 +1350,7 @@ static cudaError_t run_decode(const MegaParams& p, cudaStream_t stream, bool pre
 }  // namespace tmb
 
 extern "C" int tmb_smem_bytes(const tmb::MegaParams* p) {
-  return tmb::ring_offset(p->xs_bytes) + p->nslots * tmb::kSlotBytes;
+  return tmb::ring_offset(p->xs_bytes, p->batch) + p->nslots * tmb::kSlotBytes;
 }
 
 // Once per plan: opt in to the dynamic shared memory and prove that the whole

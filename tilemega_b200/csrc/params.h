@@ -7,12 +7,13 @@ namespace tmb {
 
 constexpr int kConsumerWarps = 8;                       // warps that do arithmetic
 constexpr int kConsumerThreads = kConsumerWarps * 32;   // 256
-constexpr int kThreads = kConsumerThreads + 32;         // + one streaming warp
+constexpr int kThreads = kConsumerThreads + 32;         // + one streaming warp (one thread of it works)
 constexpr int kSlotBytes = 32768;                       // one ring slot = one weight page / KV group
 constexpr int kMaxSlots = 6;
 constexpr int kTileN = 8;                               // weight rows per page (one 128B-swizzle atom)
 constexpr int kKvBlock = 16;                            // tokens per KV block
-constexpr int kMaxBatch = 8;                            // SIMT GEMV path
+constexpr int kMaxBatch = 4;                            // SIMT GEMV path
+constexpr int kPartialRing = 8;                         // GEMV tasks whose warp partials may be in flight (> ring slots + 1)
 constexpr int kAttnHalfBytes = kSlotBytes / 2;          // K part, then V part, of an attention slot
 
 enum StageKind : int { kQkv = 0, kOProj = 1, kGateUp = 2, kDown = 3, kHead = 4, kNumGemv = 5 };
@@ -25,9 +26,8 @@ enum Epilogue : int { kEpiStore = 0, kEpiResidual = 1, kEpiSwiGLU = 2, kEpiHead 
 struct GemvGeo {
   int n, k;            // output rows, reduction length
   int tile_k;          // columns per page; multiple of 256*? (see kernel)
-  int ksplit;          // tasks per row tile; partial sums merged by the last arriver
-  int pages_per_task;  // k / tile_k / ksplit
-  int ntasks;          // (n / 8) * ksplit
+  int pages_per_task;  // k / tile_k: a task is one 8-row tile over the whole reduction
+  int ntasks;          // n / 8
 };
 
 struct LayerPtrs {
@@ -46,6 +46,8 @@ enum StatusWord : int {
   kStFired = 0, kStSite, kStBlock, kStThread, kStStage, kStTask, kStProducer,
   kStGroup, kStRow, kStNeed, kStValue, kStIteration, kStWords
 };
+// Diagnostic switches (plan sidecar "diag"): results are meaningless when any is set.
+enum DiagFlag : int { kDiagNoCopy = 1 };   // the streaming warp posts ring slots without copying into them
 enum WaitSite : int { kSiteGrid = 1, kSiteFull = 2, kSiteEmpty = 3, kSiteDrain = 4, kSiteTest = 5 };
 
 struct MegaParams {
@@ -60,6 +62,8 @@ struct MegaParams {
   int first_step, nsteps, prompt_len;
   int write_logits;
   int grid, nslots, xs_bytes;
+  int diag;                 // DiagFlag bits
+  int static_quarters;      // quarters of a CTA's even share of a GEMV stage that are dealt, not claimed (0..4)
   unsigned long long bar_base;     // grid-barrier arrivals before this launch
   unsigned long long watchdog_ns;  // per-wait limit
   GemvGeo geo[kNumGemv];
@@ -80,15 +84,16 @@ struct MegaParams {
   void* attn;                  // bf16 [B][Hq*D]
   void* h;                     // bf16 [B][I]
   void* logits;                // f32 [B][V]: head accumulators before the bf16 rounding
-  float* gemv_part;            // [ksplit_max][B][Nmax] partial sums
-  unsigned* gemv_cnt;          // [Nmax/8]
   float* attn_part;            // [grid + B*Hkv][Gq][D+2]
   unsigned* attn_cnt;          // [B*Hkv]
   float* argmax_val;           // [grid][B]
   int* argmax_idx;             // [grid][B]
+  unsigned* stage_cnt;         // [nsteps*(5*layers+1)+1] task claim counters, zero at launch
   unsigned long long* bar;     // grid barrier arrivals (monotonic)
   unsigned long long* status;  // [kStWords]
   unsigned long long* step_ns; // [capacity+1] %globaltimer stamps
+  unsigned long long* trace;   // [grid][5*layers+1][4] stage stamps of step trace_step, or null
+  int trace_step;
 };
 
 // Per-step, per-sequence attention partition shared by the streaming warp and

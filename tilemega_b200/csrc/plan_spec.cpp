@@ -32,18 +32,15 @@ GemvGeo MakeGeo(const char* what, int n, int k, const Json& overrides) {
   g.n = n;
   g.k = k;
   g.tile_k = 2048;
-  g.ksplit = 1;
   if (overrides.has(what)) {
     g.tile_k = int(overrides.at(what).integer("tile_k", g.tile_k));
-    g.ksplit = int(overrides.at(what).integer("ksplit", g.ksplit));
   }
   if (g.tile_k != 2048) throw std::invalid_argument(std::string(what) + ": tile_k must be 2048");
   if (n <= 0 || n % kTileN) throw std::invalid_argument(std::string(what) + ": rows must be a multiple of 8");
   if (k <= 0 || k % g.tile_k) throw std::invalid_argument(std::string(what) + ": K must be a multiple of tile_k");
   const int kt = k / g.tile_k;
-  if (g.ksplit < 1 || kt % g.ksplit) throw std::invalid_argument(std::string(what) + ": ksplit must divide K/tile_k");
-  g.pages_per_task = kt / g.ksplit;
-  g.ntasks = (n / kTileN) * g.ksplit;
+  g.pages_per_task = kt;
+  g.ntasks = n / kTileN;
   return g;
 }
 
@@ -96,6 +93,9 @@ PlanSpec PlanSpec::FromJson(const Json& plan) {
   }
   s.grid = int(plan.integer("grid", 0));
   s.slots = int(plan.integer("slots", 0));
+  s.diag = int(plan.integer("diag", 0));
+  s.static_quarters = int(plan.integer("static_quarters", s.static_quarters));
+  if (s.static_quarters < 0 || s.static_quarters > 4) throw std::invalid_argument("static_quarters must lie in [0, 4]");
   s.write_logits = plan.flag("write_logits", true);
   const Json& geometry = plan.has("geometry") ? plan.at("geometry") : empty;
   s.geo[kQkv] = MakeGeo("qkv", s.qkv_rows(), s.hidden, geometry);

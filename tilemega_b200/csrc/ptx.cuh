@@ -43,6 +43,23 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// try_wait that may stay suspended for up to `hint_ns` before reporting failure: the
+// hardware wakes the thread when the phase completes, so a long hint costs no
+// latency and keeps a waiting thread from occupying the shared-memory pipeline.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      " .reg .pred p;\n"
+      " mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+      " selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+
 // Contiguous global -> shared bulk copy, completion counted in bytes on `bar`.
 // Both addresses 16-byte aligned, size a multiple of 16.
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
@@ -61,6 +78,23 @@ __device__ __forceinline__ void bulk_g2s_hint(void* dst, const void* src, uint32
           "r"(smem_u32(dst)),
       "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
       : "memory");
+}
+
+// Global -> L2 prefetch of a contiguous range (no shared memory involved).
+__device__ __forceinline__ void bulk_prefetch_l2(const void* src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
+
+// Register reallocation between warpgroups (all warps of a warpgroup execute the
+// same instruction): the streaming warpgroup gives registers up, the arithmetic
+// warpgroups take them.
+template <int Regs>
+__device__ __forceinline__ void warpgroup_reg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(Regs));
+}
+template <int Regs>
+__device__ __forceinline__ void warpgroup_reg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(Regs));
 }
 
 __device__ __forceinline__ uint64_t policy_evict_first() {
@@ -111,6 +145,40 @@ __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
   f[2] = bf_lo(v.y); f[3] = bf_hi(v.y);
   f[4] = bf_lo(v.z); f[5] = bf_hi(v.z);
   f[6] = bf_lo(v.w); f[7] = bf_hi(v.w);
+}
+
+// Four 8x8 b16 matrices from shared memory: lane l supplies the address of row
+// l%8 of matrix l/8 and receives elements 2*(l%4), 2*(l%4)+1 of row l/4 of each.
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t smem_addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem_addr));
+}
+
+// D[16x8] += A[16x16] * B[16x8], bf16 operands, fp32 accumulators. Rows 8..15 of A
+// are zero here (the batch has at most 8 rows), so a1 = a3 = 0.
+__device__ __forceinline__ void mma_bf16_m16n8k16(float (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+}
+
+// acc += w.lo * x.lo, then acc += w.hi * x.hi, on packed bf16 pairs with the
+// sm_100 mixed-precision FMA (bf16 x bf16 + f32 -> f32, exact product, one
+// rounding): the same result as converting both operands to fp32 first, without
+// the conversion instructions.
+__device__ __forceinline__ void fma_bf16x2(float& acc, uint32_t w, uint32_t x) {
+  asm("{\n"
+      " .reg .b16 a0, a1, b0, b1;\n"
+      " mov.b32 {a0, a1}, %1;\n"
+      " mov.b32 {b0, b1}, %2;\n"
+      " fma.rn.f32.bf16 %0, a0, b0, %0;\n"
+      " fma.rn.f32.bf16 %0, a1, b1, %0;\n"
+      "}\n"
+      : "+f"(acc)
+      : "r"(w), "r"(x));
 }
 
 // Round-to-nearest-even fp32 -> bf16, returned as the fp32 value it represents.

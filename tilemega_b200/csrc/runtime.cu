@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 #include <dlfcn.h>
 
+#include <algorithm>
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
@@ -101,8 +102,12 @@ struct Plan {
   uint64_t next_iteration[3] = {0, 0, 0};
   int prompt_len = 0;
   size_t smem_bytes = 0;
+  unsigned long long* trace_dev = nullptr;
+  size_t trace_bytes = 0;
+  int trace_step = -1;
   unsigned char* sync_block = nullptr;  // barrier + counters, rezeroed by every launch
   size_t sync_bytes = 0;
+  size_t claim_offset = 0;
 };
 
 Plan* AsPlan(void* handle) {
@@ -244,9 +249,13 @@ void* tm_plan_create(int batch, void* const* external, int device) {
   p.watchdog_ns = (unsigned long long)(std::max(watchdog_ms, 0.001) * 1e6);
   // shared memory: activation rows (or the attention scratch, whichever is larger) + ring
   const int attention_scratch = 4 * s.head_dim * 4 + 2 * s.head_dim * 2 + 8 * 4 * (s.head_dim + 2) * 4;
-  int xs = std::max(batch * s.max_k() * 2, attention_scratch);
+  // rows of the widest GEMV input; one extra hidden-wide row holds the RMSNorm weights
+  // (rows are padded by 8 elements so that the batch rows of a k-chunk sit on distinct banks)
+  int xs = std::max({batch * (s.max_k() + 8) * 2, (batch + 1) * (s.hidden + 8) * 2, attention_scratch});
   xs = (xs + 127) & ~127;
   p.xs_bytes = xs;
+  p.static_quarters = s.static_quarters;
+  p.diag = s.diag;
   const int limit = int(prop.sharedMemPerBlockOptin);
   p.nslots = tmb::kMaxSlots;
   if (s.slots > 0) p.nslots = std::min(s.slots, tmb::kMaxSlots);
@@ -309,20 +318,14 @@ void* tm_plan_create(int batch, void* const* external, int device) {
   p.h = plan->buffer_ptr[s.mlp_buf];
   p.logits = plan->buffer_ptr[s.logits_buf];
   // scratch
-  int ksplit_max = 1, n_max = 0;
-  for (int g = 0; g < tmb::kNumGemv; ++g) {
-    ksplit_max = std::max(ksplit_max, s.geo[g].ksplit);
-    n_max = std::max(n_max, s.geo[g].n);
-  }
   struct Scratch {
     void** out;
     size_t bytes;
   };
-  void *gemv_part = nullptr, *attn_part = nullptr, *argmax_val = nullptr, *argmax_idx = nullptr, *status = nullptr,
+  void *attn_part = nullptr, *argmax_val = nullptr, *argmax_idx = nullptr, *status = nullptr,
        *step_ns = nullptr, *past = nullptr;
   const size_t attn_tasks = size_t(p.grid) + size_t(batch) * s.kv_heads + 1;
   const Scratch scratch[] = {
-      {&gemv_part, size_t(ksplit_max) * batch * n_max * sizeof(float)},
       {&attn_part, attn_tasks * 4 * (s.head_dim + 2) * sizeof(float)},
       {&argmax_val, size_t(p.grid) * batch * sizeof(float)},
       {&argmax_idx, size_t(p.grid) * batch * sizeof(int)},
@@ -334,9 +337,12 @@ void* tm_plan_create(int batch, void* const* external, int device) {
     cudaError_t err = Alloc(*plan, item.out, item.bytes);
     if (err != cudaSuccess) return fail("scratch", err);
   }
-  // barrier word, then the GEMV and attention arrival counters: one block, rezeroed per launch
-  const size_t gemv_cnt = size_t(n_max / tmb::kTileN), attn_cnt = size_t(batch) * s.kv_heads;
-  plan->sync_bytes = 128 + (gemv_cnt + attn_cnt) * sizeof(unsigned);
+  // barrier word, then the attention arrival counters: one block, rezeroed per launch
+  const size_t attn_cnt = size_t(batch) * s.kv_heads;
+  // ... and the task claim counters of every stage instance of the longest possible launch
+  const size_t stage_cnt = size_t(s.capacity) * (5 * size_t(s.layers) + 1) + 1;
+  plan->claim_offset = 128 + attn_cnt * sizeof(unsigned);
+  plan->sync_bytes = plan->claim_offset + stage_cnt * sizeof(unsigned);
   {
     void* dev = nullptr;
     cudaError_t err = Alloc(*plan, &dev, plan->sync_bytes);
@@ -344,9 +350,8 @@ void* tm_plan_create(int batch, void* const* external, int device) {
     plan->sync_block = static_cast<unsigned char*>(dev);
   }
   p.bar = reinterpret_cast<unsigned long long*>(plan->sync_block);
-  p.gemv_cnt = reinterpret_cast<unsigned*>(plan->sync_block + 128);
-  p.attn_cnt = p.gemv_cnt + gemv_cnt;
-  p.gemv_part = static_cast<float*>(gemv_part);
+  p.attn_cnt = reinterpret_cast<unsigned*>(plan->sync_block + 128);
+  p.stage_cnt = reinterpret_cast<unsigned*>(plan->sync_block + plan->claim_offset);
   p.attn_part = static_cast<float*>(attn_part);
   p.argmax_val = static_cast<float*>(argmax_val);
   p.argmax_idx = static_cast<int*>(argmax_idx);
@@ -395,12 +400,16 @@ int tm_plan_launch_steps(void* handle, uint32_t first_step, uint32_t steps, uint
     return Fail(-2, "tm_plan_launch_steps: iteration is not the number of previous launches of this mode");
   DeviceScope scope(plan->device);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  cudaError_t err = cudaMemsetAsync(plan->sync_block, 0, plan->sync_bytes, s);
+  // only the claim counters this launch can touch are rezeroed
+  const size_t used = plan->claim_offset + (size_t(steps) * (5 * size_t(plan->params.layers) + 1) + 1) * sizeof(unsigned);
+  cudaError_t err = cudaMemsetAsync(plan->sync_block, 0, used, s);
   if (err != cudaSuccess) return Fail(int(err), std::string("tm_plan_launch_steps: ") + cudaGetErrorString(err));
   tmb::MegaParams p = plan->params;
   p.first_step = int(first_step);
   p.nsteps = int(steps);
   p.prompt_len = plan->prompt_len;
+  p.trace = plan->trace_step >= 0 ? plan->trace_dev : nullptr;
+  p.trace_step = plan->trace_step;
   const int status = tmb_launch_decode(&p, stream);
   if (status != 0)
     return Fail(status, std::string("tm_plan_launch_steps: ") + cudaGetErrorString(cudaError_t(status)));
@@ -469,6 +478,31 @@ int tm_plan_watchdog_probe(void* handle, int withhold, uint32_t limit_us, void* 
   const int fired = tm_plan_watchdog(handle, record);
   tm_plan_clear_watchdog(handle);
   return fired;
+}
+
+int tm_plan_trace_step(void* handle, int step) {
+  Plan* plan = AsPlan(handle);
+  if (!plan) return Fail(-1, "tm_plan_trace_step: bad plan");
+  DeviceScope scope(plan->device);
+  if (step >= 0 && !plan->trace_dev) {
+    plan->trace_bytes = size_t(plan->params.grid) * (5 * size_t(plan->params.layers) + 1) * 4 * sizeof(unsigned long long);
+    void* dev = nullptr;
+    cudaError_t err = Alloc(*plan, &dev, plan->trace_bytes);
+    if (err != cudaSuccess) return Fail(int(err), cudaGetErrorString(err));
+    plan->trace_dev = static_cast<unsigned long long*>(dev);
+  }
+  plan->trace_step = step;
+  return 0;
+}
+
+long long tm_plan_read_trace(void* handle, uint64_t* host, uint64_t bytes) {
+  Plan* plan = AsPlan(handle);
+  if (!plan || !plan->trace_dev) return Fail(-1, "tm_plan_read_trace: no trace was requested");
+  if (!host) return (long long)plan->trace_bytes;
+  if (bytes < plan->trace_bytes) return Fail(-1, "tm_plan_read_trace: buffer too small");
+  DeviceScope scope(plan->device);
+  cudaError_t err = cudaMemcpy(host, plan->trace_dev, plan->trace_bytes, cudaMemcpyDeviceToHost);
+  return err == cudaSuccess ? (long long)plan->trace_bytes : Fail(int(err), cudaGetErrorString(err));
 }
 
 unsigned tm_plan_pdl_enabled(void*) { return 0; }

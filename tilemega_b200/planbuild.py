@@ -23,7 +23,8 @@ MODEL_KEYS = ("hidden_size", "intermediate_size", "num_attention_heads", "num_ke
 
 def plan_document(config: dict, *, batch_lo: int = 1, batch_hi: int | None = None, capacity: int,
                   kv_layout: str = "contiguous", num_blocks: int = 0, geometry: dict | None = None,
-                  grid: int = 0, slots: int = 0, write_logits: bool = True) -> dict:
+                  grid: int = 0, slots: int = 0, write_logits: bool = True,
+                  static_quarters: int | None = None, diag: int = 0) -> dict:
     """The sidecar for one decode plan; raises ValueError on shapes the kernels do not cover."""
     model = {key: config[key] for key in MODEL_KEYS if key in config}
     model.setdefault("head_dim", config["hidden_size"] // config["num_attention_heads"])
@@ -43,6 +44,10 @@ def plan_document(config: dict, *, batch_lo: int = 1, batch_hi: int | None = Non
         "kv": {"layout": kv_layout, "block": 16, "num_blocks": num_blocks},
         "geometry": geometry or {}, "grid": grid, "slots": slots, "write_logits": write_logits,
     }
+    if static_quarters is not None:
+        document["static_quarters"] = static_quarters
+    if diag:
+        document["diag"] = diag   # diagnostic switches: results are meaningless when set
     return document
 
 

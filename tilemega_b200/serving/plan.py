@@ -63,6 +63,8 @@ _OPTIONAL = (
     ("tm_plan_clear_watchdog", C.c_int, [C.c_void_p]),
     ("tm_plan_watchdog_probe", C.c_int, [C.c_void_p, C.c_int, C.c_uint32, C.c_void_p]),
     ("tm_plan_step_bytes", C.c_uint64, [C.c_void_p, C.c_uint64]),
+    ("tm_plan_trace_step", C.c_int, [C.c_void_p, C.c_int]),
+    ("tm_plan_read_trace", C.c_longlong, [C.c_void_p, C.POINTER(C.c_uint64), C.c_uint64]),
 )
 
 
@@ -222,6 +224,20 @@ class Plan:
         if result < 0:
             raise RuntimeError(f"tm_plan_watchdog_probe failed: {self.library.last_error()}")
         return result == 1
+
+    def trace_step(self, step: int) -> None:
+        if self.library.lib.tm_plan_trace_step(self.handle, step) != 0:
+            raise RuntimeError("tm_plan_trace_step failed")
+
+    def read_trace(self) -> list[int]:
+        """Stage stamps [grid][stages][4] of the traced step, flattened."""
+        size = self.library.lib.tm_plan_read_trace(self.handle, None, 0)
+        if size <= 0:
+            raise RuntimeError("no trace was requested")
+        values = (C.c_uint64 * (size // 8))()
+        if self.library.lib.tm_plan_read_trace(self.handle, values, size) != size:
+            raise RuntimeError("tm_plan_read_trace failed")
+        return list(values)
 
     def step_bytes(self, cached_tokens_total: int) -> int:
         return int(self.library.lib.tm_plan_step_bytes(self.handle, cached_tokens_total))
