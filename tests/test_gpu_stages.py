@@ -84,8 +84,9 @@ def test_every_stage_of_one_layer(base, batch, history, plan_dir):
     # factors (O(1) here), not with a product that happens to be small
     agreement(h_gpu, h_ref, "swiglu", ulps=2.0, exact_fraction=0.97, floor=1e-3)
     # stage 5: down projection + residual (from the GPU's own activations)
+    # the sum may cancel to something much smaller than its addends, whose own ulp bounds the error
     agreement(x_gpu, x_mid + F.linear(h_gpu, w[p + "mlp.down_proj.weight"]), "residual stream", ulps=2.0,
-              exact_fraction=0.97)
+              exact_fraction=0.97, floor=2e-3)
     # stage 6: final norm + lm_head, accumulators in fp32
     head = w.get("lm_head.weight", w["model.embed_tokens.weight"])
     logits_ref = F.linear(rms_norm(x_gpu, w["model.norm.weight"], eps).float(), head.float())

@@ -505,15 +505,33 @@ struct GemvIo {
   void* out;           // kEpiStore: bf16 [B][n]; kEpiResidual: x; kEpiSwiGLU: h [B][n/2]; kEpiHead: logits
 };
 
+// Where the four 32-bit words of 16-byte chunk i of an activation row go. The
+// tensor-pipe path wants them in A-fragment order: inside every 64-column block,
+// word q (columns 8m+2q, 8m+2q+1) of chunk m sits at block*32 + q*8 + m, so that
+// lane (row g, q) reads its eight words of a block with two 128-bit loads and
+// nothing else is fetched. The CUDA-core path keeps the natural order.
+__device__ __forceinline__ void store_row_chunk(uint32_t* row, int i, const uint4& v) {
+#if TMB_GEMV_MMA
+  uint32_t* dst = row + (i >> 3) * 32 + (i & 7);
+  dst[0] = v.x;
+  dst[8] = v.y;
+  dst[16] = v.z;
+  dst[24] = v.w;
+#else
+  reinterpret_cast<uint4*>(row)[i] = v;
+#endif
+}
+
 // Stage the stage's B activation rows in shared memory; RMSNorm fused:
 // y = bf16(w * bf16(x * rsqrt(mean(x^2) + eps)))  (python/tilemega/serving/export.py:24-27).
-// The norm weights travel in the same pass as the rows (into row B of the
-// staging area) so that their L2 round trip overlaps the rows'.
+// Rows 0..B-1 of the staging area are the rows the GEMV reads; for a normalised
+// stage the raw rows go to rows B..2B-1 and the norm weights to row 2B in the same
+// pass, so that their L2 round trips overlap.
 template <int B>
 __device__ __forceinline__ void stage_rows(Ctx& c, const GemvIo& io, int k) {
   const MegaParams& p = c.p;
   const int chunks = k >> 3;
-  const int pitch = chunks + 1;   // rows are k + 8 elements apart: 16 bytes of padding keep ldmatrix row reads on distinct banks
+  const int pitch = chunks + 1;   // rows are k + 8 elements apart, so the batch rows of a block sit on distinct banks
   uint4* xs4 = reinterpret_cast<uint4*>(c.xs());
   const uint4* nw = reinterpret_cast<const uint4*>(io.norm);
   float ss[B];
@@ -531,14 +549,16 @@ __device__ __forceinline__ void stage_rows(Ctx& c, const GemvIo& io, int k) {
     float acc = 0.f;
     for (int i = c.tid; i < chunks; i += kConsumerThreads) {
       const uint4 v = io.embed ? __ldg(src + i) : __ldcg(src + i);
-      if (b == 0 && io.norm) xs4[B * pitch + i] = __ldg(nw + i);
-      xs4[b * pitch + i] = v;
       if (own) xg[i] = v;
       if (io.norm) {
+        if (b == 0) xs4[2 * B * pitch + i] = __ldg(nw + i);
+        xs4[(B + b) * pitch + i] = v;
         float f[8];
         unpack8(v, f);
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc = fmaf(f[j], f[j], acc);
+      } else {
+        store_row_chunk(reinterpret_cast<uint32_t*>(xs4 + b * pitch), i, v);
       }
     }
     ss[b] = acc;
@@ -560,8 +580,8 @@ __device__ __forceinline__ void stage_rows(Ctx& c, const GemvIo& io, int k) {
       const float inv = 1.0f / sqrtf(total / float(k) + p.eps);
       for (int i = c.tid; i < chunks; i += kConsumerThreads) {
         float f[8], w[8];
-        unpack8(xs4[b * pitch + i], f);
-        unpack8(xs4[B * pitch + i], w);   // written by this same thread above
+        unpack8(xs4[(B + b) * pitch + i], f);    // both written by this same thread above
+        unpack8(xs4[2 * B * pitch + i], w);
         uint32_t o[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -569,7 +589,7 @@ __device__ __forceinline__ void stage_rows(Ctx& c, const GemvIo& io, int k) {
           const uint32_t hi = bf16_bits(w[2 * j + 1] * bf16_round(f[2 * j + 1] * inv));
           o[j] = lo | (hi << 16);
         }
-        xs4[b * pitch + i] = make_uint4(o[0], o[1], o[2], o[3]);
+        store_row_chunk(reinterpret_cast<uint32_t*>(xs4 + b * pitch), i, make_uint4(o[0], o[1], o[2], o[3]));
       }
     }
   }
@@ -621,20 +641,21 @@ __device__ __forceinline__ void gemv_page_fma(const unsigned char* page, const u
 template <int B>
 __device__ __forceinline__ void gemv_page_mma(const unsigned char* page, const unsigned char* xs, int k, int col0,
                                               int warp, int lane, float (&d)[4][4]) {
-  const int r = lane & 7, m = lane >> 3;                 // ldmatrix: row r of matrix m
-  const int brow = min(r, B - 1);
-  const uint32_t xa = smem_u32(xs) + uint32_t((size_t(brow) * (k + 8) + col0 + 256 * warp + 8 * m) * 2);
+  const int r = lane & 7, m = lane >> 3;                 // ldmatrix: this lane addresses row r of matrix m
+  const int g = lane >> 2, q = lane & 3;                 // mma fragments: batch row g, word q
+  const unsigned char* xrow = xs + (size_t(min(g, B - 1)) * (k + 8) + col0 + 256 * warp) * 2 + 32 * q;
   const uint32_t wa = smem_u32(page) + uint32_t(1024 * (4 * warp) + 128 * r);
 #pragma unroll
   for (int cb = 0; cb < 4; ++cb) {
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      uint32_t w[4], x[4];
-      ldmatrix_x4(w, wa + 1024 * cb + 16 * ((4 * half + m) ^ r));
-      ldmatrix_x4(x, xa + 2 * (64 * cb + 32 * half));
-      mma_bf16_m16n8k16(d[2 * half], x[0], x[1], w[0], w[1]);
-      mma_bf16_m16n8k16(d[2 * half + 1], x[2], x[3], w[2], w[3]);
-    }
+    const uint4 xlo = *reinterpret_cast<const uint4*>(xrow + 128 * cb);        // words of chunks 0..3
+    const uint4 xhi = *reinterpret_cast<const uint4*>(xrow + 128 * cb + 16);   // words of chunks 4..7
+    uint32_t w[4];
+    ldmatrix_x4(w, wa + 1024 * cb + 16 * (m ^ r));                             // chunks 0..3 of the 8 rows
+    mma_bf16_m16n8k16(d[0], xlo.x, xlo.y, w[0], w[1]);
+    mma_bf16_m16n8k16(d[1], xlo.z, xlo.w, w[2], w[3]);
+    ldmatrix_x4(w, wa + 1024 * cb + 16 * ((4 + m) ^ r));                       // chunks 4..7
+    mma_bf16_m16n8k16(d[2], xhi.x, xhi.y, w[0], w[1]);
+    mma_bf16_m16n8k16(d[3], xhi.z, xhi.w, w[2], w[3]);
   }
 }
 

@@ -251,7 +251,8 @@ void* tm_plan_create(int batch, void* const* external, int device) {
   const int attention_scratch = 4 * s.head_dim * 4 + 2 * s.head_dim * 2 + 8 * 4 * (s.head_dim + 2) * 4;
   // rows of the widest GEMV input; one extra hidden-wide row holds the RMSNorm weights
   // (rows are padded by 8 elements so that the batch rows of a k-chunk sit on distinct banks)
-  int xs = std::max({batch * (s.max_k() + 8) * 2, (batch + 1) * (s.hidden + 8) * 2, attention_scratch});
+  // a normalised stage also parks its raw rows and the norm weights there: 2*batch + 1 hidden-wide rows
+  int xs = std::max({batch * (s.max_k() + 8) * 2, (2 * batch + 1) * (s.hidden + 8) * 2, attention_scratch});
   xs = (xs + 127) & ~127;
   p.xs_bytes = xs;
   p.static_quarters = s.static_quarters;
