@@ -37,9 +37,12 @@ from tilemega_b200 import synthetic  # noqa: E402
 METRIC = "decode_tokens_per_s"
 UNIT = "tok/s"
 NOMINAL_HBM_GBS = 8000.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one decode step of this workload,
-# from the ncu capture summarised in profiles/ (null until captured)
-NCU_TRAFFIC_BYTES_PER_STEP = None
+# dram__bytes_read.sum + dram__bytes_write.sum per algorithmic byte of a launch, from the ncu
+# capture of the same kernel on a 2-layer case of the same shapes (15.476 GB of DRAM traffic
+# for 15.559 GB of algorithmic bytes; profiles/decode_megakernel_llama31_8b_b1.md). Traffic
+# is proportional to the streamed weights, so the full launch's traffic is this ratio times
+# its algorithmic bytes.
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 0.9947
 
 
 def measured_peak_gbs() -> tuple[float, str]:
@@ -286,7 +289,8 @@ def run_ours(args) -> None:
                    "step_latency_us_median": statistics.median(step_us),
                    "mbu_vs_nominal_8tbs": achieved / NOMINAL_HBM_GBS},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": (NCU_TRAFFIC_BYTES_PER_STEP * steps if NCU_TRAFFIC_BYTES_PER_STEP else None),
+                     "traffic": NCU_TRAFFIC_PER_ALGORITHMIC_BYTE * bytes_timed,
+                     "traffic_source": "ncu on a 2-layer case of the same kernel, scaled by algorithmic bytes",
                      "peak_kind": f"of {peak_kind}", "bytes_per_launch": bytes_timed},
         "e2e": {"value": world * batch * steps / e2e_seconds, "unit": UNIT, "h2d_bytes_per_step": 4 * batch,
                 "d2h_bytes_per_step": 4 * batch},

@@ -30,18 +30,6 @@
 #include "params.h"
 #include "ptx.cuh"
 
-#ifndef TMB_SKIP
-#define TMB_SKIP 0   // bisecting hooks for the stage microbenchmark; 0 in the product
-#endif
-#ifndef TMB_PROFILE
-#define TMB_PROFILE 0   // cycle counters of the GEMV task loop for the stage microbenchmark
-#endif
-#if TMB_PROFILE
-__device__ long long g_prof[8];
-#define TMB_T(i) { long long now_ = clock64(); prof_[i] += now_ - last_; last_ = now_; }
-#else
-#define TMB_T(i)
-#endif
 #ifndef TMB_GEMV_MMA
 #define TMB_GEMV_MMA 1   // 1: weight pages through ldmatrix + mma.sync (bf16, fp32 accumulate); 0: fp32 FMA on CUDA cores
 #endif
@@ -785,11 +773,7 @@ __device__ TMB_GEMV_CALL void gemv_stage(Ctx& c, const GemvGeo& geo, const GemvI
   // have long arrived, so no warp ever waits for another one here, and the cost of
   // an epilogue is spread as one eighth per task instead of stalling every task.
   PendingEpilogue pending{-1, 0, 0u, 0.f};
-#if TMB_PROFILE
-  long long prof_[8] = {0, 0, 0, 0, 0, 0, 0, 0}, last_ = clock64();
-#endif
   for (int t = fifo_pop(c); t >= 0; t = fifo_pop(c)) {
-    TMB_T(0)
     const int rt = t;
 #if TMB_GEMV_MMA
     float d[4][4];
@@ -809,21 +793,15 @@ __device__ TMB_GEMV_CALL void gemv_stage(Ctx& c, const GemvGeo& geo, const GemvI
       residual = bf16_from_bits(__ldcg(reinterpret_cast<const unsigned short*>(io.out) +
                                        size_t(lane >> 3) * geo.n + rt * kTileN + (lane & 7)));
     for (int pg = 0; pg < geo.pages_per_task; ++pg) {
-      TMB_T(1)
       mbar_wait_warp(c, full0 + slot, phase, kSiteFull);
-      TMB_T(2)
-#if !(TMB_SKIP & 4)
 #if TMB_GEMV_MMA
       gemv_page_mma<B>(ring0 + slot * kSlotBytes, xs, geo.k, pg * geo.tile_k, warp, lane, d);
 #else
       gemv_page_fma<B>(ring0 + slot * kSlotBytes, xs, geo.k, pg * geo.tile_k, warp, lane, acc);
 #endif
-#endif
-      TMB_T(3)
       __syncwarp();
       if (lane == 0) mbar_arrive(empty0 + slot);
       if (++slot == nslots) { slot = 0; phase ^= 1u; }
-      TMB_T(4)
     }
     // lanes -> warps in a fixed order, so results are run-to-run identical. The warps
     // hand their partial sums over through a small ring of buffers guarded by mbarriers.
@@ -832,7 +810,6 @@ __device__ TMB_GEMV_CALL void gemv_stage(Ctx& c, const GemvGeo& geo, const GemvI
     // No wait before reusing buffer `buf`: its previous task lies kPartialRing tasks
     // back, and no warp can be more than the data ring (at most kMaxSlots pages, so
     // at most kMaxSlots tasks) ahead of the owner that reads it one task late.
-    TMB_T(5)
 #if TMB_GEMV_MMA
     // lane holds D[batch row lane/4][weight rows 2*(lane%4), +1]
     if ((lane >> 2) < B) {
@@ -859,12 +836,7 @@ __device__ TMB_GEMV_CALL void gemv_stage(Ctx& c, const GemvGeo& geo, const GemvI
     if (owner) pending = PendingEpilogue{t, buf, lap, residual};
     ++task_seq;
     ++gemv_seq;
-    TMB_T(6)
   }
-#if TMB_PROFILE
-  if (blockIdx.x == 0 && threadIdx.x == 0)
-    for (int i = 0; i < 8; ++i) g_prof[i] = prof_[i];
-#endif
   if (pending.task >= 0) gemv_epilogue<B>(c, geo, io, pending, lane, best_val, best_idx);
   c.slot = slot;
   c.phase = phase;

@@ -37,7 +37,7 @@ struct PlanSpec {
   bool paged = false;
   int num_blocks = 0, max_blocks = 0;
   // execution
-  int grid = 0, slots = 0, static_quarters = 3, diag = 0;
+  int grid = 0, slots = 0, static_quarters = 0, diag = 0;
   bool write_logits = true;
   GemvGeo geo[kNumGemv];
   // buffer table
