@@ -118,6 +118,29 @@ long long tm_plan_read_trace(void* plan, uint64_t* host, uint64_t bytes);
  * 4*L*Hkv*D bytes per cached token (scripts/estimate_r16_mbu.py:15-38). */
 uint64_t tm_plan_step_bytes(void* plan, uint64_t cached_tokens_total);
 
+/* No counterpart in the reference. The bounded-wait self test of
+ * tm_plan_watchdog_probe for callers that may not allocate device memory: a
+ * process whose HBM is fully committed to weight and KV pools, a health check
+ * between decode launches that cannot afford cudaMalloc's device-wide
+ * synchronisation, code under a framework-enforced memory budget. It needs no
+ * plan and calls no allocator: its scratch (the arrival word and one record per
+ * waiter) is a fixed 4.4 KB device array inside the library, present on every GPU
+ * that loads it until the process exits. One producer CTA and `waiters` waiting
+ * CTAs (1..TM_STATIC_PROBE_MAX_WAITERS; more is rejected with -1 and a message)
+ * run in one launch on `stream`; with `withhold` != 0 the producer never arrives
+ * and every waiter gives up after limit_us (1..1000000). Each waiter writes its
+ * 12-word record (layout of tm_plan_watchdog; word 0 = 1 if it gave up) to
+ * records_device[waiter*12 ...], a device buffer of waiters*12 u64 that the
+ * caller owns; read it after synchronising the stream. Returns 0 or a CUDA error
+ * code. The first call on a device resolves the scratch array's address; make
+ * that call before any stream capture begins. All calls share the one array
+ * (cleared on `stream` at the start of each call), so two calls whose kernels
+ * could overlap on the GPU -- different streams, no ordering -- would race: run
+ * them one after another. */
+enum { TM_STATIC_PROBE_MAX_WAITERS = 32 };
+int tm_watchdog_probe_static(int device, int waiters, int withhold, uint32_t limit_us,
+                             uint64_t* records_device, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

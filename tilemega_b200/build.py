@@ -14,7 +14,7 @@ ROOT = Path(__file__).resolve().parent
 CSRC = ROOT / "csrc"
 LIB_DIR = ROOT / "lib"
 LIBRARY = LIB_DIR / "libtilemega_b200.so"
-SOURCES = ("megakernel.cu", "runtime.cu", "plan_spec.cpp")
+SOURCES = ("megakernel.cu", "runtime.cu", "plan_spec.cpp", "static_probe.cu")
 HEADERS = ("params.h", "ptx.cuh", "plan_spec.h", "json.h")
 
 

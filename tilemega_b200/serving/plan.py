@@ -65,7 +65,9 @@ _OPTIONAL = (
     ("tm_plan_step_bytes", C.c_uint64, [C.c_void_p, C.c_uint64]),
     ("tm_plan_trace_step", C.c_int, [C.c_void_p, C.c_int]),
     ("tm_plan_read_trace", C.c_longlong, [C.c_void_p, C.POINTER(C.c_uint64), C.c_uint64]),
+    ("tm_watchdog_probe_static", C.c_int, [C.c_int, C.c_int, C.c_int, C.c_uint32, C.c_void_p, C.c_void_p]),
 )
+STATIC_PROBE_MAX_WAITERS = 32
 
 
 class PlanLibrary:
@@ -113,6 +115,17 @@ class PlanLibrary:
         query = getattr(self.lib, "tm_plan_last_error", None)
         text = query() if query is not None else b""
         return text.decode() if text else ""
+
+    def watchdog_probe_static(self, device: int, waiters: int, withhold: bool, limit_us: int,
+                              records_pointer: int, stream: int = 0) -> None:
+        """The bounded-wait self test without a plan and without any allocation: for
+        callers whose device memory is fully committed or budgeted. `records_pointer`
+        is a device buffer of waiters*12 uint64 owned by the caller; synchronise the
+        stream before reading it. Calls share one scratch array inside the library:
+        do not let two of them overlap on the GPU."""
+        status = self.lib.tm_watchdog_probe_static(device, waiters, int(withhold), limit_us, records_pointer, stream)
+        if status != 0:
+            raise RuntimeError(f"tm_watchdog_probe_static failed ({status})")
 
     @property
     def tp_world(self) -> int:
