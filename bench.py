@@ -147,6 +147,22 @@ def cpu_forward_seconds_per_step(work: dict, steps: int, threads: int) -> tuple[
     return seconds, sample
 
 
+def max_over_ranks(values: list[float], device=None) -> list[float]:
+    """Element-wise maximum of `values` over the ranks of the default process group
+    (identity without one): every reported time is the slowest rank's."""
+    import torch.distributed as dist
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
+        return list(values)
+    buffer = torch.tensor(values, dtype=torch.float64, device=device)
+    dist.all_reduce(buffer, op=dist.ReduceOp.MAX)
+    return [float(v) for v in buffer]
+
+
+def job_value(world: int, batch: int, steps: int, seconds: float) -> float:
+    """Whole-job tokens per second: every replica decodes batch*steps tokens in the slowest rank's time."""
+    return world * batch * steps / seconds
+
+
 def run_reference(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -268,13 +284,9 @@ def run_ours(args) -> None:
     fired = plan.watchdog()
     if fired is not None:
         raise SystemExit(f"a bounded device wait gave up during the end-to-end loop: {fired}")
-    if world > 1:
-        import torch.distributed as dist
-        times = torch.tensor([device_ms, e2e_seconds], device=device, dtype=torch.float64)
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-        device_ms, e2e_seconds = float(times[0]), float(times[1])
+    device_ms, e2e_seconds = max_over_ranks([device_ms, e2e_seconds], device)
     seconds = device_ms / 1e3
-    value = world * batch * steps / seconds
+    value = job_value(world, batch, steps, seconds)
     achieved = bytes_timed / seconds / 1e9
     peak, peak_kind = measured_peak_gbs()
     step_us = [(stamps[i + 1] - stamps[i]) / 1e3 for i in range(steps)]
@@ -292,7 +304,7 @@ def run_ours(args) -> None:
                      "traffic": NCU_TRAFFIC_PER_ALGORITHMIC_BYTE * bytes_timed,
                      "traffic_source": "ncu on a 2-layer case of the same kernel, scaled by algorithmic bytes",
                      "peak_kind": f"of {peak_kind}", "bytes_per_launch": bytes_timed},
-        "e2e": {"value": world * batch * steps / e2e_seconds, "unit": UNIT, "h2d_bytes_per_step": 4 * batch,
+        "e2e": {"value": job_value(world, batch, steps, e2e_seconds), "unit": UNIT, "h2d_bytes_per_step": 4 * batch,
                 "d2h_bytes_per_step": 4 * batch},
         "gpu_launches": 1,
         "clocks": sampler.summary(),

@@ -1095,10 +1095,12 @@ __device__ void attn_stage(Ctx& c, const LayerPtrs& lp, int past, bool tr, int s
     if (a.nch > 1) {
       // last arriver of (sequence, KV head) merges the chunks in chunk order
       // (include/tilemega/Backend/Sm90DenseAttentionBody.cuh:359-363,409-446)
-      __threadfence();
+      // (the CTA barrier orders every thread's partial stores before thread 0's
+      // fence + counter increment, the same pattern as the grid arrival)
       consumer_sync();
       if (c.tid == 0) {
         unsigned* cnt = p.attn_cnt + a.b * p.kv_heads + a.g;
+        __threadfence();
         const unsigned old = atomicAdd(cnt, 1u);
         const int last = old == unsigned(a.nch - 1);
         if (last) atomicExch(cnt, 0u);
