@@ -76,11 +76,12 @@ struct Ctx {
   bool dead;                         // a bounded wait gave up: stop waiting, leave at the next boundary
   uint32_t q_pos;                    // FIFO entries pushed (streaming warp) / popped (arithmetic warps)
   uint32_t inst;                     // stage instances finished in this launch (index of the claim counter)
-  int pending;                       // streaming warp, lane 0: first task id claimed for the next stage
+  int pending;                       // streaming thread: first task id claimed for the stage about to start
+  int pending_next;                  // ... and for the stage after it (claimed a whole stage ahead)
   uint32_t gemv_seq;                 // GEMV tasks finished by this CTA (partial-sum ring cursor)
   __device__ Ctx(const MegaParams& q, unsigned char* s)
       : p(q), smem(s), warp(threadIdx.x >> 5), lane(threadIdx.x & 31), tid(threadIdx.x), slot(0), phase(0),
-        bar_target(q.bar_base), task_seq(0), dead(false), q_pos(0), inst(0), pending(0), gemv_seq(0) {}
+        bar_target(q.bar_base), task_seq(0), dead(false), q_pos(0), inst(0), pending(0), pending_next(0), gemv_seq(0) {}
   __device__ uint64_t* full(int i) const { return reinterpret_cast<uint64_t*>(smem + kOffFull) + i; }
   __device__ uint64_t* empty(int i) const { return reinterpret_cast<uint64_t*>(smem + kOffEmpty) + i; }
   __device__ uint64_t* pfull(int i) const { return reinterpret_cast<uint64_t*>(smem + kOffPFull) + i; }
@@ -333,12 +334,15 @@ __device__ __forceinline__ int claim(const Ctx& c, uint32_t inst) {
   return int(atomicAdd(c.p.stage_cnt + inst, 1u));
 }
 
-// Close the stage: tell the arithmetic warps, and claim the first task of the next
-// stage right away.
+// Close the stage: tell the arithmetic warps. The first task of the next stage was
+// claimed a whole stage ago, so its id is here without waiting for a round trip
+// (an attention stage has nothing in the ring to hide one behind); claim the first
+// task of the stage after that now.
 __device__ __forceinline__ void stream_close(Ctx& c) {
   fifo_push(c, -1);
   ++c.inst;
-  c.pending = claim(c, c.inst);
+  c.pending = c.pending_next;
+  c.pending_next = claim(c, c.inst + 1);
 }
 
 // One GEMV task: post its id, then copy its weight pages into the ring.
@@ -427,9 +431,10 @@ template <int D>
 __device__ void streamer_main(Ctx& c) {
   const MegaParams& p = c.p;
   const uint64_t policy = policy_evict_first();
-  const unsigned long long bars_per_step = 5ull * p.layers + 1ull;
+  const unsigned long long bars_per_step = 4ull * p.layers + 1ull;   // grid barriers: none between QKV and attention
   const uint32_t norm_bytes = uint32_t(p.hidden) * 2u;
   c.pending = claim(c, 0);
+  c.pending_next = claim(c, 1);
   for (int si = 0; si < p.nsteps; ++si) {
     const int past = __ldg(p.past + p.first_step + si);
     // KV rows appended by the previous step were written with ordinary stores by
@@ -491,6 +496,8 @@ struct GemvIo {
   int embed;           // rows are table[tok[b]] and are also copied into x
   int epilogue;
   void* out;           // kEpiStore: bf16 [B][n]; kEpiResidual: x; kEpiSwiGLU: h [B][n/2]; kEpiHead: logits
+  unsigned long long* ready;   // kEpiStore: per-group counters bumped once per stored row tile (or null)
+  int tiles_per_group;
 };
 
 // Where the four 32-bit words of 16-byte chunk i of an activation row go. The
@@ -746,6 +753,15 @@ __device__ __forceinline__ void gemv_epilogue(Ctx& c, const GemvGeo& geo, const 
       }
     }
   }
+  if (io.ready) {
+    // one more row tile of this KV-head group is in global memory: attention tasks
+    // of that group wait for the group's count instead of a grid-wide barrier
+    __syncwarp();
+    if (lane == 0) {
+      __threadfence();
+      red_release_add(io.ready + e.task / io.tiles_per_group, 1ull);
+    }
+  }
 }
 
 template <int B>
@@ -874,7 +890,7 @@ __device__ __forceinline__ void subgroup_reduce_scatter(float (&v)[N], int hl) {
 }
 
 template <int B, int D, int GQ>
-__device__ void attn_stage(Ctx& c, const LayerPtrs& lp, int past, bool tr, int stage) {
+__device__ void attn_stage(Ctx& c, const LayerPtrs& lp, int past, bool tr, int stage, unsigned long long qkv_stages) {
   constexpr int NK = kAttnHalfBytes / (2 * D);  // keys per slot: 64 (D=128) / 128 (D=64)
   constexpr int LPK = D / 8;                    // lanes that share one key row
   constexpr int KPW = 32 / LPK;                 // sub-groups per warp
@@ -900,6 +916,16 @@ __device__ void attn_stage(Ctx& c, const LayerPtrs& lp, int past, bool tr, int s
   for (int t = fifo_pop_uniform(c); t >= 0; t = fifo_pop_uniform(c)) {
     const AttnTask a = attn_task(p, past, NK, spt, min(t, ntasks - 1));
     const bool tail = a.c == a.nch - 1;  // this chunk holds the new token
+    // the (GQ + 2) * D QKV rows of KV head a.g must be stored: their row tiles are counted per group
+    if (c.tid == 0 && !c.dead) {
+      const unsigned long long need = qkv_stages * (unsigned long long)((GQ + 2) * D / kTileN);
+      unsigned long long t0 = 0, seen;
+      uint32_t polls = 0;
+      while ((seen = ld_acquire(p.qkv_ready + a.g)) < need) {
+        if ((++polls & 63u) == 0 && wait_give_up(p, t0, kSiteGrid, need, seen)) break;
+      }
+    }
+    consumer_sync();
     // ---- q (GQ heads) and the new k: RoPE with bf16 tables, each product and the
     // sum rounded to bf16 (include/tilemega/Codegen/tasks/FusedAttentionTaskBody.h:141-151)
     const unsigned short* row = reinterpret_cast<const unsigned short*>(p.qkv) + size_t(a.b) * qkv_width +
@@ -1178,30 +1204,30 @@ __device__ void consumer_main(Ctx& c) {
         if (!grid_wait(c)) return;
       }
       trace_mark(c, tr, stage, 1);
-      io = GemvIo{l == 0 ? p.embed : p.x, lp.norm1, l == 0, kEpiStore, p.qkv};
+      io = GemvIo{l == 0 ? p.embed : p.x, lp.norm1, l == 0, kEpiStore, p.qkv, p.qkv_ready, (GQ + 2) * D / kTileN};
       gemv_stage<B>(c, p.geo[kQkv], io, tr, stage++);
+      // no grid barrier here: an attention task needs the QKV rows of its own KV head
+      // only, and waits for that group's row-tile count (qkv_ready)
+      trace_mark(c, tr, stage, 0);
+      trace_mark(c, tr, stage, 1);
+      attn_stage<B, D, GQ>(c, lp, past, tr, stage++, (unsigned long long)(si * p.layers + l + 1));
       grid_arrive(c);
       trace_mark(c, tr, stage, 0);
       if (!grid_wait(c)) return;
       trace_mark(c, tr, stage, 1);
-      attn_stage<B, D, GQ>(c, lp, past, tr, stage++);
-      grid_arrive(c);
-      trace_mark(c, tr, stage, 0);
-      if (!grid_wait(c)) return;
-      trace_mark(c, tr, stage, 1);
-      io = GemvIo{p.attn, nullptr, 0, kEpiResidual, p.x};
+      io = GemvIo{p.attn, nullptr, 0, kEpiResidual, p.x, nullptr, 1};
       gemv_stage<B>(c, p.geo[kOProj], io, tr, stage++);
       grid_arrive(c);
       trace_mark(c, tr, stage, 0);
       if (!grid_wait(c)) return;
       trace_mark(c, tr, stage, 1);
-      io = GemvIo{p.x, lp.norm2, 0, kEpiSwiGLU, p.h};
+      io = GemvIo{p.x, lp.norm2, 0, kEpiSwiGLU, p.h, nullptr, 1};
       gemv_stage<B>(c, p.geo[kGateUp], io, tr, stage++);
       grid_arrive(c);
       trace_mark(c, tr, stage, 0);
       if (!grid_wait(c)) return;
       trace_mark(c, tr, stage, 1);
-      io = GemvIo{p.h, nullptr, 0, kEpiResidual, p.x};
+      io = GemvIo{p.h, nullptr, 0, kEpiResidual, p.x, nullptr, 1};
       gemv_stage<B>(c, p.geo[kDown], io, tr, stage++);
       grid_arrive(c);
       lp = upcoming;
@@ -1209,7 +1235,7 @@ __device__ void consumer_main(Ctx& c) {
     trace_mark(c, tr, stage, 0);
     if (!grid_wait(c)) return;
     trace_mark(c, tr, stage, 1);
-    GemvIo io{p.x, p.final_norm, 0, kEpiHead, p.logits};
+    GemvIo io{p.x, p.final_norm, 0, kEpiHead, p.logits, nullptr, 1};
     gemv_stage<B>(c, p.geo[kHead], io, tr, stage);
     consumer_sync();
     if (c.tid < B) {

@@ -86,9 +86,10 @@ struct MegaParams {
   void* logits;                // f32 [B][V]: head accumulators before the bf16 rounding
   float* attn_part;            // [grid + B*Hkv][Gq][D+2]
   unsigned* attn_cnt;          // [B*Hkv]
+  unsigned long long* qkv_ready;  // [Hkv] QKV row tiles stored per KV-head group (monotonic within a launch)
   float* argmax_val;           // [grid][B]
   int* argmax_idx;             // [grid][B]
-  unsigned* stage_cnt;         // [nsteps*(5*layers+1)+1] task claim counters, zero at launch
+  unsigned* stage_cnt;         // [nsteps*(5*layers+1)+2] task claim counters, zero at launch
   unsigned long long* bar;     // grid barrier arrivals (monotonic)
   unsigned long long* status;  // [kStWords]
   unsigned long long* step_ns; // [capacity+1] %globaltimer stamps

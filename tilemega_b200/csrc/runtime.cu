@@ -341,8 +341,9 @@ void* tm_plan_create(int batch, void* const* external, int device) {
   // barrier word, then the attention arrival counters: one block, rezeroed per launch
   const size_t attn_cnt = size_t(batch) * s.kv_heads;
   // ... and the task claim counters of every stage instance of the longest possible launch
-  const size_t stage_cnt = size_t(s.capacity) * (5 * size_t(s.layers) + 1) + 1;
-  plan->claim_offset = 128 + attn_cnt * sizeof(unsigned);
+  const size_t stage_cnt = size_t(s.capacity) * (5 * size_t(s.layers) + 1) + 2;   // + the two look-ahead claims past the last stage
+  const size_t ready_offset = (128 + attn_cnt * sizeof(unsigned) + 7) & ~size_t(7);
+  plan->claim_offset = ready_offset + size_t(s.kv_heads) * sizeof(unsigned long long);
   plan->sync_bytes = plan->claim_offset + stage_cnt * sizeof(unsigned);
   {
     void* dev = nullptr;
@@ -352,6 +353,7 @@ void* tm_plan_create(int batch, void* const* external, int device) {
   }
   p.bar = reinterpret_cast<unsigned long long*>(plan->sync_block);
   p.attn_cnt = reinterpret_cast<unsigned*>(plan->sync_block + 128);
+  p.qkv_ready = reinterpret_cast<unsigned long long*>(plan->sync_block + ready_offset);
   p.stage_cnt = reinterpret_cast<unsigned*>(plan->sync_block + plan->claim_offset);
   p.attn_part = static_cast<float*>(attn_part);
   p.argmax_val = static_cast<float*>(argmax_val);
@@ -402,7 +404,7 @@ int tm_plan_launch_steps(void* handle, uint32_t first_step, uint32_t steps, uint
   DeviceScope scope(plan->device);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   // only the claim counters this launch can touch are rezeroed
-  const size_t used = plan->claim_offset + (size_t(steps) * (5 * size_t(plan->params.layers) + 1) + 1) * sizeof(unsigned);
+  const size_t used = plan->claim_offset + (size_t(steps) * (5 * size_t(plan->params.layers) + 1) + 2) * sizeof(unsigned);
   cudaError_t err = cudaMemsetAsync(plan->sync_block, 0, used, s);
   if (err != cudaSuccess) return Fail(int(err), std::string("tm_plan_launch_steps: ") + cudaGetErrorString(err));
   tmb::MegaParams p = plan->params;
