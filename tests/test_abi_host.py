@@ -65,7 +65,7 @@ def test_buffer_table_of_tiny_plan(plan_dir):
     with pytest.raises(KeyError):
         lib.create(1, {}, 0)
     with pytest.raises(ValueError):
-        lib.create(5, {}, 0)
+        lib.create(5, {}, 0)   # outside this plan's interval [1, 4]
 
 
 def test_paged_plan_lists_block_table(plan_dir):

@@ -68,6 +68,20 @@ def test_small_models_match_oracle_and_reference_fixture(name, plan_dir):
     run.close()
 
 
+def test_batch_eight_matches_oracle(plan_dir):
+    """The largest batch of the GEMV path (all eight rows of the tensor-pipe A operand, two epilogue passes)."""
+    config = synthetic.TINY
+    batch, prompt_len, new_tokens, capacity = 8, 19, 5, 32
+    weights = bf16_weights(config)
+    prompt = synthetic.seeded_tokens(batch, prompt_len, config["vocab_size"], seed=3)
+    run = GpuRun(config, weights, batch, capacity, plan_dir)
+    tokens, logits = run.greedy(prompt, new_tokens)
+    assert_as_accurate_as_reference_bf16(config, weights, prompt, tokens, logits, capacity, "tiny batch 8")
+    looped, _ = run.greedy(prompt, new_tokens, stepwise=False)
+    assert torch.equal(looped, tokens)
+    run.close()
+
+
 def test_block_table_gather_is_bit_exact(plan_dir):
     """A shuffled block table over a larger pool must reproduce the contiguous
     cache bit for bit: tokens, logits and the gathered KV rows."""

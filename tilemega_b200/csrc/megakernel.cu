@@ -56,11 +56,11 @@ constexpr int kOffCtl = 128;       // int[8]: [0] abort seen, [1] last-arriver f
 constexpr int kOffPFull = 192;     // u64[8]  all warps wrote their partial sums of a GEMV task
 constexpr int kOffTok = 256;       // int[8]
 constexpr int kOffFifo = 320;      // int[kFifo] task ids claimed by the streaming warp, -1 closes a stage
-constexpr int kOffBestVal = 448;   // float[8 warps][4]
-constexpr int kOffBestIdx = 576;   // int[8 warps][4]
-constexpr int kOffWsum = 704;      // float[4][8]
-constexpr int kOffSc = 832;        // float[8 warps][4][16]
-constexpr int kOffRed = 2880;      // float[kPartialRing][8 warps][8 rows][batch]: 2 KB per sequence of the batch
+constexpr int kOffBestVal = 448;   // float[8 warps][kMaxBatch]
+constexpr int kOffBestIdx = 704;   // int[8 warps][kMaxBatch]
+constexpr int kOffWsum = 960;      // float[kMaxBatch][8]
+constexpr int kOffSc = 1216;       // float[8 warps][4][16]
+constexpr int kOffRed = 3264;      // float[kPartialRing][8 warps][8 rows][batch]: 2 KB per sequence of the batch
 constexpr int kFifo = 32;          // entries; the streaming warp keeps at most kFifo/2 unread
 
 __host__ __device__ inline int xs_offset(int batch) { return kOffRed + kPartialRing * 8 * 8 * 4 * batch; }   // activation rows / attention scratch
@@ -693,63 +693,73 @@ __device__ __forceinline__ float silu_bf16(float g) {
 }
 
 // Everything the epilogue of one GEMV task needs, kept by the warp that owns it.
+// Output (batch row b, weight row r) of a task is handled by lane (b*8 + r) % 32 in
+// pass (b*8 + r) / 32: one pass up to batch 4, two up to batch 8.
+template <int B>
+struct EpiPasses { static constexpr int value = (kTileN * B + 31) / 32; };
+
+template <int B>
 struct PendingEpilogue {
   int task;         // -1: none
   int buf;
   uint32_t lap;
-  float residual;   // prefetched residual element of this lane (kEpiResidual)
+  float residual[EpiPasses<B>::value];   // prefetched residual elements of this lane (kEpiResidual)
 };
 
 // Epilogue of one task, run by one warp: sum the eight warps' partial sums in warp
-// order, then apply the stage's rounding sites. lane = b*8 + r.
+// order, then apply the stage's rounding sites.
 template <int B>
-__device__ __forceinline__ void gemv_epilogue(Ctx& c, const GemvGeo& geo, const GemvIo& io, const PendingEpilogue& e,
-                                              int lane, float& best_val, int& best_idx) {
+__device__ __forceinline__ void gemv_epilogue(Ctx& c, const GemvGeo& geo, const GemvIo& io, const PendingEpilogue<B>& e,
+                                              int lane, float (&best_val)[EpiPasses<B>::value],
+                                              int (&best_idx)[EpiPasses<B>::value]) {
   const MegaParams& p = c.p;
   const float* red = c.red();
   mbar_wait_warp(c, c.pfull(e.buf), e.lap, kSiteFull);
-  if (lane < kTileN * B) {
-    // kTileN*B <= 32 lanes take part, `mask` names exactly them
-    constexpr unsigned mask = kTileN * B >= 32 ? 0xffffffffu : ((1u << (kTileN * B)) - 1u);
-    const int rt = e.task;
-    const int r = lane & 7, b = lane >> 3;
-    const int row = rt * kTileN + r;
-    float v = 0.f;
 #pragma unroll
-    for (int w = 0; w < kConsumerWarps; ++w) v += red[((e.buf * 8 + w) * 8 + r) * B + b];
-    constexpr bool apply = true;
-    const float vb = bf16_round(v);
-    if (io.epilogue == kEpiSwiGLU) {
-      // rows 0..3 of the page are gate rows, rows 4..7 the matching up rows
-      const float up = __shfl_down_sync(mask, vb, 4);
-      if (apply && r < 4) {
-        __nv_bfloat16* h = static_cast<__nv_bfloat16*>(io.out);
-        h[size_t(b) * (geo.n >> 1) + rt * 4 + r] = __float2bfloat16_rn(silu_bf16(vb) * up);
-      }
-    } else if (io.epilogue == kEpiHead) {
-      // the logits buffer keeps the fp32 accumulator; the argmax below compares the
-      // bf16-rounded value, as the reference's head epilogue does
-      if (apply && p.write_logits) static_cast<float*>(io.out)[size_t(b) * geo.n + row] = v;
-      // ties -> smaller index (include/tilemega/Backend/Sm90DenseEpilogue.h:166-184)
-      float bv = row < p.vocab ? vb : -INFINITY;
-      int bi = row;
+  for (int pass = 0; pass < EpiPasses<B>::value; ++pass) {
+    constexpr int total = kTileN * B;
+    const int live = total - 32 * pass >= 32 ? 32 : total - 32 * pass;   // lanes taking part in this pass
+    if (lane < live) {
+      const unsigned mask = live >= 32 ? 0xffffffffu : ((1u << live) - 1u);   // exactly those lanes
+      const int rt = e.task;
+      const int r = lane & 7, b = 4 * pass + (lane >> 3);
+      const int row = rt * kTileN + r;
+      float v = 0.f;
 #pragma unroll
-      for (int m = 1; m < 8; m <<= 1) {
-        const float ov = __shfl_xor_sync(mask, bv, m);
-        const int oi = __shfl_xor_sync(mask, bi, m);
-        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
-      }
-      if (apply && (bv > best_val || (bv == best_val && bi < best_idx))) {
-        best_val = bv;   // lanes 8b..8b+7 all hold sequence b's candidate
-        best_idx = bi;
-      }
-    } else if (apply) {
-      __nv_bfloat16* out = static_cast<__nv_bfloat16*>(io.out) + size_t(b) * geo.n + row;
-      if (io.epilogue == kEpiResidual) {
-        // bf16(float(bf16(acc)) + float(residual)) (ServingEpilogue.h:38-43)
-        *out = __float2bfloat16_rn(vb + e.residual);
+      for (int w = 0; w < kConsumerWarps; ++w) v += red[((e.buf * 8 + w) * 8 + r) * B + b];
+      const float vb = bf16_round(v);
+      if (io.epilogue == kEpiSwiGLU) {
+        // rows 0..3 of the page are gate rows, rows 4..7 the matching up rows
+        const float up = __shfl_down_sync(mask, vb, 4);
+        if (r < 4) {
+          __nv_bfloat16* h = static_cast<__nv_bfloat16*>(io.out);
+          h[size_t(b) * (geo.n >> 1) + rt * 4 + r] = __float2bfloat16_rn(silu_bf16(vb) * up);
+        }
+      } else if (io.epilogue == kEpiHead) {
+        // the logits buffer keeps the fp32 accumulator; the argmax below compares the
+        // bf16-rounded value, as the reference's head epilogue does
+        if (p.write_logits) static_cast<float*>(io.out)[size_t(b) * geo.n + row] = v;
+        // ties -> smaller index (include/tilemega/Backend/Sm90DenseEpilogue.h:166-184)
+        float bv = row < p.vocab ? vb : -INFINITY;
+        int bi = row;
+#pragma unroll
+        for (int m = 1; m < 8; m <<= 1) {
+          const float ov = __shfl_xor_sync(mask, bv, m);
+          const int oi = __shfl_xor_sync(mask, bi, m);
+          if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if (bv > best_val[pass] || (bv == best_val[pass] && bi < best_idx[pass])) {
+          best_val[pass] = bv;   // the 8 lanes of a sequence all hold its candidate
+          best_idx[pass] = bi;
+        }
       } else {
-        *out = __float2bfloat16_rn(v);
+        __nv_bfloat16* out = static_cast<__nv_bfloat16*>(io.out) + size_t(b) * geo.n + row;
+        if (io.epilogue == kEpiResidual) {
+          // bf16(float(bf16(acc)) + float(residual)) (ServingEpilogue.h:38-43)
+          *out = __float2bfloat16_rn(vb + e.residual[pass]);
+        } else {
+          *out = __float2bfloat16_rn(v);
+        }
       }
     }
   }
@@ -770,8 +780,13 @@ __device__ TMB_GEMV_CALL void gemv_stage(Ctx& c, const GemvGeo& geo, const GemvI
   stage_rows<B>(c, io, geo.k);
   trace_mark(c, tr, stage, 2);
   // per-warp running argmax (each warp runs every eighth epilogue); merged by the caller
-  float best_val = -INFINITY;
-  int best_idx = 0x7fffffff;
+  float best_val[EpiPasses<B>::value];
+  int best_idx[EpiPasses<B>::value];
+#pragma unroll
+  for (int i = 0; i < EpiPasses<B>::value; ++i) {
+    best_val[i] = -INFINITY;
+    best_idx[i] = 0x7fffffff;
+  }
   float* red = c.red();
   uint32_t slot = c.slot, phase = c.phase, task_seq = c.task_seq, gemv_seq = c.gemv_seq;
   const int warp = c.warp, lane = c.lane;
@@ -788,7 +803,8 @@ __device__ TMB_GEMV_CALL void gemv_stage(Ctx& c, const GemvGeo& geo, const GemvI
   // late, after its own pages of task n+1: by then the other warps' partial sums
   // have long arrived, so no warp ever waits for another one here, and the cost of
   // an epilogue is spread as one eighth per task instead of stalling every task.
-  PendingEpilogue pending{-1, 0, 0u, 0.f};
+  PendingEpilogue<B> pending;
+  pending.task = -1;
   for (int t = fifo_pop(c); t >= 0; t = fifo_pop(c)) {
     const int rt = t;
 #if TMB_GEMV_MMA
@@ -804,10 +820,14 @@ __device__ TMB_GEMV_CALL void gemv_stage(Ctx& c, const GemvGeo& geo, const GemvI
 #endif
     const bool owner = warp == int(task_seq & 7);
     // the owner fetches the residual now, so the L2 round trip overlaps the arithmetic
-    float residual = 0.f;
-    if (io.epilogue == kEpiResidual && owner && lane < kTileN * B)
-      residual = bf16_from_bits(__ldcg(reinterpret_cast<const unsigned short*>(io.out) +
-                                       size_t(lane >> 3) * geo.n + rt * kTileN + (lane & 7)));
+    float residual[EpiPasses<B>::value];
+#pragma unroll
+    for (int pass = 0; pass < EpiPasses<B>::value; ++pass) {
+      residual[pass] = 0.f;
+      if (io.epilogue == kEpiResidual && owner && 32 * pass + lane < kTileN * B)
+        residual[pass] = bf16_from_bits(__ldcg(reinterpret_cast<const unsigned short*>(io.out) +
+                                               size_t(4 * pass + (lane >> 3)) * geo.n + rt * kTileN + (lane & 7)));
+    }
     for (int pg = 0; pg < geo.pages_per_task; ++pg) {
       mbar_wait_warp(c, full0 + slot, phase, kSiteFull);
 #if TMB_GEMV_MMA
@@ -849,7 +869,13 @@ __device__ TMB_GEMV_CALL void gemv_stage(Ctx& c, const GemvGeo& geo, const GemvI
       gemv_epilogue<B>(c, geo, io, pending, lane, best_val, best_idx);
       pending.task = -1;
     }
-    if (owner) pending = PendingEpilogue{t, buf, lap, residual};
+    if (owner) {
+      pending.task = t;
+      pending.buf = buf;
+      pending.lap = lap;
+#pragma unroll
+      for (int pass = 0; pass < EpiPasses<B>::value; ++pass) pending.residual[pass] = residual[pass];
+    }
     ++task_seq;
     ++gemv_seq;
   }
@@ -858,9 +884,15 @@ __device__ TMB_GEMV_CALL void gemv_stage(Ctx& c, const GemvGeo& geo, const GemvI
   c.phase = phase;
   c.task_seq = task_seq;
   c.gemv_seq = gemv_seq;
-  if (io.epilogue == kEpiHead && lane < kTileN * B && (lane & 7) == 0) {
-    c.best_val()[warp * kMaxBatch + (lane >> 3)] = best_val;
-    c.best_idx()[warp * kMaxBatch + (lane >> 3)] = best_idx;
+  if (io.epilogue == kEpiHead && (lane & 7) == 0) {
+#pragma unroll
+    for (int pass = 0; pass < EpiPasses<B>::value; ++pass) {
+      const int b = 4 * pass + (lane >> 3);
+      if (b < B) {
+        c.best_val()[warp * kMaxBatch + b] = best_val[pass];
+        c.best_idx()[warp * kMaxBatch + b] = best_idx[pass];
+      }
+    }
   }
   trace_mark(c, tr, stage, 3);
 }
@@ -1356,6 +1388,10 @@ static cudaError_t run_batch(const MegaParams& p, size_t smem_bytes, cudaStream_
     case 2: return run_instance<2, D, GQ>(p, smem_bytes, stream, prepare);
     case 3: return run_instance<3, D, GQ>(p, smem_bytes, stream, prepare);
     case 4: return run_instance<4, D, GQ>(p, smem_bytes, stream, prepare);
+    case 5: return run_instance<5, D, GQ>(p, smem_bytes, stream, prepare);
+    case 6: return run_instance<6, D, GQ>(p, smem_bytes, stream, prepare);
+    case 7: return run_instance<7, D, GQ>(p, smem_bytes, stream, prepare);
+    case 8: return run_instance<8, D, GQ>(p, smem_bytes, stream, prepare);
     default: return cudaErrorInvalidValue;
   }
 }

@@ -12,7 +12,7 @@ constexpr int kSlotBytes = 32768;                       // one ring slot = one w
 constexpr int kMaxSlots = 6;
 constexpr int kTileN = 8;                               // weight rows per page (one 128B-swizzle atom)
 constexpr int kKvBlock = 16;                            // tokens per KV block
-constexpr int kMaxBatch = 4;                            // SIMT GEMV path
+constexpr int kMaxBatch = 8;                            // batch rows of the mma A operand (rows 0..7)
 constexpr int kPartialRing = 8;                         // GEMV tasks whose warp partials may be in flight (> ring slots + 1)
 constexpr int kAttnHalfBytes = kSlotBytes / 2;          // K part, then V part, of an attention slot
 

@@ -78,8 +78,8 @@ PlanSpec PlanSpec::FromJson(const Json& plan) {
   s.batch_lo = int(plan.integer("batch_lo", 1));
   s.batch_hi = int(plan.integer("batch_hi", s.batch_lo));
   s.capacity = int(plan.integer("capacity", 0));
-  if (s.batch_lo < 1 || s.batch_hi < s.batch_lo || s.batch_hi > 4)
-    throw std::invalid_argument("batch interval must lie in [1, 4]");
+  if (s.batch_lo < 1 || s.batch_hi < s.batch_lo || s.batch_hi > kMaxBatch)
+    throw std::invalid_argument("batch interval must lie in [1, 8]");
   if (s.capacity < 2 || s.capacity % kKvBlock) throw std::invalid_argument("capacity must be a positive multiple of 16");
   const Json empty;
   const Json& kv = plan.has("kv") ? plan.at("kv") : empty;

@@ -30,8 +30,8 @@ def plan_document(config: dict, *, batch_lo: int = 1, batch_hi: int | None = Non
     model.setdefault("head_dim", config["hidden_size"] // config["num_attention_heads"])
     model.setdefault("rms_norm_eps", 1e-5)
     batch_hi = batch_lo if batch_hi is None else batch_hi
-    if not 1 <= batch_lo <= batch_hi <= 4:
-        raise ValueError("batch interval must lie in [1, 4]")
+    if not 1 <= batch_lo <= batch_hi <= 8:
+        raise ValueError("batch interval must lie in [1, 8]")
     if capacity < 16 or capacity % 16:
         raise ValueError("capacity must be a positive multiple of the KV block (16)")
     if kv_layout not in ("contiguous", "paged"):
