@@ -52,13 +52,16 @@ def measured_peak_gbs() -> tuple[float, str]:
     return 6650.0, "fallback"
 
 
+MODELS = {"llama-3.1-8b": synthetic.LLAMA_3_1_8B, "llama-3.2-1b": synthetic.LLAMA_3_2_1B}
+
+
 def workload(args) -> dict:
-    config = dict(synthetic.LLAMA_3_1_8B)
+    config = dict(MODELS[args.model])
     if args.layers:
         config["num_hidden_layers"] = args.layers
     batch = args.batch
     contexts = synthetic.seeded_contexts(batch, 512, 8192, seed=2).tolist() if args.context == 0 else [args.context] * batch
-    return {"name": "llama-3.1-8b-shaped", "config": config, "batch": batch, "contexts": contexts}
+    return {"name": f"{args.model}-shaped", "config": config, "batch": batch, "contexts": contexts}
 
 
 class ClockSampler:
@@ -328,6 +331,8 @@ def main() -> None:
     parser.add_argument("--steps", type=int, default=128)
     parser.add_argument("--warmup", type=int, default=4)
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    parser.add_argument("--model", choices=sorted(MODELS), default="llama-3.1-8b",
+                        help="shape of the synthetic model (the headline workload is llama-3.1-8b, batch 1)")
     parser.add_argument("--batch", type=int, default=1)
     parser.add_argument("--context", type=int, default=0, help="0: seeded draw in [512, 8192]")
     parser.add_argument("--layers", type=int, default=0, help="override the depth (profiling a small case)")
