@@ -16,7 +16,7 @@ import torch
 
 from oracle.decoder_oracle import OracleDecoder, PagedKV
 from tilemega_b200 import synthetic
-from tilemega_b200.serving.state import shuffled_block_table
+from tilemega_b200.serving.state import kv_row_swizzle, shuffled_block_table
 
 from harness import GpuRun, assert_parity, bf16_ulp, bf16_weights
 
@@ -124,14 +124,14 @@ def test_ragged_contexts_match_oracle(plan_dir):
     decoder = OracleDecoder(config, weights, torch.bfloat16, capacity)
     kv = PagedKV(config, batch, capacity, torch.bfloat16, table, num_blocks)
     # history: every sequence is prefilled by the oracle up to its own base, and the
-    # oracle's cache is copied into the device pool (same layout by construction)
+    # oracle's cache is copied into the device pool (same layout up to the row swizzle)
     history = synthetic.seeded_tokens(batch, max(bases) + 8, config["vocab_size"], seed=5)
     for b in range(batch):
         if bases[b]:
             sub = PagedKV(config, 1, capacity, torch.bfloat16, table[b:b + 1], num_blocks)
             sub.pool = kv.pool
             decoder.forward(history[b:b + 1, :bases[b]], [0], sub)
-    run.state.kv_storage.copy_(kv.pool)
+    run.state.kv_storage.copy_(kv_row_swizzle(kv.pool))
     prompt_len = 8
     for b in range(batch):
         run.state.tokens[b, bases[b]:bases[b] + prompt_len] = history[b, bases[b]:bases[b] + prompt_len].cuda()

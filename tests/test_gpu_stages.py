@@ -15,6 +15,7 @@ import torch.nn.functional as F
 
 from oracle.decoder_oracle import rms_norm, rotate_half, rope_tables
 from tilemega_b200 import synthetic
+from tilemega_b200.serving.state import kv_row_swizzle
 
 from harness import GpuRun, bf16_ulp, bf16_weights
 
@@ -54,7 +55,7 @@ def test_every_stage_of_one_layer(base, batch, history, plan_dir):
     h_gpu = run.read("serving.mlp").reshape(batch, -1)
     x_gpu = run.read("serving.hidden").reshape(batch, hidden)
     logits_gpu = run.read("serving.logits", torch.float32).reshape(batch, -1)
-    cache = run.state.kv_storage.cpu()                    # [1][2][B][Hkv][cap][D]
+    cache = kv_row_swizzle(run.state.kv_storage.cpu())    # [1][2][B][Hkv][cap][D], logical column order
     p = "model.layers.0."
     # stage 1: RMSNorm + QKV
     x_in = F.embedding(ids[:, pos].long(), w["model.embed_tokens.weight"])

@@ -86,3 +86,12 @@ def test_seeded_weights_are_reproducible_and_ordered():
     assert torch.equal(a["model.norm.weight"], torch.ones(2048))
     assert 0.019 < float(a["model.layers.0.mlp.up_proj.weight"].std()) < 0.021
     assert not torch.equal(a["model.embed_tokens.weight"], synthetic.seeded_weights(small, 1)["model.embed_tokens.weight"])
+
+
+def test_kv_row_swizzle_is_an_involution_with_the_kernel_mapping():
+    from tilemega_b200.serving.state import kv_row_swizzle
+    rows = torch.arange(2 * 32 * 64, dtype=torch.int32).reshape(2, 32, 64)
+    stored = kv_row_swizzle(rows)
+    assert torch.equal(kv_row_swizzle(stored), rows)
+    for t, d in ((0, 5), (13, 42), (31, 63), (8, 17)):
+        assert stored[1, t, (((d >> 3) ^ (t & 7)) << 3) | (d & 7)] == rows[1, t, d]

@@ -899,45 +899,29 @@ __device__ TMB_GEMV_CALL void gemv_stage(Ctx& c, const GemvGeo& geo, const GemvI
 
 // ---------------------------------------------------------------------------
 // arithmetic warps: RoPE + KV append + split-KV decode attention
+//
+// KV rows are stored (in either cache layout) with their 16-byte chunks XOR-ed by
+// (row position mod 8): chunk c of the row at position t sits at chunk c ^ (t & 7).
+// The format is private to the plan (the reference's driver only zero-fills the
+// cache). It makes the 8 rows of an ldmatrix tile land on distinct banks although a
+// ring slot is filled by plain contiguous bulk copies.
 // ---------------------------------------------------------------------------
-template <int N, int LPK>
-__device__ __forceinline__ void subgroup_reduce_scatter(float (&v)[N], int hl) {
-  // Halving exchange over the LPK lanes of a sub-group: afterwards lane hl holds
-  // the totals of values [hl*N/LPK, (hl+1)*N/LPK) in v[0..N/LPK).
-  int n = N;
-#pragma unroll
-  for (int m = LPK / 2; m >= 1; m >>= 1) {
-    const bool up = hl & m;
-    const int half = n / 2;
-#pragma unroll
-    for (int i = 0; i < N / 2; ++i) {
-      if (i < half) {
-        const float send = up ? v[i] : v[i + half];
-        const float recv = __shfl_xor_sync(0xffffffffu, send, m);
-        v[i] = (up ? v[i + half] : v[i]) + recv;
-      }
-    }
-    n = half;
-  }
-}
+__device__ __forceinline__ int kv_swizzled(int d, int pos) { return ((((d >> 3) ^ (pos & 7))) << 3) | (d & 7); }
 
 template <int B, int D, int GQ>
 __device__ void attn_stage(Ctx& c, const LayerPtrs& lp, int past, bool tr, int stage, unsigned long long qkv_stages) {
   constexpr int NK = kAttnHalfBytes / (2 * D);  // keys per slot: 64 (D=128) / 128 (D=64)
-  constexpr int LPK = D / 8;                    // lanes that share one key row
-  constexpr int KPW = 32 / LPK;                 // sub-groups per warp
-  constexpr int KSG = NK / (kConsumerWarps * KPW);  // keys per sub-group per slot (= 4)
-  constexpr int NV = KSG * GQ;                  // scores per sub-group per slot (= 16)
+  constexpr int KW = NK / kConsumerWarps;       // keys per warp per slot: 8 / 16
+  constexpr int KT = KW / 8;                    // 8-key tiles per warp per slot
+  constexpr int DT = D / 8;                     // 8-column tiles of the head dimension
   constexpr int PW = D + 2;                     // floats per (chunk, head) partial: acc, m, l
-  static_assert(KSG == 4 && NV == 16, "attention slot geometry");
+  static_assert(GQ <= 8 && KW % 8 == 0, "attention slot geometry");
   const MegaParams& p = c.p;
-  const int hl = c.lane % LPK, sg = c.lane / LPK;
-  const int sgi = c.warp * KPW + sg;
-  float* qs = reinterpret_cast<float*>(c.xs());                          // [GQ][D] scaled, roped q
-  __nv_bfloat16* knew = reinterpret_cast<__nv_bfloat16*>(qs + GQ * D);   // [D] roped new key
+  const int g = c.lane >> 2, q = c.lane & 3;    // mma fragments: row (query head) g, column pair q
+  __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(c.xs());          // [GQ][D] roped q (bf16, unscaled)
+  __nv_bfloat16* knew = qs + GQ * D;                                     // [D] roped new key
   __nv_bfloat16* vnew = knew + D;                                        // [D] new value
   float* scratch = reinterpret_cast<float*>(vnew + D);                   // [8 warps][GQ][PW]
-  float* sc = c.sc() + (c.warp * 4 + sg) * 16;
   const int qkv_width = (p.heads + 2 * p.kv_heads) * D;
   const __nv_bfloat16* cosb = static_cast<const __nv_bfloat16*>(p.rope_cos);
   const __nv_bfloat16* sinb = static_cast<const __nv_bfloat16*>(p.rope_sin);
@@ -973,7 +957,7 @@ __device__ void attn_stage(Ctx& c, const LayerPtrs& lp, int past, bool tr, int s
       if (hh == GQ + 1) {
         if (tail) {
           vnew[d] = __float2bfloat16_rn(xv);
-          static_cast<__nv_bfloat16*>(lp.v_pool)[new_off + d] = __float2bfloat16_rn(xv);
+          static_cast<__nv_bfloat16*>(lp.v_pool)[new_off + kv_swizzled(d, a.pos)] = __float2bfloat16_rn(xv);
         }
         continue;
       }
@@ -985,106 +969,114 @@ __device__ void attn_stage(Ctx& c, const LayerPtrs& lp, int past, bool tr, int s
       const float rot = d < D / 2 ? -xp : xp;
       const float o = bf16_round(bf16_round(xv * cs) + bf16_round(rot * sn));
       if (hh < GQ) {
-        qs[hh * D + d] = o * p.qk_scale_log2;
+        qs[hh * D + d] = __float2bfloat16_rn(o);
       } else {
         knew[d] = __float2bfloat16_rn(o);
-        static_cast<__nv_bfloat16*>(lp.k_pool)[new_off + d] = __float2bfloat16_rn(o);
+        static_cast<__nv_bfloat16*>(lp.k_pool)[new_off + kv_swizzled(d, a.pos)] = __float2bfloat16_rn(o);
       }
     }
     if (tail) fence_proxy_async();
     consumer_sync();
-    float q[GQ][8];
+    // A fragments of Q for S = Q K^T (m16n8k16): rows 0..GQ-1 are the query heads, the
+    // other rows repeat a head and are never read. qa[s][0/1] = Q[g][16s + 2q (+8), +1].
+    uint32_t qa[D / 16][2];
+    {
+      const uint32_t* qrow = reinterpret_cast<const uint32_t*>(qs + min(g, GQ - 1) * D);
 #pragma unroll
-    for (int h = 0; h < GQ; ++h)
-#pragma unroll
-      for (int j = 0; j < 8; ++j) q[h][j] = qs[h * D + hl * 8 + j];
-    float m[GQ], l[GQ], acc[GQ][8];
-#pragma unroll
-    for (int h = 0; h < GQ; ++h) {
-      m[h] = -INFINITY;
-      l[h] = 0.f;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) acc[h][j] = 0.f;
+      for (int s = 0; s < D / 16; ++s) {
+        qa[s][0] = qrow[8 * s + q];
+        qa[s][1] = qrow[8 * s + 4 + q];
+      }
     }
+    // online softmax state of this lane's row (query head g) over this warp's keys, and
+    // its output row: oacc[dt][0..1] = O[g][8 dt + 2q, +1] (oacc[dt][2..3] belong to unused rows)
+    float m = -INFINITY, l = 0.f;
+    float oacc[DT][4];
+#pragma unroll
+    for (int dt = 0; dt < DT; ++dt) oacc[dt][0] = oacc[dt][1] = oacc[dt][2] = oacc[dt][3] = 0.f;
     for (int s = a.slot0; s < a.slot1; ++s) {
       mbar_wait_warp(c, c.full(c.slot), c.phase, kSiteFull);
       unsigned char* kbase = c.ring(c.slot);
       unsigned char* vbase = kbase + kAttnHalfBytes;
+      const int nkeys = min(NK, a.pos + 1 - s * NK);
       if (tail && s == a.ns - 1) {
-        // the cache row of the new token is being written this step: take it from
-        // this CTA's own copy instead of whatever the bulk copy saw
+        // the cache row of the new token is being written this step: take it from this
+        // CTA's own copy; and rows past the context may hold anything (stale ring bytes
+        // where no block was copied): zero them in V, where a 0 * NaN would poison P*V
         const int r = a.pos - s * NK;
         if (c.tid < D / 8) {
-          reinterpret_cast<uint4*>(kbase + size_t(r) * D * 2)[c.tid] = reinterpret_cast<const uint4*>(knew)[c.tid];
+          reinterpret_cast<uint4*>(kbase + size_t(r) * D * 2)[c.tid ^ (r & 7)] = reinterpret_cast<const uint4*>(knew)[c.tid];
         } else if (c.tid < D / 4) {
-          reinterpret_cast<uint4*>(vbase + size_t(r) * D * 2)[c.tid - D / 8] =
+          reinterpret_cast<uint4*>(vbase + size_t(r) * D * 2)[(c.tid - D / 8) ^ (r & 7)] =
               reinterpret_cast<const uint4*>(vnew)[c.tid - D / 8];
         }
+        for (int i = nkeys * (D / 8) + c.tid; i < NK * (D / 8); i += kConsumerThreads)
+          reinterpret_cast<uint4*>(vbase)[i] = make_uint4(0u, 0u, 0u, 0u);
         fence_proxy_async();   // generic writes into a slot the bulk engine refills later
         consumer_sync();
       }
-      const int nkeys = min(NK, a.pos + 1 - s * NK);
-      const int key0 = sgi * KSG;
-      {
-        // every sub-group runs the dot products (the shuffles below are warp-wide);
-        // rows past nkeys hold stale bytes and are masked by selection afterwards
-        float sv[NV];
+      const int key0 = c.warp * KW;
+      if (key0 < nkeys) {   // warp-uniform
+        // ---- S = Q K^T for this warp's keys: sc[kt][0..1] = S[g][key0 + 8 kt + 2q, +1]
+        float sc[KT][4];
+        const int lr = c.lane & 7, lm = c.lane >> 3;   // ldmatrix: row lr of tile lm
 #pragma unroll
-        for (int kk = 0; kk < KSG; ++kk) {
-          float kf[8];
-          unpack8(*reinterpret_cast<const uint4*>(kbase + size_t(key0 + kk) * D * 2 + hl * 16), kf);
+        for (int kt = 0; kt < KT; ++kt) {
+          sc[kt][0] = sc[kt][1] = sc[kt][2] = sc[kt][3] = 0.f;
+          const uint32_t krow = smem_u32(kbase) + uint32_t((key0 + 8 * kt + lr) * D * 2);
 #pragma unroll
-          for (int h = 0; h < GQ; ++h) {
-            float d0 = 0.f;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) d0 = fmaf(q[h][j], kf[j], d0);
-            sv[kk * GQ + h] = d0;
+          for (int cq = 0; cq < D / 32; ++cq) {     // four 16-byte chunks = two k-steps of 16 columns
+            uint32_t kb[4];
+            ldmatrix_x4(kb, krow + 16 * ((4 * cq + lm) ^ lr));
+            mma_bf16_m16n8k16(sc[kt], qa[2 * cq][0], qa[2 * cq][1], kb[0], kb[1]);
+            mma_bf16_m16n8k16(sc[kt], qa[2 * cq + 1][0], qa[2 * cq + 1][1], kb[2], kb[3]);
           }
         }
-        subgroup_reduce_scatter<NV, LPK>(sv, hl);
-        // lane hl now owns NV/LPK consecutive scores; share all 16 through shared memory
+        // ---- online softmax in base 2 (scale log2(e)/sqrt(D)); keys past the context are masked
+        float mx = m;
 #pragma unroll
-        for (int i = 0; i < NV / LPK; ++i) sc[hl * (NV / LPK) + i] = sv[i];
-      }
-      __syncwarp();
-      if (key0 < nkeys) {
-        float pr[KSG][GQ];
-#pragma unroll
-        for (int kk = 0; kk < KSG; ++kk) {
-          const float4 s4 = *reinterpret_cast<const float4*>(sc + kk * 4);
-          const bool valid = key0 + kk < nkeys;
-          pr[kk][0] = valid ? s4.x : -INFINITY;
-          pr[kk][1] = valid ? s4.y : -INFINITY;
-          pr[kk][2] = valid ? s4.z : -INFINITY;
-          pr[kk][3] = valid ? s4.w : -INFINITY;
+        for (int kt = 0; kt < KT; ++kt) {
+          const int k = key0 + 8 * kt + 2 * q;
+          sc[kt][0] = k < nkeys ? sc[kt][0] * p.qk_scale_log2 : -INFINITY;
+          sc[kt][1] = k + 1 < nkeys ? sc[kt][1] * p.qk_scale_log2 : -INFINITY;
+          mx = fmaxf(mx, fmaxf(sc[kt][0], sc[kt][1]));
         }
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));   // key0 < nkeys: at least one finite score in the row
+        const float alpha = ex2(m - mx);
+        m = mx;
+        float sum = 0.f;
+        uint32_t phi[KT], plo[KT];
 #pragma unroll
-        for (int h = 0; h < GQ; ++h) {
-          float mn = m[h];
-#pragma unroll
-          for (int kk = 0; kk < KSG; ++kk) mn = fmaxf(mn, pr[kk][h]);
-          // key0 < nkeys, so at least one score is finite and mn is finite
-          const float alpha = ex2(m[h] - mn);
-          m[h] = mn;
-          float sum = 0.f;
-#pragma unroll
-          for (int kk = 0; kk < KSG; ++kk) {
-            pr[kk][h] = ex2(pr[kk][h] - mn);
-            sum += pr[kk][h];
-          }
-          l[h] = fmaf(l[h], alpha, sum);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) acc[h][j] *= alpha;
+        for (int kt = 0; kt < KT; ++kt) {
+          const float p0 = ex2(sc[kt][0] - mx), p1 = ex2(sc[kt][1] - mx);
+          sum += p0 + p1;
+          // P as a bf16 head plus a bf16 remainder: two tensor-pipe products keep ~16
+          // mantissa bits of the probabilities instead of 8
+          phi[kt] = pack_bf16x2(p0, p1);
+          plo[kt] = pack_bf16x2(p0 - bf_lo(phi[kt]), p1 - bf_hi(phi[kt]));
         }
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        l = fmaf(l, alpha, sum);
 #pragma unroll
-        for (int kk = 0; kk < KSG; ++kk) {
-          if (key0 + kk < nkeys) {
-            float vf[8];
-            unpack8(*reinterpret_cast<const uint4*>(vbase + size_t(key0 + kk) * D * 2 + hl * 16), vf);
+        for (int dt = 0; dt < DT; ++dt) {
+          oacc[dt][0] *= alpha;
+          oacc[dt][1] *= alpha;
+        }
+        // ---- O += P V: V tiles transposed on load (row-major V[key][d] is the B operand's k x n)
 #pragma unroll
-            for (int h = 0; h < GQ; ++h)
+        for (int kt = 0; kt < KT; ++kt) {
+          const uint32_t vrow = smem_u32(vbase) + uint32_t((key0 + 8 * kt + lr) * D * 2);
 #pragma unroll
-              for (int j = 0; j < 8; ++j) acc[h][j] = fmaf(pr[kk][h], vf[j], acc[h][j]);
+          for (int cq = 0; cq < DT / 4; ++cq) {
+            uint32_t vb[4];
+            ldmatrix_x4_trans(vb, vrow + 16 * ((4 * cq + lm) ^ lr));
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              mma_bf16_m16n8k8(oacc[4 * cq + j], phi[kt], vb[j]);
+              mma_bf16_m16n8k8(oacc[4 * cq + j], plo[kt], vb[j]);
+            }
           }
         }
       }
@@ -1092,35 +1084,17 @@ __device__ void attn_stage(Ctx& c, const LayerPtrs& lp, int past, bool tr, int s
       if (c.lane == 0) mbar_arrive(c.empty(c.slot));
       c.advance();
     }
-    // ---- merge the sub-groups of a warp with shuffles, then the warps through scratch
+    // ---- the warps' states meet in scratch: lanes of rows g < GQ hold head g
+    if (g < GQ) {
+      float* dst = scratch + (c.warp * GQ + g) * PW;
 #pragma unroll
-    for (int mask = LPK; mask < 32; mask <<= 1) {
-#pragma unroll
-      for (int h = 0; h < GQ; ++h) {
-        const float mo = __shfl_xor_sync(0xffffffffu, m[h], mask);
-        const float lo = __shfl_xor_sync(0xffffffffu, l[h], mask);
-        const float mx = fmaxf(m[h], mo);
-        const float ms = mx == -INFINITY ? 0.f : mx;
-        const float wa = ex2(m[h] - ms), wb = ex2(mo - ms);
-        l[h] = l[h] * wa + lo * wb;
-        m[h] = mx;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const float ao = __shfl_xor_sync(0xffffffffu, acc[h][j], mask);
-          acc[h][j] = acc[h][j] * wa + ao * wb;
-        }
+      for (int dt = 0; dt < DT; ++dt) {
+        dst[8 * dt + 2 * q] = oacc[dt][0];
+        dst[8 * dt + 2 * q + 1] = oacc[dt][1];
       }
-    }
-    if (sg == 0) {
-#pragma unroll
-      for (int h = 0; h < GQ; ++h) {
-        float* dst = scratch + (c.warp * GQ + h) * PW;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) dst[hl * 8 + j] = acc[h][j];
-        if (hl == 0) {
-          dst[D] = m[h];
-          dst[D + 1] = l[h];
-        }
+      if (q == 0) {
+        dst[D] = m;
+        dst[D + 1] = l;
       }
     }
     consumer_sync();

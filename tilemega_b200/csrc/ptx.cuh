@@ -155,6 +155,26 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t smem_addr
                : "r"(smem_addr));
 }
 
+// The transposing form: the same addressing, each 8x8 tile delivered transposed
+// (what the B operand of P*V needs from row-major V[key][d]).
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t smem_addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem_addr));
+}
+
+// D[16x8] += A[16x8] * B[8x8] (k = 8), bf16 operands, fp32 accumulators; rows 8..15 of A are zero.
+__device__ __forceinline__ void mma_bf16_m16n8k8(float (&d)[4], uint32_t a0, uint32_t b0) {
+  asm("mma.sync.aligned.m16n8k8.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5}, {%6}, {%0, %1, %2, %3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(0u), "r"(b0));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  return uint32_t(__bfloat16_as_ushort(__float2bfloat16_rn(lo))) |
+         (uint32_t(__bfloat16_as_ushort(__float2bfloat16_rn(hi))) << 16);
+}
+
 // D[16x8] += A[16x16] * B[16x8], bf16 operands, fp32 accumulators. Rows 8..15 of A
 // are zero here (the batch has at most 8 rows), so a1 = a3 = 0.
 __device__ __forceinline__ void mma_bf16_m16n8k16(float (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {

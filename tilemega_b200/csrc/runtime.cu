@@ -248,7 +248,7 @@ void* tm_plan_create(int batch, void* const* external, int device) {
   const double watchdog_ms = watchdog ? std::atof(watchdog) : 2000.0;
   p.watchdog_ns = (unsigned long long)(std::max(watchdog_ms, 0.001) * 1e6);
   // shared memory: activation rows (or the attention scratch, whichever is larger) + ring
-  const int attention_scratch = 4 * s.head_dim * 4 + 2 * s.head_dim * 2 + 8 * 4 * (s.head_dim + 2) * 4;
+  const int attention_scratch = 4 * s.head_dim * 2 + 2 * s.head_dim * 2 + 8 * 4 * (s.head_dim + 2) * 4 + 64;
   // rows of the widest GEMV input; one extra hidden-wide row holds the RMSNorm weights
   // (rows are padded by 8 elements so that the batch rows of a k-chunk sit on distinct banks)
   // a normalised stage also parks its raw rows and the norm weights there: 2*batch + 1 hidden-wide rows

@@ -54,6 +54,25 @@ def rotary_tables(config: dict, capacity: int, device: torch.device | str) -> tu
             table.sin().to(torch.bfloat16).to(device).contiguous())
 
 
+def kv_row_swizzle(rows: torch.Tensor) -> torch.Tensor:
+    """Convert KV rows between logical order and the plan's storage order.
+
+    `rows` is [..., T, D] with T the row position inside its allocation (a 16-row
+    block of the pool, or the capacity axis of the contiguous cache). The kernel
+    keeps 16-byte chunk c of the row at position t at chunk c ^ (t mod 8), so that
+    the eight rows of a shared-memory matrix load sit on different banks. The
+    mapping is its own inverse: call it to bring history into a cache, and again
+    to read rows back. The reference's driver only zero-fills its cache
+    (python/tilemega/serving/state.py:86-98), for which this is the identity.
+    """
+    t, d = rows.shape[-2], rows.shape[-1]
+    if d % 8:
+        raise ValueError("head_dim must be a multiple of 8")
+    chunk = torch.arange(d // 8, device=rows.device)[None, :] ^ (torch.arange(t, device=rows.device)[:, None] & 7)
+    index = (chunk[:, :, None] * 8 + torch.arange(8, device=rows.device)).reshape(t, d)
+    return torch.gather(rows, -1, index.expand(rows.shape))
+
+
 def shuffled_block_table(batch: int, max_blocks: int, num_blocks: int, seed: int = 0) -> torch.Tensor:
     """A seeded permutation of the pool dealt to the sequences: [B][max_blocks] int32."""
     if num_blocks < batch * max_blocks:
