@@ -90,12 +90,32 @@ int tm_plan_set_prompt_len(void* plan, int prompt_len);
 unsigned tm_plan_pdl_enabled(void* plan);
 /* plan.py:76. Dynamic shared memory of the persistent kernel. */
 uint64_t tm_plan_execution_smem(void* plan, unsigned mode);
-/* ServingAbi.h:49-55. Tensor-parallel extension: this plan is unsharded. */
+/* ServingAbi.h:49-55. Tensor-parallel extension. A plan whose sidecar says "tp": T is
+ * ONE RANK's plan (Megatron sharding: q/k/v, gate/up and lm_head by rows, o and down by
+ * columns; the weight recipes carry "shard" so each rank packs its slice). tp_world()
+ * returns T; tp_bytes(0) is the size of a rank's all-reduce receive region, tp_bytes(1)
+ * of its argmax exchange block; the caller allocates both ZEROED on each rank's device
+ * and gives bind_tp, on every rank, the T region pointers and T block pointers as they
+ * are valid in the calling process (the rank's own, and its peers' through peer access
+ * or CUDA IPC). bind_tp must precede the first launch; all ranks must then launch the
+ * same steps. Inside the kernel the all-reduce after o and after down is fused into the
+ * GEMV epilogue: packets of {two bf16 sums, epoch} are stored into the peers' regions
+ * and summed in rank order (Sm90DenseEpilogue.h:43-86); lm_head winners are exchanged
+ * the same way (Sm90DenseHead.cuh:139-201). */
 unsigned tm_plan_tp_world(void);
 unsigned long long tm_plan_tp_bytes(unsigned which);
 int tm_plan_bind_tp(void* plan, int rank, void* const* ar, void* const* x);
 
 /* ---- additions of this library (probed by name; absent in the reference) */
+
+/* One process per GPU: allocate a zeroed region that is an allocation of its own, export
+ * it as a 64-byte CUDA IPC handle, map a peer's handle, unmap it. The reference drives all ranks from one process
+ * (python/tilemega/serving/tp_engine.py:47-112) and needs none of these. */
+int tm_ipc_alloc(int device, uint64_t bytes, void** device_pointer);   /* zeroed, its own allocation */
+int tm_ipc_free(void* device_pointer);
+int tm_ipc_export(void* device_pointer, unsigned char* handle64);
+int tm_ipc_open(const unsigned char* handle64, void** device_pointer);
+int tm_ipc_close(void* device_pointer);
 
 /* Last error text of the calling thread's most recent failing call. */
 const char* tm_plan_last_error(void);

@@ -12,6 +12,18 @@ reference module itself (tests/golden/make_golden.py imports it from the
 reference tree); tests/test_oracle_golden.py checks this restatement against
 them in fp32 and bf16.
 
+Tensor parallelism (tp > 1) is restated as what T ranks compute together: the
+rank modules of export.py:39-47,107-112,152-163 each produce the partial o_proj /
+down_proj output of their contiguous slice of heads / intermediate columns (the
+slices of python/tilemega/serving/weights.py:78-96), and the kernel epilogue
+adds the ranks' partials, each already rounded to the model dtype, in fp32 in
+ascending rank order, rounds the sum and then adds the residual
+(include/tilemega/Backend/Sm90DenseEpilogue.h:43-86). The per-rank partials are
+pinned by tests/golden/tiny_tp2.pt (made by tests/golden/make_golden_tp.py from
+the reference's rank modules); the summation rule is read from the kernel source.
+The sharded lm_head changes nothing: each rank scores a slice of the rows and the
+ranks' winners are compared with ties to the smaller index (Sm90DenseHead.cuh:139-201).
+
 Every op is the same torch op on the same dtype as the reference, so in bf16 the
 rounding sites are the reference's: one rounding per linear output, RMSNorm
 `w * (x.float() * rsqrt(mean x^2 + eps)).to(dtype)`, RoPE product-product-sum,
@@ -94,7 +106,7 @@ class OracleDecoder:
     """forward(ids [B][S], start [B]) -> logits [B][S][V]; appends to the cache."""
 
     def __init__(self, config: dict, weights: dict[str, torch.Tensor], dtype: torch.dtype = torch.float32,
-                 capacity: int = 256, attention_fp32: bool = False):
+                 capacity: int = 256, attention_fp32: bool = False, tp: int = 1):
         # attention_fp32 restates the numerics of the reference's *kernel* instead of
         # its module: scores, softmax and the probability-value product stay in fp32
         # and only the context is rounded to the model dtype
@@ -104,6 +116,10 @@ class OracleDecoder:
         self.config = config
         self.dtype = dtype
         self.attention_fp32 = attention_fp32
+        self.tp = tp
+        for key in ("num_attention_heads", "num_key_value_heads", "intermediate_size", "vocab_size"):
+            if config[key] % tp:
+                raise ValueError(f"{key} does not divide by the tensor parallel degree {tp}")
         self.w = {name: tensor.to(dtype) for name, tensor in weights.items()}
         if "lm_head.weight" not in self.w:
             if not config.get("tie_word_embeddings", False):
@@ -115,7 +131,29 @@ class OracleDecoder:
         self.dim = head_dim_of(config)
         self.cos, self.sin = rope_tables(config, capacity, dtype)
 
+    def row_sharded_partials(self, x: torch.Tensor, weight: torch.Tensor) -> list[torch.Tensor]:
+        """The ranks' partial outputs of a linear whose reduction axis is split into tp
+        contiguous parts (o_proj, down_proj): one model-dtype rounding per rank."""
+        width = weight.shape[1] // self.tp
+        return [F.linear(x[..., q * width:(q + 1) * width], weight[:, q * width:(q + 1) * width])
+                for q in range(self.tp)]
+
+    def all_reduce(self, partials: list[torch.Tensor]) -> torch.Tensor:
+        """Sm90DenseEpilogue.h:64-86: fp32 sum in ascending rank order, then one rounding."""
+        if len(partials) == 1:
+            return partials[0]
+        total = torch.zeros_like(partials[0], dtype=torch.float32)
+        for part in partials:
+            total = total + part.float()
+        return total.to(partials[0].dtype)
+
     def attention(self, layer: int, x: torch.Tensor, start: list[int], kv: PagedKV) -> torch.Tensor:
+        return self.all_reduce(self.attention_partials(layer, x, start, kv))
+
+    def mlp(self, layer: int, x: torch.Tensor) -> torch.Tensor:
+        return self.all_reduce(self.mlp_partials(layer, x))
+
+    def attention_partials(self, layer: int, x: torch.Tensor, start: list[int], kv: PagedKV) -> list[torch.Tensor]:
         # export.py:69-100, one sequence at a time because lengths differ
         p = f"model.layers.{layer}.self_attn."
         batch, seq, _ = x.shape
@@ -145,13 +183,13 @@ class OracleDecoder:
                 probability = torch.softmax(score.float(), dim=-1).to(x.dtype)
                 attended = torch.matmul(probability, values)
             context[b] = attended.transpose(0, 1).reshape(seq, self.heads * self.dim)
-        return F.linear(context, self.w[p + "o_proj.weight"])
+        return self.row_sharded_partials(context, self.w[p + "o_proj.weight"])
 
-    def mlp(self, layer: int, x: torch.Tensor) -> torch.Tensor:
+    def mlp_partials(self, layer: int, x: torch.Tensor) -> list[torch.Tensor]:
         # export.py:115-116
         p = f"model.layers.{layer}.mlp."
-        return F.linear(F.silu(F.linear(x, self.w[p + "gate_proj.weight"])) * F.linear(x, self.w[p + "up_proj.weight"]),
-                        self.w[p + "down_proj.weight"])
+        hidden = F.silu(F.linear(x, self.w[p + "gate_proj.weight"])) * F.linear(x, self.w[p + "up_proj.weight"])
+        return self.row_sharded_partials(hidden, self.w[p + "down_proj.weight"])
 
     @torch.inference_mode()
     def forward(self, ids: torch.Tensor, start: list[int], kv: PagedKV,

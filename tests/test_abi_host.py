@@ -87,10 +87,16 @@ def test_create_without_a_gpu_fails_loudly(plan_dir):
 
 
 def test_unsupported_shapes_are_rejected(plan_dir):
-    bad = dict(synthetic.TINY, hidden_size=1024)
+    bad = dict(synthetic.TINY, hidden_size=1028)   # neither rows nor reductions in whole 16-byte chunks
     so = emit_plan(bad, plan_dir, batch_lo=1, batch_hi=1, capacity=32)
-    with pytest.raises(RuntimeError, match="K must be a multiple"):
+    with pytest.raises(RuntimeError, match="must be a multiple"):
         PlanLibrary(so)
+    # a reduction that is not a whole number of pages is padded, not rejected
+    padded = PlanLibrary(emit_plan(dict(synthetic.TINY, intermediate_size=1536), plan_dir, batch_lo=1, batch_hi=1,
+                                   capacity=32))
+    table = {buffer.name: buffer for buffer in padded.buffers}
+    assert table["l0.down.weight"].elements_constant == synthetic.TINY["hidden_size"] * 2048
+    assert table["serving.mlp"].elements_per_batch == 1536
     with pytest.raises(ValueError):
         plan_document(synthetic.TINY, batch_lo=1, batch_hi=9, capacity=32)
     with pytest.raises(ValueError):

@@ -212,3 +212,16 @@ def test_bounded_wait_gives_up_and_returns(plan_dir):
     run.plan.launch(0, 2, run.stream)
     run.check_alive()
     run.close()
+
+
+def test_reduction_padded_to_whole_pages(plan_dir):
+    """A reduction length that is not a multiple of the 2048-column page (down-proj over
+    1536 columns): the weights' pad columns are zero and the staged rows' too."""
+    config = dict(synthetic.TINY, intermediate_size=1536)
+    batch, prompt_len, new_tokens, capacity = 2, 11, 4, 32
+    weights = bf16_weights(config)
+    prompt = synthetic.seeded_tokens(batch, prompt_len, config["vocab_size"], seed=5)
+    run = GpuRun(config, weights, batch, capacity, plan_dir)
+    tokens, logits = run.greedy(prompt, new_tokens)
+    assert_as_accurate_as_reference_bf16(config, weights, prompt, tokens, logits, capacity, "padded reduction")
+    run.close()

@@ -60,3 +60,37 @@ def test_oracle_reproduces_reference_llama_1b(mode):
     top = logits.topk(8, dim=-1)
     assert torch.equal(top.indices.to(torch.int32), golden["top_indices"])
     assert (top.values - golden["top_values"]).abs().max().item() <= 0.04
+
+
+def test_oracle_tensor_parallel_partials_match_reference_rank_modules():
+    """The oracle's per-rank o_proj / down_proj partials and vocabulary slices are the
+    outputs of the reference's own rank modules (tests/golden/make_golden_tp.py), bit
+    for bit; and the rank-ordered sum of T = 1 is the unsharded linear."""
+    from oracle.decoder_oracle import rms_norm
+    import torch.nn.functional as F
+    record = torch.load(GOLDEN / "tiny_tp2.pt")
+    config, world, batch, past = record["config"], record["world"], record["batch"], record["past"]
+    weights = synthetic.seeded_weights(config, seed=0, dtype=torch.bfloat16)
+    weights.setdefault("lm_head.weight", weights["model.embed_tokens.weight"])
+    decoder = OracleDecoder(config, weights, torch.bfloat16, capacity=32, tp=world)
+    kv = PagedKV(config, batch, 32, torch.bfloat16)
+    for b in range(batch):
+        kv.append(0, b, 0, record["past_k"][b].transpose(0, 1), record["past_v"][b].transpose(0, 1))
+    x = record["x"]
+    normed = rms_norm(x, decoder.w["model.layers.0.input_layernorm.weight"], decoder.eps)
+    attention = decoder.attention_partials(0, normed, [past] * batch, kv)
+    mlp = decoder.mlp_partials(0, rms_norm(x, decoder.w["model.layers.0.post_attention_layernorm.weight"], decoder.eps))
+    assert len(attention) == len(mlp) == world
+    for rank in range(world):
+        # the rank module runs the whole batch in one GEMM; the oracle one sequence at a
+        # time for attention: identical ops per row, so the bf16 outputs agree exactly
+        assert torch.equal(attention[rank], record["attention"][rank])
+        assert torch.equal(mlp[rank], record["mlp"][rank])
+    head = F.linear(rms_norm(x, decoder.w["model.norm.weight"], decoder.eps), decoder.w["lm_head.weight"])
+    assert torch.equal(head, torch.cat(record["head"], dim=-1))
+    # the all-reduce rule: fp32 sum of the bf16 partials in rank order, one rounding
+    total = (record["mlp"][0].float() + record["mlp"][1].float()).to(torch.bfloat16)
+    assert torch.equal(decoder.mlp(0, rms_norm(x, decoder.w["model.layers.0.post_attention_layernorm.weight"],
+                                               decoder.eps)), total)
+    single = OracleDecoder(config, weights, torch.bfloat16, capacity=32, tp=1)
+    assert len(single.mlp_partials(0, x)) == 1

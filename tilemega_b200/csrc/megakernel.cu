@@ -498,6 +498,8 @@ struct GemvIo {
   void* out;           // kEpiStore: bf16 [B][n]; kEpiResidual: x; kEpiSwiGLU: h [B][n/2]; kEpiHead: logits
   unsigned long long* ready;   // kEpiStore: per-group counters bumped once per stored row tile (or null)
   int tiles_per_group;
+  int ar_region;               // kEpiResidualAllReduce: which of the two packet regions (0: o, 1: down)
+  uint32_t ar_epoch;           // ... and the epoch its packets carry (never 0, grows with every all-reduce)
 };
 
 // Where the four 32-bit words of 16-byte chunk i of an activation row go. The
@@ -522,10 +524,12 @@ __device__ __forceinline__ void store_row_chunk(uint32_t* row, int i, const uint
 // Rows 0..B-1 of the staging area are the rows the GEMV reads; for a normalised
 // stage the raw rows go to rows B..2B-1 and the norm weights to row 2B in the same
 // pass, so that their L2 round trips overlap.
+// Columns [k_src, k) do not exist in the source rows (the weights are zero-padded
+// there): they are staged as zeros.
 template <int B>
-__device__ __forceinline__ void stage_rows(Ctx& c, const GemvIo& io, int k) {
+__device__ __forceinline__ void stage_rows(Ctx& c, const GemvIo& io, int k, int k_src) {
   const MegaParams& p = c.p;
-  const int chunks = k >> 3;
+  const int chunks = k >> 3, src_chunks = k_src >> 3;
   const int pitch = chunks + 1;   // rows are k + 8 elements apart, so the batch rows of a block sit on distinct banks
   uint4* xs4 = reinterpret_cast<uint4*>(c.xs());
   const uint4* nw = reinterpret_cast<const uint4*>(io.norm);
@@ -535,18 +539,19 @@ __device__ __forceinline__ void stage_rows(Ctx& c, const GemvIo& io, int k) {
     const uint4* src;
     if (io.embed) {
       const int tok = min(max(c.tok()[b], 0), p.vocab - 1);
-      src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(io.src) + size_t(tok) * k);
+      src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(io.src) + size_t(tok) * k_src);
     } else {
-      src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(io.src) + size_t(b) * k);
+      src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(io.src) + size_t(b) * k_src);
     }
     const bool own = io.embed && (b % p.grid) == int(blockIdx.x);
-    uint4* xg = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.x) + size_t(b) * k);
+    uint4* xg = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.x) + size_t(b) * k_src);
     float acc = 0.f;
     for (int i = c.tid; i < chunks; i += kConsumerThreads) {
-      const uint4 v = io.embed ? __ldg(src + i) : __ldcg(src + i);
-      if (own) xg[i] = v;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (i < src_chunks) v = io.embed ? __ldg(src + i) : __ldcg(src + i);
+      if (own && i < src_chunks) xg[i] = v;
       if (io.norm) {
-        if (b == 0) xs4[2 * B * pitch + i] = __ldg(nw + i);
+        if (b == 0) xs4[2 * B * pitch + i] = i < src_chunks ? __ldg(nw + i) : make_uint4(0u, 0u, 0u, 0u);
         xs4[(B + b) * pitch + i] = v;
         float f[8];
         unpack8(v, f);
@@ -572,7 +577,7 @@ __device__ __forceinline__ void stage_rows(Ctx& c, const GemvIo& io, int k) {
       float total = 0.f;
 #pragma unroll
       for (int w = 0; w < kConsumerWarps; ++w) total += c.wsum()[b * 8 + w];
-      const float inv = 1.0f / sqrtf(total / float(k) + p.eps);
+      const float inv = 1.0f / sqrtf(total / float(k_src) + p.eps);
       for (int i = c.tid; i < chunks; i += kConsumerThreads) {
         float f[8], w[8];
         unpack8(xs4[(B + b) * pitch + i], f);    // both written by this same thread above
@@ -740,8 +745,8 @@ __device__ __forceinline__ void gemv_epilogue(Ctx& c, const GemvGeo& geo, const 
         // bf16-rounded value, as the reference's head epilogue does
         if (p.write_logits) static_cast<float*>(io.out)[size_t(b) * geo.n + row] = v;
         // ties -> smaller index (include/tilemega/Backend/Sm90DenseEpilogue.h:166-184)
-        float bv = row < p.vocab ? vb : -INFINITY;
-        int bi = row;
+        float bv = vb;
+        int bi = p.head_base + row;   // this rank's head rows are a slice of the vocabulary
 #pragma unroll
         for (int m = 1; m < 8; m <<= 1) {
           const float ov = __shfl_xor_sync(mask, bv, m);
@@ -751,6 +756,39 @@ __device__ __forceinline__ void gemv_epilogue(Ctx& c, const GemvGeo& geo, const 
         if (bv > best_val[pass] || (bv == best_val[pass] && bi < best_idx[pass])) {
           best_val[pass] = bv;   // the 8 lanes of a sequence all hold its candidate
           best_idx[pass] = bi;
+        }
+      } else if (io.epilogue == kEpiResidualAllReduce) {
+        // Tensor parallel: every rank holds the sum over its own slice of the reduction.
+        // The ranks exchange their sums rounded to bf16, two columns and the epoch per
+        // 8-byte packet, stored straight into each peer's receive region; every rank
+        // adds them in ascending rank order (bitwise the same x on all ranks), rounds,
+        // and adds the residual (include/tilemega/Backend/Sm90DenseEpilogue.h:43-86).
+        const float vb1 = __shfl_down_sync(mask, vb, 1);
+        const float res1 = __shfl_down_sync(mask, e.residual[pass], 1);
+        if ((r & 1) == 0) {
+          const uint32_t mine = pack_bf16x2(vb, vb1);
+          const size_t half = size_t(geo.n) >> 1;
+          const size_t region = size_t(io.ar_region) * p.tp_world * B * half + (size_t(row) >> 1);
+          const unsigned long long packet = ((unsigned long long)io.ar_epoch << 32) | mine;
+          for (int q = 0; q < p.tp_world; ++q)
+            if (q != p.tp_rank) st_relaxed_sys(p.ar[q] + region + (size_t(p.tp_rank) * B + b) * half, packet);
+          float sx = 0.f, sy = 0.f;
+          for (int q = 0; q < p.tp_world; ++q) {
+            uint32_t bits = mine;
+            if (q != p.tp_rank) {
+              const unsigned long long* slot = p.ar[p.tp_rank] + region + (size_t(q) * B + b) * half;
+              unsigned long long seen, t0 = 0;
+              uint32_t polls = 0;
+              while (uint32_t((seen = ld_relaxed_sys(slot)) >> 32) != io.ar_epoch) {
+                if ((++polls & 63u) == 0 && wait_give_up(p, t0, kSitePeer, io.ar_epoch, seen)) break;
+              }
+              bits = uint32_t(seen);
+            }
+            sx += bf_lo(bits);
+            sy += bf_hi(bits);
+          }
+          const uint32_t pair = pack_bf16x2(bf16_round(sx) + e.residual[pass], bf16_round(sy) + res1);
+          *reinterpret_cast<uint32_t*>(static_cast<__nv_bfloat16*>(io.out) + size_t(b) * geo.n + row) = pair;
         }
       } else {
         __nv_bfloat16* out = static_cast<__nv_bfloat16*>(io.out) + size_t(b) * geo.n + row;
@@ -777,7 +815,7 @@ __device__ __forceinline__ void gemv_epilogue(Ctx& c, const GemvGeo& geo, const 
 template <int B>
 __device__ TMB_GEMV_CALL void gemv_stage(Ctx& c, const GemvGeo& geo, const GemvIo& io, bool tr, int stage) {
   const MegaParams& p = c.p;
-  stage_rows<B>(c, io, geo.k);
+  stage_rows<B>(c, io, geo.k, geo.k_src);
   trace_mark(c, tr, stage, 2);
   // per-warp running argmax (each warp runs every eighth epilogue); merged by the caller
   float best_val[EpiPasses<B>::value];
@@ -795,10 +833,6 @@ __device__ TMB_GEMV_CALL void gemv_stage(Ctx& c, const GemvGeo& geo, const GemvI
   const unsigned char* const xs = c.xs();
   uint64_t* const full0 = c.full(0);
   uint64_t* const empty0 = c.empty(0);
-  // Warp (n mod 8) owns the epilogue of this CTA's n-th task and runs it one task
-  // late, after its own pages of task n+1: by then the other warps' partial sums
-  // have long arrived, so no warp ever waits for another one here, and the cost of
-  // an epilogue is spread as one eighth per task instead of stalling every task.
   // Warp (n mod 8) owns the epilogue of this CTA's n-th task and runs it one task
   // late, after its own pages of task n+1: by then the other warps' partial sums
   // have long arrived, so no warp ever waits for another one here, and the cost of
@@ -824,7 +858,7 @@ __device__ TMB_GEMV_CALL void gemv_stage(Ctx& c, const GemvGeo& geo, const GemvI
 #pragma unroll
     for (int pass = 0; pass < EpiPasses<B>::value; ++pass) {
       residual[pass] = 0.f;
-      if (io.epilogue == kEpiResidual && owner && 32 * pass + lane < kTileN * B)
+      if ((io.epilogue == kEpiResidual || io.epilogue == kEpiResidualAllReduce) && owner && 32 * pass + lane < kTileN * B)
         residual[pass] = bf16_from_bits(__ldcg(reinterpret_cast<const unsigned short*>(io.out) +
                                                size_t(4 * pass + (lane >> 3)) * geo.n + rt * kTileN + (lane & 7)));
     }
@@ -1200,6 +1234,10 @@ __device__ void consumer_main(Ctx& c) {
     const bool tr = p.trace != nullptr && step == p.trace_step;
     int stage = 0;
     LayerPtrs lp = p.layer[0];
+    // tensor parallel: o and down end in an all-reduce; epochs count all-reduces since the plan was made
+    const int residual_kind = p.tp_world > 1 ? kEpiResidualAllReduce : kEpiResidual;
+    const unsigned long long steps_before = p.tp_steps + (unsigned long long)si;
+    const uint32_t ar_epoch0 = uint32_t(steps_before * (unsigned long long)(2 * p.layers)) + 1u;
     for (int l = 0; l < p.layers; ++l) {
       // the next layer's pointer record is fetched a whole layer ahead of its use
       const LayerPtrs upcoming = p.layer[min(l + 1, p.layers - 1)];
@@ -1210,7 +1248,7 @@ __device__ void consumer_main(Ctx& c) {
         if (!grid_wait(c)) return;
       }
       trace_mark(c, tr, stage, 1);
-      io = GemvIo{l == 0 ? p.embed : p.x, lp.norm1, l == 0, kEpiStore, p.qkv, p.qkv_ready, (GQ + 2) * D / kTileN};
+      io = GemvIo{l == 0 ? p.embed : p.x, lp.norm1, l == 0, kEpiStore, p.qkv, p.qkv_ready, (GQ + 2) * D / kTileN, 0, 0u};
       gemv_stage<B>(c, p.geo[kQkv], io, tr, stage++);
       // no grid barrier here: an attention task needs the QKV rows of its own KV head
       // only, and waits for that group's row-tile count (qkv_ready)
@@ -1221,19 +1259,19 @@ __device__ void consumer_main(Ctx& c) {
       trace_mark(c, tr, stage, 0);
       if (!grid_wait(c)) return;
       trace_mark(c, tr, stage, 1);
-      io = GemvIo{p.attn, nullptr, 0, kEpiResidual, p.x, nullptr, 1};
+      io = GemvIo{p.attn, nullptr, 0, residual_kind, p.x, nullptr, 1, 0, ar_epoch0 + uint32_t(2 * l)};
       gemv_stage<B>(c, p.geo[kOProj], io, tr, stage++);
       grid_arrive(c);
       trace_mark(c, tr, stage, 0);
       if (!grid_wait(c)) return;
       trace_mark(c, tr, stage, 1);
-      io = GemvIo{p.x, lp.norm2, 0, kEpiSwiGLU, p.h, nullptr, 1};
+      io = GemvIo{p.x, lp.norm2, 0, kEpiSwiGLU, p.h, nullptr, 1, 0, 0u};
       gemv_stage<B>(c, p.geo[kGateUp], io, tr, stage++);
       grid_arrive(c);
       trace_mark(c, tr, stage, 0);
       if (!grid_wait(c)) return;
       trace_mark(c, tr, stage, 1);
-      io = GemvIo{p.h, nullptr, 0, kEpiResidual, p.x, nullptr, 1};
+      io = GemvIo{p.h, nullptr, 0, residual_kind, p.x, nullptr, 1, 1, ar_epoch0 + uint32_t(2 * l + 1)};
       gemv_stage<B>(c, p.geo[kDown], io, tr, stage++);
       grid_arrive(c);
       lp = upcoming;
@@ -1241,7 +1279,7 @@ __device__ void consumer_main(Ctx& c) {
     trace_mark(c, tr, stage, 0);
     if (!grid_wait(c)) return;
     trace_mark(c, tr, stage, 1);
-    GemvIo io{p.x, p.final_norm, 0, kEpiHead, p.logits, nullptr, 1};
+    GemvIo io{p.x, p.final_norm, 0, kEpiHead, p.logits, nullptr, 1, 0, 0u};
     gemv_stage<B>(c, p.geo[kHead], io, tr, stage);
     consumer_sync();
     if (c.tid < B) {
@@ -1274,6 +1312,42 @@ __device__ void consumer_main(Ctx& c) {
         const float ov = __shfl_xor_sync(0xffffffffu, bv, mk);
         const int oi = __shfl_xor_sync(0xffffffffu, bi, mk);
         if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+      }
+      if (p.tp_world > 1) {
+        // Each rank scored a slice of the vocabulary: CTA 0 sends its winner (the compared
+        // value is a bf16, the index fits 20 bits, so one packet holds both and a 28-bit
+        // epoch) into every peer's block; every CTA then takes the best over the ranks in
+        // ascending order, which is the whole-vocabulary argmax with ties to the smaller
+        // index (include/tilemega/Backend/Sm90DenseHead.cuh:139-201).
+        const unsigned long long epoch = (steps_before + 1ull) & 0xfffffffull;
+        if (blockIdx.x == 0 && c.lane < p.tp_world && c.lane != p.tp_rank) {
+          const unsigned long long packet =
+              (epoch << 36) | ((unsigned long long)bf16_bits(bv) << 20) | (unsigned long long)(bi & 0xfffff);
+          st_relaxed_sys(p.xchg[c.lane] + size_t(p.tp_rank) * kMaxBatch + b, packet);
+        }
+        float ov = bv;
+        int oi = bi;
+        if (c.lane < p.tp_world && c.lane != p.tp_rank) {
+          const unsigned long long* slot = p.xchg[p.tp_rank] + size_t(c.lane) * kMaxBatch + b;
+          unsigned long long seen, t0 = 0;
+          uint32_t polls = 0;
+          while (((seen = ld_relaxed_sys(slot)) >> 36) != epoch) {
+            if ((++polls & 63u) == 0 && wait_give_up(p, t0, kSitePeer, epoch, seen)) break;
+          }
+          ov = bf16_from_bits(uint16_t(seen >> 20));
+          oi = int(seen & 0xfffffull);
+        } else if (c.lane >= p.tp_world) {
+          ov = -INFINITY;
+          oi = 0x7fffffff;
+        }
+#pragma unroll
+        for (int mk = 4; mk; mk >>= 1) {   // tp_world <= 8: lanes 0..7 hold the ranks' candidates
+          const float pv = __shfl_xor_sync(0xffffffffu, ov, mk);
+          const int pi = __shfl_xor_sync(0xffffffffu, oi, mk);
+          if (pv > ov || (pv == ov && pi < oi)) { ov = pv; oi = pi; }
+        }
+        bv = __shfl_sync(0xffffffffu, ov, 0);
+        bi = __shfl_sync(0xffffffffu, oi, 0);
       }
       if (c.lane == 0) {
         const int pos = seq_pos(p, past, b);

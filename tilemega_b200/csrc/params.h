@@ -15,17 +15,20 @@ constexpr int kKvBlock = 16;                            // tokens per KV block
 constexpr int kMaxBatch = 8;                            // batch rows of the mma A operand (rows 0..7)
 constexpr int kPartialRing = 8;                         // GEMV tasks whose warp partials may be in flight (> ring slots + 1)
 constexpr int kAttnHalfBytes = kSlotBytes / 2;          // K part, then V part, of an attention slot
+constexpr int kMaxTp = 8;                               // tensor-parallel ranks of one plan
 
 enum StageKind : int { kQkv = 0, kOProj = 1, kGateUp = 2, kDown = 3, kHead = 4, kNumGemv = 5 };
-enum Epilogue : int { kEpiStore = 0, kEpiResidual = 1, kEpiSwiGLU = 2, kEpiHead = 3 };
+// kEpiResidualAllReduce: kEpiResidual after the ranks' bf16 partial sums are added in rank order.
+enum Epilogue : int { kEpiStore = 0, kEpiResidual = 1, kEpiSwiGLU = 2, kEpiHead = 3, kEpiResidualAllReduce = 4 };
 
 // Geometry of one GEMV stage. Weights are packed [N/8][K/tile_k][8*tile_k]
 // with the 8x64 128-byte XOR swizzle of the reference's tile_pages recipe
 // (python/tilemega/serving/weights.py:204-242), so one page is one contiguous
 // bulk copy.
 struct GemvGeo {
-  int n, k;            // output rows, reduction length
-  int tile_k;          // columns per page; multiple of 256*? (see kernel)
+  int n, k;            // output rows, reduction length (k: a multiple of tile_k; columns past k_src are zero)
+  int k_src;           // columns the activation rows really have (the packing recipe zero-pads the weights to k)
+  int tile_k;          // columns per page (2048)
   int pages_per_task;  // k / tile_k: a task is one 8-row tile over the whole reduction
   int ntasks;          // n / 8
 };
@@ -48,11 +51,14 @@ enum StatusWord : int {
 };
 // Diagnostic switches (plan sidecar "diag"): results are meaningless when any is set.
 enum DiagFlag : int { kDiagNoCopy = 1 };   // the streaming warp posts ring slots without copying into them
-enum WaitSite : int { kSiteGrid = 1, kSiteFull = 2, kSiteEmpty = 3, kSiteDrain = 4, kSiteTest = 5 };
+enum WaitSite : int { kSiteGrid = 1, kSiteFull = 2, kSiteEmpty = 3, kSiteDrain = 4, kSiteTest = 5, kSitePeer = 6 };
 
 struct MegaParams {
   // model
+  // (heads, kv_heads, inter are this rank's shares of a tensor-parallel plan; vocab is the
+  // whole vocabulary, of which this rank's head scores rows [head_base, head_base + geo[kHead].n))
   int batch, hidden, inter, heads, kv_heads, head_dim, layers, vocab;
+  int head_base;
   float eps;
   float qk_scale_log2;      // log2(e) / sqrt(head_dim)
   // request state
@@ -95,6 +101,13 @@ struct MegaParams {
   unsigned long long* step_ns; // [capacity+1] %globaltimer stamps
   unsigned long long* trace;   // [grid][5*layers+1][4] stage stamps of step trace_step, or null
   int trace_step;
+  // tensor parallelism (tp_world == 1: unused). ar[q] / xchg[q] are rank q's receive
+  // regions as mapped into this process; a rank stores into its peers' regions and
+  // polls its own. Every 8-byte packet carries its epoch, so no flag or fence is needed.
+  int tp_world, tp_rank;
+  unsigned long long tp_steps;        // decode steps run on this plan before this launch (equal on all ranks)
+  unsigned long long* ar[kMaxTp];     // [2 regions][tp_world sources][B][hidden/2] packets {epoch:32, bf16 pair:32}
+  unsigned long long* xchg[kMaxTp];   // [tp_world sources][kMaxBatch] packets {epoch:28, bf16 value:16, index:20}
 };
 
 // Per-step, per-sequence attention partition shared by the streaming warp and

@@ -18,7 +18,16 @@ std::string Sources(std::initializer_list<std::string> names) {
   return out + "]";
 }
 
-std::string Alias(const std::string& fqn) { return "{\"kind\":\"alias\",\"source\":" + Json::Quote(fqn) + "}"; }
+// "shard": the loader narrows every checkpoint tensor the recipe names to this rank's
+// contiguous part on `axis` before the transform (python/tilemega/serving/weights.py:78-96).
+std::string Shard(int axis, int parts) {
+  if (parts < 2) return "";
+  return ",\"shard\":{\"axis\":" + std::to_string(axis) + ",\"parts\":" + std::to_string(parts) + "}";
+}
+
+std::string Alias(const std::string& fqn, const std::string& shard = "") {
+  return "{\"kind\":\"alias\",\"source\":" + Json::Quote(fqn) + shard + "}";
+}
 
 // The reference's tile_pages recipe (python/tilemega/serving/weights.py:204-242):
 // [N/tile_n][K/tile_k][tile_n*tile_k] with the 8x64 128-byte XOR swizzle.
@@ -27,11 +36,16 @@ std::string Pages(const std::string& source, int tile_k) {
          ",\"source\":" + source + "}";
 }
 
+// A reduction length that is not a multiple of the page width is rounded up: the
+// tile_pages recipe zero-fills the weights' missing columns and the kernel zero-fills the
+// activation rows', so the extra columns add nothing (they do cost their bandwidth).
 GemvGeo MakeGeo(const char* what, int n, int k, const Json& overrides) {
   GemvGeo g{};
   g.n = n;
-  g.k = k;
+  g.k_src = k;
   g.tile_k = 2048;
+  if (k > 0 && k % 8 == 0) k = (k + g.tile_k - 1) / g.tile_k * g.tile_k;
+  g.k = k;
   if (overrides.has(what)) {
     g.tile_k = int(overrides.at(what).integer("tile_k", g.tile_k));
   }
@@ -46,12 +60,16 @@ GemvGeo MakeGeo(const char* what, int n, int k, const Json& overrides) {
 
 }  // namespace
 
-int PlanSpec::max_k() const { return std::max({hidden, inter, heads * head_dim}); }
+int PlanSpec::max_k() const {
+  int widest = 0;
+  for (int s = 0; s < kNumGemv; ++s) widest = std::max(widest, geo[s].k);
+  return widest;
+}
 
 uint64_t PlanSpec::weight_bytes() const {
   uint64_t total = 0;
   for (int s = 0; s < kNumGemv; ++s) {
-    const uint64_t one = 2ull * uint64_t(geo[s].n) * uint64_t(geo[s].k);
+    const uint64_t one = 2ull * uint64_t(geo[s].n) * uint64_t(geo[s].k_src);
     total += s == kHead ? one : one * uint64_t(layers);
   }
   return total;
@@ -75,6 +93,18 @@ PlanSpec PlanSpec::FromJson(const Json& plan) {
   if (s.head_dim != 64 && s.head_dim != 128) throw std::invalid_argument("head_dim must be 64 or 128");
   if (s.heads % s.kv_heads || s.heads / s.kv_heads != 4)
     throw std::invalid_argument("query heads per KV head must be 4");
+  // tensor parallelism: every split dimension must divide (export.py:182-192)
+  s.tp = int(plan.integer("tp", 1));
+  if (s.tp != 1 && s.tp != 2 && s.tp != 4 && s.tp != 8)
+    throw std::invalid_argument("tensor parallel degree must be 1, 2, 4 or 8");
+  if (s.heads % s.tp || s.kv_heads % s.tp || s.inter % s.tp || s.vocab % s.tp)
+    throw std::invalid_argument("heads, KV heads, intermediate size and vocabulary must divide by the tp degree");
+  s.heads /= s.tp;
+  s.kv_heads /= s.tp;
+  s.inter /= s.tp;
+  s.head_rows = s.vocab / s.tp;
+  if (s.tp > 1 && s.hidden % 2) throw std::invalid_argument("hidden size must be even for the all-reduce packets");
+  if (s.tp > 1 && s.vocab > (1 << 20)) throw std::invalid_argument("the argmax exchange packet holds 20 index bits");
   s.batch_lo = int(plan.integer("batch_lo", 1));
   s.batch_hi = int(plan.integer("batch_hi", s.batch_lo));
   s.capacity = int(plan.integer("capacity", 0));
@@ -102,7 +132,7 @@ PlanSpec PlanSpec::FromJson(const Json& plan) {
   s.geo[kOProj] = MakeGeo("o", s.hidden, s.heads * s.head_dim, geometry);
   s.geo[kGateUp] = MakeGeo("gate_up", 2 * s.inter, s.hidden, geometry);
   s.geo[kDown] = MakeGeo("down", s.hidden, s.inter, geometry);
-  s.geo[kHead] = MakeGeo("lm_head", s.vocab, s.hidden, geometry);
+  s.geo[kHead] = MakeGeo("lm_head", s.head_rows, s.hidden, geometry);
 
   auto add = [&](std::string name, uint32_t role, uint32_t dtype, uint64_t constant, uint64_t per_batch,
                  std::string recipe) {
@@ -129,7 +159,7 @@ PlanSpec PlanSpec::FromJson(const Json& plan) {
   s.qkv_buf = add("serving.qkv", 0, 0, 0, uint64_t(s.qkv_rows()), "");
   s.attn_buf = add("serving.attention", 0, 0, 0, uint64_t(s.heads) * D, "");
   s.mlp_buf = add("serving.mlp", 0, 0, 0, I, "");
-  s.logits_buf = add("serving.logits", 0, 1, 0, V, "");  // fp32 accumulators of the head
+  s.logits_buf = add("serving.logits", 0, 1, 0, uint64_t(s.head_rows), "");  // fp32 accumulators of this rank's head rows
   for (int l = 0; l < s.layers; ++l) {
     const std::string p = "l" + std::to_string(l) + ".";
     const std::string m = "model.layers." + std::to_string(l) + ".";
@@ -139,7 +169,7 @@ PlanSpec PlanSpec::FromJson(const Json& plan) {
         "{\"kind\":\"qkv_group_interleave\",\"sources\":" +
         Sources({m + "self_attn.q_proj.weight", m + "self_attn.k_proj.weight", m + "self_attn.v_proj.weight"}) +
         ",\"hkv\":" + std::to_string(s.kv_heads) + ",\"qperkv\":" + std::to_string(s.heads / s.kv_heads) +
-        ",\"head_dim\":" + std::to_string(s.head_dim) + "}";
+        ",\"head_dim\":" + std::to_string(s.head_dim) + Shard(0, s.tp) + "}";
     lb.qkv = add(p + "qkv.weight", 1, 0, uint64_t(s.geo[kQkv].n) * s.geo[kQkv].k, 0,
                  Pages(qkv_source, s.geo[kQkv].tile_k));
     if (s.paged) {
@@ -152,20 +182,20 @@ PlanSpec PlanSpec::FromJson(const Json& plan) {
       lb.v = add("kv_cache.v." + std::to_string(l), 1, 0, 0, cache, "");
     }
     lb.o = add(p + "o.weight", 1, 0, uint64_t(s.geo[kOProj].n) * s.geo[kOProj].k, 0,
-               Pages(Alias(m + "self_attn.o_proj.weight"), s.geo[kOProj].tile_k));
+               Pages(Alias(m + "self_attn.o_proj.weight", Shard(1, s.tp)), s.geo[kOProj].tile_k));
     lb.norm2 = add(p + "norm2.weight", 1, 0, H, 0, Alias(m + "post_attention_layernorm.weight"));
     const std::string gate_up_source = "{\"kind\":\"gate_up_interleave\",\"sources\":" +
                                        Sources({m + "mlp.gate_proj.weight", m + "mlp.up_proj.weight"}) +
-                                       ",\"u\":4}";
+                                       ",\"u\":4" + Shard(0, s.tp) + "}";
     lb.gate_up = add(p + "gate_up.weight", 1, 0, uint64_t(s.geo[kGateUp].n) * s.geo[kGateUp].k, 0,
                      Pages(gate_up_source, s.geo[kGateUp].tile_k));
     lb.down = add(p + "down.weight", 1, 0, uint64_t(s.geo[kDown].n) * s.geo[kDown].k, 0,
-                  Pages(Alias(m + "mlp.down_proj.weight"), s.geo[kDown].tile_k));
+                  Pages(Alias(m + "mlp.down_proj.weight", Shard(1, s.tp)), s.geo[kDown].tile_k));
     s.layer.push_back(lb);
   }
   s.final_norm = add("model.norm.weight", 1, 0, H, 0, Alias("model.norm.weight"));
   s.lm_head = add("lm_head.weight", 1, 0, uint64_t(s.geo[kHead].n) * s.geo[kHead].k, 0,
-                  Pages(Alias("lm_head.weight"), s.geo[kHead].tile_k));
+                  Pages(Alias("lm_head.weight", Shard(0, s.tp)), s.geo[kHead].tile_k));
   return s;
 }
 

@@ -29,7 +29,10 @@ struct LayerBuffers {
 
 struct PlanSpec {
   // model
+  // (heads, kv_heads, inter and head_rows are ONE RANK's shares when tp > 1: Megatron
+  // sharding as in python/tilemega/serving/export.py:39-47,107-112,152-163)
   int hidden = 0, inter = 0, heads = 0, kv_heads = 0, head_dim = 0, layers = 0, vocab = 0;
+  int tp = 1, head_rows = 0;
   double eps = 1e-5;
   bool tied = false;
   // request geometry

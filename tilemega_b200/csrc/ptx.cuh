@@ -121,6 +121,19 @@ __device__ __forceinline__ unsigned long long ld_relaxed(const unsigned long lon
   return v;
 }
 
+// System-scope strong accesses for packets that cross NVLink: a packet is one 8-byte
+// word holding data and epoch together, so a reader that sees the epoch has the data
+// (include/tilemega/Backend/Sm90DenseEpilogue.h:31-35 uses the same packet idea).
+__device__ __forceinline__ void st_relaxed_sys(unsigned long long* addr, unsigned long long v) {
+  asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(addr), "l"(v) : "memory");
+}
+
+__device__ __forceinline__ unsigned long long ld_relaxed_sys(const unsigned long long* addr) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.sys.global.b64 %0, [%1];" : "=l"(v) : "l"(addr) : "memory");
+  return v;
+}
+
 __device__ __forceinline__ unsigned long long global_timer() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));

@@ -105,6 +105,8 @@ struct Plan {
   unsigned long long* trace_dev = nullptr;
   size_t trace_bytes = 0;
   int trace_step = -1;
+  bool tp_bound = false;                // tensor-parallel plan: tm_plan_bind_tp has been called
+  uint64_t tp_steps = 0;                // decode steps launched so far (the all-reduce epochs count from it)
   unsigned char* sync_block = nullptr;  // barrier + counters, rezeroed by every launch
   size_t sync_bytes = 0;
   size_t claim_offset = 0;
@@ -233,6 +235,9 @@ void* tm_plan_create(int batch, void* const* external, int device) {
   p.head_dim = s.head_dim;
   p.layers = s.layers;
   p.vocab = s.vocab;
+  p.head_base = 0;   // set by tm_plan_bind_tp for a tensor-parallel plan
+  p.tp_world = s.tp;
+  p.tp_rank = 0;
   p.eps = float(s.eps);
   p.qk_scale_log2 = float(1.4426950408889634 / std::sqrt(double(s.head_dim)));
   p.capacity = s.capacity;
@@ -252,7 +257,7 @@ void* tm_plan_create(int batch, void* const* external, int device) {
   // rows of the widest GEMV input; one extra hidden-wide row holds the RMSNorm weights
   // (rows are padded by 8 elements so that the batch rows of a k-chunk sit on distinct banks)
   // a normalised stage also parks its raw rows and the norm weights there: 2*batch + 1 hidden-wide rows
-  int xs = std::max({batch * (s.max_k() + 8) * 2, (2 * batch + 1) * (s.hidden + 8) * 2, attention_scratch});
+  int xs = std::max({batch * (s.max_k() + 8) * 2, (2 * batch + 1) * (s.geo[tmb::kQkv].k + 8) * 2, attention_scratch});
   xs = (xs + 127) & ~127;
   p.xs_bytes = xs;
   p.static_quarters = s.static_quarters;
@@ -407,7 +412,10 @@ int tm_plan_launch_steps(void* handle, uint32_t first_step, uint32_t steps, uint
   const size_t used = plan->claim_offset + (size_t(steps) * (5 * size_t(plan->params.layers) + 1) + 2) * sizeof(unsigned);
   cudaError_t err = cudaMemsetAsync(plan->sync_block, 0, used, s);
   if (err != cudaSuccess) return Fail(int(err), std::string("tm_plan_launch_steps: ") + cudaGetErrorString(err));
+  if (plan->params.tp_world > 1 && !plan->tp_bound)
+    return Fail(-1, "tm_plan_launch_steps: a tensor-parallel plan must be bound with tm_plan_bind_tp first");
   tmb::MegaParams p = plan->params;
+  p.tp_steps = plan->tp_steps;
   p.first_step = int(first_step);
   p.nsteps = int(steps);
   p.prompt_len = plan->prompt_len;
@@ -417,6 +425,7 @@ int tm_plan_launch_steps(void* handle, uint32_t first_step, uint32_t steps, uint
   if (status != 0)
     return Fail(status, std::string("tm_plan_launch_steps: ") + cudaGetErrorString(cudaError_t(status)));
   plan->next_iteration[mode] += steps;
+  plan->tp_steps += steps;
   return 0;
 }
 
@@ -522,10 +531,84 @@ uint64_t tm_plan_step_bytes(void* handle, uint64_t cached_tokens_total) {
   return s.weight_bytes() + s.kv_bytes_per_token() * cached_tokens_total;
 }
 
-unsigned tm_plan_tp_world(void) { return 1; }
-unsigned long long tm_plan_tp_bytes(unsigned) { return 0; }
-int tm_plan_bind_tp(void*, int, void* const*, void* const*) {
-  return Fail(-1, "tm_plan_bind_tp: this plan is not tensor parallel");
+// Tensor parallelism (include/tilemega/Codegen/tasks/ServingAbi.h:53-55). The caller
+// allocates, zeroes and owns one all-reduce region (which = 0) and one argmax exchange
+// block (which = 1) per rank, on that rank's device, and hands every rank the list of all
+// of them as pointers valid in the calling process.
+unsigned tm_plan_tp_world(void) {
+  const Library& lib = Lib();
+  return lib.ok ? unsigned(lib.spec.tp) : 1u;
+}
+
+unsigned long long tm_plan_tp_bytes(unsigned which) {
+  const Library& lib = Lib();
+  if (!lib.ok || lib.spec.tp < 2) return 0;
+  const tmb::PlanSpec& s = lib.spec;
+  if (which == 0) return 2ull * s.tp * s.batch_hi * (uint64_t(s.hidden) / 2) * 8ull;   // two regions of 8-byte packets
+  if (which == 1) return uint64_t(s.tp) * tmb::kMaxBatch * 8ull;
+  return 0;
+}
+
+int tm_plan_bind_tp(void* handle, int rank, void* const* ar, void* const* x) {
+  Plan* plan = AsPlan(handle);
+  if (!plan || !ar || !x) return Fail(-1, "tm_plan_bind_tp: bad argument");
+  tmb::MegaParams& p = plan->params;
+  if (p.tp_world < 2) return Fail(-1, "tm_plan_bind_tp: this plan is not tensor parallel");
+  if (rank < 0 || rank >= p.tp_world) return Fail(-1, "tm_plan_bind_tp: rank outside the plan's degree");
+  if (plan->tp_steps != 0) return Fail(-2, "tm_plan_bind_tp: the plan has already run");
+  for (int q = 0; q < p.tp_world; ++q) {
+    if (!ar[q] || !x[q] || (reinterpret_cast<uintptr_t>(ar[q]) & 7u) || (reinterpret_cast<uintptr_t>(x[q]) & 7u))
+      return Fail(-1, "tm_plan_bind_tp: every rank needs an 8-byte aligned region and exchange block");
+    p.ar[q] = static_cast<unsigned long long*>(ar[q]);
+    p.xchg[q] = static_cast<unsigned long long*>(x[q]);
+  }
+  p.tp_rank = rank;
+  p.head_base = rank * p.geo[tmb::kHead].n;
+  plan->tp_bound = true;
+  return 0;
+}
+
+// One process per GPU: a rank makes its regions visible to its peers through CUDA IPC.
+// Additions without a reference counterpart (its driver runs every rank in one process,
+// python/tilemega/serving/tp_engine.py:47-112).
+int tm_ipc_alloc(int device, uint64_t bytes, void** device_pointer) {
+  if (!device_pointer || bytes == 0) return Fail(-1, "tm_ipc_alloc: bad argument");
+  DeviceScope scope(device);
+  // its own cudaMalloc: an IPC handle names a whole allocation, so the region must not be
+  // a slice of some pool
+  cudaError_t err = cudaMalloc(device_pointer, size_t(bytes));
+  if (err == cudaSuccess) err = cudaMemset(*device_pointer, 0, size_t(bytes));
+  if (err == cudaSuccess) err = cudaDeviceSynchronize();
+  return err == cudaSuccess ? 0 : Fail(int(err), std::string("tm_ipc_alloc: ") + cudaGetErrorString(err));
+}
+
+int tm_ipc_free(void* device_pointer) {
+  cudaError_t err = cudaFree(device_pointer);
+  return err == cudaSuccess ? 0 : Fail(int(err), std::string("tm_ipc_free: ") + cudaGetErrorString(err));
+}
+
+int tm_ipc_export(void* device_pointer, unsigned char* handle64) {
+  if (!device_pointer || !handle64) return Fail(-1, "tm_ipc_export: bad argument");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+  cudaIpcMemHandle_t handle;
+  cudaError_t err = cudaIpcGetMemHandle(&handle, device_pointer);
+  if (err != cudaSuccess) return Fail(int(err), std::string("tm_ipc_export: ") + cudaGetErrorString(err));
+  std::memcpy(handle64, &handle, 64);
+  return 0;
+}
+
+int tm_ipc_open(const unsigned char* handle64, void** device_pointer) {
+  if (!handle64 || !device_pointer) return Fail(-1, "tm_ipc_open: bad argument");
+  cudaIpcMemHandle_t handle;
+  std::memcpy(&handle, handle64, 64);
+  cudaError_t err = cudaIpcOpenMemHandle(device_pointer, handle, cudaIpcMemLazyEnablePeerAccess);
+  if (err != cudaSuccess) return Fail(int(err), std::string("tm_ipc_open: ") + cudaGetErrorString(err));
+  return 0;
+}
+
+int tm_ipc_close(void* device_pointer) {
+  cudaError_t err = cudaIpcCloseMemHandle(device_pointer);
+  return err == cudaSuccess ? 0 : Fail(int(err), std::string("tm_ipc_close: ") + cudaGetErrorString(err));
 }
 
 void tm_plan_destroy(void* handle) {

@@ -24,7 +24,7 @@ MODEL_KEYS = ("hidden_size", "intermediate_size", "num_attention_heads", "num_ke
 def plan_document(config: dict, *, batch_lo: int = 1, batch_hi: int | None = None, capacity: int,
                   kv_layout: str = "contiguous", num_blocks: int = 0, geometry: dict | None = None,
                   grid: int = 0, slots: int = 0, write_logits: bool = True,
-                  static_quarters: int | None = None, diag: int = 0) -> dict:
+                  static_quarters: int | None = None, diag: int = 0, tp: int = 1) -> dict:
     """The sidecar for one decode plan; raises ValueError on shapes the kernels do not cover."""
     model = {key: config[key] for key in MODEL_KEYS if key in config}
     model.setdefault("head_dim", config["hidden_size"] // config["num_attention_heads"])
@@ -38,12 +38,19 @@ def plan_document(config: dict, *, batch_lo: int = 1, batch_hi: int | None = Non
         raise ValueError("kv_layout must be 'contiguous' or 'paged'")
     if kv_layout == "paged" and num_blocks < batch_hi * (capacity // 16):
         raise ValueError("a paged plan needs num_blocks >= batch_hi * capacity / 16")
+    if tp not in (1, 2, 4, 8):
+        raise ValueError("tensor parallel degree must be 1, 2, 4 or 8")
+    for key in ("num_attention_heads", "num_key_value_heads", "intermediate_size", "vocab_size"):
+        if config[key] % tp:
+            raise ValueError(f"{key}={config[key]} is not divisible by the tp degree {tp}")
     document = {
         "execution": "megakernel", "pg": "ring", "arch": "sm_100a", "phase": "decode",
         "model": model, "batch_lo": batch_lo, "batch_hi": batch_hi, "capacity": capacity,
         "kv": {"layout": kv_layout, "block": 16, "num_blocks": num_blocks},
         "geometry": geometry or {}, "grid": grid, "slots": slots, "write_logits": write_logits,
     }
+    if tp > 1:
+        document["tp"] = tp   # the plan is ONE rank's: every rank loads the same library
     if static_quarters is not None:
         document["static_quarters"] = static_quarters
     if diag:

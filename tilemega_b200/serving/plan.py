@@ -66,6 +66,11 @@ _OPTIONAL = (
     ("tm_plan_trace_step", C.c_int, [C.c_void_p, C.c_int]),
     ("tm_plan_read_trace", C.c_longlong, [C.c_void_p, C.POINTER(C.c_uint64), C.c_uint64]),
     ("tm_watchdog_probe_static", C.c_int, [C.c_int, C.c_int, C.c_int, C.c_uint32, C.c_void_p, C.c_void_p]),
+    ("tm_ipc_alloc", C.c_int, [C.c_int, C.c_uint64, C.POINTER(C.c_void_p)]),
+    ("tm_ipc_free", C.c_int, [C.c_void_p]),
+    ("tm_ipc_export", C.c_int, [C.c_void_p, C.c_char_p]),
+    ("tm_ipc_open", C.c_int, [C.c_char_p, C.POINTER(C.c_void_p)]),
+    ("tm_ipc_close", C.c_int, [C.c_void_p]),
 )
 STATIC_PROBE_MAX_WAITERS = 32
 
@@ -137,6 +142,35 @@ class PlanLibrary:
             raise ValueError("an unsharded plan has no tensor parallel buffers")
         return int(self.lib.tm_plan_tp_bytes(which))
 
+    def ipc_alloc(self, device: int, nbytes: int) -> int:
+        """A zeroed device region that is one allocation of its own (what an IPC handle names)."""
+        pointer = C.c_void_p()
+        if self.lib.tm_ipc_alloc(device, nbytes, C.byref(pointer)) != 0:
+            raise RuntimeError(f"tm_ipc_alloc failed: {self.last_error()}")
+        return int(pointer.value)
+
+    def ipc_free(self, device_pointer: int) -> None:
+        if self.lib.tm_ipc_free(device_pointer) != 0:
+            raise RuntimeError(f"tm_ipc_free failed: {self.last_error()}")
+
+    def ipc_export(self, device_pointer: int) -> bytes:
+        """64-byte CUDA IPC handle of a device allocation (its base address)."""
+        handle = C.create_string_buffer(64)
+        if self.lib.tm_ipc_export(device_pointer, handle) != 0:
+            raise RuntimeError(f"tm_ipc_export failed: {self.last_error()}")
+        return handle.raw
+
+    def ipc_open(self, handle: bytes) -> int:
+        """Map a peer process's allocation; returns the pointer valid in this process."""
+        pointer = C.c_void_p()
+        if self.lib.tm_ipc_open(C.create_string_buffer(handle, 64), C.byref(pointer)) != 0:
+            raise RuntimeError(f"tm_ipc_open failed: {self.last_error()}")
+        return int(pointer.value)
+
+    def ipc_close(self, device_pointer: int) -> None:
+        if self.lib.tm_ipc_close(device_pointer) != 0:
+            raise RuntimeError(f"tm_ipc_close failed: {self.last_error()}")
+
     def create(self, batch: int, pointers: dict[str, int], device: int) -> "Plan":
         if not self.info.batch_lo <= batch <= self.info.batch_hi:
             raise ValueError("batch outside the solved interval")
@@ -190,6 +224,18 @@ class Plan:
         if status != 0:
             raise RuntimeError(f"tm_plan_launch failed ({status}): {self.library.last_error()}")
         self.iteration[mode] += 1
+
+    def bind_tp(self, rank: int, ar: list[int], exchange: list[int]) -> None:
+        """Give this rank's plan every rank's all-reduce region and exchange block
+        (python/tilemega/serving/plan.py:207-218 of the reference)."""
+        world = self.library.tp_world
+        if len(ar) != world or len(exchange) != world:
+            raise ValueError("bind_tp needs one region and one exchange block per rank")
+        regions = (C.c_void_p * world)(*ar)
+        blocks = (C.c_void_p * world)(*exchange)
+        status = self.library.lib.tm_plan_bind_tp(self.handle, rank, regions, blocks)
+        if status != 0:
+            raise RuntimeError(f"tm_plan_bind_tp failed ({status}): {self.library.last_error()}")
 
     def loop_modes(self) -> int:
         query = getattr(self.library.lib, "tm_plan_loop_modes", None)

@@ -84,7 +84,9 @@ def shuffled_block_table(batch: int, max_blocks: int, num_blocks: int, seed: int
 
 def allocate_state(config: dict, batch: int, decode: PlanLibrary, device: str | torch.device = "cuda",
                    block_table: torch.Tensor | None = None,
-                   context_base: torch.Tensor | None = None) -> ServingState:
+                   context_base: torch.Tensor | None = None, tp: int = 1) -> ServingState:
+    """`tp`: a tensor-parallel rank's state holds only its num_key_value_heads / tp KV heads
+    (reference state.py:64-82); token state and RoPE tables are whole on every rank."""
     if decode.info.phase != 1:
         raise ValueError("allocate_state needs a decode plan")
     if not decode.info.batch_lo <= batch <= decode.info.batch_hi:
@@ -93,6 +95,9 @@ def allocate_state(config: dict, batch: int, decode: PlanLibrary, device: str | 
     capacity = decode.info.capacity
     layers = int(config["num_hidden_layers"])
     hkv = int(config["num_key_value_heads"])
+    if tp < 1 or hkv % tp:
+        raise ValueError(f"{hkv} KV heads do not split across tensor parallel degree {tp}")
+    hkv //= tp
     dim = head_dim_of(config)
     names = {buffer.name for buffer in decode.buffers}
     tokens = torch.zeros((batch, capacity), dtype=torch.int32, device=device)

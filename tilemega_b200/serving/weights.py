@@ -88,6 +88,28 @@ def tile_pages(weight: torch.Tensor, tile_n: int, tile_k: int) -> torch.Tensor:
     return swizzled.reshape(-1).contiguous()
 
 
+def sharded(recipe: Mapping[str, object], source: Callable[[str], torch.Tensor],
+            tp_rank: int) -> Callable[[str], torch.Tensor]:
+    """Megatron tensor parallelism (reference weights.py:78-96): a recipe with
+    "shard": {"axis", "parts"} names whole checkpoint tensors, and a rank packs only
+    its contiguous part of each of them: rows (axis 0) for q/k/v, gate/up and
+    lm_head, columns (axis 1) for o and down."""
+    spec = recipe.get("shard")
+    if spec is None:
+        return source
+    axis, parts = int(spec["axis"]), int(spec["parts"])
+    if axis not in (0, 1) or parts < 2 or not 0 <= tp_rank < parts:
+        raise ValueError(f"invalid shard {spec} for tensor parallel rank {tp_rank}")
+
+    def narrowed(name: str) -> torch.Tensor:
+        tensor = source(name)
+        if tensor.ndim != 2 or tensor.shape[axis] % parts:
+            raise ValueError(f"{name} {tuple(tensor.shape)} does not split into {parts} on axis {axis}")
+        size = tensor.shape[axis] // parts
+        return tensor.narrow(axis, tp_rank * size, size).contiguous()
+    return narrowed
+
+
 def _sources(recipe: Mapping[str, object], source: Callable[[str], torch.Tensor]) -> list[torch.Tensor]:
     tensors = [source(str(name)) for name in recipe["sources"]]
     if not all(item.ndim == 2 for item in tensors) or len({item.shape[1] for item in tensors}) != 1:
@@ -95,12 +117,13 @@ def _sources(recipe: Mapping[str, object], source: Callable[[str], torch.Tensor]
     return tensors
 
 
-def pack(recipe: Mapping[str, object], source: Callable[[str], torch.Tensor]) -> torch.Tensor:
+def pack(recipe: Mapping[str, object], source: Callable[[str], torch.Tensor], tp_rank: int = 0) -> torch.Tensor:
     kind = recipe["kind"]
+    source = sharded(recipe, source, tp_rank)
     if kind == "alias":
         return source(str(recipe["source"]))
     if kind == "tile_pages":
-        return tile_pages(pack(recipe["source"], source), int(recipe["tile_n"]), int(recipe["tile_k"]))
+        return tile_pages(pack(recipe["source"], source, tp_rank), int(recipe["tile_n"]), int(recipe["tile_k"]))
     if kind == "qkv_group_interleave":
         # rows per KV head: its query heads, then its key head, then its value head
         # (reference weights.py:246-256)
@@ -137,8 +160,12 @@ def weight_recipes(*plans: PlanLibrary) -> dict[str, Buffer]:
 
 
 def load_weights(checkpoint: str | Path | Checkpoint | TensorCheckpoint, *plans: PlanLibrary,
-                 device: str | torch.device = "cuda") -> dict[str, torch.Tensor]:
-    """Pack every recipe buffer of the plans on `device` (bf16 unless the table says otherwise)."""
+                 device: str | torch.device = "cuda", tp: tuple[int, int] = (0, 1)) -> dict[str, torch.Tensor]:
+    """Pack every recipe buffer of the plans on `device` (bf16 unless the table says otherwise).
+    `tp` = (rank, world): this rank's slices of a tensor-parallel plan's weights."""
+    tp_rank, tp_world = tp
+    if any(plan.tp_world != tp_world for plan in plans):
+        raise ValueError("the plans' tensor parallel degree differs from the requested one")
     if isinstance(checkpoint, (str, Path)):
         checkpoint = Checkpoint(checkpoint)
     device = torch.device(device)
@@ -155,7 +182,7 @@ def load_weights(checkpoint: str | Path | Checkpoint | TensorCheckpoint, *plans:
                     staged[fqn] = checkpoint.tensor(fqn).to(device=device, dtype=dtype).contiguous()
                 return staged[fqn]
 
-            packed[buffer.pack_json] = pack(recipe, source).contiguous()
+            packed[buffer.pack_json] = pack(recipe, source, tp_rank).contiguous()
         tensor = packed[buffer.pack_json]
         if tensor.numel() != buffer.elements_constant:
             raise ValueError(f"{name} has {tensor.numel()} elements; plan expects {buffer.elements_constant}")
