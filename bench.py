@@ -12,9 +12,16 @@ step per call through the C ABI with the token id coming from pinned host memory
 and the new token read back to the host every step.
 
 Synthetic data: seeded N(0, 0.02) weights, KV rows N(0, 0.5), a seeded context
-length in [512, 8192]. Rank r > 0 of a multi-GPU run is an independent replica
-(decode of one sequence does not shard without tensor parallelism, which this
-build does not have yet); the job value is the sum over replicas.
+length in [512, 8192]. Rank r > 0 of a multi-GPU run is an independent replica of
+the headline workload (the 8B-shaped model at batch 1 is not tensor parallel in the
+benchmark list); the job value is the sum over replicas.
+
+    python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N --tp --model llama-3.1-70b
+
+shards ONE model over the N ranks instead (tensor parallelism: column/row-sharded
+weights, the all-reduce after o and down fused into the kernel's epilogues over
+peer memory); the job value is then the one model's tokens/s ("strong" scaling) and
+the roofline is each GPU's share of the bytes.
 """
 from __future__ import annotations
 
@@ -52,7 +59,8 @@ def measured_peak_gbs() -> tuple[float, str]:
     return 6650.0, "fallback"
 
 
-MODELS = {"llama-3.1-8b": synthetic.LLAMA_3_1_8B, "llama-3.2-1b": synthetic.LLAMA_3_2_1B}
+MODELS = {"llama-3.1-8b": synthetic.LLAMA_3_1_8B, "llama-3.2-1b": synthetic.LLAMA_3_2_1B,
+          "llama-3.1-70b": synthetic.LLAMA_3_1_70B}
 
 
 def workload(args) -> dict:
@@ -205,6 +213,9 @@ def run_ours(args) -> None:
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=device)
+    tp = world if args.tp else 1
+    if args.tp and world < 2:
+        raise SystemExit("--tp shards one model over the ranks: launch at least two")
 
     work = workload(args)
     config, batch, contexts = work["config"], work["batch"], work["contexts"]
@@ -215,34 +226,46 @@ def run_ours(args) -> None:
     num_blocks = batch * max_blocks + 32
     plan_dir = ROOT / "gpurun_out" / "plans" if (ROOT / "gpurun_out").exists() else Path("/tmp/tilemega_b200_plans")
     geometry = json.loads(args.geometry) if args.geometry else None
+    options = dict(batch_lo=batch, batch_hi=batch, capacity=capacity, kv_layout="paged", num_blocks=num_blocks,
+                   write_logits=False, geometry=geometry, slots=args.slots, tp=tp)
     if rank == 0 or world == 1:
-        so = emit_plan(config, plan_dir, batch_lo=batch, batch_hi=batch, capacity=capacity, kv_layout="paged",
-                       num_blocks=num_blocks, write_logits=False, geometry=geometry, slots=args.slots)
+        so = emit_plan(config, plan_dir, **options)
     if world > 1:
         import torch.distributed as dist
         dist.barrier()
-        so = emit_plan(config, plan_dir, batch_lo=batch, batch_hi=batch, capacity=capacity, kv_layout="paged",
-                       num_blocks=num_blocks, write_logits=False, geometry=geometry, slots=args.slots)
+        so = emit_plan(config, plan_dir, **options)
     lib = PlanLibrary(so)
-    raw = synthetic.seeded_weights(config, seed=rank, dtype=torch.bfloat16, device=device)
-    weights = load_weights(TensorCheckpoint(raw, config["tie_word_embeddings"]), lib, device=device)
-    keep = {tensor.data_ptr() for tensor in weights.values()}
-    raw = {name: tensor for name, tensor in raw.items() if tensor.data_ptr() in keep}
+    replica = 0 if tp > 1 else rank     # tensor-parallel ranks cut their slices out of ONE model and share one request
+    if tp > 1:
+        weights = load_weights(synthetic.LazySeededCheckpoint(config, seed=0, device=device), lib, device=device,
+                               tp=(rank, world))
+    else:
+        raw = synthetic.seeded_weights(config, seed=rank, dtype=torch.bfloat16, device=device)
+        weights = load_weights(TensorCheckpoint(raw, config["tie_word_embeddings"]), lib, device=device)
+        keep = {tensor.data_ptr() for tensor in weights.values()}
+        raw = {name: tensor for name, tensor in raw.items() if tensor.data_ptr() in keep}
     torch.cuda.empty_cache()
-    table = shuffled_block_table(batch, max_blocks, num_blocks, seed=7 + rank)
+    table = shuffled_block_table(batch, max_blocks, num_blocks, seed=7 + replica)
     base = torch.tensor(contexts, dtype=torch.int32)
-    state = allocate_state(config, batch, lib, device, block_table=table, context_base=base)
+    state = allocate_state(config, batch, lib, device, block_table=table, context_base=base, tp=tp)
     state.kv_storage.normal_(0.0, 0.5)
-    first = synthetic.seeded_tokens(batch, 1, config["vocab_size"], seed=11 + rank)
+    first = synthetic.seeded_tokens(batch, 1, config["vocab_size"], seed=11 + replica)
     for b in range(batch):
         state.tokens[b, contexts[b]] = int(first[b, 0])
     pointers = {name: tensor.data_ptr() for name, tensor in weights.items()}
     pointers.update(state.pointers)
     plan = lib.create(batch, pointers, local)
+    if tp > 1:
+        # each rank's receive regions, published to its peers as CUDA IPC handles
+        from tilemega_b200.serving.tp_engine import exchange_handles
+        regions = [lib.ipc_alloc(local, lib.tp_bytes(which)) for which in (0, 1)]
+        plan.bind_tp(rank, exchange_handles(lib, regions[0]), exchange_handles(lib, regions[1]))
+        torch.cuda.synchronize()
+        dist.barrier()
     plan.set_prompt_len(0)
     plan.set_steps(list(range(total_steps)))   # step s decodes position context_base[b] + s
     stream = torch.cuda.current_stream()
-    mode = 2
+    mode = 1 if tp > 1 else 2
 
     def barrier():
         if world > 1:
@@ -289,25 +312,30 @@ def run_ours(args) -> None:
         raise SystemExit(f"a bounded device wait gave up during the end-to-end loop: {fired}")
     device_ms, e2e_seconds = max_over_ranks([device_ms, e2e_seconds], device)
     seconds = device_ms / 1e3
-    value = job_value(world, batch, steps, seconds)
+    replicas = 1 if tp > 1 else world
+    value = job_value(replicas, batch, steps, seconds)
     achieved = bytes_timed / seconds / 1e9
     peak, peak_kind = measured_peak_gbs()
     step_us = [(stamps[i + 1] - stamps[i]) / 1e3 for i in range(steps)]
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
-        "ms_per_step": device_ms / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "ms_per_step": device_ms / steps, "higher_is_better": True, "scaling": "strong" if tp > 1 else "weak",
+        "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"{work['name']} decode, batch {batch}, context {contexts}, paged KV block 16, "
                                "shuffled block table", "layers": config["num_hidden_layers"],
                    "l2": "inputs larger than L2: every step streams its weights and KV rows from HBM",
-                   "parallelism": "replicas" if world > 1 else "single",
+                   "parallelism": f"tp{tp}" if tp > 1 else ("replicas" if world > 1 else "single"),
                    "step_latency_us_median": statistics.median(step_us),
                    "mbu_vs_nominal_8tbs": achieved / NOMINAL_HBM_GBS},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": NCU_TRAFFIC_PER_ALGORITHMIC_BYTE * bytes_timed,
-                     "traffic_source": "ncu on a 2-layer case of the same kernel, scaled by algorithmic bytes",
+                     "traffic": None if tp > 1 else NCU_TRAFFIC_PER_ALGORITHMIC_BYTE * bytes_timed,
+                     "traffic_source": ("not captured for the tensor-parallel run (ncu never wraps a multi-rank command)"
+                                        if tp > 1 else
+                                        "ncu on a 2-layer case of the same kernel, scaled by algorithmic bytes"),
+                     "per": "GPU (this rank's share of the weights and KV rows)" if tp > 1 else "GPU",
                      "peak_kind": f"of {peak_kind}", "bytes_per_launch": bytes_timed},
-        "e2e": {"value": job_value(world, batch, steps, e2e_seconds), "unit": UNIT, "h2d_bytes_per_step": 4 * batch,
+        "e2e": {"value": job_value(replicas, batch, steps, e2e_seconds), "unit": UNIT, "h2d_bytes_per_step": 4 * batch,
                 "d2h_bytes_per_step": 4 * batch},
         "gpu_launches": 1,
         "clocks": sampler.summary(),
@@ -339,6 +367,8 @@ def main() -> None:
     parser.add_argument("--geometry", default="", help="JSON overrides of the GEMV page geometry")
     parser.add_argument("--slots", type=int, default=0)
     parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    parser.add_argument("--tp", action="store_true",
+                        help="shard one model over the ranks (tensor parallelism) instead of running replicas")
     args = parser.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -225,3 +225,15 @@ def test_reduction_padded_to_whole_pages(plan_dir):
     tokens, logits = run.greedy(prompt, new_tokens)
     assert_as_accurate_as_reference_bf16(config, weights, prompt, tokens, logits, capacity, "padded reduction")
     run.close()
+
+
+def test_eight_query_heads_per_kv_head(plan_dir):
+    """The 70B-shaped grouping: 8 query heads share a KV head (all 8 rows of the attention A operand)."""
+    config = synthetic.TINY_GQ8
+    batch, prompt_len, new_tokens, capacity = 3, 23, 5, 48
+    weights = bf16_weights(config)
+    prompt = synthetic.seeded_tokens(batch, prompt_len, config["vocab_size"], seed=8)
+    run = GpuRun(config, weights, batch, capacity, plan_dir)
+    tokens, logits = run.greedy(prompt, new_tokens)
+    assert_as_accurate_as_reference_bf16(config, weights, prompt, tokens, logits, capacity, "8 query heads per KV head")
+    run.close()

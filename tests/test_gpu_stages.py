@@ -33,7 +33,7 @@ def agreement(got, ref, what, ulps=1.0, exact_fraction=0.99, floor=1e-6):
 
 
 @pytest.mark.parametrize("base,batch,history", [("TINY", 2, 37), ("TINY_D128", 3, 70), ("TINY", 1, 129),
-                                                ("TINY", 8, 21), ("TINY_D128", 5, 33)])
+                                                ("TINY", 8, 21), ("TINY_D128", 5, 33), ("TINY_GQ8", 2, 75)])
 def test_every_stage_of_one_layer(base, batch, history, plan_dir):
     config = dict(getattr(synthetic, base), num_hidden_layers=1)
     dim, heads, hkv = config["head_dim"], config["num_attention_heads"], config["num_key_value_heads"]
@@ -50,7 +50,8 @@ def test_every_stage_of_one_layer(base, batch, history, plan_dir):
     run.plan.launch(history, 2, run.stream)               # the step under test: position `history`
     run.check_alive()
     pos = history
-    qkv_gpu = run.read("serving.qkv").reshape(batch, hkv, 6, dim)
+    gq = heads // hkv
+    qkv_gpu = run.read("serving.qkv").reshape(batch, hkv, gq + 2, dim)
     attn_gpu = run.read("serving.attention").reshape(batch, heads * dim)
     h_gpu = run.read("serving.mlp").reshape(batch, -1)
     x_gpu = run.read("serving.hidden").reshape(batch, hidden)
@@ -60,13 +61,13 @@ def test_every_stage_of_one_layer(base, batch, history, plan_dir):
     # stage 1: RMSNorm + QKV
     x_in = F.embedding(ids[:, pos].long(), w["model.embed_tokens.weight"])
     xn = rms_norm(x_in, w[p + "input_layernorm.weight"], eps)
-    q = F.linear(xn, w[p + "self_attn.q_proj.weight"]).view(batch, hkv, 4, dim)
+    q = F.linear(xn, w[p + "self_attn.q_proj.weight"]).view(batch, hkv, gq, dim)
     k = F.linear(xn, w[p + "self_attn.k_proj.weight"]).view(batch, hkv, 1, dim)
     v = F.linear(xn, w[p + "self_attn.v_proj.weight"]).view(batch, hkv, 1, dim)
     agreement(qkv_gpu, torch.cat((q, k, v), dim=2), "qkv")
     # stage 2: RoPE, KV append, attention -- from the qkv the GPU produced
     cos, sin = rope_tables(config, capacity, torch.bfloat16)
-    q_gpu, k_gpu, v_gpu = qkv_gpu[:, :, :4], qkv_gpu[:, :, 4], qkv_gpu[:, :, 5]
+    q_gpu, k_gpu, v_gpu = qkv_gpu[:, :, :gq], qkv_gpu[:, :, gq], qkv_gpu[:, :, gq + 1]
     q_rot = q_gpu * cos[pos] + rotate_half(q_gpu) * sin[pos]
     k_rot = k_gpu * cos[pos] + rotate_half(k_gpu) * sin[pos]
     assert torch.equal(cache[0, 0, :, :, pos], k_rot), "appended key row is not the roped key, bit for bit"

@@ -1446,7 +1446,10 @@ static cudaError_t run_batch(const MegaParams& p, size_t smem_bytes, cudaStream_
 
 static cudaError_t run_decode(const MegaParams& p, cudaStream_t stream, bool prepare) {
   const size_t smem_bytes = size_t(ring_offset(p.xs_bytes, p.batch) + p.nslots * kSlotBytes);
-  if (p.kv_heads <= 0 || p.heads / p.kv_heads != 4) return cudaErrorInvalidValue;
+  if (p.kv_heads <= 0 || p.heads % p.kv_heads) return cudaErrorInvalidValue;
+  const int gq = p.heads / p.kv_heads;
+  if (p.head_dim == 128 && gq == 8) return run_batch<128, 8>(p, smem_bytes, stream, prepare);
+  if (gq != 4) return cudaErrorInvalidValue;
   if (p.head_dim == 128) return run_batch<128, 4>(p, smem_bytes, stream, prepare);
   if (p.head_dim == 64) return run_batch<64, 4>(p, smem_bytes, stream, prepare);
   return cudaErrorInvalidValue;

@@ -91,8 +91,10 @@ PlanSpec PlanSpec::FromJson(const Json& plan) {
   if (s.hidden <= 0 || s.inter <= 0 || s.heads <= 0 || s.kv_heads <= 0 || s.layers <= 0 || s.vocab <= 0)
     throw std::invalid_argument("model dimensions must be positive");
   if (s.head_dim != 64 && s.head_dim != 128) throw std::invalid_argument("head_dim must be 64 or 128");
-  if (s.heads % s.kv_heads || s.heads / s.kv_heads != 4)
-    throw std::invalid_argument("query heads per KV head must be 4");
+  if (s.heads % s.kv_heads || (s.heads / s.kv_heads != 4 && s.heads / s.kv_heads != 8))
+    throw std::invalid_argument("query heads per KV head must be 4 or 8");
+  if (s.heads / s.kv_heads == 8 && s.head_dim != 128)
+    throw std::invalid_argument("8 query heads per KV head are built for head_dim 128 only");
   // tensor parallelism: every split dimension must divide (export.py:182-192)
   s.tp = int(plan.integer("tp", 1));
   if (s.tp != 1 && s.tp != 2 && s.tp != 4 && s.tp != 8)

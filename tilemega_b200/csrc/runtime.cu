@@ -253,7 +253,8 @@ void* tm_plan_create(int batch, void* const* external, int device) {
   const double watchdog_ms = watchdog ? std::atof(watchdog) : 2000.0;
   p.watchdog_ns = (unsigned long long)(std::max(watchdog_ms, 0.001) * 1e6);
   // shared memory: activation rows (or the attention scratch, whichever is larger) + ring
-  const int attention_scratch = 4 * s.head_dim * 2 + 2 * s.head_dim * 2 + 8 * 4 * (s.head_dim + 2) * 4 + 64;
+  const int gq = s.heads / s.kv_heads;   // query heads per KV head (4 or 8)
+  const int attention_scratch = gq * s.head_dim * 2 + 2 * s.head_dim * 2 + 8 * gq * (s.head_dim + 2) * 4 + 64;
   // rows of the widest GEMV input; one extra hidden-wide row holds the RMSNorm weights
   // (rows are padded by 8 elements so that the batch rows of a k-chunk sit on distinct banks)
   // a normalised stage also parks its raw rows and the norm weights there: 2*batch + 1 hidden-wide rows
@@ -332,7 +333,7 @@ void* tm_plan_create(int batch, void* const* external, int device) {
        *step_ns = nullptr, *past = nullptr;
   const size_t attn_tasks = size_t(p.grid) + size_t(batch) * s.kv_heads + 1;
   const Scratch scratch[] = {
-      {&attn_part, attn_tasks * 4 * (s.head_dim + 2) * sizeof(float)},
+      {&attn_part, attn_tasks * gq * (s.head_dim + 2) * sizeof(float)},
       {&argmax_val, size_t(p.grid) * batch * sizeof(float)},
       {&argmax_idx, size_t(p.grid) * batch * sizeof(int)},
       {&status, tmb::kStWords * sizeof(unsigned long long)},

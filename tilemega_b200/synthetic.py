@@ -15,6 +15,9 @@ LLAMA_3_2_1B = dict(architectures=["LlamaForCausalLM"], hidden_size=2048, interm
 LLAMA_3_1_8B = dict(architectures=["LlamaForCausalLM"], hidden_size=4096, intermediate_size=14336,
                     num_attention_heads=32, num_key_value_heads=8, head_dim=128, num_hidden_layers=32,
                     vocab_size=128256, rms_norm_eps=1e-5, tie_word_embeddings=False, rope_theta=500000.0)
+LLAMA_3_1_70B = dict(architectures=["LlamaForCausalLM"], hidden_size=8192, intermediate_size=28672,
+                     num_attention_heads=64, num_key_value_heads=8, head_dim=128, num_hidden_layers=80,
+                     vocab_size=128256, rms_norm_eps=1e-5, tie_word_embeddings=False, rope_theta=500000.0)
 # Two-layer models (under 150 MB of bf16 weights) with every structural feature of
 # the above: 4 query heads per KV head, head_dim 64 / 128, every K a multiple of 2048.
 TINY = dict(architectures=["LlamaForCausalLM"], hidden_size=2048, intermediate_size=2048,
@@ -23,6 +26,12 @@ TINY = dict(architectures=["LlamaForCausalLM"], hidden_size=2048, intermediate_s
 TINY_D128 = dict(architectures=["LlamaForCausalLM"], hidden_size=2048, intermediate_size=4096,
                  num_attention_heads=16, num_key_value_heads=4, head_dim=128, num_hidden_layers=2,
                  vocab_size=2048, rms_norm_eps=1e-5, tie_word_embeddings=False, rope_theta=500000.0)
+
+
+# 8 query heads per KV head (the 70B-shaped grouping)
+TINY_GQ8 = dict(architectures=["LlamaForCausalLM"], hidden_size=2048, intermediate_size=2048,
+                num_attention_heads=16, num_key_value_heads=2, head_dim=128, num_hidden_layers=2,
+                vocab_size=1024, rms_norm_eps=1e-5, tie_word_embeddings=False, rope_theta=500000.0)
 
 
 def head_dim_of(config: dict) -> int:
@@ -72,6 +81,33 @@ def seeded_weights(config: dict, seed: int = 0, dtype: torch.dtype = torch.float
             draw = torch.randn(shape, generator=generator, dtype=torch.float32, device=device)
             weights[name] = (draw * std).to(dtype)
     return weights
+
+
+class LazySeededCheckpoint:
+    """A checkpoint whose tensors are drawn when asked for, each from its own generator
+    seeded by (seed, tensor name): for models too large to hold unpacked (a 70B-shaped
+    model is 140 GB in bf16). Every process that asks for a name gets the same values,
+    so tensor-parallel ranks cut their slices out of one consistent model. Throughput
+    runs only: the draws are the device generator's, not the CPU draws of seeded_weights."""
+
+    def __init__(self, config: dict, seed: int = 0, dtype: torch.dtype = torch.bfloat16,
+                 device: str | torch.device = "cuda", std: float = 0.02):
+        self.shapes = dict(parameter_shapes(config))
+        self.tie_word_embeddings = bool(config.get("tie_word_embeddings", False))
+        self.seed, self.dtype, self.device, self.std = seed, dtype, torch.device(device), std
+
+    def tensor(self, name: str) -> torch.Tensor:
+        import zlib
+        if name == "lm_head.weight" and name not in self.shapes and self.tie_word_embeddings:
+            name = "model.embed_tokens.weight"
+        if name not in self.shapes:
+            raise KeyError(f"checkpoint has no {name}")
+        shape = self.shapes[name]
+        if len(shape) == 1:
+            return torch.ones(shape, dtype=self.dtype, device=self.device)
+        generator = torch.Generator(device=self.device).manual_seed((self.seed << 32) ^ zlib.crc32(name.encode()))
+        draw = torch.empty(shape, dtype=self.dtype, device=self.device)
+        return draw.normal_(0.0, self.std, generator=generator)
 
 
 def seeded_tokens(batch: int, length: int, vocab: int, seed: int = 1) -> torch.Tensor:
