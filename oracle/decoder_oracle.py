@@ -24,6 +24,13 @@ the reference's rank modules); the summation rule is read from the kernel source
 The sharded lm_head changes nothing: each rank scores a slice of the rows and the
 ranks' winners are compared with ties to the smaller index (Sm90DenseHead.cuh:139-201).
 
+Mixture of experts (config `num_experts`): the router, top-k and expert sum of
+python/tilemega/moe/export.py:12-37,68-93 (softmax in fp32 over the router's
+model-dtype logits, top-k, optional renormalisation kept in fp32, expert outputs in
+the model dtype times the fp32 routing weight, fp32 sum over the k ranks, one
+rounding), and the per-head QK norm of Qwen3 (serving/export.py:63-65,82-84).
+`last_route[layer]` keeps the chosen expert indices [tokens][k] for the tests.
+
 Every op is the same torch op on the same dtype as the reference, so in bf16 the
 rounding sites are the reference's: one rounding per linear output, RMSNorm
 `w * (x.float() * rsqrt(mean x^2 + eps)).to(dtype)`, RoPE product-product-sum,
@@ -130,6 +137,11 @@ class OracleDecoder:
         self.kv_heads = config["num_key_value_heads"]
         self.dim = head_dim_of(config)
         self.cos, self.sin = rope_tables(config, capacity, dtype)
+        self.qk_norm = config["architectures"][0].startswith("Qwen3") if "architectures" in config else False
+        self.experts = int(config.get("num_experts", 0))
+        self.last_route: dict[int, torch.Tensor] = {}
+        if self.experts and tp != 1:
+            raise ValueError("tensor parallel MoE is out of scope (export.py:191-192)")
 
     def row_sharded_partials(self, x: torch.Tensor, weight: torch.Tensor) -> list[torch.Tensor]:
         """The ranks' partial outputs of a linear whose reduction axis is split into tp
@@ -160,6 +172,10 @@ class OracleDecoder:
         q = F.linear(x, self.w[p + "q_proj.weight"]).view(batch, seq, self.heads, self.dim)
         k = F.linear(x, self.w[p + "k_proj.weight"]).view(batch, seq, self.kv_heads, self.dim)
         v = F.linear(x, self.w[p + "v_proj.weight"]).view(batch, seq, self.kv_heads, self.dim)
+        if self.qk_norm:
+            # serving/export.py:82-84: each head normalised over its own D values, before RoPE
+            q = rms_norm(q, self.w[p + "q_norm.weight"], self.eps)
+            k = rms_norm(k, self.w[p + "k_norm.weight"], self.eps)
         context = torch.empty((batch, seq, self.heads * self.dim), dtype=x.dtype)
         for b in range(batch):
             positions = torch.arange(start[b], start[b] + seq)
@@ -185,7 +201,34 @@ class OracleDecoder:
             context[b] = attended.transpose(0, 1).reshape(seq, self.heads * self.dim)
         return self.row_sharded_partials(context, self.w[p + "o_proj.weight"])
 
+    def sparse_mlp(self, layer: int, x: torch.Tensor) -> torch.Tensor:
+        # moe/export.py:68-93 (router) and :12-37 (experts)
+        p = f"model.layers.{layer}.mlp."
+        shape = x.shape
+        rows = x.reshape(-1, shape[-1])
+        logits = F.linear(rows, self.w[p + "gate.weight"])
+        probability = torch.softmax(logits, -1, dtype=torch.float32)
+        weight, index = torch.topk(probability, int(self.config["num_experts_per_tok"]), dim=-1)
+        if self.config.get("norm_topk_prob", False):
+            weight = weight / weight.sum(-1, keepdim=True)
+        else:
+            weight = weight.to(rows.dtype)
+        self.last_route[layer] = index.clone()
+        partials = torch.empty((rows.shape[0], index.shape[1], shape[-1]),
+                               dtype=torch.promote_types(rows.dtype, weight.dtype))
+        for expert in range(self.experts):
+            token, rank = torch.where(index == expert)
+            if token.numel():
+                e = p + f"experts.{expert}."
+                gate = F.linear(rows[token], self.w[e + "gate_proj.weight"])
+                up = F.linear(rows[token], self.w[e + "up_proj.weight"])
+                projected = F.linear(F.silu(gate) * up, self.w[e + "down_proj.weight"])
+                partials[token, rank] = projected * weight[token, rank, None]
+        return partials.sum(1, dtype=torch.float32).to(rows.dtype).reshape(shape)
+
     def mlp_partials(self, layer: int, x: torch.Tensor) -> list[torch.Tensor]:
+        if self.experts:
+            return [self.sparse_mlp(layer, x)]
         # export.py:115-116
         p = f"model.layers.{layer}.mlp."
         hidden = F.silu(F.linear(x, self.w[p + "gate_proj.weight"])) * F.linear(x, self.w[p + "up_proj.weight"])

@@ -30,12 +30,28 @@ def rope(config: dict, capacity: int, dtype: torch.dtype):
     return table.cos().to(torch.bfloat16).to(dtype), table.sin().to(torch.bfloat16).to(dtype)
 
 
+def module_state(config: dict, state: dict[str, torch.Tensor]) -> dict[str, torch.Tensor]:
+    """The checkpoint holds one tensor per expert projection (HF names); the reference's
+    module keeps them stacked (python/tilemega/moe/export.py:54-65: gate rows then up rows)."""
+    if not synthetic.is_moe(config):
+        return state
+    out = {name: tensor for name, tensor in state.items() if ".mlp.experts." not in name}
+    for layer in range(config["num_hidden_layers"]):
+        p = f"model.layers.{layer}.mlp.experts."
+        out[p + "gate_up_proj"] = torch.stack([torch.cat((state[p + f"{e}.gate_proj.weight"],
+                                                          state[p + f"{e}.up_proj.weight"]))
+                                               for e in range(config["num_experts"])])
+        out[p + "down_proj"] = torch.stack([state[p + f"{e}.down_proj.weight"] for e in range(config["num_experts"])])
+    return out
+
+
 def run_reference(Decoder, config: dict, dtype: torch.dtype, prompt: torch.Tensor, new_tokens: int,
                   weight_rounding: torch.dtype):
     """Greedy decode with the reference module; weights rounded to `weight_rounding` first."""
     model = Decoder(config).eval()
     weights = synthetic.seeded_weights(config, seed=0, dtype=torch.float32)
     state = {name: tensor.to(weight_rounding).to(torch.float32) for name, tensor in weights.items()}
+    state = module_state(config, state)
     missing = model.load_state_dict(state, strict=False)
     assert not missing.unexpected_keys and set(missing.missing_keys) <= {"lm_head.weight"}, missing
     model = model.to(dtype)
@@ -67,8 +83,12 @@ def main() -> None:
         ("tiny", synthetic.TINY, 2, 21, 8, True),
         ("tiny_d128", synthetic.TINY_D128, 3, 37, 6, True),
         ("llama_3_2_1b", synthetic.LLAMA_3_2_1B, 1, 128, 32, False),
+        ("tiny_moe", synthetic.TINY_MOE, 2, 19, 6, True),
     )
+    only = set(sys.argv[2:])
     for name, config, batch, prompt_len, new_tokens, keep_logits in cases:
+        if only and name not in only:
+            continue
         prompt = synthetic.seeded_tokens(batch, prompt_len, config["vocab_size"], seed=1)
         record = {"config": config, "batch": batch, "prompt_len": prompt_len, "new_tokens": new_tokens,
                   "prompt": prompt, "torch": str(torch.__version__)}

@@ -22,7 +22,7 @@ def run_oracle(record, dtype, rounding, block_table=None, num_blocks=None):
     return decoder.greedy(record["prompt"], record["new_tokens"], kv)
 
 
-@pytest.mark.parametrize("name", ["tiny", "tiny_d128"])
+@pytest.mark.parametrize("name", ["tiny", "tiny_d128", "tiny_moe"])
 @pytest.mark.parametrize("mode", MODES, ids=[m[0] for m in MODES])
 def test_oracle_reproduces_reference_small(name, mode):
     label, dtype, rounding = mode

@@ -353,11 +353,14 @@ __device__ __forceinline__ void stream_gemv_task(Ctx& c, const GemvGeo& geo, con
   const unsigned char* src = weights + size_t(t) * size_t(geo.pages_per_task) * page_bytes;
   for (int pg = 0; pg < geo.pages_per_task; ++pg, src += page_bytes) {
     if (!stream_wait_empty(c)) return;
+    // the last page of a padded reduction: its pad columns (whole 64-column blocks at the
+    // end of the page, which no warp reads) are not copied
+    const uint32_t bytes = pg + 1 == geo.pages_per_task ? uint32_t(geo.last_page_bytes) : page_bytes;
     if (c.p.diag & kDiagNoCopy) {
       mbar_arrive(c.full(c.slot));   // diagnosis: arithmetic warps at their own speed on whatever is in the ring
     } else {
-      mbar_expect_tx(c.full(c.slot), page_bytes);
-      bulk_g2s_hint(c.ring(c.slot), src, page_bytes, c.full(c.slot), policy);
+      mbar_expect_tx(c.full(c.slot), bytes);
+      bulk_g2s_hint(c.ring(c.slot), src, bytes, c.full(c.slot), policy);
     }
     c.advance();
   }
@@ -864,11 +867,15 @@ __device__ TMB_GEMV_CALL void gemv_stage(Ctx& c, const GemvGeo& geo, const GemvI
     }
     for (int pg = 0; pg < geo.pages_per_task; ++pg) {
       mbar_wait_warp(c, full0 + slot, phase, kSiteFull);
+      // a warp whose 256 columns of this page lie wholly in the reduction's zero pad
+      // has nothing to add (and that part of the slot was not copied)
+      if (pg * geo.tile_k + 256 * warp < geo.k_src) {
 #if TMB_GEMV_MMA
-      gemv_page_mma<B>(ring0 + slot * kSlotBytes, xs, geo.k, pg * geo.tile_k, warp, lane, d);
+        gemv_page_mma<B>(ring0 + slot * kSlotBytes, xs, geo.k, pg * geo.tile_k, warp, lane, d);
 #else
-      gemv_page_fma<B>(ring0 + slot * kSlotBytes, xs, geo.k, pg * geo.tile_k, warp, lane, acc);
+        gemv_page_fma<B>(ring0 + slot * kSlotBytes, xs, geo.k, pg * geo.tile_k, warp, lane, acc);
 #endif
+      }
       __syncwarp();
       if (lane == 0) mbar_arrive(empty0 + slot);
       if (++slot == nslots) { slot = 0; phase ^= 1u; }

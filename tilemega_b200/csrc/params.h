@@ -30,6 +30,7 @@ struct GemvGeo {
   int k_src;           // columns the activation rows really have (the packing recipe zero-pads the weights to k)
   int tile_k;          // columns per page (2048)
   int pages_per_task;  // k / tile_k: a task is one 8-row tile over the whole reduction
+  int last_page_bytes; // bytes of a task's last page that are copied: k_src rounded up to 256 columns (a warp's share)
   int ntasks;          // n / 8
 };
 

@@ -38,7 +38,9 @@ std::string Pages(const std::string& source, int tile_k) {
 
 // A reduction length that is not a multiple of the page width is rounded up: the
 // tile_pages recipe zero-fills the weights' missing columns and the kernel zero-fills the
-// activation rows', so the extra columns add nothing (they do cost their bandwidth).
+// activation rows', so the extra columns add nothing. Inside a page a 64-column block of
+// the 8 rows is contiguous (1 KB), so the pad is the page's tail: the kernel copies only
+// last_page_bytes of a task's last page and the pad costs address space, not bandwidth.
 GemvGeo MakeGeo(const char* what, int n, int k, const Json& overrides) {
   GemvGeo g{};
   g.n = n;
@@ -54,6 +56,9 @@ GemvGeo MakeGeo(const char* what, int n, int k, const Json& overrides) {
   if (k <= 0 || k % g.tile_k) throw std::invalid_argument(std::string(what) + ": K must be a multiple of tile_k");
   const int kt = k / g.tile_k;
   g.pages_per_task = kt;
+  // columns of the last page that hold weights, in whole 256-column warp shares
+  const int last_columns = (g.k_src - (kt - 1) * g.tile_k + 255) / 256 * 256;
+  g.last_page_bytes = kTileN * last_columns * 2;
   g.ntasks = n / kTileN;
   return g;
 }

@@ -34,6 +34,22 @@ TINY_GQ8 = dict(architectures=["LlamaForCausalLM"], hidden_size=2048, intermedia
                 vocab_size=1024, rms_norm_eps=1e-5, tie_word_embeddings=False, rope_theta=500000.0)
 
 
+# Mixture of experts (Qwen3-30B-A3B-shaped): per-head QK norm, top-k routing over a
+# softmax, expert SwiGLU FFNs; router weights N(0, 0.1) so the expert load is uneven.
+QWEN3_30B_A3B = dict(architectures=["Qwen3MoeForCausalLM"], hidden_size=2048, intermediate_size=6144,
+                     moe_intermediate_size=768, num_experts=128, num_experts_per_tok=8, norm_topk_prob=True,
+                     num_attention_heads=32, num_key_value_heads=4, head_dim=128, num_hidden_layers=48,
+                     vocab_size=151936, rms_norm_eps=1e-6, tie_word_embeddings=False, rope_theta=1000000.0)
+TINY_MOE = dict(architectures=["Qwen3MoeForCausalLM"], hidden_size=2048, intermediate_size=6144,
+                moe_intermediate_size=768, num_experts=16, num_experts_per_tok=4, norm_topk_prob=True,
+                num_attention_heads=16, num_key_value_heads=2, head_dim=128, num_hidden_layers=2,
+                vocab_size=1024, rms_norm_eps=1e-6, tie_word_embeddings=False, rope_theta=1000000.0)
+
+
+def is_moe(config: dict) -> bool:
+    return int(config.get("num_experts", 0)) > 0
+
+
 def head_dim_of(config: dict) -> int:
     return int(config.get("head_dim") or config["hidden_size"] // config["num_attention_heads"])
 
@@ -44,6 +60,7 @@ def parameter_shapes(config: dict) -> list[tuple[str, tuple[int, ...]]]:
     dim = head_dim_of(config)
     q, kv = config["num_attention_heads"] * dim, config["num_key_value_heads"] * dim
     shapes: list[tuple[str, tuple[int, ...]]] = [("model.embed_tokens.weight", (config["vocab_size"], hidden))]
+    qk_norm = config["architectures"][0].startswith("Qwen3")
     for layer in range(config["num_hidden_layers"]):
         p = f"model.layers.{layer}."
         shapes += [
@@ -52,15 +69,30 @@ def parameter_shapes(config: dict) -> list[tuple[str, tuple[int, ...]]]:
             (p + "self_attn.k_proj.weight", (kv, hidden)),
             (p + "self_attn.v_proj.weight", (kv, hidden)),
             (p + "self_attn.o_proj.weight", (hidden, q)),
-            (p + "post_attention_layernorm.weight", (hidden,)),
-            (p + "mlp.gate_proj.weight", (inter, hidden)),
-            (p + "mlp.up_proj.weight", (inter, hidden)),
-            (p + "mlp.down_proj.weight", (hidden, inter)),
         ]
+        if qk_norm:
+            shapes += [(p + "self_attn.q_norm.weight", (dim,)), (p + "self_attn.k_norm.weight", (dim,))]
+        shapes.append((p + "post_attention_layernorm.weight", (hidden,)))
+        if is_moe(config):
+            expert_inter = int(config.get("moe_intermediate_size") or inter)
+            shapes.append((p + "mlp.gate.weight", (config["num_experts"], hidden)))
+            for expert in range(config["num_experts"]):
+                e = p + f"mlp.experts.{expert}."
+                shapes += [(e + "gate_proj.weight", (expert_inter, hidden)), (e + "up_proj.weight", (expert_inter, hidden)),
+                           (e + "down_proj.weight", (hidden, expert_inter))]
+        else:
+            shapes += [
+                (p + "mlp.gate_proj.weight", (inter, hidden)),
+                (p + "mlp.up_proj.weight", (inter, hidden)),
+                (p + "mlp.down_proj.weight", (hidden, inter)),
+            ]
     shapes.append(("model.norm.weight", (hidden,)))
     if not config.get("tie_word_embeddings", False):
         shapes.append(("lm_head.weight", (config["vocab_size"], hidden)))
     return shapes
+
+
+ROUTER_STD = 0.1
 
 
 def seeded_weights(config: dict, seed: int = 0, dtype: torch.dtype = torch.float32,
@@ -79,7 +111,7 @@ def seeded_weights(config: dict, seed: int = 0, dtype: torch.dtype = torch.float
             weights[name] = torch.ones(shape, dtype=dtype, device=device)
         else:
             draw = torch.randn(shape, generator=generator, dtype=torch.float32, device=device)
-            weights[name] = (draw * std).to(dtype)
+            weights[name] = (draw * (ROUTER_STD if name.endswith("mlp.gate.weight") else std)).to(dtype)
     return weights
 
 
@@ -107,7 +139,7 @@ class LazySeededCheckpoint:
             return torch.ones(shape, dtype=self.dtype, device=self.device)
         generator = torch.Generator(device=self.device).manual_seed((self.seed << 32) ^ zlib.crc32(name.encode()))
         draw = torch.empty(shape, dtype=self.dtype, device=self.device)
-        return draw.normal_(0.0, self.std, generator=generator)
+        return draw.normal_(0.0, ROUTER_STD if name.endswith("mlp.gate.weight") else self.std, generator=generator)
 
 
 def seeded_tokens(batch: int, length: int, vocab: int, seed: int = 1) -> torch.Tensor:
