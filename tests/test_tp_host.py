@@ -18,13 +18,13 @@ from tilemega_b200.serving.weights import TensorCheckpoint, load_weights, pack, 
 
 
 def test_rank_plan_tables(plan_dir):
-    config = synthetic.TINY
+    config = synthetic.TINY_D128
     lib = PlanLibrary(emit_plan(config, plan_dir, batch_lo=1, batch_hi=2, capacity=64, tp=2))
     assert lib.tp_world == 2
     table = {buffer.name: buffer for buffer in lib.buffers}
-    hidden, dim = config["hidden_size"], 64
-    heads, hkv, inter, vocab = 32 // 2, 8 // 2, config["intermediate_size"] // 2, config["vocab_size"] // 2
-    # one rank's shares; reductions of 1024 columns are padded to one 2048-column page
+    hidden, dim = config["hidden_size"], 128
+    heads, hkv, inter, vocab = 16 // 2, 4 // 2, config["intermediate_size"] // 2, config["vocab_size"] // 2
+    # one rank's shares; the o reduction of 1024 columns is padded to one 2048-column page
     assert table["serving.qkv"].elements_per_batch == (heads + 2 * hkv) * dim
     assert table["serving.attention"].elements_per_batch == heads * dim
     assert table["serving.mlp"].elements_per_batch == inter
@@ -42,6 +42,12 @@ def test_rank_plan_tables(plan_dir):
     # two regions of [ranks][batch_hi][hidden/2] 8-byte packets; [ranks][8] exchange packets
     assert lib.tp_bytes(0) == 2 * 2 * 2 * (hidden // 2) * 8
     assert lib.tp_bytes(1) == 2 * 8 * 8
+
+
+def test_tensor_parallel_needs_head_dim_128(plan_dir):
+    so = emit_plan(synthetic.TINY, plan_dir, batch_lo=1, batch_hi=1, capacity=64, tp=2)
+    with pytest.raises(RuntimeError, match="head_dim 128"):
+        PlanLibrary(so)
 
 
 def test_unsharded_plan_reports_world_one(plan_dir):
@@ -77,10 +83,10 @@ def test_sharded_recipe_takes_the_rank_slice():
 def _rank_main(rank: int, world: int, port: int, plan_path: str, out_dir: str) -> None:
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
-    config = dict(synthetic.TINY, num_hidden_layers=1)
+    config = dict(synthetic.TINY_D128, num_hidden_layers=1)
     lib = PlanLibrary(plan_path)
     weights = synthetic.seeded_weights(config, seed=0, dtype=torch.bfloat16)
-    packed = load_weights(TensorCheckpoint(weights, True), lib, device="cpu", tp=(rank, world))
+    packed = load_weights(TensorCheckpoint(weights, False), lib, device="cpu", tp=(rank, world))
     # element sums are layout-independent: the two ranks' slices must add up to the whole tensor
     mine = torch.tensor([packed[name].double().sum().item() for name in ("l0.qkv.weight", "l0.o.weight",
                                                                             "l0.gate_up.weight", "l0.down.weight",
@@ -92,14 +98,14 @@ def _rank_main(rank: int, world: int, port: int, plan_path: str, out_dir: str) -
         weights[p + "self_attn.o_proj.weight"].double().sum().item(),
         weights[p + "mlp.gate_proj.weight"].double().sum().item() + weights[p + "mlp.up_proj.weight"].double().sum().item(),
         weights[p + "mlp.down_proj.weight"].double().sum().item(),
-        weights["model.embed_tokens.weight"].double().sum().item()], dtype=torch.float64)
+        weights["lm_head.weight"].double().sum().item()], dtype=torch.float64)
     ok = bool(torch.allclose(mine, whole, rtol=0, atol=1e-6))
     Path(out_dir, f"rank{rank}.txt").write_text("ok" if ok else f"mismatch {mine.tolist()} {whole.tolist()}")
     dist.destroy_process_group()
 
 
 def test_two_ranks_pack_disjoint_slices_that_cover_the_checkpoint(plan_dir, tmp_path):
-    config = dict(synthetic.TINY, num_hidden_layers=1)
+    config = dict(synthetic.TINY_D128, num_hidden_layers=1)
     so = emit_plan(config, plan_dir, batch_lo=1, batch_hi=1, capacity=32, tp=2)
     with socket.socket() as probe:
         probe.bind(("127.0.0.1", 0))

@@ -101,9 +101,10 @@ def main() -> None:
     torch.cuda.set_device(dist.get_rank())
     plan_dir = Path(args.plan_dir)
     results = [
-        # o and down reductions of 1024 columns per rank: zero-padded to one 2048-column page
-        run_case("tiny tp", synthetic.TINY, 2, 21, 6, 64, plan_dir),
+        # o (and, for the second case, down) reductions of 1024 columns per rank: padded to one
+        # 2048-column page of which only the first half is copied
         run_case("tiny_d128 tp", synthetic.TINY_D128, 3, 13, 5, 32, plan_dir),
+        run_case("tiny_gq8 tp", synthetic.TINY_GQ8, 2, 21, 6, 64, plan_dir),
     ]
     if dist.get_rank() == 0 and args.out:
         Path(args.out).write_text(json.dumps(results))

@@ -14,7 +14,11 @@ ROOT = Path(__file__).resolve().parent
 CSRC = ROOT / "csrc"
 LIB_DIR = ROOT / "lib"
 LIBRARY = LIB_DIR / "libtilemega_b200.so"
-SOURCES = ("megakernel.cu", "runtime.cu", "plan_spec.cpp", "static_probe.cu")
+# (object name, source, extra flags). The kernel source is compiled twice, side by side:
+# plain (unsharded dense plans) and extended (tensor parallelism, mixture of experts, QK norm).
+UNITS = (("megakernel", "megakernel.cu", ()), ("megakernel_extended", "megakernel.cu", ("-DTMB_EXTENDED=1",)),
+         ("runtime", "runtime.cu", ()), ("plan_spec", "plan_spec.cpp", ()), ("static_probe", "static_probe.cu", ()))
+SOURCES = tuple(sorted({unit[1] for unit in UNITS}))
 HEADERS = ("params.h", "ptx.cuh", "plan_spec.h", "json.h")
 
 
@@ -45,11 +49,16 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
         common += ["-Xptxas", "-v"]
     build_dir = ROOT / "build"
     build_dir.mkdir(exist_ok=True)
-    for name in SOURCES:
-        obj = build_dir / (Path(name).stem + ".o")
-        cmd = [nvcc(), *common, "-x", "cu" if name.endswith(".cu") else "c++", "-c", str(CSRC / name), "-o", str(obj)]
-        subprocess.run(cmd, check=True)
+    running = []
+    for stem, name, flags in UNITS:
+        obj = build_dir / (stem + ".o")
+        cmd = [nvcc(), *common, *flags, "-x", "cu" if name.endswith(".cu") else "c++", "-c", str(CSRC / name), "-o",
+               str(obj)]
+        running.append((cmd, subprocess.Popen(cmd)))
         objects.append(str(obj))
+    for cmd, process in running:
+        if process.wait() != 0:
+            raise subprocess.CalledProcessError(process.returncode, cmd)
     tmp = LIBRARY.with_suffix(".so.tmp")
     subprocess.run([nvcc(), "-shared", "-o", str(tmp), *objects, "-gencode", "arch=compute_100a,code=sm_100a",
                     "-Xlinker", "--no-undefined", "-ldl"], check=True)

@@ -30,6 +30,9 @@
 #include "params.h"
 #include "ptx.cuh"
 
+#ifndef TMB_EXTENDED
+#define TMB_EXTENDED 0   // 1: the translation unit with tensor parallelism, mixture of experts and QK norm
+#endif
 #ifndef TMB_GEMV_MMA
 #define TMB_GEMV_MMA 1   // 1: weight pages through ldmatrix + mma.sync (bf16, fp32 accumulate); 0: fp32 FMA on CUDA cores
 #endif
@@ -59,7 +62,7 @@ constexpr int kOffFifo = 320;      // int[kFifo] task ids claimed by the streami
 constexpr int kOffBestVal = 448;   // float[8 warps][kMaxBatch]
 constexpr int kOffBestIdx = 704;   // int[8 warps][kMaxBatch]
 constexpr int kOffWsum = 960;      // float[kMaxBatch][8]
-constexpr int kOffSc = 1216;       // float[8 warps][4][16]
+constexpr int kOffSc = 1216;       // routing of the current layer: int expert[8], float weight[8] (+32), mbarrier (+64)
 constexpr int kOffRed = 3264;      // float[kPartialRing][8 warps][8 rows][batch]: 2 KB per sequence of the batch
 constexpr int kFifo = 32;          // entries; the streaming warp keeps at most kFifo/2 unread
 
@@ -79,9 +82,11 @@ struct Ctx {
   int pending;                       // streaming thread: first task id claimed for the stage about to start
   int pending_next;                  // ... and for the stage after it (claimed a whole stage ahead)
   uint32_t gemv_seq;                 // GEMV tasks finished by this CTA (partial-sum ring cursor)
+  uint32_t route_phase;              // routings published (arithmetic warps) / consumed (streaming thread), mod 2
   __device__ Ctx(const MegaParams& q, unsigned char* s)
       : p(q), smem(s), warp(threadIdx.x >> 5), lane(threadIdx.x & 31), tid(threadIdx.x), slot(0), phase(0),
-        bar_target(q.bar_base), task_seq(0), dead(false), q_pos(0), inst(0), pending(0), pending_next(0), gemv_seq(0) {}
+        bar_target(q.bar_base), task_seq(0), dead(false), q_pos(0), inst(0), pending(0), pending_next(0), gemv_seq(0),
+        route_phase(0) {}
   __device__ uint64_t* full(int i) const { return reinterpret_cast<uint64_t*>(smem + kOffFull) + i; }
   __device__ uint64_t* empty(int i) const { return reinterpret_cast<uint64_t*>(smem + kOffEmpty) + i; }
   __device__ uint64_t* pfull(int i) const { return reinterpret_cast<uint64_t*>(smem + kOffPFull) + i; }
@@ -91,7 +96,9 @@ struct Ctx {
   __device__ int* best_idx() const { return reinterpret_cast<int*>(smem + kOffBestIdx); }
   __device__ float* wsum() const { return reinterpret_cast<float*>(smem + kOffWsum); }
   __device__ float* red() const { return reinterpret_cast<float*>(smem + kOffRed); }
-  __device__ float* sc() const { return reinterpret_cast<float*>(smem + kOffSc); }
+  __device__ volatile int* route_e() const { return reinterpret_cast<volatile int*>(smem + kOffSc); }
+  __device__ volatile float* route_w() const { return reinterpret_cast<volatile float*>(smem + kOffSc + 32); }
+  __device__ uint64_t* route_bar() const { return reinterpret_cast<uint64_t*>(smem + kOffSc + 64); }
   __device__ unsigned char* xs() const { return smem + xs_offset(p.batch); }
   __device__ unsigned char* ring(int i) const { return smem + ring_offset(p.xs_bytes, p.batch) + i * kSlotBytes; }
   __device__ void advance() {
@@ -107,7 +114,7 @@ struct Ctx {
 // and raises status[0]; every other wait sees status[0] and falls through, and
 // every CTA leaves at its next stage boundary. Nothing traps.
 // ---------------------------------------------------------------------------
-__device__ __noinline__ bool wait_give_up(const MegaParams& p, unsigned long long& t0, int site,
+static __device__ __noinline__ bool wait_give_up(const MegaParams& p, unsigned long long& t0, int site,
                                           unsigned long long need, unsigned long long value) {
   if (ld_relaxed(p.status + kStFired) != 0) return true;
   const unsigned long long now = global_timer();
@@ -196,7 +203,7 @@ __device__ __forceinline__ bool grid_wait(Ctx& c) {
 // (include/tilemega/Codegen/tasks/ModelRuntime.h:758-766).
 __device__ __forceinline__ void trace_mark(const Ctx& c, bool on, int stage, int what) {
   if (on && c.tid == 0) {
-    const int stages = 5 * c.p.layers + 1;
+    const int stages = c.p.stages_per_layer * c.p.layers + 1;
     c.p.trace[(size_t(blockIdx.x) * stages + stage) * 4 + what] = global_timer();
   }
 }
@@ -345,12 +352,10 @@ __device__ __forceinline__ void stream_close(Ctx& c) {
   c.pending_next = claim(c, c.inst + 1);
 }
 
-// One GEMV task: post its id, then copy its weight pages into the ring.
-__device__ __forceinline__ void stream_gemv_task(Ctx& c, const GemvGeo& geo, const unsigned char* weights, int t,
-                                                 uint32_t page_bytes, uint64_t policy) {
-  fifo_push(c, t);
-  // pages of a task are consecutive: task t = (row tile, k split) starts at page t * pages_per_task
-  const unsigned char* src = weights + size_t(t) * size_t(geo.pages_per_task) * page_bytes;
+// One GEMV task: post its id, then copy its weight pages (consecutive from `src`) into the ring.
+__device__ __forceinline__ void stream_pages(Ctx& c, const GemvGeo& geo, const unsigned char* src, int id,
+                                             uint32_t page_bytes, uint64_t policy) {
+  fifo_push(c, id);
   for (int pg = 0; pg < geo.pages_per_task; ++pg, src += page_bytes) {
     if (!stream_wait_empty(c)) return;
     // the last page of a padded reduction: its pad columns (whole 64-column blocks at the
@@ -364,6 +369,12 @@ __device__ __forceinline__ void stream_gemv_task(Ctx& c, const GemvGeo& geo, con
     }
     c.advance();
   }
+}
+
+// task t = one row tile over the whole reduction: its pages start at page t * pages_per_task
+__device__ __forceinline__ void stream_gemv_task(Ctx& c, const GemvGeo& geo, const unsigned char* weights, int t,
+                                                 uint32_t page_bytes, uint64_t policy) {
+  stream_pages(c, geo, weights + size_t(t) * size_t(geo.pages_per_task) * page_bytes, t, page_bytes, policy);
 }
 
 // static_quarters/4 of a CTA's even share of a stage are dealt statically (task
@@ -385,6 +396,42 @@ __device__ __forceinline__ void stream_gemv(Ctx& c, const GemvGeo& geo, const vo
     const int upcoming = claim(c, c.inst);
     stream_gemv_task(c, geo, w, t, page_bytes, policy);
     t = dealt * c.p.grid + upcoming;
+  }
+  stream_close(c);
+}
+
+// Mixture of experts, batch 1. gate/up: the chosen experts' matrices one after the other,
+// task t = (expert slot t / tiles, row tile t % tiles). `stack` holds every expert packed
+// by itself, experts geo.ntasks * pages_per_task pages apart.
+__device__ __forceinline__ void stream_expert_gate_up(Ctx& c, const GemvGeo& geo, const void* stack,
+                                                      const int (&expert)[kMaxTopK], uint64_t policy) {
+  const uint32_t page_bytes = uint32_t(kTileN) * uint32_t(geo.tile_k) * 2u;
+  const unsigned char* w = static_cast<const unsigned char*>(stack);
+  const int total = c.p.topk * geo.ntasks;
+  int t = c.pending;
+  while (t < total && !c.dead) {
+    const int upcoming = claim(c, c.inst);
+    const int slot = t / geo.ntasks, tile = t - slot * geo.ntasks;
+    stream_pages(c, geo, w + (size_t(expert[slot]) * geo.ntasks + tile) * size_t(geo.pages_per_task) * page_bytes, t,
+                 page_bytes, policy);
+    t = upcoming;
+  }
+  stream_close(c);
+}
+
+// down: a claimed task is one row tile over ALL chosen experts (their outputs are summed
+// per row in rank order by one warp); it is posted as topk sub-tasks of one page each.
+__device__ __forceinline__ void stream_expert_down(Ctx& c, const GemvGeo& geo, const void* stack,
+                                                   const int (&expert)[kMaxTopK], uint64_t policy) {
+  const uint32_t page_bytes = uint32_t(kTileN) * uint32_t(geo.tile_k) * 2u;
+  const unsigned char* w = static_cast<const unsigned char*>(stack);
+  int t = c.pending;
+  while (t < geo.ntasks && !c.dead) {
+    const int upcoming = claim(c, c.inst);
+    for (int slot = 0; slot < c.p.topk; ++slot)
+      stream_pages(c, geo, w + (size_t(expert[slot]) * geo.ntasks + t) * page_bytes, t * c.p.topk + slot, page_bytes,
+                   policy);
+    t = upcoming;
   }
   stream_close(c);
 }
@@ -430,11 +477,11 @@ __device__ __forceinline__ void stream_attn(Ctx& c, const LayerPtrs& lp, int pas
   stream_close(c);
 }
 
-template <int D>
+template <int D, bool X>
 __device__ void streamer_main(Ctx& c) {
   const MegaParams& p = c.p;
   const uint64_t policy = policy_evict_first();
-  const unsigned long long bars_per_step = 4ull * p.layers + 1ull;   // grid barriers: none between QKV and attention
+  const unsigned long long bars_per_step = (unsigned long long)(p.stages_per_layer - 1) * p.layers + 1ull;   // grid barriers: none between QKV and attention
   const uint32_t norm_bytes = uint32_t(p.hidden) * 2u;
   c.pending = claim(c, 0);
   c.pending_next = claim(c, 1);
@@ -462,8 +509,20 @@ __device__ void streamer_main(Ctx& c) {
       }
       stream_attn<D>(c, lp, past);
       stream_gemv(c, p.geo[kOProj], lp.o, policy);
-      stream_gemv(c, p.geo[kGateUp], lp.gate_up, policy);
-      stream_gemv(c, p.geo[kDown], lp.down, policy);
+      if (X && p.experts) {
+        stream_gemv(c, p.geo[kRouter], lp.router, policy);
+        // the experts of this layer are known once the arithmetic warps have routed
+        if (!mbar_wait(c, c.route_bar(), c.route_phase, kSiteFull)) return;
+        c.route_phase ^= 1u;
+        int expert[kMaxTopK];
+#pragma unroll
+        for (int i = 0; i < kMaxTopK; ++i) expert[i] = c.route_e()[i];
+        stream_expert_gate_up(c, p.geo[kGateUp], lp.gate_up, expert, policy);
+        stream_expert_down(c, p.geo[kDown], lp.down, expert, policy);
+      } else {
+        stream_gemv(c, p.geo[kGateUp], lp.gate_up, policy);
+        stream_gemv(c, p.geo[kDown], lp.down, policy);
+      }
       if (c.dead || ld_relaxed(p.status + kStFired) != 0) return;
     }
     bulk_prefetch_l2(p.final_norm, norm_bytes);
@@ -700,6 +759,62 @@ __device__ __forceinline__ float silu_bf16(float g) {
   return bf16_round(g / (1.0f + expf(-g)));
 }
 
+// Tensor-parallel exchange of one column pair (row, row + 1) of batch row b: store this
+// rank's packet into every peer's receive region, poll this rank's own region for the
+// peers' packets, add the partials in ascending rank order. Not inlined: the loops and
+// their registers stay out of the GEMV path of unsharded plans
+// (include/tilemega/Backend/Sm90DenseEpilogue.h:43-86 keeps its Send/Finish out of line too).
+static __device__ __noinline__ float2 tp_all_reduce(const MegaParams& p, int ar_region, uint32_t epoch, int batch, int b, int n,
+                                             int row, uint32_t mine) {
+  const size_t half = size_t(n) >> 1;
+  const size_t region = size_t(ar_region) * p.tp_world * batch * half + (size_t(row) >> 1);
+  const unsigned long long packet = ((unsigned long long)epoch << 32) | mine;
+  for (int q = 0; q < p.tp_world; ++q)
+    if (q != p.tp_rank) st_relaxed_sys(p.ar[q] + region + (size_t(p.tp_rank) * batch + b) * half, packet);
+  float sx = 0.f, sy = 0.f;
+  for (int q = 0; q < p.tp_world; ++q) {
+    uint32_t bits = mine;
+    if (q != p.tp_rank) {
+      const unsigned long long* slot = p.ar[p.tp_rank] + region + (size_t(q) * batch + b) * half;
+      unsigned long long seen, t0 = 0;
+      uint32_t polls = 0;
+      while (uint32_t((seen = ld_relaxed_sys(slot)) >> 32) != epoch) {
+        if ((++polls & 63u) == 0 && wait_give_up(p, t0, kSitePeer, epoch, seen)) break;
+      }
+      bits = uint32_t(seen);
+    }
+    sx += bf_lo(bits);
+    sy += bf_hi(bits);
+  }
+  return make_float2(sx, sy);
+}
+
+// The lm_head winners of the ranks: CTA 0 sends this rank's (value, global index) of
+// batch row b to every peer as one packet {epoch 28 bits, bf16 value, 20-bit index};
+// lanes 0..tp_world-1 of the calling warp each fetch one rank's candidate. Returns the
+// candidate this lane holds (lanes past tp_world: none).
+static __device__ __noinline__ void tp_exchange_argmax(const MegaParams& p, unsigned long long epoch, int b, int lane,
+                                                float& value, int& index) {
+  if (blockIdx.x == 0 && lane < p.tp_world && lane != p.tp_rank) {
+    const unsigned long long packet =
+        (epoch << 36) | ((unsigned long long)bf16_bits(value) << 20) | (unsigned long long)(index & 0xfffff);
+    st_relaxed_sys(p.xchg[lane] + size_t(p.tp_rank) * kMaxBatch + b, packet);
+  }
+  if (lane < p.tp_world && lane != p.tp_rank) {
+    const unsigned long long* slot = p.xchg[p.tp_rank] + size_t(lane) * kMaxBatch + b;
+    unsigned long long seen, t0 = 0;
+    uint32_t polls = 0;
+    while (((seen = ld_relaxed_sys(slot)) >> 36) != epoch) {
+      if ((++polls & 63u) == 0 && wait_give_up(p, t0, kSitePeer, epoch, seen)) break;
+    }
+    value = bf16_from_bits(uint16_t(seen >> 20));
+    index = int(seen & 0xfffffull);
+  } else if (lane >= p.tp_world) {
+    value = -INFINITY;
+    index = 0x7fffffff;
+  }
+}
+
 // Everything the epilogue of one GEMV task needs, kept by the warp that owns it.
 // Output (batch row b, weight row r) of a task is handled by lane (b*8 + r) % 32 in
 // pass (b*8 + r) / 32: one pass up to batch 4, two up to batch 8.
@@ -716,7 +831,7 @@ struct PendingEpilogue {
 
 // Epilogue of one task, run by one warp: sum the eight warps' partial sums in warp
 // order, then apply the stage's rounding sites.
-template <int B>
+template <int B, bool X>
 __device__ __forceinline__ void gemv_epilogue(Ctx& c, const GemvGeo& geo, const GemvIo& io, const PendingEpilogue<B>& e,
                                               int lane, float (&best_val)[EpiPasses<B>::value],
                                               int (&best_idx)[EpiPasses<B>::value]) {
@@ -760,7 +875,7 @@ __device__ __forceinline__ void gemv_epilogue(Ctx& c, const GemvGeo& geo, const 
           best_val[pass] = bv;   // the 8 lanes of a sequence all hold its candidate
           best_idx[pass] = bi;
         }
-      } else if (io.epilogue == kEpiResidualAllReduce) {
+      } else if (X && io.epilogue == kEpiResidualAllReduce) {
         // Tensor parallel: every rank holds the sum over its own slice of the reduction.
         // The ranks exchange their sums rounded to bf16, two columns and the epoch per
         // 8-byte packet, stored straight into each peer's receive region; every rank
@@ -769,28 +884,8 @@ __device__ __forceinline__ void gemv_epilogue(Ctx& c, const GemvGeo& geo, const 
         const float vb1 = __shfl_down_sync(mask, vb, 1);
         const float res1 = __shfl_down_sync(mask, e.residual[pass], 1);
         if ((r & 1) == 0) {
-          const uint32_t mine = pack_bf16x2(vb, vb1);
-          const size_t half = size_t(geo.n) >> 1;
-          const size_t region = size_t(io.ar_region) * p.tp_world * B * half + (size_t(row) >> 1);
-          const unsigned long long packet = ((unsigned long long)io.ar_epoch << 32) | mine;
-          for (int q = 0; q < p.tp_world; ++q)
-            if (q != p.tp_rank) st_relaxed_sys(p.ar[q] + region + (size_t(p.tp_rank) * B + b) * half, packet);
-          float sx = 0.f, sy = 0.f;
-          for (int q = 0; q < p.tp_world; ++q) {
-            uint32_t bits = mine;
-            if (q != p.tp_rank) {
-              const unsigned long long* slot = p.ar[p.tp_rank] + region + (size_t(q) * B + b) * half;
-              unsigned long long seen, t0 = 0;
-              uint32_t polls = 0;
-              while (uint32_t((seen = ld_relaxed_sys(slot)) >> 32) != io.ar_epoch) {
-                if ((++polls & 63u) == 0 && wait_give_up(p, t0, kSitePeer, io.ar_epoch, seen)) break;
-              }
-              bits = uint32_t(seen);
-            }
-            sx += bf_lo(bits);
-            sy += bf_hi(bits);
-          }
-          const uint32_t pair = pack_bf16x2(bf16_round(sx) + e.residual[pass], bf16_round(sy) + res1);
+          const float2 sum = tp_all_reduce(p, io.ar_region, io.ar_epoch, B, b, geo.n, row, pack_bf16x2(vb, vb1));
+          const uint32_t pair = pack_bf16x2(bf16_round(sum.x) + e.residual[pass], bf16_round(sum.y) + res1);
           *reinterpret_cast<uint32_t*>(static_cast<__nv_bfloat16*>(io.out) + size_t(b) * geo.n + row) = pair;
         }
       } else {
@@ -815,7 +910,7 @@ __device__ __forceinline__ void gemv_epilogue(Ctx& c, const GemvGeo& geo, const 
   }
 }
 
-template <int B>
+template <int B, bool X>
 __device__ TMB_GEMV_CALL void gemv_stage(Ctx& c, const GemvGeo& geo, const GemvIo& io, bool tr, int stage) {
   const MegaParams& p = c.p;
   stage_rows<B>(c, io, geo.k, geo.k_src);
@@ -907,7 +1002,7 @@ __device__ TMB_GEMV_CALL void gemv_stage(Ctx& c, const GemvGeo& geo, const GemvI
     __syncwarp();
     if (lane == 0) mbar_arrive(c.pfull(buf));
     if (pending.task >= 0) {
-      gemv_epilogue<B>(c, geo, io, pending, lane, best_val, best_idx);
+      gemv_epilogue<B, X>(c, geo, io, pending, lane, best_val, best_idx);
       pending.task = -1;
     }
     if (owner) {
@@ -920,7 +1015,7 @@ __device__ TMB_GEMV_CALL void gemv_stage(Ctx& c, const GemvGeo& geo, const GemvI
     ++task_seq;
     ++gemv_seq;
   }
-  if (pending.task >= 0) gemv_epilogue<B>(c, geo, io, pending, lane, best_val, best_idx);
+  if (pending.task >= 0) gemv_epilogue<B, X>(c, geo, io, pending, lane, best_val, best_idx);
   c.slot = slot;
   c.phase = phase;
   c.task_seq = task_seq;
@@ -939,6 +1034,172 @@ __device__ TMB_GEMV_CALL void gemv_stage(Ctx& c, const GemvGeo& geo, const GemvI
 }
 
 // ---------------------------------------------------------------------------
+// arithmetic warps: mixture of experts (batch 1)
+// ---------------------------------------------------------------------------
+// Top-k routing of the one token, by warp 0: softmax in fp32 over the router's bf16
+// logits, the k largest probabilities in descending order (ties to the smaller expert
+// index), renormalised to sum 1 in fp32 (python/tilemega/moe/export.py:79-87). The result
+// goes to shared memory for both the arithmetic warps and the streaming thread, and from
+// CTA 0 to global memory for the host.
+static __device__ __noinline__ void route_token(Ctx& c, int layer) {
+  const MegaParams& p = c.p;
+  if (c.warp == 0) {
+    constexpr int kPerLane = 8;   // experts <= 256
+    const unsigned short* logits = reinterpret_cast<const unsigned short*>(p.router_logits);
+    float v[kPerLane];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < kPerLane; ++j) {
+      const int e = c.lane + 32 * j;
+      v[j] = e < p.experts ? bf16_from_bits(__ldcg(logits + e)) : -INFINITY;
+      mx = fmaxf(mx, v[j]);
+    }
+#pragma unroll
+    for (int m = 16; m; m >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, m));
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < kPerLane; ++j) {
+      v[j] = c.lane + 32 * j < p.experts ? expf(v[j] - mx) : 0.f;
+      sum += v[j];
+    }
+#pragma unroll
+    for (int m = 16; m; m >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, m);
+#pragma unroll
+    for (int j = 0; j < kPerLane; ++j) v[j] = c.lane + 32 * j < p.experts ? v[j] / sum : -1.f;
+    float chosen_w[kMaxTopK];
+    int chosen_e[kMaxTopK];
+    float total = 0.f;
+#pragma unroll
+    for (int s = 0; s < kMaxTopK; ++s) {
+      float bv = -1.f;
+      int bi = 0x7fffffff;
+      if (s < p.topk) {
+#pragma unroll
+        for (int j = 0; j < kPerLane; ++j)
+          if (v[j] > bv) { bv = v[j]; bi = c.lane + 32 * j; }   // ascending j: the smaller index wins a tie
+#pragma unroll
+        for (int m = 16; m; m >>= 1) {
+          const float ov = __shfl_xor_sync(0xffffffffu, bv, m);
+          const int oi = __shfl_xor_sync(0xffffffffu, bi, m);
+          if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+#pragma unroll
+        for (int j = 0; j < kPerLane; ++j)
+          if (c.lane + 32 * j == bi) v[j] = -1.f;   // taken
+        total += bv;
+      }
+      chosen_w[s] = bv;
+      chosen_e[s] = s < p.topk ? bi : 0;
+    }
+    if (c.lane == 0) {
+#pragma unroll
+      for (int s = 0; s < kMaxTopK; ++s) {
+        const float w = s < p.topk ? chosen_w[s] / total : 0.f;
+        c.route_e()[s] = chosen_e[s];
+        c.route_w()[s] = w;
+        if (blockIdx.x == 0 && s < p.topk) {
+          p.route_idx[layer * p.topk + s] = chosen_e[s];
+          p.route_w[layer * p.topk + s] = w;
+        }
+      }
+    }
+  }
+  consumer_sync();
+  if (c.tid == 0) mbar_arrive(c.route_bar());   // the streaming thread may start on the experts
+}
+
+// The chosen experts' down projections and their weighted sum, batch 1. Sub-task
+// (row tile, expert slot s) is one page; the activation row of slot s is that expert's
+// SwiGLU output. The warp that owns a row tile runs the epilogues of its topk sub-tasks
+// in slot order and keeps the running sum:
+//   y = bf16( sum_s fp32( bf16(W_s h_s) * w_s ) ), x += y
+// (python/tilemega/moe/export.py:29-37: expert outputs in the model dtype, times the fp32
+// routing weight, summed over the ranks in fp32, one rounding; then the layer's residual add).
+template <int B>
+__device__ __noinline__ void moe_down_stage(Ctx& c, const GemvGeo& geo, bool tr, int stage) {
+  static_assert(B == 1, "mixture-of-experts plans run batch 1");
+  const MegaParams& p = c.p;
+  const int topk = p.topk;
+  const int pitch_bytes = (geo.k + 8) * 2;
+  {
+    // rows: h[slot][k_src] -> shared memory in A-fragment order, pad columns zero
+    const int chunks = geo.k >> 3, src_chunks = geo.k_src >> 3;
+    for (int slot = 0; slot < topk; ++slot) {
+      const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.h) + size_t(slot) * geo.k_src);
+      uint32_t* row = reinterpret_cast<uint32_t*>(c.xs() + size_t(slot) * pitch_bytes);
+      for (int i = c.tid; i < chunks; i += kConsumerThreads)
+        store_row_chunk(row, i, i < src_chunks ? __ldcg(src + i) : make_uint4(0u, 0u, 0u, 0u));
+    }
+    consumer_sync();
+  }
+  trace_mark(c, tr, stage, 2);
+  float* red = c.red();
+  uint32_t slot = c.slot, phase = c.phase, gemv_seq = c.gemv_seq;
+  const int warp = c.warp, lane = c.lane;
+  const uint32_t nslots = uint32_t(p.nslots);
+  unsigned char* const ring0 = c.ring(0);
+  uint64_t* const full0 = c.full(0);
+  uint64_t* const empty0 = c.empty(0);
+  uint32_t sub_seq = 0;        // sub-tasks seen by this CTA in this stage
+  int pending_task = -1, pending_buf = 0;
+  uint32_t pending_lap = 0;
+  float running = 0.f, residual = 0.f;
+  auto epilogue = [&]() {
+    mbar_wait_warp(c, c.pfull(pending_buf), pending_lap, kSiteFull);
+    const int tile = pending_task / topk, s = pending_task - tile * topk;
+    if (lane < kTileN) {
+      float v = 0.f;
+#pragma unroll
+      for (int w = 0; w < kConsumerWarps; ++w) v += red[(pending_buf * 8 + w) * 8 + lane];
+      running = __fadd_rn(running, __fmul_rn(bf16_round(v), c.route_w()[s]));
+      if (s == topk - 1) {
+        static_cast<__nv_bfloat16*>(p.x)[tile * kTileN + lane] = __float2bfloat16_rn(bf16_round(running) + residual);
+        running = 0.f;
+      }
+    }
+    pending_task = -1;
+  };
+  for (int t = fifo_pop(c); t >= 0; t = fifo_pop(c)) {
+    const int tile = t / topk, s = t - tile * topk;
+    const bool owner = warp == int((sub_seq / uint32_t(topk)) & 7u);
+    if (owner && s == 0 && lane < kTileN)
+      residual = bf16_from_bits(__ldcg(reinterpret_cast<const unsigned short*>(p.x) + tile * kTileN + lane));
+    float d[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) d[0][i] = d[1][i] = d[2][i] = d[3][i] = 0.f;
+    mbar_wait_warp(c, full0 + slot, phase, kSiteFull);
+    if (256 * warp < geo.k_src)
+      gemv_page_mma<1>(ring0 + slot * kSlotBytes, c.xs() + size_t(s) * pitch_bytes, geo.k, 0, warp, lane, d);
+    __syncwarp();
+    if (lane == 0) mbar_arrive(empty0 + slot);
+    if (++slot == nslots) { slot = 0; phase ^= 1u; }
+    const int buf = gemv_seq & (kPartialRing - 1);
+    const uint32_t lap = (gemv_seq / kPartialRing) & 1u;
+    if ((lane >> 2) < 1) {   // lane q of row 0 holds weight rows 2q, 2q+1
+      float* dst = red + (buf * 8 + warp) * 8 + 2 * (lane & 3);
+      dst[0] = (d[0][0] + d[1][0]) + (d[2][0] + d[3][0]);
+      dst[1] = (d[0][1] + d[1][1]) + (d[2][1] + d[3][1]);
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(c.pfull(buf));
+    if (pending_task >= 0) epilogue();
+    if (owner) {
+      pending_task = t;
+      pending_buf = buf;
+      pending_lap = lap;
+    }
+    ++sub_seq;
+    ++gemv_seq;
+  }
+  if (pending_task >= 0) epilogue();
+  c.slot = slot;
+  c.phase = phase;
+  c.gemv_seq = gemv_seq;
+  c.task_seq += sub_seq;
+  trace_mark(c, tr, stage, 3);
+}
+
+// ---------------------------------------------------------------------------
 // arithmetic warps: RoPE + KV append + split-KV decode attention
 //
 // KV rows are stored (in either cache layout) with their 16-byte chunks XOR-ed by
@@ -949,7 +1210,7 @@ __device__ TMB_GEMV_CALL void gemv_stage(Ctx& c, const GemvGeo& geo, const GemvI
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ int kv_swizzled(int d, int pos) { return ((((d >> 3) ^ (pos & 7))) << 3) | (d & 7); }
 
-template <int B, int D, int GQ>
+template <int B, int D, int GQ, bool X>
 __device__ void attn_stage(Ctx& c, const LayerPtrs& lp, int past, bool tr, int stage, unsigned long long qkv_stages) {
   constexpr int NK = kAttnHalfBytes / (2 * D);  // keys per slot: 64 (D=128) / 128 (D=64)
   constexpr int KW = NK / kConsumerWarps;       // keys per warp per slot: 8 / 16
@@ -963,6 +1224,7 @@ __device__ void attn_stage(Ctx& c, const LayerPtrs& lp, int past, bool tr, int s
   __nv_bfloat16* knew = qs + GQ * D;                                     // [D] roped new key
   __nv_bfloat16* vnew = knew + D;                                        // [D] new value
   float* scratch = reinterpret_cast<float*>(vnew + D);                   // [8 warps][GQ][PW]
+  __nv_bfloat16* qkn = reinterpret_cast<__nv_bfloat16*>(scratch + kConsumerWarps * GQ * PW);   // [GQ + 1][D] normalised q, k (QK norm)
   const int qkv_width = (p.heads + 2 * p.kv_heads) * D;
   const __nv_bfloat16* cosb = static_cast<const __nv_bfloat16*>(p.rope_cos);
   const __nv_bfloat16* sinb = static_cast<const __nv_bfloat16*>(p.rope_sin);
@@ -992,9 +1254,33 @@ __device__ void attn_stage(Ctx& c, const LayerPtrs& lp, int past, bool tr, int s
       const long long e = table_entry(p, a.b, a.pos / kKvBlock);
       new_off = e * p.kv_block_stride + (long long)a.g * p.kv_head_stride + (a.pos % kKvBlock) * D;
     }
+    const bool qk_norm = X && lp.q_norm != nullptr;   // X: the instantiation that carries the Qwen3 / mixture-of-experts code
+    if (qk_norm) {
+      // Qwen3: every query head and the key head are RMS-normalised over their own D
+      // values before RoPE, y = w * bf16(x * rsqrt(mean x^2 + eps)), the product rounded
+      // to bf16 (python/tilemega/serving/export.py:63-65,82-84). One warp per head.
+      for (int hh = c.warp; hh < GQ + 1; hh += kConsumerWarps) {
+        const unsigned short* wn = reinterpret_cast<const unsigned short*>(hh < GQ ? lp.q_norm : lp.k_norm);
+        float xv[D / 32], ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < D / 32; ++j) {
+          xv[j] = bf16_from_bits(__ldcg(row + hh * D + c.lane + 32 * j));
+          ss = fmaf(xv[j], xv[j], ss);
+        }
+#pragma unroll
+        for (int m = 16; m; m >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
+        const float inv = 1.0f / sqrtf(ss / float(D) + p.eps);
+#pragma unroll
+        for (int j = 0; j < D / 32; ++j) {
+          const float w = bf16_from_bits(__ldg(wn + c.lane + 32 * j));
+          qkn[hh * D + c.lane + 32 * j] = __float2bfloat16_rn(w * bf16_round(xv[j] * inv));
+        }
+      }
+      consumer_sync();
+    }
     for (int e = c.tid; e < (GQ + 2) * D; e += kConsumerThreads) {
       const int hh = e / D, d = e - hh * D;
-      const float xv = bf16_from_bits(__ldcg(row + e));
+      const float xv = qk_norm && hh <= GQ ? __bfloat162float(qkn[e]) : bf16_from_bits(__ldcg(row + e));
       if (hh == GQ + 1) {
         if (tail) {
           vnew[d] = __float2bfloat16_rn(xv);
@@ -1004,7 +1290,7 @@ __device__ void attn_stage(Ctx& c, const LayerPtrs& lp, int past, bool tr, int s
       }
       if (hh == GQ && !tail) continue;
       const int d2 = d < D / 2 ? d + D / 2 : d - D / 2;
-      const float xp = bf16_from_bits(__ldcg(row + hh * D + d2));
+      const float xp = qk_norm ? __bfloat162float(qkn[hh * D + d2]) : bf16_from_bits(__ldcg(row + hh * D + d2));
       const float cs = __bfloat162float(cosb[size_t(a.pos) * D + d]);
       const float sn = __bfloat162float(sinb[size_t(a.pos) * D + d]);
       const float rot = d < D / 2 ? -xp : xp;
@@ -1225,7 +1511,7 @@ __device__ void attn_stage(Ctx& c, const LayerPtrs& lp, int past, bool tr, int s
 // ---------------------------------------------------------------------------
 // arithmetic warps: one decode step after another
 // ---------------------------------------------------------------------------
-template <int B, int D, int GQ>
+template <int B, int D, int GQ, bool X>
 __device__ void consumer_main(Ctx& c) {
   const MegaParams& p = c.p;
   for (int si = 0; si < p.nsteps; ++si) {
@@ -1242,7 +1528,7 @@ __device__ void consumer_main(Ctx& c) {
     int stage = 0;
     LayerPtrs lp = p.layer[0];
     // tensor parallel: o and down end in an all-reduce; epochs count all-reduces since the plan was made
-    const int residual_kind = p.tp_world > 1 ? kEpiResidualAllReduce : kEpiResidual;
+    const int residual_kind = X && p.tp_world > 1 ? kEpiResidualAllReduce : kEpiResidual;
     const unsigned long long steps_before = p.tp_steps + (unsigned long long)si;
     const uint32_t ar_epoch0 = uint32_t(steps_before * (unsigned long long)(2 * p.layers)) + 1u;
     for (int l = 0; l < p.layers; ++l) {
@@ -1256,30 +1542,54 @@ __device__ void consumer_main(Ctx& c) {
       }
       trace_mark(c, tr, stage, 1);
       io = GemvIo{l == 0 ? p.embed : p.x, lp.norm1, l == 0, kEpiStore, p.qkv, p.qkv_ready, (GQ + 2) * D / kTileN, 0, 0u};
-      gemv_stage<B>(c, p.geo[kQkv], io, tr, stage++);
+      gemv_stage<B, X>(c, p.geo[kQkv], io, tr, stage++);
       // no grid barrier here: an attention task needs the QKV rows of its own KV head
       // only, and waits for that group's row-tile count (qkv_ready)
       trace_mark(c, tr, stage, 0);
       trace_mark(c, tr, stage, 1);
-      attn_stage<B, D, GQ>(c, lp, past, tr, stage++, (unsigned long long)(si * p.layers + l + 1));
+      attn_stage<B, D, GQ, X>(c, lp, past, tr, stage++, (unsigned long long)(si * p.layers + l + 1));
       grid_arrive(c);
       trace_mark(c, tr, stage, 0);
       if (!grid_wait(c)) return;
       trace_mark(c, tr, stage, 1);
       io = GemvIo{p.attn, nullptr, 0, residual_kind, p.x, nullptr, 1, 0, ar_epoch0 + uint32_t(2 * l)};
-      gemv_stage<B>(c, p.geo[kOProj], io, tr, stage++);
+      gemv_stage<B, X>(c, p.geo[kOProj], io, tr, stage++);
       grid_arrive(c);
       trace_mark(c, tr, stage, 0);
       if (!grid_wait(c)) return;
       trace_mark(c, tr, stage, 1);
+      if (X && p.experts) {
+        // mixture of experts: router scores, top-k, then the chosen experts only
+        if constexpr (X && B == 1) {
+          io = GemvIo{p.x, lp.norm2, 0, kEpiStore, p.router_logits, nullptr, 1, 0, 0u};
+          gemv_stage<B, X>(c, p.geo[kRouter], io, tr, stage++);
+          grid_arrive(c);
+          trace_mark(c, tr, stage, 0);
+          if (!grid_wait(c)) return;
+          trace_mark(c, tr, stage, 1);
+          route_token(c, l);
+          // task t = (expert slot, row tile): with one token the SwiGLU epilogue's output
+          // index t * 4 + r is row `slot` of h[topk][inter]
+          io = GemvIo{p.x, lp.norm2, 0, kEpiSwiGLU, p.h, nullptr, 1, 0, 0u};
+          gemv_stage<B, X>(c, p.geo[kGateUp], io, tr, stage++);
+          grid_arrive(c);
+          trace_mark(c, tr, stage, 0);
+          if (!grid_wait(c)) return;
+          trace_mark(c, tr, stage, 1);
+          moe_down_stage<B>(c, p.geo[kDown], tr, stage++);
+          grid_arrive(c);
+        }
+        lp = upcoming;
+        continue;
+      }
       io = GemvIo{p.x, lp.norm2, 0, kEpiSwiGLU, p.h, nullptr, 1, 0, 0u};
-      gemv_stage<B>(c, p.geo[kGateUp], io, tr, stage++);
+      gemv_stage<B, X>(c, p.geo[kGateUp], io, tr, stage++);
       grid_arrive(c);
       trace_mark(c, tr, stage, 0);
       if (!grid_wait(c)) return;
       trace_mark(c, tr, stage, 1);
       io = GemvIo{p.h, nullptr, 0, residual_kind, p.x, nullptr, 1, 1, ar_epoch0 + uint32_t(2 * l + 1)};
-      gemv_stage<B>(c, p.geo[kDown], io, tr, stage++);
+      gemv_stage<B, X>(c, p.geo[kDown], io, tr, stage++);
       grid_arrive(c);
       lp = upcoming;
     }
@@ -1287,7 +1597,7 @@ __device__ void consumer_main(Ctx& c) {
     if (!grid_wait(c)) return;
     trace_mark(c, tr, stage, 1);
     GemvIo io{p.x, p.final_norm, 0, kEpiHead, p.logits, nullptr, 1, 0, 0u};
-    gemv_stage<B>(c, p.geo[kHead], io, tr, stage);
+    gemv_stage<B, X>(c, p.geo[kHead], io, tr, stage);
     consumer_sync();
     if (c.tid < B) {
       float bv = -INFINITY;
@@ -1320,33 +1630,15 @@ __device__ void consumer_main(Ctx& c) {
         const int oi = __shfl_xor_sync(0xffffffffu, bi, mk);
         if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
       }
-      if (p.tp_world > 1) {
+      if (X && p.tp_world > 1) {
         // Each rank scored a slice of the vocabulary: CTA 0 sends its winner (the compared
         // value is a bf16, the index fits 20 bits, so one packet holds both and a 28-bit
         // epoch) into every peer's block; every CTA then takes the best over the ranks in
         // ascending order, which is the whole-vocabulary argmax with ties to the smaller
         // index (include/tilemega/Backend/Sm90DenseHead.cuh:139-201).
-        const unsigned long long epoch = (steps_before + 1ull) & 0xfffffffull;
-        if (blockIdx.x == 0 && c.lane < p.tp_world && c.lane != p.tp_rank) {
-          const unsigned long long packet =
-              (epoch << 36) | ((unsigned long long)bf16_bits(bv) << 20) | (unsigned long long)(bi & 0xfffff);
-          st_relaxed_sys(p.xchg[c.lane] + size_t(p.tp_rank) * kMaxBatch + b, packet);
-        }
         float ov = bv;
         int oi = bi;
-        if (c.lane < p.tp_world && c.lane != p.tp_rank) {
-          const unsigned long long* slot = p.xchg[p.tp_rank] + size_t(c.lane) * kMaxBatch + b;
-          unsigned long long seen, t0 = 0;
-          uint32_t polls = 0;
-          while (((seen = ld_relaxed_sys(slot)) >> 36) != epoch) {
-            if ((++polls & 63u) == 0 && wait_give_up(p, t0, kSitePeer, epoch, seen)) break;
-          }
-          ov = bf16_from_bits(uint16_t(seen >> 20));
-          oi = int(seen & 0xfffffull);
-        } else if (c.lane >= p.tp_world) {
-          ov = -INFINITY;
-          oi = 0x7fffffff;
-        }
+        tp_exchange_argmax(p, (steps_before + 1ull) & 0xfffffffull, b, c.lane, ov, oi);
 #pragma unroll
         for (int mk = 4; mk; mk >>= 1) {   // tp_world <= 8: lanes 0..7 hold the ranks' candidates
           const float pv = __shfl_xor_sync(0xffffffffu, ov, mk);
@@ -1373,7 +1665,7 @@ __device__ void consumer_main(Ctx& c) {
   }
 }
 
-template <int B, int D, int GQ>
+template <int B, int D, int GQ, bool X>
 __global__ void __launch_bounds__(kThreads, 1) decode_megakernel(const __grid_constant__ MegaParams p) {
   extern __shared__ __align__(1024) unsigned char smem[];
   Ctx c(p, smem);
@@ -1385,6 +1677,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_megakernel(const __grid_co
     for (int i = 0; i < kPartialRing; ++i) {
       mbar_init(c.pfull(i), kConsumerWarps);
     }
+    mbar_init(c.route_bar(), 1);
     mbar_fence_init();
     for (int i = 0; i < 8; ++i) c.ctl()[i] = 0;
     for (int i = 0; i < kFifo; ++i) c.fifo()[i] = 0;   // sequence tag 0 never matches
@@ -1392,14 +1685,15 @@ __global__ void __launch_bounds__(kThreads, 1) decode_megakernel(const __grid_co
   __syncthreads();
   if (c.warp >= kConsumerWarps) {
     if (c.lane == 0) {
-      streamer_main<D>(c);
+      streamer_main<D, X>(c);
       streamer_drain(c);
     }
   } else {
-    consumer_main<B, D, GQ>(c);
+    consumer_main<B, D, GQ, X>(c);
   }
 }
 
+#if !TMB_EXTENDED
 // A two-CTA toy that exercises the bounded-wait path without hanging anything:
 // CTA 1 waits for an arrival CTA 0 is told to withhold; the wait gives up after
 // watchdog_ns, records the site and both CTAs return normally.
@@ -1416,9 +1710,11 @@ __global__ void watchdog_probe_kernel(MegaParams p, int withhold) {
   }
 }
 
-template <int B, int D, int GQ>
+#endif
+
+template <int B, int D, int GQ, bool X>
 static cudaError_t run_instance(const MegaParams& p, size_t smem_bytes, cudaStream_t stream, bool prepare) {
-  auto kernel = decode_megakernel<B, D, GQ>;
+  auto kernel = decode_megakernel<B, D, GQ, X>;
   if (prepare) {
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem_bytes));
     if (err != cudaSuccess) return err;
@@ -1436,34 +1732,54 @@ static cudaError_t run_instance(const MegaParams& p, size_t smem_bytes, cudaStre
   return cudaGetLastError();
 }
 
-template <int D, int GQ>
+template <int D, int GQ, bool X>
 static cudaError_t run_batch(const MegaParams& p, size_t smem_bytes, cudaStream_t stream, bool prepare) {
   switch (p.batch) {
-    case 1: return run_instance<1, D, GQ>(p, smem_bytes, stream, prepare);
-    case 2: return run_instance<2, D, GQ>(p, smem_bytes, stream, prepare);
-    case 3: return run_instance<3, D, GQ>(p, smem_bytes, stream, prepare);
-    case 4: return run_instance<4, D, GQ>(p, smem_bytes, stream, prepare);
-    case 5: return run_instance<5, D, GQ>(p, smem_bytes, stream, prepare);
-    case 6: return run_instance<6, D, GQ>(p, smem_bytes, stream, prepare);
-    case 7: return run_instance<7, D, GQ>(p, smem_bytes, stream, prepare);
-    case 8: return run_instance<8, D, GQ>(p, smem_bytes, stream, prepare);
+    case 1: return run_instance<1, D, GQ, X>(p, smem_bytes, stream, prepare);
+    case 2: return run_instance<2, D, GQ, X>(p, smem_bytes, stream, prepare);
+    case 3: return run_instance<3, D, GQ, X>(p, smem_bytes, stream, prepare);
+    case 4: return run_instance<4, D, GQ, X>(p, smem_bytes, stream, prepare);
+    case 5: return run_instance<5, D, GQ, X>(p, smem_bytes, stream, prepare);
+    case 6: return run_instance<6, D, GQ, X>(p, smem_bytes, stream, prepare);
+    case 7: return run_instance<7, D, GQ, X>(p, smem_bytes, stream, prepare);
+    case 8: return run_instance<8, D, GQ, X>(p, smem_bytes, stream, prepare);
     default: return cudaErrorInvalidValue;
   }
 }
 
+// The kernel is instantiated in two translation units (compiled side by side): the plain
+// one serves unsharded dense plans and carries none of the code below; the extended one
+// (TMB_EXTENDED) adds tensor parallelism, mixture of experts and the QK norm, for
+// head_dim 128.
+#if TMB_EXTENDED
+cudaError_t run_decode_extended(const MegaParams& p, cudaStream_t stream, bool prepare) {
+  const size_t smem_bytes = size_t(ring_offset(p.xs_bytes, p.batch) + p.nslots * kSlotBytes);
+  if (p.kv_heads <= 0 || p.heads % p.kv_heads || p.head_dim != 128) return cudaErrorInvalidValue;
+  const int gq = p.heads / p.kv_heads;
+  if ((p.experts > 0 || p.qk_norm) && p.batch != 1) return cudaErrorInvalidValue;
+  if (gq == 8) return run_batch<128, 8, true>(p, smem_bytes, stream, prepare);
+  if (gq == 4) return run_batch<128, 4, true>(p, smem_bytes, stream, prepare);
+  return cudaErrorInvalidValue;
+}
+#else
+cudaError_t run_decode_extended(const MegaParams& p, cudaStream_t stream, bool prepare);
+
 static cudaError_t run_decode(const MegaParams& p, cudaStream_t stream, bool prepare) {
+  if (p.tp_world > 1 || p.experts > 0 || p.qk_norm) return run_decode_extended(p, stream, prepare);
   const size_t smem_bytes = size_t(ring_offset(p.xs_bytes, p.batch) + p.nslots * kSlotBytes);
   if (p.kv_heads <= 0 || p.heads % p.kv_heads) return cudaErrorInvalidValue;
   const int gq = p.heads / p.kv_heads;
-  if (p.head_dim == 128 && gq == 8) return run_batch<128, 8>(p, smem_bytes, stream, prepare);
+  if (p.head_dim == 128 && gq == 8) return run_batch<128, 8, false>(p, smem_bytes, stream, prepare);
   if (gq != 4) return cudaErrorInvalidValue;
-  if (p.head_dim == 128) return run_batch<128, 4>(p, smem_bytes, stream, prepare);
-  if (p.head_dim == 64) return run_batch<64, 4>(p, smem_bytes, stream, prepare);
+  if (p.head_dim == 128) return run_batch<128, 4, false>(p, smem_bytes, stream, prepare);
+  if (p.head_dim == 64) return run_batch<64, 4, false>(p, smem_bytes, stream, prepare);
   return cudaErrorInvalidValue;
 }
+#endif
 
 }  // namespace tmb
 
+#if !TMB_EXTENDED
 extern "C" int tmb_smem_bytes(const tmb::MegaParams* p) {
   return tmb::ring_offset(p->xs_bytes, p->batch) + p->nslots * tmb::kSlotBytes;
 }
@@ -1480,3 +1796,4 @@ extern "C" int tmb_launch_watchdog_probe(const tmb::MegaParams* p, int withhold,
   tmb::watchdog_probe_kernel<<<2, 32, 0, static_cast<cudaStream_t>(stream)>>>(*p, withhold);
   return int(cudaGetLastError());
 }
+#endif

@@ -17,7 +17,9 @@ constexpr int kPartialRing = 8;                         // GEMV tasks whose warp
 constexpr int kAttnHalfBytes = kSlotBytes / 2;          // K part, then V part, of an attention slot
 constexpr int kMaxTp = 8;                               // tensor-parallel ranks of one plan
 
-enum StageKind : int { kQkv = 0, kOProj = 1, kGateUp = 2, kDown = 3, kHead = 4, kNumGemv = 5 };
+// kRouter exists in mixture-of-experts plans only; there kGateUp / kDown describe ONE expert.
+enum StageKind : int { kQkv = 0, kOProj = 1, kGateUp = 2, kDown = 3, kHead = 4, kRouter = 5, kNumGemv = 6 };
+constexpr int kMaxTopK = 8;                             // experts per token
 // kEpiResidualAllReduce: kEpiResidual after the ranks' bf16 partial sums are added in rank order.
 enum Epilogue : int { kEpiStore = 0, kEpiResidual = 1, kEpiSwiGLU = 2, kEpiHead = 3, kEpiResidualAllReduce = 4 };
 
@@ -41,6 +43,9 @@ struct LayerPtrs {
   const void* down;
   const void* norm1;     // bf16 [H]
   const void* norm2;     // bf16 [H]
+  const void* router;    // packed pages [E/8][H/tile_k] (mixture of experts), else null
+  const void* q_norm;    // bf16 [D] per-head RMSNorm weights applied before RoPE (Qwen3), else null
+  const void* k_norm;
   void* k_pool;          // bf16, addressed by block table
   void* v_pool;
 };
@@ -60,6 +65,11 @@ struct MegaParams {
   // whole vocabulary, of which this rank's head scores rows [head_base, head_base + geo[kHead].n))
   int batch, hidden, inter, heads, kv_heads, head_dim, layers, vocab;
   int head_base;
+  // mixture of experts (experts == 0: dense MLP). gate_up / down of a layer are stacks of
+  // `experts` packed matrices; geo[kGateUp] / geo[kDown] describe one of them.
+  int experts, topk, norm_topk;
+  int qk_norm;              // per-head RMSNorm of q and k before RoPE (Qwen3)
+  int stages_per_layer;     // 5 dense, 6 with a router stage
   float eps;
   float qk_scale_log2;      // log2(e) / sqrt(head_dim)
   // request state
@@ -91,6 +101,9 @@ struct MegaParams {
   void* attn;                  // bf16 [B][Hq*D]
   void* h;                     // bf16 [B][I]
   void* logits;                // f32 [B][V]: head accumulators before the bf16 rounding
+  void* router_logits;         // bf16 [B][experts]
+  int* route_idx;              // [layers][topk] chosen experts of the last step, in rank order (batch 1)
+  float* route_w;              // [layers][topk] their routing weights
   float* attn_part;            // [grid + B*Hkv][Gq][D+2]
   unsigned* attn_cnt;          // [B*Hkv]
   unsigned long long* qkv_ready;  // [Hkv] QKV row tiles stored per KV-head group (monotonic within a launch)

@@ -74,7 +74,8 @@ int PlanSpec::max_k() const {
 uint64_t PlanSpec::weight_bytes() const {
   uint64_t total = 0;
   for (int s = 0; s < kNumGemv; ++s) {
-    const uint64_t one = 2ull * uint64_t(geo[s].n) * uint64_t(geo[s].k_src);
+    uint64_t one = 2ull * uint64_t(geo[s].n) * uint64_t(geo[s].k_src);
+    if (experts && (s == kGateUp || s == kDown)) one *= uint64_t(topk) * uint64_t(batch_hi);   // experts routed to per step
     total += s == kHead ? one : one * uint64_t(layers);
   }
   return total;
@@ -93,6 +94,22 @@ PlanSpec PlanSpec::FromJson(const Json& plan) {
   s.head_dim = int(model.integer("head_dim", s.heads ? s.hidden / s.heads : 0));
   s.eps = model.num("rms_norm_eps", 1e-5);
   s.tied = model.flag("tie_word_embeddings", false);
+  // mixture of experts (python/tilemega/moe/export.py:54-93): top-k of a softmax router,
+  // expert SwiGLU FFNs of moe_intermediate_size; Qwen3 also normalises every q/k head
+  s.experts = int(model.integer("num_experts", 0));
+  if (s.experts) {
+    s.topk = int(model.integer("num_experts_per_tok", 0));
+    s.norm_topk = model.flag("norm_topk_prob", false);
+    s.inter = int(model.integer("moe_intermediate_size", s.inter));
+    if (s.experts % kTileN || s.experts > 256) throw std::invalid_argument("experts must be a multiple of 8, at most 256");
+    if (s.topk < 1 || s.topk > kMaxTopK || s.topk > s.experts) throw std::invalid_argument("experts per token must lie in [1, 8]");
+    if (!s.norm_topk) throw std::invalid_argument("only renormalised top-k routing (norm_topk_prob) is built");
+  }
+  if (model.has("architectures")) {
+    const Json& arch = model.at("architectures");
+    s.qk_norm = arch.kind == Json::kArray && !arch.items.empty() && arch.items[0].kind == Json::kString &&
+                arch.items[0].text.rfind("Qwen3", 0) == 0;
+  }
   if (s.hidden <= 0 || s.inter <= 0 || s.heads <= 0 || s.kv_heads <= 0 || s.layers <= 0 || s.vocab <= 0)
     throw std::invalid_argument("model dimensions must be positive");
   if (s.head_dim != 64 && s.head_dim != 128) throw std::invalid_argument("head_dim must be 64 or 128");
@@ -110,10 +127,15 @@ PlanSpec PlanSpec::FromJson(const Json& plan) {
   s.kv_heads /= s.tp;
   s.inter /= s.tp;
   s.head_rows = s.vocab / s.tp;
+  if (s.tp > 1 && s.head_dim != 128) throw std::invalid_argument("tensor-parallel plans are built for head_dim 128");
+  if ((s.experts || s.qk_norm) && s.head_dim != 128)
+    throw std::invalid_argument("mixture-of-experts / QK-norm plans are built for head_dim 128");
   if (s.tp > 1 && s.hidden % 2) throw std::invalid_argument("hidden size must be even for the all-reduce packets");
   if (s.tp > 1 && s.vocab > (1 << 20)) throw std::invalid_argument("the argmax exchange packet holds 20 index bits");
+  if (s.experts && s.tp != 1) throw std::invalid_argument("tensor parallel mixture of experts is not built");
   s.batch_lo = int(plan.integer("batch_lo", 1));
   s.batch_hi = int(plan.integer("batch_hi", s.batch_lo));
+  if (s.experts && s.batch_hi != 1) throw std::invalid_argument("mixture-of-experts plans are built for batch 1");
   s.capacity = int(plan.integer("capacity", 0));
   if (s.batch_lo < 1 || s.batch_hi < s.batch_lo || s.batch_hi > kMaxBatch)
     throw std::invalid_argument("batch interval must lie in [1, 8]");
@@ -140,6 +162,11 @@ PlanSpec PlanSpec::FromJson(const Json& plan) {
   s.geo[kGateUp] = MakeGeo("gate_up", 2 * s.inter, s.hidden, geometry);
   s.geo[kDown] = MakeGeo("down", s.hidden, s.inter, geometry);
   s.geo[kHead] = MakeGeo("lm_head", s.head_rows, s.hidden, geometry);
+  if (s.experts) {
+    s.geo[kRouter] = MakeGeo("router", s.experts, s.hidden, geometry);
+    if (s.geo[kDown].pages_per_task != 1)
+      throw std::invalid_argument("expert intermediate size must fit one 2048-column page");
+  }
 
   auto add = [&](std::string name, uint32_t role, uint32_t dtype, uint64_t constant, uint64_t per_batch,
                  std::string recipe) {
@@ -165,7 +192,14 @@ PlanSpec PlanSpec::FromJson(const Json& plan) {
   s.hidden_buf = add("serving.hidden", 0, 0, 0, H, "");
   s.qkv_buf = add("serving.qkv", 0, 0, 0, uint64_t(s.qkv_rows()), "");
   s.attn_buf = add("serving.attention", 0, 0, 0, uint64_t(s.heads) * D, "");
-  s.mlp_buf = add("serving.mlp", 0, 0, 0, I, "");
+  // with experts: one row per chosen expert (batch 1)
+  s.mlp_buf = add("serving.mlp", 0, 0, 0, s.experts ? I * uint64_t(s.topk) : I, "");
+  if (s.experts) {
+    s.router_buf = add("serving.router_logits", 0, 0, 0, uint64_t(s.experts), "");
+    // the experts chosen by the last step and their weights, [layers][topk] (batch 1)
+    s.route_idx_buf = add("serving.route_index", 0, 2, uint64_t(s.layers) * s.topk, 0, "");
+    s.route_weight_buf = add("serving.route_weight", 0, 1, uint64_t(s.layers) * s.topk, 0, "");
+  }
   s.logits_buf = add("serving.logits", 0, 1, 0, uint64_t(s.head_rows), "");  // fp32 accumulators of this rank's head rows
   for (int l = 0; l < s.layers; ++l) {
     const std::string p = "l" + std::to_string(l) + ".";
@@ -191,6 +225,27 @@ PlanSpec PlanSpec::FromJson(const Json& plan) {
     lb.o = add(p + "o.weight", 1, 0, uint64_t(s.geo[kOProj].n) * s.geo[kOProj].k, 0,
                Pages(Alias(m + "self_attn.o_proj.weight", Shard(1, s.tp)), s.geo[kOProj].tile_k));
     lb.norm2 = add(p + "norm2.weight", 1, 0, H, 0, Alias(m + "post_attention_layernorm.weight"));
+    if (s.qk_norm) {
+      lb.q_norm = add(p + "q_norm.weight", 1, 0, D, 0, Alias(m + "self_attn.q_norm.weight"));
+      lb.k_norm = add(p + "k_norm.weight", 1, 0, D, 0, Alias(m + "self_attn.k_norm.weight"));
+    }
+    if (s.experts) {
+      // the reference's expert_stack recipe (python/tilemega/moe/weights.py:15-47): every
+      // expert packed by itself, the packed experts one after the other
+      auto stack = [&](const char* part) {
+        return "{\"kind\":\"expert_stack\",\"prefix\":" + Json::Quote(m + "mlp.experts.") + ",\"part\":\"" + part +
+               "\",\"experts\":" + std::to_string(s.experts) + ",\"hidden\":" + std::to_string(s.hidden) +
+               ",\"intermediate\":" + std::to_string(s.inter) + ",\"u\":4}";
+      };
+      lb.router = add(p + "router.weight", 1, 0, uint64_t(s.geo[kRouter].n) * s.geo[kRouter].k, 0,
+                      Pages(Alias(m + "mlp.gate.weight"), s.geo[kRouter].tile_k));
+      lb.gate_up = add(p + "gate_up.weight", 1, 0, uint64_t(s.experts) * s.geo[kGateUp].n * s.geo[kGateUp].k, 0,
+                       Pages(stack("gate_up"), s.geo[kGateUp].tile_k));
+      lb.down = add(p + "down.weight", 1, 0, uint64_t(s.experts) * s.geo[kDown].n * s.geo[kDown].k, 0,
+                    Pages(stack("down"), s.geo[kDown].tile_k));
+      s.layer.push_back(lb);
+      continue;
+    }
     const std::string gate_up_source = "{\"kind\":\"gate_up_interleave\",\"sources\":" +
                                        Sources({m + "mlp.gate_proj.weight", m + "mlp.up_proj.weight"}) +
                                        ",\"u\":4" + Shard(0, s.tp) + "}";

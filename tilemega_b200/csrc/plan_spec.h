@@ -24,7 +24,7 @@ struct BufferSpec {
 
 // Index of the buffers the runtime binds, into PlanSpec::buffers.
 struct LayerBuffers {
-  int norm1, qkv, k, v, o, norm2, gate_up, down;
+  int norm1, qkv, k, v, o, norm2, gate_up, down, router = -1, q_norm = -1, k_norm = -1;
 };
 
 struct PlanSpec {
@@ -33,6 +33,9 @@ struct PlanSpec {
   // sharding as in python/tilemega/serving/export.py:39-47,107-112,152-163)
   int hidden = 0, inter = 0, heads = 0, kv_heads = 0, head_dim = 0, layers = 0, vocab = 0;
   int tp = 1, head_rows = 0;
+  // mixture of experts (experts == 0: dense MLP); `inter` is then ONE expert's width
+  int experts = 0, topk = 0;
+  bool norm_topk = false, qk_norm = false;
   double eps = 1e-5;
   bool tied = false;
   // request geometry
@@ -47,7 +50,8 @@ struct PlanSpec {
   std::vector<BufferSpec> buffers;
   int tokens = -1, rope_cos = -1, rope_sin = -1, block_table = -1, context_base = -1;
   int embed = -1, final_norm = -1, lm_head = -1;
-  int hidden_buf = -1, qkv_buf = -1, attn_buf = -1, mlp_buf = -1, logits_buf = -1;
+  int hidden_buf = -1, qkv_buf = -1, attn_buf = -1, mlp_buf = -1, logits_buf = -1, router_buf = -1,
+      route_idx_buf = -1, route_weight_buf = -1;
   std::vector<LayerBuffers> layer;
 
   // Throws std::invalid_argument with a precise message on any unsupported field.
@@ -55,7 +59,9 @@ struct PlanSpec {
 
   int qkv_rows() const { return (heads + 2 * kv_heads) * head_dim; }
   int max_k() const;
-  // algorithmic bytes of one decode step (weights of every GEMV + KV rows read)
+  int stages_per_layer() const { return experts ? 6 : 5; }
+  // algorithmic bytes of one decode step (weights of every GEMV + KV rows read; with experts:
+  // the dense matrices, the router, and batch * topk experts per layer)
   uint64_t weight_bytes() const;
   uint64_t kv_bytes_per_token() const { return 4ull * layers * kv_heads * head_dim; }
 };

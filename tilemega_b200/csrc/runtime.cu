@@ -238,6 +238,11 @@ void* tm_plan_create(int batch, void* const* external, int device) {
   p.head_base = 0;   // set by tm_plan_bind_tp for a tensor-parallel plan
   p.tp_world = s.tp;
   p.tp_rank = 0;
+  p.experts = s.experts;
+  p.topk = s.topk;
+  p.norm_topk = s.norm_topk ? 1 : 0;
+  p.qk_norm = s.qk_norm ? 1 : 0;
+  p.stages_per_layer = s.stages_per_layer();
   p.eps = float(s.eps);
   p.qk_scale_log2 = float(1.4426950408889634 / std::sqrt(double(s.head_dim)));
   p.capacity = s.capacity;
@@ -254,11 +259,16 @@ void* tm_plan_create(int batch, void* const* external, int device) {
   p.watchdog_ns = (unsigned long long)(std::max(watchdog_ms, 0.001) * 1e6);
   // shared memory: activation rows (or the attention scratch, whichever is larger) + ring
   const int gq = s.heads / s.kv_heads;   // query heads per KV head (4 or 8)
-  const int attention_scratch = gq * s.head_dim * 2 + 2 * s.head_dim * 2 + 8 * gq * (s.head_dim + 2) * 4 + 64;
+  // roped q, new k and v, the warps' partial states, and the QK-normalised q/k rows
+  const int attention_scratch = gq * s.head_dim * 2 + 2 * s.head_dim * 2 + 8 * gq * (s.head_dim + 2) * 4 +
+                                (gq + 1) * s.head_dim * 2 + 64;
+  // mixture of experts: the down stage stages one activation row per chosen expert
+  const int expert_rows = s.experts ? s.topk * (s.geo[tmb::kDown].k + 8) * 2 : 0;
   // rows of the widest GEMV input; one extra hidden-wide row holds the RMSNorm weights
   // (rows are padded by 8 elements so that the batch rows of a k-chunk sit on distinct banks)
   // a normalised stage also parks its raw rows and the norm weights there: 2*batch + 1 hidden-wide rows
-  int xs = std::max({batch * (s.max_k() + 8) * 2, (2 * batch + 1) * (s.geo[tmb::kQkv].k + 8) * 2, attention_scratch});
+  int xs = std::max({batch * (s.max_k() + 8) * 2, (2 * batch + 1) * (s.geo[tmb::kQkv].k + 8) * 2, attention_scratch,
+                     expert_rows});
   xs = (xs + 127) & ~127;
   p.xs_bytes = xs;
   p.static_quarters = s.static_quarters;
@@ -307,8 +317,10 @@ void* tm_plan_create(int batch, void* const* external, int device) {
   std::vector<tmb::LayerPtrs> layers(size_t(s.layers));
   for (int l = 0; l < s.layers; ++l) {
     const tmb::LayerBuffers& lb = s.layer[size_t(l)];
+    auto optional = [&](int index) -> const void* { return index >= 0 ? plan->buffer_ptr[size_t(index)] : nullptr; };
     layers[size_t(l)] = tmb::LayerPtrs{plan->buffer_ptr[lb.qkv],   plan->buffer_ptr[lb.o],     plan->buffer_ptr[lb.gate_up],
                                        plan->buffer_ptr[lb.down],  plan->buffer_ptr[lb.norm1], plan->buffer_ptr[lb.norm2],
+                                       optional(lb.router),        optional(lb.q_norm),        optional(lb.k_norm),
                                        plan->buffer_ptr[lb.k],     plan->buffer_ptr[lb.v]};
   }
   {
@@ -324,6 +336,11 @@ void* tm_plan_create(int batch, void* const* external, int device) {
   p.attn = plan->buffer_ptr[s.attn_buf];
   p.h = plan->buffer_ptr[s.mlp_buf];
   p.logits = plan->buffer_ptr[s.logits_buf];
+  if (s.experts) {
+    p.router_logits = plan->buffer_ptr[s.router_buf];
+    p.route_idx = static_cast<int*>(plan->buffer_ptr[s.route_idx_buf]);
+    p.route_w = static_cast<float*>(plan->buffer_ptr[s.route_weight_buf]);
+  }
   // scratch
   struct Scratch {
     void** out;
@@ -347,7 +364,7 @@ void* tm_plan_create(int batch, void* const* external, int device) {
   // barrier word, then the attention arrival counters: one block, rezeroed per launch
   const size_t attn_cnt = size_t(batch) * s.kv_heads;
   // ... and the task claim counters of every stage instance of the longest possible launch
-  const size_t stage_cnt = size_t(s.capacity) * (5 * size_t(s.layers) + 1) + 2;   // + the two look-ahead claims past the last stage
+  const size_t stage_cnt = size_t(s.capacity) * (size_t(s.stages_per_layer()) * size_t(s.layers) + 1) + 2;   // + the two look-ahead claims past the last stage
   const size_t ready_offset = (128 + attn_cnt * sizeof(unsigned) + 7) & ~size_t(7);
   plan->claim_offset = ready_offset + size_t(s.kv_heads) * sizeof(unsigned long long);
   plan->sync_bytes = plan->claim_offset + stage_cnt * sizeof(unsigned);
@@ -410,7 +427,8 @@ int tm_plan_launch_steps(void* handle, uint32_t first_step, uint32_t steps, uint
   DeviceScope scope(plan->device);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   // only the claim counters this launch can touch are rezeroed
-  const size_t used = plan->claim_offset + (size_t(steps) * (5 * size_t(plan->params.layers) + 1) + 2) * sizeof(unsigned);
+  const size_t used = plan->claim_offset +
+                      (size_t(steps) * (size_t(plan->params.stages_per_layer) * size_t(plan->params.layers) + 1) + 2) * sizeof(unsigned);
   cudaError_t err = cudaMemsetAsync(plan->sync_block, 0, used, s);
   if (err != cudaSuccess) return Fail(int(err), std::string("tm_plan_launch_steps: ") + cudaGetErrorString(err));
   if (plan->params.tp_world > 1 && !plan->tp_bound)
@@ -498,7 +516,8 @@ int tm_plan_trace_step(void* handle, int step) {
   if (!plan) return Fail(-1, "tm_plan_trace_step: bad plan");
   DeviceScope scope(plan->device);
   if (step >= 0 && !plan->trace_dev) {
-    plan->trace_bytes = size_t(plan->params.grid) * (5 * size_t(plan->params.layers) + 1) * 4 * sizeof(unsigned long long);
+    plan->trace_bytes = size_t(plan->params.grid) * (size_t(plan->params.stages_per_layer) * size_t(plan->params.layers) + 1) * 4 *
+                        sizeof(unsigned long long);
     void* dev = nullptr;
     cudaError_t err = Alloc(*plan, &dev, plan->trace_bytes);
     if (err != cudaSuccess) return Fail(int(err), cudaGetErrorString(err));

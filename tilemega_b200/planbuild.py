@@ -18,7 +18,8 @@ from .build import LIBRARY, build_library
 
 MODEL_KEYS = ("hidden_size", "intermediate_size", "num_attention_heads", "num_key_value_heads",
               "head_dim", "num_hidden_layers", "vocab_size", "rms_norm_eps", "tie_word_embeddings",
-              "rope_theta", "architectures")
+              "rope_theta", "architectures", "num_experts", "num_experts_per_tok", "moe_intermediate_size",
+              "norm_topk_prob")
 
 
 def plan_document(config: dict, *, batch_lo: int = 1, batch_hi: int | None = None, capacity: int,

@@ -117,13 +117,41 @@ def _sources(recipe: Mapping[str, object], source: Callable[[str], torch.Tensor]
     return tensors
 
 
+def expert_matrices(recipe: Mapping[str, object], source: Callable[[str], torch.Tensor]):
+    """The per-expert matrices of an expert_stack recipe, in expert order: gate/up rows
+    interleaved in units of `u` (as gate_up_interleave), or the down projection
+    (reference python/tilemega/moe/weights.py:15-47,56-76; names are the HF per-expert ones)."""
+    prefix, part = str(recipe["prefix"]), recipe["part"]
+    experts, hidden, inter, unit = (int(recipe[key]) for key in ("experts", "hidden", "intermediate", "u"))
+    if part not in ("gate_up", "down") or min(experts, hidden, inter, unit) <= 0 or inter % unit or not prefix.endswith("."):
+        raise ValueError("invalid expert stack recipe")
+    for expert in range(experts):
+        if part == "gate_up":
+            gate = source(f"{prefix}{expert}.gate_proj.weight")
+            up = source(f"{prefix}{expert}.up_proj.weight")
+            if tuple(gate.shape) != (inter, hidden) or tuple(up.shape) != (inter, hidden):
+                raise ValueError("expert projection has an incompatible shape")
+            yield torch.stack((gate.reshape(-1, unit, hidden), up.reshape(-1, unit, hidden)), dim=1).reshape(-1, hidden)
+        else:
+            down = source(f"{prefix}{expert}.down_proj.weight")
+            if tuple(down.shape) != (hidden, inter):
+                raise ValueError("expert projection has an incompatible shape")
+            yield down
+
+
 def pack(recipe: Mapping[str, object], source: Callable[[str], torch.Tensor], tp_rank: int = 0) -> torch.Tensor:
     kind = recipe["kind"]
     source = sharded(recipe, source, tp_rank)
     if kind == "alias":
         return source(str(recipe["source"]))
     if kind == "tile_pages":
-        return tile_pages(pack(recipe["source"], source, tp_rank), int(recipe["tile_n"]), int(recipe["tile_k"]))
+        inner = recipe["source"]
+        if isinstance(inner, Mapping) and inner.get("kind") == "expert_stack":
+            # every expert packed by itself, the packed experts one after the other
+            # (reference python/tilemega/moe/weights.py:56-88)
+            return torch.cat([tile_pages(matrix, int(recipe["tile_n"]), int(recipe["tile_k"]))
+                              for matrix in expert_matrices(inner, source)])
+        return tile_pages(pack(inner, source, tp_rank), int(recipe["tile_n"]), int(recipe["tile_k"]))
     if kind == "qkv_group_interleave":
         # rows per KV head: its query heads, then its key head, then its value head
         # (reference weights.py:246-256)
