@@ -60,7 +60,7 @@ def measured_peak_gbs() -> tuple[float, str]:
 
 
 MODELS = {"llama-3.1-8b": synthetic.LLAMA_3_1_8B, "llama-3.2-1b": synthetic.LLAMA_3_2_1B,
-          "llama-3.1-70b": synthetic.LLAMA_3_1_70B}
+          "llama-3.1-70b": synthetic.LLAMA_3_1_70B, "qwen3-30b-a3b": synthetic.QWEN3_30B_A3B}
 
 
 def workload(args) -> dict:
@@ -236,9 +236,10 @@ def run_ours(args) -> None:
         so = emit_plan(config, plan_dir, **options)
     lib = PlanLibrary(so)
     replica = 0 if tp > 1 else rank     # tensor-parallel ranks cut their slices out of ONE model and share one request
-    if tp > 1:
-        weights = load_weights(synthetic.LazySeededCheckpoint(config, seed=0, device=device), lib, device=device,
-                               tp=(rank, world))
+    if tp > 1 or synthetic.is_moe(config):
+        # models too large to hold unpacked: every tensor is drawn on the device when its recipe asks for it
+        weights = load_weights(synthetic.LazySeededCheckpoint(config, seed=replica, device=device), lib, device=device,
+                               tp=(rank, world) if tp > 1 else (0, 1))
     else:
         raw = synthetic.seeded_weights(config, seed=rank, dtype=torch.bfloat16, device=device)
         weights = load_weights(TensorCheckpoint(raw, config["tie_word_embeddings"]), lib, device=device)
