@@ -64,6 +64,10 @@ constexpr int kOffBestIdx = 704;   // int[8 warps][kMaxBatch]
 constexpr int kOffWsum = 960;      // float[kMaxBatch][8]
 constexpr int kOffSc = 1216;       // routing of the current layer: int expert[8], float weight[8] (+32), mbarrier (+64)
 constexpr int kOffRed = 3264;      // float[kPartialRing][8 warps][8 rows][batch]: 2 KB per sequence of the batch
+// Features compiled into an instantiation of the kernel (template parameter X): the plain
+// one (0) serves unsharded dense plans and carries neither.
+constexpr int kXTp = 1;    // tensor parallelism: all-reduce epilogue, argmax exchange
+constexpr int kXMoe = 2;   // mixture of experts and the per-head QK norm (batch 1)
 constexpr int kFifo = 32;          // entries; the streaming warp keeps at most kFifo/2 unread
 
 __host__ __device__ inline int xs_offset(int batch) { return kOffRed + kPartialRing * 8 * 8 * 4 * batch; }   // activation rows / attention scratch
@@ -228,7 +232,7 @@ __device__ __forceinline__ int seq_pos(const MegaParams& p, int past, int b) {
 __device__ __forceinline__ void attn_shape(const MegaParams& p, int past, int nk, int& spt, int& ntasks) {
   int total = 0;
   for (int b = 0; b < p.batch; ++b) total += (seq_pos(p, past, b) / nk + 1) * p.kv_heads;
-  spt = max(1, (total + p.grid - 1) / p.grid);
+  spt = max(max(1, p.attn_min_spt), (total + p.grid - 1) / p.grid);
   ntasks = 0;
   for (int b = 0; b < p.batch; ++b) {
     const int ns = seq_pos(p, past, b) / nk + 1;
@@ -477,7 +481,7 @@ __device__ __forceinline__ void stream_attn(Ctx& c, const LayerPtrs& lp, int pas
   stream_close(c);
 }
 
-template <int D, bool X>
+template <int D, int X>
 __device__ void streamer_main(Ctx& c) {
   const MegaParams& p = c.p;
   const uint64_t policy = policy_evict_first();
@@ -509,7 +513,7 @@ __device__ void streamer_main(Ctx& c) {
       }
       stream_attn<D>(c, lp, past);
       stream_gemv(c, p.geo[kOProj], lp.o, policy);
-      if (X && p.experts) {
+      if ((X & kXMoe) && p.experts) {
         stream_gemv(c, p.geo[kRouter], lp.router, policy);
         // the experts of this layer are known once the arithmetic warps have routed
         if (!mbar_wait(c, c.route_bar(), c.route_phase, kSiteFull)) return;
@@ -761,10 +765,10 @@ __device__ __forceinline__ float silu_bf16(float g) {
 
 // Tensor-parallel exchange of one column pair (row, row + 1) of batch row b: store this
 // rank's packet into every peer's receive region, poll this rank's own region for the
-// peers' packets, add the partials in ascending rank order. Not inlined: the loops and
-// their registers stay out of the GEMV path of unsharded plans
-// (include/tilemega/Backend/Sm90DenseEpilogue.h:43-86 keeps its Send/Finish out of line too).
-static __device__ __noinline__ float2 tp_all_reduce(const MegaParams& p, int ar_region, uint32_t epoch, int batch, int b, int n,
+// peers' packets, add the partials in ascending rank order
+// (include/tilemega/Backend/Sm90DenseEpilogue.h:43-86). Only the tensor-parallel
+// instantiation of the kernel contains it.
+__device__ __forceinline__ float2 tp_all_reduce(const MegaParams& p, int ar_region, uint32_t epoch, int batch, int b, int n,
                                              int row, uint32_t mine) {
   const size_t half = size_t(n) >> 1;
   const size_t region = size_t(ar_region) * p.tp_world * batch * half + (size_t(row) >> 1);
@@ -831,7 +835,7 @@ struct PendingEpilogue {
 
 // Epilogue of one task, run by one warp: sum the eight warps' partial sums in warp
 // order, then apply the stage's rounding sites.
-template <int B, bool X>
+template <int B, int X>
 __device__ __forceinline__ void gemv_epilogue(Ctx& c, const GemvGeo& geo, const GemvIo& io, const PendingEpilogue<B>& e,
                                               int lane, float (&best_val)[EpiPasses<B>::value],
                                               int (&best_idx)[EpiPasses<B>::value]) {
@@ -875,7 +879,7 @@ __device__ __forceinline__ void gemv_epilogue(Ctx& c, const GemvGeo& geo, const 
           best_val[pass] = bv;   // the 8 lanes of a sequence all hold its candidate
           best_idx[pass] = bi;
         }
-      } else if (X && io.epilogue == kEpiResidualAllReduce) {
+      } else if ((X & kXTp) && io.epilogue == kEpiResidualAllReduce) {
         // Tensor parallel: every rank holds the sum over its own slice of the reduction.
         // The ranks exchange their sums rounded to bf16, two columns and the epoch per
         // 8-byte packet, stored straight into each peer's receive region; every rank
@@ -910,7 +914,7 @@ __device__ __forceinline__ void gemv_epilogue(Ctx& c, const GemvGeo& geo, const 
   }
 }
 
-template <int B, bool X>
+template <int B, int X>
 __device__ TMB_GEMV_CALL void gemv_stage(Ctx& c, const GemvGeo& geo, const GemvIo& io, bool tr, int stage) {
   const MegaParams& p = c.p;
   stage_rows<B>(c, io, geo.k, geo.k_src);
@@ -1210,7 +1214,7 @@ __device__ __noinline__ void moe_down_stage(Ctx& c, const GemvGeo& geo, bool tr,
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ int kv_swizzled(int d, int pos) { return ((((d >> 3) ^ (pos & 7))) << 3) | (d & 7); }
 
-template <int B, int D, int GQ, bool X>
+template <int B, int D, int GQ, int X>
 __device__ void attn_stage(Ctx& c, const LayerPtrs& lp, int past, bool tr, int stage, unsigned long long qkv_stages) {
   constexpr int NK = kAttnHalfBytes / (2 * D);  // keys per slot: 64 (D=128) / 128 (D=64)
   constexpr int KW = NK / kConsumerWarps;       // keys per warp per slot: 8 / 16
@@ -1254,7 +1258,7 @@ __device__ void attn_stage(Ctx& c, const LayerPtrs& lp, int past, bool tr, int s
       const long long e = table_entry(p, a.b, a.pos / kKvBlock);
       new_off = e * p.kv_block_stride + (long long)a.g * p.kv_head_stride + (a.pos % kKvBlock) * D;
     }
-    const bool qk_norm = X && lp.q_norm != nullptr;   // X: the instantiation that carries the Qwen3 / mixture-of-experts code
+    const bool qk_norm = (X & kXMoe) && lp.q_norm != nullptr;   // only the mixture-of-experts / Qwen3 instantiation carries this
     if (qk_norm) {
       // Qwen3: every query head and the key head are RMS-normalised over their own D
       // values before RoPE, y = w * bf16(x * rsqrt(mean x^2 + eps)), the product rounded
@@ -1315,12 +1319,14 @@ __device__ void attn_stage(Ctx& c, const LayerPtrs& lp, int past, bool tr, int s
         qa[s][1] = qrow[8 * s + 4 + q];
       }
     }
-    // online softmax state of this lane's row (query head g) over this warp's keys, and
-    // its output row: oacc[dt][0..1] = O[g][8 dt + 2q, +1] (oacc[dt][2..3] belong to unused rows)
+    // online softmax state of this lane's row (query head g) over this warp's keys. The
+    // output is kept TRANSPOSED, O^T = V^T P^T, so that all 16 rows of the tensor-pipe tile
+    // carry head-dimension rows (with O = P V half of every tile would be the unused query
+    // rows 8..15): oacc[mt] = O[heads 2q, 2q+1][d = 16 mt + g] and the same for d + 8.
     float m = -INFINITY, l = 0.f;
-    float oacc[DT][4];
+    float oacc[D / 16][4];
 #pragma unroll
-    for (int dt = 0; dt < DT; ++dt) oacc[dt][0] = oacc[dt][1] = oacc[dt][2] = oacc[dt][3] = 0.f;
+    for (int mt = 0; mt < D / 16; ++mt) oacc[mt][0] = oacc[mt][1] = oacc[mt][2] = oacc[mt][3] = 0.f;
     for (int s = a.slot0; s < a.slot1; ++s) {
       mbar_wait_warp(c, c.full(c.slot), c.phase, kSiteFull);
       unsigned char* kbase = c.ring(c.slot);
@@ -1386,23 +1392,31 @@ __device__ void attn_stage(Ctx& c, const LayerPtrs& lp, int past, bool tr, int s
         sum += __shfl_xor_sync(0xffffffffu, sum, 1);
         sum += __shfl_xor_sync(0xffffffffu, sum, 2);
         l = fmaf(l, alpha, sum);
+        {
+          // the rescale factors of the two heads this lane's output columns belong to
+          const float alpha0 = __shfl_sync(0xffffffffu, alpha, 8 * q);
+          const float alpha1 = __shfl_sync(0xffffffffu, alpha, 8 * q + 4);
 #pragma unroll
-        for (int dt = 0; dt < DT; ++dt) {
-          oacc[dt][0] *= alpha;
-          oacc[dt][1] *= alpha;
+          for (int mt = 0; mt < D / 16; ++mt) {
+            oacc[mt][0] *= alpha0;
+            oacc[mt][1] *= alpha1;
+            oacc[mt][2] *= alpha0;
+            oacc[mt][3] *= alpha1;
+          }
         }
-        // ---- O += P V: V tiles transposed on load (row-major V[key][d] is the B operand's k x n)
+        // ---- O^T += V^T P^T: A = V^T by transposing loads of row-major V[key][d] (rows d,
+        // columns keys), B = P^T, which is the score fragment as it stands
 #pragma unroll
         for (int kt = 0; kt < KT; ++kt) {
           const uint32_t vrow = smem_u32(vbase) + uint32_t((key0 + 8 * kt + lr) * D * 2);
 #pragma unroll
           for (int cq = 0; cq < DT / 4; ++cq) {
-            uint32_t vb[4];
+            uint32_t vb[4];   // vb[j] = V[keys 2q, 2q+1][d = 8 (4 cq + j) + g]
             ldmatrix_x4_trans(vb, vrow + 16 * ((4 * cq + lm) ^ lr));
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              mma_bf16_m16n8k8(oacc[4 * cq + j], phi[kt], vb[j]);
-              mma_bf16_m16n8k8(oacc[4 * cq + j], plo[kt], vb[j]);
+            for (int jj = 0; jj < 2; ++jj) {
+              mma_bf16_m16n8k8_full(oacc[2 * cq + jj], vb[2 * jj], vb[2 * jj + 1], phi[kt]);
+              mma_bf16_m16n8k8_full(oacc[2 * cq + jj], vb[2 * jj], vb[2 * jj + 1], plo[kt]);
             }
           }
         }
@@ -1411,18 +1425,23 @@ __device__ void attn_stage(Ctx& c, const LayerPtrs& lp, int past, bool tr, int s
       if (c.lane == 0) mbar_arrive(c.empty(c.slot));
       c.advance();
     }
-    // ---- the warps' states meet in scratch: lanes of rows g < GQ hold head g
-    if (g < GQ) {
-      float* dst = scratch + (c.warp * GQ + g) * PW;
+    // ---- the warps' states meet in scratch: this lane holds columns d = 16 mt + g (+ 8) of
+    // heads 2q and 2q+1, and the softmax state of head g
 #pragma unroll
-      for (int dt = 0; dt < DT; ++dt) {
-        dst[8 * dt + 2 * q] = oacc[dt][0];
-        dst[8 * dt + 2 * q + 1] = oacc[dt][1];
+    for (int hh = 0; hh < 2; ++hh) {
+      if (2 * q + hh < GQ) {
+        float* dst = scratch + (c.warp * GQ + 2 * q + hh) * PW;
+#pragma unroll
+        for (int mt = 0; mt < D / 16; ++mt) {
+          dst[16 * mt + g] = oacc[mt][hh];
+          dst[16 * mt + 8 + g] = oacc[mt][2 + hh];
+        }
       }
-      if (q == 0) {
-        dst[D] = m;
-        dst[D + 1] = l;
-      }
+    }
+    if (g < GQ && q == 0) {
+      float* dst = scratch + (c.warp * GQ + g) * PW;
+      dst[D] = m;
+      dst[D + 1] = l;
     }
     consumer_sync();
     __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.attn) + size_t(a.b) * p.heads * D + size_t(a.g) * GQ * D;
@@ -1511,7 +1530,7 @@ __device__ void attn_stage(Ctx& c, const LayerPtrs& lp, int past, bool tr, int s
 // ---------------------------------------------------------------------------
 // arithmetic warps: one decode step after another
 // ---------------------------------------------------------------------------
-template <int B, int D, int GQ, bool X>
+template <int B, int D, int GQ, int X>
 __device__ void consumer_main(Ctx& c) {
   const MegaParams& p = c.p;
   for (int si = 0; si < p.nsteps; ++si) {
@@ -1528,7 +1547,7 @@ __device__ void consumer_main(Ctx& c) {
     int stage = 0;
     LayerPtrs lp = p.layer[0];
     // tensor parallel: o and down end in an all-reduce; epochs count all-reduces since the plan was made
-    const int residual_kind = X && p.tp_world > 1 ? kEpiResidualAllReduce : kEpiResidual;
+    const int residual_kind = (X & kXTp) && p.tp_world > 1 ? kEpiResidualAllReduce : kEpiResidual;
     const unsigned long long steps_before = p.tp_steps + (unsigned long long)si;
     const uint32_t ar_epoch0 = uint32_t(steps_before * (unsigned long long)(2 * p.layers)) + 1u;
     for (int l = 0; l < p.layers; ++l) {
@@ -1558,9 +1577,9 @@ __device__ void consumer_main(Ctx& c) {
       trace_mark(c, tr, stage, 0);
       if (!grid_wait(c)) return;
       trace_mark(c, tr, stage, 1);
-      if (X && p.experts) {
+      if ((X & kXMoe) && p.experts) {
         // mixture of experts: router scores, top-k, then the chosen experts only
-        if constexpr (X && B == 1) {
+        if constexpr ((X & kXMoe) != 0 && B == 1) {
           io = GemvIo{p.x, lp.norm2, 0, kEpiStore, p.router_logits, nullptr, 1, 0, 0u};
           gemv_stage<B, X>(c, p.geo[kRouter], io, tr, stage++);
           grid_arrive(c);
@@ -1630,7 +1649,7 @@ __device__ void consumer_main(Ctx& c) {
         const int oi = __shfl_xor_sync(0xffffffffu, bi, mk);
         if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
       }
-      if (X && p.tp_world > 1) {
+      if ((X & kXTp) && p.tp_world > 1) {
         // Each rank scored a slice of the vocabulary: CTA 0 sends its winner (the compared
         // value is a bf16, the index fits 20 bits, so one packet holds both and a 28-bit
         // epoch) into every peer's block; every CTA then takes the best over the ranks in
@@ -1665,7 +1684,7 @@ __device__ void consumer_main(Ctx& c) {
   }
 }
 
-template <int B, int D, int GQ, bool X>
+template <int B, int D, int GQ, int X>
 __global__ void __launch_bounds__(kThreads, 1) decode_megakernel(const __grid_constant__ MegaParams p) {
   extern __shared__ __align__(1024) unsigned char smem[];
   Ctx c(p, smem);
@@ -1712,7 +1731,7 @@ __global__ void watchdog_probe_kernel(MegaParams p, int withhold) {
 
 #endif
 
-template <int B, int D, int GQ, bool X>
+template <int B, int D, int GQ, int X>
 static cudaError_t run_instance(const MegaParams& p, size_t smem_bytes, cudaStream_t stream, bool prepare) {
   auto kernel = decode_megakernel<B, D, GQ, X>;
   if (prepare) {
@@ -1732,7 +1751,7 @@ static cudaError_t run_instance(const MegaParams& p, size_t smem_bytes, cudaStre
   return cudaGetLastError();
 }
 
-template <int D, int GQ, bool X>
+template <int D, int GQ, int X>
 static cudaError_t run_batch(const MegaParams& p, size_t smem_bytes, cudaStream_t stream, bool prepare) {
   switch (p.batch) {
     case 1: return run_instance<1, D, GQ, X>(p, smem_bytes, stream, prepare);
@@ -1756,10 +1775,14 @@ cudaError_t run_decode_extended(const MegaParams& p, cudaStream_t stream, bool p
   const size_t smem_bytes = size_t(ring_offset(p.xs_bytes, p.batch) + p.nslots * kSlotBytes);
   if (p.kv_heads <= 0 || p.heads % p.kv_heads || p.head_dim != 128) return cudaErrorInvalidValue;
   const int gq = p.heads / p.kv_heads;
-  if ((p.experts > 0 || p.qk_norm) && p.batch != 1) return cudaErrorInvalidValue;
-  if (gq == 8) return run_batch<128, 8, true>(p, smem_bytes, stream, prepare);
-  if (gq == 4) return run_batch<128, 4, true>(p, smem_bytes, stream, prepare);
-  return cudaErrorInvalidValue;
+  if (gq != 4 && gq != 8) return cudaErrorInvalidValue;
+  if (p.experts > 0 || p.qk_norm) {
+    if (p.batch != 1 || p.tp_world > 1) return cudaErrorInvalidValue;
+    return gq == 8 ? run_instance<1, 128, 8, kXMoe>(p, smem_bytes, stream, prepare)
+                   : run_instance<1, 128, 4, kXMoe>(p, smem_bytes, stream, prepare);
+  }
+  return gq == 8 ? run_batch<128, 8, kXTp>(p, smem_bytes, stream, prepare)
+                 : run_batch<128, 4, kXTp>(p, smem_bytes, stream, prepare);
 }
 #else
 cudaError_t run_decode_extended(const MegaParams& p, cudaStream_t stream, bool prepare);
@@ -1769,10 +1792,10 @@ static cudaError_t run_decode(const MegaParams& p, cudaStream_t stream, bool pre
   const size_t smem_bytes = size_t(ring_offset(p.xs_bytes, p.batch) + p.nslots * kSlotBytes);
   if (p.kv_heads <= 0 || p.heads % p.kv_heads) return cudaErrorInvalidValue;
   const int gq = p.heads / p.kv_heads;
-  if (p.head_dim == 128 && gq == 8) return run_batch<128, 8, false>(p, smem_bytes, stream, prepare);
+  if (p.head_dim == 128 && gq == 8) return run_batch<128, 8, 0>(p, smem_bytes, stream, prepare);
   if (gq != 4) return cudaErrorInvalidValue;
-  if (p.head_dim == 128) return run_batch<128, 4, false>(p, smem_bytes, stream, prepare);
-  if (p.head_dim == 64) return run_batch<64, 4, false>(p, smem_bytes, stream, prepare);
+  if (p.head_dim == 128) return run_batch<128, 4, 0>(p, smem_bytes, stream, prepare);
+  if (p.head_dim == 64) return run_batch<64, 4, 0>(p, smem_bytes, stream, prepare);
   return cudaErrorInvalidValue;
 }
 #endif

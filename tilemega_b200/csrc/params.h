@@ -80,6 +80,7 @@ struct MegaParams {
   int write_logits;
   int grid, nslots, xs_bytes;
   int diag;                 // DiagFlag bits
+  int attn_min_spt;         // least ring slots of keys per attention task (a task's fixed cost wants amortising)
   int static_quarters;      // quarters of a CTA's even share of a GEMV stage that are dealt, not claimed (0..4)
   unsigned long long bar_base;     // grid-barrier arrivals before this launch
   unsigned long long watchdog_ns;  // per-wait limit

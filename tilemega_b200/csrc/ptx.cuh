@@ -183,6 +183,13 @@ __device__ __forceinline__ void mma_bf16_m16n8k8(float (&d)[4], uint32_t a0, uin
       : "r"(a0), "r"(0u), "r"(b0));
 }
 
+// The same with all 16 rows of A in use.
+__device__ __forceinline__ void mma_bf16_m16n8k8_full(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+  asm("mma.sync.aligned.m16n8k8.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5}, {%6}, {%0, %1, %2, %3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(b0));
+}
+
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return uint32_t(__bfloat16_as_ushort(__float2bfloat16_rn(lo))) |
          (uint32_t(__bfloat16_as_ushort(__float2bfloat16_rn(hi))) << 16);

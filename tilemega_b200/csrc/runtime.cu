@@ -272,6 +272,7 @@ void* tm_plan_create(int batch, void* const* external, int device) {
   xs = (xs + 127) & ~127;
   p.xs_bytes = xs;
   p.static_quarters = s.static_quarters;
+  p.attn_min_spt = s.attn_min_slots;
   p.diag = s.diag;
   const int limit = int(prop.sharedMemPerBlockOptin);
   p.nslots = tmb::kMaxSlots;

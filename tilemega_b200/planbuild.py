@@ -25,7 +25,8 @@ MODEL_KEYS = ("hidden_size", "intermediate_size", "num_attention_heads", "num_ke
 def plan_document(config: dict, *, batch_lo: int = 1, batch_hi: int | None = None, capacity: int,
                   kv_layout: str = "contiguous", num_blocks: int = 0, geometry: dict | None = None,
                   grid: int = 0, slots: int = 0, write_logits: bool = True,
-                  static_quarters: int | None = None, diag: int = 0, tp: int = 1) -> dict:
+                  static_quarters: int | None = None, diag: int = 0, tp: int = 1,
+                  attn_min_slots: int | None = None) -> dict:
     """The sidecar for one decode plan; raises ValueError on shapes the kernels do not cover."""
     model = {key: config[key] for key in MODEL_KEYS if key in config}
     model.setdefault("head_dim", config["hidden_size"] // config["num_attention_heads"])
@@ -52,6 +53,8 @@ def plan_document(config: dict, *, batch_lo: int = 1, batch_hi: int | None = Non
     }
     if tp > 1:
         document["tp"] = tp   # the plan is ONE rank's: every rank loads the same library
+    if attn_min_slots is not None:
+        document["attn_min_slots"] = attn_min_slots   # least ring slots of keys per attention task
     if static_quarters is not None:
         document["static_quarters"] = static_quarters
     if diag:
