@@ -51,3 +51,70 @@ def test_moe_decode_matches_oracle_and_routes_identically(plan_dir):
     looped, _ = run.greedy(prompt, new_tokens, stepwise=False)
     assert torch.equal(looped, tokens)
     run.close()
+
+
+def test_every_moe_stage_of_one_layer(plan_dir):
+    """Router logits, routing, expert SwiGLU rows and the weighted expert sum, each recomputed on
+    the CPU from the buffers the GPU had (see tests/test_gpu_stages.py for the method); the QK norm
+    is checked through the appended key row."""
+    import torch.nn.functional as F
+    from oracle.decoder_oracle import rms_norm, rotate_half, rope_tables
+    from tilemega_b200.serving.state import kv_row_swizzle
+    from test_gpu_stages import agreement
+
+    config = dict(synthetic.TINY_MOE, num_hidden_layers=1)
+    hidden, eps, dim = config["hidden_size"], config["rms_norm_eps"], config["head_dim"]
+    heads, hkv, topk = config["num_attention_heads"], config["num_key_value_heads"], config["num_experts_per_tok"]
+    inter = config["moe_intermediate_size"]
+    history = 41
+    capacity = (history + 18) // 16 * 16
+    w = bf16_weights(config)
+    run = GpuRun(config, w, 1, capacity, plan_dir)
+    ids = synthetic.seeded_tokens(1, history + 2, config["vocab_size"], seed=9)
+    run.state.tokens.zero_()
+    run.state.tokens[:, :history + 2].copy_(ids)
+    run.plan.set_prompt_len(history + 2)
+    run.plan.set_steps(list(range(history + 1)))
+    run.plan.launch_steps(0, history, 2, run.stream)
+    run.plan.launch(history, 2, run.stream)
+    run.check_alive()
+    pos = history
+    gq = heads // hkv
+    qkv_gpu = run.read("serving.qkv").reshape(1, hkv, gq + 2, dim)
+    attn_gpu = run.read("serving.attention").reshape(1, heads * dim)
+    router_gpu = run.read("serving.router_logits").reshape(-1)
+    route = run.read("serving.route_index", torch.int32).reshape(-1)
+    route_weight = run.read("serving.route_weight", torch.float32).reshape(-1)
+    h_gpu = run.read("serving.mlp").reshape(topk, inter)
+    x_gpu = run.read("serving.hidden").reshape(1, hidden)
+    cache = kv_row_swizzle(run.state.kv_storage.cpu())
+    p = "model.layers.0."
+    # QK norm + RoPE of the new key, from the GPU's own projection
+    cos, sin = rope_tables(config, capacity, torch.bfloat16)
+    k_normed = rms_norm(qkv_gpu[:, :, gq], w[p + "self_attn.k_norm.weight"], eps)
+    k_rot = k_normed * cos[pos] + rotate_half(k_normed) * sin[pos]
+    agreement(cache[0, 0, :, :, pos], k_rot, "normalised, roped key row", ulps=1.0, exact_fraction=0.97)
+    # residual stream after attention, from the GPU's attention output
+    x_in = F.embedding(ids[:, pos].long(), w["model.embed_tokens.weight"])
+    x_mid = x_in + F.linear(attn_gpu, w[p + "self_attn.o_proj.weight"])
+    xm = rms_norm(x_mid, w[p + "post_attention_layernorm.weight"], eps)
+    # router: one bf16 rounding per logit
+    agreement(router_gpu, F.linear(xm, w[p + "mlp.gate.weight"]).reshape(-1), "router logits", ulps=1.0, exact_fraction=0.9)
+    # routing from the GPU's own logits: indices bit-exact and in rank order, weights renormalised in fp32
+    probability = torch.softmax(router_gpu.float(), -1)
+    weight, index = torch.topk(probability, topk)
+    assert torch.equal(route, index.to(torch.int32)), (route.tolist(), index.tolist())
+    assert torch.allclose(route_weight, weight / weight.sum(), rtol=0, atol=2e-6)
+    # expert SwiGLU rows, one per chosen expert
+    for slot in range(topk):
+        e = p + f"mlp.experts.{int(route[slot])}."
+        h_ref = F.silu(F.linear(xm, w[e + "gate_proj.weight"])) * F.linear(xm, w[e + "up_proj.weight"])
+        agreement(h_gpu[slot], h_ref.reshape(-1), f"expert {int(route[slot])} swiglu", ulps=2.0, exact_fraction=0.95, floor=1e-3)
+    # weighted sum of the experts' down projections (from the GPU's rows and weights), then the residual
+    total = torch.zeros(hidden)
+    for slot in range(topk):
+        e = p + f"mlp.experts.{int(route[slot])}."
+        total = total + F.linear(h_gpu[slot], w[e + "down_proj.weight"]).float() * route_weight[slot]
+    agreement(x_gpu, x_mid + total.to(torch.bfloat16).reshape(1, hidden), "residual stream after the experts", ulps=2.0,
+              exact_fraction=0.95, floor=2e-3)
+    run.close()
