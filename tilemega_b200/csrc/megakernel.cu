@@ -763,23 +763,33 @@ __device__ __forceinline__ float silu_bf16(float g) {
   return bf16_round(g / (1.0f + expf(-g)));
 }
 
-// Tensor-parallel exchange of one column pair (row, row + 1) of batch row b: store this
-// rank's packet into every peer's receive region, poll this rank's own region for the
-// peers' packets, add the partials in ascending rank order
-// (include/tilemega/Backend/Sm90DenseEpilogue.h:43-86). Only the tensor-parallel
-// instantiation of the kernel contains it.
-__device__ __forceinline__ float2 tp_all_reduce(const MegaParams& p, int ar_region, uint32_t epoch, int batch, int b, int n,
-                                             int row, uint32_t mine) {
+// Tensor-parallel all-reduce of one tile, in two halves that are run an epilogue apart
+// (include/tilemega/Backend/Sm90DenseEpilogue.h:43-86 splits it the same way). Send: the
+// lane that holds the column pair (row, row + 1) of batch row b stores this rank's packet
+// {two bf16 sums, epoch} into every peer's receive region. Only the tensor-parallel
+// instantiation of the kernel contains these.
+__device__ __forceinline__ size_t tp_slot(const MegaParams& p, int ar_region, int batch, int n, int source, int b, int row) {
   const size_t half = size_t(n) >> 1;
-  const size_t region = size_t(ar_region) * p.tp_world * batch * half + (size_t(row) >> 1);
+  return (size_t(ar_region) * p.tp_world * batch + size_t(source) * batch + b) * half + (size_t(row) >> 1);
+}
+
+__device__ __forceinline__ void tp_send(const MegaParams& p, int ar_region, uint32_t epoch, int batch, int b, int n, int row,
+                                        uint32_t mine) {
+  const size_t slot = tp_slot(p, ar_region, batch, n, p.tp_rank, b, row);
   const unsigned long long packet = ((unsigned long long)epoch << 32) | mine;
   for (int q = 0; q < p.tp_world; ++q)
-    if (q != p.tp_rank) st_relaxed_sys(p.ar[q] + region + (size_t(p.tp_rank) * batch + b) * half, packet);
+    if (q != p.tp_rank) st_relaxed_sys(p.ar[q] + slot, packet);
+}
+
+// Finish: poll this rank's own region for the peers' packets of the same column pair and
+// add the partials in ascending rank order, so the sum is bitwise the same on every rank.
+__device__ __forceinline__ float2 tp_finish(const MegaParams& p, int ar_region, uint32_t epoch, int batch, int b, int n,
+                                            int row, uint32_t mine) {
   float sx = 0.f, sy = 0.f;
   for (int q = 0; q < p.tp_world; ++q) {
     uint32_t bits = mine;
     if (q != p.tp_rank) {
-      const unsigned long long* slot = p.ar[p.tp_rank] + region + (size_t(q) * batch + b) * half;
+      const unsigned long long* slot = p.ar[p.tp_rank] + tp_slot(p, ar_region, batch, n, q, b, row);
       unsigned long long seen, t0 = 0;
       uint32_t polls = 0;
       while (uint32_t((seen = ld_relaxed_sys(slot)) >> 32) != epoch) {
@@ -833,14 +843,45 @@ struct PendingEpilogue {
   float residual[EpiPasses<B>::value];   // prefetched residual elements of this lane (kEpiResidual)
 };
 
+// A tile whose all-reduce packets are sent but whose sum is not taken yet. The owning warp
+// finishes it at its NEXT epilogue, eight of the CTA's tasks later (or at the end of the
+// stage): by then the peers' packets have crossed NVLink, so the wait costs nothing. Taken
+// right after the send, the round trip stalls the warp on every tile, and with the short
+// tiles of an 8-way sharded model the whole CTA behind it.
+template <int B>
+struct PendingAr {
+  int task;         // -1: none
+  uint32_t mine[EpiPasses<B>::value];
+  float res0[EpiPasses<B>::value], res1[EpiPasses<B>::value];
+};
+
+template <int B>
+__device__ __forceinline__ void tp_finish_tile(Ctx& c, const GemvGeo& geo, const GemvIo& io, PendingAr<B>& ar, int lane) {
+  const MegaParams& p = c.p;
+#pragma unroll
+  for (int pass = 0; pass < EpiPasses<B>::value; ++pass) {
+    constexpr int total = kTileN * B;
+    const int live = total - 32 * pass >= 32 ? 32 : total - 32 * pass;
+    if (lane < live && (lane & 1) == 0) {
+      const int r = lane & 7, b = 4 * pass + (lane >> 3);
+      const int row = ar.task * kTileN + r;
+      const float2 sum = tp_finish(p, io.ar_region, io.ar_epoch, B, b, geo.n, row, ar.mine[pass]);
+      const uint32_t pair = pack_bf16x2(bf16_round(sum.x) + ar.res0[pass], bf16_round(sum.y) + ar.res1[pass]);
+      *reinterpret_cast<uint32_t*>(static_cast<__nv_bfloat16*>(io.out) + size_t(b) * geo.n + row) = pair;
+    }
+  }
+  ar.task = -1;
+}
+
 // Epilogue of one task, run by one warp: sum the eight warps' partial sums in warp
 // order, then apply the stage's rounding sites.
 template <int B, int X>
 __device__ __forceinline__ void gemv_epilogue(Ctx& c, const GemvGeo& geo, const GemvIo& io, const PendingEpilogue<B>& e,
                                               int lane, float (&best_val)[EpiPasses<B>::value],
-                                              int (&best_idx)[EpiPasses<B>::value]) {
+                                              int (&best_idx)[EpiPasses<B>::value], PendingAr<B>& ar) {
   const MegaParams& p = c.p;
   const float* red = c.red();
+  if ((X & kXTp) && io.epilogue == kEpiResidualAllReduce && ar.task >= 0) tp_finish_tile<B>(c, geo, io, ar, lane);
   mbar_wait_warp(c, c.pfull(e.buf), e.lap, kSiteFull);
 #pragma unroll
   for (int pass = 0; pass < EpiPasses<B>::value; ++pass) {
@@ -888,10 +929,12 @@ __device__ __forceinline__ void gemv_epilogue(Ctx& c, const GemvGeo& geo, const 
         const float vb1 = __shfl_down_sync(mask, vb, 1);
         const float res1 = __shfl_down_sync(mask, e.residual[pass], 1);
         if ((r & 1) == 0) {
-          const float2 sum = tp_all_reduce(p, io.ar_region, io.ar_epoch, B, b, geo.n, row, pack_bf16x2(vb, vb1));
-          const uint32_t pair = pack_bf16x2(bf16_round(sum.x) + e.residual[pass], bf16_round(sum.y) + res1);
-          *reinterpret_cast<uint32_t*>(static_cast<__nv_bfloat16*>(io.out) + size_t(b) * geo.n + row) = pair;
+          ar.mine[pass] = pack_bf16x2(vb, vb1);
+          ar.res0[pass] = e.residual[pass];
+          ar.res1[pass] = res1;
+          tp_send(p, io.ar_region, io.ar_epoch, B, b, geo.n, row, ar.mine[pass]);
         }
+        ar.task = e.task;   // finished at this warp's next epilogue, or when the stage ends
       } else {
         __nv_bfloat16* out = static_cast<__nv_bfloat16*>(io.out) + size_t(b) * geo.n + row;
         if (io.epilogue == kEpiResidual) {
@@ -941,6 +984,8 @@ __device__ TMB_GEMV_CALL void gemv_stage(Ctx& c, const GemvGeo& geo, const GemvI
   // an epilogue is spread as one eighth per task instead of stalling every task.
   PendingEpilogue<B> pending;
   pending.task = -1;
+  PendingAr<B> ar;
+  ar.task = -1;
   for (int t = fifo_pop(c); t >= 0; t = fifo_pop(c)) {
     const int rt = t;
 #if TMB_GEMV_MMA
@@ -1006,7 +1051,7 @@ __device__ TMB_GEMV_CALL void gemv_stage(Ctx& c, const GemvGeo& geo, const GemvI
     __syncwarp();
     if (lane == 0) mbar_arrive(c.pfull(buf));
     if (pending.task >= 0) {
-      gemv_epilogue<B, X>(c, geo, io, pending, lane, best_val, best_idx);
+      gemv_epilogue<B, X>(c, geo, io, pending, lane, best_val, best_idx, ar);
       pending.task = -1;
     }
     if (owner) {
@@ -1019,7 +1064,8 @@ __device__ TMB_GEMV_CALL void gemv_stage(Ctx& c, const GemvGeo& geo, const GemvI
     ++task_seq;
     ++gemv_seq;
   }
-  if (pending.task >= 0) gemv_epilogue<B, X>(c, geo, io, pending, lane, best_val, best_idx);
+  if (pending.task >= 0) gemv_epilogue<B, X>(c, geo, io, pending, lane, best_val, best_idx, ar);
+  if ((X & kXTp) && ar.task >= 0) tp_finish_tile<B>(c, geo, io, ar, lane);
   c.slot = slot;
   c.phase = phase;
   c.task_seq = task_seq;
@@ -1047,6 +1093,11 @@ __device__ TMB_GEMV_CALL void gemv_stage(Ctx& c, const GemvGeo& geo, const GemvI
 // CTA 0 to global memory for the host.
 static __device__ __noinline__ void route_token(Ctx& c, int layer) {
   const MegaParams& p = c.p;
+  // probabilities of all experts in shared memory (the activation-row area is free between
+  // stages), then every value's rank by counting: rank = how many experts beat it (larger
+  // probability, or equal and smaller index). The k experts of rank < k are the top-k in
+  // descending order, found by all lanes at once instead of k sequential arg-max rounds.
+  float* prob = reinterpret_cast<float*>(c.xs());
   if (c.warp == 0) {
     constexpr int kPerLane = 8;   // experts <= 256
     const unsigned short* logits = reinterpret_cast<const unsigned short*>(p.router_logits);
@@ -1069,42 +1120,41 @@ static __device__ __noinline__ void route_token(Ctx& c, int layer) {
 #pragma unroll
     for (int m = 16; m; m >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, m);
 #pragma unroll
-    for (int j = 0; j < kPerLane; ++j) v[j] = c.lane + 32 * j < p.experts ? v[j] / sum : -1.f;
-    float chosen_w[kMaxTopK];
-    int chosen_e[kMaxTopK];
-    float total = 0.f;
-#pragma unroll
-    for (int s = 0; s < kMaxTopK; ++s) {
-      float bv = -1.f;
-      int bi = 0x7fffffff;
-      if (s < p.topk) {
-#pragma unroll
-        for (int j = 0; j < kPerLane; ++j)
-          if (v[j] > bv) { bv = v[j]; bi = c.lane + 32 * j; }   // ascending j: the smaller index wins a tie
-#pragma unroll
-        for (int m = 16; m; m >>= 1) {
-          const float ov = __shfl_xor_sync(0xffffffffu, bv, m);
-          const int oi = __shfl_xor_sync(0xffffffffu, bi, m);
-          if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
-        }
-#pragma unroll
-        for (int j = 0; j < kPerLane; ++j)
-          if (c.lane + 32 * j == bi) v[j] = -1.f;   // taken
-        total += bv;
-      }
-      chosen_w[s] = bv;
-      chosen_e[s] = s < p.topk ? bi : 0;
+    for (int j = 0; j < kPerLane; ++j) {
+      v[j] = v[j] / sum;
+      if (c.lane + 32 * j < p.experts) prob[c.lane + 32 * j] = v[j];
     }
-    if (c.lane == 0) {
+    __syncwarp();
+    float total = 0.f;   // sum of the chosen probabilities, in rank order
 #pragma unroll
-      for (int s = 0; s < kMaxTopK; ++s) {
-        const float w = s < p.topk ? chosen_w[s] / total : 0.f;
-        c.route_e()[s] = chosen_e[s];
-        c.route_w()[s] = w;
-        if (blockIdx.x == 0 && s < p.topk) {
-          p.route_idx[layer * p.topk + s] = chosen_e[s];
-          p.route_w[layer * p.topk + s] = w;
+    for (int j = 0; j < kPerLane; ++j) {
+      const int e = c.lane + 32 * j;
+      int rank = 0;
+      if (e < p.experts) {
+        for (int o = 0; o < p.experts; ++o) {
+          const float ov = prob[o];
+          rank += (ov > v[j] || (ov == v[j] && o < e)) ? 1 : 0;
         }
+      } else {
+        rank = 0x7fffffff;
+      }
+      if (rank < p.topk) {
+        c.route_e()[rank] = e;
+        c.route_w()[rank] = v[j];
+      }
+    }
+    __syncwarp();
+    for (int s = 0; s < p.topk; ++s) total += c.route_w()[s];
+    __syncwarp();
+    if (c.lane < kMaxTopK) {
+      const int s = c.lane;
+      const float w = s < p.topk ? c.route_w()[s] / total : 0.f;
+      const int e = s < p.topk ? c.route_e()[s] : 0;
+      c.route_w()[s] = w;
+      c.route_e()[s] = e;
+      if (blockIdx.x == 0 && s < p.topk) {
+        p.route_idx[layer * p.topk + s] = e;
+        p.route_w[layer * p.topk + s] = w;
       }
     }
   }
@@ -1128,11 +1178,17 @@ __device__ __noinline__ void moe_down_stage(Ctx& c, const GemvGeo& geo, bool tr,
   {
     // rows: h[slot][k_src] -> shared memory in A-fragment order, pad columns zero
     const int chunks = geo.k >> 3, src_chunks = geo.k_src >> 3;
-    for (int slot = 0; slot < topk; ++slot) {
-      const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.h) + size_t(slot) * geo.k_src);
-      uint32_t* row = reinterpret_cast<uint32_t*>(c.xs() + size_t(slot) * pitch_bytes);
-      for (int i = c.tid; i < chunks; i += kConsumerThreads)
-        store_row_chunk(row, i, i < src_chunks ? __ldcg(src + i) : make_uint4(0u, 0u, 0u, 0u));
+    for (int i = c.tid; i < chunks; i += kConsumerThreads) {
+      uint4 v[kMaxTopK];   // all rows' loads in flight together: one L2 round trip, not one per row
+#pragma unroll
+      for (int slot = 0; slot < kMaxTopK; ++slot) {
+        v[slot] = make_uint4(0u, 0u, 0u, 0u);
+        if (slot < topk && i < src_chunks)
+          v[slot] = __ldcg(reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.h) + size_t(slot) * geo.k_src) + i);
+      }
+#pragma unroll
+      for (int slot = 0; slot < kMaxTopK; ++slot)
+        if (slot < topk) store_row_chunk(reinterpret_cast<uint32_t*>(c.xs() + size_t(slot) * pitch_bytes), i, v[slot]);
     }
     consumer_sync();
   }

@@ -45,7 +45,7 @@ struct PlanSpec {
   // execution
   int grid = 0, slots = 0, static_quarters = 0, diag = 0, attn_min_slots = 4;
   bool write_logits = true;
-  GemvGeo geo[kNumGemv];
+  GemvGeo geo[kNumGemv] = {};   // stages a plan does not have (kRouter in a dense plan) stay zero
   // buffer table
   std::vector<BufferSpec> buffers;
   int tokens = -1, rope_cos = -1, rope_sin = -1, block_table = -1, context_base = -1;
