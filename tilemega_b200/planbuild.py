@@ -11,6 +11,7 @@ from __future__ import annotations
 
 import hashlib
 import json
+import os
 import shutil
 from pathlib import Path
 
@@ -71,11 +72,18 @@ def emit_plan(config: dict, out_dir: str | Path, **options) -> Path:
     out_dir.mkdir(parents=True, exist_ok=True)
     library = build_library()
     target = out_dir / f"tilemega_b200_{digest}.so"
+    sidecar = Path(str(target) + ".plan.json")
+    # Several processes (the ranks of one job) may emit the same plan at once: every file
+    # appears under its final name complete or not at all, and an identical plan is left alone.
+    unique = f".{os.getpid()}.tmp"
     if not target.exists() or target.stat().st_mtime < library.stat().st_mtime:
-        tmp = target.with_suffix(".so.tmp")
+        tmp = Path(str(target) + unique)
         shutil.copyfile(library, tmp)
-        tmp.replace(target)
-    Path(str(target) + ".plan.json").write_text(text)
+        os.replace(tmp, target)
+    if not sidecar.exists() or sidecar.read_text() != text:
+        tmp = Path(str(sidecar) + unique)
+        tmp.write_text(text)
+        os.replace(tmp, sidecar)
     return target
 
 
