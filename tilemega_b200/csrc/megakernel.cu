@@ -395,11 +395,18 @@ __device__ __forceinline__ void stream_gemv(Ctx& c, const GemvGeo& geo, const vo
   const int dealt = static_share(c.p, geo.ntasks);
   for (int j = 0; j < dealt && !c.dead; ++j)
     stream_gemv_task(c, geo, w, int(blockIdx.x) + j * c.p.grid, page_bytes, policy);
-  int t = dealt * c.p.grid + c.pending;
-  while (t < geo.ntasks && !c.dead) {
+  // Tasks are claimed in chunks of geo.claim_chunk (about 64 KB of pages): the claim for the
+  // next chunk is in flight while this one is copied, and its round trip to L2 and back
+  // (~1 us) must not be longer than that copying, or short tasks wait for their ids.
+  const int chunk_tasks = geo.claim_chunk;
+  int chunk = c.pending;
+  while (dealt * c.p.grid + chunk * chunk_tasks < geo.ntasks && !c.dead) {
     const int upcoming = claim(c, c.inst);
-    stream_gemv_task(c, geo, w, t, page_bytes, policy);
-    t = dealt * c.p.grid + upcoming;
+    for (int j = 0; j < chunk_tasks; ++j) {
+      const int t = dealt * c.p.grid + chunk * chunk_tasks + j;
+      if (t < geo.ntasks) stream_gemv_task(c, geo, w, t, page_bytes, policy);
+    }
+    chunk = upcoming;
   }
   stream_close(c);
 }
@@ -412,13 +419,18 @@ __device__ __forceinline__ void stream_expert_gate_up(Ctx& c, const GemvGeo& geo
   const uint32_t page_bytes = uint32_t(kTileN) * uint32_t(geo.tile_k) * 2u;
   const unsigned char* w = static_cast<const unsigned char*>(stack);
   const int total = c.p.topk * geo.ntasks;
-  int t = c.pending;
-  while (t < total && !c.dead) {
+  const int chunk_tasks = geo.claim_chunk;
+  int chunk = c.pending;
+  while (chunk * chunk_tasks < total && !c.dead) {
     const int upcoming = claim(c, c.inst);
-    const int slot = t / geo.ntasks, tile = t - slot * geo.ntasks;
-    stream_pages(c, geo, w + (size_t(expert[slot]) * geo.ntasks + tile) * size_t(geo.pages_per_task) * page_bytes, t,
-                 page_bytes, policy);
-    t = upcoming;
+    for (int j = 0; j < chunk_tasks; ++j) {
+      const int t = chunk * chunk_tasks + j;
+      if (t >= total) break;
+      const int slot = t / geo.ntasks, tile = t - slot * geo.ntasks;
+      stream_pages(c, geo, w + (size_t(expert[slot]) * geo.ntasks + tile) * size_t(geo.pages_per_task) * page_bytes, t,
+                   page_bytes, policy);
+    }
+    chunk = upcoming;
   }
   stream_close(c);
 }
@@ -1094,9 +1106,10 @@ __device__ TMB_GEMV_CALL void gemv_stage(Ctx& c, const GemvGeo& geo, const GemvI
 static __device__ __noinline__ void route_token(Ctx& c, int layer) {
   const MegaParams& p = c.p;
   // probabilities of all experts in shared memory (the activation-row area is free between
-  // stages), then every value's rank by counting: rank = how many experts beat it (larger
+  // stages), then every expert's rank by counting: rank = how many experts beat it (larger
   // probability, or equal and smaller index). The k experts of rank < k are the top-k in
-  // descending order, found by all lanes at once instead of k sequential arg-max rounds.
+  // descending order. One thread per expert does the counting: a single warp doing k
+  // sequential arg-max rounds, or all the counting, issues too slowly next to nothing.
   float* prob = reinterpret_cast<float*>(c.xs());
   if (c.warp == 0) {
     constexpr int kPerLane = 8;   // experts <= 256
@@ -1120,42 +1133,36 @@ static __device__ __noinline__ void route_token(Ctx& c, int layer) {
 #pragma unroll
     for (int m = 16; m; m >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, m);
 #pragma unroll
-    for (int j = 0; j < kPerLane; ++j) {
-      v[j] = v[j] / sum;
-      if (c.lane + 32 * j < p.experts) prob[c.lane + 32 * j] = v[j];
+    for (int j = 0; j < kPerLane; ++j)
+      if (c.lane + 32 * j < p.experts) prob[c.lane + 32 * j] = v[j] / sum;
+  }
+  consumer_sync();
+  if (c.tid < p.experts) {
+    const float mine = prob[c.tid];
+    int rank = 0;
+#pragma unroll 8
+    for (int o = 0; o < p.experts; ++o) {
+      const float other = prob[o];   // every thread reads the same word: a broadcast
+      rank += (other > mine || (other == mine && o < c.tid)) ? 1 : 0;
     }
-    __syncwarp();
+    if (rank < p.topk) {
+      c.route_e()[rank] = c.tid;
+      c.route_w()[rank] = mine;
+    }
+  }
+  consumer_sync();
+  if (c.tid < kMaxTopK) {
     float total = 0.f;   // sum of the chosen probabilities, in rank order
-#pragma unroll
-    for (int j = 0; j < kPerLane; ++j) {
-      const int e = c.lane + 32 * j;
-      int rank = 0;
-      if (e < p.experts) {
-        for (int o = 0; o < p.experts; ++o) {
-          const float ov = prob[o];
-          rank += (ov > v[j] || (ov == v[j] && o < e)) ? 1 : 0;
-        }
-      } else {
-        rank = 0x7fffffff;
-      }
-      if (rank < p.topk) {
-        c.route_e()[rank] = e;
-        c.route_w()[rank] = v[j];
-      }
-    }
-    __syncwarp();
     for (int s = 0; s < p.topk; ++s) total += c.route_w()[s];
-    __syncwarp();
-    if (c.lane < kMaxTopK) {
-      const int s = c.lane;
-      const float w = s < p.topk ? c.route_w()[s] / total : 0.f;
-      const int e = s < p.topk ? c.route_e()[s] : 0;
-      c.route_w()[s] = w;
-      c.route_e()[s] = e;
-      if (blockIdx.x == 0 && s < p.topk) {
-        p.route_idx[layer * p.topk + s] = e;
-        p.route_w[layer * p.topk + s] = w;
-      }
+    const int s = c.tid;
+    const float w = s < p.topk ? c.route_w()[s] / total : 0.f;
+    const int e = s < p.topk ? c.route_e()[s] : 0;
+    __syncwarp(0xffu);   // every lane has read all weights before any is overwritten
+    c.route_w()[s] = w;
+    c.route_e()[s] = e;
+    if (blockIdx.x == 0 && s < p.topk) {
+      p.route_idx[layer * p.topk + s] = e;
+      p.route_w[layer * p.topk + s] = w;
     }
   }
   consumer_sync();

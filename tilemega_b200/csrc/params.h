@@ -34,6 +34,7 @@ struct GemvGeo {
   int pages_per_task;  // k / tile_k: a task is one 8-row tile over the whole reduction
   int last_page_bytes; // bytes of a task's last page that are copied: k_src rounded up to 256 columns (a warp's share)
   int ntasks;          // n / 8
+  int claim_chunk;     // tasks taken per claim: about 64 KB of pages, so a claim's round trip hides behind the copies
 };
 
 struct LayerPtrs {

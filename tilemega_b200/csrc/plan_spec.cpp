@@ -60,6 +60,10 @@ GemvGeo MakeGeo(const char* what, int n, int k, const Json& overrides) {
   const int last_columns = (g.k_src - (kt - 1) * g.tile_k + 255) / 256 * 256;
   g.last_page_bytes = kTileN * last_columns * 2;
   g.ntasks = n / kTileN;
+  const int task_bytes = (kt - 1) * kTileN * g.tile_k * 2 + g.last_page_bytes;
+  g.claim_chunk = std::max(1, std::min(8, (65536 + task_bytes - 1) / task_bytes));
+  if (overrides.has(what)) g.claim_chunk = int(overrides.at(what).integer("claim_chunk", g.claim_chunk));
+  if (g.claim_chunk < 1 || g.claim_chunk > 64) throw std::invalid_argument(std::string(what) + ": claim_chunk must lie in [1, 64]");
   return g;
 }
 
