@@ -224,7 +224,7 @@ def run_ours(args) -> None:
     capacity = (max(contexts) + total_steps + 17) // 16 * 16
     max_blocks = capacity // 16
     num_blocks = batch * max_blocks + 32
-    plan_dir = ROOT / "gpurun_out" / "plans" if (ROOT / "gpurun_out").exists() else Path("/tmp/tilemega_b200_plans")
+    plan_dir = Path(os.environ.get("TILEMEGA_PLAN_DIR", "/tmp/tilemega_b200_plans"))
     geometry = json.loads(args.geometry) if args.geometry else None
     options = dict(batch_lo=batch, batch_hi=batch, capacity=capacity, kv_layout="paged", num_blocks=num_blocks,
                    write_logits=False, geometry=geometry, slots=args.slots, tp=tp)

@@ -237,3 +237,19 @@ def test_eight_query_heads_per_kv_head(plan_dir):
     tokens, logits = run.greedy(prompt, new_tokens)
     assert_as_accurate_as_reference_bf16(config, weights, prompt, tokens, logits, capacity, "8 query heads per KV head")
     run.close()
+
+
+def test_wide_batch_takes_the_down_reduction_in_parts(plan_dir):
+    """Batch 8 with a down reduction of four pages: its rows do not fit beside the ring at once,
+    so the stage runs as two parts with fp32 running sums in between (and the RMSNorm stages
+    re-read their rows instead of parking them)."""
+    config = dict(synthetic.TINY, intermediate_size=8192)
+    batch, prompt_len, new_tokens, capacity = 8, 9, 4, 32
+    weights = bf16_weights(config)
+    prompt = synthetic.seeded_tokens(batch, prompt_len, config["vocab_size"], seed=6)
+    run = GpuRun(config, weights, batch, capacity, plan_dir)
+    tokens, logits = run.greedy(prompt, new_tokens)
+    assert_as_accurate_as_reference_bf16(config, weights, prompt, tokens, logits, capacity, "split down, batch 8")
+    looped, _ = run.greedy(prompt, new_tokens, stepwise=False)
+    assert torch.equal(looped, tokens)
+    run.close()

@@ -378,7 +378,7 @@ __device__ __forceinline__ void stream_pages(Ctx& c, const GemvGeo& geo, const u
 // task t = one row tile over the whole reduction: its pages start at page t * pages_per_task
 __device__ __forceinline__ void stream_gemv_task(Ctx& c, const GemvGeo& geo, const unsigned char* weights, int t,
                                                  uint32_t page_bytes, uint64_t policy) {
-  stream_pages(c, geo, weights + size_t(t) * size_t(geo.pages_per_task) * page_bytes, t, page_bytes, policy);
+  stream_pages(c, geo, weights + (size_t(t) * size_t(geo.task_pages) + size_t(geo.page0)) * page_bytes, t, page_bytes, policy);
 }
 
 // static_quarters/4 of a CTA's even share of a stage are dealt statically (task
@@ -537,7 +537,11 @@ __device__ void streamer_main(Ctx& c) {
         stream_expert_down(c, p.geo[kDown], lp.down, expert, policy);
       } else {
         stream_gemv(c, p.geo[kGateUp], lp.gate_up, policy);
-        stream_gemv(c, p.geo[kDown], lp.down, policy);
+        if (p.down_splits > 1) {
+          for (int part = 0; part < p.down_splits; ++part) stream_gemv(c, p.down_part[part], lp.down, policy);
+        } else {
+          stream_gemv(c, p.geo[kDown], lp.down, policy);
+        }
       }
       if (c.dead || ld_relaxed(p.status + kStFired) != 0) return;
     }
@@ -576,6 +580,7 @@ struct GemvIo {
   void* out;           // kEpiStore: bf16 [B][n]; kEpiResidual: x; kEpiSwiGLU: h [B][n/2]; kEpiHead: logits
   unsigned long long* ready;   // kEpiStore: per-group counters bumped once per stored row tile (or null)
   int tiles_per_group;
+  const float* partial_in;     // fp32 sums of the earlier parts of a split reduction, added before any rounding (or null)
   int ar_region;               // kEpiResidualAllReduce: which of the two packet regions (0: o, 1: down)
   uint32_t ar_epoch;           // ... and the epoch its packets carry (never 0, grows with every all-reduce)
 };
@@ -605,10 +610,15 @@ __device__ __forceinline__ void store_row_chunk(uint32_t* row, int i, const uint
 // Columns [k_src, k) do not exist in the source rows (the weights are zero-padded
 // there): they are staged as zeros.
 template <int B>
-__device__ __forceinline__ void stage_rows(Ctx& c, const GemvIo& io, int k, int k_src) {
+__device__ __forceinline__ void stage_rows(Ctx& c, const GemvIo& io, const GemvGeo& geo) {
   const MegaParams& p = c.p;
+  const int k = geo.k, k_src = geo.k_src;
   const int chunks = k >> 3, src_chunks = k_src >> 3;
   const int pitch = chunks + 1;   // rows are k + 8 elements apart, so the batch rows of a block sit on distinct banks
+  // A wide batch has no room to park the raw rows next to the normalised ones: the second
+  // pass reads them from global memory again (an L2 hit) and only the norm weights are kept.
+  constexpr bool kWide = B > 4;
+  constexpr int kNormRow = kWide ? B : 2 * B;
   uint4* xs4 = reinterpret_cast<uint4*>(c.xs());
   const uint4* nw = reinterpret_cast<const uint4*>(io.norm);
   float ss[B];
@@ -617,9 +627,9 @@ __device__ __forceinline__ void stage_rows(Ctx& c, const GemvIo& io, int k, int 
     const uint4* src;
     if (io.embed) {
       const int tok = min(max(c.tok()[b], 0), p.vocab - 1);
-      src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(io.src) + size_t(tok) * k_src);
+      src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(io.src) + size_t(tok) * geo.src_stride);
     } else {
-      src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(io.src) + size_t(b) * k_src);
+      src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(io.src) + size_t(b) * geo.src_stride + geo.src_off);
     }
     const bool own = io.embed && (b % p.grid) == int(blockIdx.x);
     uint4* xg = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.x) + size_t(b) * k_src);
@@ -629,8 +639,8 @@ __device__ __forceinline__ void stage_rows(Ctx& c, const GemvIo& io, int k, int 
       if (i < src_chunks) v = io.embed ? __ldg(src + i) : __ldcg(src + i);
       if (own && i < src_chunks) xg[i] = v;
       if (io.norm) {
-        if (b == 0) xs4[2 * B * pitch + i] = i < src_chunks ? __ldg(nw + i) : make_uint4(0u, 0u, 0u, 0u);
-        xs4[(B + b) * pitch + i] = v;
+        if (b == 0) xs4[kNormRow * pitch + i] = i < src_chunks ? __ldg(nw + i) : make_uint4(0u, 0u, 0u, 0u);
+        if (!kWide) xs4[(B + b) * pitch + i] = v;
         float f[8];
         unpack8(v, f);
 #pragma unroll
@@ -656,10 +666,19 @@ __device__ __forceinline__ void stage_rows(Ctx& c, const GemvIo& io, int k, int 
 #pragma unroll
       for (int w = 0; w < kConsumerWarps; ++w) total += c.wsum()[b * 8 + w];
       const float inv = 1.0f / sqrtf(total / float(k_src) + p.eps);
+      const uint4* again = nullptr;
+      if (kWide) {
+        const int tok = io.embed ? min(max(c.tok()[b], 0), p.vocab - 1) : 0;
+        again = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(io.src) +
+                                               (io.embed ? size_t(tok) * geo.src_stride : size_t(b) * geo.src_stride + geo.src_off));
+      }
       for (int i = c.tid; i < chunks; i += kConsumerThreads) {
         float f[8], w[8];
-        unpack8(xs4[(B + b) * pitch + i], f);    // both written by this same thread above
-        unpack8(xs4[2 * B * pitch + i], w);
+        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+        if (!kWide) raw = xs4[(B + b) * pitch + i];    // written by this same thread above
+        else if (i < src_chunks) raw = io.embed ? __ldg(again + i) : __ldcg(again + i);
+        unpack8(raw, f);
+        unpack8(xs4[kNormRow * pitch + i], w);
         uint32_t o[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -907,8 +926,11 @@ __device__ __forceinline__ void gemv_epilogue(Ctx& c, const GemvGeo& geo, const 
       float v = 0.f;
 #pragma unroll
       for (int w = 0; w < kConsumerWarps; ++w) v += red[((e.buf * 8 + w) * 8 + r) * B + b];
+      if (io.partial_in) v += __ldcg(io.partial_in + size_t(b) * geo.n + row);   // earlier parts of a split reduction
       const float vb = bf16_round(v);
-      if (io.epilogue == kEpiSwiGLU) {
+      if (io.epilogue == kEpiPartial) {
+        static_cast<float*>(io.out)[size_t(b) * geo.n + row] = v;
+      } else if (io.epilogue == kEpiSwiGLU) {
         // rows 0..3 of the page are gate rows, rows 4..7 the matching up rows
         const float up = __shfl_down_sync(mask, vb, 4);
         if (r < 4) {
@@ -972,7 +994,7 @@ __device__ __forceinline__ void gemv_epilogue(Ctx& c, const GemvGeo& geo, const 
 template <int B, int X>
 __device__ TMB_GEMV_CALL void gemv_stage(Ctx& c, const GemvGeo& geo, const GemvIo& io, bool tr, int stage) {
   const MegaParams& p = c.p;
-  stage_rows<B>(c, io, geo.k, geo.k_src);
+  stage_rows<B>(c, io, geo);
   trace_mark(c, tr, stage, 2);
   // per-warp running argmax (each warp runs every eighth epilogue); merged by the caller
   float best_val[EpiPasses<B>::value];
@@ -1623,7 +1645,7 @@ __device__ void consumer_main(Ctx& c) {
         if (!grid_wait(c)) return;
       }
       trace_mark(c, tr, stage, 1);
-      io = GemvIo{l == 0 ? p.embed : p.x, lp.norm1, l == 0, kEpiStore, p.qkv, p.qkv_ready, (GQ + 2) * D / kTileN, 0, 0u};
+      io = GemvIo{l == 0 ? p.embed : p.x, lp.norm1, l == 0, kEpiStore, p.qkv, p.qkv_ready, (GQ + 2) * D / kTileN, nullptr, 0, 0u};
       gemv_stage<B, X>(c, p.geo[kQkv], io, tr, stage++);
       // no grid barrier here: an attention task needs the QKV rows of its own KV head
       // only, and waits for that group's row-tile count (qkv_ready)
@@ -1634,7 +1656,7 @@ __device__ void consumer_main(Ctx& c) {
       trace_mark(c, tr, stage, 0);
       if (!grid_wait(c)) return;
       trace_mark(c, tr, stage, 1);
-      io = GemvIo{p.attn, nullptr, 0, residual_kind, p.x, nullptr, 1, 0, ar_epoch0 + uint32_t(2 * l)};
+      io = GemvIo{p.attn, nullptr, 0, residual_kind, p.x, nullptr, 1, nullptr, 0, ar_epoch0 + uint32_t(2 * l)};
       gemv_stage<B, X>(c, p.geo[kOProj], io, tr, stage++);
       grid_arrive(c);
       trace_mark(c, tr, stage, 0);
@@ -1643,7 +1665,7 @@ __device__ void consumer_main(Ctx& c) {
       if ((X & kXMoe) && p.experts) {
         // mixture of experts: router scores, top-k, then the chosen experts only
         if constexpr ((X & kXMoe) != 0 && B == 1) {
-          io = GemvIo{p.x, lp.norm2, 0, kEpiStore, p.router_logits, nullptr, 1, 0, 0u};
+          io = GemvIo{p.x, lp.norm2, 0, kEpiStore, p.router_logits, nullptr, 1, nullptr, 0, 0u};
           gemv_stage<B, X>(c, p.geo[kRouter], io, tr, stage++);
           grid_arrive(c);
           trace_mark(c, tr, stage, 0);
@@ -1652,7 +1674,7 @@ __device__ void consumer_main(Ctx& c) {
           route_token(c, l);
           // task t = (expert slot, row tile): with one token the SwiGLU epilogue's output
           // index t * 4 + r is row `slot` of h[topk][inter]
-          io = GemvIo{p.x, lp.norm2, 0, kEpiSwiGLU, p.h, nullptr, 1, 0, 0u};
+          io = GemvIo{p.x, lp.norm2, 0, kEpiSwiGLU, p.h, nullptr, 1, nullptr, 0, 0u};
           gemv_stage<B, X>(c, p.geo[kGateUp], io, tr, stage++);
           grid_arrive(c);
           trace_mark(c, tr, stage, 0);
@@ -1664,21 +1686,38 @@ __device__ void consumer_main(Ctx& c) {
         lp = upcoming;
         continue;
       }
-      io = GemvIo{p.x, lp.norm2, 0, kEpiSwiGLU, p.h, nullptr, 1, 0, 0u};
+      io = GemvIo{p.x, lp.norm2, 0, kEpiSwiGLU, p.h, nullptr, 1, nullptr, 0, 0u};
       gemv_stage<B, X>(c, p.geo[kGateUp], io, tr, stage++);
       grid_arrive(c);
       trace_mark(c, tr, stage, 0);
       if (!grid_wait(c)) return;
       trace_mark(c, tr, stage, 1);
-      io = GemvIo{p.h, nullptr, 0, residual_kind, p.x, nullptr, 1, 1, ar_epoch0 + uint32_t(2 * l + 1)};
-      gemv_stage<B, X>(c, p.geo[kDown], io, tr, stage++);
-      grid_arrive(c);
+      if (p.down_splits > 1) {
+        // the reduction in parts: each part's rows fit in shared memory; the fp32 sums of the
+        // parts so far wait in global memory, and only the last part rounds and adds the residual
+        for (int part = 0; part < p.down_splits; ++part) {
+          const bool last = part + 1 == p.down_splits;
+          io = GemvIo{p.h, nullptr, 0, last ? residual_kind : int(kEpiPartial), last ? p.x : static_cast<void*>(p.down_partial),
+                      nullptr, 1, part ? p.down_partial : nullptr, 1, ar_epoch0 + uint32_t(2 * l + 1)};
+          gemv_stage<B, X>(c, p.down_part[part], io, tr, stage++);
+          grid_arrive(c);
+          if (!last) {
+            trace_mark(c, tr, stage, 0);
+            if (!grid_wait(c)) return;
+            trace_mark(c, tr, stage, 1);
+          }
+        }
+      } else {
+        io = GemvIo{p.h, nullptr, 0, residual_kind, p.x, nullptr, 1, nullptr, 1, ar_epoch0 + uint32_t(2 * l + 1)};
+        gemv_stage<B, X>(c, p.geo[kDown], io, tr, stage++);
+        grid_arrive(c);
+      }
       lp = upcoming;
     }
     trace_mark(c, tr, stage, 0);
     if (!grid_wait(c)) return;
     trace_mark(c, tr, stage, 1);
-    GemvIo io{p.x, p.final_norm, 0, kEpiHead, p.logits, nullptr, 1, 0, 0u};
+    GemvIo io{p.x, p.final_norm, 0, kEpiHead, p.logits, nullptr, 1, nullptr, 0, 0u};
     gemv_stage<B, X>(c, p.geo[kHead], io, tr, stage);
     consumer_sync();
     if (c.tid < B) {

@@ -19,9 +19,11 @@ constexpr int kMaxTp = 8;                               // tensor-parallel ranks
 
 // kRouter exists in mixture-of-experts plans only; there kGateUp / kDown describe ONE expert.
 enum StageKind : int { kQkv = 0, kOProj = 1, kGateUp = 2, kDown = 3, kHead = 4, kRouter = 5, kNumGemv = 6 };
-constexpr int kMaxTopK = 8;                             // experts per token
+constexpr int kMaxTopK = 8;
+constexpr int kMaxDownSplits = 8;                       // stages a down projection's reduction may be cut into                             // experts per token
 // kEpiResidualAllReduce: kEpiResidual after the ranks' bf16 partial sums are added in rank order.
-enum Epilogue : int { kEpiStore = 0, kEpiResidual = 1, kEpiSwiGLU = 2, kEpiHead = 3, kEpiResidualAllReduce = 4 };
+// kEpiPartial: the fp32 sums of one part of a split reduction, kept in global memory for the next part.
+enum Epilogue : int { kEpiStore = 0, kEpiResidual = 1, kEpiSwiGLU = 2, kEpiHead = 3, kEpiResidualAllReduce = 4, kEpiPartial = 5 };
 
 // Geometry of one GEMV stage. Weights are packed [N/8][K/tile_k][8*tile_k]
 // with the 8x64 128-byte XOR swizzle of the reference's tile_pages recipe
@@ -34,6 +36,11 @@ struct GemvGeo {
   int pages_per_task;  // k / tile_k: a task is one 8-row tile over the whole reduction
   int last_page_bytes; // bytes of a task's last page that are copied: k_src rounded up to 256 columns (a warp's share)
   int ntasks;          // n / 8
+  // A stage may cover only pages [page0, page0 + pages_per_task) of every task's run of
+  // task_pages pages (the reduction of a wide-batch down projection is taken in several
+  // stages, so that its activation rows fit in shared memory); its rows then start src_off
+  // columns into source rows that are src_stride columns apart.
+  int page0, task_pages, src_off, src_stride;
   int claim_chunk;     // tasks taken per claim: about 64 KB of pages, so a claim's round trip hides behind the copies
 };
 
@@ -86,6 +93,8 @@ struct MegaParams {
   unsigned long long bar_base;     // grid-barrier arrivals before this launch
   unsigned long long watchdog_ns;  // per-wait limit
   GemvGeo geo[kNumGemv];
+  int down_splits;                       // 1: geo[kDown] is the whole stage; else down_part[0..down_splits-1] run in turn
+  GemvGeo down_part[kMaxDownSplits];
   // external buffers
   int* tokens;                 // [B][capacity]
   const void* rope_cos;        // bf16 [capacity][D]
@@ -106,6 +115,7 @@ struct MegaParams {
   void* router_logits;         // bf16 [B][experts]
   int* route_idx;              // [layers][topk] chosen experts of the last step, in rank order (batch 1)
   float* route_w;              // [layers][topk] their routing weights
+  float* down_partial;         // f32 [B][H]: running sums of a split down projection
   float* attn_part;            // [grid + B*Hkv][Gq][D+2]
   unsigned* attn_cnt;          // [B*Hkv]
   unsigned long long* qkv_ready;  // [Hkv] QKV row tiles stored per KV-head group (monotonic within a launch)

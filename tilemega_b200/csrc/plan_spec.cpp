@@ -60,6 +60,10 @@ GemvGeo MakeGeo(const char* what, int n, int k, const Json& overrides) {
   const int last_columns = (g.k_src - (kt - 1) * g.tile_k + 255) / 256 * 256;
   g.last_page_bytes = kTileN * last_columns * 2;
   g.ntasks = n / kTileN;
+  g.page0 = 0;
+  g.task_pages = kt;
+  g.src_off = 0;
+  g.src_stride = g.k_src;
   const int task_bytes = (kt - 1) * kTileN * g.tile_k * 2 + g.last_page_bytes;
   g.claim_chunk = std::max(1, std::min(8, (65536 + task_bytes - 1) / task_bytes));
   if (overrides.has(what)) g.claim_chunk = int(overrides.at(what).integer("claim_chunk", g.claim_chunk));
@@ -71,7 +75,8 @@ GemvGeo MakeGeo(const char* what, int n, int k, const Json& overrides) {
 
 int PlanSpec::max_k() const {
   int widest = 0;
-  for (int s = 0; s < kNumGemv; ++s) widest = std::max(widest, geo[s].k);
+  for (int s = 0; s < kNumGemv; ++s)
+    widest = std::max(widest, s == kDown && down_splits > 1 ? down_part[0].k : geo[s].k);   // columns staged at once
   return widest;
 }
 
@@ -168,6 +173,29 @@ PlanSpec PlanSpec::FromJson(const Json& plan) {
   s.geo[kGateUp] = MakeGeo("gate_up", 2 * s.inter, s.hidden, geometry);
   s.geo[kDown] = MakeGeo("down", s.hidden, s.inter, geometry);
   s.geo[kHead] = MakeGeo("lm_head", s.head_rows, s.hidden, geometry);
+  // A wide batch times a long down reduction does not fit in shared memory beside the ring
+  // (8 rows x 14336 columns are 229 KB): the reduction is then cut into parts of whole pages
+  // whose rows take about 80 KB, one stage per part, fp32 running sums in global memory.
+  if (!s.experts) {
+    const GemvGeo& down = s.geo[kDown];
+    const int budget_columns = 81920 / (2 * s.batch_hi) - 8;
+    const int part_pages = std::max(1, std::min(down.pages_per_task, budget_columns / down.tile_k));
+    s.down_splits = (down.pages_per_task + part_pages - 1) / part_pages;
+    if (s.down_splits > kMaxDownSplits) throw std::invalid_argument("down projection would need more than 8 parts");
+    for (int i = 0; i < s.down_splits; ++i) {
+      GemvGeo part = down;
+      part.page0 = i * part_pages;
+      part.pages_per_task = std::min(part_pages, down.pages_per_task - part.page0);
+      part.k = part.pages_per_task * down.tile_k;
+      part.src_off = part.page0 * down.tile_k;
+      part.k_src = std::min(part.k, down.k_src - part.src_off);
+      const bool last = i + 1 == s.down_splits;
+      part.last_page_bytes = last ? down.last_page_bytes : kTileN * down.tile_k * 2;
+      const int task_bytes = (part.pages_per_task - 1) * kTileN * down.tile_k * 2 + part.last_page_bytes;
+      part.claim_chunk = std::max(1, std::min(8, (65536 + task_bytes - 1) / task_bytes));
+      s.down_part[i] = part;
+    }
+  }
   if (s.experts) {
     s.geo[kRouter] = MakeGeo("router", s.experts, s.hidden, geometry);
     if (s.geo[kDown].pages_per_task != 1)

@@ -45,6 +45,8 @@ struct PlanSpec {
   // execution
   int grid = 0, slots = 0, static_quarters = 0, diag = 0, attn_min_slots = 4;
   bool write_logits = true;
+  int down_splits = 1;
+  GemvGeo down_part[kMaxDownSplits] = {};
   GemvGeo geo[kNumGemv] = {};   // stages a plan does not have (kRouter in a dense plan) stay zero
   // buffer table
   std::vector<BufferSpec> buffers;
@@ -59,7 +61,7 @@ struct PlanSpec {
 
   int qkv_rows() const { return (heads + 2 * kv_heads) * head_dim; }
   int max_k() const;
-  int stages_per_layer() const { return experts ? 6 : 5; }
+  int stages_per_layer() const { return (experts ? 6 : 5) + down_splits - 1; }
   // algorithmic bytes of one decode step (weights of every GEMV + KV rows read; with experts:
   // the dense matrices, the router, and batch * topk experts per layer)
   uint64_t weight_bytes() const;

@@ -253,6 +253,8 @@ void* tm_plan_create(int batch, void* const* external, int device) {
   p.write_logits = s.write_logits ? 1 : 0;
   p.grid = s.grid > 0 ? std::min(s.grid, prop.multiProcessorCount) : prop.multiProcessorCount;
   for (int g = 0; g < tmb::kNumGemv; ++g) p.geo[g] = s.geo[g];
+  p.down_splits = s.down_splits;
+  for (int i = 0; i < tmb::kMaxDownSplits; ++i) p.down_part[i] = s.down_part[i];
   p.bar_base = 0;
   const char* watchdog = std::getenv("TILEMEGA_WATCHDOG_MS");
   const double watchdog_ms = watchdog ? std::atof(watchdog) : 2000.0;
@@ -267,7 +269,8 @@ void* tm_plan_create(int batch, void* const* external, int device) {
   // rows of the widest GEMV input; one extra hidden-wide row holds the RMSNorm weights
   // (rows are padded by 8 elements so that the batch rows of a k-chunk sit on distinct banks)
   // a normalised stage also parks its raw rows and the norm weights there: 2*batch + 1 hidden-wide rows
-  int xs = std::max({batch * (s.max_k() + 8) * 2, (2 * batch + 1) * (s.geo[tmb::kQkv].k + 8) * 2, attention_scratch,
+  // (batch > 4: the rows are normalised in a second pass over global memory instead: batch + 1 rows)
+  int xs = std::max({batch * (s.max_k() + 8) * 2, (batch > 4 ? batch + 1 : 2 * batch + 1) * (s.geo[tmb::kQkv].k + 8) * 2, attention_scratch,
                      expert_rows});
   xs = (xs + 127) & ~127;
   p.xs_bytes = xs;
@@ -347,10 +350,11 @@ void* tm_plan_create(int batch, void* const* external, int device) {
     void** out;
     size_t bytes;
   };
-  void *attn_part = nullptr, *argmax_val = nullptr, *argmax_idx = nullptr, *status = nullptr,
+  void *down_partial = nullptr, *attn_part = nullptr, *argmax_val = nullptr, *argmax_idx = nullptr, *status = nullptr,
        *step_ns = nullptr, *past = nullptr;
   const size_t attn_tasks = size_t(p.grid) + size_t(batch) * s.kv_heads + 1;
   const Scratch scratch[] = {
+      {&down_partial, size_t(batch) * s.hidden * sizeof(float)},
       {&attn_part, attn_tasks * gq * (s.head_dim + 2) * sizeof(float)},
       {&argmax_val, size_t(p.grid) * batch * sizeof(float)},
       {&argmax_idx, size_t(p.grid) * batch * sizeof(int)},
@@ -379,6 +383,7 @@ void* tm_plan_create(int batch, void* const* external, int device) {
   p.attn_cnt = reinterpret_cast<unsigned*>(plan->sync_block + 128);
   p.qkv_ready = reinterpret_cast<unsigned long long*>(plan->sync_block + ready_offset);
   p.stage_cnt = reinterpret_cast<unsigned*>(plan->sync_block + plan->claim_offset);
+  p.down_partial = static_cast<float*>(down_partial);
   p.attn_part = static_cast<float*>(attn_part);
   p.argmax_val = static_cast<float*>(argmax_val);
   p.argmax_idx = static_cast<int*>(argmax_idx);
