@@ -45,11 +45,11 @@ METRIC = "decode_tokens_per_s"
 UNIT = "tok/s"
 NOMINAL_HBM_GBS = 8000.0
 # dram__bytes_read.sum + dram__bytes_write.sum per algorithmic byte of a launch, from the ncu
-# capture of the same kernel on a 2-layer case of the same shapes (15.476 GB of DRAM traffic
+# capture of the same kernel on a 2-layer case of the same shapes (15.473 GB of DRAM traffic
 # for 15.559 GB of algorithmic bytes; profiles/decode_megakernel_llama31_8b_b1.md). Traffic
 # is proportional to the streamed weights, so the full launch's traffic is this ratio times
 # its algorithmic bytes.
-NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 0.9947
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 0.9945
 
 
 def measured_peak_gbs() -> tuple[float, str]:
