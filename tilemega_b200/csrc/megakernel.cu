@@ -229,14 +229,27 @@ __device__ __forceinline__ int seq_pos(const MegaParams& p, int past, int b) {
 }
 
 // slots-per-task and task count for one attention stage
-__device__ __forceinline__ void attn_shape(const MegaParams& p, int past, int nk, int& spt, int& ntasks) {
-  int total = 0;
-  for (int b = 0; b < p.batch; ++b) total += (seq_pos(p, past, b) / nk + 1) * p.kv_heads;
-  spt = max(max(1, p.attn_min_spt), (total + p.grid - 1) / p.grid);
-  ntasks = 0;
+__device__ __forceinline__ int attn_count(const MegaParams& p, int past, int nk, int spt) {
+  int ntasks = 0;
   for (int b = 0; b < p.batch; ++b) {
     const int ns = seq_pos(p, past, b) / nk + 1;
     ntasks += p.kv_heads * ((ns + spt - 1) / spt);
+  }
+  return ntasks;
+}
+
+__device__ __forceinline__ void attn_shape(const MegaParams& p, int past, int nk, int& spt, int& ntasks) {
+  int total = 0;
+  for (int b = 0; b < p.batch; ++b) total += (seq_pos(p, past, b) / nk + 1) * p.kv_heads;
+  // a task's fixed cost wants at least attn_min_spt slots; with much more work than that per
+  // CTA, about two tasks per CTA let the claims even out sequences of different lengths
+  const int per_cta = (total + p.grid - 1) / p.grid;
+  spt = max(max(1, p.attn_min_spt), per_cta >= 2 * max(1, p.attn_min_spt) ? (per_cta + 1) / 2 : per_cta);
+  ntasks = attn_count(p, past, nk, spt);
+  // every task owns one record of partial results: never more tasks than records
+  while (ntasks > p.attn_part_tasks) {
+    spt += 1;
+    ntasks = attn_count(p, past, nk, spt);
   }
 }
 
@@ -256,8 +269,9 @@ __device__ __forceinline__ AttnTask attn_task(const MegaParams& p, int past, int
       a.pos = pos;
       a.ns = ns;
       a.nch = nch;
-      a.slot0 = a.c * spt;
-      a.slot1 = min(ns, a.slot0 + spt);
+      const int even = (ns + nch - 1) / nch;   // the chunks of a sequence are equally long (even <= spt: none is empty)
+      a.slot0 = a.c * even;
+      a.slot1 = min(ns, a.slot0 + even);
       a.task0 = base + a.g * nch;
       return a;
     }
@@ -621,35 +635,43 @@ __device__ __forceinline__ void stage_rows(Ctx& c, const GemvIo& io, const GemvG
   constexpr int kNormRow = kWide ? B : 2 * B;
   uint4* xs4 = reinterpret_cast<uint4*>(c.xs());
   const uint4* nw = reinterpret_cast<const uint4*>(io.norm);
-  float ss[B];
+  // The chunk loop is the outer one and the loads of all B rows of a chunk are issued
+  // before any is used: one L2 round trip per chunk, not one per row.
+  const uint4* src[B];
 #pragma unroll
   for (int b = 0; b < B; ++b) {
-    const uint4* src;
     if (io.embed) {
       const int tok = min(max(c.tok()[b], 0), p.vocab - 1);
-      src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(io.src) + size_t(tok) * geo.src_stride);
+      src[b] = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(io.src) + size_t(tok) * geo.src_stride);
     } else {
-      src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(io.src) + size_t(b) * geo.src_stride + geo.src_off);
+      src[b] = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(io.src) + size_t(b) * geo.src_stride + geo.src_off);
     }
-    const bool own = io.embed && (b % p.grid) == int(blockIdx.x);
-    uint4* xg = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.x) + size_t(b) * k_src);
-    float acc = 0.f;
-    for (int i = c.tid; i < chunks; i += kConsumerThreads) {
-      uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (i < src_chunks) v = io.embed ? __ldg(src + i) : __ldcg(src + i);
-      if (own && i < src_chunks) xg[i] = v;
-      if (io.norm) {
-        if (b == 0) xs4[kNormRow * pitch + i] = i < src_chunks ? __ldg(nw + i) : make_uint4(0u, 0u, 0u, 0u);
-        if (!kWide) xs4[(B + b) * pitch + i] = v;
-        float f[8];
-        unpack8(v, f);
+  }
+  float ss[B];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc = fmaf(f[j], f[j], acc);
+  for (int b = 0; b < B; ++b) ss[b] = 0.f;
+  for (int i = c.tid; i < chunks; i += kConsumerThreads) {
+    uint4 v[B];
+#pragma unroll
+    for (int b = 0; b < B; ++b) {
+      v[b] = make_uint4(0u, 0u, 0u, 0u);
+      if (i < src_chunks) v[b] = io.embed ? __ldg(src[b] + i) : __ldcg(src[b] + i);
+    }
+    if (io.norm) xs4[kNormRow * pitch + i] = i < src_chunks ? __ldg(nw + i) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+    for (int b = 0; b < B; ++b) {
+      if (io.embed && (b % p.grid) == int(blockIdx.x) && i < src_chunks)
+        reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.x) + size_t(b) * k_src)[i] = v[b];
+      if (io.norm) {
+        if (!kWide) xs4[(B + b) * pitch + i] = v[b];
+        float f[8];
+        unpack8(v[b], f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss[b] = fmaf(f[j], f[j], ss[b]);
       } else {
-        store_row_chunk(reinterpret_cast<uint32_t*>(xs4 + b * pitch), i, v);
+        store_row_chunk(reinterpret_cast<uint32_t*>(xs4 + b * pitch), i, v[b]);
       }
     }
-    ss[b] = acc;
   }
   if (io.norm) {
 #pragma unroll
@@ -660,30 +682,33 @@ __device__ __forceinline__ void stage_rows(Ctx& c, const GemvIo& io, const GemvG
       if (c.lane == 0) c.wsum()[b * 8 + c.warp] = v;
     }
     consumer_sync();
+    float inv[B];
 #pragma unroll
     for (int b = 0; b < B; ++b) {
       float total = 0.f;
 #pragma unroll
       for (int w = 0; w < kConsumerWarps; ++w) total += c.wsum()[b * 8 + w];
-      const float inv = 1.0f / sqrtf(total / float(k_src) + p.eps);
-      const uint4* again = nullptr;
-      if (kWide) {
-        const int tok = io.embed ? min(max(c.tok()[b], 0), p.vocab - 1) : 0;
-        again = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(io.src) +
-                                               (io.embed ? size_t(tok) * geo.src_stride : size_t(b) * geo.src_stride + geo.src_off));
+      inv[b] = 1.0f / sqrtf(total / float(k_src) + p.eps);
+    }
+    for (int i = c.tid; i < chunks; i += kConsumerThreads) {
+      uint4 raw[B];
+#pragma unroll
+      for (int b = 0; b < B; ++b) {
+        raw[b] = make_uint4(0u, 0u, 0u, 0u);
+        if (!kWide) raw[b] = xs4[(B + b) * pitch + i];    // written by this same thread above
+        else if (i < src_chunks) raw[b] = io.embed ? __ldg(src[b] + i) : __ldcg(src[b] + i);
       }
-      for (int i = c.tid; i < chunks; i += kConsumerThreads) {
-        float f[8], w[8];
-        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
-        if (!kWide) raw = xs4[(B + b) * pitch + i];    // written by this same thread above
-        else if (i < src_chunks) raw = io.embed ? __ldg(again + i) : __ldcg(again + i);
-        unpack8(raw, f);
-        unpack8(xs4[kNormRow * pitch + i], w);
+      float w[8];
+      unpack8(xs4[kNormRow * pitch + i], w);
+#pragma unroll
+      for (int b = 0; b < B; ++b) {
+        float f[8];
+        unpack8(raw[b], f);
         uint32_t o[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const uint32_t lo = bf16_bits(w[2 * j] * bf16_round(f[2 * j] * inv));
-          const uint32_t hi = bf16_bits(w[2 * j + 1] * bf16_round(f[2 * j + 1] * inv));
+          const uint32_t lo = bf16_bits(w[2 * j] * bf16_round(f[2 * j] * inv[b]));
+          const uint32_t hi = bf16_bits(w[2 * j + 1] * bf16_round(f[2 * j + 1] * inv[b]));
           o[j] = lo | (hi << 16);
         }
         store_row_chunk(reinterpret_cast<uint32_t*>(xs4 + b * pitch), i, make_uint4(o[0], o[1], o[2], o[3]));

@@ -116,7 +116,8 @@ struct MegaParams {
   int* route_idx;              // [layers][topk] chosen experts of the last step, in rank order (batch 1)
   float* route_w;              // [layers][topk] their routing weights
   float* down_partial;         // f32 [B][H]: running sums of a split down projection
-  float* attn_part;            // [grid + B*Hkv][Gq][D+2]
+  float* attn_part;            // [attn_part_tasks][Gq][D+2]: one record per attention task
+  int attn_part_tasks;         // 2*grid + B*Hkv + 2: about two tasks per CTA, plus the rounding up per (sequence, KV head)
   unsigned* attn_cnt;          // [B*Hkv]
   unsigned long long* qkv_ready;  // [Hkv] QKV row tiles stored per KV-head group (monotonic within a launch)
   float* argmax_val;           // [grid][B]

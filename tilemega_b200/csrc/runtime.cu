@@ -352,7 +352,8 @@ void* tm_plan_create(int batch, void* const* external, int device) {
   };
   void *down_partial = nullptr, *attn_part = nullptr, *argmax_val = nullptr, *argmax_idx = nullptr, *status = nullptr,
        *step_ns = nullptr, *past = nullptr;
-  const size_t attn_tasks = size_t(p.grid) + size_t(batch) * s.kv_heads + 1;
+  const size_t attn_tasks = 2 * size_t(p.grid) + size_t(batch) * s.kv_heads + 2;
+  p.attn_part_tasks = int(attn_tasks);
   const Scratch scratch[] = {
       {&down_partial, size_t(batch) * s.hidden * sizeof(float)},
       {&attn_part, attn_tasks * gq * (s.head_dim + 2) * sizeof(float)},
