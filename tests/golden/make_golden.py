@@ -74,7 +74,9 @@ def run_reference(Decoder, config: dict, dtype: torch.dtype, prompt: torch.Tenso
 
 
 def main() -> None:
-    reference = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python " + Path(__file__).name + " /path/to/TileMega [case ...]")
+    reference = Path(sys.argv[1])
     sys.path.insert(0, str(reference / "python"))
     from tilemega.serving.export import Decoder
     torch.set_num_threads(8)

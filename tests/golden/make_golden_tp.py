@@ -40,7 +40,9 @@ def rank_state(weights: dict[str, torch.Tensor], rank: int, world: int) -> dict[
 
 
 def main() -> None:
-    reference = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python " + Path(__file__).name + " /path/to/TileMega [case ...]")
+    reference = Path(sys.argv[1])
     sys.path.insert(0, str(reference / "python"))
     from tilemega.serving.export import Decoder
     world, batch, past = 2, 2, 19
