@@ -253,3 +253,22 @@ def test_wide_batch_takes_the_down_reduction_in_parts(plan_dir):
     looped, _ = run.greedy(prompt, new_tokens, stepwise=False)
     assert torch.equal(looped, tokens)
     run.close()
+
+
+def test_generation_up_to_the_last_position_of_the_cache(plan_dir):
+    """The last decode step runs position capacity - 1: its token has no slot in the token
+    state and must not be written anywhere; everything before it matches the oracle."""
+    config = synthetic.TINY_D128
+    batch, prompt_len, capacity = 2, 20, 32
+    steps = capacity - prompt_len + 1               # the last one decodes position capacity - 1
+    weights = bf16_weights(config)
+    prompt = synthetic.seeded_tokens(batch, prompt_len, config["vocab_size"], seed=12)
+    run = GpuRun(config, weights, batch, capacity, plan_dir)
+    tokens, logits = run.greedy(prompt, steps)      # tokens: the capacity - prompt_len that fit
+    assert tokens.shape == (batch, capacity - prompt_len) and logits.shape[0] == steps
+    assert_as_accurate_as_reference_bf16(config, weights, prompt, tokens, logits[:tokens.shape[1]], capacity, "full cache")
+    state = run.state.tokens.cpu()
+    assert torch.equal(state[:, :prompt_len], prompt) and torch.equal(state[:, prompt_len:], tokens)
+    looped, _ = run.greedy(prompt, steps, stepwise=False)
+    assert torch.equal(looped, tokens)
+    run.close()

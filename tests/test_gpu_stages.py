@@ -33,7 +33,9 @@ def agreement(got, ref, what, ulps=1.0, exact_fraction=0.99, floor=1e-6):
 
 
 @pytest.mark.parametrize("base,batch,history", [("TINY", 2, 37), ("TINY_D128", 3, 70), ("TINY", 1, 129),
-                                                ("TINY", 8, 21), ("TINY_D128", 5, 33), ("TINY_GQ8", 2, 75)])
+                                                ("TINY", 8, 21), ("TINY_D128", 5, 33), ("TINY_GQ8", 2, 75),
+                                                # long histories: several chunks per KV head, merged by the last arriver
+                                                ("TINY_D128", 2, 701), ("TINY", 1, 1533), ("TINY_GQ8", 3, 389)])
 def test_every_stage_of_one_layer(base, batch, history, plan_dir):
     config = dict(getattr(synthetic, base), num_hidden_layers=1)
     dim, heads, hkv = config["head_dim"], config["num_attention_heads"], config["num_key_value_heads"]
