@@ -1392,28 +1392,59 @@ __device__ void attn_stage(Ctx& c, const LayerPtrs& lp, int past, bool tr, int s
       }
       consumer_sync();
     }
-    for (int e = c.tid; e < (GQ + 2) * D; e += kConsumerThreads) {
-      const int hh = e / D, d = e - hh * D;
-      const float xv = qk_norm && hh <= GQ ? __bfloat162float(qkn[e]) : bf16_from_bits(__ldcg(row + e));
-      if (hh == GQ + 1) {
-        if (tail) {
-          vnew[d] = __float2bfloat16_rn(xv);
-          static_cast<__nv_bfloat16*>(lp.v_pool)[new_off + kv_swizzled(d, a.pos)] = __float2bfloat16_rn(xv);
+    {
+      // every element's four inputs (the value, its rotation partner, cos, sin) are fetched
+      // for all of this thread's elements before any is used: one L2 round trip for the
+      // whole staging instead of one per element
+      constexpr int kElements = (GQ + 2) * D;
+      constexpr int NI = (kElements + kConsumerThreads - 1) / kConsumerThreads;
+      const unsigned short* cosr = reinterpret_cast<const unsigned short*>(cosb) + size_t(a.pos) * D;
+      const unsigned short* sinr = reinterpret_cast<const unsigned short*>(sinb) + size_t(a.pos) * D;
+      unsigned short rv[NI], rp[NI], rc[NI], rs[NI];
+#pragma unroll
+      for (int it = 0; it < NI; ++it) {
+        const int e = c.tid + it * kConsumerThreads;
+        rv[it] = rp[it] = rc[it] = rs[it] = 0;
+        if (e < kElements) {
+          const int hh = e / D, d = e - hh * D;
+          const int d2 = d < D / 2 ? d + D / 2 : d - D / 2;
+          const bool normed = qk_norm && hh <= GQ;
+          const bool roped = hh < GQ || (hh == GQ && tail);
+          if (!normed && (roped || (hh == GQ + 1 && tail))) rv[it] = __ldcg(row + e);
+          if (roped) {
+            if (!normed) rp[it] = __ldcg(row + hh * D + d2);
+            rc[it] = __ldg(cosr + d);
+            rs[it] = __ldg(sinr + d);
+          }
         }
-        continue;
       }
-      if (hh == GQ && !tail) continue;
-      const int d2 = d < D / 2 ? d + D / 2 : d - D / 2;
-      const float xp = qk_norm ? __bfloat162float(qkn[hh * D + d2]) : bf16_from_bits(__ldcg(row + hh * D + d2));
-      const float cs = __bfloat162float(cosb[size_t(a.pos) * D + d]);
-      const float sn = __bfloat162float(sinb[size_t(a.pos) * D + d]);
-      const float rot = d < D / 2 ? -xp : xp;
-      const float o = bf16_round(bf16_round(xv * cs) + bf16_round(rot * sn));
-      if (hh < GQ) {
-        qs[hh * D + d] = __float2bfloat16_rn(o);
-      } else {
-        knew[d] = __float2bfloat16_rn(o);
-        static_cast<__nv_bfloat16*>(lp.k_pool)[new_off + kv_swizzled(d, a.pos)] = __float2bfloat16_rn(o);
+#pragma unroll
+      for (int it = 0; it < NI; ++it) {
+        const int e = c.tid + it * kConsumerThreads;
+        if (e >= kElements) continue;
+        const int hh = e / D, d = e - hh * D;
+        const bool normed = qk_norm && hh <= GQ;
+        const float xv = normed ? __bfloat162float(qkn[e]) : bf16_from_bits(rv[it]);
+        if (hh == GQ + 1) {
+          if (tail) {
+            vnew[d] = __float2bfloat16_rn(xv);
+            static_cast<__nv_bfloat16*>(lp.v_pool)[new_off + kv_swizzled(d, a.pos)] = __float2bfloat16_rn(xv);
+          }
+          continue;
+        }
+        if (hh == GQ && !tail) continue;
+        const int d2 = d < D / 2 ? d + D / 2 : d - D / 2;
+        const float xp = normed ? __bfloat162float(qkn[hh * D + d2]) : bf16_from_bits(rp[it]);
+        const float cs = bf16_from_bits(rc[it]);
+        const float sn = bf16_from_bits(rs[it]);
+        const float rot = d < D / 2 ? -xp : xp;
+        const float o = bf16_round(bf16_round(xv * cs) + bf16_round(rot * sn));
+        if (hh < GQ) {
+          qs[hh * D + d] = __float2bfloat16_rn(o);
+        } else {
+          knew[d] = __float2bfloat16_rn(o);
+          static_cast<__nv_bfloat16*>(lp.k_pool)[new_off + kv_swizzled(d, a.pos)] = __float2bfloat16_rn(o);
+        }
       }
     }
     if (tail) fence_proxy_async();
@@ -1600,13 +1631,14 @@ __device__ void attn_stage(Ctx& c, const LayerPtrs& lp, int past, bool tr, int s
         const float* parts = p.attn_part + size_t(a.task0) * GQ * PW;
         for (int o = c.tid; o < GQ * D; o += kConsumerThreads) {
           const int h = o / D, d = o - h * D;
-          // chunks in ascending order, eight at a time so that their loads are in
+          // chunks in ascending order, sixteen at a time so that their loads are in
           // flight together (one L2 round trip per batch instead of one per chunk)
           float mx = -INFINITY, ls = 0.f, as = 0.f;
-          for (int c0 = 0; c0 < a.nch; c0 += 8) {
-            float mc[8], lc[8], ac[8];
+          constexpr int kMergeBatch = 16;
+          for (int c0 = 0; c0 < a.nch; c0 += kMergeBatch) {
+            float mc[kMergeBatch], lc[kMergeBatch], ac[kMergeBatch];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
+            for (int j = 0; j < kMergeBatch; ++j) {
               const bool live = c0 + j < a.nch;
               const float* src = parts + (size_t(live ? c0 + j : c0) * GQ + h) * PW;
               mc[j] = live ? __ldcg(src + D) : -INFINITY;
@@ -1615,13 +1647,13 @@ __device__ void attn_stage(Ctx& c, const LayerPtrs& lp, int past, bool tr, int s
             }
             float mb = mx;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) mb = fmaxf(mb, mc[j]);
+            for (int j = 0; j < kMergeBatch; ++j) mb = fmaxf(mb, mc[j]);
             const float rescale = ex2(mx - mb);   // mb is finite: chunk c0 exists and holds a valid key
             ls *= rescale;
             as *= rescale;
             mx = mb;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
+            for (int j = 0; j < kMergeBatch; ++j) {
               const float wgt = ex2(mc[j] - mb);
               ls = fmaf(lc[j], wgt, ls);
               as = fmaf(ac[j], wgt, as);
