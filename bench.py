@@ -220,7 +220,7 @@ def run_ours(args) -> None:
     work = workload(args)
     config, batch, contexts = work["config"], work["batch"], work["contexts"]
     steps, warmup = args.steps, max(args.warmup, 3)
-    total_steps = warmup + 2 * steps + 1       # device-timed launch, then the end-to-end loop
+    total_steps = warmup + 2 * steps + 1 + 4   # device-timed launch, the end-to-end loop, and the optional traced steps
     capacity = (max(contexts) + total_steps + 17) // 16 * 16
     max_blocks = capacity // 16
     num_blocks = batch * max_blocks + 32
@@ -311,6 +311,18 @@ def run_ours(args) -> None:
     fired = plan.watchdog()
     if fired is not None:
         raise SystemExit(f"a bounded device wait gave up during the end-to-end loop: {fired}")
+    if args.trace:
+        # per-stage stamps of one more step (every rank of a tensor-parallel job runs it; rank 0 reports)
+        import numpy as np
+        from tilemega_b200.stage_trace import print_table
+        plan.trace_step(warmup + 2 * steps + 2)
+        plan.launch_steps(warmup + 2 * steps, 4, mode, stream.cuda_stream)
+        barrier()
+        stamps = np.array(plan.read_trace(), dtype=np.int64)
+        grid = torch.cuda.get_device_properties(local).multi_processor_count
+        per_layer = (stamps.size // 4 // grid - 1) // config["num_hidden_layers"]
+        if rank == 0:
+            print_table(config, stamps.reshape(grid, -1, 4), per_layer, max(contexts) + warmup + 2 * steps, batch, tp=tp)
     device_ms, e2e_seconds = max_over_ranks([device_ms, e2e_seconds], device)
     seconds = device_ms / 1e3
     replicas = 1 if tp > 1 else world
@@ -368,6 +380,8 @@ def main() -> None:
     parser.add_argument("--geometry", default="", help="JSON overrides of the GEMV page geometry")
     parser.add_argument("--slots", type=int, default=0)
     parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    parser.add_argument("--trace", action="store_true",
+                        help="after the timed runs, stamp one more step and print the per-stage table (rank 0)")
     parser.add_argument("--tp", action="store_true",
                         help="shard one model over the ranks (tensor parallelism) instead of running replicas")
     args = parser.parse_args()

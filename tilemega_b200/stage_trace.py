@@ -104,6 +104,14 @@ def main() -> None:
         per_layer = (stamps.size // 4 // grid - 1) // layers
         trace = stamps.reshape(grid, per_layer * layers + 1, 4)
         plan.close()
+    print_table(config, trace, per_layer, context, batch)
+
+
+def print_table(config: dict, trace, per_layer: int, context: int, batch: int, tp: int = 1) -> None:
+    """`trace`: int64 [grid][per_layer * layers + 1][4] stage stamps of one step (one rank's)."""
+    import numpy as np
+    layers = config["num_hidden_layers"]
+    kinds = ["qkv", "attn", "o"] + (["router"] if synthetic.is_moe(config) else []) + ["gate_up", "down"]
     parts = per_layer - len(kinds) + 1
     if parts > 1:
         kinds = kinds[:-1] + [f"down part {i}" for i in range(parts)]
@@ -111,6 +119,7 @@ def main() -> None:
     done, first_done = trace[:, :, 3].max(axis=0), trace[:, :, 3].min(axis=0)
     wall = np.diff(np.concatenate(([start], done)))
     sizes, peak = stage_bytes(config, context + 18, batch), measured_gbs()
+    sizes = {name: value / tp for name, value in sizes.items()}
     print(f"{'stage':12s} {'wall':>7s} {'ideal':>7s} {'wait':>6s} {'rows':>6s} {'tasks':>6s} {'max':>6s} {'spread':>6s}   (us; "
           f"ideal = bytes / {peak:.0f} GB/s; medians over CTAs, means over layers 1..{layers - 1})")
     for k, kind in enumerate(kinds):
@@ -124,7 +133,7 @@ def main() -> None:
               f"{np.median(trace[:, index, 3] - trace[:, index, 2], axis=0).mean() / 1e3:6.2f} "
               f"{(trace[:, index, 3] - trace[:, index, 2]).max(axis=0).mean() / 1e3:6.2f} "
               f"{(done[index] - first_done[index]).mean() / 1e3:6.2f}")
-    print(f"{'head':12s} {wall[-1] / 1e3:7.2f} {config['vocab_size'] * config['hidden_size'] * 2 / peak / 1e3:7.2f}")
+    print(f"{'head':12s} {wall[-1] / 1e3:7.2f} {config['vocab_size'] * config['hidden_size'] * 2 / tp / peak / 1e3:7.2f}")
     if layers > 1:
         print(f"layer total  {wall[per_layer:per_layer * layers].sum() / (layers - 1) / 1e3:7.2f} "
               f"{sum(sizes.values()) / peak / 1e3:7.2f}")
