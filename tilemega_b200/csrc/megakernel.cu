@@ -4,7 +4,7 @@
 // (one per SM) has one streaming warp and eight arithmetic warps:
 //
 //  * the streaming warp claims tasks of the current stage from a global counter
-//    (one atomicAdd per task, issued one task ahead), posts each task id into a
+//    (one atomicAdd per chunk of about 64 KB of pages, issued one chunk ahead), posts each task id into a
 //    small shared-memory FIFO and copies the task's data -- weight pages of a GEMV
 //    stage, KV block groups of an attention stage -- into a shared-memory ring
 //    with cp.async.bulk. It never waits for a stage boundary, only for a free ring
@@ -13,16 +13,21 @@
 //    that streams faster simply takes more of them and every stage ends together.
 //  * the arithmetic warps pop the FIFO, wait for the stage's inputs (a grid-wide
 //    arrival counter with release/acquire), stage the activation rows in shared
-//    memory (RMSNorm fused), and consume ring slots: 128-bit shared-memory loads,
-//    fp32 FMA, the rounding sites of the reference's epilogues. Results do not
-//    depend on which CTA ran a task, so the run-to-run bits are identical.
+//    memory (RMSNorm fused), and consume ring slots: ldmatrix + mma.sync (bf16 in,
+//    fp32 accumulate) for the weight pages and for the attention tiles, then the
+//    rounding sites of the reference's epilogues. Results do not depend on which
+//    CTA ran a task, so the run-to-run bits are identical.
 //
 // Stage list per layer (reference: include/tilemega/Codegen/tasks/
 // Sm90DenseProgram.cuh:903-939): qkv (RMSNorm fused) -> RoPE + KV append +
 // split-KV attention (+ last-arriver merge) -> o (+residual) -> gate/up
 // (RMSNorm, SwiGLU) -> down (+residual); after the last layer lm_head
 // (RMSNorm, bf16 logits, argmax partials) and the argmax reduction that also
-// feeds the next step's embedding.
+// feeds the next step's embedding. Attention tasks wait for their own KV group's QKV
+// rows (a per-group counter), not for a grid barrier. A second instantiation of the
+// kernel (TMB_EXTENDED) adds tensor parallelism (all-reduce packets exchanged over peer
+// memory inside the o / down epilogues), a mixture-of-experts MLP (router stage,
+// in-kernel top-k, chosen experts only) and the per-head QK norm.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
