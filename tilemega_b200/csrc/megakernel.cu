@@ -440,12 +440,18 @@ __device__ __forceinline__ void stream_expert_gate_up(Ctx& c, const GemvGeo& geo
   const int total = c.p.topk * geo.ntasks;
   const int chunk_tasks = geo.claim_chunk;
   int chunk = c.pending;
+  int slot = 0, tile = 0, at = 0;   // (expert slot, row tile) of task `at`: claims only grow, so no division is needed
   while (chunk * chunk_tasks < total && !c.dead) {
     const int upcoming = claim(c, c.inst);
     for (int j = 0; j < chunk_tasks; ++j) {
       const int t = chunk * chunk_tasks + j;
       if (t >= total) break;
-      const int slot = t / geo.ntasks, tile = t - slot * geo.ntasks;
+      tile += t - at;
+      at = t;
+      while (tile >= geo.ntasks) {
+        tile -= geo.ntasks;
+        ++slot;
+      }
       stream_pages(c, geo, w + (size_t(expert[slot]) * geo.ntasks + tile) * size_t(geo.pages_per_task) * page_bytes, t,
                    page_bytes, policy);
     }
@@ -464,8 +470,8 @@ __device__ __forceinline__ void stream_expert_down(Ctx& c, const GemvGeo& geo, c
   while (t < geo.ntasks && !c.dead) {
     const int upcoming = claim(c, c.inst);
     for (int slot = 0; slot < c.p.topk; ++slot)
-      stream_pages(c, geo, w + (size_t(expert[slot]) * geo.ntasks + t) * page_bytes, t * c.p.topk + slot, page_bytes,
-                   policy);
+      stream_pages(c, geo, w + (size_t(expert[slot]) * geo.ntasks + t) * page_bytes, t * kMaxTopK + slot, page_bytes,
+                   policy);   // id = tile * 8 + slot: the arithmetic warps split it with a shift and a mask
     t = upcoming;
   }
   stream_close(c);
@@ -1260,12 +1266,13 @@ __device__ __noinline__ void moe_down_stage(Ctx& c, const GemvGeo& geo, bool tr,
   uint64_t* const full0 = c.full(0);
   uint64_t* const empty0 = c.empty(0);
   uint32_t sub_seq = 0;        // sub-tasks seen by this CTA in this stage
+  uint32_t tile_seq = 0;       // row tiles completed: the owner warp rotates per tile
   int pending_task = -1, pending_buf = 0;
   uint32_t pending_lap = 0;
   float running = 0.f, residual = 0.f;
   auto epilogue = [&]() {
     mbar_wait_warp(c, c.pfull(pending_buf), pending_lap, kSiteFull);
-    const int tile = pending_task / topk, s = pending_task - tile * topk;
+    const int tile = pending_task / kMaxTopK, s = pending_task % kMaxTopK;
     if (lane < kTileN) {
       float v = 0.f;
 #pragma unroll
@@ -1279,8 +1286,8 @@ __device__ __noinline__ void moe_down_stage(Ctx& c, const GemvGeo& geo, bool tr,
     pending_task = -1;
   };
   for (int t = fifo_pop(c); t >= 0; t = fifo_pop(c)) {
-    const int tile = t / topk, s = t - tile * topk;
-    const bool owner = warp == int((sub_seq / uint32_t(topk)) & 7u);
+    const int tile = t / kMaxTopK, s = t % kMaxTopK;   // powers of two: no division in the loop
+    const bool owner = warp == int(tile_seq & 7u);
     if (owner && s == 0 && lane < kTileN)
       residual = bf16_from_bits(__ldcg(reinterpret_cast<const unsigned short*>(p.x) + tile * kTileN + lane));
     float d[4][4];
@@ -1308,6 +1315,7 @@ __device__ __noinline__ void moe_down_stage(Ctx& c, const GemvGeo& geo, bool tr,
       pending_lap = lap;
     }
     ++sub_seq;
+    if (s == topk - 1) ++tile_seq;
     ++gemv_seq;
   }
   if (pending_task >= 0) epilogue();
