@@ -1742,6 +1742,7 @@ __device__ void consumer_main(Ctx& c) {
           if (!grid_wait(c)) return;
           trace_mark(c, tr, stage, 1);
           route_token(c, l);
+          trace_mark(c, tr, stage, 1);   // the experts' inputs are there once the token is routed
           // task t = (expert slot, row tile): with one token the SwiGLU epilogue's output
           // index t * 4 + r is row `slot` of h[topk][inter]
           io = GemvIo{p.x, lp.norm2, 0, kEpiSwiGLU, p.h, nullptr, 1, nullptr, 0, 0u};
