@@ -117,14 +117,32 @@ int tm_ipc_export(void* device_pointer, unsigned char* handle64);
 int tm_ipc_open(const unsigned char* handle64, void** device_pointer);
 int tm_ipc_close(void* device_pointer);
 
+/* Several ranks of one tensor-parallel job on ONE device, as one cooperative launch:
+ * plans[q] is rank q's plan (all created from this library on the same device, all bound
+ * with tm_plan_bind_tp to regions in that device's memory), emitted with a "grid" small
+ * enough that the ranks' grids together fit the device's SMs. Same step and iteration
+ * rules as tm_plan_launch_steps, applied to every plan. The reference's driver launches
+ * each rank's plan on its own GPU in turn (python/tilemega/serving/tp_engine.py:113-131);
+ * ranks wait for one another's packets, and on one GPU only a single launch guarantees
+ * that they run at the same time, so a box with fewer GPUs than ranks (and the one-GPU
+ * test of the exchange code) goes through this entry point. Batch 1..4. */
+int tm_plan_launch_steps_ranks(void* const* plans, uint32_t count, uint32_t first_step, uint32_t steps,
+                               uint32_t mode, uint64_t base_iteration, void* stream);
+
 /* Last error text of the calling thread's most recent failing call. */
 const char* tm_plan_last_error(void);
 /* Clear a fired watchdog so the plan can launch again (counters are rezeroed
- * by every launch). */
+ * by every launch). Once tm_plan_watchdog (or the probe) has reported a fired
+ * wait, every launch on the plan answers -4 until this is called: the kernel's
+ * other waits fall through while the record stands, so its results would be
+ * garbage. Read tm_plan_watchdog after synchronising a launch. */
 int tm_plan_clear_watchdog(void* plan);
 /* Bounded-wait self test: a two-CTA kernel whose producer withholds its arrival
  * when `withhold` != 0; the waiter gives up after limit_us and the kernel
- * returns normally. Returns 1 if the wait gave up, 0 if it was satisfied. */
+ * returns normally. Returns 1 if the wait gave up, 0 if it was satisfied, and
+ * leaves the plan clean; `withhold` == 2 withholds too but leaves the record
+ * standing, which is the state after a real abandoned launch (launches answer
+ * -4 until tm_plan_clear_watchdog). */
 int tm_plan_watchdog_probe(void* plan, int withhold, uint32_t limit_us, void* stream);
 /* Stage trace of one step (the reference's TILEMEGA_TRACE_STAGE build,
  * include/tilemega/Codegen/tasks/ModelRuntime.h:758-766, as a run-time switch):
@@ -137,6 +155,15 @@ long long tm_plan_read_trace(void* plan, uint64_t* host, uint64_t bytes);
 /* Algorithmic HBM bytes of one decode step: GEMV weights incl. lm_head plus
  * 4*L*Hkv*D bytes per cached token (scripts/estimate_r16_mbu.py:15-38). */
 uint64_t tm_plan_step_bytes(void* plan, uint64_t cached_tokens_total);
+
+/* The reference's `tile_pages` packing recipe (python/tilemega/serving/weights.py:204-242,
+ * which runs as PyTorch indexing ops) as one kernel on the device: `src` is a row-major
+ * bf16 matrix [rows][cols] whose rows are src_pitch elements apart, `dst` receives
+ * ceil(rows/tile_n) * ceil(cols/tile_k) pages of tile_n*tile_k elements, zero where the
+ * matrix ends. Both on the current device, 16-byte aligned; cols and src_pitch multiples
+ * of 8. Asynchronous on `stream`. 0, -1 (bad argument) or a CUDA error code. */
+int tm_pack_tile_pages(const void* src, uint64_t rows, uint64_t cols, uint64_t src_pitch, uint32_t tile_n,
+                       uint32_t tile_k, void* dst, void* stream);
 
 /* No counterpart in the reference. The bounded-wait self test of
  * tm_plan_watchdog_probe for callers that may not allocate device memory: a

@@ -23,5 +23,9 @@ def library():
 
 
 @pytest.fixture(scope="session")
-def plan_dir(tmp_path_factory):
-    return tmp_path_factory.mktemp("plans")
+def plan_dir():
+    """Plan libraries of this test session: inside the package tree, removed afterwards."""
+    from tilemega_b200.planbuild import PLAN_DIR, remove_plans
+    folder = PLAN_DIR / f"pytest-{os.getpid()}"
+    yield folder
+    remove_plans(folder)

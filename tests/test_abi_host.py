@@ -19,15 +19,24 @@ ROOT = Path(__file__).resolve().parents[1]
 def declared_symbols():
     header = (ROOT / "include" / "tilemega_b200.h").read_text()
     header = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
-    return sorted(set(re.findall(r"\b(tm_plan_\w+)\s*\(", header)))
+    return sorted(set(re.findall(r"\b(tm_\w+)\s*\(", header)))
 
 
 def test_library_exports_every_declared_symbol(library):
     lib = ctypes.CDLL(str(library))
     names = declared_symbols()
-    assert len(names) >= 20
+    assert len(names) >= 28
+    for extra in ("tm_watchdog_probe_static", "tm_ipc_alloc", "tm_ipc_free", "tm_ipc_export", "tm_ipc_open", "tm_ipc_close",
+                  "tm_pack_tile_pages", "tm_plan_launch_steps_ranks"):
+        assert extra in names
     for name in names:
         assert hasattr(lib, name), f"{name} is declared in include/tilemega_b200.h but not exported"
+
+
+def test_binding_table_covers_the_header():
+    """Every entry point the header declares has a row in the ctypes binding, and the other way round."""
+    from tilemega_b200.serving.plan import SIGNATURES
+    assert sorted(SIGNATURES) == declared_symbols()
 
 
 def test_query_without_sidecar_fails(library, tmp_path, monkeypatch):

@@ -272,3 +272,80 @@ def test_generation_up_to_the_last_position_of_the_cache(plan_dir):
     looped, _ = run.greedy(prompt, steps, stepwise=False)
     assert torch.equal(looped, tokens)
     run.close()
+
+
+def test_serving_engine_generates_the_tokens_of_the_stepwise_run(plan_dir):
+    """The reference-facing driver class (ServingEngine.generate) in each of its launch
+    schedules -- one persistent launch for all decode steps, chunks of two steps, one launch
+    per step, mode L1 -- against the step-by-step run of the same plan."""
+    from tilemega_b200.planbuild import emit_plan
+    from tilemega_b200.serving.engine import ServingEngine
+    from tilemega_b200.serving.weights import TensorCheckpoint
+
+    config = synthetic.TINY
+    batch, prompt_len, new_tokens, capacity = 2, 7, 6, 32
+    weights = bf16_weights(config)
+    prompt = synthetic.seeded_tokens(batch, prompt_len, config["vocab_size"], seed=1)
+    run = GpuRun(config, weights, batch, capacity, plan_dir)
+    tokens, _ = run.greedy(prompt, new_tokens)
+    run.close()
+    so = emit_plan(config, plan_dir, batch_lo=batch, batch_hi=batch, capacity=capacity)
+    checkpoint = TensorCheckpoint(weights, config["tie_word_embeddings"])
+    for options in ({}, {"decode_chunk": 2}, {"decode_loop": False}, {"mode": "L1"}):
+        with ServingEngine(checkpoint, config, so, batch, prompt_len=prompt_len, max_new_tokens=new_tokens,
+                           **options) as engine:
+            result = engine.generate(prompt)
+            assert torch.equal(result.tokens, tokens), options
+            assert result.decode_loop_used == options.get("decode_loop", True)
+            assert len(result.step_ms) == new_tokens and result.step_ns_read and result.ttft_ms > 0
+            assert all(ms > 0 for ms in result.step_ms)
+            shorter = engine.generate(prompt, 3)     # the same engine again, fewer tokens
+            assert torch.equal(shorter.tokens, tokens[:, :3])
+            with pytest.raises(ValueError):
+                engine.generate(prompt[:, :3])
+            with pytest.raises(ValueError):
+                engine.generate(prompt, new_tokens + 1)
+    with pytest.raises(ValueError):
+        ServingEngine(checkpoint, config, so, batch, prompt_len=prompt_len, max_new_tokens=capacity)
+
+
+def test_a_fired_wait_blocks_launches_until_cleared(plan_dir):
+    """Status -4: after a bounded wait gave up and tm_plan_watchdog reported it, the plan
+    refuses launches until tm_plan_clear_watchdog (the record makes every other wait fall through)."""
+    config = dict(synthetic.TINY, num_hidden_layers=1)
+    run = GpuRun(config, bf16_weights(config), 1, 32, plan_dir)
+    run.plan.set_steps([0, 1])
+    run.state.tokens[:, 0] = 3
+    # the probe leaves a clean plan behind: it clears the record it provoked
+    assert run.plan.watchdog_probe(withhold=True, limit_us=2000)
+    run.plan.launch(0, 2, run.stream)
+    run.check_alive()
+    # withhold = 2 leaves the record standing, as a real abandoned launch does
+    assert run.lib.lib.tm_plan_watchdog_probe(run.plan.handle, 2, 2000, run.stream) == 1
+    record = run.plan.watchdog()
+    assert record is not None and record["fired"] == 1 and record["site"] == 5
+    with pytest.raises(RuntimeError, match=r"\(-4\)"):
+        run.plan.launch(1, 2, run.stream)
+    run.plan.clear_watchdog()
+    assert run.plan.watchdog() is None
+    run.plan.launch(1, 2, run.stream)
+    run.check_alive()
+    run.close()
+
+
+@pytest.mark.parametrize("rows,cols,tile_n,tile_k", [(64, 4096, 8, 2048), (24, 1536, 8, 2048), (256, 256, 128, 128),
+                                                     (1000, 1096, 128, 128), (6144, 4096, 8, 2048)])
+def test_pack_kernel_writes_the_tile_pages_layout(rows, cols, tile_n, tile_k):
+    """tm_pack_tile_pages against the indexing definition of the recipe
+    (python/tilemega/serving/weights.py:204-242 of the reference), bit for bit, ragged edges included."""
+    from tilemega_b200.serving.weights import tile_pages, tile_pages_by_indexing
+
+    generator = torch.Generator().manual_seed(5)
+    weight = torch.randn(rows, cols, generator=generator).to(torch.bfloat16)
+    expect = tile_pages_by_indexing(weight, tile_n, tile_k)
+    got = tile_pages(weight.cuda(), tile_n, tile_k)
+    assert torch.equal(got.cpu(), expect)
+    # a view whose rows are further apart than their length (a column shard of a larger matrix)
+    wide = torch.randn(rows, cols + 64, generator=generator).to(torch.bfloat16)
+    got = tile_pages(wide.cuda()[:, :cols], tile_n, tile_k)
+    assert torch.equal(got.cpu(), tile_pages_by_indexing(wide[:, :cols].contiguous(), tile_n, tile_k))

@@ -53,7 +53,10 @@ def test_moe_decode_matches_oracle_and_routes_identically(plan_dir):
     run.close()
 
 
-def test_every_moe_stage_of_one_layer(plan_dir):
+# TINY_MOE has 16 experts and 4 per token; the Qwen3-30B-A3B shape is the benchmark's own: 128 experts,
+# 8 per token (all eight slots of the routing and of the down stage's sub-tasks), vocabulary 151936.
+@pytest.mark.parametrize("base", ["TINY_MOE", "QWEN3_30B_A3B"])
+def test_every_moe_stage_of_one_layer(base, plan_dir):
     """Router logits, routing, expert SwiGLU rows and the weighted expert sum, each recomputed on
     the CPU from the buffers the GPU had (see tests/test_gpu_stages.py for the method); the QK norm
     is checked through the appended key row."""
@@ -62,7 +65,7 @@ def test_every_moe_stage_of_one_layer(plan_dir):
     from tilemega_b200.serving.state import kv_row_swizzle
     from test_gpu_stages import agreement
 
-    config = dict(synthetic.TINY_MOE, num_hidden_layers=1)
+    config = dict(getattr(synthetic, base), num_hidden_layers=1)
     hidden, eps, dim = config["hidden_size"], config["rms_norm_eps"], config["head_dim"]
     heads, hkv, topk = config["num_attention_heads"], config["num_key_value_heads"], config["num_experts_per_tok"]
     inter = config["moe_intermediate_size"]

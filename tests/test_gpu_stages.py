@@ -37,7 +37,19 @@ def agreement(got, ref, what, ulps=1.0, exact_fraction=0.99, floor=1e-6):
                                                 # long histories: several chunks per KV head, merged by the last arriver
                                                 ("TINY_D128", 2, 701), ("TINY", 1, 1533), ("TINY_GQ8", 3, 389)])
 def test_every_stage_of_one_layer(base, batch, history, plan_dir):
-    config = dict(getattr(synthetic, base), num_hidden_layers=1)
+    check_every_stage(dict(getattr(synthetic, base), num_hidden_layers=1), batch, history, plan_dir)
+
+
+# The benchmark configurations' own widths, one layer each: the Llama-3.2-1B shape (hidden 2048, head_dim
+# 64, FFN 8192, vocabulary 128256, tied) and the Llama-3.1-8B shape (hidden 4096, head_dim 128, FFN 14336 =
+# seven 2048-column pages per down task, vocabulary 128256) at batch 1 and at the GEMV path's widest batch.
+@pytest.mark.parametrize("base,batch,history", [("LLAMA_3_2_1B", 1, 130), ("LLAMA_3_1_8B", 1, 150),
+                                                ("LLAMA_3_1_8B", 8, 45)])
+def test_every_stage_at_benchmark_widths(base, batch, history, plan_dir):
+    check_every_stage(dict(getattr(synthetic, base), num_hidden_layers=1), batch, history, plan_dir)
+
+
+def check_every_stage(config, batch, history, plan_dir):
     dim, heads, hkv = config["head_dim"], config["num_attention_heads"], config["num_key_value_heads"]
     hidden, eps = config["hidden_size"], config["rms_norm_eps"]
     capacity = (history + 18) // 16 * 16

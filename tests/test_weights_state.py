@@ -8,6 +8,8 @@ from tilemega_b200 import synthetic
 from tilemega_b200.serving.state import rotary_tables, shuffled_block_table
 from tilemega_b200.serving.weights import TensorCheckpoint, pack, tile_pages
 
+GOLDEN = __import__("pathlib").Path(__file__).resolve().parent / "golden"
+
 
 def closed_form_offset(row, col, tn):
     # the layout contract of the reference's tile_pages recipe
@@ -72,7 +74,7 @@ def test_rotary_tables_and_block_tables():
     with pytest.raises(ValueError):
         shuffled_block_table(3, 8, 10)
     with pytest.raises(ValueError):
-        rotary_tables(dict(config, rope_scaling={"rope_type": "llama3"}), 8, "cpu")
+        rotary_tables(dict(config, rope_scaling={"rope_type": "yarn", "factor": 4.0}), 8, "cpu")
 
 
 def test_seeded_weights_are_reproducible_and_ordered():
@@ -95,3 +97,24 @@ def test_kv_row_swizzle_is_an_involution_with_the_kernel_mapping():
     assert torch.equal(kv_row_swizzle(stored), rows)
     for t, d in ((0, 5), (13, 42), (31, 63), (8, 17)):
         assert stored[1, t, (((d >> 3) ^ (t & 7)) << 3) | (d & 7)] == rows[1, t, d]
+
+
+@pytest.mark.parametrize("case", ["llama31_8b", "llama32_1b", "linear4"])
+def test_scaled_rope_tables_match_the_hf_rotary_module(case):
+    """rope_scaling of the real Llama-3.1/3.2 checkpoints ("llama3") and "linear": inv_freq and
+    the bf16 cos/sin rows against the fixture written from the HF rotary module the reference
+    calls (tests/golden/make_golden_rope.py)."""
+    from tilemega_b200.serving.state import inverse_frequencies, rotary_tables
+    record = torch.load(GOLDEN / "rope_llama3.pt")[case]
+    config = dict(record["config"], hidden_size=record["config"]["head_dim"] * 4, num_attention_heads=4)
+    assert torch.allclose(inverse_frequencies(config), record["inv_freq"], rtol=1e-6, atol=0)
+    capacity = max(record["positions"]) + 1
+    cos, sin = rotary_tables(config, capacity, "cpu")
+    rows = torch.tensor(record["positions"])
+    # angles of ~1e5 rad in fp32 carry ~1e-2 rad of rounding, so two correct evaluations may
+    # round a few table entries to neighbouring bf16 values; almost all must be identical
+    for ours, theirs in ((cos[rows], record["cos"]), (sin[rows], record["sin"])):
+        assert (ours.float() - theirs.float()).abs().max().item() <= 2 ** -7
+        assert (ours == theirs).float().mean().item() >= 0.98
+    with pytest.raises(ValueError):
+        rotary_tables(dict(config, rope_scaling={"rope_type": "yarn", "factor": 2.0}), 16, "cpu")

@@ -17,7 +17,8 @@ LIBRARY = LIB_DIR / "libtilemega_b200.so"
 # (object name, source, extra flags). The kernel source is compiled twice, side by side:
 # plain (unsharded dense plans) and extended (tensor parallelism, mixture of experts, QK norm).
 UNITS = (("megakernel", "megakernel.cu", ()), ("megakernel_extended", "megakernel.cu", ("-DTMB_EXTENDED=1",)),
-         ("runtime", "runtime.cu", ()), ("plan_spec", "plan_spec.cpp", ()), ("static_probe", "static_probe.cu", ()))
+         ("runtime", "runtime.cu", ()), ("plan_spec", "plan_spec.cpp", ()), ("static_probe", "static_probe.cu", ()),
+         ("pack", "pack.cu", ()))
 SOURCES = tuple(sorted({unit[1] for unit in UNITS}))
 HEADERS = ("params.h", "ptx.cuh", "plan_spec.h", "json.h")
 
@@ -50,12 +51,16 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
     build_dir = ROOT / "build"
     build_dir.mkdir(exist_ok=True)
     running = []
+    headers = [CSRC / name for name in HEADERS] + [ROOT.parent / "include" / "tilemega_b200.h"]
     for stem, name, flags in UNITS:
         obj = build_dir / (stem + ".o")
+        objects.append(str(obj))
+        inputs = [CSRC / name] + headers
+        if not force and not verbose and obj.exists() and all(path.stat().st_mtime <= obj.stat().st_mtime for path in inputs):
+            continue   # this unit's object is newer than its source and every header
         cmd = [nvcc(), *common, *flags, "-x", "cu" if name.endswith(".cu") else "c++", "-c", str(CSRC / name), "-o",
                str(obj)]
         running.append((cmd, subprocess.Popen(cmd)))
-        objects.append(str(obj))
     for cmd, process in running:
         if process.wait() != 0:
             raise subprocess.CalledProcessError(process.returncode, cmd)

@@ -38,20 +38,6 @@
 #ifndef TMB_EXTENDED
 #define TMB_EXTENDED 0   // 1: the translation unit with tensor parallelism, mixture of experts and QK norm
 #endif
-#ifndef TMB_GEMV_MMA
-#define TMB_GEMV_MMA 1   // 1: weight pages through ldmatrix + mma.sync (bf16, fp32 accumulate); 0: fp32 FMA on CUDA cores
-#endif
-#ifndef TMB_MIXED_FMA
-#define TMB_MIXED_FMA 0
-#endif
-#ifndef TMB_GEMV_NOINLINE
-#define TMB_GEMV_NOINLINE 0
-#endif
-#if TMB_GEMV_NOINLINE
-#define TMB_GEMV_CALL __noinline__
-#else
-#define TMB_GEMV_CALL __forceinline__
-#endif
 
 namespace tmb {
 
@@ -82,6 +68,7 @@ struct Ctx {
   const MegaParams& p;
   unsigned char* smem;
   int warp, lane, tid;
+  int cta;                           // this CTA's index in its plan's grid (several plans may share one launch)
   uint32_t slot, phase;              // ring cursor
   unsigned long long bar_target;     // arrivals that complete the previous stage
   uint32_t task_seq;                 // tasks finished by this CTA (epilogue warp rotation)
@@ -92,8 +79,8 @@ struct Ctx {
   int pending_next;                  // ... and for the stage after it (claimed a whole stage ahead)
   uint32_t gemv_seq;                 // GEMV tasks finished by this CTA (partial-sum ring cursor)
   uint32_t route_phase;              // routings published (arithmetic warps) / consumed (streaming thread), mod 2
-  __device__ Ctx(const MegaParams& q, unsigned char* s)
-      : p(q), smem(s), warp(threadIdx.x >> 5), lane(threadIdx.x & 31), tid(threadIdx.x), slot(0), phase(0),
+  __device__ Ctx(const MegaParams& q, unsigned char* s, int cta_index)
+      : p(q), smem(s), warp(threadIdx.x >> 5), lane(threadIdx.x & 31), tid(threadIdx.x), cta(cta_index), slot(0), phase(0),
         bar_target(q.bar_base), task_seq(0), dead(false), q_pos(0), inst(0), pending(0), pending_next(0), gemv_seq(0),
         route_phase(0) {}
   __device__ uint64_t* full(int i) const { return reinterpret_cast<uint64_t*>(smem + kOffFull) + i; }
@@ -213,7 +200,7 @@ __device__ __forceinline__ bool grid_wait(Ctx& c) {
 __device__ __forceinline__ void trace_mark(const Ctx& c, bool on, int stage, int what) {
   if (on && c.tid == 0) {
     const int stages = c.p.stages_per_layer * c.p.layers + 1;
-    c.p.trace[(size_t(blockIdx.x) * stages + stage) * 4 + what] = global_timer();
+    c.p.trace[(size_t(c.cta) * stages + stage) * 4 + what] = global_timer();
   }
 }
 
@@ -384,12 +371,8 @@ __device__ __forceinline__ void stream_pages(Ctx& c, const GemvGeo& geo, const u
     // the last page of a padded reduction: its pad columns (whole 64-column blocks at the
     // end of the page, which no warp reads) are not copied
     const uint32_t bytes = pg + 1 == geo.pages_per_task ? uint32_t(geo.last_page_bytes) : page_bytes;
-    if (c.p.diag & kDiagNoCopy) {
-      mbar_arrive(c.full(c.slot));   // diagnosis: arithmetic warps at their own speed on whatever is in the ring
-    } else {
-      mbar_expect_tx(c.full(c.slot), bytes);
-      bulk_g2s_hint(c.ring(c.slot), src, bytes, c.full(c.slot), policy);
-    }
+    mbar_expect_tx(c.full(c.slot), bytes);
+    bulk_g2s_hint(c.ring(c.slot), src, bytes, c.full(c.slot), policy);
     c.advance();
   }
 }
@@ -400,29 +383,18 @@ __device__ __forceinline__ void stream_gemv_task(Ctx& c, const GemvGeo& geo, con
   stream_pages(c, geo, weights + (size_t(t) * size_t(geo.task_pages) + size_t(geo.page0)) * page_bytes, t, page_bytes, policy);
 }
 
-// static_quarters/4 of a CTA's even share of a stage are dealt statically (task
-// cta + j*grid), so the first pages of the next stage are known without a round
-// trip and stream behind the current stage's last ones; the rest is claimed from
-// the stage's counter, so the stage still ends together on every SM.
-__device__ __forceinline__ int static_share(const MegaParams& p, int ntasks) {
-  return (ntasks / p.grid) * p.static_quarters / 4;
-}
-
 __device__ __forceinline__ void stream_gemv(Ctx& c, const GemvGeo& geo, const void* weights, uint64_t policy) {
   const uint32_t page_bytes = uint32_t(kTileN) * uint32_t(geo.tile_k) * 2u;
   const unsigned char* w = static_cast<const unsigned char*>(weights);
-  const int dealt = static_share(c.p, geo.ntasks);
-  for (int j = 0; j < dealt && !c.dead; ++j)
-    stream_gemv_task(c, geo, w, int(blockIdx.x) + j * c.p.grid, page_bytes, policy);
   // Tasks are claimed in chunks of geo.claim_chunk (about 64 KB of pages): the claim for the
   // next chunk is in flight while this one is copied, and its round trip to L2 and back
   // (~1 us) must not be longer than that copying, or short tasks wait for their ids.
   const int chunk_tasks = geo.claim_chunk;
   int chunk = c.pending;
-  while (dealt * c.p.grid + chunk * chunk_tasks < geo.ntasks && !c.dead) {
+  while (chunk * chunk_tasks < geo.ntasks && !c.dead) {
     const int upcoming = claim(c, c.inst);
     for (int j = 0; j < chunk_tasks; ++j) {
-      const int t = dealt * c.p.grid + chunk * chunk_tasks + j;
+      const int t = chunk * chunk_tasks + j;
       if (t < geo.ntasks) stream_gemv_task(c, geo, w, t, page_bytes, policy);
     }
     chunk = upcoming;
@@ -491,7 +463,7 @@ __device__ __forceinline__ void stream_attn(Ctx& c, const LayerPtrs& lp, int pas
     const AttnTask a = attn_task(c.p, past, NK, spt, t);
     const int nblk = a.pos / kKvBlock + 1;
     for (int s = a.slot0; s < a.slot1; ++s) {
-      const int nb = (c.p.diag & kDiagNoCopy) ? 0 : min(NB, nblk - s * NB);
+      const int nb = min(NB, nblk - s * NB);
       // the block-table entries of the slot first (independent loads), then the copies
       long long off[NB];
 #pragma unroll
@@ -610,21 +582,16 @@ struct GemvIo {
   uint32_t ar_epoch;           // ... and the epoch its packets carry (never 0, grows with every all-reduce)
 };
 
-// Where the four 32-bit words of 16-byte chunk i of an activation row go. The
-// tensor-pipe path wants them in A-fragment order: inside every 64-column block,
-// word q (columns 8m+2q, 8m+2q+1) of chunk m sits at block*32 + q*8 + m, so that
-// lane (row g, q) reads its eight words of a block with two 128-bit loads and
-// nothing else is fetched. The CUDA-core path keeps the natural order.
+// Where the four 32-bit words of 16-byte chunk i of an activation row go: A-fragment
+// order. Inside every 64-column block, word q (columns 8m+2q, 8m+2q+1) of chunk m sits
+// at block*32 + q*8 + m, so that lane (row g, q) reads its eight words of a block with
+// two 128-bit loads and nothing else is fetched.
 __device__ __forceinline__ void store_row_chunk(uint32_t* row, int i, const uint4& v) {
-#if TMB_GEMV_MMA
   uint32_t* dst = row + (i >> 3) * 32 + (i & 7);
   dst[0] = v.x;
   dst[8] = v.y;
   dst[16] = v.z;
   dst[24] = v.w;
-#else
-  reinterpret_cast<uint4*>(row)[i] = v;
-#endif
 }
 
 // Stage the stage's B activation rows in shared memory; RMSNorm fused:
@@ -671,7 +638,7 @@ __device__ __forceinline__ void stage_rows(Ctx& c, const GemvIo& io, const GemvG
     if (io.norm) xs4[kNormRow * pitch + i] = i < src_chunks ? __ldg(nw + i) : make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
     for (int b = 0; b < B; ++b) {
-      if (io.embed && (b % p.grid) == int(blockIdx.x) && i < src_chunks)
+      if (io.embed && (b % p.grid) == c.cta && i < src_chunks)
         reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.x) + size_t(b) * k_src)[i] = v[b];
       if (io.norm) {
         if (!kWide) xs4[(B + b) * pitch + i] = v[b];
@@ -732,39 +699,9 @@ __device__ __forceinline__ void stage_rows(Ctx& c, const GemvIo& io, const GemvG
 // One page = 8 weight rows x 2048 columns, 128-byte swizzled in 8x64 atoms:
 // element (r, col) sits at 1024*(col/64) + 128*r + 16*((col%64/8) ^ r) + 2*(col%8)
 // bytes (python/tilemega/serving/weights.py:239-240 with tn = 8). Warp w owns
-// columns [256w, 256w+256), lane l the 8 columns 8l.. of that segment.
-// CUDA-core form: lane l of warp w multiplies its 8 columns of each of the 8 rows.
-template <int B>
-__device__ __forceinline__ void gemv_page_fma(const unsigned char* page, const unsigned char* xs, int k, int col0,
-                                              int warp, int lane, float (&acc)[kTileN][B]) {
-  uint4 xv[B];
-#pragma unroll
-  for (int b = 0; b < B; ++b)
-    xv[b] = *reinterpret_cast<const uint4*>(xs + (size_t(b) * (k + 8) + col0 + 256 * warp + 8 * lane) * 2);
-  const unsigned char* pg = page + 1024 * (4 * warp + (lane >> 3));
-  const int sw = lane & 7;
-#pragma unroll
-  for (int r = 0; r < kTileN; ++r) {
-    const uint4 w = *reinterpret_cast<const uint4*>(pg + 128 * r + 16 * (sw ^ r));
-#pragma unroll
-    for (int b = 0; b < B; ++b) {
-#if TMB_MIXED_FMA
-      fma_bf16x2(acc[r][b], w.x, xv[b].x);
-      fma_bf16x2(acc[r][b], w.y, xv[b].y);
-      fma_bf16x2(acc[r][b], w.z, xv[b].z);
-      fma_bf16x2(acc[r][b], w.w, xv[b].w);
-#else
-      float wf[8], xf[8];
-      unpack8(w, wf);
-      unpack8(xv[b], xf);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) acc[r][b] = fmaf(wf[j], xf[j], acc[r][b]);
-#endif
-    }
-  }
-}
-
-// Tensor-pipe form of the same page: D[batch row][weight row] += X * W^T with
+// columns [256w, 256w+256) of every page.
+//
+// A page on the tensor pipe: D[batch row][weight row] += X * W^T with
 // mma.sync m16n8k16. The 8 weight rows of the page are the B operand's 8 columns
 // (an 8x64 swizzle atom of the page IS four ldmatrix tiles), the batch rows are the A
 // operand's rows 0..7 (rows past the batch alias row B-1 and their outputs are never
@@ -790,38 +727,6 @@ __device__ __forceinline__ void gemv_page_mma(const unsigned char* page, const u
     mma_bf16_m16n8k16(d[2], xhi.x, xhi.y, w[0], w[1]);
     mma_bf16_m16n8k16(d[3], xhi.z, xhi.w, w[2], w[3]);
   }
-}
-
-// Sum 8 per-lane values over the 32 lanes of a warp with 9 shuffles: three
-// halving exchanges (lane bits 4,3,2 select the row) then two full exchanges.
-// On return lane l holds the total of row (l >> 2) in v[0].
-__device__ __forceinline__ void warp_reduce_rows(float (&v)[kTileN], int lane) {
-  {
-    const bool up = lane & 16;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float send = up ? v[i] : v[i + 4];
-      const float recv = __shfl_xor_sync(0xffffffffu, send, 16);
-      v[i] = (up ? v[i + 4] : v[i]) + recv;
-    }
-  }
-  {
-    const bool up = lane & 8;
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const float send = up ? v[i] : v[i + 2];
-      const float recv = __shfl_xor_sync(0xffffffffu, send, 8);
-      v[i] = (up ? v[i + 2] : v[i]) + recv;
-    }
-  }
-  {
-    const bool up = lane & 4;
-    const float send = up ? v[0] : v[1];
-    const float recv = __shfl_xor_sync(0xffffffffu, send, 4);
-    v[0] = (up ? v[1] : v[0]) + recv;
-  }
-  v[0] += __shfl_xor_sync(0xffffffffu, v[0], 2);
-  v[0] += __shfl_xor_sync(0xffffffffu, v[0], 1);
 }
 
 __device__ __forceinline__ float silu_bf16(float g) {
@@ -874,9 +779,9 @@ __device__ __forceinline__ float2 tp_finish(const MegaParams& p, int ar_region, 
 // batch row b to every peer as one packet {epoch 28 bits, bf16 value, 20-bit index};
 // lanes 0..tp_world-1 of the calling warp each fetch one rank's candidate. Returns the
 // candidate this lane holds (lanes past tp_world: none).
-static __device__ __noinline__ void tp_exchange_argmax(const MegaParams& p, unsigned long long epoch, int b, int lane,
+static __device__ __noinline__ void tp_exchange_argmax(const MegaParams& p, int cta, unsigned long long epoch, int b, int lane,
                                                 float& value, int& index) {
-  if (blockIdx.x == 0 && lane < p.tp_world && lane != p.tp_rank) {
+  if (cta == 0 && lane < p.tp_world && lane != p.tp_rank) {
     const unsigned long long packet =
         (epoch << 36) | ((unsigned long long)bf16_bits(value) << 20) | (unsigned long long)(index & 0xfffff);
     st_relaxed_sys(p.xchg[lane] + size_t(p.tp_rank) * kMaxBatch + b, packet);
@@ -1028,7 +933,7 @@ __device__ __forceinline__ void gemv_epilogue(Ctx& c, const GemvGeo& geo, const 
 }
 
 template <int B, int X>
-__device__ TMB_GEMV_CALL void gemv_stage(Ctx& c, const GemvGeo& geo, const GemvIo& io, bool tr, int stage) {
+__device__ __forceinline__ void gemv_stage(Ctx& c, const GemvGeo& geo, const GemvIo& io, bool tr, int stage) {
   const MegaParams& p = c.p;
   stage_rows<B>(c, io, geo);
   trace_mark(c, tr, stage, 2);
@@ -1058,17 +963,9 @@ __device__ TMB_GEMV_CALL void gemv_stage(Ctx& c, const GemvGeo& geo, const GemvI
   ar.task = -1;
   for (int t = fifo_pop(c); t >= 0; t = fifo_pop(c)) {
     const int rt = t;
-#if TMB_GEMV_MMA
     float d[4][4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) d[0][i] = d[1][i] = d[2][i] = d[3][i] = 0.f;
-#else
-    float acc[kTileN][B];
-#pragma unroll
-    for (int r = 0; r < kTileN; ++r)
-#pragma unroll
-      for (int b = 0; b < B; ++b) acc[r][b] = 0.f;
-#endif
     const bool owner = warp == int(task_seq & 7);
     // the owner fetches the residual now, so the L2 round trip overlaps the arithmetic
     float residual[EpiPasses<B>::value];
@@ -1083,13 +980,8 @@ __device__ TMB_GEMV_CALL void gemv_stage(Ctx& c, const GemvGeo& geo, const GemvI
       mbar_wait_warp(c, full0 + slot, phase, kSiteFull);
       // a warp whose 256 columns of this page lie wholly in the reduction's zero pad
       // has nothing to add (and that part of the slot was not copied)
-      if (pg * geo.tile_k + 256 * warp < geo.k_src) {
-#if TMB_GEMV_MMA
+      if (pg * geo.tile_k + 256 * warp < geo.k_src)
         gemv_page_mma<B>(ring0 + slot * kSlotBytes, xs, geo.k, pg * geo.tile_k, warp, lane, d);
-#else
-        gemv_page_fma<B>(ring0 + slot * kSlotBytes, xs, geo.k, pg * geo.tile_k, warp, lane, acc);
-#endif
-      }
       __syncwarp();
       if (lane == 0) mbar_arrive(empty0 + slot);
       if (++slot == nslots) { slot = 0; phase ^= 1u; }
@@ -1101,23 +993,12 @@ __device__ TMB_GEMV_CALL void gemv_stage(Ctx& c, const GemvGeo& geo, const GemvI
     // No wait before reusing buffer `buf`: its previous task lies kPartialRing tasks
     // back, and no warp can be more than the data ring (at most kMaxSlots pages, so
     // at most kMaxSlots tasks) ahead of the owner that reads it one task late.
-#if TMB_GEMV_MMA
     // lane holds D[batch row lane/4][weight rows 2*(lane%4), +1]
     if ((lane >> 2) < B) {
       float* dst = red + ((buf * 8 + warp) * 8 + 2 * (lane & 3)) * B + (lane >> 2);
       dst[0] = (d[0][0] + d[1][0]) + (d[2][0] + d[3][0]);
       dst[B] = (d[0][1] + d[1][1]) + (d[2][1] + d[3][1]);
     }
-#else
-#pragma unroll
-    for (int b = 0; b < B; ++b) {
-      float v[kTileN];
-#pragma unroll
-      for (int r = 0; r < kTileN; ++r) v[r] = acc[r][b];
-      warp_reduce_rows(v, lane);
-      if ((lane & 3) == 0) red[((buf * 8 + warp) * 8 + (lane >> 2)) * B + b] = v[0];
-    }
-#endif
     __syncwarp();
     if (lane == 0) mbar_arrive(c.pfull(buf));
     if (pending.task >= 0) {
@@ -1218,7 +1099,7 @@ static __device__ __noinline__ void route_token(Ctx& c, int layer) {
     __syncwarp(0xffu);   // every lane has read all weights before any is overwritten
     c.route_w()[s] = w;
     c.route_e()[s] = e;
-    if (blockIdx.x == 0 && s < p.topk) {
+    if (c.cta == 0 && s < p.topk) {
       p.route_idx[layer * p.topk + s] = e;
       p.route_w[layer * p.topk + s] = w;
     }
@@ -1697,7 +1578,7 @@ __device__ void consumer_main(Ctx& c) {
       if (c.tid < B) c.tok()[c.tid] = __ldcg(p.tokens + size_t(c.tid) * p.capacity + seq_pos(p, past, c.tid));
       consumer_sync();
     }
-    if (blockIdx.x == 0 && c.tid == 0) p.step_ns[step] = global_timer();
+    if (c.cta == 0 && c.tid == 0) p.step_ns[step] = global_timer();
     const bool tr = p.trace != nullptr && step == p.trace_step;
     int stage = 0;
     LayerPtrs lp = p.layer[0];
@@ -1799,8 +1680,8 @@ __device__ void consumer_main(Ctx& c) {
         const int i = c.best_idx()[w * kMaxBatch + c.tid];
         if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
       }
-      p.argmax_val[size_t(blockIdx.x) * B + c.tid] = bv;
-      p.argmax_idx[size_t(blockIdx.x) * B + c.tid] = bi;
+      p.argmax_val[size_t(c.cta) * B + c.tid] = bv;
+      p.argmax_idx[size_t(c.cta) * B + c.tid] = bi;
     }
     grid_arrive(c);
     if (!grid_wait(c)) return;
@@ -1830,7 +1711,7 @@ __device__ void consumer_main(Ctx& c) {
         // index (include/tilemega/Backend/Sm90DenseHead.cuh:139-201).
         float ov = bv;
         int oi = bi;
-        tp_exchange_argmax(p, (steps_before + 1ull) & 0xfffffffull, b, c.lane, ov, oi);
+        tp_exchange_argmax(p, c.cta, (steps_before + 1ull) & 0xfffffffull, b, c.lane, ov, oi);
 #pragma unroll
         for (int mk = 4; mk; mk >>= 1) {   // tp_world <= 8: lanes 0..7 hold the ranks' candidates
           const float pv = __shfl_xor_sync(0xffffffffu, ov, mk);
@@ -1846,21 +1727,21 @@ __device__ void consumer_main(Ctx& c) {
         int tok = min(max(bi, 0), p.vocab - 1);
         if (pos + 1 < p.prompt_len) {
           tok = __ldcg(slot);   // teacher-forced prompt position: the token state wins
-        } else if (blockIdx.x == 0 && pos + 1 < p.capacity) {
+        } else if (c.cta == 0 && pos + 1 < p.capacity) {
           *slot = tok;
         }
         c.tok()[b] = tok;
       }
     }
-    if (blockIdx.x == 0 && c.tid == 0) p.step_ns[step + 1] = global_timer();
+    if (c.cta == 0 && c.tid == 0) p.step_ns[step + 1] = global_timer();
     consumer_sync();
   }
 }
 
 template <int B, int D, int GQ, int X>
-__global__ void __launch_bounds__(kThreads, 1) decode_megakernel(const __grid_constant__ MegaParams p) {
+__device__ __forceinline__ void run_cta(const MegaParams& p, int cta) {
   extern __shared__ __align__(1024) unsigned char smem[];
-  Ctx c(p, smem);
+  Ctx c(p, smem, cta);
   if (threadIdx.x == 0) {
     for (int i = 0; i < p.nslots; ++i) {
       mbar_init(c.full(i), 1);
@@ -1883,6 +1764,23 @@ __global__ void __launch_bounds__(kThreads, 1) decode_megakernel(const __grid_co
   } else {
     consumer_main<B, D, GQ, X>(c);
   }
+}
+
+template <int B, int D, int GQ, int X>
+__global__ void __launch_bounds__(kThreads, 1) decode_megakernel(const __grid_constant__ MegaParams p) {
+  run_cta<B, D, GQ, X>(p, int(blockIdx.x));
+}
+
+// Several rank plans of one tensor-parallel job as ONE cooperative launch on one device:
+// CTAs [0, grid_0) run rank 0's plan, the next grid_1 rank 1's, and so on. The ranks wait
+// for one another's packets, so they must be co-resident, which separate launches on one
+// GPU cannot promise and a cooperative launch does. For boxes with fewer GPUs than ranks
+// (and for tests); a rank's parameters are read from global memory here.
+template <int B, int D, int GQ, int X>
+__global__ void __launch_bounds__(kThreads, 1) decode_megakernel_ranks(const MegaParams* ranks, int count) {
+  int base = 0, r = 0;
+  while (r + 1 < count && int(blockIdx.x) >= base + ranks[r].grid) base += ranks[r++].grid;
+  run_cta<B, D, GQ, X>(ranks[r], int(blockIdx.x) - base);
 }
 
 #if !TMB_EXTENDED
@@ -1957,8 +1855,43 @@ cudaError_t run_decode_extended(const MegaParams& p, cudaStream_t stream, bool p
   return gq == 8 ? run_batch<128, 8, kXTp>(p, smem_bytes, stream, prepare)
                  : run_batch<128, 4, kXTp>(p, smem_bytes, stream, prepare);
 }
+
+template <int B, int GQ>
+static cudaError_t run_ranks_instance(const MegaParams* ranks_dev, int count, int total_grid, size_t smem_bytes,
+                                      cudaStream_t stream) {
+  auto kernel = decode_megakernel_ranks<B, 128, GQ, kXTp>;
+  cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem_bytes));
+  if (err != cudaSuccess) return err;
+  void* args[] = {static_cast<void*>(&ranks_dev), static_cast<void*>(&count)};
+  // cooperative: the launch fails unless every CTA of every rank is resident at once
+  return cudaLaunchCooperativeKernel(reinterpret_cast<void*>(kernel), dim3(unsigned(total_grid)), dim3(kThreads), args,
+                                     smem_bytes, stream);
+}
+
+// `first` is the host copy of ranks_dev[0]: all ranks of a job share one plan geometry.
+cudaError_t run_decode_ranks(const MegaParams& first, const MegaParams* ranks_dev, int count, int total_grid,
+                             cudaStream_t stream) {
+  const size_t smem_bytes = size_t(ring_offset(first.xs_bytes, first.batch) + first.nslots * kSlotBytes);
+  if (first.kv_heads <= 0 || first.heads % first.kv_heads || first.head_dim != 128 || first.experts > 0 || first.qk_norm)
+    return cudaErrorInvalidValue;
+  const int gq = first.heads / first.kv_heads;
+  if (gq != 4 && gq != 8) return cudaErrorInvalidValue;
+  switch (first.batch) {
+    case 1: return gq == 8 ? run_ranks_instance<1, 8>(ranks_dev, count, total_grid, smem_bytes, stream)
+                           : run_ranks_instance<1, 4>(ranks_dev, count, total_grid, smem_bytes, stream);
+    case 2: return gq == 8 ? run_ranks_instance<2, 8>(ranks_dev, count, total_grid, smem_bytes, stream)
+                           : run_ranks_instance<2, 4>(ranks_dev, count, total_grid, smem_bytes, stream);
+    case 3: return gq == 8 ? run_ranks_instance<3, 8>(ranks_dev, count, total_grid, smem_bytes, stream)
+                           : run_ranks_instance<3, 4>(ranks_dev, count, total_grid, smem_bytes, stream);
+    case 4: return gq == 8 ? run_ranks_instance<4, 8>(ranks_dev, count, total_grid, smem_bytes, stream)
+                           : run_ranks_instance<4, 4>(ranks_dev, count, total_grid, smem_bytes, stream);
+    default: return cudaErrorInvalidValue;   // the one-device form is built for batch 1..4
+  }
+}
 #else
 cudaError_t run_decode_extended(const MegaParams& p, cudaStream_t stream, bool prepare);
+cudaError_t run_decode_ranks(const MegaParams& first, const MegaParams* ranks_dev, int count, int total_grid,
+                             cudaStream_t stream);
 
 static cudaError_t run_decode(const MegaParams& p, cudaStream_t stream, bool prepare) {
   if (p.tp_world > 1 || p.experts > 0 || p.qk_norm) return run_decode_extended(p, stream, prepare);
@@ -1986,6 +1919,11 @@ extern "C" int tmb_prepare_decode(const tmb::MegaParams* p) { return int(tmb::ru
 
 extern "C" int tmb_launch_decode(const tmb::MegaParams* p, void* stream) {
   return int(tmb::run_decode(*p, static_cast<cudaStream_t>(stream), false));
+}
+
+extern "C" int tmb_launch_decode_ranks(const tmb::MegaParams* first, const tmb::MegaParams* ranks_dev, int count,
+                                       int total_grid, void* stream) {
+  return int(tmb::run_decode_ranks(*first, ranks_dev, count, total_grid, static_cast<cudaStream_t>(stream)));
 }
 
 extern "C" int tmb_launch_watchdog_probe(const tmb::MegaParams* p, int withhold, void* stream) {

@@ -19,8 +19,8 @@ constexpr int kMaxTp = 8;                               // tensor-parallel ranks
 
 // kRouter exists in mixture-of-experts plans only; there kGateUp / kDown describe ONE expert.
 enum StageKind : int { kQkv = 0, kOProj = 1, kGateUp = 2, kDown = 3, kHead = 4, kRouter = 5, kNumGemv = 6 };
-constexpr int kMaxTopK = 8;
-constexpr int kMaxDownSplits = 8;                       // stages a down projection's reduction may be cut into                             // experts per token
+constexpr int kMaxTopK = 8;                             // experts per token
+constexpr int kMaxDownSplits = 8;                       // stages a down projection's reduction may be cut into
 // kEpiResidualAllReduce: kEpiResidual after the ranks' bf16 partial sums are added in rank order.
 // kEpiPartial: the fp32 sums of one part of a split reduction, kept in global memory for the next part.
 enum Epilogue : int { kEpiStore = 0, kEpiResidual = 1, kEpiSwiGLU = 2, kEpiHead = 3, kEpiResidualAllReduce = 4, kEpiPartial = 5 };
@@ -63,9 +63,7 @@ enum StatusWord : int {
   kStFired = 0, kStSite, kStBlock, kStThread, kStStage, kStTask, kStProducer,
   kStGroup, kStRow, kStNeed, kStValue, kStIteration, kStWords
 };
-// Diagnostic switches (plan sidecar "diag"): results are meaningless when any is set.
-enum DiagFlag : int { kDiagNoCopy = 1 };   // the streaming warp posts ring slots without copying into them
-enum WaitSite : int { kSiteGrid = 1, kSiteFull = 2, kSiteEmpty = 3, kSiteDrain = 4, kSiteTest = 5, kSitePeer = 6 };
+enum WaitSite : int { kSiteGrid = 1, kSiteFull = 2, kSiteEmpty = 3, kSiteTest = 5, kSitePeer = 6 };
 
 struct MegaParams {
   // model
@@ -87,9 +85,7 @@ struct MegaParams {
   int first_step, nsteps, prompt_len;
   int write_logits;
   int grid, nslots, xs_bytes;
-  int diag;                 // DiagFlag bits
   int attn_min_spt;         // least ring slots of keys per attention task (a task's fixed cost wants amortising)
-  int static_quarters;      // quarters of a CTA's even share of a GEMV stage that are dealt, not claimed (0..4)
   unsigned long long bar_base;     // grid-barrier arrivals before this launch
   unsigned long long watchdog_ns;  // per-wait limit
   GemvGeo geo[kNumGemv];
@@ -136,16 +132,5 @@ struct MegaParams {
   unsigned long long* ar[kMaxTp];     // [2 regions][tp_world sources][B][hidden/2] packets {epoch:32, bf16 pair:32}
   unsigned long long* xchg[kMaxTp];   // [tp_world sources][kMaxBatch] packets {epoch:28, bf16 value:16, index:20}
 };
-
-// Per-step, per-sequence attention partition shared by the streaming warp and
-// the arithmetic warps (both must enumerate exactly the same slots).
-struct AttnSeq {
-  int pos;        // position of the new token
-  int nslots;     // ring slots covering positions [0, pos]
-  int nchunks;    // tasks per KV head
-  int task_base;  // first task index of this sequence
-};
-
-static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
 }  // namespace tmb

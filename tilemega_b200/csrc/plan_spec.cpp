@@ -161,9 +161,6 @@ PlanSpec PlanSpec::FromJson(const Json& plan) {
   }
   s.grid = int(plan.integer("grid", 0));
   s.slots = int(plan.integer("slots", 0));
-  s.diag = int(plan.integer("diag", 0));
-  s.static_quarters = int(plan.integer("static_quarters", s.static_quarters));
-  if (s.static_quarters < 0 || s.static_quarters > 4) throw std::invalid_argument("static_quarters must lie in [0, 4]");
   s.attn_min_slots = int(plan.integer("attn_min_slots", s.attn_min_slots));
   if (s.attn_min_slots < 1 || s.attn_min_slots > 64) throw std::invalid_argument("attn_min_slots must lie in [1, 64]");
   s.write_logits = plan.flag("write_logits", true);

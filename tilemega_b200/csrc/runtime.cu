@@ -24,6 +24,8 @@
 extern "C" int tmb_smem_bytes(const tmb::MegaParams* p);
 extern "C" int tmb_prepare_decode(const tmb::MegaParams* p);
 extern "C" int tmb_launch_decode(const tmb::MegaParams* p, void* stream);
+extern "C" int tmb_launch_decode_ranks(const tmb::MegaParams* first, const tmb::MegaParams* ranks_dev, int count,
+                                       int total_grid, void* stream);
 extern "C" int tmb_launch_watchdog_probe(const tmb::MegaParams* p, int withhold, void* stream);
 
 namespace {
@@ -108,6 +110,8 @@ struct Plan {
   bool tp_bound = false;                // tensor-parallel plan: tm_plan_bind_tp has been called
   uint64_t tp_steps = 0;                // decode steps launched so far (the all-reduce epochs count from it)
   unsigned char* sync_block = nullptr;  // barrier + counters, rezeroed by every launch
+  bool abandoned = false;               // a bounded device wait was seen to give up: launches answer -4 until cleared
+  tmb::MegaParams* ranks_dev = nullptr; // parameter records of a several-ranks-in-one-launch job (owned by its first plan)
   size_t sync_bytes = 0;
   size_t claim_offset = 0;
 };
@@ -274,9 +278,7 @@ void* tm_plan_create(int batch, void* const* external, int device) {
                      expert_rows});
   xs = (xs + 127) & ~127;
   p.xs_bytes = xs;
-  p.static_quarters = s.static_quarters;
   p.attn_min_spt = s.attn_min_slots;
-  p.diag = s.diag;
   const int limit = int(prop.sharedMemPerBlockOptin);
   p.nslots = tmb::kMaxSlots;
   if (s.slots > 0) p.nslots = std::min(s.slots, tmb::kMaxSlots);
@@ -422,36 +424,109 @@ int tm_plan_set_prompt_len(void* handle, int prompt_len) {
   return 0;
 }
 
-int tm_plan_launch_steps(void* handle, uint32_t first_step, uint32_t steps, uint32_t mode, uint64_t base_iteration,
-                         void* stream) {
-  Plan* plan = AsPlan(handle);
-  if (!plan || steps == 0) return Fail(-1, "tm_plan_launch_steps: bad argument");
-  if (mode != TM_SERVING_L1 && mode != TM_SERVING_L2) return Fail(-3, "tm_plan_launch_steps: unknown mode");
+}  // extern "C"
+
+namespace {
+
+// Everything a launch of `steps` steps checks and prepares before the kernel goes out:
+// the argument and iteration rules, the counters rezeroed on the stream, the parameter
+// record of this launch in `out`. Returns 0 or the error code to hand back.
+int PrepareLaunch(Plan* plan, const char* who, uint32_t first_step, uint32_t steps, uint32_t mode, uint64_t base_iteration,
+                  cudaStream_t s, tmb::MegaParams* out) {
+  const std::string name = who;
+  if (!plan || steps == 0) return Fail(-1, name + ": bad argument");
+  if (mode != TM_SERVING_L1 && mode != TM_SERVING_L2) return Fail(-3, name + ": unknown mode");
+  if (plan->abandoned)
+    return Fail(-4, name + ": a bounded device wait gave up on this plan; read tm_plan_watchdog, then tm_plan_clear_watchdog");
   if (uint64_t(first_step) + steps > plan->step_count)
-    return Fail(-2, "tm_plan_launch_steps: steps outside the interval given to tm_plan_set_steps");
+    return Fail(-2, name + ": steps outside the interval given to tm_plan_set_steps");
   if (base_iteration != plan->next_iteration[mode])
-    return Fail(-2, "tm_plan_launch_steps: iteration is not the number of previous launches of this mode");
-  DeviceScope scope(plan->device);
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
+    return Fail(-2, name + ": iteration is not the number of previous launches of this mode");
+  if (plan->params.tp_world > 1 && !plan->tp_bound)
+    return Fail(-1, name + ": a tensor-parallel plan must be bound with tm_plan_bind_tp first");
   // only the claim counters this launch can touch are rezeroed
   const size_t used = plan->claim_offset +
                       (size_t(steps) * (size_t(plan->params.stages_per_layer) * size_t(plan->params.layers) + 1) + 2) * sizeof(unsigned);
   cudaError_t err = cudaMemsetAsync(plan->sync_block, 0, used, s);
-  if (err != cudaSuccess) return Fail(int(err), std::string("tm_plan_launch_steps: ") + cudaGetErrorString(err));
-  if (plan->params.tp_world > 1 && !plan->tp_bound)
-    return Fail(-1, "tm_plan_launch_steps: a tensor-parallel plan must be bound with tm_plan_bind_tp first");
-  tmb::MegaParams p = plan->params;
-  p.tp_steps = plan->tp_steps;
-  p.first_step = int(first_step);
-  p.nsteps = int(steps);
-  p.prompt_len = plan->prompt_len;
-  p.trace = plan->trace_step >= 0 ? plan->trace_dev : nullptr;
-  p.trace_step = plan->trace_step;
+  if (err != cudaSuccess) return Fail(int(err), name + ": " + cudaGetErrorString(err));
+  *out = plan->params;
+  out->tp_steps = plan->tp_steps;
+  out->first_step = int(first_step);
+  out->nsteps = int(steps);
+  out->prompt_len = plan->prompt_len;
+  out->trace = plan->trace_step >= 0 ? plan->trace_dev : nullptr;
+  out->trace_step = plan->trace_step;
+  return 0;
+}
+
+void Launched(Plan* plan, uint32_t steps, uint32_t mode) {
+  plan->next_iteration[mode] += steps;
+  plan->tp_steps += steps;
+}
+
+}  // namespace
+
+extern "C" {
+
+int tm_plan_launch_steps(void* handle, uint32_t first_step, uint32_t steps, uint32_t mode, uint64_t base_iteration,
+                         void* stream) {
+  Plan* plan = AsPlan(handle);
+  if (!plan) return Fail(-1, "tm_plan_launch_steps: bad argument");
+  DeviceScope scope(plan->device);
+  tmb::MegaParams p;
+  const int ready = PrepareLaunch(plan, "tm_plan_launch_steps", first_step, steps, mode, base_iteration,
+                                  static_cast<cudaStream_t>(stream), &p);
+  if (ready != 0) return ready;
   const int status = tmb_launch_decode(&p, stream);
   if (status != 0)
     return Fail(status, std::string("tm_plan_launch_steps: ") + cudaGetErrorString(cudaError_t(status)));
-  plan->next_iteration[mode] += steps;
-  plan->tp_steps += steps;
+  Launched(plan, steps, mode);
+  return 0;
+}
+
+int tm_plan_launch_steps_ranks(void* const* handles, uint32_t count, uint32_t first_step, uint32_t steps, uint32_t mode,
+                               uint64_t base_iteration, void* stream) {
+  if (!handles || count < 2 || count > uint32_t(tmb::kMaxTp)) return Fail(-1, "tm_plan_launch_steps_ranks: bad argument");
+  std::vector<Plan*> plans;
+  for (uint32_t q = 0; q < count; ++q) {
+    Plan* plan = AsPlan(handles[q]);
+    if (!plan) return Fail(-1, "tm_plan_launch_steps_ranks: bad plan");
+    plans.push_back(plan);
+  }
+  Plan* lead = plans[0];
+  int total_grid = 0;
+  for (uint32_t q = 0; q < count; ++q) {
+    const tmb::MegaParams& p = plans[q]->params;
+    if (plans[q]->device != lead->device || p.tp_world != int(count) || p.tp_rank != int(q) || p.batch != lead->params.batch ||
+        plans[q]->smem_bytes != lead->smem_bytes)
+      return Fail(-1, "tm_plan_launch_steps_ranks: the plans must be ranks 0..count-1 of one job, in order, on one device");
+    total_grid += p.grid;
+  }
+  DeviceScope scope(lead->device);
+  int sms = 0;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, lead->device);
+  if (total_grid > sms)
+    return Fail(-1, "tm_plan_launch_steps_ranks: the ranks' grids together exceed the device's SMs (emit the plans with a smaller \"grid\")");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (!lead->ranks_dev) {
+    void* dev = nullptr;
+    cudaError_t err = Alloc(*lead, &dev, size_t(tmb::kMaxTp) * sizeof(tmb::MegaParams));
+    if (err != cudaSuccess) return Fail(int(err), std::string("tm_plan_launch_steps_ranks: ") + cudaGetErrorString(err));
+    lead->ranks_dev = static_cast<tmb::MegaParams*>(dev);
+  }
+  std::vector<tmb::MegaParams> records(count);
+  for (uint32_t q = 0; q < count; ++q) {
+    const int ready = PrepareLaunch(plans[q], "tm_plan_launch_steps_ranks", first_step, steps, mode, base_iteration, s, &records[q]);
+    if (ready != 0) return ready;
+  }
+  // stream-ordered after the previous launch, which may still be reading its records
+  cudaError_t err = cudaMemcpyAsync(lead->ranks_dev, records.data(), records.size() * sizeof(tmb::MegaParams),
+                                    cudaMemcpyHostToDevice, s);
+  if (err != cudaSuccess) return Fail(int(err), std::string("tm_plan_launch_steps_ranks: ") + cudaGetErrorString(err));
+  const int status = tmb_launch_decode_ranks(&records[0], lead->ranks_dev, int(count), total_grid, stream);
+  if (status != 0)
+    return Fail(status, std::string("tm_plan_launch_steps_ranks: ") + cudaGetErrorString(cudaError_t(status)));
+  for (Plan* plan : plans) Launched(plan, steps, mode);
   return 0;
 }
 
@@ -487,6 +562,7 @@ int tm_plan_watchdog(void* handle, uint64_t* record12) {
   unsigned long long words[tmb::kStWords] = {};
   if (cudaMemcpy(words, plan->params.status, sizeof(words), cudaMemcpyDeviceToHost) != cudaSuccess) return 0;
   for (int i = 0; i < 12; ++i) record12[i] = words[i];
+  if (words[tmb::kStFired]) plan->abandoned = true;   // launches answer -4 until tm_plan_clear_watchdog
   return words[tmb::kStFired] ? 1 : 0;
 }
 
@@ -495,6 +571,7 @@ int tm_plan_clear_watchdog(void* handle) {
   if (!plan) return Fail(-1, "tm_plan_clear_watchdog: bad plan");
   DeviceScope scope(plan->device);
   cudaError_t err = cudaMemset(plan->params.status, 0, tmb::kStWords * sizeof(unsigned long long));
+  if (err == cudaSuccess) plan->abandoned = false;
   return err == cudaSuccess ? 0 : Fail(int(err), cudaGetErrorString(err));
 }
 
@@ -514,7 +591,7 @@ int tm_plan_watchdog_probe(void* handle, int withhold, uint32_t limit_us, void* 
   if (err != cudaSuccess) return Fail(int(err), cudaGetErrorString(err));
   uint64_t record[12];
   const int fired = tm_plan_watchdog(handle, record);
-  tm_plan_clear_watchdog(handle);
+  if (withhold != 2) tm_plan_clear_watchdog(handle);   // 2: the record stays, as after a real abandoned launch
   return fired;
 }
 

@@ -15,7 +15,11 @@ import os
 import shutil
 from pathlib import Path
 
-from .build import LIBRARY, build_library
+from .build import LIB_DIR, LIBRARY, build_library
+
+# Plan libraries are emitted inside the package tree (a git-ignored folder next to the built
+# library), so that every shared object a process loads is one of this repository's files.
+PLAN_DIR = LIB_DIR / "plans"
 
 MODEL_KEYS = ("hidden_size", "intermediate_size", "num_attention_heads", "num_key_value_heads",
               "head_dim", "num_hidden_layers", "vocab_size", "rms_norm_eps", "tie_word_embeddings",
@@ -26,7 +30,7 @@ MODEL_KEYS = ("hidden_size", "intermediate_size", "num_attention_heads", "num_ke
 def plan_document(config: dict, *, batch_lo: int = 1, batch_hi: int | None = None, capacity: int,
                   kv_layout: str = "contiguous", num_blocks: int = 0, geometry: dict | None = None,
                   grid: int = 0, slots: int = 0, write_logits: bool = True,
-                  static_quarters: int | None = None, diag: int = 0, tp: int = 1,
+                  tp: int = 1,
                   attn_min_slots: int | None = None) -> dict:
     """The sidecar for one decode plan; raises ValueError on shapes the kernels do not cover."""
     model = {key: config[key] for key in MODEL_KEYS if key in config}
@@ -56,15 +60,13 @@ def plan_document(config: dict, *, batch_lo: int = 1, batch_hi: int | None = Non
         document["tp"] = tp   # the plan is ONE rank's: every rank loads the same library
     if attn_min_slots is not None:
         document["attn_min_slots"] = attn_min_slots   # least ring slots of keys per attention task
-    if static_quarters is not None:
-        document["static_quarters"] = static_quarters
-    if diag:
-        document["diag"] = diag   # diagnostic switches: results are meaningless when set
     return document
 
 
-def emit_plan(config: dict, out_dir: str | Path, **options) -> Path:
-    """Write `<out_dir>/<digest>.so` + `.so.plan.json` and return the library path."""
+def emit_plan(config: dict, out_dir: str | Path | None = None, **options) -> Path:
+    """Write `<out_dir>/<digest>.so` + `.so.plan.json` and return the library path
+    (`out_dir` defaults to PLAN_DIR, inside the package tree)."""
+    out_dir = PLAN_DIR if out_dir is None else out_dir
     document = plan_document(config, **options)
     text = json.dumps(document, indent=1, sort_keys=True) + "\n"
     digest = hashlib.sha256(text.encode()).hexdigest()[:16]
@@ -87,4 +89,14 @@ def emit_plan(config: dict, out_dir: str | Path, **options) -> Path:
     return target
 
 
-__all__ = ["emit_plan", "plan_document", "LIBRARY"]
+def remove_plans(out_dir: str | Path) -> None:
+    """Delete the plan libraries (and sidecars) this module wrote into `out_dir`."""
+    out_dir = Path(out_dir)
+    if out_dir.is_dir():
+        for path in out_dir.glob("tilemega_b200_*.so*"):
+            path.unlink(missing_ok=True)
+        if not any(out_dir.iterdir()):
+            out_dir.rmdir()
+
+
+__all__ = ["emit_plan", "plan_document", "remove_plans", "LIBRARY", "PLAN_DIR"]

@@ -1,9 +1,14 @@
-"""Static-batch serving driver over one decode plan.
+"""Static-batch generation over one decode plan.
 
-Mirrors python/tilemega/serving/engine.py:27-178 of the reference in its prompt
-mode: there is no prefill binary, the prompt positions run teacher-forced
-through the decode plan (engine.py:38-41,144-148) and the whole generation is
-one or two persistent launches.
+Same entry point as the reference's driver (python/tilemega/serving/engine.py:27-178:
+`ServingEngine(checkpoint, config, decode_so, batch, ...)`, `generate(prompt_ids)`
+returning a `Generation`), in its prompt mode: no prefill binary exists, the prompt's
+positions run teacher-forced through the decode plan (engine.py:38-41 of the
+reference) and the sampled tokens never leave the device until the end.
+
+A generation is a list of spans of plan steps (step s decodes position s): one span
+for the prompt, then the decode steps in spans of `decode_chunk` (one span when the
+plan loops on the device, one span per step otherwise). Each span is one launch.
 """
 from __future__ import annotations
 
@@ -13,19 +18,33 @@ from pathlib import Path
 
 import torch
 
-from .plan import PlanLibrary
+from .plan import L1, L2, PlanLibrary
 from .state import allocate_state
 from .weights import Checkpoint, TensorCheckpoint, load_weights
+
+MODES = {"auto": L2, "L1": L1, "L2": L2}
 
 
 @dataclass
 class Generation:
-    tokens: torch.Tensor
-    ttft_ms: float
-    step_ms: list[float]
-    e2e_ms: float
+    tokens: torch.Tensor          # int32 [batch][new tokens], pinned host memory
+    ttft_ms: float                # the prompt span, timed on the device
+    step_ms: list[float]          # [ttft, then one entry per decode step when the plan stamps them]
+    e2e_ms: float                 # host wall clock from the prompt upload to the tokens on the host
     decode_loop_used: bool = False
     step_ns_read: bool = False
+
+
+def decode_spans(first: int, steps: int, chunk: int | None, looped: bool) -> list[tuple[int, int]]:
+    """(first step, count) of every launch that covers decode steps [first, first + steps)."""
+    if steps <= 0:
+        return []
+    if not looped:
+        return [(first + offset, 1) for offset in range(steps)]
+    size = steps if chunk is None else chunk
+    if size < 1:
+        raise ValueError("decode_chunk must be positive")
+    return [(first + offset, min(size, steps - offset)) for offset in range(0, steps, size)]
 
 
 class ServingEngine:
@@ -34,80 +53,67 @@ class ServingEngine:
                  mode: str = "auto", device: int = 0, decode_loop: bool = True,
                  decode_chunk: int | None = None, step_events: bool = True,
                  block_table: torch.Tensor | None = None, weights: dict[str, torch.Tensor] | None = None):
-        if prompt_len < 1 or max_new_tokens < 1:
+        if min(prompt_len, max_new_tokens) < 1:
             raise ValueError("prompt length and output length must be positive")
+        if mode not in MODES:
+            raise ValueError(f"unknown serving mode {mode}")
         if not torch.cuda.is_available():
             raise RuntimeError("ServingEngine needs a CUDA device; there is no CPU path")
         torch.cuda.set_device(device)
-        torch.cuda.init()
         self.decode_lib = PlanLibrary(decode_so)
-        if self.decode_lib.info.seq != 1 or prompt_len + max_new_tokens > self.decode_lib.info.capacity:
+        described = self.decode_lib.info
+        if described.seq != 1 or prompt_len + max_new_tokens > described.capacity:
             raise ValueError("plan metadata does not cover this generation")
-        self.batch = batch
-        self.prompt_len = prompt_len
-        self.max_new_tokens = max_new_tokens
-        self.decode_loop = bool(decode_loop)
-        self.decode_chunk = decode_chunk
-        self.step_events = bool(step_events)
-        if mode not in ("auto", "L1", "L2"):
-            raise ValueError(f"unknown serving mode {mode}")
-        self.decode_mode = 1 if mode == "L1" else 2
-        if not self.decode_lib.info.modes & self.decode_mode:
+        self.decode_mode = MODES[mode]
+        if not described.modes & self.decode_mode:
             raise ValueError("requested mode is not in the plan library")
-        target = torch.device("cuda", device)
-        self.weights = weights if weights is not None else load_weights(checkpoint, self.decode_lib, device=target)
-        self.state = allocate_state(config, batch, self.decode_lib, device=target, block_table=block_table)
-        pointers = {name: tensor.data_ptr() for name, tensor in self.weights.items()}
-        pointers.update(self.state.pointers)
-        self.decode = self.decode_lib.create(batch, pointers, device)
+        self.batch, self.prompt_len, self.max_new_tokens = batch, prompt_len, max_new_tokens
+        self.decode_loop, self.decode_chunk, self.step_events = bool(decode_loop), decode_chunk, bool(step_events)
+        where = torch.device("cuda", device)
+        self.weights = load_weights(checkpoint, self.decode_lib, device=where) if weights is None else weights
+        self.state = allocate_state(config, batch, self.decode_lib, device=where, block_table=block_table)
+        bound = {name: tensor.data_ptr() for name, tensor in self.weights.items()} | self.state.pointers
+        self.decode = self.decode_lib.create(batch, bound, device)
         self.loop_modes = self.decode.loop_modes()
-        # step s runs position s: the prompt's positions, then the decode steps
         self.decode.set_prompt_len(prompt_len)
-        self.decode.set_steps(list(range(0, prompt_len + max_new_tokens - 1)))
+        self.decode.set_steps(list(range(prompt_len + max_new_tokens - 1)))
 
     def generate(self, prompt_ids: torch.Tensor, new_tokens: int | None = None) -> Generation:
-        count = new_tokens or self.max_new_tokens
-        if count < 1 or count > self.max_new_tokens:
+        wanted = self.max_new_tokens if new_tokens is None else new_tokens
+        if not 1 <= wanted <= self.max_new_tokens:
             raise ValueError("token count outside allocated step ring")
         if tuple(prompt_ids.shape) != (self.batch, self.prompt_len):
             raise ValueError("prompt tensor shape disagrees with plan")
-        source = prompt_ids.to(device="cpu", dtype=torch.int32).contiguous()
-        if not source.is_pinned():
-            source = source.pin_memory()
+        looped = self.decode_loop and wanted > 1 and bool(self.loop_modes & self.decode_mode)
+        spans = [(0, self.prompt_len)] + decode_spans(self.prompt_len, wanted - 1, self.decode_chunk, looped)
+        host_prompt = prompt_ids.to(device="cpu", dtype=torch.int32).contiguous()
+        host_prompt = host_prompt if host_prompt.is_pinned() else host_prompt.pin_memory()
+        host_tokens = torch.empty((self.batch, wanted), dtype=torch.int32, pin_memory=True)
         stream = torch.cuda.current_stream()
-        start, first, final = (torch.cuda.Event(enable_timing=True) for _ in range(3))
-        cpu_tokens = torch.empty((self.batch, count), dtype=torch.int32, pin_memory=True)
-        use_loop = bool(self.loop_modes & self.decode_mode) and self.decode_loop and count > 1
-        wall_start = time.perf_counter()
-        self.state.tokens[:, :self.prompt_len].copy_(source, non_blocking=True)
-        start.record(stream)
-        self.decode.launch_steps(0, self.prompt_len, self.decode_mode, stream.cuda_stream)
-        first.record(stream)
-        offset = self.prompt_len
-        if use_loop:
-            chunk = self.decode_chunk or count - 1
-            if chunk < 1:
-                raise ValueError("decode_chunk must be positive")
-            for begin in range(0, count - 1, chunk):
-                self.decode.launch_steps(offset + begin, min(chunk, count - 1 - begin), self.decode_mode,
-                                         stream.cuda_stream)
-        else:
-            for step in range(count - 1):
-                self.decode.launch(offset + step, self.decode_mode, stream.cuda_stream)
-        final.record(stream)
-        cpu_tokens.copy_(self.state.tokens[:, self.prompt_len:self.prompt_len + count], non_blocking=True)
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        began = time.perf_counter()
+        self.state.tokens[:, :self.prompt_len].copy_(host_prompt, non_blocking=True)
+        for number, (first, count) in enumerate(spans):
+            if number == 0:
+                marks[0].record(stream)
+            if count == 1 and not looped and number > 0:
+                self.decode.launch(first, self.decode_mode, stream.cuda_stream)
+            else:
+                self.decode.launch_steps(first, count, self.decode_mode, stream.cuda_stream)
+            if number == 0:
+                marks[1].record(stream)
+        host_tokens.copy_(self.state.tokens[:, self.prompt_len:self.prompt_len + wanted], non_blocking=True)
         stream.synchronize()
-        e2e_ms = (time.perf_counter() - wall_start) * 1e3
-        fired = self.decode.watchdog()
-        if fired is not None:
-            raise RuntimeError(f"a bounded device wait gave up: {fired}")
-        step_ms = [start.elapsed_time(first)]
-        step_ns_read = False
-        if count > 1 and self.step_events:
-            ns = self.decode.read_step_ns(offset, count)
-            step_ms.extend((ns[i] - ns[i - 1]) / 1e6 for i in range(1, count))
-            step_ns_read = True
-        return Generation(cpu_tokens, step_ms[0], step_ms, e2e_ms, use_loop, step_ns_read)
+        e2e_ms = (time.perf_counter() - began) * 1e3
+        gave_up = self.decode.watchdog()
+        if gave_up is not None:
+            raise RuntimeError(f"a bounded device wait gave up: {gave_up}")
+        step_ms = [marks[0].elapsed_time(marks[1])]
+        stamped = self.step_events and wanted > 1
+        if stamped:
+            stamps = self.decode.read_step_ns(self.prompt_len, wanted)
+            step_ms += [(later - earlier) / 1e6 for earlier, later in zip(stamps, stamps[1:])]
+        return Generation(host_tokens, step_ms[0], step_ms, e2e_ms, looped, stamped)
 
     def close(self) -> None:
         self.decode.close()

@@ -8,6 +8,7 @@ and `serving.context_base` i32 [B] (per-sequence position offset).
 """
 from __future__ import annotations
 
+import math
 from dataclasses import dataclass, field
 
 import torch
@@ -35,19 +36,43 @@ def head_dim_of(config: dict) -> int:
     return int(config.get("head_dim") or config["hidden_size"] // config["num_attention_heads"])
 
 
-def rotary_tables(config: dict, capacity: int, device: torch.device | str) -> tuple[torch.Tensor, torch.Tensor]:
-    """bf16 cos/sin [capacity][D], the half duplicated (rotate-half convention).
+def inverse_frequencies(config: dict) -> torch.Tensor:
+    """inv_freq [D/2] in fp32: theta^(-2i/D), then the checkpoint's `rope_scaling`.
 
-    The reference takes these from the HF rotary modules (state.py:30-59); for
-    the default RoPE that is inv_freq = theta^(-2i/D), angles in fp32, cast to
-    the model dtype. Scaled RoPE variants are not built.
-    """
-    scaling = config.get("rope_scaling")
-    if scaling and scaling.get("rope_type", scaling.get("type", "default")) != "default":
-        raise ValueError("only the default RoPE is built")
+    The reference takes its tables from the HF rotary module (python/tilemega/serving/state.py:30-59),
+    which applies the scaling the config names. Built here: "default", "linear" (every frequency
+    divided by `factor`) and "llama3" (Llama 3.1/3.2 checkpoints: wavelengths longer than
+    original_max_position_embeddings / low_freq_factor are slowed by `factor`, wavelengths shorter than
+    original / high_freq_factor are kept, the band between is interpolated). All three leave the
+    attention scale at 1. Anything else is refused."""
     dim = head_dim_of(config)
     theta = float(config.get("rope_theta", 10000.0))
     inv_freq = 1.0 / (theta ** (torch.arange(0, dim, 2, dtype=torch.int64).float() / dim))
+    scaling = config.get("rope_scaling") or {}
+    kind = scaling.get("rope_type", scaling.get("type", "default"))
+    if kind == "default":
+        return inv_freq
+    if kind not in ("linear", "llama3"):
+        raise ValueError(f"rope_scaling of type {kind!r} is not built (default, linear, llama3 are)")
+    factor = float(scaling["factor"])
+    if kind == "linear":
+        return inv_freq / factor
+    if kind == "llama3":
+        low, high = float(scaling["low_freq_factor"]), float(scaling["high_freq_factor"])
+        original = float(scaling["original_max_position_embeddings"])
+        wavelength = 2.0 * math.pi / inv_freq
+        slowed = torch.where(wavelength > original / low, inv_freq / factor, inv_freq)
+        blend = (original / wavelength - low) / (high - low)
+        between = (1.0 - blend) * slowed / factor + blend * slowed
+        in_band = (wavelength >= original / high) & (wavelength <= original / low)
+        return torch.where(in_band, between, slowed)
+    raise AssertionError(kind)
+
+
+def rotary_tables(config: dict, capacity: int, device: torch.device | str) -> tuple[torch.Tensor, torch.Tensor]:
+    """bf16 cos/sin [capacity][D], the half duplicated (rotate-half convention): angles
+    position * inv_freq in fp32, cosine and sine in fp32, cast to the model dtype."""
+    inv_freq = inverse_frequencies(config)
     angles = torch.arange(capacity, dtype=torch.float32)[:, None] * inv_freq[None, :]
     table = torch.cat((angles, angles), dim=-1)
     return (table.cos().to(torch.bfloat16).to(device).contiguous(),

@@ -18,34 +18,41 @@ from .plan import Buffer, PlanLibrary
 DTYPES = {0: torch.bfloat16, 1: torch.float32, 2: torch.int32}
 
 
+def _tied_name(name: str, known, tied: bool) -> str:
+    """A tied model has no lm_head tensor of its own: the embedding table stands in."""
+    return "model.embed_tokens.weight" if tied and name == "lm_head.weight" and name not in known else name
+
+
 class Checkpoint:
-    """A directory of *.safetensors files keyed by tensor name (weights.py:17-49)."""
+    """The *.safetensors files of a model directory, addressed by HF tensor name. Tensors are
+    read one at a time when a recipe asks for them (the reference's loader works the same
+    way, python/tilemega/serving/weights.py:17-49), so the host never holds the whole model."""
 
     def __init__(self, model_dir: str | Path):
         from safetensors import safe_open
-        self._open = safe_open
+        self._reader = lambda path: safe_open(path, framework="pt", device="cpu")
         self.model_dir = Path(model_dir)
+        self.tie_word_embeddings = False
         config = self.model_dir / "config.json"
-        self.tie_word_embeddings = bool(json.loads(config.read_text()).get(
-            "tie_word_embeddings", False)) if config.exists() else False
+        if config.exists():
+            self.tie_word_embeddings = bool(json.loads(config.read_text()).get("tie_word_embeddings", False))
         self.files: dict[str, Path] = {}
-        for path in sorted(self.model_dir.glob("*.safetensors")):
-            with safe_open(path, framework="pt", device="cpu") as stream:
-                for name in stream.keys():
-                    if name in self.files:
-                        raise ValueError(f"duplicate checkpoint tensor {name}")
-                    self.files[name] = path
+        for shard in sorted(self.model_dir.glob("*.safetensors")):
+            with self._reader(shard) as handle:
+                names = list(handle.keys())
+            clash = [name for name in names if name in self.files]
+            if clash:
+                raise ValueError(f"duplicate checkpoint tensor {clash[0]}")
+            self.files.update((name, shard) for name in names)
         if not self.files:
             raise FileNotFoundError(f"no safetensors in {self.model_dir}")
 
     def tensor(self, name: str) -> torch.Tensor:
-        if name == "lm_head.weight" and name not in self.files and self.tie_word_embeddings:
-            name = "model.embed_tokens.weight"
-        path = self.files.get(name)
-        if path is None:
+        name = _tied_name(name, self.files, self.tie_word_embeddings)
+        if name not in self.files:
             raise KeyError(f"checkpoint has no {name}")
-        with self._open(path, framework="pt", device="cpu") as stream:
-            return stream.get_tensor(name)
+        with self._reader(self.files[name]) as handle:
+            return handle.get_tensor(name)
 
 
 class TensorCheckpoint:
@@ -56,8 +63,7 @@ class TensorCheckpoint:
         self.tie_word_embeddings = tie_word_embeddings
 
     def tensor(self, name: str) -> torch.Tensor:
-        if name == "lm_head.weight" and name not in self.tensors and self.tie_word_embeddings:
-            name = "model.embed_tokens.weight"
+        name = _tied_name(name, self.tensors, self.tie_word_embeddings)
         if name not in self.tensors:
             raise KeyError(f"checkpoint has no {name}")
         return self.tensors[name]
@@ -73,6 +79,40 @@ def tile_pages(weight: torch.Tensor, tile_n: int, tile_k: int) -> torch.Tensor:
     """
     if weight.ndim != 2 or tile_n <= 0 or tile_k <= 0 or tile_n % 8 or tile_k % 64:
         raise ValueError("invalid tile_pages source or geometry")
+    if weight.is_cuda and weight.dtype == torch.bfloat16 and weight.shape[1] % 8 == 0:
+        return tile_pages_on_device(weight, tile_n, tile_k)
+    return tile_pages_by_indexing(weight, tile_n, tile_k)
+
+
+_PACKER = None
+
+
+def tile_pages_on_device(weight: torch.Tensor, tile_n: int, tile_k: int) -> torch.Tensor:
+    """The same layout written by the library's pack kernel (tm_pack_tile_pages): one pass over
+    the matrix on the device instead of a chain of indexing ops."""
+    global _PACKER
+    if _PACKER is None:
+        import ctypes as C
+        from ..build import build_library
+        _PACKER = C.CDLL(str(build_library())).tm_pack_tile_pages
+        _PACKER.restype = C.c_int
+        _PACKER.argtypes = [C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p]
+    if weight.stride(1) != 1 or weight.stride(0) % 8 or weight.data_ptr() % 16:
+        weight = weight.contiguous()
+    n, k = weight.shape
+    pages = -(-n // tile_n) * -(-k // tile_k)
+    packed = torch.empty(pages * tile_n * tile_k, dtype=torch.bfloat16, device=weight.device)
+    with torch.cuda.device(weight.device):
+        status = _PACKER(weight.data_ptr(), n, k, weight.stride(0), tile_n, tile_k, packed.data_ptr(),
+                         torch.cuda.current_stream().cuda_stream)
+    if status != 0:
+        raise RuntimeError(f"tm_pack_tile_pages failed ({status})")
+    return packed
+
+
+def tile_pages_by_indexing(weight: torch.Tensor, tile_n: int, tile_k: int) -> torch.Tensor:
+    """The layout of tile_pages as tensor indexing (any device and dtype): the definition the
+    pack kernel is tested against."""
     n, k = weight.shape
     nt, kt = -(-n // tile_n), -(-k // tile_k)
     if (nt * tile_n, kt * tile_k) != (n, k):
@@ -175,16 +215,14 @@ def pack(recipe: Mapping[str, object], source: Callable[[str], torch.Tensor], tp
 
 
 def weight_recipes(*plans: PlanLibrary) -> dict[str, Buffer]:
-    result: dict[str, Buffer] = {}
-    for plan in plans:
-        for buffer in plan.buffers:
-            if not buffer.pack_json:
-                continue
-            prior = result.setdefault(buffer.name, buffer)
-            if (prior.pack_json, prior.dtype, prior.elements_constant) != (
-                    buffer.pack_json, buffer.dtype, buffer.elements_constant):
-                raise ValueError(f"plans disagree on weight {buffer.name}")
-    return result
+    """Every buffer of the plans that carries a packing recipe, by name; plans that share a
+    weight must describe it identically."""
+    chosen: dict[str, Buffer] = {}
+    for buffer in (buffer for plan in plans for buffer in plan.buffers if buffer.pack_json):
+        seen = chosen.setdefault(buffer.name, buffer)
+        if (seen.pack_json, seen.dtype, seen.elements_constant) != (buffer.pack_json, buffer.dtype, buffer.elements_constant):
+            raise ValueError(f"plans disagree on weight {buffer.name}")
+    return chosen
 
 
 def load_weights(checkpoint: str | Path | Checkpoint | TensorCheckpoint, *plans: PlanLibrary,

@@ -14,14 +14,12 @@ staging / task time. The reference's counterpart is its TILEMEGA_TRACE_STAGE bui
 from __future__ import annotations
 
 import argparse
-import json
-import tempfile
-from pathlib import Path
+import os
 
 import torch
 
 from . import synthetic
-from .planbuild import emit_plan
+from .planbuild import PLAN_DIR, emit_plan, remove_plans
 from .serving.plan import PlanLibrary
 from .serving.state import allocate_state, shuffled_block_table
 from .serving.weights import load_weights
@@ -30,9 +28,9 @@ MODELS = {"llama-3.1-8b": synthetic.LLAMA_3_1_8B, "llama-3.2-1b": synthetic.LLAM
           "qwen3-30b-a3b": synthetic.QWEN3_30B_A3B}
 
 
-def measured_gbs() -> float:
-    path = Path(__file__).resolve().parents[1] / "MEASURED_PEAKS.json"
-    return float(json.loads(path.read_text())["hbm_gbs"]) if path.exists() else 6650.0
+# Copy bandwidth of a B200 as a plain device-to-device copy measures it (GB/s): the default
+# denominator of the "ideal" column; pass the figure of the box at hand with --peak-gbs.
+DEFAULT_PEAK_GBS = 6552.6
 
 
 def stage_bytes(config: dict, context: int, batch: int) -> dict[str, float]:
@@ -57,6 +55,8 @@ def main() -> None:
     parser.add_argument("--context", type=int, default=2646)
     parser.add_argument("--batch", type=int, default=1)
     parser.add_argument("--attn-min-slots", type=int, default=None)
+    parser.add_argument("--peak-gbs", type=float, default=DEFAULT_PEAK_GBS,
+                        help="measured HBM copy bandwidth the ideal stage times are computed from")
     args = parser.parse_args()
     if not torch.cuda.is_available():
         raise SystemExit("stage_trace needs a CUDA device")
@@ -68,7 +68,8 @@ def main() -> None:
     capacity = (context + steps + 40) // 16 * 16
     device = torch.device("cuda", 0)
     num_blocks = batch * capacity // 16 + 8
-    with tempfile.TemporaryDirectory() as folder:
+    folder = PLAN_DIR / f"trace-{os.getpid()}"
+    try:
         so = emit_plan(config, folder, batch_lo=batch, batch_hi=batch, capacity=capacity, kv_layout="paged",
                        num_blocks=num_blocks, write_logits=False, attn_min_slots=args.attn_min_slots)
         lib = PlanLibrary(so)
@@ -104,10 +105,13 @@ def main() -> None:
         per_layer = (stamps.size // 4 // grid - 1) // layers
         trace = stamps.reshape(grid, per_layer * layers + 1, 4)
         plan.close()
-    print_table(config, trace, per_layer, context, batch)
+    finally:
+        remove_plans(folder)
+    print_table(config, trace, per_layer, context, batch, peak=args.peak_gbs)
 
 
-def print_table(config: dict, trace, per_layer: int, context: int, batch: int, tp: int = 1) -> None:
+def print_table(config: dict, trace, per_layer: int, context: int, batch: int, tp: int = 1,
+                peak: float = DEFAULT_PEAK_GBS) -> None:
     """`trace`: int64 [grid][per_layer * layers + 1][4] stage stamps of one step (one rank's)."""
     import numpy as np
     layers = config["num_hidden_layers"]
@@ -118,7 +122,7 @@ def print_table(config: dict, trace, per_layer: int, context: int, batch: int, t
     start = trace[:, 0, 1].min()
     done, first_done = trace[:, :, 3].max(axis=0), trace[:, :, 3].min(axis=0)
     wall = np.diff(np.concatenate(([start], done)))
-    sizes, peak = stage_bytes(config, context + 18, batch), measured_gbs()
+    sizes = stage_bytes(config, context + 18, batch)
     sizes = {name: value / tp for name, value in sizes.items()}
     print(f"{'stage':12s} {'wall':>7s} {'ideal':>7s} {'wait':>6s} {'rows':>6s} {'tasks':>6s} {'max':>6s} {'spread':>6s}   (us; "
           f"ideal = bytes / {peak:.0f} GB/s; medians over CTAs, means over layers 1..{layers - 1})")
