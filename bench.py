@@ -1,32 +1,36 @@
-"""Decode benchmark: tokens/s and step latency of the persistent decode kernel on a
-Llama-3.1-8B-shaped model (bf16, batch 1, paged KV with a shuffled block table),
-with the HBM roofline of the kernel and the CPU forward timed beside it.
+"""Decode benchmark: tokens/s and step latency of the persistent decode kernel, with the
+HBM roofline of the kernel and the reference's CPU forward timed beside it.
 
     python bench.py --gpus 1 --steps K --warmup W          # this repository's CUDA path
     python bench.py --impl reference --steps K --warmup W  # the reference's CPU forward
+    python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N --steps K --warmup W
 
-One "step" is one decode step of every sequence in the batch. The timed region is
-ONE persistent launch that runs K steps; inputs (weights, KV pool, block table,
-token state) are resident in HBM when it starts. `e2e` drives the same plan one
-step per call through the C ABI with the token id coming from pinned host memory
-and the new token read back to the host every step.
+One GPU: a Llama-3.1-8B-shaped model (bf16, batch 1, paged KV with a shuffled block table,
+a seeded context length in [512, 8192]). N > 1 GPUs: ONE Llama-3.1-70B-shaped model at context
+4096 sharded over the N ranks (tensor parallelism: column/row-sharded weights, the all-reduce
+after o and down fused into the kernel's epilogues over peer memory, argmax winners exchanged
+the same way); the job value is that one model's tokens/s ("strong" scaling), the roofline is
+each GPU's share of the bytes, and every rank's tokens are compared. `--replicas` runs N
+independent copies of the one-GPU workload instead.
 
-Synthetic data: seeded N(0, 0.02) weights, KV rows N(0, 0.5), a seeded context
-length in [512, 8192]. Rank r > 0 of a multi-GPU run is an independent replica of
-the headline workload (the 8B-shaped model at batch 1 is not tensor parallel in the
-benchmark list); the job value is the sum over replicas.
+One "step" is one decode step of every sequence in the batch. The timed region is ONE persistent
+launch that runs K steps; inputs (weights, KV pool, block table, token state) are resident in
+HBM when it starts. `e2e` drives the same plan one step per call through the C ABI with the
+token id coming from pinned host memory and the new token read back to the host every step.
 
-    python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N --tp --model llama-3.1-70b
+The reference arm and the `cpu_baseline` leg time the reference's own PyTorch module
+(`Decoder.execute`, from oracle/_ref/ when oracle/build_ref.py has filled it; otherwise the
+restatement in oracle/decoder_oracle.py) in fp32 on all host cores, on slices of 4 and 8 layers
+of the workload's shapes at its context length, and extrapolate linearly to the full depth: the
+line says so ("extrapolated", the depths, the steps really timed).
 
-shards ONE model over the N ranks instead (tensor parallelism: column/row-sharded
-weights, the all-reduce after o and down fused into the kernel's epilogues over
-peer memory); the job value is then the one model's tokens/s ("strong" scaling) and
-the roofline is each GPU's share of the bytes.
+Synthetic data: seeded N(0, 0.02) weights, KV rows N(0, 0.5).
 """
 from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import statistics
 import sys
@@ -44,12 +48,15 @@ from tilemega_b200 import synthetic  # noqa: E402
 METRIC = "decode_tokens_per_s"
 UNIT = "tok/s"
 NOMINAL_HBM_GBS = 8000.0
-# dram__bytes_read.sum + dram__bytes_write.sum per algorithmic byte of a launch, from the ncu
-# capture of the same kernel on a 2-layer case of the same shapes (15.473 GB of DRAM traffic
-# for 15.559 GB of algorithmic bytes; profiles/decode_megakernel_llama31_8b_b1.md). Traffic
-# is proportional to the streamed weights, so the full launch's traffic is this ratio times
-# its algorithmic bytes.
-NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 0.9945
+# dram__bytes_read.sum + dram__bytes_write.sum per algorithmic byte of a launch, from ncu captures
+# of the same kernel on 2-layer cases of the same shapes (traffic is proportional to the streamed
+# weights, so a full launch's traffic is this ratio times its algorithmic bytes). Keyed by
+# (model, batch): a workload without a capture reports no traffic.
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = {("llama-3.1-8b", 1): 0.9945}
+# roofline.frac of the one-GPU headline run (profiles/decode_megakernel_llama31_8b_b1.md): the
+# denominator of config.mbu_retained_vs_1gpu in a tensor-parallel line
+SINGLE_GPU_FRAC = 0.775
+TP_MODEL, TP_CONTEXT = "llama-3.1-70b", 4096
 
 
 def measured_peak_gbs() -> tuple[float, str]:
@@ -64,12 +71,21 @@ MODELS = {"llama-3.1-8b": synthetic.LLAMA_3_1_8B, "llama-3.2-1b": synthetic.LLAM
 
 
 def workload(args) -> dict:
-    config = dict(MODELS[args.model])
+    """What this invocation measures: one GPU (or --replicas) -> the 8B-shaped headline; several
+    GPUs -> one 70B-shaped model sharded over them. --model / --context / --batch / --layers override."""
+    tp = args.gpus if args.gpus > 1 and not args.replicas else 1
+    model = args.model or (TP_MODEL if tp > 1 else "llama-3.1-8b")
+    context = args.context if args.context is not None else (TP_CONTEXT if tp > 1 else 0)
+    config = dict(MODELS[model])
     if args.layers:
         config["num_hidden_layers"] = args.layers
     batch = args.batch
-    contexts = synthetic.seeded_contexts(batch, 512, 8192, seed=2).tolist() if args.context == 0 else [args.context] * batch
-    return {"name": f"{args.model}-shaped", "config": config, "batch": batch, "contexts": contexts}
+    contexts = synthetic.seeded_contexts(batch, 512, 8192, seed=2).tolist() if context == 0 else [context] * batch
+    label = f"{model}-shaped decode, batch {batch}, context {contexts}, paged KV block 16, shuffled block table"
+    if tp > 1:
+        label += f", tensor parallel over {tp} GPUs"
+    return {"name": f"{model}-shaped", "model": model, "config": config, "batch": batch, "contexts": contexts, "tp": tp,
+            "label": label}
 
 
 class ClockSampler:
@@ -124,38 +140,90 @@ class ClockSampler:
                 "reasons": names, "samples": len(self.samples)}
 
 
-def cpu_forward_seconds_per_step(work: dict, steps: int, threads: int) -> tuple[float, str]:
-    """The reference's CPU forward (the oracle port) on a bounded sample of the
-    workload: 1-layer and 2-layer slices of the same shapes at the same context,
-    fp32, timed per decode step; the full depth is layer_time * L + head_time."""
-    from oracle.decoder_oracle import OracleDecoder, PagedKV
+def cpu_forward(work: dict, steps: int, threads: int, repeats: int = 3) -> dict:
+    """Seconds per decode step of the reference's CPU forward, fp32, `threads` host threads.
+
+    With oracle/_ref/ present this drives the reference's own module (`Decoder.execute`,
+    python/tilemega/serving/export.py:165-172: token ids, the per-layer caches, the RoPE tables in,
+    logits and the grown caches out) -- kind "reference"; otherwise the restatement in
+    oracle/decoder_oracle.py -- kind "port". The full model does not fit a bounded sample (the
+    8B-shaped weights are 32 GB in fp32), so slices of 4 and 8 layers of the same shapes are timed
+    at the workload's context, `steps` decode steps each, `repeats` times (the median counts), and
+    the full depth is head + layers * per-layer time."""
+    sys.path.insert(0, str(ROOT / "oracle"))
+    from build_ref import load_decoder
     torch.set_num_threads(threads)
     config, batch, contexts = work["config"], work["batch"], work["contexts"]
     layers = config["num_hidden_layers"]
-    capacity = (max(contexts) + steps + 17) // 16 * 16
-    two = dict(config, num_hidden_layers=min(2, layers))
-    weights = synthetic.seeded_weights(two, seed=0, dtype=torch.float32)
-    times = {}
-    for depth in sorted({1, min(2, layers)}):
+    # the deeper slice is the deepest (at most 8 layers) whose fp32 weights stay under 16 GB of host memory
+    shapes = dict(synthetic.parameter_shapes(dict(config, num_hidden_layers=1)))
+    count = lambda names: sum(math.prod(shapes[name]) for name in names)
+    per_layer_bytes = 4 * count(name for name in shapes if name.startswith("model.layers.0."))
+    fixed_bytes = 4 * count(name for name in shapes if not name.startswith("model.layers."))
+    deepest = max(1, min(8, layers, int((16e9 - fixed_bytes) // per_layer_bytes)))
+    depths = sorted({max(1, deepest // 2), deepest})
+    Decoder = None if synthetic.is_moe(config) else load_decoder()
+    dim = synthetic.head_dim_of(config)
+    hkv = config["num_key_value_heads"]
+    context = max(contexts)
+    timed = {}
+    for depth in depths:
         sliced = dict(config, num_hidden_layers=depth)
-        decoder = OracleDecoder(sliced, weights, torch.float32, capacity)
-        kv = PagedKV(sliced, batch, capacity, torch.float32)
-        kv.pool.normal_(0.0, 0.5, generator=torch.Generator().manual_seed(3))
-        ids = synthetic.seeded_tokens(batch, steps + 1, config["vocab_size"], seed=4)
-        decoder.forward(ids[:, :1], list(contexts), kv)  # warm-up
-        begin = time.perf_counter()
-        for step in range(steps):
-            decoder.forward(ids[:, step + 1:step + 2], [c + step + 1 for c in contexts], kv)
-        times[depth] = (time.perf_counter() - begin) / steps
-    if layers >= 2:
-        layer_time = max(times[2] - times[1], 1e-9)
-        head_time = max(times[1] - layer_time, 0.0)
+        ids = synthetic.seeded_tokens(batch, steps + 2, config["vocab_size"], seed=4).long()
+        if Decoder is not None:
+            with torch.device("meta"):
+                model = Decoder(sliced)
+            model = model.to_empty(device="cpu").float().eval()
+            generator = torch.Generator().manual_seed(0)
+            with torch.no_grad():
+                for name, parameter in model.named_parameters():
+                    if parameter.ndim == 1:
+                        parameter.fill_(1.0)
+                    else:
+                        parameter.normal_(0.0, 0.02, generator=generator)
+            from tilemega_b200.serving.state import rotary_tables
+            cos, sin = (table.float() for table in rotary_tables(sliced, context + steps + 2, "cpu"))
+            kv = torch.Generator().manual_seed(3)
+            first = tuple(torch.randn(batch, hkv, context, dim, generator=kv) * 0.5 for _ in range(2 * depth))
+
+            def run_steps(count: int) -> None:
+                caches = first
+                with torch.inference_mode():
+                    for step in range(count):
+                        out = model.execute(ids[:, step:step + 1], caches, cos, sin)   # the module picks row `past`
+                        caches = out[1:]
+        else:
+            from oracle.decoder_oracle import OracleDecoder, PagedKV
+            weights = synthetic.seeded_weights(sliced, seed=0, dtype=torch.float32)
+            capacity = (context + steps + 17) // 16 * 16
+            decoder = OracleDecoder(sliced, weights, torch.float32, capacity)
+            kv = PagedKV(sliced, batch, capacity, torch.float32)
+            kv.pool.normal_(0.0, 0.5, generator=torch.Generator().manual_seed(3))
+
+            def run_steps(count: int) -> None:
+                for step in range(count):
+                    decoder.forward(ids[:, step:step + 1].int(), [c + step for c in contexts], kv)
+        run_steps(1)   # warm-up
+        samples = []
+        for _ in range(repeats):
+            begin = time.perf_counter()
+            run_steps(steps)
+            samples.append((time.perf_counter() - begin) / steps)
+        timed[depth] = statistics.median(samples)
+        del run_steps
+    if len(depths) == 2:
+        per_layer = max((timed[depths[1]] - timed[depths[0]]) / (depths[1] - depths[0]), 1e-9)
+        head = max(timed[depths[0]] - per_layer * depths[0], 0.0)
     else:
-        layer_time, head_time = times[1], 0.0
-    seconds = layer_time * layers + head_time
-    sample = (f"fp32 oracle port, 1- and 2-layer slices + lm_head of the same shapes at context {contexts}, "
-              f"{steps} decode steps each, extrapolated linearly to {layers} layers")
-    return seconds, sample
+        per_layer, head = timed[depths[0]] / depths[0], 0.0
+    kind = "reference" if Decoder is not None else "port"
+    what = ("the reference's Decoder.execute (oracle/_ref)" if Decoder is not None
+            else "the restatement of the reference's forward (oracle/decoder_oracle.py)")
+    return {"seconds": head + per_layer * layers, "kind": kind, "depths": depths, "steps_timed": steps, "repeats": repeats,
+            "extrapolated": layers not in depths,
+            "sample": (f"{what}, fp32, {threads} threads: slices of {depths} layers + lm_head of the same shapes at "
+                       f"context {context}, {steps} decode steps each, median of {repeats}" +
+                       (f", extrapolated linearly to {layers} layers" if layers not in depths else ""))}
 
 
 def max_over_ranks(values: list[float], device=None) -> list[float]:
@@ -180,16 +248,18 @@ def run_reference(args) -> None:
         return
     work = workload(args)
     threads = os.cpu_count() or 1
-    steps = max(1, min(args.steps, 4))
-    seconds, sample = cpu_forward_seconds_per_step(work, steps, threads)
-    value = work["batch"] / seconds
+    steps = max(8, min(args.steps, 16))   # a bounded sample: the line reports what was really timed
+    result = cpu_forward(work, steps, threads)
+    value = work["batch"] / result["seconds"]
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": seconds * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"{work['name']} decode, batch {work['batch']}, context {work['contexts']}, "
-                               "reference PyTorch CPU forward (restated in oracle/)"},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "steps": result["steps_timed"], "steps_requested": args.steps, "warmup": 1,
+        "ms_per_step": result["seconds"] * 1e3, "higher_is_better": True,
+        "scaling": "strong" if work["tp"] > 1 else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "extrapolated": result["extrapolated"], "slice_layers": result["depths"],
+        "config": {"workload": work["label"], "layers": work["config"]["num_hidden_layers"],
+                   "parallelism": "host cores", "arm": "reference PyTorch CPU forward"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": result["kind"], "sample": result["sample"]},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
@@ -198,7 +268,7 @@ def run_reference(args) -> None:
 def run_ours(args) -> None:
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the product path has no CPU implementation")
-    from tilemega_b200.planbuild import emit_plan
+    from tilemega_b200.planbuild import PLAN_DIR, emit_plan, remove_plans
     from tilemega_b200.serving.plan import PlanLibrary
     from tilemega_b200.serving.state import allocate_state, shuffled_block_table
     from tilemega_b200.serving.weights import TensorCheckpoint, load_weights
@@ -210,30 +280,26 @@ def run_ours(args) -> None:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
+    dist = None
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=device)
-    tp = world if args.tp else 1
-    if args.tp and world < 2:
-        raise SystemExit("--tp shards one model over the ranks: launch at least two")
 
     work = workload(args)
-    config, batch, contexts = work["config"], work["batch"], work["contexts"]
+    config, batch, contexts, tp = work["config"], work["batch"], work["contexts"], work["tp"]
     steps, warmup = args.steps, max(args.warmup, 3)
     total_steps = warmup + 2 * steps + 1 + 4   # device-timed launch, the end-to-end loop, and the optional traced steps
     capacity = (max(contexts) + total_steps + 17) // 16 * 16
     max_blocks = capacity // 16
     num_blocks = batch * max_blocks + 32
-    plan_dir = Path(os.environ.get("TILEMEGA_PLAN_DIR", "/tmp/tilemega_b200_plans"))
-    geometry = json.loads(args.geometry) if args.geometry else None
+    plan_dir = PLAN_DIR / "bench"    # inside the package tree: every library this process loads is the repository's
     options = dict(batch_lo=batch, batch_hi=batch, capacity=capacity, kv_layout="paged", num_blocks=num_blocks,
-                   write_logits=False, geometry=geometry, slots=args.slots, tp=tp)
-    if rank == 0 or world == 1:
+                   write_logits=False, tp=tp)
+    if rank == 0:
         so = emit_plan(config, plan_dir, **options)
     if world > 1:
-        import torch.distributed as dist
         dist.barrier()
-        so = emit_plan(config, plan_dir, **options)
+        so = emit_plan(config, plan_dir, **options)   # an identical plan is left alone: this only returns its path
     lib = PlanLibrary(so)
     replica = 0 if tp > 1 else rank     # tensor-parallel ranks cut their slices out of ONE model and share one request
     if tp > 1 or synthetic.is_moe(config):
@@ -253,8 +319,7 @@ def run_ours(args) -> None:
     first = synthetic.seeded_tokens(batch, 1, config["vocab_size"], seed=11 + replica)
     for b in range(batch):
         state.tokens[b, contexts[b]] = int(first[b, 0])
-    pointers = {name: tensor.data_ptr() for name, tensor in weights.items()}
-    pointers.update(state.pointers)
+    pointers = {name: tensor.data_ptr() for name, tensor in weights.items()} | state.pointers
     plan = lib.create(batch, pointers, local)
     if tp > 1:
         # each rank's receive regions, published to its peers as CUDA IPC handles
@@ -270,9 +335,21 @@ def run_ours(args) -> None:
 
     def barrier():
         if world > 1:
-            import torch.distributed as dist
             dist.barrier()
         torch.cuda.synchronize()
+
+    def tokens_agree(first_position: int, count: int, what: str) -> None:
+        """Tensor parallel: every rank must have written the same tokens (the ranks' residual
+        streams are bitwise equal by construction; a difference means a broken exchange)."""
+        if tp <= 1:
+            return
+        mine = torch.stack([state.tokens[b, contexts[b] + first_position:contexts[b] + first_position + count]
+                            for b in range(batch)]).contiguous()
+        everyone = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(everyone, mine)
+        for q in range(world):
+            if not torch.equal(everyone[q], everyone[0]):
+                raise SystemExit(f"{what}: rank {q} generated tokens that differ from rank 0's")
 
     bytes_timed = sum(plan.step_bytes(sum(c + warmup + i + 1 for c in contexts)) for i in range(steps))
     sampler = ClockSampler(local)
@@ -288,6 +365,7 @@ def run_ours(args) -> None:
         fired = plan.watchdog()
         if fired is not None:
             raise SystemExit(f"a bounded device wait gave up during the timed launch: {fired}")
+        tokens_agree(1, warmup + steps, "timed launch")
         stamps = plan.read_step_ns(warmup, steps + 1)
         # end to end: one step per ABI call, token id from pinned host memory, new token back to the host
         host_in = torch.empty(batch, dtype=torch.int32).pin_memory()
@@ -311,6 +389,8 @@ def run_ours(args) -> None:
     fired = plan.watchdog()
     if fired is not None:
         raise SystemExit(f"a bounded device wait gave up during the end-to-end loop: {fired}")
+    tokens_agree(warmup + steps + 1, steps, "end-to-end loop")
+    peak, peak_kind = measured_peak_gbs()
     if args.trace:
         # per-stage stamps of one more step (every rank of a tensor-parallel job runs it; rank 0 reports)
         import numpy as np
@@ -318,34 +398,34 @@ def run_ours(args) -> None:
         plan.trace_step(warmup + 2 * steps + 2)
         plan.launch_steps(warmup + 2 * steps, 4, mode, stream.cuda_stream)
         barrier()
-        stamps = np.array(plan.read_trace(), dtype=np.int64)
+        trace = np.array(plan.read_trace(), dtype=np.int64)
         grid = torch.cuda.get_device_properties(local).multi_processor_count
-        per_layer = (stamps.size // 4 // grid - 1) // config["num_hidden_layers"]
+        per_layer = (trace.size // 4 // grid - 1) // config["num_hidden_layers"]
         if rank == 0:
-            print_table(config, stamps.reshape(grid, -1, 4), per_layer, max(contexts) + warmup + 2 * steps, batch, tp=tp)
+            print_table(config, trace.reshape(grid, -1, 4), per_layer, max(contexts) + warmup + 2 * steps, batch, tp=tp,
+                        peak=peak)
     device_ms, e2e_seconds = max_over_ranks([device_ms, e2e_seconds], device)
     seconds = device_ms / 1e3
     replicas = 1 if tp > 1 else world
     value = job_value(replicas, batch, steps, seconds)
     achieved = bytes_timed / seconds / 1e9
-    peak, peak_kind = measured_peak_gbs()
     step_us = [(stamps[i + 1] - stamps[i]) / 1e3 for i in range(steps)]
+    ratio = NCU_TRAFFIC_PER_ALGORITHMIC_BYTE.get((work["model"], batch)) if tp == 1 else None
+    parallelism = f"tp{tp}" if tp > 1 else ("replicas" if world > 1 else "single")
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
         "ms_per_step": device_ms / steps, "higher_is_better": True, "scaling": "strong" if tp > 1 else "weak",
-        "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"{work['name']} decode, batch {batch}, context {contexts}, paged KV block 16, "
-                               "shuffled block table", "layers": config["num_hidden_layers"],
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": work["label"], "layers": config["num_hidden_layers"],
                    "l2": "inputs larger than L2: every step streams its weights and KV rows from HBM",
-                   "parallelism": f"tp{tp}" if tp > 1 else ("replicas" if world > 1 else "single"),
-                   "step_latency_us_median": statistics.median(step_us),
+                   "parallelism": parallelism, "step_latency_us_median": statistics.median(step_us),
                    "mbu_vs_nominal_8tbs": achieved / NOMINAL_HBM_GBS},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": None if tp > 1 else NCU_TRAFFIC_PER_ALGORITHMIC_BYTE * bytes_timed,
-                     "traffic_source": ("not captured for the tensor-parallel run (ncu never wraps a multi-rank command)"
-                                        if tp > 1 else
-                                        "ncu on a 2-layer case of the same kernel, scaled by algorithmic bytes"),
+                     "traffic": ratio * bytes_timed if ratio else None,
+                     "traffic_source": ("ncu capture of the same kernel on a 2-layer case of this model and batch, scaled by "
+                                        "algorithmic bytes" if ratio else
+                                        "none: no ncu capture exists for this model/batch" +
+                                        (" (ncu never wraps a multi-rank command)" if tp > 1 else "")),
                      "per": "GPU (this rank's share of the weights and KV rows)" if tp > 1 else "GPU",
                      "peak_kind": f"of {peak_kind}", "bytes_per_launch": bytes_timed},
         "e2e": {"value": job_value(replicas, batch, steps, e2e_seconds), "unit": UNIT, "h2d_bytes_per_step": 4 * batch,
@@ -353,16 +433,23 @@ def run_ours(args) -> None:
         "gpu_launches": 1,
         "clocks": sampler.summary(),
     }
+    if tp > 1:
+        # per-GPU roofline fraction kept against the one-GPU 8B-shaped headline: the curve to read for
+        # a tensor-parallel run (tokens/s at N GPUs and at one GPU belong to two different models)
+        line["config"]["mbu_retained_vs_1gpu"] = achieved / peak / SINGLE_GPU_FRAC
+        line["config"]["ranks_agree_on_tokens"] = True
     if rank == 0 and world == 1 and not args.no_cpu:
         threads = os.cpu_count() or 1
-        seconds_cpu, sample = cpu_forward_seconds_per_step(work, 3, threads)
-        line["cpu_baseline"] = {"value": batch / seconds_cpu, "unit": UNIT, "cores": threads, "kind": "port",
-                                "sample": sample}
+        result = cpu_forward(work, 8, threads, repeats=2)
+        line["cpu_baseline"] = {"value": batch / result["seconds"], "unit": UNIT, "cores": threads, "kind": result["kind"],
+                                "sample": result["sample"]}
     plan.close()
+    if world > 1:
+        dist.barrier()
     if rank == 0:
+        remove_plans(plan_dir)
         print(json.dumps(line), flush=True)
     if world > 1:
-        import torch.distributed as dist
         dist.destroy_process_group()
 
 
@@ -372,18 +459,18 @@ def main() -> None:
     parser.add_argument("--steps", type=int, default=128)
     parser.add_argument("--warmup", type=int, default=4)
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
-    parser.add_argument("--model", choices=sorted(MODELS), default="llama-3.1-8b",
-                        help="shape of the synthetic model (the headline workload is llama-3.1-8b, batch 1)")
+    parser.add_argument("--model", choices=sorted(MODELS), default=None,
+                        help="shape of the synthetic model (default: llama-3.1-8b on one GPU, llama-3.1-70b sharded over several)")
     parser.add_argument("--batch", type=int, default=1)
-    parser.add_argument("--context", type=int, default=0, help="0: seeded draw in [512, 8192]")
+    parser.add_argument("--context", type=int, default=None,
+                        help="0: seeded draw in [512, 8192] (the one-GPU default); several GPUs default to 4096")
     parser.add_argument("--layers", type=int, default=0, help="override the depth (profiling a small case)")
-    parser.add_argument("--geometry", default="", help="JSON overrides of the GEMV page geometry")
-    parser.add_argument("--slots", type=int, default=0)
     parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     parser.add_argument("--trace", action="store_true",
                         help="after the timed runs, stamp one more step and print the per-stage table (rank 0)")
-    parser.add_argument("--tp", action="store_true",
-                        help="shard one model over the ranks (tensor parallelism) instead of running replicas")
+    parser.add_argument("--replicas", action="store_true",
+                        help="several GPUs: independent copies of the one-GPU workload instead of one sharded model")
+    parser.add_argument("--tp", action="store_true", help="accepted for compatibility: several GPUs shard one model by default")
     args = parser.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -86,6 +86,7 @@ struct MegaParams {
   int write_logits;
   int grid, nslots, xs_bytes;
   int attn_min_spt;         // least ring slots of keys per attention task (a task's fixed cost wants amortising)
+  int prefetch_window;      // weight pages (over all CTAs) the streaming threads may pull into L2 ahead of the ring while it is full; 0: off
   unsigned long long bar_base;     // grid-barrier arrivals before this launch
   unsigned long long watchdog_ns;  // per-wait limit
   GemvGeo geo[kNumGemv];
