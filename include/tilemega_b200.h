@@ -165,6 +165,18 @@ uint64_t tm_plan_step_bytes(void* plan, uint64_t cached_tokens_total);
 int tm_pack_tile_pages(const void* src, uint64_t rows, uint64_t cols, uint64_t src_pitch, uint32_t tile_n,
                        uint32_t tile_k, void* dst, void* stream);
 
+/* Microbenchmarks behind configs/targets/sm_100.json: the reference fills the "calibration"
+ * block of its target descriptions with lib/Target/Calibration.cu and its siblings; this runs
+ * the named benchmark on `device` and writes its numbers to out[0..capacity). `what`: "clock"
+ * (SM MHz under load), "pipes" (fp32 / int32 / ex2 / rsqrt G(fl)op/s), "tensor" (mma.sync fp16,
+ * bf16 GFLOP/s), "smem" (GB/s at 1, 2, 4, 8 CTAs per SM, then the bank-conflict slope),
+ * "latency" (L1, L2, DRAM ns per dependent load), "l2_curve" (pairs footprint bytes, GB/s),
+ * "dram" (copy GB/s), "sync" (atomic, __threadfence, __syncthreads, named barrier, cluster
+ * barrier ns), "atomic_contention" and "grid_barrier" (pairs CTAs, ns). Returns the count of
+ * numbers written or a negative status. Allocates and frees its own buffers; changes no
+ * device setting. */
+int tm_calibrate(int device, const char* what, double* out, int capacity);
+
 /* No counterpart in the reference. The bounded-wait self test of
  * tm_plan_watchdog_probe for callers that may not allocate device memory: a
  * process whose HBM is fully committed to weight and KV pools, a health check

@@ -105,8 +105,11 @@ def test_every_moe_stage_of_one_layer(base, plan_dir):
     agreement(router_gpu, F.linear(xm, w[p + "mlp.gate.weight"]).reshape(-1), "router logits", ulps=1.0, exact_fraction=0.9)
     # routing from the GPU's own logits: indices bit-exact and in rank order, weights renormalised in fp32
     probability = torch.softmax(router_gpu.float(), -1)
-    weight, index = torch.topk(probability, topk)
-    assert torch.equal(route, index.to(torch.int32)), (route.tolist(), index.tolist())
+    # descending probability, ties to the smaller expert index (include/tilemega/Backend/Sm90DenseMoe.cuh:30-35;
+    # torch.topk leaves the order of exact ties open, and bf16 logits of 128 experts do tie)
+    order = sorted(range(probability.numel()), key=lambda e: (-probability[e].item(), e))[:topk]
+    assert route.tolist() == order, (route.tolist(), order)
+    weight = probability[order]
     assert torch.allclose(route_weight, weight / weight.sum(), rtol=0, atol=2e-6)
     # expert SwiGLU rows, one per chosen expert
     for slot in range(topk):

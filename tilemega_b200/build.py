@@ -15,10 +15,12 @@ CSRC = ROOT / "csrc"
 LIB_DIR = ROOT / "lib"
 LIBRARY = LIB_DIR / "libtilemega_b200.so"
 # (object name, source, extra flags). The kernel source is compiled twice, side by side:
-# plain (unsharded dense plans) and extended (tensor parallelism, mixture of experts, QK norm).
+# plain (unsharded dense plans), extended (tensor parallelism, mixture of experts, QK norm) and dense-batch
+# (batch 16..64: GEMM stages on tcgen05 tiles).
 UNITS = (("megakernel", "megakernel.cu", ()), ("megakernel_extended", "megakernel.cu", ("-DTMB_EXTENDED=1",)),
+         ("megakernel_dense", "megakernel.cu", ("-DTMB_DENSE=1",)),
          ("runtime", "runtime.cu", ()), ("plan_spec", "plan_spec.cpp", ()), ("static_probe", "static_probe.cu", ()),
-         ("pack", "pack.cu", ()))
+         ("pack", "pack.cu", ()), ("calibrate", "calibrate.cu", ()))
 SOURCES = tuple(sorted({unit[1] for unit in UNITS}))
 HEADERS = ("params.h", "ptx.cuh", "plan_spec.h", "json.h")
 
@@ -45,7 +47,7 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
     LIB_DIR.mkdir(exist_ok=True)
     objects = []
     common = ["-O3", "-std=c++17", "-Xcompiler", "-fPIC", "-gencode", "arch=compute_100a,code=sm_100a",
-              "-lineinfo"]
+              "-lineinfo", "-diag-suppress", "177"]   # 177: helpers one of the three kernel translation units does not use
     if verbose:
         common += ["-Xptxas", "-v"]
     build_dir = ROOT / "build"

@@ -38,6 +38,9 @@
 #ifndef TMB_EXTENDED
 #define TMB_EXTENDED 0   // 1: the translation unit with tensor parallelism, mixture of experts and QK norm
 #endif
+#ifndef TMB_DENSE
+#define TMB_DENSE 0      // 1: the translation unit with the dense-batch kernel (GEMM stages on tcgen05 tiles)
+#endif
 
 namespace tmb {
 
@@ -55,13 +58,28 @@ constexpr int kOffBestIdx = 704;   // int[8 warps][kMaxBatch]
 constexpr int kOffWsum = 960;      // float[kMaxBatch][8]
 constexpr int kOffSc = 1216;       // routing of the current layer: int expert[8], float weight[8] (+32), mbarrier (+64)
 constexpr int kOffRed = 3264;      // float[kPartialRing][8 warps][8 rows][batch]: 2 KB per sequence of the batch
+// Dense-batch plans (batch > kMaxBatch) have no GEMV partial-sum area; bytes [kOffRed, kOffDenseXs) hold the
+// control words of their GEMM stages instead, and the activation chunks / attention scratch start at kOffDenseXs.
+constexpr int kOffDXFull = 3264;     // u64[4] activation chunk landed
+constexpr int kOffDXEmpty = 3296;    // u64[4] activation chunk consumed by the tensor cores
+constexpr int kOffDAccFull = 3328;   // u64[2] accumulator complete
+constexpr int kOffDAccEmpty = 3344;  // u64[2] accumulator read out by its four epilogue warps
+constexpr int kOffDDrain = 3360;     // u64    every tensor-core operation of the launch has completed
+constexpr int kOffDTmem = 3368;      // u32    tensor memory base address
+constexpr int kOffDFifo = 3392;      // int[kFifo] GEMM tasks for the issuing thread: id, first ring slot and its phase
+constexpr int kOffDTok = 3520;       // int[kDenseMaxBatch]
+constexpr int kOffDBestVal = 3840;   // float[8 warps][kDenseMaxBatch]
+constexpr int kOffDBestIdx = 5888;   // int[8 warps][kDenseMaxBatch]
+constexpr int kOffDenseXs = 8192;
 // Features compiled into an instantiation of the kernel (template parameter X): the plain
 // one (0) serves unsharded dense plans and carries neither.
 constexpr int kXTp = 1;    // tensor parallelism: all-reduce epilogue, argmax exchange
 constexpr int kXMoe = 2;   // mixture of experts and the per-head QK norm (batch 1)
 constexpr int kFifo = 32;          // entries; the streaming warp keeps at most kFifo/2 unread
 
-__host__ __device__ inline int xs_offset(int batch) { return kOffRed + kPartialRing * 8 * 8 * 4 * batch; }   // activation rows / attention scratch
+__host__ __device__ inline int xs_offset(int batch) {   // activation rows / attention scratch
+  return batch > kMaxBatch ? kOffDenseXs : kOffRed + kPartialRing * 8 * 8 * 4 * batch;
+}
 __host__ __device__ inline int ring_offset(int xs_bytes, int batch) { return (xs_offset(batch) + xs_bytes + 1023) & ~1023; }
 
 struct Ctx {
@@ -79,6 +97,7 @@ struct Ctx {
   int pending_next;                  // ... and for the stage after it (claimed a whole stage ahead)
   uint32_t gemv_seq;                 // GEMV tasks finished by this CTA (partial-sum ring cursor)
   uint32_t route_phase;              // routings published (arithmetic warps) / consumed (streaming thread), mod 2
+  uint32_t dq_pos;                   // dense plans: GEMM FIFO entries pushed (streaming thread) / popped (issuing thread)
   // streaming thread: where it is in the launch's sequence of weight pages, and how far ahead of
   // that it has prefetched into L2 (absolute page numbers count every GEMV stage's pages in program order)
   int cur_seq, cur_npages, cur_ppt, cur_task;   // GEMV stage being streamed: its number, pages, pages per task, last task posted
@@ -87,7 +106,7 @@ struct Ctx {
   __device__ Ctx(const MegaParams& q, unsigned char* s, int cta_index)
       : p(q), smem(s), warp(threadIdx.x >> 5), lane(threadIdx.x & 31), tid(threadIdx.x), cta(cta_index), slot(0), phase(0),
         bar_target(q.bar_base), task_seq(0), dead(false), q_pos(0), inst(0), pending(0), pending_next(0), gemv_seq(0),
-        route_phase(0), cur_seq(-1), cur_npages(0), cur_ppt(1), cur_task(0), pf_seq(0), cur_abs_base(0), pf_abs(-1),
+        route_phase(0), dq_pos(0), cur_seq(-1), cur_npages(0), cur_ppt(1), cur_task(0), pf_seq(0), cur_abs_base(0), pf_abs(-1),
         pf_abs_base(0) {}
   __device__ uint64_t* full(int i) const { return reinterpret_cast<uint64_t*>(smem + kOffFull) + i; }
   __device__ uint64_t* empty(int i) const { return reinterpret_cast<uint64_t*>(smem + kOffEmpty) + i; }
@@ -436,10 +455,32 @@ __device__ __forceinline__ void stream_close(Ctx& c) {
   c.pending_next = claim(c, c.inst + 1);
 }
 
+// Dense plans: the thread that issues the tensor-core work gets every GEMM task through a FIFO of its
+// own, each entry carrying the task id (16 bits; 0xFFFF closes a stage), the ring slot the task's
+// first page goes to and that slot's phase, under the entry's sequence tag.
+constexpr uint32_t kDFifoClose = 0xFFFFu;
+
+__device__ __forceinline__ void dfifo_push(Ctx& c, int value, uint32_t slot, uint32_t phase) {
+  if (!c.dead) {
+    volatile int* head = c.ctl() + 6;
+    if (int(c.dq_pos) - *head >= kFifo / 2) {
+      unsigned long long t0 = 0;
+      uint32_t polls = 0;
+      while (int(c.dq_pos) - *head >= kFifo / 2) {
+        if ((++polls & 255u) == 0 && wait_give_up(c.p, t0, kSiteEmpty, c.dq_pos, uint32_t(*head))) break;
+      }
+    }
+    reinterpret_cast<volatile uint32_t*>(c.smem + kOffDFifo)[c.dq_pos & (kFifo - 1)] =
+        (((c.dq_pos + 1u) & 0xFFFu) << 20) | (slot << 17) | (phase << 16) | (value < 0 ? kDFifoClose : uint32_t(value));
+  }
+  ++c.dq_pos;
+}
+
 // One GEMV task: post its id, then copy its weight pages (consecutive from `src`) into the ring.
 __device__ __forceinline__ void stream_pages(Ctx& c, const GemvGeo& geo, const unsigned char* src, int id,
                                              uint32_t page_bytes, uint64_t policy) {
   fifo_push(c, id);
+  if (c.p.dense) dfifo_push(c, id, c.slot, c.phase);
   for (int pg = 0; pg < geo.pages_per_task; ++pg, src += page_bytes) {
     if (!stream_wait_empty(c)) return;
     // the last page of a padded reduction: its pad columns (whole 64-column blocks at the
@@ -481,6 +522,7 @@ __device__ __forceinline__ void stream_gemv(Ctx& c, const GemvGeo& geo, const vo
     chunk = upcoming;
   }
   stream_close(c);
+  if (c.p.dense) dfifo_push(c, -1, 0u, 0u);
 }
 
 // Mixture of experts, batch 1. gate/up: the chosen experts' matrices one after the other,
@@ -575,7 +617,7 @@ template <int D, int X>
 __device__ void streamer_main(Ctx& c) {
   const MegaParams& p = c.p;
   const uint64_t policy = policy_evict_first();
-  const unsigned long long bars_per_step = (unsigned long long)(p.stages_per_layer - 1) * p.layers + 1ull;   // grid barriers: none between QKV and attention
+  const unsigned long long bars_per_step = (unsigned long long)p.bars_per_step;   // grid-wide arrivals of one step
   const uint32_t norm_bytes = uint32_t(p.hidden) * 2u;
   c.pending = claim(c, 0);
   c.pending_next = claim(c, 1);
@@ -1864,7 +1906,529 @@ __global__ void __launch_bounds__(kThreads, 1) decode_megakernel_ranks(const Meg
   run_cta<B, D, GQ, X>(ranks[r], int(blockIdx.x) - base);
 }
 
-#if !TMB_EXTENDED
+#if TMB_DENSE
+// ---------------------------------------------------------------------------
+// Dense-batch plans (batch 16..64): the GEMM stages on the 5th-generation tensor cores.
+//
+// A decode step keeps its stage list; what changes is who does the arithmetic of a GEMV
+// stage. With B >= 16 rows the contraction is dense enough for a tcgen05 tile with the
+// operands swapped: A = a weight page (M = 128 weight rows, K-major, 128-byte swizzled --
+// exactly what the tile_pages recipe writes for tile_n = 128, so a page is still one
+// contiguous 32 KB bulk copy and one ring slot), B = the activation rows of the batch
+// (N = B, a 128-column chunk fetched by two tiled TMA loads through a tensor map over the
+// row-major [B][K] buffer, swizzle done by the copy engine), D = fp32 [128 weight rows][B]
+// in tensor memory. Roles per CTA:
+//  * the streaming thread as before: it claims tasks, posts them and fills the ring with
+//    weight pages (and KV slots), never waiting for a stage boundary;
+//  * lane 0 of one more warp waits for the stage's inputs (the grid-wide arrival counter),
+//    loads the activation chunks of each task, issues tcgen05.mma for every chunk that has
+//    landed and lets tcgen05.commit release the slots and publish the accumulator;
+//  * the arithmetic warps are two groups of four (a warp reads tensor-memory lanes
+//    32*(warp%4)..+31): group g runs the epilogues of the CTA's tasks g, g+2, ... out of
+//    accumulator g, so the next task's products overlap the previous task's epilogue. A
+//    thread owns ONE weight row (output feature) for all batch rows.
+// RMSNorm is a stage of its own here (rows spread over the CTAs, result in `xn`): a
+// normalised row cannot stay in shared memory next to a ring when there are 64 of them.
+// Attention is the same code as in the small-batch kernel.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint64_t* dbar(const Ctx& c, int offset, int i) {
+  return reinterpret_cast<uint64_t*>(c.smem + offset) + i;
+}
+__device__ __forceinline__ int* dtok(const Ctx& c) { return reinterpret_cast<int*>(c.smem + kOffDTok); }
+__device__ __forceinline__ void group_sync(int group) { asm volatile("bar.sync %0, 128;" ::"r"(2 + group) : "memory"); }
+
+// The issuing thread: next GEMM task of the stage. Returns the task id (or -1: stage closed,
+// -2: the launch is being abandoned) and the first ring slot / phase of its pages.
+__device__ __forceinline__ int dfifo_pop(Ctx& c, uint32_t& slot, uint32_t& phase) {
+  const volatile uint32_t* entry = reinterpret_cast<volatile uint32_t*>(c.smem + kOffDFifo) + (c.dq_pos & (kFifo - 1));
+  const uint32_t tag = (c.dq_pos + 1u) & 0xFFFu;
+  uint32_t word = *entry;
+  if (!c.dead && (word >> 20) != tag) {
+    unsigned long long t0 = 0;
+    uint32_t polls = 0;
+    while (((word = *entry) >> 20) != tag) {
+      if ((++polls & 255u) == 0 && wait_give_up(c.p, t0, kSiteFull, c.dq_pos, word)) {
+        c.dead = true;
+        break;
+      }
+    }
+  }
+  if (c.dead) return -2;
+  ++c.dq_pos;
+  c.ctl()[6] = int(c.dq_pos);
+  slot = (word >> 17) & 7u;
+  phase = (word >> 16) & 1u;
+  const uint32_t value = word & kDFifoClose;
+  return value == kDFifoClose ? -1 : int(value);
+}
+
+struct MmaState {
+  uint32_t tmem, idesc;
+  uint32_t x_loaded, x_used;   // activation chunks loaded / consumed by this CTA so far (slot = n % kDenseXSlots)
+  uint32_t task_seq;           // GEMM tasks issued by this CTA (accumulator = task_seq & 1)
+};
+
+// One GEMM stage, issuing side. `arrivals`: grid-wide arrivals (counted from the start of the launch)
+// after which the stage's input rows are complete in global memory.
+__device__ __forceinline__ bool mma_stage(Ctx& c, MmaState& st, const DenseGeo& g, const void* tensor_map,
+                                          unsigned long long arrivals) {
+  const MegaParams& p = c.p;
+  {
+    const unsigned long long need = p.bar_base + arrivals * (unsigned long long)p.grid;
+    unsigned long long t0 = 0, seen;
+    uint32_t polls = 0;
+    while ((seen = ld_acquire(p.bar)) < need) {
+      if ((++polls & 63u) == 0 && wait_give_up(p, t0, kSiteGrid, need, seen)) {
+        c.dead = true;
+        return false;
+      }
+    }
+    fence_proxy_async();   // the rows were written with ordinary stores by other CTAs; the copy engine reads them
+  }
+  const uint32_t chunk_bytes = uint32_t(p.batch) * kDenseTileK * 2u;
+  const uint32_t block_bytes = uint32_t(p.batch) * 128u;   // one 64-column swizzle block of the batch rows
+  unsigned char* const xring = c.smem + kOffDenseXs;
+  uint32_t slot = 0, phase = 0;
+  for (int t = dfifo_pop(c, slot, phase); t >= 0; t = dfifo_pop(c, slot, phase)) {
+    const int part = t % g.nsplit;
+    const int k0 = part * g.cps * kDenseTileK;
+    const uint32_t buf = st.task_seq & 1u;
+    // the accumulator's previous tile (two tasks ago) must have been read out
+    if (!mbar_wait(c, dbar(c, kOffDAccEmpty, buf), ((st.task_seq >> 1) & 1u) ^ 1u, kSiteEmpty)) return false;
+    tcgen05_fence_after();
+    const uint32_t d_tmem = st.tmem + buf * uint32_t(kDenseMaxBatch);
+    int loaded = 0;
+    for (int i = 0; i < g.cps; ++i) {
+      // keep up to kDenseXSlots activation chunks of this task in flight
+      while (loaded < g.cps && loaded < i + kDenseXSlots) {
+        const uint32_t xs = st.x_loaded % kDenseXSlots, xphase = (st.x_loaded / kDenseXSlots) & 1u;
+        if (!mbar_wait(c, dbar(c, kOffDXEmpty, xs), xphase ^ 1u, kSiteEmpty)) return false;
+        mbar_expect_tx(dbar(c, kOffDXFull, xs), chunk_bytes);
+        unsigned char* dst = xring + xs * chunk_bytes;
+        tma_load_2d(dst, tensor_map, k0 + loaded * kDenseTileK, 0, dbar(c, kOffDXFull, xs));
+        tma_load_2d(dst + block_bytes, tensor_map, k0 + loaded * kDenseTileK + 64, 0, dbar(c, kOffDXFull, xs));
+        ++st.x_loaded;
+        ++loaded;
+      }
+      const uint32_t xs = st.x_used % kDenseXSlots, xphase = (st.x_used / kDenseXSlots) & 1u;
+      if (!mbar_wait(c, c.full(slot), phase, kSiteFull)) return false;
+      if (!mbar_wait(c, dbar(c, kOffDXFull, xs), xphase, kSiteFull)) return false;
+      tcgen05_fence_after();
+      const uint32_t w_addr = smem_u32(c.ring(slot)), x_addr = smem_u32(xring + xs * chunk_bytes);
+#pragma unroll
+      for (int cb = 0; cb < 2; ++cb) {
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+          const uint64_t a = umma_desc_k_sw128(w_addr + cb * (kDenseTileN * 128) + ks * 32, 1024);
+          const uint64_t b = umma_desc_k_sw128(x_addr + cb * block_bytes + ks * 32, 1024);
+          umma_bf16(d_tmem, a, b, st.idesc, (i | cb | ks) != 0 ? 1u : 0u);
+        }
+      }
+      // the slot's release barrier counts the eight arithmetic warps of an attention stage: eight arrivals
+#pragma unroll
+      for (int r = 0; r < kConsumerWarps; ++r) umma_commit(c.empty(slot));
+      umma_commit(dbar(c, kOffDXEmpty, xs));
+      ++st.x_used;
+      if (++slot == uint32_t(p.nslots)) { slot = 0; phase ^= 1u; }
+    }
+    umma_commit(dbar(c, kOffDAccFull, buf));
+    ++st.task_seq;
+  }
+  return !c.dead;
+}
+
+template <int GQ>
+__device__ void mma_main_dense(Ctx& c) {
+  const MegaParams& p = c.p;
+  MmaState st;
+  st.tmem = *reinterpret_cast<volatile uint32_t*>(c.smem + kOffDTmem);
+  st.idesc = umma_idesc_bf16(kDenseTileN, p.batch);
+  st.x_loaded = st.x_used = st.task_seq = 0;
+  const unsigned char* maps = static_cast<const unsigned char*>(p.tmaps);
+  bool alive = true;
+  for (int si = 0; si < p.nsteps && alive; ++si) {
+    // arrivals of a step, in program order: per layer norm1, attention, o, norm2, gate/up, down; then final norm, head
+    const unsigned long long step0 = (unsigned long long)si * p.bars_per_step;
+    for (int l = 0; l < p.layers && alive; ++l) {
+      const unsigned long long base = step0 + 6ull * l;
+      alive = mma_stage(c, st, p.dgeo[kQkv], maps, base + 1) && mma_stage(c, st, p.dgeo[kOProj], maps + 128, base + 2) &&
+              mma_stage(c, st, p.dgeo[kGateUp], maps, base + 4) && mma_stage(c, st, p.dgeo[kDown], maps + 256, base + 5);
+    }
+    if (alive) alive = mma_stage(c, st, p.dgeo[kHead], maps, step0 + 6ull * p.layers + 1);
+  }
+  // nothing of this CTA may still be running on the tensor cores when tensor memory is freed
+  umma_commit(dbar(c, kOffDDrain, 0));
+  unsigned long long t0 = 0;
+  uint32_t polls = 0;
+  while (!mbar_try_wait(dbar(c, kOffDDrain, 0), 0u)) {
+    if ((++polls & 127u) == 0) {
+      const unsigned long long now = global_timer();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > p.watchdog_ns) break;
+    }
+  }
+}
+
+// RMSNorm stage: row b of the batch is normalised by CTA b mod grid and written to xn
+// (y = bf16(w * bf16(x * rsqrt(mean x^2 + eps))), python/tilemega/serving/export.py:24-27). Layer 0
+// reads the embedding row of the sequence's token and also seeds the residual stream with it.
+__device__ void norm_stage_dense(Ctx& c, const void* src, const void* weight, bool embed) {
+  const MegaParams& p = c.p;
+  const int chunks = p.hidden >> 3;
+  const uint4* nw = reinterpret_cast<const uint4*>(weight);
+  for (int b = c.cta; b < p.batch; b += p.grid) {
+    const __nv_bfloat16* row = static_cast<const __nv_bfloat16*>(src) +
+                               (embed ? size_t(min(max(dtok(c)[b], 0), p.vocab - 1)) : size_t(b)) * p.hidden;
+    constexpr int kHold = 4;   // hidden <= 8192: at most four 16-byte chunks per thread
+    uint4 v[kHold];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < kHold; ++j) {
+      const int i = c.tid + j * kConsumerThreads;
+      v[j] = make_uint4(0u, 0u, 0u, 0u);
+      if (i < chunks) v[j] = embed ? __ldg(reinterpret_cast<const uint4*>(row) + i) : __ldcg(reinterpret_cast<const uint4*>(row) + i);
+      float f[8];
+      unpack8(v[j], f);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ss = fmaf(f[e], f[e], ss);
+    }
+#pragma unroll
+    for (int m = 16; m; m >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
+    if (c.lane == 0) c.wsum()[c.warp] = ss;
+    consumer_sync();
+    float total = 0.f;
+#pragma unroll
+    for (int w = 0; w < kConsumerWarps; ++w) total += c.wsum()[w];
+    const float inv = 1.0f / sqrtf(total / float(p.hidden) + p.eps);
+#pragma unroll
+    for (int j = 0; j < kHold; ++j) {
+      const int i = c.tid + j * kConsumerThreads;
+      if (i < chunks) {
+        float f[8], w[8];
+        unpack8(v[j], f);
+        unpack8(__ldg(nw + i), w);
+        uint32_t o[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          o[e] = uint32_t(bf16_bits(w[2 * e] * bf16_round(f[2 * e] * inv))) |
+                 (uint32_t(bf16_bits(w[2 * e + 1] * bf16_round(f[2 * e + 1] * inv))) << 16);
+        reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.xn) + size_t(b) * p.hidden)[i] = make_uint4(o[0], o[1], o[2], o[3]);
+        if (embed) reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.x) + size_t(b) * p.hidden)[i] = v[j];
+      }
+    }
+    consumer_sync();   // wsum is reused by the next row
+  }
+}
+
+// The rounding sites of one stage's epilogue on 16 batch rows (b0 .. b0+15) of ONE output feature
+// `row`, held by one thread (include/tilemega/Backend/ServingEpilogue.h:38-57; Sm90DenseEpilogue.h:166-184).
+__device__ __forceinline__ void dense_epilogue_16(Ctx& c, const DenseGeo& g, const GemvIo& io, const float (&v)[16], int b0,
+                                                  int row, int tile) {
+  const MegaParams& p = c.p;
+  const int lane = c.lane, wq = c.warp & 3;
+  if (io.epilogue == kEpiStore) {
+    __nv_bfloat16* out = static_cast<__nv_bfloat16*>(io.out) + row;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) out[size_t(b0 + j) * g.n] = __float2bfloat16_rn(v[j]);
+  } else if (io.epilogue == kEpiResidual) {
+    unsigned short* out = reinterpret_cast<unsigned short*>(io.out) + row;
+    float res[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) res[j] = bf16_from_bits(__ldcg(out + size_t(b0 + j) * g.n));
+#pragma unroll
+    for (int j = 0; j < 16; ++j) out[size_t(b0 + j) * g.n] = bf16_bits(bf16_round(v[j]) + res[j]);
+  } else if (io.epilogue == kEpiSwiGLU) {
+    // rows come in units of 16 gate rows followed by their 16 up rows: lane l < 16 holds the gate of
+    // feature tile*64 + wq*16 + l, lane l + 16 its up value
+    __nv_bfloat16* h = static_cast<__nv_bfloat16*>(io.out) + tile * (kDenseTileN / 2) + wq * 16 + (lane & 15);
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const float vb = bf16_round(v[j]);
+      const float up = __shfl_down_sync(0xffffffffu, vb, 16);
+      if (lane < 16) h[size_t(b0 + j) * (g.n >> 1)] = __float2bfloat16_rn(silu_bf16(vb) * up);
+    }
+  } else {   // kEpiHead
+    float* best_val = reinterpret_cast<float*>(c.smem + kOffDBestVal) + c.warp * kDenseMaxBatch;
+    int* best_idx = reinterpret_cast<int*>(c.smem + kOffDBestIdx) + c.warp * kDenseMaxBatch;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      if (p.write_logits) static_cast<float*>(io.out)[size_t(b0 + j) * g.n + row] = v[j];
+      float bv = bf16_round(v[j]);
+      int bi = p.head_base + row;
+#pragma unroll
+      for (int m = 1; m < 32; m <<= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, m);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, m);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+      }
+      if (lane == ((b0 + j) & 31)) {   // one lane keeps the warp's running best of this batch row
+        const float old = best_val[b0 + j];
+        if (bv > old || (bv == old && bi < best_idx[b0 + j])) {
+          best_val[b0 + j] = bv;
+          best_idx[b0 + j] = bi;
+        }
+      }
+    }
+  }
+}
+
+// One GEMM stage, epilogue side. Both warp groups walk the CTA's task list; group g takes every
+// second task. `seq` counts the CTA's GEMM tasks across stages (it selects the accumulator).
+__device__ void gemm_epilogue_stage(Ctx& c, const DenseGeo& g, const GemvIo& io, uint32_t& seq) {
+  const MegaParams& p = c.p;
+  const int group = c.warp >> 2, wq = c.warp & 3, m = wq * 32 + c.lane;
+  const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(c.smem + kOffDTmem);
+  const int nb = p.batch >> 4;   // 16-row chunks of the batch
+  volatile int* last_flag = c.ctl() + (group ? 7 : 5);
+  for (int t = fifo_pop(c); t >= 0; t = fifo_pop(c)) {
+    // the ring cursor follows every task (the attention stages consume slots from it)
+    for (int i = 0; i < g.cps; ++i) c.advance();
+    const uint32_t my_seq = seq++;
+    if (int(my_seq & 1u) != group) continue;
+    const int tile = t / g.nsplit;
+    const int row = tile * kDenseTileN + m;
+    mbar_wait_warp(c, dbar(c, kOffDAccFull, group), (my_seq >> 1) & 1u, kSiteFull);
+    tcgen05_fence_after();
+    const uint32_t taddr = tmem + (uint32_t(wq * 32) << 16) + uint32_t(group) * uint32_t(kDenseMaxBatch);
+    if (g.nsplit == 1) {
+      for (int j = 0; j < nb; ++j) {
+        float v[16];
+        tmem_load_16(taddr + 16 * j, v);
+        if (j == nb - 1) {   // the accumulator is in registers: the tensor cores may overwrite it
+          tcgen05_fence_before();
+          __syncwarp();
+          if (c.lane == 0) mbar_arrive(dbar(c, kOffDAccEmpty, group));
+        }
+        dense_epilogue_16(c, g, io, v, 16 * j, row, tile);
+      }
+    } else {
+      // this part's fp32 tile goes to global memory; the last part to arrive adds all parts in
+      // ascending order (so the sum does not depend on arrival order) and runs the epilogue
+      float* mine = p.gemm_part + (size_t(t) * kDenseTileN + m) * p.batch;
+      for (int j = 0; j < nb; ++j) {
+        float v[16];
+        tmem_load_16(taddr + 16 * j, v);
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          reinterpret_cast<float4*>(mine + 16 * j)[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (c.lane == 0) mbar_arrive(dbar(c, kOffDAccEmpty, group));
+      group_sync(group);   // every thread's partial stores are ordered before the counter below
+      if ((c.tid & 127) == 0) {
+        __threadfence();
+        const unsigned old = atomicAdd(p.gemm_cnt + tile, 1u);
+        const int last = old == unsigned(g.nsplit - 1);
+        if (last) atomicExch(p.gemm_cnt + tile, 0u);
+        *last_flag = last;
+      }
+      group_sync(group);
+      const bool last = *last_flag != 0;
+      group_sync(group);   // everyone has read the flag before the next task may overwrite it
+      if (!last) continue;
+      __threadfence();
+      const float* parts = p.gemm_part + (size_t(tile) * g.nsplit * kDenseTileN + m) * p.batch;
+      for (int j = 0; j < nb; ++j) {
+        float v[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) v[e] = 0.f;
+        for (int part = 0; part < g.nsplit; ++part) {
+          const float4* src = reinterpret_cast<const float4*>(parts + size_t(part) * kDenseTileN * p.batch + 16 * j);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float4 x = __ldcg(src + q);
+            v[4 * q] += x.x; v[4 * q + 1] += x.y; v[4 * q + 2] += x.z; v[4 * q + 3] += x.w;
+          }
+        }
+        dense_epilogue_16(c, g, io, v, 16 * j, row, tile);
+      }
+    }
+    if (io.ready) {
+      // one more 128-row tile of this KV-head group is in global memory (counted in 8-row units, the
+      // unit the attention tasks' readiness test uses)
+      group_sync(group);
+      if ((c.tid & 127) == 0) {
+        __threadfence();
+        red_release_add(io.ready + tile / io.tiles_per_group, (unsigned long long)(kDenseTileN / kTileN));
+      }
+    }
+  }
+}
+
+template <int GQ>
+__device__ void consumer_main_dense(Ctx& c) {
+  const MegaParams& p = c.p;
+  constexpr int D = 128;
+  const int B = p.batch;
+  uint32_t seq = 0;
+  for (int si = 0; si < p.nsteps; ++si) {
+    const int step = p.first_step + si;
+    const int past = __ldg(p.past + step);
+    if (si == 0) {
+      if (c.tid < B) dtok(c)[c.tid] = __ldcg(p.tokens + size_t(c.tid) * p.capacity + seq_pos(p, past, c.tid));
+      consumer_sync();
+    }
+    if (c.cta == 0 && c.tid == 0) p.step_ns[step] = global_timer();
+    for (int l = 0; l < p.layers; ++l) {
+      const LayerPtrs lp = p.layer[l];
+      GemvIo io;
+      if (l > 0 && !grid_wait(c)) return;                      // the previous layer's down projection is complete
+      norm_stage_dense(c, l == 0 ? p.embed : p.x, lp.norm1, l == 0);
+      grid_arrive(c);
+      io = GemvIo{nullptr, nullptr, 0, kEpiStore, p.qkv, p.qkv_ready, (GQ + 2) * D / kDenseTileN, nullptr, 0, 0u};
+      gemm_epilogue_stage(c, p.dgeo[kQkv], io, seq);
+      attn_stage<1, D, GQ, 0>(c, lp, past, false, 0, (unsigned long long)(si * p.layers + l + 1));
+      grid_arrive(c);
+      io = GemvIo{nullptr, nullptr, 0, kEpiResidual, p.x, nullptr, 1, nullptr, 0, 0u};
+      gemm_epilogue_stage(c, p.dgeo[kOProj], io, seq);
+      grid_arrive(c);
+      if (!grid_wait(c)) return;                               // the residual stream after attention is complete
+      norm_stage_dense(c, p.x, lp.norm2, false);
+      grid_arrive(c);
+      io = GemvIo{nullptr, nullptr, 0, kEpiSwiGLU, p.h, nullptr, 1, nullptr, 0, 0u};
+      gemm_epilogue_stage(c, p.dgeo[kGateUp], io, seq);
+      grid_arrive(c);
+      io = GemvIo{nullptr, nullptr, 0, kEpiResidual, p.x, nullptr, 1, nullptr, 0, 0u};
+      gemm_epilogue_stage(c, p.dgeo[kDown], io, seq);
+      grid_arrive(c);
+    }
+    if (!grid_wait(c)) return;
+    norm_stage_dense(c, p.x, p.final_norm, false);
+    grid_arrive(c);
+    // lm_head: every warp keeps a running (value, index) per batch row
+    float* best_val = reinterpret_cast<float*>(c.smem + kOffDBestVal);
+    int* best_idx = reinterpret_cast<int*>(c.smem + kOffDBestIdx);
+    for (int i = c.tid; i < kConsumerWarps * kDenseMaxBatch; i += kConsumerThreads) {
+      best_val[i] = -INFINITY;
+      best_idx[i] = 0x7fffffff;
+    }
+    consumer_sync();
+    GemvIo io{nullptr, nullptr, 0, kEpiHead, p.logits, nullptr, 1, nullptr, 0, 0u};
+    gemm_epilogue_stage(c, p.dgeo[kHead], io, seq);
+    consumer_sync();
+    if (c.tid < B) {
+      float bv = -INFINITY;
+      int bi = 0x7fffffff;
+      for (int w = 0; w < kConsumerWarps; ++w) {
+        const float v = best_val[w * kDenseMaxBatch + c.tid];
+        const int i = best_idx[w * kDenseMaxBatch + c.tid];
+        if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+      }
+      p.argmax_val[size_t(c.cta) * B + c.tid] = bv;
+      p.argmax_idx[size_t(c.cta) * B + c.tid] = bi;
+    }
+    grid_arrive(c);
+    if (!grid_wait(c)) return;
+    // every CTA reduces the per-CTA candidates itself (it needs the tokens for the next step's
+    // embedding); CTA 0 records them (include/tilemega/Backend/Sm90DenseHead.cuh:48-135)
+    for (int b = c.warp; b < B; b += kConsumerWarps) {
+      float bv = -INFINITY;
+      int bi = 0x7fffffff;
+      for (int gi = c.lane; gi < p.grid; gi += 32) {
+        const float v = __ldcg(p.argmax_val + size_t(gi) * B + b);
+        const int i = __ldcg(p.argmax_idx + size_t(gi) * B + b);
+        if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+      }
+#pragma unroll
+      for (int mk = 16; mk; mk >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, mk);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, mk);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+      }
+      if (c.lane == 0) {
+        const int pos = seq_pos(p, past, b);
+        int* slot = p.tokens + size_t(b) * p.capacity + min(pos + 1, p.capacity - 1);
+        int tok = min(max(bi, 0), p.vocab - 1);
+        if (pos + 1 < p.prompt_len) {
+          tok = __ldcg(slot);   // teacher-forced prompt position: the token state wins
+        } else if (c.cta == 0 && pos + 1 < p.capacity) {
+          *slot = tok;
+        }
+        dtok(c)[b] = tok;
+      }
+    }
+    if (c.cta == 0 && c.tid == 0) p.step_ns[step + 1] = global_timer();
+    consumer_sync();
+  }
+}
+
+template <int GQ>
+__global__ void __launch_bounds__(kDenseThreads, 1) dense_megakernel(const __grid_constant__ MegaParams p) {
+  extern __shared__ __align__(1024) unsigned char smem[];
+  Ctx c(p, smem, int(blockIdx.x));
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < p.nslots; ++i) {
+      mbar_init(c.full(i), 1);
+      mbar_init(c.empty(i), kConsumerWarps);
+    }
+    for (int i = 0; i < kDenseXSlots; ++i) {
+      mbar_init(dbar(c, kOffDXFull, i), 1);
+      mbar_init(dbar(c, kOffDXEmpty, i), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(dbar(c, kOffDAccFull, i), 1);
+      mbar_init(dbar(c, kOffDAccEmpty, i), 4);
+    }
+    mbar_init(dbar(c, kOffDDrain, 0), 1);
+    mbar_fence_init();
+    for (int i = 0; i < 8; ++i) c.ctl()[i] = 0;
+    for (int i = 0; i < kFifo; ++i) {
+      c.fifo()[i] = 0;   // sequence tag 0 never matches
+      reinterpret_cast<int*>(smem + kOffDFifo)[i] = 0;
+    }
+  }
+  const bool issuer = c.warp == kConsumerWarps + 1;
+  if (issuer) tmem_alloc(reinterpret_cast<uint32_t*>(smem + kOffDTmem), kDenseTmemColumns);   // the whole warp
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  if (c.warp == kConsumerWarps) {
+    if (c.lane == 0) {
+      streamer_main<128, 0>(c);
+      streamer_drain(c);
+    }
+  } else if (issuer) {
+    if (c.lane == 0) mma_main_dense<GQ>(c);
+  } else {
+    consumer_main_dense<GQ>(c);
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (issuer) tmem_dealloc(*reinterpret_cast<volatile uint32_t*>(smem + kOffDTmem), kDenseTmemColumns);
+}
+
+template <int GQ>
+static cudaError_t run_dense_instance(const MegaParams& p, size_t smem_bytes, cudaStream_t stream, bool prepare) {
+  auto kernel = dense_megakernel<GQ>;
+  if (prepare) {
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem_bytes));
+    if (err != cudaSuccess) return err;
+    int resident = 0;
+    err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, kernel, kDenseThreads, smem_bytes);
+    if (err != cudaSuccess) return err;
+    int device = 0, sms = 0;
+    cudaGetDevice(&device);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    return (resident < 1 || p.grid > sms * resident) ? cudaErrorLaunchOutOfResources : cudaSuccess;
+  }
+  kernel<<<p.grid, kDenseThreads, smem_bytes, stream>>>(p);
+  return cudaGetLastError();
+}
+
+cudaError_t run_decode_dense(const MegaParams& p, cudaStream_t stream, bool prepare) {
+  const size_t smem_bytes = size_t(ring_offset(p.xs_bytes, p.batch) + p.nslots * kSlotBytes);
+  if (p.kv_heads <= 0 || p.heads % p.kv_heads || p.head_dim != 128 || p.batch < 16 || p.batch > kDenseMaxBatch || p.batch % 16 ||
+      p.hidden > 8192 || p.tp_world > 1 || p.experts > 0 || p.qk_norm)
+    return cudaErrorInvalidValue;
+  const int gq = p.heads / p.kv_heads;
+  if (gq == 4) return run_dense_instance<4>(p, smem_bytes, stream, prepare);
+  if (gq == 8) return run_dense_instance<8>(p, smem_bytes, stream, prepare);
+  return cudaErrorInvalidValue;
+}
+#endif   // TMB_DENSE
+
+#if !TMB_EXTENDED && !TMB_DENSE
 // A two-CTA toy that exercises the bounded-wait path without hanging anything:
 // CTA 1 waits for an arrival CTA 0 is told to withhold; the wait gives up after
 // watchdog_ns, records the site and both CTAs return normally.
@@ -1921,8 +2485,9 @@ static cudaError_t run_batch(const MegaParams& p, size_t smem_bytes, cudaStream_
 // The kernel is instantiated in two translation units (compiled side by side): the plain
 // one serves unsharded dense plans and carries none of the code below; the extended one
 // (TMB_EXTENDED) adds tensor parallelism, mixture of experts and the QK norm, for
-// head_dim 128.
-#if TMB_EXTENDED
+// head_dim 128; a third one (TMB_DENSE) holds the dense-batch kernel.
+#if TMB_DENSE
+#elif TMB_EXTENDED
 cudaError_t run_decode_extended(const MegaParams& p, cudaStream_t stream, bool prepare) {
   const size_t smem_bytes = size_t(ring_offset(p.xs_bytes, p.batch) + p.nslots * kSlotBytes);
   if (p.kv_heads <= 0 || p.heads % p.kv_heads || p.head_dim != 128) return cudaErrorInvalidValue;
@@ -1971,10 +2536,12 @@ cudaError_t run_decode_ranks(const MegaParams& first, const MegaParams* ranks_de
 }
 #else
 cudaError_t run_decode_extended(const MegaParams& p, cudaStream_t stream, bool prepare);
+cudaError_t run_decode_dense(const MegaParams& p, cudaStream_t stream, bool prepare);
 cudaError_t run_decode_ranks(const MegaParams& first, const MegaParams* ranks_dev, int count, int total_grid,
                              cudaStream_t stream);
 
 static cudaError_t run_decode(const MegaParams& p, cudaStream_t stream, bool prepare) {
+  if (p.dense) return run_decode_dense(p, stream, prepare);
   if (p.tp_world > 1 || p.experts > 0 || p.qk_norm) return run_decode_extended(p, stream, prepare);
   const size_t smem_bytes = size_t(ring_offset(p.xs_bytes, p.batch) + p.nslots * kSlotBytes);
   if (p.kv_heads <= 0 || p.heads % p.kv_heads) return cudaErrorInvalidValue;
@@ -1989,7 +2556,7 @@ static cudaError_t run_decode(const MegaParams& p, cudaStream_t stream, bool pre
 
 }  // namespace tmb
 
-#if !TMB_EXTENDED
+#if !TMB_EXTENDED && !TMB_DENSE
 extern "C" int tmb_smem_bytes(const tmb::MegaParams* p) {
   return tmb::ring_offset(p->xs_bytes, p->batch) + p->nslots * tmb::kSlotBytes;
 }

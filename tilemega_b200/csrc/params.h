@@ -16,6 +16,16 @@ constexpr int kMaxBatch = 8;                            // batch rows of the mma
 constexpr int kPartialRing = 8;                         // GEMV tasks whose warp partials may be in flight (> ring slots + 1)
 constexpr int kAttnHalfBytes = kSlotBytes / 2;          // K part, then V part, of an attention slot
 constexpr int kMaxTp = 8;                               // tensor-parallel ranks of one plan
+// Dense-batch plans (batch 16..64, a multiple of 16): the GEMM stages run on the 5th-generation tensor
+// cores. A weight page is 128 rows x 128 columns (two 64-column swizzle blocks of 128 rows x 128 bytes:
+// the K-major 128-byte-swizzled operand layout of tcgen05.mma, which is what the tile_pages recipe
+// writes for tile_n = 128), again one 32 KB ring slot; the batch rows are the N side of the tile.
+constexpr int kDenseTileN = 128;
+constexpr int kDenseTileK = 128;
+constexpr int kDenseMaxBatch = 64;
+constexpr int kDenseXSlots = 3;                         // activation chunks (batch x 128 columns) in flight per CTA
+constexpr int kDenseThreads = kThreads + 32;            // + the warp whose lane 0 loads activations and issues tcgen05.mma
+constexpr int kDenseTmemColumns = 128;                  // two accumulators of up to 64 fp32 columns
 
 // kRouter exists in mixture-of-experts plans only; there kGateUp / kDown describe ONE expert.
 enum StageKind : int { kQkv = 0, kOProj = 1, kGateUp = 2, kDown = 3, kHead = 4, kRouter = 5, kNumGemv = 6 };
@@ -42,6 +52,16 @@ struct GemvGeo {
   // columns into source rows that are src_stride columns apart.
   int page0, task_pages, src_off, src_stride;
   int claim_chunk;     // tasks taken per claim: about 64 KB of pages, so a claim's round trip hides behind the copies
+};
+
+// Geometry of one GEMM stage of a dense-batch plan: `tiles` row tiles of 128 weight rows, the
+// reduction cut into `nsplit` parts of `cps` 128-column chunks each, so that there are enough tasks
+// (tile, part) for every SM to stream; task id = tile * nsplit + part, its pages are contiguous.
+// With nsplit > 1 every task leaves its fp32 partial tile in global memory and the last arriver of a
+// tile adds the parts in ascending order (bit-reproducible) and runs the epilogue.
+struct DenseGeo {
+  int n, k;
+  int tiles, nsplit, cps, ntasks;
 };
 
 struct LayerPtrs {
@@ -86,6 +106,7 @@ struct MegaParams {
   int write_logits;
   int grid, nslots, xs_bytes;
   int attn_min_spt;         // least ring slots of keys per attention task (a task's fixed cost wants amortising)
+  int bars_per_step;        // grid-wide arrivals of one decode step
   int prefetch_window;      // weight pages (over all CTAs) the streaming threads may pull into L2 ahead of the ring while it is full; 0: off
   unsigned long long bar_base;     // grid-barrier arrivals before this launch
   unsigned long long watchdog_ns;  // per-wait limit
@@ -125,6 +146,13 @@ struct MegaParams {
   unsigned long long* step_ns; // [capacity+1] %globaltimer stamps
   unsigned long long* trace;   // [grid][5*layers+1][4] stage stamps of step trace_step, or null
   int trace_step;
+  // dense-batch plans (dense != 0): GEMM stages on tcgen05 tiles
+  int dense;
+  DenseGeo dgeo[kNumGemv];     // indexed by StageKind (kRouter unused)
+  void* xn;                    // bf16 [B][H]: the RMSNorm output a GEMM stage reads
+  float* gemm_part;            // f32 [max tasks][128][B]: partial tiles of split reductions
+  unsigned* gemm_cnt;          // [max tiles]: parts of a tile that have arrived (zero between stages)
+  const void* tmaps;           // three 128-byte tensor maps over [B][K] bf16 rows: 0 xn, 1 attention output, 2 mlp activations
   // tensor parallelism (tp_world == 1: unused). ar[q] / xchg[q] are rank q's receive
   // regions as mapped into this process; a rank stores into its peers' regions and
   // polls its own. Every 8-byte packet carries its epoch, so no flag or fence is needed.

@@ -31,9 +31,48 @@ std::string Alias(const std::string& fqn, const std::string& shard = "") {
 
 // The reference's tile_pages recipe (python/tilemega/serving/weights.py:204-242):
 // [N/tile_n][K/tile_k][tile_n*tile_k] with the 8x64 128-byte XOR swizzle.
-std::string Pages(const std::string& source, int tile_k) {
-  return "{\"kind\":\"tile_pages\",\"tile_n\":" + std::to_string(kTileN) + ",\"tile_k\":" + std::to_string(tile_k) +
+std::string Pages(const std::string& source, int tile_k, int tile_n = kTileN) {
+  return "{\"kind\":\"tile_pages\",\"tile_n\":" + std::to_string(tile_n) + ",\"tile_k\":" + std::to_string(tile_k) +
          ",\"source\":" + source + "}";
+}
+
+// Dense-batch GEMM stage: row tiles of 128, the reduction in 128-column chunks cut into nsplit parts so
+// that there are about two tasks per SM or more (a part keeps at least four chunks, 128 KB of weights).
+DenseGeo MakeDenseGeo(const char* what, int n, int k, int sms) {
+  if (n <= 0 || n % kDenseTileN) throw std::invalid_argument(std::string(what) + ": rows must be a multiple of 128 for a dense-batch plan");
+  if (k <= 0 || k % kDenseTileK) throw std::invalid_argument(std::string(what) + ": K must be a multiple of 128 for a dense-batch plan");
+  DenseGeo g{};
+  g.n = n;
+  g.k = k;
+  g.tiles = n / kDenseTileN;
+  const int chunks = k / kDenseTileK;
+  g.nsplit = 1;
+  for (int d = 1; d <= chunks; ++d) {
+    if (chunks % d || chunks / d < std::min(4, chunks)) continue;
+    g.nsplit = d;
+    if (g.tiles * d >= 2 * sms) break;
+  }
+  g.cps = chunks / g.nsplit;
+  g.ntasks = g.tiles * g.nsplit;
+  if (g.ntasks >= 0xFFFF) throw std::invalid_argument(std::string(what) + ": too many tasks for the task FIFO's 16-bit ids");
+  return g;
+}
+
+// The page stream of a dense-batch stage in the streaming thread's terms: a task is cps consecutive
+// 32 KB pages. (tile_k = 2048 only makes kTileN * tile_k * 2 the page size; the page is 128 x 128.)
+GemvGeo StreamGeo(const DenseGeo& d) {
+  GemvGeo g{};
+  g.n = d.n;
+  g.k = g.k_src = d.k;
+  g.tile_k = 2048;
+  g.pages_per_task = g.task_pages = d.cps;
+  g.last_page_bytes = kSlotBytes;
+  g.ntasks = d.ntasks;
+  g.page0 = 0;
+  g.src_off = 0;
+  g.src_stride = d.k;
+  g.claim_chunk = std::max(1, 65536 / (d.cps * kSlotBytes));
+  return g;
 }
 
 // A reduction length that is not a multiple of the page width is rounded up: the
@@ -146,8 +185,15 @@ PlanSpec PlanSpec::FromJson(const Json& plan) {
   s.batch_hi = int(plan.integer("batch_hi", s.batch_lo));
   if (s.experts && s.batch_hi != 1) throw std::invalid_argument("mixture-of-experts plans are built for batch 1");
   s.capacity = int(plan.integer("capacity", 0));
-  if (s.batch_lo < 1 || s.batch_hi < s.batch_lo || s.batch_hi > kMaxBatch)
-    throw std::invalid_argument("batch interval must lie in [1, 8]");
+  s.dense_batch = s.batch_hi > kMaxBatch;
+  if (s.dense_batch) {
+    if (s.batch_lo <= kMaxBatch || s.batch_hi > kDenseMaxBatch || s.batch_lo % 16 || s.batch_hi % 16 || s.batch_hi < s.batch_lo)
+      throw std::invalid_argument("a dense-batch plan covers batch sizes 16, 32, 48, 64 (interval bounds multiples of 16)");
+    if (s.head_dim != 128 || s.tp != 1 || s.experts || s.qk_norm || s.hidden > 8192)
+      throw std::invalid_argument("dense-batch plans are built for unsharded dense models with head_dim 128 and hidden <= 8192");
+  } else if (s.batch_lo < 1 || s.batch_hi < s.batch_lo) {
+    throw std::invalid_argument("batch interval must lie in [1, 8] (or in [16, 64] in steps of 16 for a dense-batch plan)");
+  }
   if (s.capacity < 2 || s.capacity % kKvBlock) throw std::invalid_argument("capacity must be a positive multiple of 16");
   const Json empty;
   const Json& kv = plan.has("kv") ? plan.at("kv") : empty;
@@ -175,7 +221,15 @@ PlanSpec PlanSpec::FromJson(const Json& plan) {
   // A wide batch times a long down reduction does not fit in shared memory beside the ring
   // (8 rows x 14336 columns are 229 KB): the reduction is then cut into parts of whole pages
   // whose rows take about 80 KB, one stage per part, fp32 running sums in global memory.
-  if (!s.experts) {
+  if (s.dense_batch) {
+    const int sms = 148;   // the task count aims at two per SM of a B200; any grid runs it
+    s.dgeo[kQkv] = MakeDenseGeo("qkv", s.qkv_rows(), s.hidden, sms);
+    s.dgeo[kOProj] = MakeDenseGeo("o", s.hidden, s.heads * s.head_dim, sms);
+    s.dgeo[kGateUp] = MakeDenseGeo("gate_up", 2 * s.inter, s.hidden, sms);
+    s.dgeo[kDown] = MakeDenseGeo("down", s.hidden, s.inter, sms);
+    s.dgeo[kHead] = MakeDenseGeo("lm_head", s.head_rows, s.hidden, sms);
+    for (int g : {kQkv, kOProj, kGateUp, kDown, kHead}) s.geo[g] = StreamGeo(s.dgeo[g]);
+  } else if (!s.experts) {
     const GemvGeo& down = s.geo[kDown];
     const int budget_columns = 81920 / (2 * s.batch_hi) - 8;
     const int part_pages = std::max(1, std::min(down.pages_per_task, budget_columns / down.tile_k));
@@ -223,6 +277,11 @@ PlanSpec PlanSpec::FromJson(const Json& plan) {
   }
   s.embed = add("model.embed_tokens.weight", 1, 0, V * H, 0, Alias("model.embed_tokens.weight"));
   s.hidden_buf = add("serving.hidden", 0, 0, 0, H, "");
+  if (s.dense_batch) s.normed_buf = add("serving.normed", 0, 0, 0, H, "");   // RMSNorm output read by the GEMM stages
+  // weight pages: 8 rows x 2048 columns for the GEMV path, 128 x 128 (a tcgen05 operand tile) for dense-batch plans
+  const int page_n = s.dense_batch ? kDenseTileN : kTileN;
+  auto page_k = [&](int stage) { return s.dense_batch ? kDenseTileK : s.geo[stage].tile_k; };
+  const int swiglu_unit = s.dense_batch ? 16 : 4;   // gate rows followed by as many up rows
   s.qkv_buf = add("serving.qkv", 0, 0, 0, uint64_t(s.qkv_rows()), "");
   s.attn_buf = add("serving.attention", 0, 0, 0, uint64_t(s.heads) * D, "");
   // with experts: one row per chosen expert (batch 1)
@@ -245,7 +304,7 @@ PlanSpec PlanSpec::FromJson(const Json& plan) {
         ",\"hkv\":" + std::to_string(s.kv_heads) + ",\"qperkv\":" + std::to_string(s.heads / s.kv_heads) +
         ",\"head_dim\":" + std::to_string(s.head_dim) + Shard(0, s.tp) + "}";
     lb.qkv = add(p + "qkv.weight", 1, 0, uint64_t(s.geo[kQkv].n) * s.geo[kQkv].k, 0,
-                 Pages(qkv_source, s.geo[kQkv].tile_k));
+                 Pages(qkv_source, page_k(kQkv), page_n));
     if (s.paged) {
       const uint64_t pool = uint64_t(s.num_blocks) * s.kv_heads * kKvBlock * D;
       lb.k = add("kv_pool.k." + std::to_string(l), 1, 0, pool, 0, "");
@@ -256,7 +315,7 @@ PlanSpec PlanSpec::FromJson(const Json& plan) {
       lb.v = add("kv_cache.v." + std::to_string(l), 1, 0, 0, cache, "");
     }
     lb.o = add(p + "o.weight", 1, 0, uint64_t(s.geo[kOProj].n) * s.geo[kOProj].k, 0,
-               Pages(Alias(m + "self_attn.o_proj.weight", Shard(1, s.tp)), s.geo[kOProj].tile_k));
+               Pages(Alias(m + "self_attn.o_proj.weight", Shard(1, s.tp)), page_k(kOProj), page_n));
     lb.norm2 = add(p + "norm2.weight", 1, 0, H, 0, Alias(m + "post_attention_layernorm.weight"));
     if (s.qk_norm) {
       lb.q_norm = add(p + "q_norm.weight", 1, 0, D, 0, Alias(m + "self_attn.q_norm.weight"));
@@ -281,16 +340,16 @@ PlanSpec PlanSpec::FromJson(const Json& plan) {
     }
     const std::string gate_up_source = "{\"kind\":\"gate_up_interleave\",\"sources\":" +
                                        Sources({m + "mlp.gate_proj.weight", m + "mlp.up_proj.weight"}) +
-                                       ",\"u\":4" + Shard(0, s.tp) + "}";
+                                       ",\"u\":" + std::to_string(swiglu_unit) + Shard(0, s.tp) + "}";
     lb.gate_up = add(p + "gate_up.weight", 1, 0, uint64_t(s.geo[kGateUp].n) * s.geo[kGateUp].k, 0,
-                     Pages(gate_up_source, s.geo[kGateUp].tile_k));
+                     Pages(gate_up_source, page_k(kGateUp), page_n));
     lb.down = add(p + "down.weight", 1, 0, uint64_t(s.geo[kDown].n) * s.geo[kDown].k, 0,
-                  Pages(Alias(m + "mlp.down_proj.weight", Shard(1, s.tp)), s.geo[kDown].tile_k));
+                  Pages(Alias(m + "mlp.down_proj.weight", Shard(1, s.tp)), page_k(kDown), page_n));
     s.layer.push_back(lb);
   }
   s.final_norm = add("model.norm.weight", 1, 0, H, 0, Alias("model.norm.weight"));
   s.lm_head = add("lm_head.weight", 1, 0, uint64_t(s.geo[kHead].n) * s.geo[kHead].k, 0,
-                  Pages(Alias("lm_head.weight", Shard(0, s.tp)), s.geo[kHead].tile_k));
+                  Pages(Alias("lm_head.weight", Shard(0, s.tp)), page_k(kHead), page_n));
   return s;
 }
 

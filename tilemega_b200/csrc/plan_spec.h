@@ -48,6 +48,11 @@ struct PlanSpec {
   int down_splits = 1;
   GemvGeo down_part[kMaxDownSplits] = {};
   GemvGeo geo[kNumGemv] = {};   // stages a plan does not have (kRouter in a dense plan) stay zero
+  // dense-batch plans (batch_hi > kMaxBatch): GEMM stages on tcgen05 tiles; geo[] then describes the
+  // page stream only (one task = cps pages of 128 rows x 128 columns)
+  bool dense_batch = false;
+  DenseGeo dgeo[kNumGemv] = {};
+  int normed_buf = -1;
   // buffer table
   std::vector<BufferSpec> buffers;
   int tokens = -1, rope_cos = -1, rope_sin = -1, block_table = -1, context_base = -1;

@@ -43,23 +43,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// try_wait that may stay suspended for up to `hint_ns` before reporting failure: the
-// hardware wakes the thread when the phase completes, so a long hint costs no
-// latency and keeps a waiting thread from occupying the shared-memory pipeline.
-__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
-  uint32_t ok;
-  asm volatile(
-      "{\n"
-      " .reg .pred p;\n"
-      " mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
-      " selp.u32 %0, 1, 0, p;\n"
-      "}\n"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
-      : "memory");
-  return ok != 0;
-}
-
 // Contiguous global -> shared bulk copy, completion counted in bytes on `bar`.
 // Both addresses 16-byte aligned, size a multiple of 16.
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
@@ -83,18 +66,6 @@ __device__ __forceinline__ void bulk_g2s_hint(void* dst, const void* src, uint32
 // Global -> L2 prefetch of a contiguous range (no shared memory involved).
 __device__ __forceinline__ void bulk_prefetch_l2(const void* src, uint32_t bytes) {
   asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
-}
-
-// Register reallocation between warpgroups (all warps of a warpgroup execute the
-// same instruction): the streaming warpgroup gives registers up, the arithmetic
-// warpgroups take them.
-template <int Regs>
-__device__ __forceinline__ void warpgroup_reg_dec() {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(Regs));
-}
-template <int Regs>
-__device__ __forceinline__ void warpgroup_reg_inc() {
-  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(Regs));
 }
 
 __device__ __forceinline__ uint64_t policy_evict_first() {
@@ -176,14 +147,7 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t sme
                : "r"(smem_addr));
 }
 
-// D[16x8] += A[16x8] * B[8x8] (k = 8), bf16 operands, fp32 accumulators; rows 8..15 of A are zero.
-__device__ __forceinline__ void mma_bf16_m16n8k8(float (&d)[4], uint32_t a0, uint32_t b0) {
-  asm("mma.sync.aligned.m16n8k8.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5}, {%6}, {%0, %1, %2, %3};"
-      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-      : "r"(a0), "r"(0u), "r"(b0));
-}
-
-// The same with all 16 rows of A in use.
+// D[16x8] += A[16x8] * B[8x8] (k = 8), bf16 operands, fp32 accumulators, all 16 rows of A in use.
 __device__ __forceinline__ void mma_bf16_m16n8k8_full(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
   asm("mma.sync.aligned.m16n8k8.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5}, {%6}, {%0, %1, %2, %3};"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
@@ -204,22 +168,6 @@ __device__ __forceinline__ void mma_bf16_m16n8k16(float (&d)[4], uint32_t a0, ui
       : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
 }
 
-// acc += w.lo * x.lo, then acc += w.hi * x.hi, on packed bf16 pairs with the
-// sm_100 mixed-precision FMA (bf16 x bf16 + f32 -> f32, exact product, one
-// rounding): the same result as converting both operands to fp32 first, without
-// the conversion instructions.
-__device__ __forceinline__ void fma_bf16x2(float& acc, uint32_t w, uint32_t x) {
-  asm("{\n"
-      " .reg .b16 a0, a1, b0, b1;\n"
-      " mov.b32 {a0, a1}, %1;\n"
-      " mov.b32 {b0, b1}, %2;\n"
-      " fma.rn.f32.bf16 %0, a0, b0, %0;\n"
-      " fma.rn.f32.bf16 %0, a1, b1, %0;\n"
-      "}\n"
-      : "+f"(acc)
-      : "r"(w), "r"(x));
-}
-
 // Round-to-nearest-even fp32 -> bf16, returned as the fp32 value it represents.
 __device__ __forceinline__ float bf16_round(float x) {
   return __bfloat162float(__float2bfloat16_rn(x));
@@ -230,5 +178,87 @@ __device__ __forceinline__ uint16_t bf16_bits(float x) {
 }
 
 __device__ __forceinline__ float bf16_from_bits(uint16_t b) { return __uint_as_float(uint32_t(b) << 16); }
+
+// ---------------------------------------------------------------------------
+// 5th-generation tensor cores (tcgen05) and tensor memory, for the dense-batch
+// GEMM stages: operands in shared memory (128-byte swizzled, K-major), the fp32
+// accumulator in tensor memory, one thread issues, completion arrives on mbarriers.
+// ---------------------------------------------------------------------------
+
+// Tiled 2-D tensor copy global -> shared through a tensor map (no multicast). `x` is the
+// innermost coordinate in elements and must be a multiple of 8 for 16-bit data.
+__device__ __forceinline__ void tma_load_2d(void* dst, const void* tensor_map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+          smem_u32(dst)),
+      "l"(tensor_map), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
+}
+
+// Tensor memory columns for this CTA (a power of two >= 32); the base address lands in
+// shared memory. Executed by one whole warp, which also frees the columns.
+__device__ __forceinline__ void tmem_alloc(uint32_t* base_in_smem, uint32_t columns) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(base_in_smem)), "r"(columns)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc(uint32_t base, uint32_t columns) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(base), "r"(columns) : "memory");
+}
+
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// Shared-memory operand descriptor: K-major rows of 128 bytes, 128-byte swizzle, 8-row groups
+// `group_bytes` apart (1024 for densely stacked rows). `address` may point 32*j bytes into a
+// swizzle row to select k-step j; the atom it lies in must start on a 1024-byte boundary.
+__device__ __forceinline__ uint64_t umma_desc_k_sw128(uint32_t address, uint32_t group_bytes) {
+  const uint64_t lo = uint64_t((address >> 4) & 0x3FFFu) | (uint64_t(1) << 16);            // start, leading offset (unused: 1)
+  const uint64_t hi = uint64_t((group_bytes >> 4) & 0x3FFFu) | (uint64_t(1) << 14) |       // stride offset, descriptor version 1
+                      (uint64_t(2) << 29);                                                  // layout: 128-byte swizzle
+  return lo | (hi << 32);
+}
+
+// Instruction descriptor of kind::f16: bf16 x bf16 -> fp32, both operands K-major, M x N tile.
+__device__ __forceinline__ uint32_t umma_idesc_bf16(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(n >> 3) << 17) | (uint32_t(m >> 4) << 24);
+}
+
+// D[tmem] (+)= A[smem] * B[smem]^T, issued by ONE thread; `accumulate` = 0 overwrites D.
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      " .reg .pred p;\n"
+      " setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// One arrival on `bar` once every tensor-core operation this thread issued so far is complete.
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// 16 consecutive fp32 columns of this thread's tensor-memory lane (lane = 32 * (warp % 4) + lane id).
+__device__ __forceinline__ void tmem_load_16(uint32_t address, float (&v)[16]) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(address));
+  // the registers are valid only after the wait: naming them as operands of the wait keeps the
+  // compiler from reading them earlier
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]),
+                 "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
+               :
+               : "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
 
 }  // namespace tmb

@@ -2,6 +2,7 @@
 // sidecar, publishes the buffer table, owns the internal device buffers and
 // launches the persistent decode kernel. The reference's counterpart is
 // include/tilemega/Codegen/tasks/Sm90DenseRuntime.cuh:244-559.
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <dlfcn.h>
 
@@ -137,6 +138,61 @@ void Destroy(Plan* plan) {
   delete plan;
 }
 
+// Tiled tensor map over a row-major bf16 matrix [rows][cols]: boxes of `rows` x 64 columns, 128-byte
+// swizzle (what tcgen05.mma expects of a K-major operand). The encoder is the driver's; it is looked
+// up at run time so that the library has no link-time dependency on the driver library.
+const char* EncodeRowsMap(CUtensorMap* map, void* base, uint64_t rows, uint64_t cols) {
+  using Encode = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static Encode encode = nullptr;
+  if (!encode) {
+    void* entry = nullptr;
+    cudaDriverEntryPointQueryResult found{};
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault, &found) != cudaSuccess || !entry ||
+        found != cudaDriverEntryPointSuccess)
+      return "the driver does not offer cuTensorMapEncodeTiled";
+    encode = reinterpret_cast<Encode>(entry);
+  }
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols * 2};
+  const cuuint32_t box[2] = {64, cuuint32_t(rows)};
+  const cuuint32_t steps[2] = {1, 1};
+  const CUresult status = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, steps,
+                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return status == CUDA_SUCCESS ? nullptr : "cuTensorMapEncodeTiled rejected an activation buffer";
+}
+
+// What a dense-batch plan needs beyond the table's buffers: tensor maps over the three activation
+// buffers its GEMM stages read, and the scratch of split reductions. Returns an error text or null.
+const char* BindDense(Plan& plan, const tmb::PlanSpec& s, int batch) {
+  tmb::MegaParams& p = plan.params;
+  p.xn = plan.buffer_ptr[size_t(s.normed_buf)];
+  alignas(64) CUtensorMap maps[3];
+  void* const bases[3] = {p.xn, plan.buffer_ptr[size_t(s.attn_buf)], plan.buffer_ptr[size_t(s.mlp_buf)]};
+  const uint64_t widths[3] = {uint64_t(s.hidden), uint64_t(s.heads) * s.head_dim, uint64_t(s.inter)};
+  for (int i = 0; i < 3; ++i)
+    if (const char* why = EncodeRowsMap(&maps[i], bases[i], uint64_t(batch), widths[i])) return why;
+  static_assert(sizeof(CUtensorMap) == 128, "the kernel addresses the maps 128 bytes apart");
+  void* dev = nullptr;
+  if (Alloc(plan, &dev, sizeof(maps)) != cudaSuccess || cudaMemcpy(dev, maps, sizeof(maps), cudaMemcpyHostToDevice) != cudaSuccess)
+    return "no device memory for the tensor maps";
+  p.tmaps = dev;
+  size_t part_tasks = 1, tiles = 1;
+  for (int g : {tmb::kQkv, tmb::kOProj, tmb::kGateUp, tmb::kDown, tmb::kHead}) {
+    tiles = std::max(tiles, size_t(s.dgeo[g].tiles));
+    if (s.dgeo[g].nsplit > 1) part_tasks = std::max(part_tasks, size_t(s.dgeo[g].ntasks));
+  }
+  void *part = nullptr, *count = nullptr;
+  if (Alloc(plan, &part, part_tasks * tmb::kDenseTileN * size_t(batch) * sizeof(float)) != cudaSuccess ||
+      Alloc(plan, &count, tiles * sizeof(unsigned)) != cudaSuccess)
+    return "no device memory for the split-reduction scratch";
+  p.gemm_part = static_cast<float*>(part);
+  p.gemm_cnt = static_cast<unsigned*>(count);
+  return nullptr;
+}
+
 }  // namespace
 
 extern "C" {
@@ -205,6 +261,10 @@ void* tm_plan_create(int batch, void* const* external, int device) {
       return nullptr;
     }
   }
+  if (s.dense_batch && batch % 16) {
+    Fail(-1, "tm_plan_create: a dense-batch plan runs batch sizes 16, 32, 48 or 64");
+    return nullptr;
+  }
   DeviceScope scope(device);
   cudaDeviceProp prop{};
   if (cudaGetDeviceProperties(&prop, device) != cudaSuccess || prop.major < 10) {
@@ -247,6 +307,11 @@ void* tm_plan_create(int batch, void* const* external, int device) {
   p.norm_topk = s.norm_topk ? 1 : 0;
   p.qk_norm = s.qk_norm ? 1 : 0;
   p.stages_per_layer = s.stages_per_layer();
+  p.dense = s.dense_batch ? 1 : 0;
+  // grid-wide arrivals of a step: one per stage except QKV (attention tasks wait per KV-head group)
+  // plus the argmax hand-over; a dense-batch plan's RMSNorm stages arrive too
+  p.bars_per_step = s.dense_batch ? 6 * s.layers + 2 : (s.stages_per_layer() - 1) * s.layers + 1;
+  for (int g = 0; g < tmb::kNumGemv; ++g) p.dgeo[g] = s.dgeo[g];
   p.eps = float(s.eps);
   p.qk_scale_log2 = float(1.4426950408889634 / std::sqrt(double(s.head_dim)));
   p.capacity = s.capacity;
@@ -276,12 +341,15 @@ void* tm_plan_create(int batch, void* const* external, int device) {
   // (batch > 4: the rows are normalised in a second pass over global memory instead: batch + 1 rows)
   int xs = std::max({batch * (s.max_k() + 8) * 2, (batch > 4 ? batch + 1 : 2 * batch + 1) * (s.geo[tmb::kQkv].k + 8) * 2, attention_scratch,
                      expert_rows});
-  xs = (xs + 127) & ~127;
+  // dense-batch: the activation chunks of the GEMM stages (batch x 128 columns each) share the area
+  // with the attention scratch; chunks must start on 1024-byte boundaries (128-byte swizzle)
+  if (s.dense_batch) xs = std::max(attention_scratch, tmb::kDenseXSlots * batch * tmb::kDenseTileK * 2);
+  xs = s.dense_batch ? (xs + 1023) & ~1023 : (xs + 127) & ~127;
   p.xs_bytes = xs;
   p.attn_min_spt = s.attn_min_slots;
   // the idle prefetch walks the dense stage sequence QKV, O, gate/up, down, head: plans whose weight
   // stream is not that (chosen experts, a down projection cut into parts) run without it
-  p.prefetch_window = (s.experts || s.down_splits > 1) ? 0 : s.prefetch_window;
+  p.prefetch_window = (s.experts || s.down_splits > 1 || s.dense_batch) ? 0 : s.prefetch_window;
   const int limit = int(prop.sharedMemPerBlockOptin);
   p.nslots = tmb::kMaxSlots;
   if (s.slots > 0) p.nslots = std::min(s.slots, tmb::kMaxSlots);
@@ -389,6 +457,12 @@ void* tm_plan_create(int batch, void* const* external, int device) {
   p.attn_cnt = reinterpret_cast<unsigned*>(plan->sync_block + 128);
   p.qkv_ready = reinterpret_cast<unsigned long long*>(plan->sync_block + ready_offset);
   p.stage_cnt = reinterpret_cast<unsigned*>(plan->sync_block + plan->claim_offset);
+  if (s.dense_batch) {
+    if (const char* why = BindDense(*plan, s, batch)) {
+      Fail(-1, std::string("tm_plan_create: ") + why);
+      return nullptr;
+    }
+  }
   p.down_partial = static_cast<float*>(down_partial);
   p.attn_part = static_cast<float*>(attn_part);
   p.argmax_val = static_cast<float*>(argmax_val);
@@ -601,6 +675,7 @@ int tm_plan_watchdog_probe(void* handle, int withhold, uint32_t limit_us, void* 
 int tm_plan_trace_step(void* handle, int step) {
   Plan* plan = AsPlan(handle);
   if (!plan) return Fail(-1, "tm_plan_trace_step: bad plan");
+  if (plan->params.dense && step >= 0) return Fail(-3, "tm_plan_trace_step: the dense-batch kernel records no stage trace");
   DeviceScope scope(plan->device);
   if (step >= 0 && !plan->trace_dev) {
     plan->trace_bytes = size_t(plan->params.grid) * (size_t(plan->params.stages_per_layer) * size_t(plan->params.layers) + 1) * 4 *

@@ -37,8 +37,11 @@ def plan_document(config: dict, *, batch_lo: int = 1, batch_hi: int | None = Non
     model.setdefault("head_dim", config["hidden_size"] // config["num_attention_heads"])
     model.setdefault("rms_norm_eps", 1e-5)
     batch_hi = batch_lo if batch_hi is None else batch_hi
-    if not 1 <= batch_lo <= batch_hi <= 8:
-        raise ValueError("batch interval must lie in [1, 8]")
+    dense_batch = batch_hi > 8   # batch 16..64: the GEMM stages run on tcgen05 tiles, weight pages are 128 x 128
+    if dense_batch and (batch_lo <= 8 or batch_hi > 64 or batch_lo % 16 or batch_hi % 16 or batch_lo > batch_hi):
+        raise ValueError("a dense-batch plan covers batch sizes 16, 32, 48, 64 (interval bounds multiples of 16)")
+    if not dense_batch and not 1 <= batch_lo <= batch_hi:
+        raise ValueError("batch interval must lie in [1, 8], or in [16, 64] in steps of 16")
     if capacity < 16 or capacity % 16:
         raise ValueError("capacity must be a positive multiple of the KV block (16)")
     if kv_layout not in ("contiguous", "paged"):

@@ -75,6 +75,7 @@ SIGNATURES = {
     "tm_plan_trace_step": (_I, [_P, _I], False),
     "tm_plan_read_trace": (C.c_longlong, [_P, C.POINTER(_U64), _U64], False),
     "tm_pack_tile_pages": (_I, [_P, _U64, _U64, _U64, _U32, _U32, _P, _P], False),
+    "tm_calibrate": (_I, [_I, C.c_char_p, C.POINTER(C.c_double), _I], False),
     "tm_watchdog_probe_static": (_I, [_I, _I, _I, _U32, _P, _P], False),
     "tm_ipc_alloc": (_I, [_I, _U64, C.POINTER(_P)], False),
     "tm_ipc_free": (_I, [_P], False),
