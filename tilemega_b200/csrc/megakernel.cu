@@ -193,6 +193,9 @@ __device__ __forceinline__ bool mbar_wait_warp(Ctx& c, uint64_t* bar, uint32_t p
 
 // Arrive on the grid-wide counter: this CTA's stage outputs are in global memory.
 __device__ __forceinline__ void grid_arrive(Ctx& c) {
+  // dense-batch plans: the next stage reads this stage's rows with the copy engine (async proxy), so
+  // every thread first orders its own ordinary stores before that proxy
+  if (c.p.dense) fence_proxy_async();
   consumer_sync();
   if (c.tid == 0) {
     __threadfence();
@@ -2273,22 +2276,31 @@ __device__ void consumer_main_dense(Ctx& c) {
     for (int l = 0; l < p.layers; ++l) {
       const LayerPtrs lp = p.layer[l];
       GemvIo io;
+      // Every stage starts with the wait for the previous stage's arrivals, also where the epilogue
+      // warps would be held back by their accumulators anyway: the arrival counter is one monotonic
+      // count, so a CTA (one without tasks in a stage, say) must never arrive for stage n+1 before it
+      // has seen every CTA's arrival for stage n.
       if (l > 0 && !grid_wait(c)) return;                      // the previous layer's down projection is complete
       norm_stage_dense(c, l == 0 ? p.embed : p.x, lp.norm1, l == 0);
       grid_arrive(c);
+      if (!grid_wait(c)) return;
       io = GemvIo{nullptr, nullptr, 0, kEpiStore, p.qkv, p.qkv_ready, (GQ + 2) * D / kDenseTileN, nullptr, 0, 0u};
       gemm_epilogue_stage(c, p.dgeo[kQkv], io, seq);
+      // no arrival here: an attention task waits for the QKV rows of its own KV head only
       attn_stage<1, D, GQ, 0>(c, lp, past, false, 0, (unsigned long long)(si * p.layers + l + 1));
       grid_arrive(c);
+      if (!grid_wait(c)) return;
       io = GemvIo{nullptr, nullptr, 0, kEpiResidual, p.x, nullptr, 1, nullptr, 0, 0u};
       gemm_epilogue_stage(c, p.dgeo[kOProj], io, seq);
       grid_arrive(c);
       if (!grid_wait(c)) return;                               // the residual stream after attention is complete
       norm_stage_dense(c, p.x, lp.norm2, false);
       grid_arrive(c);
+      if (!grid_wait(c)) return;
       io = GemvIo{nullptr, nullptr, 0, kEpiSwiGLU, p.h, nullptr, 1, nullptr, 0, 0u};
       gemm_epilogue_stage(c, p.dgeo[kGateUp], io, seq);
       grid_arrive(c);
+      if (!grid_wait(c)) return;
       io = GemvIo{nullptr, nullptr, 0, kEpiResidual, p.x, nullptr, 1, nullptr, 0, 0u};
       gemm_epilogue_stage(c, p.dgeo[kDown], io, seq);
       grid_arrive(c);
@@ -2296,6 +2308,7 @@ __device__ void consumer_main_dense(Ctx& c) {
     if (!grid_wait(c)) return;
     norm_stage_dense(c, p.x, p.final_norm, false);
     grid_arrive(c);
+    if (!grid_wait(c)) return;
     // lm_head: every warp keeps a running (value, index) per batch row
     float* best_val = reinterpret_cast<float*>(c.smem + kOffDBestVal);
     int* best_idx = reinterpret_cast<int*>(c.smem + kOffDBestIdx);
