@@ -85,7 +85,10 @@ def check_every_stage(config, batch, history, plan_dir):
     q = F.linear(xn, w[p + "self_attn.q_proj.weight"]).view(batch, hkv, gq, dim)
     k = F.linear(xn, w[p + "self_attn.k_proj.weight"]).view(batch, hkv, 1, dim)
     v = F.linear(xn, w[p + "self_attn.v_proj.weight"]).view(batch, hkv, 1, dim)
-    agreement(qkv_gpu, torch.cat((q, k, v), dim=2), "qkv")
+    # (a handful of elements per hundred thousand may sit two steps apart: the CPU's bf16 GEMM and the GPU
+    # sum 2048+ products in different orders and block sizes)
+    reference_qkv = torch.cat((q, k, v), dim=2)
+    agreement(qkv_gpu, reference_qkv, "qkv", outliers=2e-5, outlier_bound=2 * bf16_ulp(reference_qkv.float().abs().max()).item())
     # stage 2: RoPE, KV append, attention -- from the qkv the GPU produced
     cos, sin = rope_tables(config, capacity, torch.bfloat16)
     q_gpu, k_gpu, v_gpu = qkv_gpu[:, :, :gq], qkv_gpu[:, :, gq], qkv_gpu[:, :, gq + 1]

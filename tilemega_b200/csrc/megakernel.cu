@@ -70,6 +70,7 @@ constexpr int kOffDFifo = 3392;      // int[kFifo] GEMM tasks for the issuing th
 constexpr int kOffDTok = 3520;       // int[kDenseMaxBatch]
 constexpr int kOffDBestVal = 3840;   // float[8 warps][kDenseMaxBatch]
 constexpr int kOffDBestIdx = 5888;   // int[8 warps][kDenseMaxBatch]
+constexpr int kOffDWEmpty = 7936;    // u64[8] ring slot released by the tensor cores (one arrival: tcgen05.commit)
 constexpr int kOffDenseXs = 8192;
 // Features compiled into an instantiation of the kernel (template parameter X): the plain
 // one (0) serves unsharded dense plans and carries neither.
@@ -98,6 +99,10 @@ struct Ctx {
   uint32_t gemv_seq;                 // GEMV tasks finished by this CTA (partial-sum ring cursor)
   uint32_t route_phase;              // routings published (arithmetic warps) / consumed (streaming thread), mod 2
   uint32_t dq_pos;                   // dense plans: GEMM FIFO entries pushed (streaming thread) / popped (issuing thread)
+  // dense plans, streaming thread: a slot is released through one of two barriers, by the eight arithmetic
+  // warps when it held keys, by one tcgen05.commit when it held a weight page. Per slot: was it filled at
+  // all, did it last hold a weight page, and the parity of the next release through either barrier.
+  uint32_t slot_used, slot_gemm, parity_warps, parity_mma;
   // streaming thread: where it is in the launch's sequence of weight pages, and how far ahead of
   // that it has prefetched into L2 (absolute page numbers count every GEMV stage's pages in program order)
   int cur_seq, cur_npages, cur_ppt, cur_task;   // GEMV stage being streamed: its number, pages, pages per task, last task posted
@@ -106,7 +111,7 @@ struct Ctx {
   __device__ Ctx(const MegaParams& q, unsigned char* s, int cta_index)
       : p(q), smem(s), warp(threadIdx.x >> 5), lane(threadIdx.x & 31), tid(threadIdx.x), cta(cta_index), slot(0), phase(0),
         bar_target(q.bar_base), task_seq(0), dead(false), q_pos(0), inst(0), pending(0), pending_next(0), gemv_seq(0),
-        route_phase(0), dq_pos(0), cur_seq(-1), cur_npages(0), cur_ppt(1), cur_task(0), pf_seq(0), cur_abs_base(0), pf_abs(-1),
+        route_phase(0), dq_pos(0), slot_used(0), slot_gemm(0), parity_warps(0), parity_mma(0), cur_seq(-1), cur_npages(0), cur_ppt(1), cur_task(0), pf_seq(0), cur_abs_base(0), pf_abs(-1),
         pf_abs_base(0) {}
   __device__ uint64_t* full(int i) const { return reinterpret_cast<uint64_t*>(smem + kOffFull) + i; }
   __device__ uint64_t* empty(int i) const { return reinterpret_cast<uint64_t*>(smem + kOffEmpty) + i; }
@@ -227,8 +232,7 @@ __device__ __forceinline__ bool grid_wait(Ctx& c) {
 // (include/tilemega/Codegen/tasks/ModelRuntime.h:758-766).
 __device__ __forceinline__ void trace_mark(const Ctx& c, bool on, int stage, int what) {
   if (on && c.tid == 0) {
-    const int stages = c.p.stages_per_layer * c.p.layers + 1;
-    c.p.trace[(size_t(c.cta) * stages + stage) * 4 + what] = global_timer();
+    c.p.trace[(size_t(c.cta) * c.p.trace_stages + stage) * 4 + what] = global_timer();
   }
 }
 
@@ -426,7 +430,24 @@ static __device__ __noinline__ PrefetchCursor idle_prefetch(const MegaParams& p,
   return cur;
 }
 
-__device__ __forceinline__ bool stream_wait_empty(Ctx& c) {
+__device__ __forceinline__ bool stream_wait_empty(Ctx& c, bool weight_page = true) {
+  if (c.p.dense) {
+    // wait for the release that matches what the slot held, then note what it is about to hold
+    const uint32_t bit = 1u << c.slot;
+    bool ok = true;
+    if (c.slot_used & bit) {
+      if (c.slot_gemm & bit) {
+        ok = mbar_wait(c, reinterpret_cast<uint64_t*>(c.smem + kOffDWEmpty) + c.slot, (c.parity_mma >> c.slot) & 1u, kSiteEmpty);
+        c.parity_mma ^= bit;
+      } else {
+        ok = mbar_wait(c, c.empty(c.slot), (c.parity_warps >> c.slot) & 1u, kSiteEmpty);
+        c.parity_warps ^= bit;
+      }
+    }
+    c.slot_used |= bit;
+    c.slot_gemm = weight_page ? (c.slot_gemm | bit) : (c.slot_gemm & ~bit);
+    return ok;
+  }
   if (c.p.prefetch_window > 0 && !c.dead) {
     while (!mbar_try_wait(c.empty(c.slot), c.phase ^ 1u)) {
       const long long here = c.cur_abs_base + (long long)c.cur_task * c.cur_ppt;
@@ -597,7 +618,7 @@ __device__ __forceinline__ void stream_attn(Ctx& c, const LayerPtrs& lp, int pas
         const long long e = table_entry(c.p, a.b, s * NB + min(j, max(nb - 1, 0)));
         off[j] = (e * c.p.kv_block_stride + (long long)a.g * c.p.kv_head_stride) * 2;
       }
-      if (!stream_wait_empty(c)) break;
+      if (!stream_wait_empty(c, false)) break;
       if (nb) mbar_expect_tx(c.full(c.slot), uint32_t(nb) * 2u * BLKB);
       else mbar_arrive(c.full(c.slot));
       unsigned char* dst = c.ring(c.slot);
@@ -1967,8 +1988,9 @@ __device__ __forceinline__ int dfifo_pop(Ctx& c, uint32_t& slot, uint32_t& phase
 
 struct MmaState {
   uint32_t tmem, idesc;
-  uint32_t x_loaded, x_used;   // activation chunks loaded / consumed by this CTA so far (slot = n % kDenseXSlots)
-  uint32_t task_seq;           // GEMM tasks issued by this CTA (accumulator = task_seq & 1)
+  uint32_t nx;                                             // activation chunk slots in use (as many of 4 as fit 48 KB)
+  uint32_t x_load_slot, x_load_phase, x_use_slot, x_use_phase;   // activation ring: next slot to fill / to consume
+  uint32_t task_seq;                                       // GEMM tasks issued by this CTA (accumulator = task_seq & 1)
 };
 
 // One GEMM stage, issuing side. `arrivals`: grid-wide arrivals (counted from the start of the launch)
@@ -1991,10 +2013,14 @@ __device__ __forceinline__ bool mma_stage(Ctx& c, MmaState& st, const DenseGeo& 
   const uint32_t chunk_bytes = uint32_t(p.batch) * kDenseTileK * 2u;
   const uint32_t block_bytes = uint32_t(p.batch) * 128u;   // one 64-column swizzle block of the batch rows
   unsigned char* const xring = c.smem + kOffDenseXs;
+  const uint32_t nx = st.nx;
+  // operand descriptors differ from a slot's base descriptor by the byte offset >> 4 only (shared memory
+  // addresses have 18 bits, the field 14): k-step ks of swizzle block cb lies cb * block + 32 * ks bytes in
+  const uint64_t desc_hi = umma_desc_k_sw128(0u, 1024u);
   uint32_t slot = 0, phase = 0;
   for (int t = dfifo_pop(c, slot, phase); t >= 0; t = dfifo_pop(c, slot, phase)) {
     const int part = t % g.nsplit;
-    const int k0 = part * g.cps * kDenseTileK;
+    const int block0 = part * g.cps * (kDenseTileK / 64);   // first 64-column block of this part of the reduction
     const uint32_t buf = st.task_seq & 1u;
     // the accumulator's previous tile (two tasks ago) must have been read out
     if (!mbar_wait(c, dbar(c, kOffDAccEmpty, buf), ((st.task_seq >> 1) & 1u) ^ 1u, kSiteEmpty)) return false;
@@ -2002,36 +2028,29 @@ __device__ __forceinline__ bool mma_stage(Ctx& c, MmaState& st, const DenseGeo& 
     const uint32_t d_tmem = st.tmem + buf * uint32_t(kDenseMaxBatch);
     int loaded = 0;
     for (int i = 0; i < g.cps; ++i) {
-      // keep up to kDenseXSlots activation chunks of this task in flight
-      while (loaded < g.cps && loaded < i + kDenseXSlots) {
-        const uint32_t xs = st.x_loaded % kDenseXSlots, xphase = (st.x_loaded / kDenseXSlots) & 1u;
-        if (!mbar_wait(c, dbar(c, kOffDXEmpty, xs), xphase ^ 1u, kSiteEmpty)) return false;
-        mbar_expect_tx(dbar(c, kOffDXFull, xs), chunk_bytes);
-        unsigned char* dst = xring + xs * chunk_bytes;
-        tma_load_2d(dst, tensor_map, k0 + loaded * kDenseTileK, 0, dbar(c, kOffDXFull, xs));
-        tma_load_2d(dst + block_bytes, tensor_map, k0 + loaded * kDenseTileK + 64, 0, dbar(c, kOffDXFull, xs));
-        ++st.x_loaded;
+      // keep up to nx activation chunks of this task in flight
+      while (loaded < g.cps && loaded < i + int(nx)) {
+        if (!mbar_wait(c, dbar(c, kOffDXEmpty, st.x_load_slot), st.x_load_phase ^ 1u, kSiteEmpty)) return false;
+        mbar_expect_tx(dbar(c, kOffDXFull, st.x_load_slot), chunk_bytes);
+        tma_load_3d(xring + st.x_load_slot * chunk_bytes, tensor_map, 0, 0, block0 + 2 * loaded, dbar(c, kOffDXFull, st.x_load_slot));
+        if (++st.x_load_slot == nx) { st.x_load_slot = 0; st.x_load_phase ^= 1u; }
         ++loaded;
       }
-      const uint32_t xs = st.x_used % kDenseXSlots, xphase = (st.x_used / kDenseXSlots) & 1u;
       if (!mbar_wait(c, c.full(slot), phase, kSiteFull)) return false;
-      if (!mbar_wait(c, dbar(c, kOffDXFull, xs), xphase, kSiteFull)) return false;
+      if (!mbar_wait(c, dbar(c, kOffDXFull, st.x_use_slot), st.x_use_phase, kSiteFull)) return false;
       tcgen05_fence_after();
-      const uint32_t w_addr = smem_u32(c.ring(slot)), x_addr = smem_u32(xring + xs * chunk_bytes);
+      const uint64_t a0 = desc_hi + (smem_u32(c.ring(slot)) >> 4);
+      const uint64_t b0 = desc_hi + (smem_u32(xring + st.x_use_slot * chunk_bytes) >> 4);
 #pragma unroll
       for (int cb = 0; cb < 2; ++cb) {
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-          const uint64_t a = umma_desc_k_sw128(w_addr + cb * (kDenseTileN * 128) + ks * 32, 1024);
-          const uint64_t b = umma_desc_k_sw128(x_addr + cb * block_bytes + ks * 32, 1024);
-          umma_bf16(d_tmem, a, b, st.idesc, (i | cb | ks) != 0 ? 1u : 0u);
-        }
+        for (int ks = 0; ks < 4; ++ks)
+          umma_bf16(d_tmem, a0 + ((cb * (kDenseTileN * 128) + ks * 32) >> 4), b0 + ((cb * block_bytes + ks * 32) >> 4), st.idesc,
+                    (i | cb | ks) != 0 ? 1u : 0u);
       }
-      // the slot's release barrier counts the eight arithmetic warps of an attention stage: eight arrivals
-#pragma unroll
-      for (int r = 0; r < kConsumerWarps; ++r) umma_commit(c.empty(slot));
-      umma_commit(dbar(c, kOffDXEmpty, xs));
-      ++st.x_used;
+      umma_commit(dbar(c, kOffDWEmpty, slot));                 // the weight page's slot, back to the streaming thread
+      umma_commit(dbar(c, kOffDXEmpty, st.x_use_slot));
+      if (++st.x_use_slot == nx) { st.x_use_slot = 0; st.x_use_phase ^= 1u; }
       if (++slot == uint32_t(p.nslots)) { slot = 0; phase ^= 1u; }
     }
     umma_commit(dbar(c, kOffDAccFull, buf));
@@ -2046,7 +2065,8 @@ __device__ void mma_main_dense(Ctx& c) {
   MmaState st;
   st.tmem = *reinterpret_cast<volatile uint32_t*>(c.smem + kOffDTmem);
   st.idesc = umma_idesc_bf16(kDenseTileN, p.batch);
-  st.x_loaded = st.x_used = st.task_seq = 0;
+  st.nx = uint32_t(dense_x_slots(p.batch));
+  st.x_load_slot = st.x_load_phase = st.x_use_slot = st.x_use_phase = st.task_seq = 0;
   const unsigned char* maps = static_cast<const unsigned char*>(p.tmaps);
   bool alive = true;
   for (int si = 0; si < p.nsteps && alive; ++si) {
@@ -2205,15 +2225,16 @@ __device__ void gemm_epilogue_stage(Ctx& c, const DenseGeo& g, const GemvIo& io,
         dense_epilogue_16(c, g, io, v, 16 * j, row, tile);
       }
     } else {
-      // this part's fp32 tile goes to global memory; the last part to arrive adds all parts in
-      // ascending order (so the sum does not depend on arrival order) and runs the epilogue
-      float* mine = p.gemm_part + (size_t(t) * kDenseTileN + m) * p.batch;
+      // this part's fp32 tile goes to global memory, laid out [batch row][weight row] so that a warp's
+      // accesses are one 128-byte line each; the last part to arrive adds all parts in ascending
+      // order (so the sum does not depend on arrival order) and runs the epilogue
+      const size_t tile_floats = size_t(kDenseTileN) * p.batch;
+      float* mine = p.gemm_part + size_t(t) * tile_floats + m;
       for (int j = 0; j < nb; ++j) {
         float v[16];
         tmem_load_16(taddr + 16 * j, v);
 #pragma unroll
-        for (int q = 0; q < 4; ++q)
-          reinterpret_cast<float4*>(mine + 16 * j)[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+        for (int e = 0; e < 16; ++e) mine[size_t(16 * j + e) * kDenseTileN] = v[e];
       }
       tcgen05_fence_before();
       __syncwarp();
@@ -2231,17 +2252,25 @@ __device__ void gemm_epilogue_stage(Ctx& c, const DenseGeo& g, const GemvIo& io,
       group_sync(group);   // everyone has read the flag before the next task may overwrite it
       if (!last) continue;
       __threadfence();
-      const float* parts = p.gemm_part + (size_t(tile) * g.nsplit * kDenseTileN + m) * p.batch;
+      const float* parts = p.gemm_part + size_t(tile) * g.nsplit * tile_floats + m;
       for (int j = 0; j < nb; ++j) {
         float v[16];
 #pragma unroll
         for (int e = 0; e < 16; ++e) v[e] = 0.f;
-        for (int part = 0; part < g.nsplit; ++part) {
-          const float4* src = reinterpret_cast<const float4*>(parts + size_t(part) * kDenseTileN * p.batch + 16 * j);
+        // two parts' loads in flight together (32 per thread, each a full line per warp), added in ascending order
+        for (int part0 = 0; part0 < g.nsplit; part0 += 2) {
+          float x[2][16];
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const float4 x = __ldcg(src + q);
-            v[4 * q] += x.x; v[4 * q + 1] += x.y; v[4 * q + 2] += x.z; v[4 * q + 3] += x.w;
+          for (int pp = 0; pp < 2; ++pp) {
+            const bool live = part0 + pp < g.nsplit;
+            const float* src = parts + size_t(live ? part0 + pp : part0) * tile_floats + size_t(16 * j) * kDenseTileN;
+#pragma unroll
+            for (int e = 0; e < 16; ++e) x[pp][e] = live ? __ldcg(src + size_t(e) * kDenseTileN) : 0.f;
+          }
+#pragma unroll
+          for (int pp = 0; pp < 2; ++pp) {
+#pragma unroll
+            for (int e = 0; e < 16; ++e) v[e] += x[pp][e];
           }
         }
         dense_epilogue_16(c, g, io, v, 16 * j, row, tile);
@@ -2273,6 +2302,8 @@ __device__ void consumer_main_dense(Ctx& c) {
       consumer_sync();
     }
     if (c.cta == 0 && c.tid == 0) p.step_ns[step] = global_timer();
+    const bool tr = p.trace != nullptr && step == p.trace_step;
+    int stage = 0;
     for (int l = 0; l < p.layers; ++l) {
       const LayerPtrs lp = p.layer[l];
       GemvIo io;
@@ -2280,35 +2311,68 @@ __device__ void consumer_main_dense(Ctx& c) {
       // warps would be held back by their accumulators anyway: the arrival counter is one monotonic
       // count, so a CTA (one without tasks in a stage, say) must never arrive for stage n+1 before it
       // has seen every CTA's arrival for stage n.
+      trace_mark(c, tr, stage, 0);
       if (l > 0 && !grid_wait(c)) return;                      // the previous layer's down projection is complete
+      trace_mark(c, tr, stage, 1);
+      trace_mark(c, tr, stage, 2);
       norm_stage_dense(c, l == 0 ? p.embed : p.x, lp.norm1, l == 0);
+      trace_mark(c, tr, stage++, 3);
       grid_arrive(c);
+      trace_mark(c, tr, stage, 0);
       if (!grid_wait(c)) return;
+      trace_mark(c, tr, stage, 1);
+      trace_mark(c, tr, stage, 2);
       io = GemvIo{nullptr, nullptr, 0, kEpiStore, p.qkv, p.qkv_ready, (GQ + 2) * D / kDenseTileN, nullptr, 0, 0u};
       gemm_epilogue_stage(c, p.dgeo[kQkv], io, seq);
+      trace_mark(c, tr, stage++, 3);
       // no arrival here: an attention task waits for the QKV rows of its own KV head only
-      attn_stage<1, D, GQ, 0>(c, lp, past, false, 0, (unsigned long long)(si * p.layers + l + 1));
+      trace_mark(c, tr, stage, 0);
+      trace_mark(c, tr, stage, 1);
+      attn_stage<1, D, GQ, 0>(c, lp, past, tr, stage++, (unsigned long long)(si * p.layers + l + 1));
       grid_arrive(c);
+      trace_mark(c, tr, stage, 0);
       if (!grid_wait(c)) return;
+      trace_mark(c, tr, stage, 1);
+      trace_mark(c, tr, stage, 2);
       io = GemvIo{nullptr, nullptr, 0, kEpiResidual, p.x, nullptr, 1, nullptr, 0, 0u};
       gemm_epilogue_stage(c, p.dgeo[kOProj], io, seq);
+      trace_mark(c, tr, stage++, 3);
       grid_arrive(c);
+      trace_mark(c, tr, stage, 0);
       if (!grid_wait(c)) return;                               // the residual stream after attention is complete
+      trace_mark(c, tr, stage, 1);
+      trace_mark(c, tr, stage, 2);
       norm_stage_dense(c, p.x, lp.norm2, false);
+      trace_mark(c, tr, stage++, 3);
       grid_arrive(c);
+      trace_mark(c, tr, stage, 0);
       if (!grid_wait(c)) return;
+      trace_mark(c, tr, stage, 1);
+      trace_mark(c, tr, stage, 2);
       io = GemvIo{nullptr, nullptr, 0, kEpiSwiGLU, p.h, nullptr, 1, nullptr, 0, 0u};
       gemm_epilogue_stage(c, p.dgeo[kGateUp], io, seq);
+      trace_mark(c, tr, stage++, 3);
       grid_arrive(c);
+      trace_mark(c, tr, stage, 0);
       if (!grid_wait(c)) return;
+      trace_mark(c, tr, stage, 1);
+      trace_mark(c, tr, stage, 2);
       io = GemvIo{nullptr, nullptr, 0, kEpiResidual, p.x, nullptr, 1, nullptr, 0, 0u};
       gemm_epilogue_stage(c, p.dgeo[kDown], io, seq);
+      trace_mark(c, tr, stage++, 3);
       grid_arrive(c);
     }
+    trace_mark(c, tr, stage, 0);
     if (!grid_wait(c)) return;
+    trace_mark(c, tr, stage, 1);
+    trace_mark(c, tr, stage, 2);
     norm_stage_dense(c, p.x, p.final_norm, false);
+    trace_mark(c, tr, stage++, 3);
     grid_arrive(c);
+    trace_mark(c, tr, stage, 0);
     if (!grid_wait(c)) return;
+    trace_mark(c, tr, stage, 1);
+    trace_mark(c, tr, stage, 2);
     // lm_head: every warp keeps a running (value, index) per batch row
     float* best_val = reinterpret_cast<float*>(c.smem + kOffDBestVal);
     int* best_idx = reinterpret_cast<int*>(c.smem + kOffDBestIdx);
@@ -2319,6 +2383,7 @@ __device__ void consumer_main_dense(Ctx& c) {
     consumer_sync();
     GemvIo io{nullptr, nullptr, 0, kEpiHead, p.logits, nullptr, 1, nullptr, 0, 0u};
     gemm_epilogue_stage(c, p.dgeo[kHead], io, seq);
+    trace_mark(c, tr, stage, 3);
     consumer_sync();
     if (c.tid < B) {
       float bv = -INFINITY;
@@ -2379,6 +2444,7 @@ __global__ void __launch_bounds__(kDenseThreads, 1) dense_megakernel(const __gri
       mbar_init(dbar(c, kOffDXFull, i), 1);
       mbar_init(dbar(c, kOffDXEmpty, i), 1);
     }
+    for (int i = 0; i < p.nslots; ++i) mbar_init(dbar(c, kOffDWEmpty, i), 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(dbar(c, kOffDAccFull, i), 1);
       mbar_init(dbar(c, kOffDAccEmpty, i), 4);

@@ -3,6 +3,11 @@
 #pragma once
 #include <stdint.h>
 
+#ifndef __CUDACC__
+#define __host__
+#define __device__
+#endif
+
 namespace tmb {
 
 constexpr int kConsumerWarps = 8;                       // warps that do arithmetic
@@ -23,7 +28,12 @@ constexpr int kMaxTp = 8;                               // tensor-parallel ranks
 constexpr int kDenseTileN = 128;
 constexpr int kDenseTileK = 128;
 constexpr int kDenseMaxBatch = 64;
-constexpr int kDenseXSlots = 3;                         // activation chunks (batch x 128 columns) in flight per CTA
+constexpr int kDenseXSlots = 4;                         // at most this many activation chunks (batch x 128 columns) in flight per CTA
+// ... as many of them as fit 48 KB: 3 at batch 64, 4 below
+__host__ __device__ inline int dense_x_slots(int batch) {
+  const int fit = 49152 / (batch * kDenseTileK * 2);
+  return fit < kDenseXSlots ? fit : kDenseXSlots;
+}
 constexpr int kDenseThreads = kThreads + 32;            // + the warp whose lane 0 loads activations and issues tcgen05.mma
 constexpr int kDenseTmemColumns = 128;                  // two accumulators of up to 64 fp32 columns
 
@@ -96,6 +106,7 @@ struct MegaParams {
   int experts, topk, norm_topk;
   int qk_norm;              // per-head RMSNorm of q and k before RoPE (Qwen3)
   int stages_per_layer;     // 5 dense, 6 with a router stage
+  int trace_stages;         // stage records per CTA of a traced step (dense-batch plans record their RMSNorm stages too)
   float eps;
   float qk_scale_log2;      // log2(e) / sqrt(head_dim)
   // request state

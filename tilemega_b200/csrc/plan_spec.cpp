@@ -36,8 +36,10 @@ std::string Pages(const std::string& source, int tile_k, int tile_n = kTileN) {
          ",\"source\":" + source + "}";
 }
 
-// Dense-batch GEMM stage: row tiles of 128, the reduction in 128-column chunks cut into nsplit parts so
-// that there are about two tasks per SM or more (a part keeps at least four chunks, 128 KB of weights).
+// Dense-batch GEMM stage: row tiles of 128, the reduction in 128-column chunks cut into the fewest parts
+// that give tasks to at least 85 % of the SMs (a part keeps at least four chunks, 128 KB of weights). Few
+// parts matter: the last arriver of a tile reads every part's fp32 tile back, nsplit * batch loads per
+// thread (measured at batch 64: 8 and 14 parts cost the QKV and down stages 3-4 times their streaming time).
 DenseGeo MakeDenseGeo(const char* what, int n, int k, int sms) {
   if (n <= 0 || n % kDenseTileN) throw std::invalid_argument(std::string(what) + ": rows must be a multiple of 128 for a dense-batch plan");
   if (k <= 0 || k % kDenseTileK) throw std::invalid_argument(std::string(what) + ": K must be a multiple of 128 for a dense-batch plan");
@@ -50,7 +52,7 @@ DenseGeo MakeDenseGeo(const char* what, int n, int k, int sms) {
   for (int d = 1; d <= chunks; ++d) {
     if (chunks % d || chunks / d < std::min(4, chunks)) continue;
     g.nsplit = d;
-    if (g.tiles * d >= 2 * sms) break;
+    if (g.tiles * d * 20 >= sms * 17) break;   // tasks for at least 85 % of the SMs
   }
   g.cps = chunks / g.nsplit;
   g.ntasks = g.tiles * g.nsplit;

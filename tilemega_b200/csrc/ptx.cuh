@@ -195,6 +195,15 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const void* tensor_map, i
       : "memory");
 }
 
+// The same with three coordinates (x innermost).
+__device__ __forceinline__ void tma_load_3d(void* dst, const void* tensor_map, int x, int y, int z, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(
+          smem_u32(dst)),
+      "l"(tensor_map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
+      : "memory");
+}
+
 // Tensor memory columns for this CTA (a power of two >= 32); the base address lands in
 // shared memory. Executed by one whole warp, which also frees the columns.
 __device__ __forceinline__ void tmem_alloc(uint32_t* base_in_smem, uint32_t columns) {

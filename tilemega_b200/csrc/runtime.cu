@@ -138,8 +138,8 @@ void Destroy(Plan* plan) {
   delete plan;
 }
 
-// Tiled tensor map over a row-major bf16 matrix [rows][cols]: boxes of `rows` x 64 columns, 128-byte
-// swizzle (what tcgen05.mma expects of a K-major operand). The encoder is the driver's; it is looked
+// Tiled tensor map over a row-major bf16 matrix [rows][cols]: boxes of two blocks of `rows` x 64 columns,
+// 128-byte swizzle (what tcgen05.mma expects of a K-major operand). The encoder is the driver's; it is looked
 // up at run time so that the library has no link-time dependency on the driver library.
 const char* EncodeRowsMap(CUtensorMap* map, void* base, uint64_t rows, uint64_t cols) {
   using Encode = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -154,11 +154,13 @@ const char* EncodeRowsMap(CUtensorMap* map, void* base, uint64_t rows, uint64_t 
       return "the driver does not offer cuTensorMapEncodeTiled";
     encode = reinterpret_cast<Encode>(entry);
   }
-  const cuuint64_t dims[2] = {cols, rows};
-  const cuuint64_t strides[1] = {cols * 2};
-  const cuuint32_t box[2] = {64, cuuint32_t(rows)};
-  const cuuint32_t steps[2] = {1, 1};
-  const CUresult status = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, steps,
+  // seen as [cols / 64][rows][64]: one copy fetches both 64-column swizzle blocks of a 128-column chunk,
+  // block after block in shared memory (coordinates: column in block, row, block)
+  const cuuint64_t dims[3] = {64, rows, cols / 64};
+  const cuuint64_t strides[2] = {cols * 2, 128};
+  const cuuint32_t box[3] = {64, cuuint32_t(rows), 2};
+  const cuuint32_t steps[3] = {1, 1, 1};
+  const CUresult status = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, base, dims, strides, box, steps,
                                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return status == CUDA_SUCCESS ? nullptr : "cuTensorMapEncodeTiled rejected an activation buffer";
@@ -308,6 +310,8 @@ void* tm_plan_create(int batch, void* const* external, int device) {
   p.qk_norm = s.qk_norm ? 1 : 0;
   p.stages_per_layer = s.stages_per_layer();
   p.dense = s.dense_batch ? 1 : 0;
+  // a traced step: one record per stage; dense-batch plans have 7 per layer (two RMSNorm stages) and norm + head at the end
+  p.trace_stages = s.dense_batch ? 7 * s.layers + 2 : s.stages_per_layer() * s.layers + 1;
   // grid-wide arrivals of a step: one per stage except QKV (attention tasks wait per KV-head group)
   // plus the argmax hand-over; a dense-batch plan's RMSNorm stages arrive too
   p.bars_per_step = s.dense_batch ? 6 * s.layers + 2 : (s.stages_per_layer() - 1) * s.layers + 1;
@@ -343,7 +347,7 @@ void* tm_plan_create(int batch, void* const* external, int device) {
                      expert_rows});
   // dense-batch: the activation chunks of the GEMM stages (batch x 128 columns each) share the area
   // with the attention scratch; chunks must start on 1024-byte boundaries (128-byte swizzle)
-  if (s.dense_batch) xs = std::max(attention_scratch, tmb::kDenseXSlots * batch * tmb::kDenseTileK * 2);
+  if (s.dense_batch) xs = std::max(attention_scratch, tmb::dense_x_slots(batch) * batch * tmb::kDenseTileK * 2);
   xs = s.dense_batch ? (xs + 1023) & ~1023 : (xs + 127) & ~127;
   p.xs_bytes = xs;
   p.attn_min_spt = s.attn_min_slots;
@@ -675,11 +679,9 @@ int tm_plan_watchdog_probe(void* handle, int withhold, uint32_t limit_us, void* 
 int tm_plan_trace_step(void* handle, int step) {
   Plan* plan = AsPlan(handle);
   if (!plan) return Fail(-1, "tm_plan_trace_step: bad plan");
-  if (plan->params.dense && step >= 0) return Fail(-3, "tm_plan_trace_step: the dense-batch kernel records no stage trace");
   DeviceScope scope(plan->device);
   if (step >= 0 && !plan->trace_dev) {
-    plan->trace_bytes = size_t(plan->params.grid) * (size_t(plan->params.stages_per_layer) * size_t(plan->params.layers) + 1) * 4 *
-                        sizeof(unsigned long long);
+    plan->trace_bytes = size_t(plan->params.grid) * size_t(plan->params.trace_stages) * 4 * sizeof(unsigned long long);
     void* dev = nullptr;
     cudaError_t err = Alloc(*plan, &dev, plan->trace_bytes);
     if (err != cudaSuccess) return Fail(int(err), cudaGetErrorString(err));

@@ -116,6 +116,8 @@ def print_table(config: dict, trace, per_layer: int, context: int, batch: int, t
     import numpy as np
     layers = config["num_hidden_layers"]
     kinds = ["qkv", "attn", "o"] + (["router"] if synthetic.is_moe(config) else []) + ["gate_up", "down"]
+    if batch > 8:   # dense-batch plans: RMSNorm is a stage of its own, twice per layer
+        kinds = ["norm1", "qkv", "attn", "o", "norm2", "gate_up", "down"]
     parts = per_layer - len(kinds) + 1
     if parts > 1:
         kinds = kinds[:-1] + [f"down part {i}" for i in range(parts)]
