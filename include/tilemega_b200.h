@@ -30,7 +30,11 @@ enum { TM_SERVING_ABI_VERSION = 1 };
 enum { TM_SERVING_PREFILL = 0, TM_SERVING_DECODE = 1, TM_SERVING_FORWARD = 2 };
 enum { TM_SERVING_L1 = 1, TM_SERVING_L2 = 2 };
 enum { TM_BUFFER_INTERNAL = 0, TM_BUFFER_EXTERNAL = 1 };
-enum { TM_DTYPE_BF16 = 0, TM_DTYPE_F32 = 1, TM_DTYPE_I32 = 2 };
+enum { TM_DTYPE_BF16 = 0, TM_DTYPE_F32 = 1, TM_DTYPE_I32 = 2,
+       /* addition (the reference has no 8-bit weights): e4m3 bytes, one element per byte, in the
+        * weight buffers of a plan whose sidecar says "weights": "e4m3"; each such buffer comes with an
+        * fp32 buffer "<name>.scale" of one scale per output row */
+       TM_DTYPE_E4M3 = 4 };
 
 /* ServingAbi.h:17-23 */
 typedef struct {

@@ -16,9 +16,9 @@ LIB_DIR = ROOT / "lib"
 LIBRARY = LIB_DIR / "libtilemega_b200.so"
 # (object name, source, extra flags). The kernel source is compiled twice, side by side:
 # plain (unsharded dense plans), extended (tensor parallelism, mixture of experts, QK norm) and dense-batch
-# (batch 16..64: GEMM stages on tcgen05 tiles).
+# (batch 16..64: GEMM stages on tcgen05 tiles) and e4m3 weights (the small-batch kernel with 8-bit weight pages).
 UNITS = (("megakernel", "megakernel.cu", ()), ("megakernel_extended", "megakernel.cu", ("-DTMB_EXTENDED=1",)),
-         ("megakernel_dense", "megakernel.cu", ("-DTMB_DENSE=1",)),
+         ("megakernel_dense", "megakernel.cu", ("-DTMB_DENSE=1",)), ("megakernel_fp8", "megakernel.cu", ("-DTMB_FP8=1",)),
          ("runtime", "runtime.cu", ()), ("plan_spec", "plan_spec.cpp", ()), ("static_probe", "static_probe.cu", ()),
          ("pack", "pack.cu", ()), ("calibrate", "calibrate.cu", ()))
 SOURCES = tuple(sorted({unit[1] for unit in UNITS}))

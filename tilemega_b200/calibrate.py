@@ -73,7 +73,7 @@ def assemble(props: dict, measured: dict[str, list[float]], stamp: str) -> dict:
         "caps": {"cluster": True, "tma": True, "warp_specialized": True, "tcgen05": True, "l1_5": True, "net": False,
                  "cp_async": True, "mbarrier": True, "mbarrier_try_wait": True, "mbarrier_tx": True, "bulk_copy": True,
                  "bulk_prefetch": True, "pdl": True, "wgmma": False, "setmaxnreg": True, "tma_im2col": True,
-                 "tma_multicast": True, "bulk_reduce": True, "dsmem": True, "elect_sync": True},
+                 "bulk_reduce": True, "dsmem": True, "elect_sync": True},
         "resources_provenance": "cudaGetDeviceProperties of the calibrated device",
         "resources": {"num_sms": props["sms"], "l2_bytes": props["l2_bytes"], "max_smem_per_sm": props["smem_per_sm"],
                       "max_dynamic_smem_per_cta": props["smem_optin"], "regs_per_sm": props["regs_per_sm"],

@@ -38,6 +38,9 @@
 #ifndef TMB_EXTENDED
 #define TMB_EXTENDED 0   // 1: the translation unit with tensor parallelism, mixture of experts and QK norm
 #endif
+#ifndef TMB_FP8
+#define TMB_FP8 0        // 1: the translation unit with the e4m3-weight instantiations of the small-batch kernel
+#endif
 #ifndef TMB_DENSE
 #define TMB_DENSE 0      // 1: the translation unit with the dense-batch kernel (GEMM stages on tcgen05 tiles)
 #endif
@@ -76,6 +79,7 @@ constexpr int kOffDenseXs = 8192;
 // one (0) serves unsharded dense plans and carries neither.
 constexpr int kXTp = 1;    // tensor parallelism: all-reduce epilogue, argmax exchange
 constexpr int kXMoe = 2;   // mixture of experts and the per-head QK norm (batch 1)
+constexpr int kXFp8 = 4;   // weights are e4m3 bytes with fp32 row scales (pages of 8 rows x 4096 columns)
 constexpr int kFifo = 32;          // entries; the streaming warp keeps at most kFifo/2 unread
 
 __host__ __device__ inline int xs_offset(int batch) {   // activation rows / attention scratch
@@ -524,7 +528,7 @@ __device__ __forceinline__ void stream_gemv_task(Ctx& c, const GemvGeo& geo, con
 }
 
 __device__ __forceinline__ void stream_gemv(Ctx& c, const GemvGeo& geo, const void* weights, uint64_t policy) {
-  const uint32_t page_bytes = uint32_t(kTileN) * uint32_t(geo.tile_k) * 2u;
+  const uint32_t page_bytes = uint32_t(geo.page_bytes);
   // position of this stage in the launch's page sequence (the idle prefetch works from it)
   c.cur_abs_base += c.cur_npages;
   c.cur_npages = geo.ntasks * geo.task_pages;
@@ -554,7 +558,7 @@ __device__ __forceinline__ void stream_gemv(Ctx& c, const GemvGeo& geo, const vo
 // by itself, experts geo.ntasks * pages_per_task pages apart.
 __device__ __forceinline__ void stream_expert_gate_up(Ctx& c, const GemvGeo& geo, const void* stack,
                                                       const int (&expert)[kMaxTopK], uint64_t policy) {
-  const uint32_t page_bytes = uint32_t(kTileN) * uint32_t(geo.tile_k) * 2u;
+  const uint32_t page_bytes = uint32_t(geo.page_bytes);
   const unsigned char* w = static_cast<const unsigned char*>(stack);
   const int total = c.p.topk * geo.ntasks;
   const int chunk_tasks = geo.claim_chunk;
@@ -583,7 +587,7 @@ __device__ __forceinline__ void stream_expert_gate_up(Ctx& c, const GemvGeo& geo
 // per row in rank order by one warp); it is posted as topk sub-tasks of one page each.
 __device__ __forceinline__ void stream_expert_down(Ctx& c, const GemvGeo& geo, const void* stack,
                                                    const int (&expert)[kMaxTopK], uint64_t policy) {
-  const uint32_t page_bytes = uint32_t(kTileN) * uint32_t(geo.tile_k) * 2u;
+  const uint32_t page_bytes = uint32_t(geo.page_bytes);
   const unsigned char* w = static_cast<const unsigned char*>(stack);
   int t = c.pending;
   while (t < geo.ntasks && !c.dead) {
@@ -727,6 +731,7 @@ struct GemvIo {
   const float* partial_in;     // fp32 sums of the earlier parts of a split reduction, added before any rounding (or null)
   int ar_region;               // kEpiResidualAllReduce: which of the two packet regions (0: o, 1: down)
   uint32_t ar_epoch;           // ... and the epoch its packets carry (never 0, grows with every all-reduce)
+  const float* scale;          // e4m3 weights: fp32 scale per output row, applied to the fp32 sum (or null)
 };
 
 // Where the four 32-bit words of 16-byte chunk i of an activation row go: A-fragment
@@ -741,6 +746,31 @@ __device__ __forceinline__ void store_row_chunk(uint32_t* row, int i, const uint
   dst[24] = v.w;
 }
 
+// e4m3 weight plans multiply with f16 tensor-pipe instructions (the weights convert to f16 pairs
+// exactly, one instruction per pair), so the rows are staged as f16, and in the order that path's
+// fragments want: a lane (row g, q) needs, of every 16-column block m of a 128-column atom, the four
+// columns 16m + 4q .. + 3 (its e4m3 word of the weight tile covers exactly those), so inside an atom
+// the two words of (q, m) sit at q*16 + m*2 and a lane reads its sixteen words with four 128-bit loads.
+__device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t w) {
+  const __half2 h = __floats2half2_rn(bf_lo(w), bf_hi(w));
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+__device__ __forceinline__ void store_row_chunk_f16(uint32_t* row, int i, const uint4& v) {   // v: eight bf16 values, columns 8i..8i+7
+  const int r = i & 15;
+  uint32_t* dst = row + (i >> 4) * 64 + ((r & 1) * 2) * 16 + (r >> 1) * 2;
+  dst[0] = bf16x2_to_f16x2(v.x);
+  dst[1] = bf16x2_to_f16x2(v.y);
+  dst[16] = bf16x2_to_f16x2(v.z);
+  dst[17] = bf16x2_to_f16x2(v.w);
+}
+
+template <bool FP8>
+__device__ __forceinline__ void store_row(uint32_t* row, int i, const uint4& v) {
+  if (FP8) store_row_chunk_f16(row, i, v);
+  else store_row_chunk(row, i, v);
+}
+
 // Stage the stage's B activation rows in shared memory; RMSNorm fused:
 // y = bf16(w * bf16(x * rsqrt(mean(x^2) + eps)))  (python/tilemega/serving/export.py:24-27).
 // Rows 0..B-1 of the staging area are the rows the GEMV reads; for a normalised
@@ -748,7 +778,7 @@ __device__ __forceinline__ void store_row_chunk(uint32_t* row, int i, const uint
 // pass, so that their L2 round trips overlap.
 // Columns [k_src, k) do not exist in the source rows (the weights are zero-padded
 // there): they are staged as zeros.
-template <int B>
+template <int B, bool FP8>
 __device__ __forceinline__ void stage_rows(Ctx& c, const GemvIo& io, const GemvGeo& geo) {
   const MegaParams& p = c.p;
   const int k = geo.k, k_src = geo.k_src;
@@ -794,7 +824,7 @@ __device__ __forceinline__ void stage_rows(Ctx& c, const GemvIo& io, const GemvG
 #pragma unroll
         for (int j = 0; j < 8; ++j) ss[b] = fmaf(f[j], f[j], ss[b]);
       } else {
-        store_row_chunk(reinterpret_cast<uint32_t*>(xs4 + b * pitch), i, v[b]);
+        store_row<FP8>(reinterpret_cast<uint32_t*>(xs4 + b * pitch), i, v[b]);
       }
     }
   }
@@ -836,7 +866,7 @@ __device__ __forceinline__ void stage_rows(Ctx& c, const GemvIo& io, const GemvG
           const uint32_t hi = bf16_bits(w[2 * j + 1] * bf16_round(f[2 * j + 1] * inv[b]));
           o[j] = lo | (hi << 16);
         }
-        store_row_chunk(reinterpret_cast<uint32_t*>(xs4 + b * pitch), i, make_uint4(o[0], o[1], o[2], o[3]));
+        store_row<FP8>(reinterpret_cast<uint32_t*>(xs4 + b * pitch), i, make_uint4(o[0], o[1], o[2], o[3]));
       }
     }
   }
@@ -873,6 +903,57 @@ __device__ __forceinline__ void gemv_page_mma(const unsigned char* page, const u
     ldmatrix_x4(w, wa + 1024 * cb + 16 * ((4 + m) ^ r));                       // chunks 4..7
     mma_bf16_m16n8k16(d[2], xhi.x, xhi.y, w[0], w[1]);
     mma_bf16_m16n8k16(d[3], xhi.z, xhi.w, w[2], w[3]);
+  }
+}
+
+// The same page loop for e4m3 weights: a page is 8 rows x 4096 one-byte columns laid out like a
+// bf16 page of 8 x 2048 (2-byte units, the same swizzle), so ldmatrix delivers to lane (g, q), per
+// 16-byte chunk, the four e4m3 values W[g][16m + 4q .. + 3] in one register. Two conversions make them
+// two f16 pairs; with the activations staged in the matching order (store_row_chunk_f16) they are the
+// B fragments of one m16n8k16 product whose sixteen k positions are a permutation of the block's
+// sixteen columns, which a sum does not mind. Per page and warp: 8 ldmatrix.x4, 64 conversions, 32 mma.
+__device__ __forceinline__ void e4m3x4_to_f16x2(uint32_t w, uint32_t& lo, uint32_t& hi) {
+  asm("{\n"
+      " .reg .b16 a, b;\n"
+      " mov.b32 {a, b}, %2;\n"
+      " cvt.rn.f16x2.e4m3x2 %0, a;\n"
+      " cvt.rn.f16x2.e4m3x2 %1, b;\n"
+      "}\n"
+      : "=r"(lo), "=r"(hi)
+      : "r"(w));
+}
+
+__device__ __forceinline__ void mma_f16_m16n8k16(float (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+}
+
+template <int B>
+__device__ __forceinline__ void gemv_page_mma_e4m3(const unsigned char* page, const unsigned char* xs, int k, int col0,
+                                                   int warp, int lane, float (&d)[4][4]) {
+  const int r = lane & 7, m = lane >> 3;                 // ldmatrix: this lane addresses row r of matrix m
+  const int g = lane >> 2, q = lane & 3;                 // mma fragments: batch row g, word q
+  // this warp's 512 columns of the page are four 128-column atoms; the lane's 16 words of an atom are contiguous
+  const unsigned char* xrow = xs + (size_t(min(g, B - 1)) * (k + 8) + col0 + 512 * warp) * 2 + 64 * q;
+  const uint32_t wa = smem_u32(page) + uint32_t(1024 * (4 * warp) + 128 * r);
+#pragma unroll
+  for (int cb = 0; cb < 4; ++cb) {
+    uint4 x[4];   // x[j]: the words of blocks m = 2j, 2j+1: {a0, a2} of block 2j, {a0, a2} of block 2j+1
+#pragma unroll
+    for (int j = 0; j < 4; ++j) x[j] = *reinterpret_cast<const uint4*>(xrow + 256 * cb + 16 * j);
+    uint32_t w[4], lo, hi;
+    ldmatrix_x4(w, wa + 1024 * cb + 16 * (m ^ r));                             // 16-byte chunks 0..3 of the 8 rows
+    e4m3x4_to_f16x2(w[0], lo, hi); mma_f16_m16n8k16(d[0], x[0].x, x[0].y, lo, hi);
+    e4m3x4_to_f16x2(w[1], lo, hi); mma_f16_m16n8k16(d[1], x[0].z, x[0].w, lo, hi);
+    e4m3x4_to_f16x2(w[2], lo, hi); mma_f16_m16n8k16(d[2], x[1].x, x[1].y, lo, hi);
+    e4m3x4_to_f16x2(w[3], lo, hi); mma_f16_m16n8k16(d[3], x[1].z, x[1].w, lo, hi);
+    ldmatrix_x4(w, wa + 1024 * cb + 16 * ((4 + m) ^ r));                       // chunks 4..7
+    e4m3x4_to_f16x2(w[0], lo, hi); mma_f16_m16n8k16(d[0], x[2].x, x[2].y, lo, hi);
+    e4m3x4_to_f16x2(w[1], lo, hi); mma_f16_m16n8k16(d[1], x[2].z, x[2].w, lo, hi);
+    e4m3x4_to_f16x2(w[2], lo, hi); mma_f16_m16n8k16(d[2], x[3].x, x[3].y, lo, hi);
+    e4m3x4_to_f16x2(w[3], lo, hi); mma_f16_m16n8k16(d[3], x[3].z, x[3].w, lo, hi);
   }
 }
 
@@ -1015,6 +1096,7 @@ __device__ __forceinline__ void gemv_epilogue(Ctx& c, const GemvGeo& geo, const 
 #pragma unroll
       for (int w = 0; w < kConsumerWarps; ++w) v += red[((e.buf * 8 + w) * 8 + r) * B + b];
       if (io.partial_in) v += __ldcg(io.partial_in + size_t(b) * geo.n + row);   // earlier parts of a split reduction
+      if ((X & kXFp8) && io.scale && io.epilogue != kEpiPartial) v *= __ldg(io.scale + row);   // e4m3 weights: the row's scale
       const float vb = bf16_round(v);
       if (io.epilogue == kEpiPartial) {
         static_cast<float*>(io.out)[size_t(b) * geo.n + row] = v;
@@ -1082,7 +1164,7 @@ __device__ __forceinline__ void gemv_epilogue(Ctx& c, const GemvGeo& geo, const 
 template <int B, int X>
 __device__ __forceinline__ void gemv_stage(Ctx& c, const GemvGeo& geo, const GemvIo& io, bool tr, int stage) {
   const MegaParams& p = c.p;
-  stage_rows<B>(c, io, geo);
+  stage_rows<B, (X & kXFp8) != 0>(c, io, geo);
   trace_mark(c, tr, stage, 2);
   // per-warp running argmax (each warp runs every eighth epilogue); merged by the caller
   float best_val[EpiPasses<B>::value];
@@ -1127,8 +1209,10 @@ __device__ __forceinline__ void gemv_stage(Ctx& c, const GemvGeo& geo, const Gem
       mbar_wait_warp(c, full0 + slot, phase, kSiteFull);
       // a warp whose 256 columns of this page lie wholly in the reduction's zero pad
       // has nothing to add (and that part of the slot was not copied)
-      if (pg * geo.tile_k + 256 * warp < geo.k_src)
-        gemv_page_mma<B>(ring0 + slot * kSlotBytes, xs, geo.k, pg * geo.tile_k, warp, lane, d);
+      if (pg * geo.tile_k + (geo.tile_k >> 3) * warp < geo.k_src) {
+        if constexpr ((X & kXFp8) != 0) gemv_page_mma_e4m3<B>(ring0 + slot * kSlotBytes, xs, geo.k, pg * geo.tile_k, warp, lane, d);
+        else gemv_page_mma<B>(ring0 + slot * kSlotBytes, xs, geo.k, pg * geo.tile_k, warp, lane, d);
+      }
       __syncwarp();
       if (lane == 0) mbar_arrive(empty0 + slot);
       if (++slot == nslots) { slot = 0; phase ^= 1u; }
@@ -1743,7 +1827,8 @@ __device__ void consumer_main(Ctx& c) {
         if (!grid_wait(c)) return;
       }
       trace_mark(c, tr, stage, 1);
-      io = GemvIo{l == 0 ? p.embed : p.x, lp.norm1, l == 0, kEpiStore, p.qkv, p.qkv_ready, (GQ + 2) * D / kTileN, nullptr, 0, 0u};
+      io = GemvIo{l == 0 ? p.embed : p.x, lp.norm1, l == 0, kEpiStore, p.qkv, p.qkv_ready, (GQ + 2) * D / kTileN, nullptr, 0, 0u,
+                  lp.qkv_scale};
       gemv_stage<B, X>(c, p.geo[kQkv], io, tr, stage++);
       // no grid barrier here: an attention task needs the QKV rows of its own KV head
       // only, and waits for that group's row-tile count (qkv_ready)
@@ -1754,7 +1839,7 @@ __device__ void consumer_main(Ctx& c) {
       trace_mark(c, tr, stage, 0);
       if (!grid_wait(c)) return;
       trace_mark(c, tr, stage, 1);
-      io = GemvIo{p.attn, nullptr, 0, residual_kind, p.x, nullptr, 1, nullptr, 0, ar_epoch0 + uint32_t(2 * l)};
+      io = GemvIo{p.attn, nullptr, 0, residual_kind, p.x, nullptr, 1, nullptr, 0, ar_epoch0 + uint32_t(2 * l), lp.o_scale};
       gemv_stage<B, X>(c, p.geo[kOProj], io, tr, stage++);
       grid_arrive(c);
       trace_mark(c, tr, stage, 0);
@@ -1785,7 +1870,7 @@ __device__ void consumer_main(Ctx& c) {
         lp = upcoming;
         continue;
       }
-      io = GemvIo{p.x, lp.norm2, 0, kEpiSwiGLU, p.h, nullptr, 1, nullptr, 0, 0u};
+      io = GemvIo{p.x, lp.norm2, 0, kEpiSwiGLU, p.h, nullptr, 1, nullptr, 0, 0u, lp.gate_up_scale};
       gemv_stage<B, X>(c, p.geo[kGateUp], io, tr, stage++);
       grid_arrive(c);
       trace_mark(c, tr, stage, 0);
@@ -1797,7 +1882,7 @@ __device__ void consumer_main(Ctx& c) {
         for (int part = 0; part < p.down_splits; ++part) {
           const bool last = part + 1 == p.down_splits;
           io = GemvIo{p.h, nullptr, 0, last ? residual_kind : int(kEpiPartial), last ? p.x : static_cast<void*>(p.down_partial),
-                      nullptr, 1, part ? p.down_partial : nullptr, 1, ar_epoch0 + uint32_t(2 * l + 1)};
+                      nullptr, 1, part ? p.down_partial : nullptr, 1, ar_epoch0 + uint32_t(2 * l + 1), lp.down_scale};
           gemv_stage<B, X>(c, p.down_part[part], io, tr, stage++);
           grid_arrive(c);
           if (!last) {
@@ -1807,7 +1892,7 @@ __device__ void consumer_main(Ctx& c) {
           }
         }
       } else {
-        io = GemvIo{p.h, nullptr, 0, residual_kind, p.x, nullptr, 1, nullptr, 1, ar_epoch0 + uint32_t(2 * l + 1)};
+        io = GemvIo{p.h, nullptr, 0, residual_kind, p.x, nullptr, 1, nullptr, 1, ar_epoch0 + uint32_t(2 * l + 1), lp.down_scale};
         gemv_stage<B, X>(c, p.geo[kDown], io, tr, stage++);
         grid_arrive(c);
       }
@@ -1816,7 +1901,7 @@ __device__ void consumer_main(Ctx& c) {
     trace_mark(c, tr, stage, 0);
     if (!grid_wait(c)) return;
     trace_mark(c, tr, stage, 1);
-    GemvIo io{p.x, p.final_norm, 0, kEpiHead, p.logits, nullptr, 1, nullptr, 0, 0u};
+    GemvIo io{p.x, p.final_norm, 0, kEpiHead, p.logits, nullptr, 1, nullptr, 0, 0u, p.lm_head_scale};
     gemv_stage<B, X>(c, p.geo[kHead], io, tr, stage);
     consumer_sync();
     if (c.tid < B) {
@@ -2507,7 +2592,7 @@ cudaError_t run_decode_dense(const MegaParams& p, cudaStream_t stream, bool prep
 }
 #endif   // TMB_DENSE
 
-#if !TMB_EXTENDED && !TMB_DENSE
+#if !TMB_EXTENDED && !TMB_DENSE && !TMB_FP8
 // A two-CTA toy that exercises the bounded-wait path without hanging anything:
 // CTA 1 waits for an arrival CTA 0 is told to withhold; the wait gives up after
 // watchdog_ns, records the site and both CTAs return normally.
@@ -2566,6 +2651,15 @@ static cudaError_t run_batch(const MegaParams& p, size_t smem_bytes, cudaStream_
 // (TMB_EXTENDED) adds tensor parallelism, mixture of experts and the QK norm, for
 // head_dim 128; a third one (TMB_DENSE) holds the dense-batch kernel.
 #if TMB_DENSE
+#elif TMB_FP8
+cudaError_t run_decode_fp8(const MegaParams& p, cudaStream_t stream, bool prepare) {
+  const size_t smem_bytes = size_t(ring_offset(p.xs_bytes, p.batch) + p.nslots * kSlotBytes);
+  if (p.kv_heads <= 0 || p.heads % p.kv_heads || p.head_dim != 128 || p.experts > 0 || p.qk_norm) return cudaErrorInvalidValue;
+  const int gq = p.heads / p.kv_heads;
+  if (gq == 8) return run_batch<128, 8, kXFp8 | kXTp>(p, smem_bytes, stream, prepare);
+  if (gq == 4) return run_batch<128, 4, kXFp8 | kXTp>(p, smem_bytes, stream, prepare);
+  return cudaErrorInvalidValue;
+}
 #elif TMB_EXTENDED
 cudaError_t run_decode_extended(const MegaParams& p, cudaStream_t stream, bool prepare) {
   const size_t smem_bytes = size_t(ring_offset(p.xs_bytes, p.batch) + p.nslots * kSlotBytes);
@@ -2616,11 +2710,13 @@ cudaError_t run_decode_ranks(const MegaParams& first, const MegaParams* ranks_de
 #else
 cudaError_t run_decode_extended(const MegaParams& p, cudaStream_t stream, bool prepare);
 cudaError_t run_decode_dense(const MegaParams& p, cudaStream_t stream, bool prepare);
+cudaError_t run_decode_fp8(const MegaParams& p, cudaStream_t stream, bool prepare);
 cudaError_t run_decode_ranks(const MegaParams& first, const MegaParams* ranks_dev, int count, int total_grid,
                              cudaStream_t stream);
 
 static cudaError_t run_decode(const MegaParams& p, cudaStream_t stream, bool prepare) {
   if (p.dense) return run_decode_dense(p, stream, prepare);
+  if (p.fp8) return run_decode_fp8(p, stream, prepare);
   if (p.tp_world > 1 || p.experts > 0 || p.qk_norm) return run_decode_extended(p, stream, prepare);
   const size_t smem_bytes = size_t(ring_offset(p.xs_bytes, p.batch) + p.nslots * kSlotBytes);
   if (p.kv_heads <= 0 || p.heads % p.kv_heads) return cudaErrorInvalidValue;
@@ -2635,7 +2731,7 @@ static cudaError_t run_decode(const MegaParams& p, cudaStream_t stream, bool pre
 
 }  // namespace tmb
 
-#if !TMB_EXTENDED && !TMB_DENSE
+#if !TMB_EXTENDED && !TMB_DENSE && !TMB_FP8
 extern "C" int tmb_smem_bytes(const tmb::MegaParams* p) {
   return tmb::ring_offset(p->xs_bytes, p->batch) + p->nslots * tmb::kSlotBytes;
 }

@@ -62,6 +62,7 @@ struct GemvGeo {
   // columns into source rows that are src_stride columns apart.
   int page0, task_pages, src_off, src_stride;
   int claim_chunk;     // tasks taken per claim: about 64 KB of pages, so a claim's round trip hides behind the copies
+  int page_bytes;      // bytes of one page = one ring slot (8 rows x tile_k columns of 2 bytes, or of 1 byte for e4m3 weights)
 };
 
 // Geometry of one GEMM stage of a dense-batch plan: `tiles` row tiles of 128 weight rows, the
@@ -75,6 +76,11 @@ struct DenseGeo {
 };
 
 struct LayerPtrs {
+  // e4m3 weight plans: fp32 scale per output row of the four matrices (else null)
+  const float* qkv_scale;
+  const float* o_scale;
+  const float* gate_up_scale;
+  const float* down_scale;
   const void* qkv;       // packed pages, rows group-interleaved [Gq q heads][k][v] per KV head
   const void* o;
   const void* gate_up;   // packed pages, rows interleaved 4 gate / 4 up
@@ -134,6 +140,8 @@ struct MegaParams {
   const void* embed;           // bf16 [V][H]
   const void* final_norm;      // bf16 [H]
   const void* lm_head;         // packed pages [V/8][H/tile_k][8*tile_k]
+  const float* lm_head_scale;  // e4m3 weight plans: fp32 scale per vocabulary row (else null)
+  int fp8;                     // weights are e4m3 bytes with per-row scales: pages of 8 rows x 4096 columns
   const LayerPtrs* layer;      // [L]
   // internal buffers
   void* x;                     // bf16 [B][H] residual stream

@@ -61,14 +61,14 @@ DenseGeo MakeDenseGeo(const char* what, int n, int k, int sms) {
 }
 
 // The page stream of a dense-batch stage in the streaming thread's terms: a task is cps consecutive
-// 32 KB pages. (tile_k = 2048 only makes kTileN * tile_k * 2 the page size; the page is 128 x 128.)
+// 32 KB pages of 128 rows x 128 columns.
 GemvGeo StreamGeo(const DenseGeo& d) {
   GemvGeo g{};
   g.n = d.n;
   g.k = g.k_src = d.k;
-  g.tile_k = 2048;
+  g.tile_k = kDenseTileK;
   g.pages_per_task = g.task_pages = d.cps;
-  g.last_page_bytes = kSlotBytes;
+  g.last_page_bytes = g.page_bytes = kSlotBytes;
   g.ntasks = d.ntasks;
   g.page0 = 0;
   g.src_off = 0;
@@ -82,30 +82,28 @@ GemvGeo StreamGeo(const DenseGeo& d) {
 // activation rows', so the extra columns add nothing. Inside a page a 64-column block of
 // the 8 rows is contiguous (1 KB), so the pad is the page's tail: the kernel copies only
 // last_page_bytes of a task's last page and the pad costs address space, not bandwidth.
-GemvGeo MakeGeo(const char* what, int n, int k, const Json& overrides) {
+GemvGeo MakeGeo(const char* what, int n, int k, const Json& overrides, int elem_bytes = 2) {
   GemvGeo g{};
   g.n = n;
   g.k_src = k;
-  g.tile_k = 2048;
+  g.tile_k = kSlotBytes / (kTileN * elem_bytes);   // 2048 columns of bf16, 4096 of e4m3: a page is one 32 KB slot
   if (k > 0 && k % 8 == 0) k = (k + g.tile_k - 1) / g.tile_k * g.tile_k;
   g.k = k;
-  if (overrides.has(what)) {
-    g.tile_k = int(overrides.at(what).integer("tile_k", g.tile_k));
-  }
-  if (g.tile_k != 2048) throw std::invalid_argument(std::string(what) + ": tile_k must be 2048");
   if (n <= 0 || n % kTileN) throw std::invalid_argument(std::string(what) + ": rows must be a multiple of 8");
-  if (k <= 0 || k % g.tile_k) throw std::invalid_argument(std::string(what) + ": K must be a multiple of tile_k");
+  if (k <= 0 || k % g.tile_k) throw std::invalid_argument(std::string(what) + ": K must be a multiple of 8");
   const int kt = k / g.tile_k;
   g.pages_per_task = kt;
-  // columns of the last page that hold weights, in whole 256-column warp shares
-  const int last_columns = (g.k_src - (kt - 1) * g.tile_k + 255) / 256 * 256;
-  g.last_page_bytes = kTileN * last_columns * 2;
+  // columns of the last page that hold weights, in whole warp shares (an eighth of a page)
+  const int share = g.tile_k / 8;
+  const int last_columns = (g.k_src - (kt - 1) * g.tile_k + share - 1) / share * share;
+  g.last_page_bytes = kTileN * last_columns * elem_bytes;
+  g.page_bytes = kSlotBytes;
   g.ntasks = n / kTileN;
   g.page0 = 0;
   g.task_pages = kt;
   g.src_off = 0;
   g.src_stride = g.k_src;
-  const int task_bytes = (kt - 1) * kTileN * g.tile_k * 2 + g.last_page_bytes;
+  const int task_bytes = (kt - 1) * g.page_bytes + g.last_page_bytes;
   g.claim_chunk = std::max(1, std::min(8, (65536 + task_bytes - 1) / task_bytes));
   if (overrides.has(what)) g.claim_chunk = int(overrides.at(what).integer("claim_chunk", g.claim_chunk));
   if (g.claim_chunk < 1 || g.claim_chunk > 64) throw std::invalid_argument(std::string(what) + ": claim_chunk must lie in [1, 64]");
@@ -124,7 +122,8 @@ int PlanSpec::max_k() const {
 uint64_t PlanSpec::weight_bytes() const {
   uint64_t total = 0;
   for (int s = 0; s < kNumGemv; ++s) {
-    uint64_t one = 2ull * uint64_t(geo[s].n) * uint64_t(geo[s].k_src);
+    uint64_t one = fp8 ? uint64_t(geo[s].n) * uint64_t(geo[s].k_src) + 4ull * uint64_t(geo[s].n)   // bytes + a scale per row
+                       : 2ull * uint64_t(geo[s].n) * uint64_t(geo[s].k_src);
     if (experts && (s == kGateUp || s == kDown)) one *= uint64_t(topk) * uint64_t(batch_hi);   // experts routed to per step
     total += s == kHead ? one : one * uint64_t(layers);
   }
@@ -215,11 +214,19 @@ PlanSpec PlanSpec::FromJson(const Json& plan) {
   if (s.prefetch_window < 0 || s.prefetch_window > 8192) throw std::invalid_argument("prefetch_window must lie in [0, 8192] pages");
   s.write_logits = plan.flag("write_logits", true);
   const Json& geometry = plan.has("geometry") ? plan.at("geometry") : empty;
-  s.geo[kQkv] = MakeGeo("qkv", s.qkv_rows(), s.hidden, geometry);
-  s.geo[kOProj] = MakeGeo("o", s.hidden, s.heads * s.head_dim, geometry);
-  s.geo[kGateUp] = MakeGeo("gate_up", 2 * s.inter, s.hidden, geometry);
-  s.geo[kDown] = MakeGeo("down", s.hidden, s.inter, geometry);
-  s.geo[kHead] = MakeGeo("lm_head", s.head_rows, s.hidden, geometry);
+  // "weights": "e4m3": every GEMV matrix as e4m3 bytes with one fp32 scale per output row (the scale
+  // is applied to the fp32 sum before the stage's rounding sites); pages are 8 rows x 4096 columns
+  const std::string weights = plan.str("weights", "bf16");
+  if (weights != "bf16" && weights != "e4m3") throw std::invalid_argument("weights must be bf16 or e4m3");
+  s.fp8 = weights == "e4m3";
+  if (s.fp8 && (s.dense_batch || s.experts || s.head_dim != 128))
+    throw std::invalid_argument("e4m3 weights are built for dense models with head_dim 128 at batch 1..8");
+  const int elem = s.fp8 ? 1 : 2;
+  s.geo[kQkv] = MakeGeo("qkv", s.qkv_rows(), s.hidden, geometry, elem);
+  s.geo[kOProj] = MakeGeo("o", s.hidden, s.heads * s.head_dim, geometry, elem);
+  s.geo[kGateUp] = MakeGeo("gate_up", 2 * s.inter, s.hidden, geometry, elem);
+  s.geo[kDown] = MakeGeo("down", s.hidden, s.inter, geometry, elem);
+  s.geo[kHead] = MakeGeo("lm_head", s.head_rows, s.hidden, geometry, elem);
   // A wide batch times a long down reduction does not fit in shared memory beside the ring
   // (8 rows x 14336 columns are 229 KB): the reduction is then cut into parts of whole pages
   // whose rows take about 80 KB, one stage per part, fp32 running sums in global memory.
@@ -233,7 +240,7 @@ PlanSpec PlanSpec::FromJson(const Json& plan) {
     for (int g : {kQkv, kOProj, kGateUp, kDown, kHead}) s.geo[g] = StreamGeo(s.dgeo[g]);
   } else if (!s.experts) {
     const GemvGeo& down = s.geo[kDown];
-    const int budget_columns = 81920 / (2 * s.batch_hi) - 8;
+    const int budget_columns = 81920 / (2 * s.batch_hi) - 8;   // activation rows are 2-byte elements whatever the weights are
     const int part_pages = std::max(1, std::min(down.pages_per_task, budget_columns / down.tile_k));
     s.down_splits = (down.pages_per_task + part_pages - 1) / part_pages;
     if (s.down_splits > kMaxDownSplits) throw std::invalid_argument("down projection would need more than 8 parts");
@@ -245,8 +252,8 @@ PlanSpec PlanSpec::FromJson(const Json& plan) {
       part.src_off = part.page0 * down.tile_k;
       part.k_src = std::min(part.k, down.k_src - part.src_off);
       const bool last = i + 1 == s.down_splits;
-      part.last_page_bytes = last ? down.last_page_bytes : kTileN * down.tile_k * 2;
-      const int task_bytes = (part.pages_per_task - 1) * kTileN * down.tile_k * 2 + part.last_page_bytes;
+      part.last_page_bytes = last ? down.last_page_bytes : down.page_bytes;
+      const int task_bytes = (part.pages_per_task - 1) * down.page_bytes + part.last_page_bytes;
       part.claim_chunk = std::max(1, std::min(8, (65536 + task_bytes - 1) / task_bytes));
       s.down_part[i] = part;
     }
@@ -284,6 +291,17 @@ PlanSpec PlanSpec::FromJson(const Json& plan) {
   const int page_n = s.dense_batch ? kDenseTileN : kTileN;
   auto page_k = [&](int stage) { return s.dense_batch ? kDenseTileK : s.geo[stage].tile_k; };
   const int swiglu_unit = s.dense_batch ? 16 : 4;   // gate rows followed by as many up rows
+  // e4m3 plans: the matrix is quantised row by row ("e4m3_pairs": its bytes seen as 2-byte units, so
+  // that tile_pages and its 128-byte swizzle apply unchanged: a page of 8 x 2048 units is 8 x 4096
+  // e4m3 columns) and the row scales travel as an fp32 buffer of their own ("e4m3_scale")
+  const uint32_t weight_dtype = s.fp8 ? 4u : 0u;
+  auto weight_pages = [&](const std::string& source, int stage) {
+    if (!s.fp8) return Pages(source, page_k(stage), page_n);
+    return Pages("{\"kind\":\"e4m3_pairs\",\"source\":" + source + "}", 2048, kTileN);
+  };
+  auto scale_of = [&](const std::string& name, const std::string& source, int rows) {
+    return s.fp8 ? add(name, 1, 1, uint64_t(rows), 0, "{\"kind\":\"e4m3_scale\",\"source\":" + source + "}") : -1;
+  };
   s.qkv_buf = add("serving.qkv", 0, 0, 0, uint64_t(s.qkv_rows()), "");
   s.attn_buf = add("serving.attention", 0, 0, 0, uint64_t(s.heads) * D, "");
   // with experts: one row per chosen expert (batch 1)
@@ -305,8 +323,8 @@ PlanSpec PlanSpec::FromJson(const Json& plan) {
         Sources({m + "self_attn.q_proj.weight", m + "self_attn.k_proj.weight", m + "self_attn.v_proj.weight"}) +
         ",\"hkv\":" + std::to_string(s.kv_heads) + ",\"qperkv\":" + std::to_string(s.heads / s.kv_heads) +
         ",\"head_dim\":" + std::to_string(s.head_dim) + Shard(0, s.tp) + "}";
-    lb.qkv = add(p + "qkv.weight", 1, 0, uint64_t(s.geo[kQkv].n) * s.geo[kQkv].k, 0,
-                 Pages(qkv_source, page_k(kQkv), page_n));
+    lb.qkv = add(p + "qkv.weight", 1, weight_dtype, uint64_t(s.geo[kQkv].n) * s.geo[kQkv].k, 0, weight_pages(qkv_source, kQkv));
+    lb.qkv_scale = scale_of(p + "qkv.scale", qkv_source, s.geo[kQkv].n);
     if (s.paged) {
       const uint64_t pool = uint64_t(s.num_blocks) * s.kv_heads * kKvBlock * D;
       lb.k = add("kv_pool.k." + std::to_string(l), 1, 0, pool, 0, "");
@@ -316,8 +334,9 @@ PlanSpec PlanSpec::FromJson(const Json& plan) {
       lb.k = add("kv_cache.k." + std::to_string(l), 1, 0, 0, cache, "");
       lb.v = add("kv_cache.v." + std::to_string(l), 1, 0, 0, cache, "");
     }
-    lb.o = add(p + "o.weight", 1, 0, uint64_t(s.geo[kOProj].n) * s.geo[kOProj].k, 0,
-               Pages(Alias(m + "self_attn.o_proj.weight", Shard(1, s.tp)), page_k(kOProj), page_n));
+    const std::string o_source = Alias(m + "self_attn.o_proj.weight", Shard(1, s.tp));
+    lb.o = add(p + "o.weight", 1, weight_dtype, uint64_t(s.geo[kOProj].n) * s.geo[kOProj].k, 0, weight_pages(o_source, kOProj));
+    lb.o_scale = scale_of(p + "o.scale", o_source, s.geo[kOProj].n);
     lb.norm2 = add(p + "norm2.weight", 1, 0, H, 0, Alias(m + "post_attention_layernorm.weight"));
     if (s.qk_norm) {
       lb.q_norm = add(p + "q_norm.weight", 1, 0, D, 0, Alias(m + "self_attn.q_norm.weight"));
@@ -343,15 +362,18 @@ PlanSpec PlanSpec::FromJson(const Json& plan) {
     const std::string gate_up_source = "{\"kind\":\"gate_up_interleave\",\"sources\":" +
                                        Sources({m + "mlp.gate_proj.weight", m + "mlp.up_proj.weight"}) +
                                        ",\"u\":" + std::to_string(swiglu_unit) + Shard(0, s.tp) + "}";
-    lb.gate_up = add(p + "gate_up.weight", 1, 0, uint64_t(s.geo[kGateUp].n) * s.geo[kGateUp].k, 0,
-                     Pages(gate_up_source, page_k(kGateUp), page_n));
-    lb.down = add(p + "down.weight", 1, 0, uint64_t(s.geo[kDown].n) * s.geo[kDown].k, 0,
-                  Pages(Alias(m + "mlp.down_proj.weight", Shard(1, s.tp)), page_k(kDown), page_n));
+    lb.gate_up = add(p + "gate_up.weight", 1, weight_dtype, uint64_t(s.geo[kGateUp].n) * s.geo[kGateUp].k, 0,
+                     weight_pages(gate_up_source, kGateUp));
+    lb.gate_up_scale = scale_of(p + "gate_up.scale", gate_up_source, s.geo[kGateUp].n);
+    const std::string down_source = Alias(m + "mlp.down_proj.weight", Shard(1, s.tp));
+    lb.down = add(p + "down.weight", 1, weight_dtype, uint64_t(s.geo[kDown].n) * s.geo[kDown].k, 0, weight_pages(down_source, kDown));
+    lb.down_scale = scale_of(p + "down.scale", down_source, s.geo[kDown].n);
     s.layer.push_back(lb);
   }
   s.final_norm = add("model.norm.weight", 1, 0, H, 0, Alias("model.norm.weight"));
-  s.lm_head = add("lm_head.weight", 1, 0, uint64_t(s.geo[kHead].n) * s.geo[kHead].k, 0,
-                  Pages(Alias("lm_head.weight", Shard(0, s.tp)), page_k(kHead), page_n));
+  const std::string head_source = Alias("lm_head.weight", Shard(0, s.tp));
+  s.lm_head = add("lm_head.weight", 1, weight_dtype, uint64_t(s.geo[kHead].n) * s.geo[kHead].k, 0, weight_pages(head_source, kHead));
+  s.lm_head_scale = scale_of("lm_head.scale", head_source, s.geo[kHead].n);
   return s;
 }
 

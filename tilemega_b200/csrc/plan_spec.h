@@ -25,6 +25,7 @@ struct BufferSpec {
 // Index of the buffers the runtime binds, into PlanSpec::buffers.
 struct LayerBuffers {
   int norm1, qkv, k, v, o, norm2, gate_up, down, router = -1, q_norm = -1, k_norm = -1;
+  int qkv_scale = -1, o_scale = -1, gate_up_scale = -1, down_scale = -1;   // e4m3 weight plans: fp32 row scales
 };
 
 struct PlanSpec {
@@ -50,6 +51,8 @@ struct PlanSpec {
   GemvGeo geo[kNumGemv] = {};   // stages a plan does not have (kRouter in a dense plan) stay zero
   // dense-batch plans (batch_hi > kMaxBatch): GEMM stages on tcgen05 tiles; geo[] then describes the
   // page stream only (one task = cps pages of 128 rows x 128 columns)
+  bool fp8 = false;             // GEMV matrices as e4m3 bytes + fp32 row scales
+  int lm_head_scale = -1;
   bool dense_batch = false;
   DenseGeo dgeo[kNumGemv] = {};
   int normed_buf = -1;

@@ -122,7 +122,7 @@ Plan* AsPlan(void* handle) {
   return plan && plan->magic == kMagic ? plan : nullptr;
 }
 
-uint64_t ElementBytes(uint32_t dtype) { return dtype == TM_DTYPE_BF16 ? 2 : 4; }
+uint64_t ElementBytes(uint32_t dtype) { return dtype == TM_DTYPE_BF16 ? 2 : dtype == TM_DTYPE_E4M3 ? 1 : 4; }
 
 cudaError_t Alloc(Plan& plan, void** out, size_t bytes) {
   cudaError_t err = cudaMalloc(out, bytes ? bytes : 16);
@@ -395,14 +395,18 @@ void* tm_plan_create(int batch, void* const* external, int device) {
   p.embed = plan->buffer_ptr[s.embed];
   p.final_norm = plan->buffer_ptr[s.final_norm];
   p.lm_head = plan->buffer_ptr[s.lm_head];
+  p.fp8 = s.fp8 ? 1 : 0;
+  p.lm_head_scale = s.fp8 ? static_cast<const float*>(plan->buffer_ptr[size_t(s.lm_head_scale)]) : nullptr;
   std::vector<tmb::LayerPtrs> layers(size_t(s.layers));
   for (int l = 0; l < s.layers; ++l) {
     const tmb::LayerBuffers& lb = s.layer[size_t(l)];
     auto optional = [&](int index) -> const void* { return index >= 0 ? plan->buffer_ptr[size_t(index)] : nullptr; };
-    layers[size_t(l)] = tmb::LayerPtrs{plan->buffer_ptr[lb.qkv],   plan->buffer_ptr[lb.o],     plan->buffer_ptr[lb.gate_up],
-                                       plan->buffer_ptr[lb.down],  plan->buffer_ptr[lb.norm1], plan->buffer_ptr[lb.norm2],
-                                       optional(lb.router),        optional(lb.q_norm),        optional(lb.k_norm),
-                                       plan->buffer_ptr[lb.k],     plan->buffer_ptr[lb.v]};
+    auto scale = [&](int index) { return static_cast<const float*>(optional(index)); };
+    layers[size_t(l)] = tmb::LayerPtrs{scale(lb.qkv_scale),        scale(lb.o_scale),          scale(lb.gate_up_scale),
+                                       scale(lb.down_scale),       plan->buffer_ptr[lb.qkv],   plan->buffer_ptr[lb.o],
+                                       plan->buffer_ptr[lb.gate_up], plan->buffer_ptr[lb.down], plan->buffer_ptr[lb.norm1],
+                                       plan->buffer_ptr[lb.norm2], optional(lb.router),        optional(lb.q_norm),
+                                       optional(lb.k_norm),        plan->buffer_ptr[lb.k],     plan->buffer_ptr[lb.v]};
   }
   {
     void* dev = nullptr;

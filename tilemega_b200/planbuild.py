@@ -31,7 +31,8 @@ def plan_document(config: dict, *, batch_lo: int = 1, batch_hi: int | None = Non
                   kv_layout: str = "contiguous", num_blocks: int = 0, geometry: dict | None = None,
                   grid: int = 0, slots: int = 0, write_logits: bool = True,
                   tp: int = 1,
-                  attn_min_slots: int | None = None, prefetch_window: int | None = None) -> dict:
+                  attn_min_slots: int | None = None, prefetch_window: int | None = None,
+                  weights: str = "bf16") -> dict:
     """The sidecar for one decode plan; raises ValueError on shapes the kernels do not cover."""
     model = {key: config[key] for key in MODEL_KEYS if key in config}
     model.setdefault("head_dim", config["hidden_size"] // config["num_attention_heads"])
@@ -61,6 +62,10 @@ def plan_document(config: dict, *, batch_lo: int = 1, batch_hi: int | None = Non
     }
     if tp > 1:
         document["tp"] = tp   # the plan is ONE rank's: every rank loads the same library
+    if weights not in ("bf16", "e4m3"):
+        raise ValueError("weights must be 'bf16' or 'e4m3'")
+    if weights == "e4m3":
+        document["weights"] = "e4m3"   # GEMV matrices as e4m3 bytes + one fp32 scale per output row
     if prefetch_window is not None:
         document["prefetch_window"] = prefetch_window   # weight pages pulled into L2 ahead of a full ring (0: off)
     if attn_min_slots is not None:

@@ -15,7 +15,8 @@ import torch
 
 from .plan import Buffer, PlanLibrary
 
-DTYPES = {0: torch.bfloat16, 1: torch.float32, 2: torch.int32}
+DTYPES = {0: torch.bfloat16, 1: torch.float32, 2: torch.int32, 4: torch.uint8}   # 4: e4m3 bytes (an addition of this library)
+E4M3_MAX = 448.0
 
 
 def _tied_name(name: str, known, tied: bool) -> str:
@@ -79,7 +80,7 @@ def tile_pages(weight: torch.Tensor, tile_n: int, tile_k: int) -> torch.Tensor:
     """
     if weight.ndim != 2 or tile_n <= 0 or tile_k <= 0 or tile_n % 8 or tile_k % 64:
         raise ValueError("invalid tile_pages source or geometry")
-    if weight.is_cuda and weight.dtype == torch.bfloat16 and weight.shape[1] % 8 == 0:
+    if weight.is_cuda and weight.element_size() == 2 and weight.shape[1] % 8 == 0:
         return tile_pages_on_device(weight, tile_n, tile_k)
     return tile_pages_by_indexing(weight, tile_n, tile_k)
 
@@ -101,7 +102,7 @@ def tile_pages_on_device(weight: torch.Tensor, tile_n: int, tile_k: int) -> torc
         weight = weight.contiguous()
     n, k = weight.shape
     pages = -(-n // tile_n) * -(-k // tile_k)
-    packed = torch.empty(pages * tile_n * tile_k, dtype=torch.bfloat16, device=weight.device)
+    packed = torch.empty(pages * tile_n * tile_k, dtype=weight.dtype, device=weight.device)
     with torch.cuda.device(weight.device):
         status = _PACKER(weight.data_ptr(), n, k, weight.stride(0), tile_n, tile_k, packed.data_ptr(),
                          torch.cuda.current_stream().cuda_stream)
@@ -179,8 +180,34 @@ def expert_matrices(recipe: Mapping[str, object], source: Callable[[str], torch.
             yield down
 
 
+def quantize_e4m3(matrix: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """Row-wise e4m3 quantisation of a weight matrix [N][K]: scale[n] = max_k |W[n][k]| / 448 (1 for an
+    all-zero row), code[n][k] = e4m3(W[n][k] / scale[n]) rounded to nearest even. Returns the codes as
+    uint8 [N][K] and the scales as float32 [N]; code * scale is the weight the kernel multiplies with."""
+    if matrix.ndim != 2:
+        raise ValueError("e4m3 quantisation takes a matrix")
+    values = matrix.float()
+    peak = values.abs().amax(dim=1)
+    scale = torch.where(peak > 0, peak / E4M3_MAX, torch.ones_like(peak))
+    codes = (values / scale[:, None]).clamp_(-E4M3_MAX, E4M3_MAX).to(torch.float8_e4m3fn)
+    return codes.view(torch.uint8), scale
+
+
+def dequantize_e4m3(codes: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    """float32 [N][K]: the weights an e4m3 plan computes with."""
+    return codes.view(torch.float8_e4m3fn).float() * scale[:, None].float()
+
+
 def pack(recipe: Mapping[str, object], source: Callable[[str], torch.Tensor], tp_rank: int = 0) -> torch.Tensor:
     kind = recipe["kind"]
+    if kind in ("e4m3_pairs", "e4m3_scale"):
+        # the inner recipe's matrix (this rank's slice, rows already interleaved), quantised row by row
+        codes, scale = quantize_e4m3(pack(recipe["source"], source, tp_rank))
+        if kind == "e4m3_scale":
+            return scale.contiguous()
+        if codes.shape[1] % 2:
+            raise ValueError("e4m3 weight rows need an even number of columns")
+        return codes.contiguous().view(torch.bfloat16)   # two codes per 2-byte unit: tile_pages applies unchanged
     source = sharded(recipe, source, tp_rank)
     if kind == "alias":
         return source(str(recipe["source"]))
@@ -240,7 +267,9 @@ def load_weights(checkpoint: str | Path | Checkpoint | TensorCheckpoint, *plans:
     for name, buffer in weight_recipes(*plans).items():
         if buffer.pack_json not in packed:
             recipe = json.loads(buffer.pack_json)
-            dtype = DTYPES[buffer.dtype]
+            # checkpoint tensors are staged in the model dtype; e4m3 codes and their scales are both derived from that
+            derived = buffer.dtype == 4 or recipe.get("kind") == "e4m3_scale"
+            dtype = torch.bfloat16 if derived else DTYPES[buffer.dtype]
             staged: dict[str, torch.Tensor] = {}
 
             def source(fqn: str) -> torch.Tensor:
@@ -250,6 +279,8 @@ def load_weights(checkpoint: str | Path | Checkpoint | TensorCheckpoint, *plans:
 
             packed[buffer.pack_json] = pack(recipe, source, tp_rank).contiguous()
         tensor = packed[buffer.pack_json]
+        if buffer.dtype == 4:
+            tensor = packed[buffer.pack_json] = tensor.view(torch.uint8)   # one element per e4m3 byte
         if tensor.numel() != buffer.elements_constant:
             raise ValueError(f"{name} has {tensor.numel()} elements; plan expects {buffer.elements_constant}")
         result[name] = tensor
