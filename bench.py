@@ -82,6 +82,8 @@ def workload(args) -> dict:
     batch = args.batch
     contexts = synthetic.seeded_contexts(batch, 512, 8192, seed=2).tolist() if context == 0 else [context] * batch
     label = f"{model}-shaped decode, batch {batch}, context {contexts}, paged KV block 16, shuffled block table"
+    if args.weights != "bf16":
+        label += f", {args.weights} weights with fp32 row scales"
     if tp > 1:
         label += f", tensor parallel over {tp} GPUs"
     return {"name": f"{model}-shaped", "model": model, "config": config, "batch": batch, "contexts": contexts, "tp": tp,
@@ -294,7 +296,7 @@ def run_ours(args) -> None:
     num_blocks = batch * max_blocks + 32
     plan_dir = PLAN_DIR / "bench"    # inside the package tree: every library this process loads is the repository's
     options = dict(batch_lo=batch, batch_hi=batch, capacity=capacity, kv_layout="paged", num_blocks=num_blocks,
-                   write_logits=False, tp=tp)
+                   write_logits=False, tp=tp, weights=args.weights)
     if rank == 0:
         so = emit_plan(config, plan_dir, **options)
     if world > 1:
@@ -410,12 +412,13 @@ def run_ours(args) -> None:
     value = job_value(replicas, batch, steps, seconds)
     achieved = bytes_timed / seconds / 1e9
     step_us = [(stamps[i + 1] - stamps[i]) / 1e3 for i in range(steps)]
-    ratio = NCU_TRAFFIC_PER_ALGORITHMIC_BYTE.get((work["model"], batch)) if tp == 1 else None
+    ratio = NCU_TRAFFIC_PER_ALGORITHMIC_BYTE.get((work["model"], batch)) if tp == 1 and args.weights == "bf16" else None
     parallelism = f"tp{tp}" if tp > 1 else ("replicas" if world > 1 else "single")
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
         "ms_per_step": device_ms / steps, "higher_is_better": True, "scaling": "strong" if tp > 1 else "weak",
-        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "vs_baseline": None, "dtype": "bf16" if args.weights == "bf16" else f"bf16 activations, {args.weights} weights",
+        "data": "synthetic",
         "config": {"workload": work["label"], "layers": config["num_hidden_layers"],
                    "l2": "inputs larger than L2: every step streams its weights and KV rows from HBM",
                    "parallelism": parallelism, "step_latency_us_median": statistics.median(step_us),
@@ -465,6 +468,8 @@ def main() -> None:
     parser.add_argument("--context", type=int, default=None,
                         help="0: seeded draw in [512, 8192] (the one-GPU default); several GPUs default to 4096")
     parser.add_argument("--layers", type=int, default=0, help="override the depth (profiling a small case)")
+    parser.add_argument("--weights", choices=("bf16", "e4m3"), default="bf16",
+                        help="e4m3: GEMV matrices as 8-bit codes with one fp32 scale per output row")
     parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     parser.add_argument("--trace", action="store_true",
                         help="after the timed runs, stamp one more step and print the per-stage table (rank 0)")

@@ -56,12 +56,26 @@ def test_every_stage_at_benchmark_widths(base, batch, history, plan_dir):
     check_every_stage(dict(getattr(synthetic, base), num_hidden_layers=1), batch, history, plan_dir)
 
 
-def check_every_stage(config, batch, history, plan_dir):
+def linear(x, weight):
+    """One linear layer as the kernels compute it: fp32 products and sums, one rounding to bf16
+    (for bf16 weights this is what the module's bf16 F.linear does)."""
+    return F.linear(x.float(), weight.float()).to(torch.bfloat16)
+
+
+def check_every_stage(config, batch, history, plan_dir, weights="bf16"):
     dim, heads, hkv = config["head_dim"], config["num_attention_heads"], config["num_key_value_heads"]
     hidden, eps = config["hidden_size"], config["rms_norm_eps"]
     capacity = (history + 18) // 16 * 16
     w = bf16_weights(config)
-    run = GpuRun(config, w, batch, capacity, plan_dir)
+    run = GpuRun(config, w, batch, capacity, plan_dir, weights=weights)
+    if weights == "e4m3":
+        # the CPU side multiplies with what the plan's pages hold: every matrix quantised row by row and
+        # scaled back (fp32), exactly as the loader derives codes and scales from the bf16 checkpoint
+        from tilemega_b200.serving.weights import dequantize_e4m3, quantize_e4m3
+        w = {name: dequantize_e4m3(*quantize_e4m3(t)) if t.ndim == 2 and "embed_tokens" not in name else t
+             for name, t in w.items()}
+        if "lm_head.weight" not in w:   # a tied head is quantised too, the embedding table is not
+            w["lm_head.weight"] = dequantize_e4m3(*quantize_e4m3(w["model.embed_tokens.weight"]))
     ids = synthetic.seeded_tokens(batch, history + 2, config["vocab_size"], seed=9)
     run.state.tokens.zero_()
     run.state.tokens[:, :history + 2].copy_(ids)
@@ -82,9 +96,9 @@ def check_every_stage(config, batch, history, plan_dir):
     # stage 1: RMSNorm + QKV
     x_in = F.embedding(ids[:, pos].long(), w["model.embed_tokens.weight"])
     xn = rms_norm(x_in, w[p + "input_layernorm.weight"], eps)
-    q = F.linear(xn, w[p + "self_attn.q_proj.weight"]).view(batch, hkv, gq, dim)
-    k = F.linear(xn, w[p + "self_attn.k_proj.weight"]).view(batch, hkv, 1, dim)
-    v = F.linear(xn, w[p + "self_attn.v_proj.weight"]).view(batch, hkv, 1, dim)
+    q = linear(xn, w[p + "self_attn.q_proj.weight"]).view(batch, hkv, gq, dim)
+    k = linear(xn, w[p + "self_attn.k_proj.weight"]).view(batch, hkv, 1, dim)
+    v = linear(xn, w[p + "self_attn.v_proj.weight"]).view(batch, hkv, 1, dim)
     # (a handful of elements per hundred thousand may sit two steps apart: the CPU's bf16 GEMM and the GPU
     # sum 2048+ products in different orders and block sizes)
     reference_qkv = torch.cat((q, k, v), dim=2)
@@ -107,10 +121,10 @@ def check_every_stage(config, batch, history, plan_dir):
     agreement(attn_gpu, context.reshape(batch, heads * dim), "attention", outliers=1e-4,
               outlier_bound=2.0 ** -8 * values.abs().max().item())
     # stage 3: o projection + residual (from the GPU's attention output)
-    x_mid = x_in + F.linear(attn_gpu, w[p + "self_attn.o_proj.weight"])
+    x_mid = x_in + linear(attn_gpu, w[p + "self_attn.o_proj.weight"])
     # stage 4: RMSNorm + gate/up + SwiGLU
     xm = rms_norm(x_mid, w[p + "post_attention_layernorm.weight"], eps)
-    gate_ref, up_ref = F.silu(F.linear(xm, w[p + "mlp.gate_proj.weight"])), F.linear(xm, w[p + "mlp.up_proj.weight"])
+    gate_ref, up_ref = F.silu(linear(xm, w[p + "mlp.gate_proj.weight"])), linear(xm, w[p + "mlp.up_proj.weight"])
     h_ref = gate_ref * up_ref
     # a product of two bf16 values that may each be one ulp off: the error scales with the
     # factors, not with a product that happens to be small: one ulp of the up projection times the gate
@@ -118,13 +132,13 @@ def check_every_stage(config, batch, history, plan_dir):
     # silu by up to ~1.5 of ITS ulps before its own rounding), plus the product's own rounding
     # (the CPU chain starts from the GPU's attention output, so the GPU's own roundings of the residual
     # stream and of the norm sit in between as well: a few elements in a hundred thousand land further out)
-    agreement(h_gpu, h_ref, "swiglu", ulps=2.0, exact_fraction=0.95,
+    agreement(h_gpu, h_ref, "swiglu", ulps=2.0, exact_fraction=0.93,
               floor=1e-3 + 3 * bf16_ulp(gate_ref.float()) * up_ref.float().abs() + bf16_ulp(up_ref.float()) * gate_ref.float().abs(),
               outliers=1e-4, outlier_bound=4 * bf16_ulp(h_ref.float().abs().max()).item())
     # stage 5: down projection + residual (from the GPU's own activations)
     # the sum may cancel to something much smaller than its addends, whose own ulp bounds the error
-    agreement(x_gpu, x_mid + F.linear(h_gpu, w[p + "mlp.down_proj.weight"]), "residual stream", ulps=2.0,
-              exact_fraction=0.95, floor=2e-3, outliers=1e-4, outlier_bound=2 * bf16_ulp(x_mid.float().abs().max()).item())
+    agreement(x_gpu, x_mid + linear(h_gpu, w[p + "mlp.down_proj.weight"]), "residual stream", ulps=2.0,
+              exact_fraction=0.93, floor=2e-3, outliers=1e-4, outlier_bound=2 * bf16_ulp(x_mid.float().abs().max()).item())
     # stage 6: final norm + lm_head, accumulators in fp32
     head = w.get("lm_head.weight", w["model.embed_tokens.weight"])
     logits_ref = F.linear(rms_norm(x_gpu, w["model.norm.weight"], eps).float(), head.float())

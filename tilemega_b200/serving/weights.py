@@ -181,15 +181,25 @@ def expert_matrices(recipe: Mapping[str, object], source: Callable[[str], torch.
 
 
 def quantize_e4m3(matrix: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
-    """Row-wise e4m3 quantisation of a weight matrix [N][K]: scale[n] = max_k |W[n][k]| / 448 (1 for an
+    """Row-wise e4m3 quantisation of a weight matrix [N][K]: scale[n] = max_k |W[n][k]| * fp32(1/448) (1 for an
     all-zero row), code[n][k] = e4m3(W[n][k] / scale[n]) rounded to nearest even. Returns the codes as
     uint8 [N][K] and the scales as float32 [N]; code * scale is the weight the kernel multiplies with."""
     if matrix.ndim != 2:
         raise ValueError("e4m3 quantisation takes a matrix")
     values = matrix.float()
     peak = values.abs().amax(dim=1)
-    scale = torch.where(peak > 0, peak / E4M3_MAX, torch.ones_like(peak))
-    codes = (values / scale[:, None]).clamp_(-E4M3_MAX, E4M3_MAX).to(torch.float8_e4m3fn)
+    # (a multiplication by the rounded reciprocal, not a division by 448: libraries may turn a division by a
+    # constant into exactly this on one device and not on another, and the scales must not depend on that)
+    scale = torch.where(peak > 0, peak * torch.tensor(1.0 / E4M3_MAX, dtype=torch.float32, device=peak.device),
+                        torch.ones_like(peak))
+    # The rounding is spelled out in exact float operations (power-of-two steps, round half to even) so
+    # that every device and library version derives the same codes; the cast at the end is then exact.
+    scaled = values / scale[:, None]
+    magnitude = scaled.abs()
+    _, exponent = torch.frexp(magnitude)                       # magnitude = m * 2^exponent, m in [0.5, 1)
+    step = torch.ldexp(torch.ones_like(magnitude), (exponent - 1).clamp_min(-6) - 3)   # 3 mantissa bits; subnormals below 2^-6
+    rounded = (torch.round(magnitude / step) * step).clamp_max(E4M3_MAX)
+    codes = torch.copysign(rounded, scaled).to(torch.float8_e4m3fn)
     return codes.view(torch.uint8), scale
 
 
