@@ -17,10 +17,16 @@ pytestmark = pytest.mark.gpu
 LOGIT_TOLERANCE = 2e-2
 
 
-def held_weights(weights, dtype):
-    """What an e4m3 plan multiplies with, as `dtype` tensors for the oracle."""
-    out = {name: (dequantize_e4m3(*quantize_e4m3(t)) if t.ndim == 2 and "embed_tokens" not in name else t.float()).to(dtype)
-           for name, t in weights.items()}
+def held_weights(weights, dtype, ranks=1):
+    """What an e4m3 plan multiplies with, as `dtype` tensors for the oracle. A tensor-parallel rank
+    quantises its own slice: the column-sharded matrices (o, down) get their row scales per column part."""
+    def held(name, t):
+        if t.ndim != 2 or "embed_tokens" in name:
+            return t.float()
+        if ranks > 1 and (name.endswith("o_proj.weight") or name.endswith("down_proj.weight")):
+            return torch.cat([dequantize_e4m3(*quantize_e4m3(part.contiguous())) for part in t.chunk(ranks, dim=1)], dim=1)
+        return dequantize_e4m3(*quantize_e4m3(t))
+    out = {name: held(name, t).to(dtype) for name, t in weights.items()}
     if "lm_head.weight" not in out:
         out["lm_head.weight"] = dequantize_e4m3(*quantize_e4m3(weights["model.embed_tokens.weight"])).to(dtype)
     return out
@@ -62,3 +68,27 @@ def test_e4m3_decode_matches_the_forward_with_the_held_weights(plan_dir):
     _, plain_logits = plain.greedy(prompt, new_tokens)
     plain.close()
     assert (plain_logits - logits).abs().max().item() > 1e-3
+
+
+@pytest.mark.parametrize("base,ranks,batch", [("TINY_D128", 2, 2), ("TINY_GQ8", 2, 1)])
+def test_e4m3_tensor_parallel_ranks_on_one_device(base, ranks, batch, plan_dir):
+    """The benchmark's tensor-parallel configuration in its e4m3 variant: every rank quantises its own
+    slices; the ranks run as one cooperative launch on this GPU (tests/test_gpu_tp_one_device.py)."""
+    from test_gpu_tp_one_device import RanksOnOneDevice
+    config = dict(getattr(synthetic, base), tie_word_embeddings=False)
+    prompt_len, new_tokens, capacity = 11, 5, 32
+    weights = bf16_weights(config)
+    prompt = synthetic.seeded_tokens(batch, prompt_len, config["vocab_size"], seed=1)
+    run = RanksOnOneDevice(config, weights, batch, capacity, plan_dir, ranks, weights="e4m3")
+    tokens, logits = run.greedy(prompt, new_tokens)
+    run.close()
+
+    def forced(dtype):
+        decoder = OracleDecoder(config, held_weights(weights, dtype, ranks), dtype, capacity, tp=ranks)
+        return decoder.greedy(prompt, new_tokens, PagedKV(config, batch, capacity, dtype), forced=tokens, head_fp32=True)[1]
+
+    exact, module = forced(torch.float32), forced(torch.bfloat16)
+    ours, theirs = (logits - exact).abs(), (module - exact).abs()
+    assert ours.max().item() <= 1.25 * theirs.max().item(), (ours.max().item(), theirs.max().item())
+    assert ours.mean().item() <= 1.25 * theirs.mean().item(), (ours.mean().item(), theirs.mean().item())
+    assert_parity(tokens, logits, exact, max(LOGIT_TOLERANCE, 1.25 * theirs.max().item()), f"e4m3 {base} tp{ranks}")

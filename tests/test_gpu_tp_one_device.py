@@ -38,18 +38,19 @@ WIDE_70B_LAYER = dict(synthetic.LLAMA_3_1_70B, num_hidden_layers=1, vocab_size=1
 class RanksOnOneDevice:
     """T rank plans of one library on cuda:0, bound to one another's regions, launched together."""
 
-    def __init__(self, config, weights_cpu, batch, capacity, plan_dir, ranks):
+    def __init__(self, config, weights_cpu, batch, capacity, plan_dir, ranks, weights="bf16"):
         sms = torch.cuda.get_device_properties(0).multi_processor_count
-        so = emit_plan(config, plan_dir, batch_lo=batch, batch_hi=batch, capacity=capacity, tp=ranks, grid=sms // ranks)
+        so = emit_plan(config, plan_dir, batch_lo=batch, batch_hi=batch, capacity=capacity, tp=ranks, grid=sms // ranks,
+                       weights=weights)
         self.lib = PlanLibrary(so)
         self.ranks, self.batch, self.config = ranks, batch, config
         checkpoint = TensorCheckpoint(weights_cpu, config.get("tie_word_embeddings", False))
         self.weights, self.states, self.plans = [], [], []
         for rank in range(ranks):
-            weights = load_weights(checkpoint, self.lib, device="cuda:0", tp=(rank, ranks))
+            packed = load_weights(checkpoint, self.lib, device="cuda:0", tp=(rank, ranks))
             state = allocate_state(config, batch, self.lib, "cuda:0", tp=ranks)
-            pointers = {name: tensor.data_ptr() for name, tensor in weights.items()} | state.pointers
-            self.weights.append(weights)
+            pointers = {name: tensor.data_ptr() for name, tensor in packed.items()} | state.pointers
+            self.weights.append(packed)
             self.states.append(state)
             self.plans.append(self.lib.create(batch, pointers, 0))
         # every rank's receive region and exchange block: zeroed device memory, here all on one device

@@ -23,13 +23,19 @@ def test_static_probe_agrees_with_plan_probe_twice_in_a_row(plan_dir):
     lib = run.lib
     waiters = 3
     records = torch.full((waiters, 12), 7, dtype=torch.int64, device="cuda:0")   # caller-owned output
+    # the first call may load the kernel's module (lazy loading takes device memory once); from the second on the
+    # driver's own count of free device memory must not move either, which also covers cudaMalloc calls that
+    # bypass torch's allocator
+    lib.watchdog_probe_static(0, waiters, False, 3000, records.data_ptr(), run.stream)
+    torch.cuda.synchronize()
     for withhold in (True, False, True, False):        # two rounds in a row: the shared scratch must be cleared each time
         expected = run.plan.watchdog_probe(withhold=withhold, limit_us=3000)
         records.fill_(7)
-        before = torch.cuda.memory_allocated()
+        before, free_before = torch.cuda.memory_allocated(), torch.cuda.mem_get_info()[0]
         lib.watchdog_probe_static(0, waiters, withhold, 3000, records.data_ptr(), run.stream)
         torch.cuda.synchronize()
         assert torch.cuda.memory_allocated() == before
+        assert torch.cuda.mem_get_info()[0] == free_before
         host = records.cpu()
         assert host[:, 0].tolist() == [int(expected)] * waiters            # gave up exactly when the plan-based probe did
         assert host[:, 2].tolist() == [1, 2, 3]                            # waiting CTA

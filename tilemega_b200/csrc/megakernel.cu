@@ -2650,6 +2650,41 @@ static cudaError_t run_batch(const MegaParams& p, size_t smem_bytes, cudaStream_
 // one serves unsharded dense plans and carries none of the code below; the extended one
 // (TMB_EXTENDED) adds tensor parallelism, mixture of experts and the QK norm, for
 // head_dim 128; a third one (TMB_DENSE) holds the dense-batch kernel.
+#if (TMB_EXTENDED || TMB_FP8) && !TMB_DENSE
+template <int B, int GQ, int X>
+static cudaError_t run_ranks_instance(const MegaParams* ranks_dev, int count, int total_grid, size_t smem_bytes,
+                                      cudaStream_t stream) {
+  auto kernel = decode_megakernel_ranks<B, 128, GQ, X>;
+  cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem_bytes));
+  if (err != cudaSuccess) return err;
+  void* args[] = {static_cast<void*>(&ranks_dev), static_cast<void*>(&count)};
+  // cooperative: the launch fails unless every CTA of every rank is resident at once
+  return cudaLaunchCooperativeKernel(reinterpret_cast<void*>(kernel), dim3(unsigned(total_grid)), dim3(kThreads), args,
+                                     smem_bytes, stream);
+}
+
+// `first` is the host copy of ranks_dev[0]: all ranks of a job share one plan geometry.
+template <int X>
+static cudaError_t run_ranks(const MegaParams& first, const MegaParams* ranks_dev, int count, int total_grid, cudaStream_t stream) {
+  const size_t smem_bytes = size_t(ring_offset(first.xs_bytes, first.batch) + first.nslots * kSlotBytes);
+  if (first.kv_heads <= 0 || first.heads % first.kv_heads || first.head_dim != 128 || first.experts > 0 || first.qk_norm)
+    return cudaErrorInvalidValue;
+  const int gq = first.heads / first.kv_heads;
+  if (gq != 4 && gq != 8) return cudaErrorInvalidValue;
+  switch (first.batch) {
+    case 1: return gq == 8 ? run_ranks_instance<1, 8, X>(ranks_dev, count, total_grid, smem_bytes, stream)
+                           : run_ranks_instance<1, 4, X>(ranks_dev, count, total_grid, smem_bytes, stream);
+    case 2: return gq == 8 ? run_ranks_instance<2, 8, X>(ranks_dev, count, total_grid, smem_bytes, stream)
+                           : run_ranks_instance<2, 4, X>(ranks_dev, count, total_grid, smem_bytes, stream);
+    case 3: return gq == 8 ? run_ranks_instance<3, 8, X>(ranks_dev, count, total_grid, smem_bytes, stream)
+                           : run_ranks_instance<3, 4, X>(ranks_dev, count, total_grid, smem_bytes, stream);
+    case 4: return gq == 8 ? run_ranks_instance<4, 8, X>(ranks_dev, count, total_grid, smem_bytes, stream)
+                           : run_ranks_instance<4, 4, X>(ranks_dev, count, total_grid, smem_bytes, stream);
+    default: return cudaErrorInvalidValue;   // the one-device form is built for batch 1..4
+  }
+}
+#endif
+
 #if TMB_DENSE
 #elif TMB_FP8
 cudaError_t run_decode_fp8(const MegaParams& p, cudaStream_t stream, bool prepare) {
@@ -2659,6 +2694,11 @@ cudaError_t run_decode_fp8(const MegaParams& p, cudaStream_t stream, bool prepar
   if (gq == 8) return run_batch<128, 8, kXFp8 | kXTp>(p, smem_bytes, stream, prepare);
   if (gq == 4) return run_batch<128, 4, kXFp8 | kXTp>(p, smem_bytes, stream, prepare);
   return cudaErrorInvalidValue;
+}
+
+cudaError_t run_decode_ranks_fp8(const MegaParams& first, const MegaParams* ranks_dev, int count, int total_grid,
+                                 cudaStream_t stream) {
+  return run_ranks<kXFp8 | kXTp>(first, ranks_dev, count, total_grid, stream);
 }
 #elif TMB_EXTENDED
 cudaError_t run_decode_extended(const MegaParams& p, cudaStream_t stream, bool prepare) {
@@ -2675,37 +2715,9 @@ cudaError_t run_decode_extended(const MegaParams& p, cudaStream_t stream, bool p
                  : run_batch<128, 4, kXTp>(p, smem_bytes, stream, prepare);
 }
 
-template <int B, int GQ>
-static cudaError_t run_ranks_instance(const MegaParams* ranks_dev, int count, int total_grid, size_t smem_bytes,
-                                      cudaStream_t stream) {
-  auto kernel = decode_megakernel_ranks<B, 128, GQ, kXTp>;
-  cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem_bytes));
-  if (err != cudaSuccess) return err;
-  void* args[] = {static_cast<void*>(&ranks_dev), static_cast<void*>(&count)};
-  // cooperative: the launch fails unless every CTA of every rank is resident at once
-  return cudaLaunchCooperativeKernel(reinterpret_cast<void*>(kernel), dim3(unsigned(total_grid)), dim3(kThreads), args,
-                                     smem_bytes, stream);
-}
-
-// `first` is the host copy of ranks_dev[0]: all ranks of a job share one plan geometry.
 cudaError_t run_decode_ranks(const MegaParams& first, const MegaParams* ranks_dev, int count, int total_grid,
                              cudaStream_t stream) {
-  const size_t smem_bytes = size_t(ring_offset(first.xs_bytes, first.batch) + first.nslots * kSlotBytes);
-  if (first.kv_heads <= 0 || first.heads % first.kv_heads || first.head_dim != 128 || first.experts > 0 || first.qk_norm)
-    return cudaErrorInvalidValue;
-  const int gq = first.heads / first.kv_heads;
-  if (gq != 4 && gq != 8) return cudaErrorInvalidValue;
-  switch (first.batch) {
-    case 1: return gq == 8 ? run_ranks_instance<1, 8>(ranks_dev, count, total_grid, smem_bytes, stream)
-                           : run_ranks_instance<1, 4>(ranks_dev, count, total_grid, smem_bytes, stream);
-    case 2: return gq == 8 ? run_ranks_instance<2, 8>(ranks_dev, count, total_grid, smem_bytes, stream)
-                           : run_ranks_instance<2, 4>(ranks_dev, count, total_grid, smem_bytes, stream);
-    case 3: return gq == 8 ? run_ranks_instance<3, 8>(ranks_dev, count, total_grid, smem_bytes, stream)
-                           : run_ranks_instance<3, 4>(ranks_dev, count, total_grid, smem_bytes, stream);
-    case 4: return gq == 8 ? run_ranks_instance<4, 8>(ranks_dev, count, total_grid, smem_bytes, stream)
-                           : run_ranks_instance<4, 4>(ranks_dev, count, total_grid, smem_bytes, stream);
-    default: return cudaErrorInvalidValue;   // the one-device form is built for batch 1..4
-  }
+  return run_ranks<kXTp>(first, ranks_dev, count, total_grid, stream);
 }
 #else
 cudaError_t run_decode_extended(const MegaParams& p, cudaStream_t stream, bool prepare);
@@ -2713,6 +2725,8 @@ cudaError_t run_decode_dense(const MegaParams& p, cudaStream_t stream, bool prep
 cudaError_t run_decode_fp8(const MegaParams& p, cudaStream_t stream, bool prepare);
 cudaError_t run_decode_ranks(const MegaParams& first, const MegaParams* ranks_dev, int count, int total_grid,
                              cudaStream_t stream);
+cudaError_t run_decode_ranks_fp8(const MegaParams& first, const MegaParams* ranks_dev, int count, int total_grid,
+                                 cudaStream_t stream);
 
 static cudaError_t run_decode(const MegaParams& p, cudaStream_t stream, bool prepare) {
   if (p.dense) return run_decode_dense(p, stream, prepare);
@@ -2746,7 +2760,8 @@ extern "C" int tmb_launch_decode(const tmb::MegaParams* p, void* stream) {
 
 extern "C" int tmb_launch_decode_ranks(const tmb::MegaParams* first, const tmb::MegaParams* ranks_dev, int count,
                                        int total_grid, void* stream) {
-  return int(tmb::run_decode_ranks(*first, ranks_dev, count, total_grid, static_cast<cudaStream_t>(stream)));
+  return int(first->fp8 ? tmb::run_decode_ranks_fp8(*first, ranks_dev, count, total_grid, static_cast<cudaStream_t>(stream))
+                        : tmb::run_decode_ranks(*first, ranks_dev, count, total_grid, static_cast<cudaStream_t>(stream)));
 }
 
 extern "C" int tmb_launch_watchdog_probe(const tmb::MegaParams* p, int withhold, void* stream) {

@@ -109,7 +109,8 @@ def shuffled_block_table(batch: int, max_blocks: int, num_blocks: int, seed: int
 
 def allocate_state(config: dict, batch: int, decode: PlanLibrary, device: str | torch.device = "cuda",
                    block_table: torch.Tensor | None = None,
-                   context_base: torch.Tensor | None = None, tp: int = 1) -> ServingState:
+                   context_base: torch.Tensor | None = None, tp: int = 1,
+                   shared_blocks: bool = False) -> ServingState:
     """`tp`: a tensor-parallel rank's state holds only its num_key_value_heads / tp KV heads
     (reference state.py:64-82); token state and RoPE tables are whole on every rank."""
     if decode.info.phase != 1:
@@ -140,7 +141,9 @@ def allocate_state(config: dict, batch: int, decode: PlanLibrary, device: str | 
             raise ValueError("block table must be int32 [batch][capacity/16]")
         if int(table.min()) < 0 or int(table.max()) >= num_blocks:
             raise ValueError("block table entry outside the pool")
-        if table.reshape(-1).unique().numel() != table.numel():
+        # a static batch owns every block it names; a scheduler that parks idle rows on one scratch block
+        # (serving/continuous.py) passes shared_blocks=True and keeps the live rows disjoint itself
+        if not shared_blocks and table.reshape(-1).unique().numel() != table.numel():
             raise ValueError("block table maps two logical blocks to one pool block")
         table = table.to(device).contiguous()
         base = (context_base if context_base is not None else torch.zeros(batch, dtype=torch.int32))
