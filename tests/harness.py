@@ -15,12 +15,14 @@ class GpuRun:
     """One plan + state + weights on cuda:0."""
 
     def __init__(self, config, weights_cpu, batch, capacity, plan_dir, kv_layout="contiguous",
-                 block_table=None, context_base=None, num_blocks=0, geometry=None, slots=0, grid=0, weights="bf16"):
+                 block_table=None, context_base=None, num_blocks=0, geometry=None, slots=0, grid=0, weights="bf16",
+                 attn_min_slots=None):
         self.config = config
         self.batch = batch
         self.capacity = capacity
         so = emit_plan(config, plan_dir, batch_lo=batch, batch_hi=batch, capacity=capacity, kv_layout=kv_layout,
-                       num_blocks=num_blocks, geometry=geometry, slots=slots, grid=grid, weights=weights)
+                       num_blocks=num_blocks, geometry=geometry, slots=slots, grid=grid, weights=weights,
+                       attn_min_slots=attn_min_slots)
         self.lib = PlanLibrary(so)
         checkpoint = TensorCheckpoint(weights_cpu, config.get("tie_word_embeddings", False))
         self.weights = load_weights(checkpoint, self.lib, device="cuda:0")

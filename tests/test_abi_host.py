@@ -111,4 +111,4 @@ def test_unsupported_shapes_are_rejected(plan_dir):
     with pytest.raises(ValueError):
         plan_document(synthetic.TINY, batch_lo=1, capacity=40)
     with pytest.raises(ValueError):
-        plan_document(synthetic.TINY, batch_lo=2, capacity=64, kv_layout="paged", num_blocks=4)
+        plan_document(synthetic.TINY, batch_lo=2, capacity=64, kv_layout="paged", num_blocks=1)

@@ -111,16 +111,19 @@ def test_block_table_gather_is_bit_exact(plan_dir):
     paged.close()
 
 
-def test_ragged_contexts_match_oracle(plan_dir):
+@pytest.mark.parametrize("bases,capacity,grid,min_slots", [
+    ([0, 37, 70], 128, 0, None),
+    ([0, 137, 300], 384, 4, 1)])   # 1, 2 and 3 slots per KV head, cut into equal ranges over 4 CTAs
+def test_ragged_contexts_match_oracle(bases, capacity, grid, min_slots, plan_dir):
     """Sequences at different positions in one batch (context_base), paged KV."""
     config = synthetic.TINY
-    batch, capacity, new_tokens = 3, 128, 4
+    batch, new_tokens = 3, 4
     weights = bf16_weights(config)
-    bases = [0, 37, 70]
     num_blocks = batch * capacity // 16 + 5
     table = shuffled_block_table(batch, capacity // 16, num_blocks, seed=3)
     run = GpuRun(config, weights, batch, capacity, plan_dir, kv_layout="paged", block_table=table,
-                 context_base=torch.tensor(bases, dtype=torch.int32), num_blocks=num_blocks)
+                 context_base=torch.tensor(bases, dtype=torch.int32), num_blocks=num_blocks, grid=grid,
+                 attn_min_slots=min_slots)
     decoder = OracleDecoder(config, weights, torch.bfloat16, capacity)
     kv = PagedKV(config, batch, capacity, torch.bfloat16, table, num_blocks)
     # history: every sequence is prefilled by the oracle up to its own base, and the

@@ -20,6 +20,7 @@ pytestmark = pytest.mark.gpu
 
 @pytest.mark.parametrize("base,batch,history", [
     ("TINY_D128", 16, 40), ("TINY_GQ8", 32, 21), ("TINY_D128", 64, 33), ("TINY_D128", 48, 300),
+    ("TINY_D128", 64, 420),    # 1792 attention slots on 148 CTAs: equal ranges of 13 slots across units of 7
     # the Llama-3.1-8B shape's own widths, one layer: hidden 4096, FFN 14336 (112 chunks in 14 parts),
     # vocabulary 128256 (1002 row tiles)
     ("LLAMA_3_1_8B", 16, 37), ("LLAMA_3_1_8B", 64, 70)])

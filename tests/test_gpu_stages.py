@@ -47,6 +47,16 @@ def test_every_stage_of_one_layer(base, batch, history, plan_dir):
     check_every_stage(dict(getattr(synthetic, base), num_hidden_layers=1), batch, history, plan_dir)
 
 
+# Much attention work per CTA (forced here with a small grid): the slots of all (sequence, KV head) units are cut
+# into equal ranges, one per CTA, and a range crosses unit boundaries -- units of 11 slots in ranges of 9, units
+# of 3 slots in ranges of 12.
+@pytest.mark.parametrize("base,batch,history,grid,min_slots", [("TINY_D128", 3, 701, 8, 1), ("TINY", 8, 300, 16, 2),
+                                                              ("TINY_GQ8", 2, 1100, 3, 1)])
+def test_attention_in_equal_ranges(base, batch, history, grid, min_slots, plan_dir):
+    check_every_stage(dict(getattr(synthetic, base), num_hidden_layers=1), batch, history, plan_dir, grid=grid,
+                      attn_min_slots=min_slots)
+
+
 # The benchmark configurations' own widths, one layer each: the Llama-3.2-1B shape (hidden 2048, head_dim
 # 64, FFN 8192, vocabulary 128256, tied) and the Llama-3.1-8B shape (hidden 4096, head_dim 128, FFN 14336 =
 # seven 2048-column pages per down task, vocabulary 128256) at batch 1 and at the GEMV path's widest batch.
@@ -62,12 +72,12 @@ def linear(x, weight):
     return F.linear(x.float(), weight.float()).to(torch.bfloat16)
 
 
-def check_every_stage(config, batch, history, plan_dir, weights="bf16"):
+def check_every_stage(config, batch, history, plan_dir, weights="bf16", grid=0, attn_min_slots=None):
     dim, heads, hkv = config["head_dim"], config["num_attention_heads"], config["num_key_value_heads"]
     hidden, eps = config["hidden_size"], config["rms_norm_eps"]
     capacity = (history + 18) // 16 * 16
     w = bf16_weights(config)
-    run = GpuRun(config, w, batch, capacity, plan_dir, weights=weights)
+    run = GpuRun(config, w, batch, capacity, plan_dir, weights=weights, grid=grid, attn_min_slots=attn_min_slots)
     if weights == "e4m3":
         # the CPU side multiplies with what the plan's pages hold: every matrix quantised row by row and
         # scaled back (fp32), exactly as the loader derives codes and scales from the bf16 checkpoint

@@ -206,10 +206,9 @@ __device__ __forceinline__ void grid_arrive(Ctx& c) {
   // every thread first orders its own ordinary stores before that proxy
   if (c.p.dense) fence_proxy_async();
   consumer_sync();
-  if (c.tid == 0) {
-    __threadfence();
-    red_release_add(c.p.bar, 1ull);
-  }
+  // The CTA barrier orders every thread's stores before thread 0's release, and a release is
+  // cumulative: no separate fence (one costs about half a microsecond per stage boundary).
+  if (c.tid == 0) red_release_add(c.p.bar, 1ull);
   c.bar_target += (unsigned long long)c.p.grid;
 }
 
@@ -266,19 +265,37 @@ __device__ __forceinline__ int attn_count(const MegaParams& p, int past, int nk,
   return ntasks;
 }
 
-__device__ __forceinline__ void attn_shape(const MegaParams& p, int past, int nk, int& spt, int& ntasks) {
-  int total = 0;
-  for (int b = 0; b < p.batch; ++b) total += (seq_pos(p, past, b) / nk + 1) * p.kv_heads;
-  // a task's fixed cost wants at least attn_min_spt slots; with much more work than that per
-  // CTA, about two tasks per CTA let the claims even out sequences of different lengths
-  const int per_cta = (total + p.grid - 1) / p.grid;
-  spt = max(max(1, p.attn_min_spt), per_cta >= 2 * max(1, p.attn_min_spt) ? (per_cta + 1) / 2 : per_cta);
-  ntasks = attn_count(p, past, nk, spt);
-  // every task owns one record of partial results: never more tasks than records
-  while (ntasks > p.attn_part_tasks) {
-    spt += 1;
-    ntasks = attn_count(p, past, nk, spt);
+// How one attention stage is cut into tasks. Two regimes:
+//  * little work per CTA (per == 0): a task is one chunk of `spt` slots of one (sequence, KV head);
+//  * much work per CTA (per > 0): the slots of all (sequence, KV head) units, laid end to end in
+//    (sequence, head, slot) order, are cut into `ntasks` <= grid RANGES of `per` slots, one claim
+//    each, so every CTA streams the same number of slots whatever the sequences' lengths; a range
+//    is worked through as the SEGMENTS where it meets the units, each segment a partial of its unit.
+struct AttnShape {
+  int spt, ntasks, per, total;
+};
+
+__device__ __forceinline__ AttnShape attn_shape(const MegaParams& p, int past, int nk) {
+  AttnShape sh;
+  sh.total = 0;
+  for (int b = 0; b < p.batch; ++b) sh.total += (seq_pos(p, past, b) / nk + 1) * p.kv_heads;
+  const int floor_spt = max(1, p.attn_min_spt);   // a task's fixed cost wants at least this many slots
+  const int per_cta = (sh.total + p.grid - 1) / p.grid;
+  if (per_cta >= 2 * floor_spt) {
+    sh.per = per_cta;
+    sh.spt = per_cta;
+    sh.ntasks = (sh.total + per_cta - 1) / per_cta;
+    return sh;
   }
+  sh.per = 0;
+  sh.spt = max(floor_spt, per_cta);
+  sh.ntasks = attn_count(p, past, nk, sh.spt);
+  // every task owns one record of partial results: never more tasks than records
+  while (sh.ntasks > p.attn_part_tasks) {
+    sh.spt += 1;
+    sh.ntasks = attn_count(p, past, nk, sh.spt);
+  }
+  return sh;
 }
 
 __device__ __forceinline__ AttnTask attn_task(const MegaParams& p, int past, int nk, int spt, int t) {
@@ -305,6 +322,63 @@ __device__ __forceinline__ AttnTask attn_task(const MegaParams& p, int past, int
     }
     base += n;
   }
+}
+
+// The segments of claimed task t, one after another (a chunk task has exactly one).
+struct AttnWalk {
+  int t, x, x1;        // task; next flattened slot and the end of the range
+  int b, base, ns;     // sequence under the cursor, its first flattened slot, its slots per KV head
+  bool done;
+};
+
+__device__ __forceinline__ AttnWalk attn_walk(const MegaParams& p, int past, int nk, const AttnShape& sh, int t) {
+  AttnWalk w;
+  w.t = t;
+  w.done = false;
+  w.x = t * sh.per;
+  w.x1 = min(sh.total, w.x + sh.per);
+  w.b = 0;
+  w.base = 0;
+  w.ns = seq_pos(p, past, 0) / nk + 1;
+  return w;
+}
+
+// Next segment of the walk into `a`; false when the task is exhausted. A unit (sequence b, head g)
+// occupies flattened slots [u0, u0 + ns); the ranges that meet it are u0 / per .. (u0 + ns - 1) / per,
+// and its partial records are consecutive from (first such range) + (unit index): along the
+// flattened axis every new segment advances the range, the unit or both, so no two segments
+// share a record and there are at most ntasks + B * Hkv of them.
+__device__ __forceinline__ bool attn_next(const MegaParams& p, int past, int nk, const AttnShape& sh, AttnWalk& w,
+                                          AttnTask& a) {
+  if (sh.per == 0) {
+    if (w.done) return false;
+    w.done = true;
+    a = attn_task(p, past, nk, sh.spt, w.t);
+    return true;
+  }
+  if (w.x >= w.x1) return false;
+  while (w.x >= w.base + w.ns * p.kv_heads && w.b < p.batch - 1) {
+    w.base += w.ns * p.kv_heads;
+    ++w.b;
+    w.ns = seq_pos(p, past, w.b) / nk + 1;
+  }
+  const int rel = w.x - w.base;
+  const int g = min(rel / w.ns, p.kv_heads - 1);
+  const int s0 = rel - g * w.ns;
+  const int len = min(w.ns - s0, w.x1 - w.x);
+  const int u0 = w.base + g * w.ns;
+  const int first = u0 / sh.per, last = (u0 + w.ns - 1) / sh.per;
+  a.b = w.b;
+  a.g = g;
+  a.pos = seq_pos(p, past, w.b);
+  a.ns = w.ns;
+  a.nch = last - first + 1;
+  a.c = w.x / sh.per - first;
+  a.slot0 = s0;
+  a.slot1 = s0 + len;
+  a.task0 = first + w.b * p.kv_heads + g;
+  w.x += len;
+  return true;
 }
 
 __device__ __forceinline__ int table_entry(const MegaParams& p, int b, int blk) {
@@ -600,101 +674,141 @@ __device__ __forceinline__ void stream_expert_down(Ctx& c, const GemvGeo& geo, c
   stream_close(c);
 }
 
+// The streaming WARP (all 32 lanes; every other streaming function runs on lane 0 alone, which owns
+// the ring cursor, the claims and the FIFO). A ring slot of keys and values is 2 * NB pieces of one
+// KV block of one head each, scattered over the pool by the block table: lane j < 2 * NB looks up
+// its own block and issues its own copy, so a slot costs the issuing side one table load, one
+// address and one copy in parallel instead of 2 * NB of each in a row -- a single thread issuing
+// them one after another sustains about 0.7 of the HBM rate on long contexts.
 template <int D>
 __device__ __forceinline__ void stream_attn(Ctx& c, const LayerPtrs& lp, int past) {
   constexpr int NK = kAttnHalfBytes / (2 * D);   // keys per slot
   constexpr int NB = NK / kKvBlock;              // KV blocks per slot
   constexpr uint32_t BLKB = kKvBlock * D * 2;    // bytes of one block of one head
-  int spt, ntasks;
-  attn_shape(c.p, past, NK, spt, ntasks);
-  int t = c.pending;
-  while (t < ntasks && !c.dead) {
-    const int upcoming = claim(c, c.inst);
-    fifo_push(c, t);
-    const AttnTask a = attn_task(c.p, past, NK, spt, t);
-    const int nblk = a.pos / kKvBlock + 1;
-    for (int s = a.slot0; s < a.slot1; ++s) {
-      const int nb = min(NB, nblk - s * NB);
-      // the block-table entries of the slot first (independent loads), then the copies
-      long long off[NB];
-#pragma unroll
-      for (int j = 0; j < NB; ++j) {
-        const long long e = table_entry(c.p, a.b, s * NB + min(j, max(nb - 1, 0)));
-        off[j] = (e * c.p.kv_block_stride + (long long)a.g * c.p.kv_head_stride) * 2;
-      }
-      if (!stream_wait_empty(c, false)) break;
-      if (nb) mbar_expect_tx(c.full(c.slot), uint32_t(nb) * 2u * BLKB);
-      else mbar_arrive(c.full(c.slot));
-      unsigned char* dst = c.ring(c.slot);
-#pragma unroll
-      for (int j = 0; j < NB; ++j) {
-        if (j < nb) {
-          bulk_g2s(dst + j * BLKB, static_cast<const unsigned char*>(lp.k_pool) + off[j], BLKB, c.full(c.slot));
-          bulk_g2s(dst + kAttnHalfBytes + j * BLKB, static_cast<const unsigned char*>(lp.v_pool) + off[j], BLKB,
-                   c.full(c.slot));
-        }
-      }
-      c.advance();
+  static_assert(2 * NB <= 32, "one lane per piece of a slot");
+  constexpr unsigned kAll = 0xffffffffu;
+  const bool lead = c.lane == 0;
+  const int piece = c.lane % NB;                 // block of the slot this lane copies
+  const bool is_v = c.lane >= NB;
+  const unsigned char* pool = static_cast<const unsigned char*>(is_v ? lp.v_pool : lp.k_pool);
+  const AttnShape sh = attn_shape(c.p, past, NK);
+  int t = __shfl_sync(kAll, c.pending, 0);
+  bool dead = __shfl_sync(kAll, c.dead ? 1 : 0, 0) != 0;
+  while (t < sh.ntasks && !dead) {
+    int upcoming = 0;
+    if (lead) {
+      upcoming = claim(c, c.inst);
+      fifo_push(c, t);
     }
-    t = upcoming;
+    AttnWalk walk = attn_walk(c.p, past, NK, sh, t);
+    AttnTask a;
+    while (!dead && attn_next(c.p, past, NK, sh, walk, a)) {
+      const int nblk = a.pos / kKvBlock + 1;
+      for (int s = a.slot0; s < a.slot1; ++s) {
+        const int nb = min(NB, nblk - s * NB);
+        // this lane's block-table entry first (its load is in flight during the wait below)
+        const long long e = table_entry(c.p, a.b, s * NB + min(piece, max(nb - 1, 0)));
+        const long long off = (e * c.p.kv_block_stride + (long long)a.g * c.p.kv_head_stride) * 2;
+        int word = -1;                           // the slot to fill, or -1: the wait gave up
+        if (lead && stream_wait_empty(c, false)) {
+          if (nb > 0) mbar_expect_tx(c.full(c.slot), uint32_t(nb) * 2u * BLKB);
+          else mbar_arrive(c.full(c.slot));
+          word = int(c.slot);
+          c.advance();
+        }
+        word = __shfl_sync(kAll, word, 0);       // (also orders the expectation before the copies)
+        if (word < 0) {
+          dead = true;
+          break;
+        }
+        if (c.lane < 2 * NB && piece < nb)
+          bulk_g2s(c.ring(uint32_t(word)) + (is_v ? kAttnHalfBytes : 0) + piece * BLKB, pool + off, BLKB, c.full(uint32_t(word)));
+      }
+    }
+    t = __shfl_sync(kAll, upcoming, 0);
+    dead = __shfl_sync(kAll, (dead || c.dead) ? 1 : 0, 0) != 0;
   }
-  stream_close(c);
+  if (lead) stream_close(c);
+  __syncwarp();
 }
 
+// Lane 0's part of a layer before its attention stage: QKV pages, and the ordering of the cache rows
+// the previous step appended.
+__device__ __forceinline__ void stream_layer_head(Ctx& c, const LayerPtrs& lp, int si, bool& kv_ordered, uint64_t policy) {
+  const MegaParams& p = c.p;
+  const uint32_t norm_bytes = uint32_t(p.hidden) * 2u;
+  // the RMSNorm weights are read by every CTA right after a barrier: have them in L2 by then
+  bulk_prefetch_l2(lp.norm1, norm_bytes);
+  bulk_prefetch_l2(lp.norm2, norm_bytes);
+  stream_gemv(c, p.geo[kQkv], lp.qkv, policy);
+  if (!kv_ordered) {
+    // KV rows appended by the previous step were written with ordinary stores by other CTAs: take the
+    // previous step's last grid barrier before any bulk (async-proxy) read of the pools
+    const unsigned long long need = p.bar_base + (unsigned long long)p.bars_per_step * (unsigned long long)si * p.grid;
+    unsigned long long t0 = 0, seen;
+    uint32_t polls = 0;
+    while ((seen = ld_acquire(p.bar)) < need) {
+      if ((++polls & 63u) == 0 && wait_give_up(p, t0, kSiteGrid, need, seen)) break;
+    }
+    kv_ordered = true;
+  }
+}
+
+// Lane 0's part of a layer after its attention stage. False: the launch is being abandoned.
+template <int X>
+__device__ __forceinline__ bool stream_layer_tail(Ctx& c, const LayerPtrs& lp, uint64_t policy) {
+  const MegaParams& p = c.p;
+  stream_gemv(c, p.geo[kOProj], lp.o, policy);
+  if ((X & kXMoe) && p.experts) {
+    stream_gemv(c, p.geo[kRouter], lp.router, policy);
+    // the experts of this layer are known once the arithmetic warps have routed
+    if (!mbar_wait(c, c.route_bar(), c.route_phase, kSiteFull)) return false;
+    c.route_phase ^= 1u;
+    int expert[kMaxTopK];
+#pragma unroll
+    for (int i = 0; i < kMaxTopK; ++i) expert[i] = c.route_e()[i];
+    stream_expert_gate_up(c, p.geo[kGateUp], lp.gate_up, expert, policy);
+    stream_expert_down(c, p.geo[kDown], lp.down, expert, policy);
+  } else {
+    stream_gemv(c, p.geo[kGateUp], lp.gate_up, policy);
+    if (p.down_splits > 1) {
+      for (int part = 0; part < p.down_splits; ++part) stream_gemv(c, p.down_part[part], lp.down, policy);
+    } else {
+      stream_gemv(c, p.geo[kDown], lp.down, policy);
+    }
+  }
+  return !(c.dead || ld_relaxed(p.status + kStFired) != 0);
+}
+
+// The streaming warp. Lane 0 runs everything except the attention stages' copies, which the lanes share.
 template <int D, int X>
 __device__ void streamer_main(Ctx& c) {
   const MegaParams& p = c.p;
   const uint64_t policy = policy_evict_first();
-  const unsigned long long bars_per_step = (unsigned long long)p.bars_per_step;   // grid-wide arrivals of one step
-  const uint32_t norm_bytes = uint32_t(p.hidden) * 2u;
-  c.pending = claim(c, 0);
-  c.pending_next = claim(c, 1);
+  const bool lead = c.lane == 0;
+  if (lead) {
+    c.pending = claim(c, 0);
+    c.pending_next = claim(c, 1);
+  }
   for (int si = 0; si < p.nsteps; ++si) {
     const int past = __ldg(p.past + p.first_step + si);
-    // KV rows appended by the previous step were written with ordinary stores by
-    // other CTAs: take the previous step's last grid barrier before any bulk
-    // (async-proxy) read of the pools, then order the proxies.
     bool kv_ordered = si == 0;
     for (int l = 0; l < p.layers; ++l) {
       const LayerPtrs lp = p.layer[l];
-      // the RMSNorm weights are read by every CTA right after a barrier: have them in L2 by then
-      bulk_prefetch_l2(lp.norm1, norm_bytes);
-      bulk_prefetch_l2(lp.norm2, norm_bytes);
-      stream_gemv(c, p.geo[kQkv], lp.qkv, policy);
-      if (!kv_ordered) {
-        const unsigned long long need = p.bar_base + bars_per_step * (unsigned long long)si * p.grid;
-        unsigned long long t0 = 0, seen;
-        uint32_t polls = 0;
-        while ((seen = ld_acquire(p.bar)) < need) {
-          if ((++polls & 63u) == 0 && wait_give_up(p, t0, kSiteGrid, need, seen)) break;
-        }
-        fence_proxy_async();
-        kv_ordered = true;
-      }
+      if (lead) stream_layer_head(c, lp, si, kv_ordered, policy);
+      __syncwarp();
+      // lane 0 has just taken the previous step's last barrier: every lane's copies read cache rows
+      // that ordinary stores of other CTAs wrote before it (once per step; the fence is not cheap)
+      if (l == 0 && si > 0) fence_proxy_async();
       stream_attn<D>(c, lp, past);
-      stream_gemv(c, p.geo[kOProj], lp.o, policy);
-      if ((X & kXMoe) && p.experts) {
-        stream_gemv(c, p.geo[kRouter], lp.router, policy);
-        // the experts of this layer are known once the arithmetic warps have routed
-        if (!mbar_wait(c, c.route_bar(), c.route_phase, kSiteFull)) return;
-        c.route_phase ^= 1u;
-        int expert[kMaxTopK];
-#pragma unroll
-        for (int i = 0; i < kMaxTopK; ++i) expert[i] = c.route_e()[i];
-        stream_expert_gate_up(c, p.geo[kGateUp], lp.gate_up, expert, policy);
-        stream_expert_down(c, p.geo[kDown], lp.down, expert, policy);
-      } else {
-        stream_gemv(c, p.geo[kGateUp], lp.gate_up, policy);
-        if (p.down_splits > 1) {
-          for (int part = 0; part < p.down_splits; ++part) stream_gemv(c, p.down_part[part], lp.down, policy);
-        } else {
-          stream_gemv(c, p.geo[kDown], lp.down, policy);
-        }
-      }
-      if (c.dead || ld_relaxed(p.status + kStFired) != 0) return;
+      int go = 1;
+      if (lead) go = stream_layer_tail<X>(c, lp, policy) ? 1 : 0;
+      if (__shfl_sync(0xffffffffu, go, 0) == 0) return;
     }
-    bulk_prefetch_l2(p.final_norm, norm_bytes);
-    stream_gemv(c, p.geo[kHead], p.lm_head, policy);
+    if (lead) {
+      bulk_prefetch_l2(p.final_norm, uint32_t(p.hidden) * 2u);
+      stream_gemv(c, p.geo[kHead], p.lm_head, policy);
+    }
   }
 }
 
@@ -1154,10 +1268,7 @@ __device__ __forceinline__ void gemv_epilogue(Ctx& c, const GemvGeo& geo, const 
     // one more row tile of this KV-head group is in global memory: attention tasks
     // of that group wait for the group's count instead of a grid-wide barrier
     __syncwarp();
-    if (lane == 0) {
-      __threadfence();
-      red_release_add(io.ready + e.task / io.tiles_per_group, 1ull);
-    }
+    if (lane == 0) red_release_add(io.ready + e.task / io.tiles_per_group, 1ull);   // (the release is cumulative over the warp's stores)
   }
 }
 
@@ -1468,12 +1579,13 @@ __device__ void attn_stage(Ctx& c, const LayerPtrs& lp, int past, bool tr, int s
   const __nv_bfloat16* cosb = static_cast<const __nv_bfloat16*>(p.rope_cos);
   const __nv_bfloat16* sinb = static_cast<const __nv_bfloat16*>(p.rope_sin);
 
-  int spt, ntasks;
-  attn_shape(p, past, NK, spt, ntasks);
+  const AttnShape sh = attn_shape(p, past, NK);
   trace_mark(c, tr, stage, 2);
   for (int t = fifo_pop_uniform(c); t >= 0; t = fifo_pop_uniform(c)) {
-    const AttnTask a = attn_task(p, past, NK, spt, min(t, ntasks - 1));
-    const bool tail = a.c == a.nch - 1;  // this chunk holds the new token
+    AttnWalk walk = attn_walk(p, past, NK, sh, min(t, sh.ntasks - 1));
+    AttnTask a;
+    while (attn_next(p, past, NK, sh, walk, a)) {
+    const bool tail = a.slot1 == a.ns;   // this chunk holds the new token
     // the (GQ + 2) * D QKV rows of KV head a.g must be stored: their row tiles are counted per group
     if (c.tid == 0 && !c.dead) {
       const unsigned long long need = qkv_stages * (unsigned long long)((GQ + 2) * D / kTileN);
@@ -1711,7 +1823,7 @@ __device__ void attn_stage(Ctx& c, const LayerPtrs& lp, int past, bool tr, int s
     }
     consumer_sync();
     __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.attn) + size_t(a.b) * p.heads * D + size_t(a.g) * GQ * D;
-    float* part = p.attn_part + size_t(t) * GQ * PW;
+    float* part = p.attn_part + size_t(a.task0 + a.c) * GQ * PW;
     for (int o = c.tid; o < GQ * D; o += kConsumerThreads) {
       const int h = o / D, d = o - h * D;
       float mx = -INFINITY;
@@ -1739,20 +1851,19 @@ __device__ void attn_stage(Ctx& c, const LayerPtrs& lp, int past, bool tr, int s
     if (a.nch > 1) {
       // last arriver of (sequence, KV head) merges the chunks in chunk order
       // (include/tilemega/Backend/Sm90DenseAttentionBody.cuh:359-363,409-446)
-      // (the CTA barrier orders every thread's partial stores before thread 0's
-      // fence + counter increment, the same pattern as the grid arrival)
+      // (the CTA barrier orders every thread's partial stores before thread 0's counter
+      // increment, which releases them and acquires the other chunks' -- the same pattern as
+      // the grid arrival; the second barrier hands the acquired view to the other threads)
       consumer_sync();
       if (c.tid == 0) {
         unsigned* cnt = p.attn_cnt + a.b * p.kv_heads + a.g;
-        __threadfence();
-        const unsigned old = atomicAdd(cnt, 1u);
+        const unsigned old = atom_acq_rel_add(cnt, 1u);
         const int last = old == unsigned(a.nch - 1);
         if (last) atomicExch(cnt, 0u);
         c.ctl()[1] = last;
       }
       consumer_sync();
       if (c.ctl()[1]) {
-        __threadfence();
         const float* parts = p.attn_part + size_t(a.task0) * GQ * PW;
         for (int o = c.tid; o < GQ * D; o += kConsumerThreads) {
           const int h = o / D, d = o - h * D;
@@ -1788,6 +1899,7 @@ __device__ void attn_stage(Ctx& c, const LayerPtrs& lp, int past, bool tr, int s
         }
       }
       consumer_sync();
+    }
     }
     ++c.task_seq;
   }
@@ -1989,10 +2101,8 @@ __device__ __forceinline__ void run_cta(const MegaParams& p, int cta) {
   }
   __syncthreads();
   if (c.warp >= kConsumerWarps) {
-    if (c.lane == 0) {
-      streamer_main<D, X>(c);
-      streamer_drain(c);
-    }
+    streamer_main<D, X>(c);   // the whole warp; lane 0 leads
+    if (c.lane == 0) streamer_drain(c);
   } else {
     consumer_main<B, D, GQ, X>(c);
   }
@@ -2326,8 +2436,7 @@ __device__ void gemm_epilogue_stage(Ctx& c, const DenseGeo& g, const GemvIo& io,
       if (c.lane == 0) mbar_arrive(dbar(c, kOffDAccEmpty, group));
       group_sync(group);   // every thread's partial stores are ordered before the counter below
       if ((c.tid & 127) == 0) {
-        __threadfence();
-        const unsigned old = atomicAdd(p.gemm_cnt + tile, 1u);
+        const unsigned old = atom_acq_rel_add(p.gemm_cnt + tile, 1u);
         const int last = old == unsigned(g.nsplit - 1);
         if (last) atomicExch(p.gemm_cnt + tile, 0u);
         *last_flag = last;
@@ -2336,7 +2445,6 @@ __device__ void gemm_epilogue_stage(Ctx& c, const DenseGeo& g, const GemvIo& io,
       const bool last = *last_flag != 0;
       group_sync(group);   // everyone has read the flag before the next task may overwrite it
       if (!last) continue;
-      __threadfence();
       const float* parts = p.gemm_part + size_t(tile) * g.nsplit * tile_floats + m;
       for (int j = 0; j < nb; ++j) {
         float v[16];
@@ -2365,10 +2473,7 @@ __device__ void gemm_epilogue_stage(Ctx& c, const DenseGeo& g, const GemvIo& io,
       // one more 128-row tile of this KV-head group is in global memory (counted in 8-row units, the
       // unit the attention tasks' readiness test uses)
       group_sync(group);
-      if ((c.tid & 127) == 0) {
-        __threadfence();
-        red_release_add(io.ready + tile / io.tiles_per_group, (unsigned long long)(kDenseTileN / kTileN));
-      }
+      if ((c.tid & 127) == 0) red_release_add(io.ready + tile / io.tiles_per_group, (unsigned long long)(kDenseTileN / kTileN));
     }
   }
 }
@@ -2548,10 +2653,8 @@ __global__ void __launch_bounds__(kDenseThreads, 1) dense_megakernel(const __gri
   __syncthreads();
   tcgen05_fence_after();
   if (c.warp == kConsumerWarps) {
-    if (c.lane == 0) {
-      streamer_main<128, 0>(c);
-      streamer_drain(c);
-    }
+    streamer_main<128, 0>(c);   // the whole warp; lane 0 leads
+    if (c.lane == 0) streamer_drain(c);
   } else if (issuer) {
     if (c.lane == 0) mma_main_dense<GQ>(c);
   } else {

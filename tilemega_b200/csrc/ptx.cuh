@@ -80,6 +80,14 @@ __device__ __forceinline__ void red_release_add(unsigned long long* addr, unsign
   asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(addr), "l"(v) : "memory");
 }
 
+// Counter increment that both publishes this thread's earlier stores (and those ordered before it by a
+// barrier) and, for the thread that finds itself last, makes the other arrivers' stores visible.
+__device__ __forceinline__ unsigned atom_acq_rel_add(unsigned* addr, unsigned v) {
+  unsigned old;
+  asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], %2;" : "=r"(old) : "l"(addr), "r"(v) : "memory");
+  return old;
+}
+
 __device__ __forceinline__ unsigned long long ld_acquire(const unsigned long long* addr) {
   unsigned long long v;
   asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(addr) : "memory");

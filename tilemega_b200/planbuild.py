@@ -47,8 +47,10 @@ def plan_document(config: dict, *, batch_lo: int = 1, batch_hi: int | None = Non
         raise ValueError("capacity must be a positive multiple of the KV block (16)")
     if kv_layout not in ("contiguous", "paged"):
         raise ValueError("kv_layout must be 'contiguous' or 'paged'")
-    if kv_layout == "paged" and num_blocks < batch_hi * (capacity // 16):
-        raise ValueError("a paged plan needs num_blocks >= batch_hi * capacity / 16")
+    # the pool may be smaller than batch_hi * capacity / 16 blocks: a scheduler that knows its sequences' lengths
+    # (serving/continuous.py) hands out blocks on demand; a static batch with full-length rows needs that many
+    if kv_layout == "paged" and num_blocks < 2:
+        raise ValueError("a paged plan needs a pool of at least 2 blocks (kv num_blocks)")
     if tp not in (1, 2, 4, 8):
         raise ValueError("tensor parallel degree must be 1, 2, 4 or 8")
     for key in ("num_attention_heads", "num_key_value_heads", "intermediate_size", "vocab_size"):

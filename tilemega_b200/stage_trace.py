@@ -55,6 +55,10 @@ def main() -> None:
     parser.add_argument("--context", type=int, default=2646)
     parser.add_argument("--batch", type=int, default=1)
     parser.add_argument("--attn-min-slots", type=int, default=None)
+    parser.add_argument("--dump", default=None, help="also save the raw stamps, int64 [grid][stages][4], as a .npy file")
+    parser.add_argument("--kv-layout", choices=("paged", "contiguous"), default="paged")
+    parser.add_argument("--table", choices=("shuffled", "identity"), default="shuffled",
+                        help="paged layout: pool blocks of a sequence in random order (the serving case) or in order")
     parser.add_argument("--peak-gbs", type=float, default=DEFAULT_PEAK_GBS,
                         help="measured HBM copy bandwidth the ideal stage times are computed from")
     args = parser.parse_args()
@@ -70,19 +74,26 @@ def main() -> None:
     num_blocks = batch * capacity // 16 + 8
     folder = PLAN_DIR / f"trace-{os.getpid()}"
     try:
-        so = emit_plan(config, folder, batch_lo=batch, batch_hi=batch, capacity=capacity, kv_layout="paged",
-                       num_blocks=num_blocks, write_logits=False, attn_min_slots=args.attn_min_slots)
+        paged = args.kv_layout == "paged"
+        so = emit_plan(config, folder, batch_lo=batch, batch_hi=batch, capacity=capacity, kv_layout=args.kv_layout,
+                       num_blocks=num_blocks if paged else 0, write_logits=False, attn_min_slots=args.attn_min_slots)
         lib = PlanLibrary(so)
         weights = load_weights(synthetic.LazySeededCheckpoint(config, seed=0, device=device), lib, device=device)
-        table = shuffled_block_table(batch, capacity // 16, num_blocks, seed=7)
-        state = allocate_state(config, batch, lib, device, block_table=table,
-                               context_base=torch.tensor([context] * batch, dtype=torch.int32))
+        if paged:
+            table = (shuffled_block_table(batch, capacity // 16, num_blocks, seed=7) if args.table == "shuffled"
+                     else torch.arange(batch * (capacity // 16), dtype=torch.int32).reshape(batch, capacity // 16))
+            state = allocate_state(config, batch, lib, device, block_table=table,
+                                   context_base=torch.tensor([context] * batch, dtype=torch.int32))
+            first = 0
+        else:
+            state = allocate_state(config, batch, lib, device)
+            first = context      # a contiguous cache has no per-sequence offset: the step numbers carry the context
         state.kv_storage.normal_(0, 0.5)
         pointers = {name: tensor.data_ptr() for name, tensor in weights.items()}
         pointers.update(state.pointers)
         plan = lib.create(batch, pointers, 0)
         plan.set_prompt_len(0)
-        plan.set_steps(list(range(steps)))
+        plan.set_steps(list(range(first, first + steps)))
         stream = torch.cuda.current_stream().cuda_stream
         plan.launch_steps(0, 4, 2, stream)
         torch.cuda.synchronize()
@@ -102,8 +113,10 @@ def main() -> None:
         # [grid][stages][4] words; the grid is one CTA per SM; a wide batch has a few more stages
         # per layer than `kinds` (its down reduction runs in parts)
         grid = torch.cuda.get_device_properties(0).multi_processor_count
-        per_layer = (stamps.size // 4 // grid - 1) // layers
-        trace = stamps.reshape(grid, per_layer * layers + 1, 4)
+        trace = stamps.reshape(grid, -1, 4)
+        per_layer = (trace.shape[1] - 1) // layers
+        if args.dump:
+            np.save(args.dump, trace)
         plan.close()
     finally:
         remove_plans(folder)
