@@ -50,3 +50,22 @@ def test_admission_waits_for_blocks_in_arrival_order():
         scheduler.submit(Request(3, [1] * 60, 10))   # longer than a sequence's share of the table
     with pytest.raises(ValueError):
         scheduler.submit(Request(4, [], 3))
+
+
+def test_prefilled_slot_starts_behind_its_prompt():
+    from tilemega_b200.serving.prefill import pack_rows
+    scheduler = SlotScheduler(slots=1, num_blocks=8, max_blocks_per_sequence=4)
+    scheduler.submit(Request(0, [5, 6, 7, 8], 2))
+    scheduler.submit(Request(1, [9], 1))
+    assert scheduler.admit() == [0]
+    assert scheduler.prefilled(0, 42) is None
+    assert scheduler.slots[0].position == 4 and scheduler.forced_token(0) is None
+    ended = scheduler.advance({0: 43})
+    assert [r.generated for r in ended] == [[42, 43]]
+    assert scheduler.admit() == [0]
+    done = scheduler.prefilled(0, 11)                 # one new token: the prefill's sample ends the request
+    assert done is not None and done.generated == [11] and scheduler.idle()
+    assert len(scheduler.pool.free) == 7
+    # rows are packed sequence after sequence, positions ascending, chunks of at most `rows`
+    chunks = pack_rows([3, 1, 4], rows=4)
+    assert chunks == [[(0, 0), (0, 1), (0, 2), (1, 0)], [(2, 0), (2, 1), (2, 2), (2, 3)]]

@@ -1,0 +1,104 @@
+"""Chunked prefill on the GPU: prompts run through a dense-batch plan whose rows are consecutive
+positions (tcgen05 GEMM stages, every row's key and value appended behind a grid barrier before any
+row attends), checked against the oracle's prefill forward -- the reference module's causal forward
+over the whole prompt (python/tilemega/serving/export.py:134-172), which the fixtures under
+tests/golden pin -- at every position; then decoding continues from the prefilled pool."""
+import pytest
+import torch
+
+from oracle.decoder_oracle import OracleDecoder, PagedKV
+from tilemega_b200 import synthetic
+from tilemega_b200.planbuild import emit_plan
+from tilemega_b200.serving.continuous import ContinuousEngine, Request
+from tilemega_b200.serving.prefill import ChunkedPrefill
+from tilemega_b200.serving.state import kv_row_swizzle
+from tilemega_b200.serving.weights import TensorCheckpoint
+
+from harness import bf16_ulp, bf16_weights
+
+pytestmark = pytest.mark.gpu
+LOGIT_TOLERANCE = 2e-2
+
+
+def oracle_prefill(config, weights, prompt, capacity, dtype):
+    decoder = OracleDecoder(config, weights, dtype, capacity)
+    kv = PagedKV(config, 1, capacity, dtype)
+    logits = decoder.forward(torch.tensor([prompt], dtype=torch.int32), [0], kv, head_fp32=True)[0].float()
+    return logits, kv
+
+
+@pytest.mark.parametrize("base,rows,lengths", [("TINY_D128", 16, [37, 20, 1]), ("TINY_GQ8", 32, [70])])
+def test_chunked_prefill_matches_the_oracle_at_every_position(base, rows, lengths, plan_dir):
+    config = getattr(synthetic, base)
+    capacity, num_blocks = 96, 40
+    weights = bf16_weights(config)
+    prompts = [synthetic.seeded_tokens(1, length, config["vocab_size"], seed=30 + i)[0].tolist()
+               for i, length in enumerate(lengths)]
+    so = emit_plan(config, plan_dir, batch_lo=rows, batch_hi=rows, capacity=capacity, kv_layout="paged",
+                   num_blocks=num_blocks, chunk_rows=True)
+    layers, hkv, dim = config["num_hidden_layers"], config["num_key_value_heads"], config["head_dim"]
+    pool = torch.zeros((layers, 2, num_blocks, hkv, 16, dim), dtype=torch.bfloat16, device="cuda:0")
+    # blocks handed out in a scattered order, block 0 left to the pad rows
+    order = (torch.randperm(num_blocks - 1, generator=torch.Generator().manual_seed(4)) + 1).tolist()
+    blocks, taken = [], 0
+    for length in lengths:
+        need = -(-(length + 1) // 16)
+        blocks.append(order[taken:taken + need])
+        taken += need
+    checkpoint = TensorCheckpoint(weights, config.get("tie_word_embeddings", False))
+    with ChunkedPrefill(checkpoint, config, so, rows, pool) as prefill:
+        results = prefill.run(prompts, blocks, want_logits=True)
+        assert prefill.chunks_run == -(-sum(lengths) // rows)
+    cache = kv_row_swizzle(pool.cpu())          # [L][2][blocks][Hkv][16][D], logical column order
+    for prompt, owned, result in zip(prompts, blocks, results):
+        exact, _ = oracle_prefill(config, weights, prompt, capacity, torch.float32)
+        module, kv = oracle_prefill(config, weights, prompt, capacity, torch.bfloat16)
+        ours, theirs = (result.logits - exact).abs(), (module - exact).abs()
+        bound = max(LOGIT_TOLERANCE, 1.25 * theirs.max().item())
+        assert ours.max().item() <= bound, (len(prompt), ours.max().item(), theirs.max().item())
+        assert ours.mean().item() <= max(1.25 * theirs.mean().item(), LOGIT_TOLERANCE / 4)
+        # the token after the prompt: the fp32 forward's choice wherever that is not a near tie
+        top2 = exact[-1].topk(2).values
+        if (top2[0] - top2[1]).item() > 2 * bound:
+            assert result.first_token == int(exact[-1].argmax())
+        assert exact[-1, result.first_token].item() >= top2[0].item() - 2 * bound
+        # the cache rows the prefill wrote: the module's own keys and values, up to the bf16 drift of a two-layer model
+        length = len(prompt)
+        positions = torch.arange(length)
+        # (index tensors on two separated axes move to the front: [len][L][2][Hkv][D] -> [L][2][len][Hkv][D])
+        mine = cache[:, :, torch.tensor(owned)[positions // 16], :, positions % 16].permute(1, 2, 0, 3, 4)
+        reference = kv.pool[:, :, kv.table[0, positions // 16].long(), :, positions % 16].permute(1, 2, 0, 3, 4)
+        first_layer = (mine[0].float() - reference[0].float()).abs()
+        assert (first_layer <= 2 * bf16_ulp(reference[0].float()) + 1e-6).float().mean().item() >= 0.999
+        assert (mine.float() - reference.float()).abs().max().item() <= 0.05 * reference.float().abs().max().item()
+
+
+def test_continuous_engine_decodes_on_from_a_prefilled_pool(plan_dir):
+    config = synthetic.TINY_D128
+    capacity, slots, num_blocks, rows = 64, 2, 9, 16
+    weights = bf16_weights(config)
+    shapes = [(21, 5), (3, 6), (40, 4), (17, 1)]
+    requests = [Request(i, synthetic.seeded_tokens(1, length, config["vocab_size"], seed=50 + i)[0].tolist(), new)
+                for i, (length, new) in enumerate(shapes)]
+    decode_so = emit_plan(config, plan_dir, batch_lo=slots, batch_hi=slots, capacity=capacity, kv_layout="paged",
+                          num_blocks=num_blocks)
+    prefill_so = emit_plan(config, plan_dir, batch_lo=rows, batch_hi=rows, capacity=capacity, kv_layout="paged",
+                           num_blocks=num_blocks, chunk_rows=True, write_logits=False)
+    checkpoint = TensorCheckpoint(weights, config.get("tie_word_embeddings", False))
+    with ContinuousEngine(checkpoint, config, decode_so, slots, prefill_so=prefill_so, prefill_rows=rows) as engine:
+        for request in requests:
+            engine.submit(request)
+        finished = engine.run_until_done()
+        # the prompts never went through the decode plan: steps = generated tokens after the first, shared by two slots
+        assert engine.steps_run <= sum(new - 1 for _, new in shapes)
+        assert len(engine.scheduler.pool.free) == num_blocks - 1
+    assert sorted(request.id for request in finished) == [0, 1, 2, 3]
+    decoder = OracleDecoder(config, weights, torch.float32, capacity)
+    for request in finished:
+        assert len(request.generated) == shapes[request.id][1]
+        # teacher-forced on what the engine generated, every token must be the fp32 forward's choice or a near tie of it
+        history = torch.tensor([request.prompt + request.generated[:-1]], dtype=torch.int32)
+        kv = PagedKV(config, 1, capacity, torch.float32)
+        logits = decoder.forward(history, [0], kv, head_fp32=True)[0].float()[len(request.prompt) - 1:]
+        chosen = logits[torch.arange(len(request.generated)), torch.tensor(request.generated)]
+        assert (chosen >= logits.max(dim=-1).values - 4 * LOGIT_TOLERANCE).all(), (request.id, request.generated)

@@ -734,7 +734,7 @@ __device__ __forceinline__ void stream_attn(Ctx& c, const LayerPtrs& lp, int pas
 
 // Lane 0's part of a layer before its attention stage: QKV pages, and the ordering of the cache rows
 // the previous step appended.
-__device__ __forceinline__ void stream_layer_head(Ctx& c, const LayerPtrs& lp, int si, bool& kv_ordered, uint64_t policy) {
+__device__ __forceinline__ void stream_layer_head(Ctx& c, const LayerPtrs& lp, int si, int layer, bool& kv_ordered, uint64_t policy) {
   const MegaParams& p = c.p;
   const uint32_t norm_bytes = uint32_t(p.hidden) * 2u;
   // the RMSNorm weights are read by every CTA right after a barrier: have them in L2 by then
@@ -751,6 +751,16 @@ __device__ __forceinline__ void stream_layer_head(Ctx& c, const LayerPtrs& lp, i
       if ((++polls & 63u) == 0 && wait_give_up(p, t0, kSiteGrid, need, seen)) break;
     }
     kv_ordered = true;
+  }
+  if (p.chunk_rows) {
+    // this layer's keys and values of ALL rows are appended (arrival 3 of the layer: norm1, QKV, append)
+    const unsigned long long need =
+        p.bar_base + ((unsigned long long)p.bars_per_step * (unsigned long long)si + 8ull * (unsigned long long)layer + 3ull) * p.grid;
+    unsigned long long t0 = 0, seen;
+    uint32_t polls = 0;
+    while ((seen = ld_acquire(p.bar)) < need) {
+      if ((++polls & 63u) == 0 && wait_give_up(p, t0, kSiteGrid, need, seen)) break;
+    }
   }
 }
 
@@ -795,11 +805,11 @@ __device__ void streamer_main(Ctx& c) {
     bool kv_ordered = si == 0;
     for (int l = 0; l < p.layers; ++l) {
       const LayerPtrs lp = p.layer[l];
-      if (lead) stream_layer_head(c, lp, si, kv_ordered, policy);
+      if (lead) stream_layer_head(c, lp, si, l, kv_ordered, policy);
       __syncwarp();
       // lane 0 has just taken the previous step's last barrier: every lane's copies read cache rows
       // that ordinary stores of other CTAs wrote before it (once per step; the fence is not cheap)
-      if (l == 0 && si > 0) fence_proxy_async();
+      if ((l == 0 && si > 0) || p.chunk_rows) fence_proxy_async();
       stream_attn<D>(c, lp, past);
       int go = 1;
       if (lead) go = stream_layer_tail<X>(c, lp, policy) ? 1 : 0;
@@ -1580,6 +1590,20 @@ __device__ void attn_stage(Ctx& c, const LayerPtrs& lp, int past, bool tr, int s
   const __nv_bfloat16* sinb = static_cast<const __nv_bfloat16*>(p.rope_sin);
 
   const AttnShape sh = attn_shape(p, past, NK);
+#if TMB_DENSE
+  // Dense-batch plans leave a QKV reduction that ran in parts unsummed: the tasks here add the
+  // parts' fp32 tiles (ascending, then one rounding to bf16 -- what a summing epilogue would have
+  // stored) for the (GQ + 2) * D values of their own (sequence, KV head) while they stage them.
+  const int qkv_parts = p.dense ? p.dgeo[kQkv].nsplit : 1;
+  unsigned short* qraw = reinterpret_cast<unsigned short*>(qkn + (GQ + 1) * D);   // [GQ + 2][D] summed q, k, v
+#else
+  constexpr int qkv_parts = 1;
+  unsigned short* qraw = nullptr;
+#endif
+  const bool summed_here = qkv_parts > 1;
+  // chunk_rows plans appended every row's key and value in a stage of their own (other rows of the batch
+  // may be later positions of the same sequence and read them): nothing is written to the pools here
+  const bool appended = p.chunk_rows != 0;
   trace_mark(c, tr, stage, 2);
   for (int t = fifo_pop_uniform(c); t >= 0; t = fifo_pop_uniform(c)) {
     AttnWalk walk = attn_walk(p, past, NK, sh, min(t, sh.ntasks - 1));
@@ -1588,7 +1612,8 @@ __device__ void attn_stage(Ctx& c, const LayerPtrs& lp, int past, bool tr, int s
     const bool tail = a.slot1 == a.ns;   // this chunk holds the new token
     // the (GQ + 2) * D QKV rows of KV head a.g must be stored: their row tiles are counted per group
     if (c.tid == 0 && !c.dead) {
-      const unsigned long long need = qkv_stages * (unsigned long long)((GQ + 2) * D / kTileN);
+      // (dense-batch plans whose QKV reduction runs in parts count every part's tile)
+      const unsigned long long need = qkv_stages * (unsigned long long)((GQ + 2) * D / kTileN) * (unsigned long long)qkv_parts;
       unsigned long long t0 = 0, seen;
       uint32_t polls = 0;
       while ((seen = ld_acquire(p.qkv_ready + a.g)) < need) {
@@ -1600,6 +1625,24 @@ __device__ void attn_stage(Ctx& c, const LayerPtrs& lp, int past, bool tr, int s
     // sum rounded to bf16 (include/tilemega/Codegen/tasks/FusedAttentionTaskBody.h:141-151)
     const unsigned short* row = reinterpret_cast<const unsigned short*>(p.qkv) + size_t(a.b) * qkv_width +
                                 size_t(a.g) * (GQ + 2) * D;
+#if TMB_DENSE
+    if (summed_here) {
+      const size_t tile_floats = size_t(kDenseTileN) * p.batch;
+      const int count = tail ? (GQ + 2) * D : GQ * D;   // the key and value rows matter to the chunk with the new token only
+      for (int e = c.tid; e < count; e += kConsumerThreads) {
+        const int n = a.g * (GQ + 2) * D + e;          // feature index of the QKV output
+        const float* src = p.gemm_part + (size_t(n >> 7) * qkv_parts * p.batch + a.b) * kDenseTileN + (n & 127);
+        float v = 0.f;
+#pragma unroll 4
+        for (int part = 0; part < qkv_parts; ++part) v += __ldcg(src + size_t(part) * tile_floats);
+        const unsigned short bits = bf16_bits(v);
+        qraw[e] = bits;
+        if (tail) const_cast<unsigned short*>(row)[e] = bits;   // the plan's qkv buffer holds the rows as before
+      }
+      consumer_sync();
+    }
+#endif
+    auto qkv_value = [&](int idx) -> unsigned short { return summed_here ? qraw[idx] : __ldcg(row + idx); };
     long long new_off = 0;
     if (tail) {
       const long long e = table_entry(p, a.b, a.pos / kKvBlock);
@@ -1647,9 +1690,9 @@ __device__ void attn_stage(Ctx& c, const LayerPtrs& lp, int past, bool tr, int s
           const int d2 = d < D / 2 ? d + D / 2 : d - D / 2;
           const bool normed = qk_norm && hh <= GQ;
           const bool roped = hh < GQ || (hh == GQ && tail);
-          if (!normed && (roped || (hh == GQ + 1 && tail))) rv[it] = __ldcg(row + e);
+          if (!normed && (roped || (hh == GQ + 1 && tail))) rv[it] = qkv_value(e);
           if (roped) {
-            if (!normed) rp[it] = __ldcg(row + hh * D + d2);
+            if (!normed) rp[it] = qkv_value(hh * D + d2);
             rc[it] = __ldg(cosr + d);
             rs[it] = __ldg(sinr + d);
           }
@@ -1665,7 +1708,7 @@ __device__ void attn_stage(Ctx& c, const LayerPtrs& lp, int past, bool tr, int s
         if (hh == GQ + 1) {
           if (tail) {
             vnew[d] = __float2bfloat16_rn(xv);
-            static_cast<__nv_bfloat16*>(lp.v_pool)[new_off + kv_swizzled(d, a.pos)] = __float2bfloat16_rn(xv);
+            if (!appended) static_cast<__nv_bfloat16*>(lp.v_pool)[new_off + kv_swizzled(d, a.pos)] = __float2bfloat16_rn(xv);
           }
           continue;
         }
@@ -1680,7 +1723,7 @@ __device__ void attn_stage(Ctx& c, const LayerPtrs& lp, int past, bool tr, int s
           qs[hh * D + d] = __float2bfloat16_rn(o);
         } else {
           knew[d] = __float2bfloat16_rn(o);
-          static_cast<__nv_bfloat16*>(lp.k_pool)[new_off + kv_swizzled(d, a.pos)] = __float2bfloat16_rn(o);
+          if (!appended) static_cast<__nv_bfloat16*>(lp.k_pool)[new_off + kv_swizzled(d, a.pos)] = __float2bfloat16_rn(o);
         }
       }
     }
@@ -1865,38 +1908,46 @@ __device__ void attn_stage(Ctx& c, const LayerPtrs& lp, int past, bool tr, int s
       consumer_sync();
       if (c.ctl()[1]) {
         const float* parts = p.attn_part + size_t(a.task0) * GQ * PW;
-        for (int o = c.tid; o < GQ * D; o += kConsumerThreads) {
-          const int h = o / D, d = o - h * D;
-          // chunks in ascending order, sixteen at a time so that their loads are in
-          // flight together (one L2 round trip per batch instead of one per chunk)
-          float mx = -INFINITY, ls = 0.f, as = 0.f;
-          constexpr int kMergeBatch = 16;
-          for (int c0 = 0; c0 < a.nch; c0 += kMergeBatch) {
-            float mc[kMergeBatch], lc[kMergeBatch], ac[kMergeBatch];
+        // A thread merges NO outputs of ONE head, so the chunks' (max, sum) pairs are loaded once per
+        // thread, and all of a batch of chunks' loads -- pairs and outputs -- are in flight together:
+        // one L2 round trip for up to kMergeBatch chunks, where a loop over outputs paid one each.
+        constexpr int TPH = kConsumerThreads / GQ;   // threads per head
+        constexpr int NO = D / TPH;                  // outputs per thread: columns d0 + TPH * k
+        static_assert(kConsumerThreads % GQ == 0 && D % TPH == 0, "merge mapping");
+        constexpr int kMergeBatch = NO >= 4 ? 6 : 12;   // at most 48 loads per thread in flight (registers)
+        const int h = c.tid / TPH, d0 = c.tid - h * TPH;
+        float mx = -INFINITY, ls = 0.f, as[NO];
 #pragma unroll
-            for (int j = 0; j < kMergeBatch; ++j) {
-              const bool live = c0 + j < a.nch;
-              const float* src = parts + (size_t(live ? c0 + j : c0) * GQ + h) * PW;
-              mc[j] = live ? __ldcg(src + D) : -INFINITY;
-              lc[j] = live ? __ldcg(src + D + 1) : 0.f;
-              ac[j] = live ? __ldcg(src + d) : 0.f;
-            }
-            float mb = mx;
+        for (int k = 0; k < NO; ++k) as[k] = 0.f;
+        for (int c0 = 0; c0 < a.nch; c0 += kMergeBatch) {   // chunks in ascending order
+          float mc[kMergeBatch], lc[kMergeBatch], ac[kMergeBatch][NO];
 #pragma unroll
-            for (int j = 0; j < kMergeBatch; ++j) mb = fmaxf(mb, mc[j]);
-            const float rescale = ex2(mx - mb);   // mb is finite: chunk c0 exists and holds a valid key
-            ls *= rescale;
-            as *= rescale;
-            mx = mb;
+          for (int j = 0; j < kMergeBatch; ++j) {
+            const bool live = c0 + j < a.nch;
+            const float* src = parts + (size_t(live ? c0 + j : c0) * GQ + h) * PW;
+            mc[j] = live ? __ldcg(src + D) : -INFINITY;
+            lc[j] = live ? __ldcg(src + D + 1) : 0.f;
 #pragma unroll
-            for (int j = 0; j < kMergeBatch; ++j) {
-              const float wgt = ex2(mc[j] - mb);
-              ls = fmaf(lc[j], wgt, ls);
-              as = fmaf(ac[j], wgt, as);
-            }
+            for (int k = 0; k < NO; ++k) ac[j][k] = live ? __ldcg(src + d0 + TPH * k) : 0.f;
           }
-          out[o] = __float2bfloat16_rn(as / ls);
+          float mb = mx;
+#pragma unroll
+          for (int j = 0; j < kMergeBatch; ++j) mb = fmaxf(mb, mc[j]);
+          const float rescale = ex2(mx - mb);   // mb is finite: chunk c0 exists and holds a valid key
+          ls *= rescale;
+#pragma unroll
+          for (int k = 0; k < NO; ++k) as[k] *= rescale;
+          mx = mb;
+#pragma unroll
+          for (int j = 0; j < kMergeBatch; ++j) {
+            const float wgt = ex2(mc[j] - mb);
+            ls = fmaf(lc[j], wgt, ls);
+#pragma unroll
+            for (int k = 0; k < NO; ++k) as[k] = fmaf(ac[j][k], wgt, as[k]);
+          }
         }
+#pragma unroll
+        for (int k = 0; k < NO; ++k) out[h * D + d0 + TPH * k] = __float2bfloat16_rn(as[k] / ls);
       }
       consumer_sync();
     }
@@ -2265,14 +2316,16 @@ __device__ void mma_main_dense(Ctx& c) {
   const unsigned char* maps = static_cast<const unsigned char*>(p.tmaps);
   bool alive = true;
   for (int si = 0; si < p.nsteps && alive; ++si) {
-    // arrivals of a step, in program order: per layer norm1, attention, o, norm2, gate/up, down; then final norm, head
+    // arrivals of a step, in program order: per layer norm1, [chunk_rows: QKV, append,] attention, o, norm2,
+    // gate/up, down; then final norm, head
     const unsigned long long step0 = (unsigned long long)si * p.bars_per_step;
+    const unsigned long long extra = p.chunk_rows ? 2ull : 0ull, per_layer = 6ull + extra;
     for (int l = 0; l < p.layers && alive; ++l) {
-      const unsigned long long base = step0 + 6ull * l;
-      alive = mma_stage(c, st, p.dgeo[kQkv], maps, base + 1) && mma_stage(c, st, p.dgeo[kOProj], maps + 128, base + 2) &&
-              mma_stage(c, st, p.dgeo[kGateUp], maps, base + 4) && mma_stage(c, st, p.dgeo[kDown], maps + 256, base + 5);
+      const unsigned long long base = step0 + per_layer * l;
+      alive = mma_stage(c, st, p.dgeo[kQkv], maps, base + 1) && mma_stage(c, st, p.dgeo[kOProj], maps + 128, base + 2 + extra) &&
+              mma_stage(c, st, p.dgeo[kGateUp], maps, base + 4 + extra) && mma_stage(c, st, p.dgeo[kDown], maps + 256, base + 5 + extra);
     }
-    if (alive) alive = mma_stage(c, st, p.dgeo[kHead], maps, step0 + 6ull * p.layers + 1);
+    if (alive) alive = mma_stage(c, st, p.dgeo[kHead], maps, step0 + per_layer * p.layers + 1);
   }
   // nothing of this CTA may still be running on the tensor cores when tensor memory is freed
   umma_commit(dbar(c, kOffDDrain, 0));
@@ -2290,10 +2343,14 @@ __device__ void mma_main_dense(Ctx& c) {
 // RMSNorm stage: row b of the batch is normalised by CTA b mod grid and written to xn
 // (y = bf16(w * bf16(x * rsqrt(mean x^2 + eps))), python/tilemega/serving/export.py:24-27). Layer 0
 // reads the embedding row of the sequence's token and also seeds the residual stream with it.
-__device__ void norm_stage_dense(Ctx& c, const void* src, const void* weight, bool embed) {
+// `parts` > 1: the projection into the residual stream that ran before this stage (o, or the previous
+// layer's down) left its reduction as `parts` fp32 tiles per 128 features; the row is first completed
+// here, x = bf16(bf16(sum of the parts, ascending) + x), and written back.
+__device__ void norm_stage_dense(Ctx& c, const void* src, const void* weight, bool embed, int parts = 1) {
   const MegaParams& p = c.p;
   const int chunks = p.hidden >> 3;
   const uint4* nw = reinterpret_cast<const uint4*>(weight);
+  const size_t tile_floats = size_t(kDenseTileN) * p.batch;
   for (int b = c.cta; b < p.batch; b += p.grid) {
     const __nv_bfloat16* row = static_cast<const __nv_bfloat16*>(src) +
                                (embed ? size_t(min(max(dtok(c)[b], 0), p.vocab - 1)) : size_t(b)) * p.hidden;
@@ -2307,6 +2364,38 @@ __device__ void norm_stage_dense(Ctx& c, const void* src, const void* weight, bo
       if (i < chunks) v[j] = embed ? __ldg(reinterpret_cast<const uint4*>(row) + i) : __ldcg(reinterpret_cast<const uint4*>(row) + i);
       float f[8];
       unpack8(v[j], f);
+      if (parts > 1 && i < chunks) {
+        // columns 8i .. 8i+7 lie in tile i / 16 at feature 8 * (i % 16): two 16-byte loads per part,
+        // four parts in flight together
+        const float4* tile0 = reinterpret_cast<const float4*>(p.gemm_part + (size_t(i >> 4) * parts * p.batch + b) * kDenseTileN + ((i & 15) << 3));
+        float sum[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sum[e] = 0.f;
+        for (int part0 = 0; part0 < parts; part0 += 4) {
+          float4 x[4][2];
+#pragma unroll
+          for (int pp = 0; pp < 4; ++pp) {
+            const bool live = part0 + pp < parts;
+            const float4* at = tile0 + size_t(live ? part0 + pp : part0) * (tile_floats >> 2);
+            x[pp][0] = live ? __ldcg(at) : make_float4(0.f, 0.f, 0.f, 0.f);
+            x[pp][1] = live ? __ldcg(at + 1) : make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+#pragma unroll
+          for (int pp = 0; pp < 4; ++pp) {
+            sum[0] += x[pp][0].x; sum[1] += x[pp][0].y; sum[2] += x[pp][0].z; sum[3] += x[pp][0].w;
+            sum[4] += x[pp][1].x; sum[5] += x[pp][1].y; sum[6] += x[pp][1].z; sum[7] += x[pp][1].w;
+          }
+        }
+        uint32_t o[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          f[2 * e] = bf16_round(bf16_round(sum[2 * e]) + f[2 * e]);
+          f[2 * e + 1] = bf16_round(bf16_round(sum[2 * e + 1]) + f[2 * e + 1]);
+          o[e] = uint32_t(bf16_bits(f[2 * e])) | (uint32_t(bf16_bits(f[2 * e + 1])) << 16);
+        }
+        v[j] = make_uint4(o[0], o[1], o[2], o[3]);
+        reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.x) + size_t(b) * p.hidden)[i] = v[j];
+      }
 #pragma unroll
       for (int e = 0; e < 8; ++e) ss = fmaf(f[e], f[e], ss);
     }
@@ -2392,7 +2481,11 @@ __device__ __forceinline__ void dense_epilogue_16(Ctx& c, const DenseGeo& g, con
 
 // One GEMM stage, epilogue side. Both warp groups walk the CTA's task list; group g takes every
 // second task. `seq` counts the CTA's GEMM tasks across stages (it selects the accumulator).
-__device__ void gemm_epilogue_stage(Ctx& c, const DenseGeo& g, const GemvIo& io, uint32_t& seq) {
+// `fold`: a reduction that runs in parts ends here with the parts' fp32 tiles in global memory; the
+// stage that consumes the output adds them (attention staging for QKV, the next RMSNorm stage for the
+// residual stream). Without it the last part to arrive adds them here -- a tail of dependent L2 round
+// trips on one CTA per tile that the whole grid then waits for.
+__device__ void gemm_epilogue_stage(Ctx& c, const DenseGeo& g, const GemvIo& io, uint32_t& seq, bool fold = false) {
   const MegaParams& p = c.p;
   const int group = c.warp >> 2, wq = c.warp & 3, m = wq * 32 + c.lane;
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(c.smem + kOffDTmem);
@@ -2434,6 +2527,14 @@ __device__ void gemm_epilogue_stage(Ctx& c, const DenseGeo& g, const GemvIo& io,
       tcgen05_fence_before();
       __syncwarp();
       if (c.lane == 0) mbar_arrive(dbar(c, kOffDAccEmpty, group));
+      if (fold) {
+        if (io.ready) {
+          // one more part of a 128-row tile of this KV-head group is in global memory
+          group_sync(group);
+          if ((c.tid & 127) == 0) red_release_add(io.ready + tile / io.tiles_per_group, (unsigned long long)(kDenseTileN / kTileN));
+        }
+        continue;
+      }
       group_sync(group);   // every thread's partial stores are ordered before the counter below
       if ((c.tid & 127) == 0) {
         const unsigned old = atom_acq_rel_add(p.gemm_cnt + tile, 1u);
@@ -2478,6 +2579,49 @@ __device__ void gemm_epilogue_stage(Ctx& c, const DenseGeo& g, const GemvIo& io,
   }
 }
 
+// chunk_rows plans: RoPE and cache append for every (row, KV head), spread over the CTAs, before any
+// attention task runs. Rows of the batch may be consecutive positions of one sequence (chunked
+// prefill): row i then attends to the keys and values rows j < i append in this same step, which
+// therefore have to be in the pool -- behind a grid barrier -- first. Same arithmetic as the
+// attention tasks' own staging (include/tilemega/Codegen/tasks/FusedAttentionTaskBody.h:141-151).
+template <int GQ>
+__device__ void append_stage_dense(Ctx& c, const LayerPtrs& lp, int past) {
+  constexpr int D = 128;
+  static_assert(kConsumerThreads == 2 * D, "one thread per key column and per value column");
+  const MegaParams& p = c.p;
+  const int parts = p.dgeo[kQkv].nsplit;
+  const size_t tile_floats = size_t(kDenseTileN) * p.batch;
+  const int qkv_width = (p.heads + 2 * p.kv_heads) * D;
+  const bool is_v = c.tid >= D;
+  const int d = c.tid & (D - 1);
+  for (int u = c.cta; u < p.batch * p.kv_heads; u += p.grid) {
+    const int b = u / p.kv_heads, g = u - b * p.kv_heads;
+    const int pos = seq_pos(p, past, b);
+    const long long e = table_entry(p, b, pos / kKvBlock);
+    const long long at = e * p.kv_block_stride + (long long)g * p.kv_head_stride + (pos % kKvBlock) * D + kv_swizzled(d, pos);
+    const int n0 = g * (GQ + 2) * D + (GQ + (is_v ? 1 : 0)) * D;   // first feature of this head's key (value) row
+    auto feature = [&](int col) -> float {
+      const int n = n0 + col;
+      if (parts == 1) return bf16_from_bits(__ldcg(reinterpret_cast<const unsigned short*>(p.qkv) + size_t(b) * qkv_width + n));
+      const float* src = p.gemm_part + (size_t(n >> 7) * parts * p.batch + b) * kDenseTileN + (n & 127);
+      float v = 0.f;
+#pragma unroll 4
+      for (int part = 0; part < parts; ++part) v += __ldcg(src + size_t(part) * tile_floats);
+      return bf16_round(v);
+    };
+    const float x = feature(d);
+    if (is_v) {
+      static_cast<__nv_bfloat16*>(lp.v_pool)[at] = __float2bfloat16_rn(x);
+    } else {
+      const float xp = feature(d < D / 2 ? d + D / 2 : d - D / 2);
+      const float cs = bf16_from_bits(__ldg(reinterpret_cast<const unsigned short*>(p.rope_cos) + size_t(pos) * D + d));
+      const float sn = bf16_from_bits(__ldg(reinterpret_cast<const unsigned short*>(p.rope_sin) + size_t(pos) * D + d));
+      const float rot = d < D / 2 ? -xp : xp;
+      static_cast<__nv_bfloat16*>(lp.k_pool)[at] = __float2bfloat16_rn(bf16_round(bf16_round(x * cs) + bf16_round(rot * sn)));
+    }
+  }
+}
+
 template <int GQ>
 __device__ void consumer_main_dense(Ctx& c) {
   const MegaParams& p = c.p;
@@ -2505,7 +2649,7 @@ __device__ void consumer_main_dense(Ctx& c) {
       if (l > 0 && !grid_wait(c)) return;                      // the previous layer's down projection is complete
       trace_mark(c, tr, stage, 1);
       trace_mark(c, tr, stage, 2);
-      norm_stage_dense(c, l == 0 ? p.embed : p.x, lp.norm1, l == 0);
+      norm_stage_dense(c, l == 0 ? p.embed : p.x, lp.norm1, l == 0, l == 0 ? 1 : p.dgeo[kDown].nsplit);
       trace_mark(c, tr, stage++, 3);
       grid_arrive(c);
       trace_mark(c, tr, stage, 0);
@@ -2513,9 +2657,17 @@ __device__ void consumer_main_dense(Ctx& c) {
       trace_mark(c, tr, stage, 1);
       trace_mark(c, tr, stage, 2);
       io = GemvIo{nullptr, nullptr, 0, kEpiStore, p.qkv, p.qkv_ready, (GQ + 2) * D / kDenseTileN, nullptr, 0, 0u};
-      gemm_epilogue_stage(c, p.dgeo[kQkv], io, seq);
+      gemm_epilogue_stage(c, p.dgeo[kQkv], io, seq, true);   // parts summed by the attention tasks
       trace_mark(c, tr, stage++, 3);
       // no arrival here: an attention task waits for the QKV rows of its own KV head only
+      // (chunk_rows: all of QKV, then every row's cache append, each behind a grid barrier)
+      if (p.chunk_rows) {
+        grid_arrive(c);
+        if (!grid_wait(c)) return;
+        append_stage_dense<GQ>(c, lp, past);
+        grid_arrive(c);
+        if (!grid_wait(c)) return;
+      }
       trace_mark(c, tr, stage, 0);
       trace_mark(c, tr, stage, 1);
       attn_stage<1, D, GQ, 0>(c, lp, past, tr, stage++, (unsigned long long)(si * p.layers + l + 1));
@@ -2525,14 +2677,14 @@ __device__ void consumer_main_dense(Ctx& c) {
       trace_mark(c, tr, stage, 1);
       trace_mark(c, tr, stage, 2);
       io = GemvIo{nullptr, nullptr, 0, kEpiResidual, p.x, nullptr, 1, nullptr, 0, 0u};
-      gemm_epilogue_stage(c, p.dgeo[kOProj], io, seq);
+      gemm_epilogue_stage(c, p.dgeo[kOProj], io, seq, true);   // parts summed by the RMSNorm stage that follows
       trace_mark(c, tr, stage++, 3);
       grid_arrive(c);
       trace_mark(c, tr, stage, 0);
       if (!grid_wait(c)) return;                               // the residual stream after attention is complete
       trace_mark(c, tr, stage, 1);
       trace_mark(c, tr, stage, 2);
-      norm_stage_dense(c, p.x, lp.norm2, false);
+      norm_stage_dense(c, p.x, lp.norm2, false, p.dgeo[kOProj].nsplit);
       trace_mark(c, tr, stage++, 3);
       grid_arrive(c);
       trace_mark(c, tr, stage, 0);
@@ -2548,7 +2700,7 @@ __device__ void consumer_main_dense(Ctx& c) {
       trace_mark(c, tr, stage, 1);
       trace_mark(c, tr, stage, 2);
       io = GemvIo{nullptr, nullptr, 0, kEpiResidual, p.x, nullptr, 1, nullptr, 0, 0u};
-      gemm_epilogue_stage(c, p.dgeo[kDown], io, seq);
+      gemm_epilogue_stage(c, p.dgeo[kDown], io, seq, true);   // parts summed by the next RMSNorm stage
       trace_mark(c, tr, stage++, 3);
       grid_arrive(c);
     }
@@ -2556,7 +2708,7 @@ __device__ void consumer_main_dense(Ctx& c) {
     if (!grid_wait(c)) return;
     trace_mark(c, tr, stage, 1);
     trace_mark(c, tr, stage, 2);
-    norm_stage_dense(c, p.x, p.final_norm, false);
+    norm_stage_dense(c, p.x, p.final_norm, false, p.dgeo[kDown].nsplit);
     trace_mark(c, tr, stage++, 3);
     grid_arrive(c);
     trace_mark(c, tr, stage, 0);

@@ -167,6 +167,7 @@ struct MegaParams {
   int trace_step;
   // dense-batch plans (dense != 0): GEMM stages on tcgen05 tiles
   int dense;
+  int chunk_rows;              // rows may be consecutive positions of one sequence: append stage + barrier before attention
   DenseGeo dgeo[kNumGemv];     // indexed by StageKind (kRouter unused)
   void* xn;                    // bf16 [B][H]: the RMSNorm output a GEMM stage reads
   float* gemm_part;            // f32 [max tasks][128][B]: partial tiles of split reductions

@@ -198,6 +198,10 @@ PlanSpec PlanSpec::FromJson(const Json& plan) {
   if (s.capacity < 2 || s.capacity % kKvBlock) throw std::invalid_argument("capacity must be a positive multiple of 16");
   const Json empty;
   const Json& kv = plan.has("kv") ? plan.at("kv") : empty;
+  // "chunk_rows": rows of the batch may be consecutive positions of one sequence (their block-table rows name
+  // the same pool blocks): every row's key and value are appended before any row attends (chunked prefill)
+  s.chunk_rows = plan.flag("chunk_rows", false);
+  if (s.chunk_rows && !s.dense_batch) throw std::invalid_argument("chunk_rows needs a dense-batch plan (batch 16..64)");
   const std::string layout = kv.str("layout", "contiguous");
   if (layout != "contiguous" && layout != "paged") throw std::invalid_argument("kv.layout must be contiguous or paged");
   s.paged = layout == "paged";

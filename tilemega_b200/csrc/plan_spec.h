@@ -54,6 +54,7 @@ struct PlanSpec {
   bool fp8 = false;             // GEMV matrices as e4m3 bytes + fp32 row scales
   int lm_head_scale = -1;
   bool dense_batch = false;
+  bool chunk_rows = false;      // dense-batch plans: several rows of the batch may be consecutive positions of ONE sequence
   DenseGeo dgeo[kNumGemv] = {};
   int normed_buf = -1;
   // buffer table

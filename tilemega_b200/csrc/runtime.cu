@@ -310,11 +310,13 @@ void* tm_plan_create(int batch, void* const* external, int device) {
   p.qk_norm = s.qk_norm ? 1 : 0;
   p.stages_per_layer = s.stages_per_layer();
   p.dense = s.dense_batch ? 1 : 0;
+  p.chunk_rows = s.chunk_rows ? 1 : 0;
   // a traced step: one record per stage; dense-batch plans have 7 per layer (two RMSNorm stages) and norm + head at the end
   p.trace_stages = s.dense_batch ? 7 * s.layers + 2 : s.stages_per_layer() * s.layers + 1;
   // grid-wide arrivals of a step: one per stage except QKV (attention tasks wait per KV-head group)
   // plus the argmax hand-over; a dense-batch plan's RMSNorm stages arrive too
-  p.bars_per_step = s.dense_batch ? 6 * s.layers + 2 : (s.stages_per_layer() - 1) * s.layers + 1;
+  // (with chunk_rows also the QKV stage and the append stage that follows it)
+  p.bars_per_step = s.dense_batch ? (s.chunk_rows ? 8 : 6) * s.layers + 2 : (s.stages_per_layer() - 1) * s.layers + 1;
   for (int g = 0; g < tmb::kNumGemv; ++g) p.dgeo[g] = s.dgeo[g];
   p.eps = float(s.eps);
   p.qk_scale_log2 = float(1.4426950408889634 / std::sqrt(double(s.head_dim)));
@@ -347,7 +349,9 @@ void* tm_plan_create(int batch, void* const* external, int device) {
                      expert_rows});
   // dense-batch: the activation chunks of the GEMM stages (batch x 128 columns each) share the area
   // with the attention scratch; chunks must start on 1024-byte boundaries (128-byte swizzle)
-  if (s.dense_batch) xs = std::max(attention_scratch, tmb::dense_x_slots(batch) * batch * tmb::kDenseTileK * 2);
+  // (their attention tasks also hold the summed q, k, v rows of one KV head: gq + 2 more rows)
+  if (s.dense_batch)
+    xs = std::max(attention_scratch + (gq + 2) * s.head_dim * 2, tmb::dense_x_slots(batch) * batch * tmb::kDenseTileK * 2);
   xs = s.dense_batch ? (xs + 1023) & ~1023 : (xs + 127) & ~127;
   p.xs_bytes = xs;
   p.attn_min_spt = s.attn_min_slots;

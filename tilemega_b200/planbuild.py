@@ -32,7 +32,7 @@ def plan_document(config: dict, *, batch_lo: int = 1, batch_hi: int | None = Non
                   grid: int = 0, slots: int = 0, write_logits: bool = True,
                   tp: int = 1,
                   attn_min_slots: int | None = None, prefetch_window: int | None = None,
-                  weights: str = "bf16") -> dict:
+                  weights: str = "bf16", chunk_rows: bool = False) -> dict:
     """The sidecar for one decode plan; raises ValueError on shapes the kernels do not cover."""
     model = {key: config[key] for key in MODEL_KEYS if key in config}
     model.setdefault("head_dim", config["hidden_size"] // config["num_attention_heads"])
@@ -68,6 +68,10 @@ def plan_document(config: dict, *, batch_lo: int = 1, batch_hi: int | None = Non
         raise ValueError("weights must be 'bf16' or 'e4m3'")
     if weights == "e4m3":
         document["weights"] = "e4m3"   # GEMV matrices as e4m3 bytes + one fp32 scale per output row
+    if chunk_rows:
+        if not dense_batch or kv_layout != "paged":
+            raise ValueError("chunk_rows (rows of one sequence at consecutive positions) needs a paged dense-batch plan")
+        document["chunk_rows"] = True   # every row's key and value are appended before any row attends
     if prefetch_window is not None:
         document["prefetch_window"] = prefetch_window   # weight pages pulled into L2 ahead of a full ring (0: off)
     if attn_min_slots is not None:

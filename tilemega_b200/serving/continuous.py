@@ -14,6 +14,9 @@ host side, for a plan emitted with `kv_layout="paged"`:
   prompt mode runs a prompt through the decode plan, engine.py:38-41);
 * a request ends after `max_new_tokens` tokens or at its `eos` token.
 
+With a `chunk_rows` prefill plan (serving/prefill.py) an admitted prompt is prefilled in chunks into the
+same pool and decoding starts behind it; without one the prompt is teacher-forced as described above.
+
 `SlotScheduler` (admission, block accounting, completion) is plain Python and tested on the CPU;
 `ContinuousEngine` binds it to a plan and needs a CUDA device.
 """
@@ -112,6 +115,19 @@ class SlotScheduler:
                 ended.append(request)
         return ended
 
+    def prefilled(self, index: int, first_token: int) -> Request | None:
+        """The slot's whole prompt went through a prefill plan, which sampled `first_token` after its last
+        position: decoding starts behind the prompt. Returns the request if that token already ends it."""
+        slot = self.slots[index]
+        request = slot.request
+        slot.position = len(request.prompt)
+        request.generated.append(first_token)
+        if len(request.generated) >= request.max_new_tokens or first_token == request.eos:
+            self.pool.give_back(slot.blocks)
+            self.slots[index] = Slot()
+            return request
+        return None
+
     def forced_token(self, index: int) -> int | None:
         """The prompt token that must stand at the slot's NEXT position (None once the prompt is consumed)."""
         slot = self.slots[index]
@@ -125,7 +141,8 @@ class SlotScheduler:
 class ContinuousEngine:
     """A paged decode plan driven one step at a time with a changing set of sequences."""
 
-    def __init__(self, checkpoint, config: dict, decode_so, batch: int, device: int = 0, weights=None):
+    def __init__(self, checkpoint, config: dict, decode_so, batch: int, device: int = 0, weights=None,
+                 prefill_so=None, prefill_rows: int = 16):
         import torch
 
         from .plan import L2, PlanLibrary
@@ -157,6 +174,12 @@ class ContinuousEngine:
         self.host_tokens = torch.zeros(batch, dtype=torch.int32).pin_memory()
         self.rows = torch.arange(batch, device=where)
         self.steps_run = 0
+        # with a chunk_rows plan of the same model and pool size, prompts are prefilled in chunks of `prefill_rows`
+        # positions into this engine's pool instead of being teacher-forced through the decode plan
+        self.prefill = None
+        if prefill_so is not None:
+            from .prefill import ChunkedPrefill
+            self.prefill = ChunkedPrefill(checkpoint, config, prefill_so, prefill_rows, self.state.kv_storage, device)
 
     def submit(self, request: Request) -> None:
         self.scheduler.submit(request)
@@ -173,10 +196,20 @@ class ContinuousEngine:
     def step(self) -> list[Request]:
         """Admit what fits, run one decode step for every slot, collect the tokens. Returns the requests that ended."""
         torch = self.torch
-        for index in self.scheduler.admit():
+        admitted = self.scheduler.admit()
+        for index in admitted:
             self._place(index)
+        ended_in_prefill = []
+        if self.prefill is not None and admitted:
+            slots = [self.scheduler.slots[index] for index in admitted]
+            results = self.prefill.run([slot.request.prompt for slot in slots], [slot.blocks for slot in slots])
+            for index, slot, result in zip(admitted, slots, results):
+                self.state.tokens[index, len(slot.request.prompt)] = result.first_token
+                done = self.scheduler.prefilled(index, result.first_token)
+                if done is not None:
+                    ended_in_prefill.append(done)
         if not self.scheduler.active():
-            return []
+            return ended_in_prefill
         for index, slot in enumerate(self.scheduler.slots):
             self.host_positions[index] = slot.position if slot.request is not None else 0
         self.state.context_base.copy_(self.host_positions, non_blocking=True)
@@ -194,7 +227,7 @@ class ContinuousEngine:
             raise RuntimeError(f"a bounded device wait gave up: {gave_up}")
         self.steps_run += 1
         sampled = {index: int(self.host_tokens[index]) for index in self.scheduler.active()}
-        return self.scheduler.advance(sampled)
+        return ended_in_prefill + self.scheduler.advance(sampled)
 
     def run_until_done(self, limit: int = 100000) -> list[Request]:
         finished = []
@@ -205,6 +238,8 @@ class ContinuousEngine:
         return finished
 
     def close(self) -> None:
+        if self.prefill is not None:
+            self.prefill.close()
         self.plan.close()
 
     def __enter__(self) -> "ContinuousEngine":

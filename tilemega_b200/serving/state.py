@@ -110,7 +110,7 @@ def shuffled_block_table(batch: int, max_blocks: int, num_blocks: int, seed: int
 def allocate_state(config: dict, batch: int, decode: PlanLibrary, device: str | torch.device = "cuda",
                    block_table: torch.Tensor | None = None,
                    context_base: torch.Tensor | None = None, tp: int = 1,
-                   shared_blocks: bool = False) -> ServingState:
+                   shared_blocks: bool = False, kv_storage: torch.Tensor | None = None) -> ServingState:
     """`tp`: a tensor-parallel rank's state holds only its num_key_value_heads / tp KV heads
     (reference state.py:64-82); token state and RoPE tables are whole on every rank."""
     if decode.info.phase != 1:
@@ -134,7 +134,13 @@ def allocate_state(config: dict, batch: int, decode: PlanLibrary, device: str | 
         num_blocks = int(decode.manifest["kv"]["num_blocks"])
         max_blocks = capacity // KV_BLOCK
         # rows past a sequence's length are masked by selection, so the pool starts zeroed
-        kv_storage = torch.zeros((layers, 2, num_blocks, hkv, KV_BLOCK, dim), dtype=torch.bfloat16, device=device)
+        # `kv_storage`: the pool of another plan of the same model (a prefill plan and a decode plan serve the
+        # same sequences out of one pool)
+        shape = (layers, 2, num_blocks, hkv, KV_BLOCK, dim)
+        if kv_storage is None:
+            kv_storage = torch.zeros(shape, dtype=torch.bfloat16, device=device)
+        elif tuple(kv_storage.shape) != shape or kv_storage.dtype != torch.bfloat16 or kv_storage.device != device:
+            raise ValueError("the shared KV pool has another shape, dtype or device than this plan's")
         table = (block_table if block_table is not None
                  else torch.arange(batch * max_blocks, dtype=torch.int32).reshape(batch, max_blocks))
         if tuple(table.shape) != (batch, max_blocks) or table.dtype != torch.int32:
