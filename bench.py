@@ -52,10 +52,10 @@ NOMINAL_HBM_GBS = 8000.0
 # of the same kernel on 2-layer cases of the same shapes (traffic is proportional to the streamed
 # weights, so a full launch's traffic is this ratio times its algorithmic bytes). Keyed by
 # (model, batch): a workload without a capture reports no traffic.
-NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = {("llama-3.1-8b", 1): 0.9945}
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = {("llama-3.1-8b", 1): 0.9906, ("llama-3.1-8b", 64): 1.0142}
 # roofline.frac of the one-GPU headline run (profiles/decode_megakernel_llama31_8b_b1.md): the
 # denominator of config.mbu_retained_vs_1gpu in a tensor-parallel line
-SINGLE_GPU_FRAC = 0.775
+SINGLE_GPU_FRAC = 0.791
 TP_MODEL, TP_CONTEXT = "llama-3.1-70b", 4096
 
 
@@ -267,6 +267,67 @@ def run_reference(args) -> None:
     print(json.dumps(line), flush=True)
 
 
+def run_prefill(args) -> None:
+    """Secondary workload: chunked prefill of one prompt of `--prefill` tokens through the dense-batch plan
+    with chunk_rows (64 positions per step, weights streamed once per chunk). One JSON line in the same
+    shape as the decode line; a step is one chunk."""
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU implementation")
+    import time
+
+    from tilemega_b200.planbuild import PLAN_DIR, emit_plan, remove_plans
+    from tilemega_b200.serving.prefill import ChunkedPrefill
+    config = dict(MODELS[args.model or "llama-3.1-8b"])
+    if args.layers:
+        config["num_hidden_layers"] = args.layers
+    rows, length = 64, args.prefill
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    capacity = (length + 32) // 16 * 16
+    num_blocks = capacity // 16 + 2
+    plan_dir = PLAN_DIR / "bench"
+    so = emit_plan(config, plan_dir, batch_lo=rows, batch_hi=rows, capacity=capacity, kv_layout="paged",
+                   num_blocks=num_blocks, write_logits=False, chunk_rows=True)
+    layers, hkv, dim = config["num_hidden_layers"], config["num_key_value_heads"], synthetic.head_dim_of(config)
+    pool = torch.zeros((layers, 2, num_blocks, hkv, 16, dim), dtype=torch.bfloat16, device=device)
+    prompt = synthetic.seeded_tokens(1, length, config["vocab_size"], seed=3)[0].tolist()
+    blocks = (torch.randperm(num_blocks - 1, generator=torch.Generator().manual_seed(7)) + 1)[:-(-(length + 1) // 16)].tolist()
+    prefill = ChunkedPrefill(synthetic.LazySeededCheckpoint(config, seed=0, device=device), config, so, rows, pool, 0)
+    prefill.run([prompt[:2 * rows]], [blocks])                  # warm-up: two chunks
+    peak, peak_kind = measured_peak_gbs()
+    with ClockSampler(0) as clocks:
+        prefill.device_ms, prefill.chunks_run = 0.0, 0
+        torch.cuda.synchronize()
+        begin = time.perf_counter()
+        result = prefill.run([prompt], [blocks])[0]
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - begin
+    chunks, device_s = prefill.chunks_run, prefill.device_ms / 1e3
+    # algorithmic bytes: every chunk streams the GEMM weights once; row i of a chunk reads the p0 + i cached positions
+    hidden, inter, heads, vocab = config["hidden_size"], config["intermediate_size"], config["num_attention_heads"], config["vocab_size"]
+    weight_bytes = 2 * (layers * (hidden * (heads + 2 * hkv) * dim + heads * dim * hidden + 3 * hidden * inter) + vocab * hidden)
+    kv_bytes = sum(position + 1 for position in range(length)) * layers * 2 * hkv * dim * 2
+    total_bytes = chunks * weight_bytes + kv_bytes
+    flops = 2.0 * length * weight_bytes / 2
+    line = {
+        "metric": "prefill_tokens_per_s", "value": length / device_s, "unit": UNIT, "n_gpus": 1, "steps": chunks, "warmup": 2,
+        "ms_per_step": prefill.device_ms / chunks, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"{args.model or 'llama-3.1-8b'}-shaped chunked prefill, one prompt of {length} tokens, "
+                               f"{rows} positions per step, paged KV block 16, scattered blocks", "layers": layers,
+                   "l2": "inputs (15 GB of weights per chunk) exceed L2", "first_token": result.first_token},
+        "roofline": {"bound": "hbm", "achieved": total_bytes / device_s / 1e9, "peak": peak, "unit": "GB/s",
+                     "frac": total_bytes / device_s / 1e9 / peak, "traffic": None, "peak_kind": "of " + peak_kind,
+                     "bytes_per_launch": total_bytes / chunks, "tensor_tflops": flops / device_s / 1e12},
+        "e2e": {"value": length / wall, "unit": UNIT, "h2d_bytes_per_step": rows * (capacity // 16 + 2) * 4,
+                "d2h_bytes_per_step": 4},
+        "gpu_launches": chunks, "clocks": clocks.summary(),
+    }
+    prefill.close()
+    remove_plans(plan_dir)
+    print(json.dumps(line), flush=True)
+
+
 def run_ours(args) -> None:
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the product path has no CPU implementation")
@@ -470,6 +531,8 @@ def main() -> None:
     parser.add_argument("--layers", type=int, default=0, help="override the depth (profiling a small case)")
     parser.add_argument("--weights", choices=("bf16", "e4m3"), default="bf16",
                         help="e4m3: GEMV matrices as 8-bit codes with one fp32 scale per output row")
+    parser.add_argument("--prefill", type=int, default=0,
+                        help="secondary workload: chunked prefill of one prompt of this many tokens (one GPU)")
     parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     parser.add_argument("--trace", action="store_true",
                         help="after the timed runs, stamp one more step and print the per-stage table (rank 0)")
@@ -479,6 +542,8 @@ def main() -> None:
     args = parser.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.prefill:
+        run_prefill(args)
     else:
         run_ours(args)
 

@@ -67,6 +67,8 @@ class ChunkedPrefill:
         self.vocab = int(config["vocab_size"])
         self.has_logits = "serving.logits" in self.library.index
         self.chunks_run = 0
+        self.device_ms = 0.0    # kernel time of the chunks run so far (CUDA events around each launch)
+        self._events = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
 
     def run(self, prompts: list[list[int]], blocks: list[list[int]], want_logits: bool = False) -> list[PrefillResult]:
         """Prefill every prompt into its blocks of the pool. `blocks[s]` are sequence s's pool blocks in
@@ -96,8 +98,11 @@ class ChunkedPrefill:
             self.state.context_base.copy_(base)
             rows = torch.arange(self.rows, device=self.state.tokens.device)
             self.state.tokens[rows, base.to(rows.device).long()] = ids.to(rows.device)
+            self._events[0].record(self.stream)
             self.plan.launch(0, self.mode, self.stream.cuda_stream)
+            self._events[1].record(self.stream)
             self.stream.synchronize()
+            self.device_ms += self._events[0].elapsed_time(self._events[1])
             gave_up = self.plan.watchdog()
             if gave_up is not None:
                 raise RuntimeError(f"a bounded device wait gave up: {gave_up}")
