@@ -109,14 +109,10 @@ struct Ctx {
   uint32_t slot_used, slot_gemm, parity_warps, parity_mma;
   // streaming thread: where it is in the launch's sequence of weight pages, and how far ahead of
   // that it has prefetched into L2 (absolute page numbers count every GEMV stage's pages in program order)
-  int cur_seq, cur_npages, cur_ppt, cur_task;   // GEMV stage being streamed: its number, pages, pages per task, last task posted
-  int pf_seq;                                   // GEMV stage the prefetch cursor is in
-  long long cur_abs_base, pf_abs, pf_abs_base;  // first page of the streamed stage; cursor; first page of the cursor's stage
   __device__ Ctx(const MegaParams& q, unsigned char* s, int cta_index)
       : p(q), smem(s), warp(threadIdx.x >> 5), lane(threadIdx.x & 31), tid(threadIdx.x), cta(cta_index), slot(0), phase(0),
         bar_target(q.bar_base), task_seq(0), dead(false), q_pos(0), inst(0), pending(0), pending_next(0), gemv_seq(0),
-        route_phase(0), dq_pos(0), slot_used(0), slot_gemm(0), parity_warps(0), parity_mma(0), cur_seq(-1), cur_npages(0), cur_ppt(1), cur_task(0), pf_seq(0), cur_abs_base(0), pf_abs(-1),
-        pf_abs_base(0) {}
+        route_phase(0), dq_pos(0), slot_used(0), slot_gemm(0), parity_warps(0), parity_mma(0) {}
   __device__ uint64_t* full(int i) const { return reinterpret_cast<uint64_t*>(smem + kOffFull) + i; }
   __device__ uint64_t* empty(int i) const { return reinterpret_cast<uint64_t*>(smem + kOffEmpty) + i; }
   __device__ uint64_t* pfull(int i) const { return reinterpret_cast<uint64_t*>(smem + kOffPFull) + i; }
@@ -451,63 +447,6 @@ __device__ __forceinline__ int fifo_pop_uniform(Ctx& c) {
 // busy arithmetic warps, so every instruction on this path costs ring refill rate;
 // the loop is kept to a wait, a byte-count arrive and a bulk copy per slot.
 // ---------------------------------------------------------------------------
-// GEMV stage number `seq` of the launch (program order: per layer QKV, O, gate/up, down; after the
-// last layer the head; then the next step): where its pages are and how many.
-__device__ __forceinline__ void gemv_stage_pages(const MegaParams& p, int seq, const unsigned char*& pages, int& npages) {
-  const int per_step = 4 * p.layers + 1;
-  const int idx = seq % per_step;
-  const void* w;
-  int kind;
-  if (idx == 4 * p.layers) {
-    w = p.lm_head;
-    kind = kHead;
-  } else {
-    const LayerPtrs* lp = p.layer + (idx >> 2);
-    kind = idx & 3;   // kQkv, kOProj, kGateUp, kDown in this order
-    w = kind == kQkv ? lp->qkv : kind == kOProj ? lp->o : kind == kGateUp ? lp->gate_up : lp->down;
-  }
-  pages = static_cast<const unsigned char*>(w);
-  npages = p.geo[kind].ntasks * p.geo[kind].task_pages;
-}
-
-// The ring is full and the arithmetic warps are busy elsewhere (a grid barrier, row staging, the
-// attention chain): HBM would idle. Use the time to pull weight pages that lie just ahead of the
-// ring into L2, so that the ring refills from L2 when it drains. Every CTA prefetches the pages
-// whose absolute number is congruent to its index, at most prefetch_window pages (over all CTAs)
-// ahead of its own position, and never a page twice. One page per call; false when there is
-// nothing (more) to prefetch.
-struct PrefetchCursor {
-  long long abs, abs_base;   // next page of this CTA's share; first page of the stage it lies in
-  int seq;                   // that stage's number
-  int issued;                // 1: a page was prefetched by this call
-};
-
-static __device__ __noinline__ PrefetchCursor idle_prefetch(const MegaParams& p, int cta, long long here, int here_seq,
-                                                            long long here_base, PrefetchCursor cur) {
-  cur.issued = 0;
-  if (cur.abs < here) {
-    // the ring has overtaken the cursor: restart at this CTA's first page at or after `here`
-    cur.seq = here_seq;
-    cur.abs_base = here_base;
-    cur.abs = here + ((long long)cta - here % p.grid + p.grid) % p.grid;
-  }
-  if (cur.abs >= here + p.prefetch_window) return cur;
-  const int last_seq = p.nsteps * (4 * p.layers + 1);
-  const unsigned char* pages;
-  int npages;
-  for (;;) {
-    if (cur.seq >= last_seq) return cur;
-    gemv_stage_pages(p, cur.seq, pages, npages);
-    if (cur.abs - cur.abs_base < npages) break;
-    cur.abs_base += npages;
-    ++cur.seq;
-  }
-  bulk_prefetch_l2(pages + size_t(cur.abs - cur.abs_base) * kSlotBytes, kSlotBytes);
-  cur.abs += p.grid;
-  cur.issued = 1;
-  return cur;
-}
-
 __device__ __forceinline__ bool stream_wait_empty(Ctx& c, bool weight_page = true) {
   if (c.p.dense) {
     // wait for the release that matches what the slot held, then note what it is about to hold
@@ -525,17 +464,6 @@ __device__ __forceinline__ bool stream_wait_empty(Ctx& c, bool weight_page = tru
     c.slot_used |= bit;
     c.slot_gemm = weight_page ? (c.slot_gemm | bit) : (c.slot_gemm & ~bit);
     return ok;
-  }
-  if (c.p.prefetch_window > 0 && !c.dead) {
-    while (!mbar_try_wait(c.empty(c.slot), c.phase ^ 1u)) {
-      const long long here = c.cur_abs_base + (long long)c.cur_task * c.cur_ppt;
-      const PrefetchCursor next =
-          idle_prefetch(c.p, c.cta, here, c.cur_seq, c.cur_abs_base, PrefetchCursor{c.pf_abs, c.pf_abs_base, c.pf_seq, 0});
-      c.pf_abs = next.abs;
-      c.pf_abs_base = next.abs_base;
-      c.pf_seq = next.seq;
-      if (!next.issued) break;
-    }
   }
   return mbar_wait(c, c.empty(c.slot), c.phase ^ 1u, kSiteEmpty);
 }
@@ -597,18 +525,11 @@ __device__ __forceinline__ void stream_pages(Ctx& c, const GemvGeo& geo, const u
 // task t = one row tile over the whole reduction: its pages start at page t * pages_per_task
 __device__ __forceinline__ void stream_gemv_task(Ctx& c, const GemvGeo& geo, const unsigned char* weights, int t,
                                                  uint32_t page_bytes, uint64_t policy) {
-  c.cur_task = t;
   stream_pages(c, geo, weights + (size_t(t) * size_t(geo.task_pages) + size_t(geo.page0)) * page_bytes, t, page_bytes, policy);
 }
 
 __device__ __forceinline__ void stream_gemv(Ctx& c, const GemvGeo& geo, const void* weights, uint64_t policy) {
   const uint32_t page_bytes = uint32_t(geo.page_bytes);
-  // position of this stage in the launch's page sequence (the idle prefetch works from it)
-  c.cur_abs_base += c.cur_npages;
-  c.cur_npages = geo.ntasks * geo.task_pages;
-  c.cur_ppt = geo.task_pages;
-  c.cur_task = 0;
-  ++c.cur_seq;
   const unsigned char* w = static_cast<const unsigned char*>(weights);
   // Tasks are claimed in chunks of geo.claim_chunk (about 64 KB of pages): the claim for the
   // next chunk is in flight while this one is copied, and its round trip to L2 and back

@@ -124,7 +124,6 @@ struct MegaParams {
   int grid, nslots, xs_bytes;
   int attn_min_spt;         // least ring slots of keys per attention task (a task's fixed cost wants amortising)
   int bars_per_step;        // grid-wide arrivals of one decode step
-  int prefetch_window;      // weight pages (over all CTAs) the streaming threads may pull into L2 ahead of the ring while it is full; 0: off
   unsigned long long bar_base;     // grid-barrier arrivals before this launch
   unsigned long long watchdog_ns;  // per-wait limit
   GemvGeo geo[kNumGemv];

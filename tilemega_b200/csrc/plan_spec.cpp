@@ -214,8 +214,6 @@ PlanSpec PlanSpec::FromJson(const Json& plan) {
   s.slots = int(plan.integer("slots", 0));
   s.attn_min_slots = int(plan.integer("attn_min_slots", s.attn_min_slots));
   if (s.attn_min_slots < 1 || s.attn_min_slots > 64) throw std::invalid_argument("attn_min_slots must lie in [1, 64]");
-  s.prefetch_window = int(plan.integer("prefetch_window", s.prefetch_window));
-  if (s.prefetch_window < 0 || s.prefetch_window > 8192) throw std::invalid_argument("prefetch_window must lie in [0, 8192] pages");
   s.write_logits = plan.flag("write_logits", true);
   const Json& geometry = plan.has("geometry") ? plan.at("geometry") : empty;
   // "weights": "e4m3": every GEMV matrix as e4m3 bytes with one fp32 scale per output row (the scale

@@ -44,7 +44,7 @@ struct PlanSpec {
   bool paged = false;
   int num_blocks = 0, max_blocks = 0;
   // execution
-  int grid = 0, slots = 0, attn_min_slots = 4, prefetch_window = 0;
+  int grid = 0, slots = 0, attn_min_slots = 4;
   bool write_logits = true;
   int down_splits = 1;
   GemvGeo down_part[kMaxDownSplits] = {};

@@ -355,9 +355,6 @@ void* tm_plan_create(int batch, void* const* external, int device) {
   xs = s.dense_batch ? (xs + 1023) & ~1023 : (xs + 127) & ~127;
   p.xs_bytes = xs;
   p.attn_min_spt = s.attn_min_slots;
-  // the idle prefetch walks the dense stage sequence QKV, O, gate/up, down, head: plans whose weight
-  // stream is not that (chosen experts, a down projection cut into parts) run without it
-  p.prefetch_window = (s.experts || s.down_splits > 1 || s.dense_batch) ? 0 : s.prefetch_window;
   const int limit = int(prop.sharedMemPerBlockOptin);
   p.nslots = tmb::kMaxSlots;
   if (s.slots > 0) p.nslots = std::min(s.slots, tmb::kMaxSlots);

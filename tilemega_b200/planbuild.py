@@ -31,7 +31,7 @@ def plan_document(config: dict, *, batch_lo: int = 1, batch_hi: int | None = Non
                   kv_layout: str = "contiguous", num_blocks: int = 0, geometry: dict | None = None,
                   grid: int = 0, slots: int = 0, write_logits: bool = True,
                   tp: int = 1,
-                  attn_min_slots: int | None = None, prefetch_window: int | None = None,
+                  attn_min_slots: int | None = None,
                   weights: str = "bf16", chunk_rows: bool = False) -> dict:
     """The sidecar for one decode plan; raises ValueError on shapes the kernels do not cover."""
     model = {key: config[key] for key in MODEL_KEYS if key in config}
@@ -72,8 +72,6 @@ def plan_document(config: dict, *, batch_lo: int = 1, batch_hi: int | None = Non
         if not dense_batch or kv_layout != "paged":
             raise ValueError("chunk_rows (rows of one sequence at consecutive positions) needs a paged dense-batch plan")
         document["chunk_rows"] = True   # every row's key and value are appended before any row attends
-    if prefetch_window is not None:
-        document["prefetch_window"] = prefetch_window   # weight pages pulled into L2 ahead of a full ring (0: off)
     if attn_min_slots is not None:
         document["attn_min_slots"] = attn_min_slots   # least ring slots of keys per attention task
     return document
