@@ -1574,21 +1574,32 @@ __device__ void attn_stage(Ctx& c, const LayerPtrs& lp, int past, bool tr, int s
       // Qwen3: every query head and the key head are RMS-normalised over their own D
       // values before RoPE, y = w * bf16(x * rsqrt(mean x^2 + eps)), the product rounded
       // to bf16 (python/tilemega/serving/export.py:63-65,82-84). One warp per head.
-      for (int hh = c.warp; hh < GQ + 1; hh += kConsumerWarps) {
+      // (a warp with two heads -- GQ + 1 = 9 heads on 8 warps -- fetches both before it uses either:
+      // one L2 round trip, not two)
+      constexpr int kHeadsPerWarp = (GQ + 1 + kConsumerWarps - 1) / kConsumerWarps;
+      float xv[kHeadsPerWarp][D / 32], wv[kHeadsPerWarp][D / 32];
+#pragma unroll
+      for (int i = 0; i < kHeadsPerWarp; ++i) {
+        const int hh = c.warp + i * kConsumerWarps;
         const unsigned short* wn = reinterpret_cast<const unsigned short*>(hh < GQ ? lp.q_norm : lp.k_norm);
-        float xv[D / 32], ss = 0.f;
 #pragma unroll
         for (int j = 0; j < D / 32; ++j) {
-          xv[j] = bf16_from_bits(__ldcg(row + hh * D + c.lane + 32 * j));
-          ss = fmaf(xv[j], xv[j], ss);
+          xv[i][j] = hh < GQ + 1 ? bf16_from_bits(__ldcg(row + hh * D + c.lane + 32 * j)) : 0.f;
+          wv[i][j] = hh < GQ + 1 ? bf16_from_bits(__ldg(wn + c.lane + 32 * j)) : 0.f;
         }
+      }
+#pragma unroll
+      for (int i = 0; i < kHeadsPerWarp; ++i) {
+        const int hh = c.warp + i * kConsumerWarps;
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < D / 32; ++j) ss = fmaf(xv[i][j], xv[i][j], ss);
 #pragma unroll
         for (int m = 16; m; m >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
         const float inv = 1.0f / sqrtf(ss / float(D) + p.eps);
+        if (hh < GQ + 1) {
 #pragma unroll
-        for (int j = 0; j < D / 32; ++j) {
-          const float w = bf16_from_bits(__ldg(wn + c.lane + 32 * j));
-          qkn[hh * D + c.lane + 32 * j] = __float2bfloat16_rn(w * bf16_round(xv[j] * inv));
+          for (int j = 0; j < D / 32; ++j) qkn[hh * D + c.lane + 32 * j] = __float2bfloat16_rn(wv[i][j] * bf16_round(xv[i][j] * inv));
         }
       }
       consumer_sync();
@@ -1835,7 +1846,7 @@ __device__ void attn_stage(Ctx& c, const LayerPtrs& lp, int past, bool tr, int s
         constexpr int TPH = kConsumerThreads / GQ;   // threads per head
         constexpr int NO = D / TPH;                  // outputs per thread: columns d0 + TPH * k
         static_assert(kConsumerThreads % GQ == 0 && D % TPH == 0, "merge mapping");
-        constexpr int kMergeBatch = NO >= 4 ? 6 : 12;   // at most 48 loads per thread in flight (registers)
+        constexpr int kMergeBatch = NO >= 4 ? 9 : 12;   // at most 54 loads per thread in flight (registers)
         const int h = c.tid / TPH, d0 = c.tid - h * TPH;
         float mx = -INFINITY, ls = 0.f, as[NO];
 #pragma unroll
