@@ -102,3 +102,63 @@ def test_continuous_engine_decodes_on_from_a_prefilled_pool(plan_dir):
         logits = decoder.forward(history, [0], kv, head_fp32=True)[0].float()[len(request.prompt) - 1:]
         chosen = logits[torch.arange(len(request.generated)), torch.tensor(request.generated)]
         assert (chosen >= logits.max(dim=-1).values - 4 * LOGIT_TOLERANCE).all(), (request.id, request.generated)
+
+
+def test_llama_8b_shape_prefill_is_chunk_size_invariant_and_agrees_with_the_decode_path(plan_dir):
+    """At the benchmark's widths (hidden 4096, FFN 14336, vocabulary 128256; 8 of the 32 layers keep it
+    quick), where the CPU oracle is too slow: properties. (1) Chunks of 16 and of 64 positions write the
+    same cache bit for bit and sample the same token -- a row's sums do not depend on how many other
+    rows share its tile; (2) a rerun is bit-identical; (3) the decode plan teacher-forced over the same
+    prompt (GEMV path, other summation order) writes a cache that agrees to bf16 drift and samples the
+    same token or a near tie of it."""
+    from tilemega_b200.serving.plan import PlanLibrary
+    from tilemega_b200.serving.state import allocate_state
+    from tilemega_b200.serving.weights import load_weights
+    config = dict(synthetic.LLAMA_3_1_8B, num_hidden_layers=8)
+    length, capacity, num_blocks = 150, 192, 16
+    device = torch.device("cuda", 0)
+    checkpoint = synthetic.LazySeededCheckpoint(config, seed=0, device=device)
+    prompt = synthetic.seeded_tokens(1, length, config["vocab_size"], seed=8)[0].tolist()
+    blocks = [5, 2, 9, 1, 7, 3, 11, 4, 6, 8]            # ten scattered blocks: 160 positions
+    layers, hkv, dim = config["num_hidden_layers"], config["num_key_value_heads"], config["head_dim"]
+    pools, tokens = {}, {}
+    for run, rows in enumerate((16, 64, 64)):
+        so = emit_plan(config, plan_dir, batch_lo=rows, batch_hi=rows, capacity=capacity, kv_layout="paged",
+                       num_blocks=num_blocks, chunk_rows=True, write_logits=False)
+        pool = torch.zeros((layers, 2, num_blocks, hkv, 16, dim), dtype=torch.bfloat16, device=device)
+        with ChunkedPrefill(checkpoint, config, so, rows, pool) as prefill:
+            result = prefill.run([prompt], [blocks])[0]
+        pools[run], tokens[run] = pool[:, :, blocks].clone(), result.first_token
+        del pool
+        torch.cuda.empty_cache()
+    assert torch.equal(pools[0], pools[1]) and tokens[0] == tokens[1], "chunks of 16 and of 64 positions disagree"
+    assert torch.equal(pools[1], pools[2]) and tokens[1] == tokens[2], "a rerun is not bit-identical"
+    # the same prompt teacher-forced through the batch-1 decode plan
+    so = emit_plan(config, plan_dir, batch_lo=1, batch_hi=1, capacity=capacity, kv_layout="paged", num_blocks=num_blocks)
+    lib = PlanLibrary(so)
+    weights = load_weights(checkpoint, lib, device=device)
+    table = torch.zeros((1, capacity // 16), dtype=torch.int32)
+    table[0, :len(blocks)] = torch.tensor(blocks, dtype=torch.int32)
+    table[0, len(blocks):] = torch.tensor([12, 13], dtype=torch.int32)
+    state = allocate_state(config, 1, lib, device, block_table=table)
+    plan = lib.create(1, {name: t.data_ptr() for name, t in weights.items()} | state.pointers, 0)
+    state.tokens[0, :length] = torch.tensor(prompt, dtype=torch.int32, device=device)
+    plan.set_prompt_len(length)
+    plan.set_steps(list(range(length)))
+    plan.launch_steps(0, length, 2, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert plan.watchdog() is None
+    decoded = state.kv_storage[:, :, blocks].float()
+    prefilled = pools[1].float()
+    used = slice(0, length)                                    # positions written: rows of the ten blocks in order
+    a = decoded.permute(0, 1, 3, 2, 4, 5).reshape(layers, 2, hkv, -1, dim)[:, :, :, used]
+    b = prefilled.permute(0, 1, 3, 2, 4, 5).reshape(layers, 2, hkv, -1, dim)[:, :, :, used]
+    assert torch.equal(a[0], b[0]) or ((a[0] - b[0]).abs() <= 2 * bf16_ulp(b[0]) + 1e-6).float().mean().item() >= 0.999
+    assert (a - b).abs().mean().item() <= 0.01 * b.abs().max().item()
+    assert (a - b).abs().max().item() <= 0.10 * b.abs().max().item()
+    host = torch.empty(config["vocab_size"], dtype=torch.float32)
+    plan.read_buffer("serving.logits", host.data_ptr(), host.numel() * 4)
+    best = host.max().item()
+    assert host[int(state.tokens[0, length])].item() >= best - 4 * LOGIT_TOLERANCE      # the decode path's own choice
+    assert host[tokens[1]].item() >= best - 4 * LOGIT_TOLERANCE                         # the prefill's choice
+    plan.close()
