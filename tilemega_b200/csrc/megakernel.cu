@@ -18,6 +18,11 @@
 //    rounding sites of the reference's epilogues. Results do not depend on which
 //    CTA ran a task, so the run-to-run bits are identical.
 //
+// A third kernel in this file (TMB_DENSE, batch 16..64) keeps the streaming warp and the
+// stage list but runs the GEMM stages on tcgen05 tiles with accumulators in tensor memory
+// (see "Dense-batch plans" below); with chunk_rows its rows may be consecutive positions
+// of one sequence (chunked prefill). A fourth instantiation (TMB_FP8) reads e4m3 weight pages.
+//
 // Stage list per layer (reference: include/tilemega/Codegen/tasks/
 // Sm90DenseProgram.cuh:903-939): qkv (RMSNorm fused) -> RoPE + KV append +
 // split-KV attention (+ last-arriver merge) -> o (+residual) -> gate/up
@@ -443,7 +448,8 @@ __device__ __forceinline__ int fifo_pop_uniform(Ctx& c) {
 }
 
 // ---------------------------------------------------------------------------
-// streaming warp: ONE thread runs it. A lone warp issues slowly next to eight
+// streaming warp: lane 0 runs it (the other lanes only share the scattered copies
+// of an attention slot, see stream_attn). A lone warp issues slowly next to eight
 // busy arithmetic warps, so every instruction on this path costs ring refill rate;
 // the loop is kept to a wait, a byte-count arrive and a bulk copy per slot.
 // ---------------------------------------------------------------------------
