@@ -17,7 +17,7 @@ def test_moe_plan_tables(plan_dir):
     hidden, experts, inter, topk = config["hidden_size"], config["num_experts"], config["moe_intermediate_size"], 4
     assert table["serving.router_logits"].elements_per_batch == experts
     assert table["serving.mlp"].elements_per_batch == topk * inter            # one row per chosen expert
-    assert table["serving.route_index"].elements_constant == config["num_hidden_layers"] * topk
+    assert table["serving.route_index"].elements_per_batch == config["num_hidden_layers"] * topk   # [layers][batch][topk]
     assert table["l0.router.weight"].elements_constant == experts * hidden
     assert table["l0.gate_up.weight"].elements_constant == experts * 2 * inter * hidden
     assert table["l0.down.weight"].elements_constant == experts * hidden * 2048   # 768 columns padded to one page
@@ -50,7 +50,8 @@ def test_expert_stack_recipe_packs_every_expert_by_itself():
 
 
 def test_moe_limits(plan_dir):
-    with pytest.raises(RuntimeError, match="batch 1"):
-        PlanLibrary(emit_plan(synthetic.TINY_MOE, plan_dir, batch_lo=1, batch_hi=2, capacity=64))
+    assert PlanLibrary(emit_plan(synthetic.TINY_MOE, plan_dir, batch_lo=1, batch_hi=8, capacity=64)).info.batch_hi == 8
+    with pytest.raises((RuntimeError, ValueError)):      # 16 and more rows would need the experts on the dense-batch tiles
+        PlanLibrary(emit_plan(synthetic.TINY_MOE, plan_dir, batch_lo=16, batch_hi=16, capacity=64))
     with pytest.raises(RuntimeError, match="norm_topk_prob"):
         PlanLibrary(emit_plan(dict(synthetic.TINY_MOE, norm_topk_prob=False), plan_dir, batch_lo=1, batch_hi=1, capacity=64))

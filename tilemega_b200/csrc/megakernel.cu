@@ -83,7 +83,7 @@ constexpr int kOffDenseXs = 8192;
 // Features compiled into an instantiation of the kernel (template parameter X): the plain
 // one (0) serves unsharded dense plans and carries neither.
 constexpr int kXTp = 1;    // tensor parallelism: all-reduce epilogue, argmax exchange
-constexpr int kXMoe = 2;   // mixture of experts and the per-head QK norm (batch 1)
+constexpr int kXMoe = 2;   // mixture of experts and the per-head QK norm
 constexpr int kXFp8 = 4;   // weights are e4m3 bytes with fp32 row scales (pages of 8 rows x 4096 columns)
 constexpr int kFifo = 32;          // entries; the streaming warp keeps at most kFifo/2 unread
 
@@ -698,14 +698,16 @@ __device__ __forceinline__ bool stream_layer_tail(Ctx& c, const LayerPtrs& lp, u
   stream_gemv(c, p.geo[kOProj], lp.o, policy);
   if ((X & kXMoe) && p.experts) {
     stream_gemv(c, p.geo[kRouter], lp.router, policy);
-    // the experts of this layer are known once the arithmetic warps have routed
-    if (!mbar_wait(c, c.route_bar(), c.route_phase, kSiteFull)) return false;
-    c.route_phase ^= 1u;
-    int expert[kMaxTopK];
+    for (int b = 0; b < p.batch; ++b) {   // token by token, as the arithmetic warps route them
+      // the token's experts are known once the arithmetic warps have routed it
+      if (!mbar_wait(c, c.route_bar(), c.route_phase, kSiteFull)) return false;
+      c.route_phase ^= 1u;
+      int expert[kMaxTopK];
 #pragma unroll
-    for (int i = 0; i < kMaxTopK; ++i) expert[i] = c.route_e()[i];
-    stream_expert_gate_up(c, p.geo[kGateUp], lp.gate_up, expert, policy);
-    stream_expert_down(c, p.geo[kDown], lp.down, expert, policy);
+      for (int i = 0; i < kMaxTopK; ++i) expert[i] = c.route_e()[i];
+      stream_expert_gate_up(c, p.geo[kGateUp], lp.gate_up, expert, policy);
+      stream_expert_down(c, p.geo[kDown], lp.down, expert, policy);
+    }
   } else {
     stream_gemv(c, p.geo[kGateUp], lp.gate_up, policy);
     if (p.down_splits > 1) {
@@ -1314,14 +1316,14 @@ __device__ __forceinline__ void gemv_stage(Ctx& c, const GemvGeo& geo, const Gem
 }
 
 // ---------------------------------------------------------------------------
-// arithmetic warps: mixture of experts (batch 1)
+// arithmetic warps: mixture of experts (one token at a time)
 // ---------------------------------------------------------------------------
-// Top-k routing of the one token, by warp 0: softmax in fp32 over the router's bf16
+// Top-k routing of token b, by warp 0: softmax in fp32 over the router's bf16
 // logits, the k largest probabilities in descending order (ties to the smaller expert
 // index), renormalised to sum 1 in fp32 (python/tilemega/moe/export.py:79-87). The result
 // goes to shared memory for both the arithmetic warps and the streaming thread, and from
 // CTA 0 to global memory for the host.
-static __device__ __noinline__ void route_token(Ctx& c, int layer) {
+static __device__ __noinline__ void route_token(Ctx& c, int layer, int b) {
   const MegaParams& p = c.p;
   // probabilities of all experts in shared memory (the activation-row area is free between
   // stages), then every expert's rank by counting: rank = how many experts beat it (larger
@@ -1331,7 +1333,7 @@ static __device__ __noinline__ void route_token(Ctx& c, int layer) {
   float* prob = reinterpret_cast<float*>(c.xs());
   if (c.warp == 0) {
     constexpr int kPerLane = 8;   // experts <= 256
-    const unsigned short* logits = reinterpret_cast<const unsigned short*>(p.router_logits);
+    const unsigned short* logits = reinterpret_cast<const unsigned short*>(p.router_logits) + size_t(b) * p.experts;
     float v[kPerLane];
     float mx = -INFINITY;
 #pragma unroll
@@ -1378,26 +1380,25 @@ static __device__ __noinline__ void route_token(Ctx& c, int layer) {
     __syncwarp(0xffu);   // every lane has read all weights before any is overwritten
     c.route_w()[s] = w;
     c.route_e()[s] = e;
-    if (c.cta == 0 && s < p.topk) {
-      p.route_idx[layer * p.topk + s] = e;
-      p.route_w[layer * p.topk + s] = w;
+    if (c.cta == 0 && s < p.topk) {   // [layer][token][rank]
+      p.route_idx[(layer * p.batch + b) * p.topk + s] = e;
+      p.route_w[(layer * p.batch + b) * p.topk + s] = w;
     }
   }
   consumer_sync();
   if (c.tid == 0) mbar_arrive(c.route_bar());   // the streaming thread may start on the experts
 }
 
-// The chosen experts' down projections and their weighted sum, batch 1. Sub-task
+// The chosen experts' down projections and their weighted sum for ONE token (row b of the batch). Sub-task
 // (row tile, expert slot s) is one page; the activation row of slot s is that expert's
 // SwiGLU output. The warp that owns a row tile runs the epilogues of its topk sub-tasks
 // in slot order and keeps the running sum:
 //   y = bf16( sum_s fp32( bf16(W_s h_s) * w_s ) ), x += y
 // (python/tilemega/moe/export.py:29-37: expert outputs in the model dtype, times the fp32
 // routing weight, summed over the ranks in fp32, one rounding; then the layer's residual add).
-template <int B>
-__device__ __noinline__ void moe_down_stage(Ctx& c, const GemvGeo& geo, bool tr, int stage) {
-  static_assert(B == 1, "mixture-of-experts plans run batch 1");
+static __device__ __noinline__ void moe_down_stage(Ctx& c, const GemvGeo& geo, bool tr, int stage, int b) {
   const MegaParams& p = c.p;
+  unsigned short* const xrow = reinterpret_cast<unsigned short*>(p.x) + size_t(b) * p.hidden;   // token b's residual stream
   const int topk = p.topk;
   const int pitch_bytes = (geo.k + 8) * 2;
   {
@@ -1439,7 +1440,7 @@ __device__ __noinline__ void moe_down_stage(Ctx& c, const GemvGeo& geo, bool tr,
       for (int w = 0; w < kConsumerWarps; ++w) v += red[(pending_buf * 8 + w) * 8 + lane];
       running = __fadd_rn(running, __fmul_rn(bf16_round(v), c.route_w()[s]));
       if (s == topk - 1) {
-        static_cast<__nv_bfloat16*>(p.x)[tile * kTileN + lane] = __float2bfloat16_rn(bf16_round(running) + residual);
+        xrow[tile * kTileN + lane] = bf16_bits(bf16_round(running) + residual);
         running = 0.f;
       }
     }
@@ -1449,7 +1450,7 @@ __device__ __noinline__ void moe_down_stage(Ctx& c, const GemvGeo& geo, bool tr,
     const int tile = t / kMaxTopK, s = t % kMaxTopK;   // powers of two: no division in the loop
     const bool owner = warp == int(tile_seq & 7u);
     if (owner && s == 0 && lane < kTileN)
-      residual = bf16_from_bits(__ldcg(reinterpret_cast<const unsigned short*>(p.x) + tile * kTileN + lane));
+      residual = bf16_from_bits(__ldcg(xrow + tile * kTileN + lane));
     float d[4][4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) d[0][i] = d[1][i] = d[2][i] = d[3][i] = 0.f;
@@ -1948,25 +1949,30 @@ __device__ void consumer_main(Ctx& c) {
       trace_mark(c, tr, stage, 1);
       if ((X & kXMoe) && p.experts) {
         // mixture of experts: router scores, top-k, then the chosen experts only
-        if constexpr ((X & kXMoe) != 0 && B == 1) {
+        if constexpr ((X & kXMoe) != 0) {
           io = GemvIo{p.x, lp.norm2, 0, kEpiStore, p.router_logits, nullptr, 1, nullptr, 0, 0u};
           gemv_stage<B, X>(c, p.geo[kRouter], io, tr, stage++);
           grid_arrive(c);
-          trace_mark(c, tr, stage, 0);
-          if (!grid_wait(c)) return;
-          trace_mark(c, tr, stage, 1);
-          route_token(c, l);
-          trace_mark(c, tr, stage, 1);   // the experts' inputs are there once the token is routed
-          // task t = (expert slot, row tile): with one token the SwiGLU epilogue's output
-          // index t * 4 + r is row `slot` of h[topk][inter]
-          io = GemvIo{p.x, lp.norm2, 0, kEpiSwiGLU, p.h, nullptr, 1, nullptr, 0, 0u};
-          gemv_stage<B, X>(c, p.geo[kGateUp], io, tr, stage++);
-          grid_arrive(c);
-          trace_mark(c, tr, stage, 0);
-          if (!grid_wait(c)) return;
-          trace_mark(c, tr, stage, 1);
-          moe_down_stage<B>(c, p.geo[kDown], tr, stage++);
-          grid_arrive(c);
+          // The experts' MLP runs token by token: every token has its own experts, so their weights are
+          // streamed per token (nothing is shared between tokens), each token a gate/up and a down stage
+          // of the one-token form; 2 * B stages and arrivals per layer after the router's.
+          for (int b = 0; b < B; ++b) {
+            trace_mark(c, tr, stage, 0);
+            if (!grid_wait(c)) return;         // b == 0: the router's scores; b > 0: token b-1's down stage read h
+            trace_mark(c, tr, stage, 1);
+            route_token(c, l, b);
+            trace_mark(c, tr, stage, 1);   // the experts' inputs are there once the token is routed
+            // task t = (expert slot, row tile): with one token the SwiGLU epilogue's output
+            // index t * 4 + r is row `slot` of h[topk][inter]
+            io = GemvIo{static_cast<const __nv_bfloat16*>(p.x) + size_t(b) * p.hidden, lp.norm2, 0, kEpiSwiGLU, p.h, nullptr, 1, nullptr, 0, 0u};
+            gemv_stage<1, X>(c, p.geo[kGateUp], io, tr, stage++);
+            grid_arrive(c);
+            trace_mark(c, tr, stage, 0);
+            if (!grid_wait(c)) return;
+            trace_mark(c, tr, stage, 1);
+            moe_down_stage(c, p.geo[kDown], tr, stage++, b);
+            grid_arrive(c);
+          }
         }
         lp = upcoming;
         continue;
@@ -2900,9 +2906,9 @@ cudaError_t run_decode_extended(const MegaParams& p, cudaStream_t stream, bool p
   const int gq = p.heads / p.kv_heads;
   if (gq != 4 && gq != 8) return cudaErrorInvalidValue;
   if (p.experts > 0 || p.qk_norm) {
-    if (p.batch != 1 || p.tp_world > 1) return cudaErrorInvalidValue;
-    return gq == 8 ? run_instance<1, 128, 8, kXMoe>(p, smem_bytes, stream, prepare)
-                   : run_instance<1, 128, 4, kXMoe>(p, smem_bytes, stream, prepare);
+    if (p.tp_world > 1) return cudaErrorInvalidValue;
+    return gq == 8 ? run_batch<128, 8, kXMoe>(p, smem_bytes, stream, prepare)
+                   : run_batch<128, 4, kXMoe>(p, smem_bytes, stream, prepare);
   }
   return gq == 8 ? run_batch<128, 8, kXTp>(p, smem_bytes, stream, prepare)
                  : run_batch<128, 4, kXTp>(p, smem_bytes, stream, prepare);

@@ -184,7 +184,7 @@ PlanSpec PlanSpec::FromJson(const Json& plan) {
   if (s.experts && s.tp != 1) throw std::invalid_argument("tensor parallel mixture of experts is not built");
   s.batch_lo = int(plan.integer("batch_lo", 1));
   s.batch_hi = int(plan.integer("batch_hi", s.batch_lo));
-  if (s.experts && s.batch_hi != 1) throw std::invalid_argument("mixture-of-experts plans are built for batch 1");
+  if (s.experts && s.batch_hi > kMaxBatch) throw std::invalid_argument("mixture-of-experts plans are built for batch 1..8");
   s.capacity = int(plan.integer("capacity", 0));
   s.dense_batch = s.batch_hi > kMaxBatch;
   if (s.dense_batch) {
@@ -306,13 +306,13 @@ PlanSpec PlanSpec::FromJson(const Json& plan) {
   };
   s.qkv_buf = add("serving.qkv", 0, 0, 0, uint64_t(s.qkv_rows()), "");
   s.attn_buf = add("serving.attention", 0, 0, 0, uint64_t(s.heads) * D, "");
-  // with experts: one row per chosen expert (batch 1)
+  // with experts: one row per chosen expert of the token being served (tokens take turns)
   s.mlp_buf = add("serving.mlp", 0, 0, 0, s.experts ? I * uint64_t(s.topk) : I, "");
   if (s.experts) {
     s.router_buf = add("serving.router_logits", 0, 0, 0, uint64_t(s.experts), "");
-    // the experts chosen by the last step and their weights, [layers][topk] (batch 1)
-    s.route_idx_buf = add("serving.route_index", 0, 2, uint64_t(s.layers) * s.topk, 0, "");
-    s.route_weight_buf = add("serving.route_weight", 0, 1, uint64_t(s.layers) * s.topk, 0, "");
+    // the experts chosen by the last step and their weights, [layers][batch][topk]
+    s.route_idx_buf = add("serving.route_index", 0, 2, 0, uint64_t(s.layers) * s.topk, "");
+    s.route_weight_buf = add("serving.route_weight", 0, 1, 0, uint64_t(s.layers) * s.topk, "");
   }
   s.logits_buf = add("serving.logits", 0, 1, 0, uint64_t(s.head_rows), "");  // fp32 accumulators of this rank's head rows
   for (int l = 0; l < s.layers; ++l) {

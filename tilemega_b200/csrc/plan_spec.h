@@ -70,7 +70,9 @@ struct PlanSpec {
 
   int qkv_rows() const { return (heads + 2 * kv_heads) * head_dim; }
   int max_k() const;
-  int stages_per_layer() const { return (experts ? 6 : 5) + down_splits - 1; }
+  // stages of a layer at a batch size: QKV, attention, O, gate/up, down (in parts for a wide batch); with
+  // experts a router stage, and gate/up + down once per token
+  int stages_per_layer(int batch) const { return experts ? 4 + 2 * batch : 5 + down_splits - 1; }
   // algorithmic bytes of one decode step (weights of every GEMV + KV rows read; with experts:
   // the dense matrices, the router, and batch * topk experts per layer)
   uint64_t weight_bytes() const;

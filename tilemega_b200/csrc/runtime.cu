@@ -308,15 +308,15 @@ void* tm_plan_create(int batch, void* const* external, int device) {
   p.topk = s.topk;
   p.norm_topk = s.norm_topk ? 1 : 0;
   p.qk_norm = s.qk_norm ? 1 : 0;
-  p.stages_per_layer = s.stages_per_layer();
+  p.stages_per_layer = s.stages_per_layer(batch);
   p.dense = s.dense_batch ? 1 : 0;
   p.chunk_rows = s.chunk_rows ? 1 : 0;
   // a traced step: one record per stage; dense-batch plans have 7 per layer (two RMSNorm stages) and norm + head at the end
-  p.trace_stages = s.dense_batch ? 7 * s.layers + 2 : s.stages_per_layer() * s.layers + 1;
+  p.trace_stages = s.dense_batch ? 7 * s.layers + 2 : s.stages_per_layer(batch) * s.layers + 1;
   // grid-wide arrivals of a step: one per stage except QKV (attention tasks wait per KV-head group)
   // plus the argmax hand-over; a dense-batch plan's RMSNorm stages arrive too
   // (with chunk_rows also the QKV stage and the append stage that follows it)
-  p.bars_per_step = s.dense_batch ? (s.chunk_rows ? 8 : 6) * s.layers + 2 : (s.stages_per_layer() - 1) * s.layers + 1;
+  p.bars_per_step = s.dense_batch ? (s.chunk_rows ? 8 : 6) * s.layers + 2 : (s.stages_per_layer(batch) - 1) * s.layers + 1;
   for (int g = 0; g < tmb::kNumGemv; ++g) p.dgeo[g] = s.dgeo[g];
   p.eps = float(s.eps);
   p.qk_scale_log2 = float(1.4426950408889634 / std::sqrt(double(s.head_dim)));
@@ -452,7 +452,7 @@ void* tm_plan_create(int batch, void* const* external, int device) {
   // barrier word, then the attention arrival counters: one block, rezeroed per launch
   const size_t attn_cnt = size_t(batch) * s.kv_heads;
   // ... and the task claim counters of every stage instance of the longest possible launch
-  const size_t stage_cnt = size_t(s.capacity) * (size_t(s.stages_per_layer()) * size_t(s.layers) + 1) + 2;   // + the two look-ahead claims past the last stage
+  const size_t stage_cnt = size_t(s.capacity) * (size_t(s.stages_per_layer(batch)) * size_t(s.layers) + 1) + 2;   // + the two look-ahead claims past the last stage
   const size_t ready_offset = (128 + attn_cnt * sizeof(unsigned) + 7) & ~size_t(7);
   plan->claim_offset = ready_offset + size_t(s.kv_heads) * sizeof(unsigned long long);
   plan->sync_bytes = plan->claim_offset + stage_cnt * sizeof(unsigned);
