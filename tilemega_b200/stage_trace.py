@@ -132,6 +132,9 @@ def print_table(config: dict, trace, per_layer: int, context: int, batch: int, t
     if batch > 8:   # dense-batch plans: RMSNorm is a stage of its own, twice per layer
         kinds = ["norm1", "qkv", "attn", "o", "norm2", "gate_up", "down"]
     parts = per_layer - len(kinds) + 1
+    if synthetic.is_moe(config) and batch > 1:   # the experts' MLP runs token by token
+        kinds = kinds[:-2] + [f"{kind} tok {b}" for b in range(batch) for kind in ("gate_up", "down")]
+        parts = 1
     if parts > 1:
         kinds = kinds[:-1] + [f"down part {i}" for i in range(parts)]
     start = trace[:, 0, 1].min()
@@ -143,7 +146,7 @@ def print_table(config: dict, trace, per_layer: int, context: int, batch: int, t
           f"ideal = bytes / {peak:.0f} GB/s; medians over CTAs, means over layers 1..{layers - 1})")
     for k, kind in enumerate(kinds):
         index = [l * per_layer + k for l in range(1, layers)] or [k]
-        ideal = sizes.get(kind.split(" part")[0], 0) / peak / 1e3
+        ideal = sizes.get(kind.split(" part")[0].split(" tok")[0], 0) / peak / 1e3
         if " part" in kind:
             ideal /= parts
         print(f"{kind:12s} {wall[index].mean() / 1e3:7.2f} {ideal:7.2f} "
