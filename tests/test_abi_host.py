@@ -112,3 +112,24 @@ def test_unsupported_shapes_are_rejected(plan_dir):
         plan_document(synthetic.TINY, batch_lo=1, capacity=40)
     with pytest.raises(ValueError):
         plan_document(synthetic.TINY, batch_lo=2, capacity=64, kv_layout="paged", num_blocks=1)
+
+
+def test_prefill_plan_tables(plan_dir):
+    """A prefill plan (phase 0) as the reference's driver sees it: seq = the prompt length, one step, the
+    sequences' state buffers shared with the decode plan by name, GEMM weights under names of their own."""
+    config = synthetic.TINY_D128
+    so = emit_plan(config, plan_dir, batch_lo=1, batch_hi=4, capacity=64, phase="prefill", seq=21)
+    lib = PlanLibrary(so)
+    assert (lib.info.phase, lib.info.seq, lib.info.batch_lo, lib.info.batch_hi, lib.info.capacity) == (0, 21, 1, 4, 64)
+    assert (lib.info.past_lo, lib.info.past_hi) == (0, 0)
+    table = {buffer.name: buffer for buffer in lib.buffers}
+    decode = {buffer.name: buffer for buffer in PlanLibrary(emit_plan(config, plan_dir, batch_lo=1, batch_hi=4, capacity=64)).buffers}
+    for name in ("serving.tokens", "serving.rope_cos", "kv_cache.k.0", "kv_cache.v.1", "model.embed_tokens.weight", "l0.norm1.weight"):
+        assert (table[name].elements_constant, table[name].elements_per_batch, table[name].pack_json) == \
+               (decode[name].elements_constant, decode[name].elements_per_batch, decode[name].pack_json), name
+    hidden = config["hidden_size"]
+    assert (table["serving.hidden"].elements_constant, table["serving.hidden"].elements_per_batch) == (64 * hidden, 0)
+    assert "prefill.l0.qkv.weight" in table and "l0.qkv.weight" not in table and "prefill.lm_head.weight" in table
+    assert '"tile_n":128' in table["prefill.l1.down.weight"].pack_json.replace(" ", "")
+    with pytest.raises(ValueError):
+        emit_plan(config, plan_dir, batch_lo=1, batch_hi=2, capacity=64, phase="prefill", seq=64)

@@ -162,3 +162,47 @@ def test_llama_8b_shape_prefill_is_chunk_size_invariant_and_agrees_with_the_deco
     assert host[int(state.tokens[0, length])].item() >= best - 4 * LOGIT_TOLERANCE      # the decode path's own choice
     assert host[tokens[1]].item() >= best - 4 * LOGIT_TOLERANCE                         # the prefill's choice
     plan.close()
+
+
+@pytest.mark.parametrize("kv_layout", ["contiguous", "paged"])
+def test_prefill_plan_behind_the_abi_feeds_the_decode_plan(kv_layout, plan_dir):
+    """The reference driver's flow with a prefill binary (python/tilemega/serving/engine.py:41-57,89-92,
+    144-146): a phase-0 plan whose ONE step runs the whole batch of prompts over the state the decode plan
+    shares, then the decode plan's steps behind the prompt. Checked against the engine's prompt mode (the
+    prompt teacher-forced through the decode plan) and, teacher-forced, against the fp32 forward."""
+    from tilemega_b200.serving.engine import ServingEngine
+    from tilemega_b200.serving.state import shuffled_block_table
+    config = synthetic.TINY_D128
+    batch, prompt_len, new_tokens, capacity = 3, 37, 6, 64      # 111 (sequence, position) rows: two kernel steps
+    weights = bf16_weights(config)
+    checkpoint = TensorCheckpoint(weights, config.get("tie_word_embeddings", False))
+    prompt = synthetic.seeded_tokens(batch, prompt_len, config["vocab_size"], seed=12)
+    num_blocks = batch * capacity // 16 + 3
+    layout = dict(kv_layout=kv_layout, num_blocks=num_blocks if kv_layout == "paged" else 0)
+    table = shuffled_block_table(batch, capacity // 16, num_blocks, seed=2) if kv_layout == "paged" else None
+    decode_so = emit_plan(config, plan_dir, batch_lo=batch, batch_hi=batch, capacity=capacity, **layout)
+    prefill_so = emit_plan(config, plan_dir, batch_lo=batch, batch_hi=batch, capacity=capacity, phase="prefill",
+                           seq=prompt_len, **layout)
+    with ServingEngine(checkpoint, config, decode_so, batch, prompt_len, new_tokens, block_table=table) as engine:
+        by_decode = engine.generate(prompt).tokens.clone()
+        cache_by_decode = engine.state.kv_storage.clone()
+    with ServingEngine(checkpoint, config, decode_so, batch, prompt_len, new_tokens, block_table=table,
+                       prefill_so=prefill_so) as engine:
+        result = engine.generate(prompt)
+        tokens = result.tokens.clone()
+        again = engine.generate(prompt).tokens.clone()          # a second request through the same plans
+        cache = engine.state.kv_storage.clone()
+    assert torch.equal(again, tokens)
+    # the two paths differ in the summation order of their GEMMs only: bf16 drift of a two-layer model
+    drift = (cache.float() - cache_by_decode.float()).abs()
+    assert drift.max().item() <= 0.05 * cache_by_decode.float().abs().max().item()
+    decoder = OracleDecoder(config, weights, torch.float32, capacity)
+    for b in range(batch):
+        history = torch.cat((prompt[b], tokens[b, :-1].to(prompt.dtype))).view(1, -1).to(torch.int32)
+        kv = PagedKV(config, 1, capacity, torch.float32)
+        logits = decoder.forward(history, [0], kv, head_fp32=True)[0].float()[prompt_len - 1:]
+        chosen = logits[torch.arange(new_tokens), tokens[b].long()]
+        assert (chosen >= logits.max(dim=-1).values - 4 * LOGIT_TOLERANCE).all(), (b, tokens[b].tolist())
+        decided = (logits.topk(2).values[:, 0] - logits.topk(2).values[:, 1]) > 4 * LOGIT_TOLERANCE
+        if decided.all():
+            assert torch.equal(tokens[b], by_decode[b])

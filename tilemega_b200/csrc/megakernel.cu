@@ -244,15 +244,27 @@ __device__ __forceinline__ void trace_mark(const Ctx& c, bool on, int stage, int
 // attention partition (identical on the streaming and the arithmetic side)
 // ---------------------------------------------------------------------------
 struct AttnTask {
-  int b, g, c;       // sequence, KV head, chunk
+  int b, g, c;       // row of the batch, KV head, chunk
+  int sq;            // the sequence the row belongs to (= b outside prefill plans)
   int pos;           // position of the new token (= number of cached tokens)
   int ns, nch;       // slots of the sequence, chunks per KV head
   int slot0, slot1;  // slot range of this chunk
   int task0;         // first task of (b, g)
 };
 
+// Which sequence row b of the batch belongs to (its block-table row, its token row): itself, except in a
+// prefill plan, whose rows are (sequence, position) pairs listed per step (`past` is then the step's first pair).
+__device__ __forceinline__ int seq_of(const MegaParams& p, int past, int b) {
+  return p.row_seq ? __ldg(p.row_seq + past + b) : b;
+}
+
 __device__ __forceinline__ int seq_pos(const MegaParams& p, int past, int b) {
-  int pos = past + (p.ctx_base ? __ldg(p.ctx_base + b) : 0);
+  int pos;
+  if (p.row_pos) {
+    pos = __ldg(p.row_pos + past + b) + (p.ctx_base ? __ldg(p.ctx_base + __ldg(p.row_seq + past + b)) : 0);
+  } else {
+    pos = past + (p.ctx_base ? __ldg(p.ctx_base + b) : 0);
+  }
   return min(max(pos, 0), p.capacity - 1);
 }
 
@@ -310,6 +322,7 @@ __device__ __forceinline__ AttnTask attn_task(const MegaParams& p, int past, int
     if (t < base + n || b == p.batch - 1) {
       const int r = t - base;
       a.b = b;
+      a.sq = seq_of(p, past, b);
       a.g = r / nch;
       a.c = r % nch;
       a.pos = pos;
@@ -370,6 +383,7 @@ __device__ __forceinline__ bool attn_next(const MegaParams& p, int past, int nk,
   const int u0 = w.base + g * w.ns;
   const int first = u0 / sh.per, last = (u0 + w.ns - 1) / sh.per;
   a.b = w.b;
+  a.sq = seq_of(p, past, w.b);
   a.g = g;
   a.pos = seq_pos(p, past, w.b);
   a.ns = w.ns;
@@ -634,7 +648,7 @@ __device__ __forceinline__ void stream_attn(Ctx& c, const LayerPtrs& lp, int pas
       for (int s = a.slot0; s < a.slot1; ++s) {
         const int nb = min(NB, nblk - s * NB);
         // this lane's block-table entry first (its load is in flight during the wait below)
-        const long long e = table_entry(c.p, a.b, s * NB + min(piece, max(nb - 1, 0)));
+        const long long e = table_entry(c.p, a.sq, s * NB + min(piece, max(nb - 1, 0)));
         const long long off = (e * c.p.kv_block_stride + (long long)a.g * c.p.kv_head_stride) * 2;
         int word = -1;                           // the slot to fill, or -1: the wait gave up
         if (lead && stream_wait_empty(c, false)) {
@@ -1573,7 +1587,7 @@ __device__ void attn_stage(Ctx& c, const LayerPtrs& lp, int past, bool tr, int s
     auto qkv_value = [&](int idx) -> unsigned short { return summed_here ? qraw[idx] : __ldcg(row + idx); };
     long long new_off = 0;
     if (tail) {
-      const long long e = table_entry(p, a.b, a.pos / kKvBlock);
+      const long long e = table_entry(p, a.sq, a.pos / kKvBlock);
       new_off = e * p.kv_block_stride + (long long)a.g * p.kv_head_stride + (a.pos % kKvBlock) * D;
     }
     const bool qk_norm = (X & kXMoe) && lp.q_norm != nullptr;   // only the mixture-of-experts / Qwen3 instantiation carries this
@@ -2541,7 +2555,7 @@ __device__ void append_stage_dense(Ctx& c, const LayerPtrs& lp, int past) {
   for (int u = c.cta; u < p.batch * p.kv_heads; u += p.grid) {
     const int b = u / p.kv_heads, g = u - b * p.kv_heads;
     const int pos = seq_pos(p, past, b);
-    const long long e = table_entry(p, b, pos / kKvBlock);
+    const long long e = table_entry(p, seq_of(p, past, b), pos / kKvBlock);
     const long long at = e * p.kv_block_stride + (long long)g * p.kv_head_stride + (pos % kKvBlock) * D + kv_swizzled(d, pos);
     const int n0 = g * (GQ + 2) * D + (GQ + (is_v ? 1 : 0)) * D;   // first feature of this head's key (value) row
     auto feature = [&](int col) -> float {
@@ -2575,8 +2589,8 @@ __device__ void consumer_main_dense(Ctx& c) {
   for (int si = 0; si < p.nsteps; ++si) {
     const int step = p.first_step + si;
     const int past = __ldg(p.past + step);
-    if (si == 0) {
-      if (c.tid < B) dtok(c)[c.tid] = __ldcg(p.tokens + size_t(c.tid) * p.capacity + seq_pos(p, past, c.tid));
+    if (si == 0 || p.row_seq) {   // (a prefill plan's rows are other (sequence, position) pairs in every step)
+      if (c.tid < B) dtok(c)[c.tid] = __ldcg(p.tokens + size_t(seq_of(p, past, c.tid)) * p.capacity + seq_pos(p, past, c.tid));
       consumer_sync();
     }
     if (c.cta == 0 && c.tid == 0) p.step_ns[step] = global_timer();
@@ -2702,7 +2716,7 @@ __device__ void consumer_main_dense(Ctx& c) {
       }
       if (c.lane == 0) {
         const int pos = seq_pos(p, past, b);
-        int* slot = p.tokens + size_t(b) * p.capacity + min(pos + 1, p.capacity - 1);
+        int* slot = p.tokens + size_t(seq_of(p, past, b)) * p.capacity + min(pos + 1, p.capacity - 1);
         int tok = min(max(bi, 0), p.vocab - 1);
         if (pos + 1 < p.prompt_len) {
           tok = __ldcg(slot);   // teacher-forced prompt position: the token state wins

@@ -167,6 +167,10 @@ struct MegaParams {
   // dense-batch plans (dense != 0): GEMM stages on tcgen05 tiles
   int dense;
   int chunk_rows;              // rows may be consecutive positions of one sequence: append stage + barrier before attention
+  // prefill plans: row r of step s is position row_pos[s * batch + r] (plus the sequence's context_base) of sequence
+  // row_seq[s * batch + r]; the plan's `past` entry of step s is s * batch (null: row b is sequence b at position past)
+  const int* row_seq;
+  const int* row_pos;
   DenseGeo dgeo[kNumGemv];     // indexed by StageKind (kRouter unused)
   void* xn;                    // bf16 [B][H]: the RMSNorm output a GEMM stage reads
   float* gemm_part;            // f32 [max tasks][128][B]: partial tiles of split reductions

@@ -132,7 +132,9 @@ uint64_t PlanSpec::weight_bytes() const {
 
 PlanSpec PlanSpec::FromJson(const Json& plan) {
   PlanSpec s;
-  if (plan.str("phase", "decode") != "decode") throw std::invalid_argument("only decode plans are built");
+  const std::string phase = plan.str("phase", "decode");
+  if (phase != "decode" && phase != "prefill") throw std::invalid_argument("decode and prefill plans are built (phase)");
+  s.prefill = phase == "prefill";
   const Json& model = plan.at("model");
   s.hidden = int(model.integer("hidden_size", 0));
   s.inter = int(model.integer("intermediate_size", 0));
@@ -186,9 +188,17 @@ PlanSpec PlanSpec::FromJson(const Json& plan) {
   s.batch_hi = int(plan.integer("batch_hi", s.batch_lo));
   if (s.experts && s.batch_hi > kMaxBatch) throw std::invalid_argument("mixture-of-experts plans are built for batch 1..8");
   s.capacity = int(plan.integer("capacity", 0));
-  s.dense_batch = s.batch_hi > kMaxBatch;
+  s.dense_batch = s.batch_hi > kMaxBatch || s.prefill;
+  if (s.prefill) {
+    // the batch interval counts sequences; the kernel's rows are (sequence, position) pairs, 64 per step
+    s.prefill_seq = int(plan.integer("seq", 0));
+    if (s.batch_lo < 1 || s.batch_hi < s.batch_lo || s.batch_hi > kDenseMaxBatch)
+      throw std::invalid_argument("a prefill plan covers 1..64 sequences");
+    if (s.prefill_seq < 1 || s.prefill_seq >= s.capacity) throw std::invalid_argument("seq must lie in [1, capacity)");
+  }
   if (s.dense_batch) {
-    if (s.batch_lo <= kMaxBatch || s.batch_hi > kDenseMaxBatch || s.batch_lo % 16 || s.batch_hi % 16 || s.batch_hi < s.batch_lo)
+    if (!s.prefill &&
+        (s.batch_lo <= kMaxBatch || s.batch_hi > kDenseMaxBatch || s.batch_lo % 16 || s.batch_hi % 16 || s.batch_hi < s.batch_lo))
       throw std::invalid_argument("a dense-batch plan covers batch sizes 16, 32, 48, 64 (interval bounds multiples of 16)");
     if (s.head_dim != 128 || s.tp != 1 || s.experts || s.qk_norm || s.hidden > 8192)
       throw std::invalid_argument("dense-batch plans are built for unsharded dense models with head_dim 128 and hidden <= 8192");
@@ -200,7 +210,7 @@ PlanSpec PlanSpec::FromJson(const Json& plan) {
   const Json& kv = plan.has("kv") ? plan.at("kv") : empty;
   // "chunk_rows": rows of the batch may be consecutive positions of one sequence (their block-table rows name
   // the same pool blocks): every row's key and value are appended before any row attends (chunked prefill)
-  s.chunk_rows = plan.flag("chunk_rows", false);
+  s.chunk_rows = plan.flag("chunk_rows", false) || s.prefill;
   if (s.chunk_rows && !s.dense_batch) throw std::invalid_argument("chunk_rows needs a dense-batch plan (batch 16..64)");
   const std::string layout = kv.str("layout", "contiguous");
   if (layout != "contiguous" && layout != "paged") throw std::invalid_argument("kv.layout must be contiguous or paged");
@@ -287,8 +297,16 @@ PlanSpec PlanSpec::FromJson(const Json& plan) {
     s.context_base = add("serving.context_base", 1, 2, 0, 1, "");
   }
   s.embed = add("model.embed_tokens.weight", 1, 0, V * H, 0, Alias("model.embed_tokens.weight"));
-  s.hidden_buf = add("serving.hidden", 0, 0, 0, H, "");
-  if (s.dense_batch) s.normed_buf = add("serving.normed", 0, 0, 0, H, "");   // RMSNorm output read by the GEMM stages
+  // activation buffers hold one row per row of the kernel's batch: per sequence in a decode plan, a fixed
+  // kDenseMaxBatch rows in a prefill plan (whose batch counts sequences)
+  auto act = [&](const char* name, uint32_t dtype, uint64_t per_row) {
+    return s.prefill ? add(name, 0, dtype, uint64_t(kDenseMaxBatch) * per_row, 0, "") : add(name, 0, dtype, 0, per_row, "");
+  };
+  // a prefill plan's GEMM weights are packed as 128 x 128 pages, a small-batch decode plan's as 8 x 2048: the
+  // names differ so that a driver can hold both plans' buffers in one table (python/tilemega/serving/engine.py:49-57)
+  const std::string wp = s.prefill ? "prefill." : "";
+  s.hidden_buf = act("serving.hidden", 0, H);
+  if (s.dense_batch) s.normed_buf = act("serving.normed", 0, H);   // RMSNorm output read by the GEMM stages
   // weight pages: 8 rows x 2048 columns for the GEMV path, 128 x 128 (a tcgen05 operand tile) for dense-batch plans
   const int page_n = s.dense_batch ? kDenseTileN : kTileN;
   auto page_k = [&](int stage) { return s.dense_batch ? kDenseTileK : s.geo[stage].tile_k; };
@@ -304,17 +322,17 @@ PlanSpec PlanSpec::FromJson(const Json& plan) {
   auto scale_of = [&](const std::string& name, const std::string& source, int rows) {
     return s.fp8 ? add(name, 1, 1, uint64_t(rows), 0, "{\"kind\":\"e4m3_scale\",\"source\":" + source + "}") : -1;
   };
-  s.qkv_buf = add("serving.qkv", 0, 0, 0, uint64_t(s.qkv_rows()), "");
-  s.attn_buf = add("serving.attention", 0, 0, 0, uint64_t(s.heads) * D, "");
+  s.qkv_buf = act("serving.qkv", 0, uint64_t(s.qkv_rows()));
+  s.attn_buf = act("serving.attention", 0, uint64_t(s.heads) * D);
   // with experts: one row per chosen expert of the token being served (tokens take turns)
-  s.mlp_buf = add("serving.mlp", 0, 0, 0, s.experts ? I * uint64_t(s.topk) : I, "");
+  s.mlp_buf = act("serving.mlp", 0, s.experts ? I * uint64_t(s.topk) : I);
   if (s.experts) {
     s.router_buf = add("serving.router_logits", 0, 0, 0, uint64_t(s.experts), "");
     // the experts chosen by the last step and their weights, [layers][batch][topk]
     s.route_idx_buf = add("serving.route_index", 0, 2, 0, uint64_t(s.layers) * s.topk, "");
     s.route_weight_buf = add("serving.route_weight", 0, 1, 0, uint64_t(s.layers) * s.topk, "");
   }
-  s.logits_buf = add("serving.logits", 0, 1, 0, uint64_t(s.head_rows), "");  // fp32 accumulators of this rank's head rows
+  s.logits_buf = act("serving.logits", 1, uint64_t(s.head_rows));  // fp32 accumulators of this rank's head rows
   for (int l = 0; l < s.layers; ++l) {
     const std::string p = "l" + std::to_string(l) + ".";
     const std::string m = "model.layers." + std::to_string(l) + ".";
@@ -325,7 +343,7 @@ PlanSpec PlanSpec::FromJson(const Json& plan) {
         Sources({m + "self_attn.q_proj.weight", m + "self_attn.k_proj.weight", m + "self_attn.v_proj.weight"}) +
         ",\"hkv\":" + std::to_string(s.kv_heads) + ",\"qperkv\":" + std::to_string(s.heads / s.kv_heads) +
         ",\"head_dim\":" + std::to_string(s.head_dim) + Shard(0, s.tp) + "}";
-    lb.qkv = add(p + "qkv.weight", 1, weight_dtype, uint64_t(s.geo[kQkv].n) * s.geo[kQkv].k, 0, weight_pages(qkv_source, kQkv));
+    lb.qkv = add(wp + p + "qkv.weight", 1, weight_dtype, uint64_t(s.geo[kQkv].n) * s.geo[kQkv].k, 0, weight_pages(qkv_source, kQkv));
     lb.qkv_scale = scale_of(p + "qkv.scale", qkv_source, s.geo[kQkv].n);
     if (s.paged) {
       const uint64_t pool = uint64_t(s.num_blocks) * s.kv_heads * kKvBlock * D;
@@ -337,7 +355,7 @@ PlanSpec PlanSpec::FromJson(const Json& plan) {
       lb.v = add("kv_cache.v." + std::to_string(l), 1, 0, 0, cache, "");
     }
     const std::string o_source = Alias(m + "self_attn.o_proj.weight", Shard(1, s.tp));
-    lb.o = add(p + "o.weight", 1, weight_dtype, uint64_t(s.geo[kOProj].n) * s.geo[kOProj].k, 0, weight_pages(o_source, kOProj));
+    lb.o = add(wp + p + "o.weight", 1, weight_dtype, uint64_t(s.geo[kOProj].n) * s.geo[kOProj].k, 0, weight_pages(o_source, kOProj));
     lb.o_scale = scale_of(p + "o.scale", o_source, s.geo[kOProj].n);
     lb.norm2 = add(p + "norm2.weight", 1, 0, H, 0, Alias(m + "post_attention_layernorm.weight"));
     if (s.qk_norm) {
@@ -364,17 +382,17 @@ PlanSpec PlanSpec::FromJson(const Json& plan) {
     const std::string gate_up_source = "{\"kind\":\"gate_up_interleave\",\"sources\":" +
                                        Sources({m + "mlp.gate_proj.weight", m + "mlp.up_proj.weight"}) +
                                        ",\"u\":" + std::to_string(swiglu_unit) + Shard(0, s.tp) + "}";
-    lb.gate_up = add(p + "gate_up.weight", 1, weight_dtype, uint64_t(s.geo[kGateUp].n) * s.geo[kGateUp].k, 0,
+    lb.gate_up = add(wp + p + "gate_up.weight", 1, weight_dtype, uint64_t(s.geo[kGateUp].n) * s.geo[kGateUp].k, 0,
                      weight_pages(gate_up_source, kGateUp));
     lb.gate_up_scale = scale_of(p + "gate_up.scale", gate_up_source, s.geo[kGateUp].n);
     const std::string down_source = Alias(m + "mlp.down_proj.weight", Shard(1, s.tp));
-    lb.down = add(p + "down.weight", 1, weight_dtype, uint64_t(s.geo[kDown].n) * s.geo[kDown].k, 0, weight_pages(down_source, kDown));
+    lb.down = add(wp + p + "down.weight", 1, weight_dtype, uint64_t(s.geo[kDown].n) * s.geo[kDown].k, 0, weight_pages(down_source, kDown));
     lb.down_scale = scale_of(p + "down.scale", down_source, s.geo[kDown].n);
     s.layer.push_back(lb);
   }
   s.final_norm = add("model.norm.weight", 1, 0, H, 0, Alias("model.norm.weight"));
   const std::string head_source = Alias("lm_head.weight", Shard(0, s.tp));
-  s.lm_head = add("lm_head.weight", 1, weight_dtype, uint64_t(s.geo[kHead].n) * s.geo[kHead].k, 0, weight_pages(head_source, kHead));
+  s.lm_head = add(wp + "lm_head.weight", 1, weight_dtype, uint64_t(s.geo[kHead].n) * s.geo[kHead].k, 0, weight_pages(head_source, kHead));
   s.lm_head_scale = scale_of("lm_head.scale", head_source, s.geo[kHead].n);
   return s;
 }

@@ -55,6 +55,10 @@ struct PlanSpec {
   int lm_head_scale = -1;
   bool dense_batch = false;
   bool chunk_rows = false;      // dense-batch plans: several rows of the batch may be consecutive positions of ONE sequence
+  // prefill plans (phase 0): batch_lo..batch_hi count SEQUENCES of `prefill_seq` prompt positions each; the kernel
+  // runs kDenseMaxBatch rows per step, (sequence, position) pairs in order, ceil(batch * seq / rows) steps per launch
+  bool prefill = false;
+  int prefill_seq = 0;
   DenseGeo dgeo[kNumGemv] = {};
   int normed_buf = -1;
   // buffer table

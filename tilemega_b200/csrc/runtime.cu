@@ -115,6 +115,7 @@ struct Plan {
   tmb::MegaParams* ranks_dev = nullptr; // parameter records of a several-ranks-in-one-launch job (owned by its first plan)
   size_t sync_bytes = 0;
   size_t claim_offset = 0;
+  uint32_t prefill_chunks = 0;          // prefill plan: kernel steps (64 rows each) behind its one plan step
 };
 
 Plan* AsPlan(void* handle) {
@@ -208,12 +209,12 @@ int tm_plan_query(tm_plan_info* out) {
   const tmb::PlanSpec& s = lib.spec;
   std::memset(out, 0, sizeof(*out));
   out->abi_version = TM_SERVING_ABI_VERSION;
-  out->phase = TM_SERVING_DECODE;
+  out->phase = s.prefill ? TM_SERVING_PREFILL : TM_SERVING_DECODE;
   out->batch_lo = s.batch_lo;
   out->batch_hi = s.batch_hi;
-  out->seq = 1;
+  out->seq = s.prefill ? s.prefill_seq : 1;
   out->past_lo = 0;
-  out->past_hi = s.capacity - 1;
+  out->past_hi = s.prefill ? 0 : s.capacity - 1;
   out->capacity = s.capacity;
   out->grid = s.grid;  // 0: one CTA per SM of the device the plan is created on
   out->residency = 1;
@@ -263,10 +264,14 @@ void* tm_plan_create(int batch, void* const* external, int device) {
       return nullptr;
     }
   }
-  if (s.dense_batch && batch % 16) {
+  if (s.dense_batch && !s.prefill && batch % 16) {
     Fail(-1, "tm_plan_create: a dense-batch plan runs batch sizes 16, 32, 48 or 64");
     return nullptr;
   }
+  // rows of the kernel's batch: the sequences themselves, except in a prefill plan, whose `batch` sequences of
+  // `seq` positions run as (sequence, position) rows, kDenseMaxBatch per kernel step
+  const int seqs = batch;
+  const int rows = s.prefill ? tmb::kDenseMaxBatch : batch;
   DeviceScope scope(device);
   cudaDeviceProp prop{};
   if (cudaGetDeviceProperties(&prop, device) != cudaSuccess || prop.major < 10) {
@@ -293,7 +298,7 @@ void* tm_plan_create(int batch, void* const* external, int device) {
     }
   }
   tmb::MegaParams& p = plan->params;
-  p.batch = batch;
+  p.batch = rows;
   p.hidden = s.hidden;
   p.inter = s.inter;
   p.heads = s.heads;
@@ -308,15 +313,15 @@ void* tm_plan_create(int batch, void* const* external, int device) {
   p.topk = s.topk;
   p.norm_topk = s.norm_topk ? 1 : 0;
   p.qk_norm = s.qk_norm ? 1 : 0;
-  p.stages_per_layer = s.stages_per_layer(batch);
+  p.stages_per_layer = s.stages_per_layer(rows);
   p.dense = s.dense_batch ? 1 : 0;
   p.chunk_rows = s.chunk_rows ? 1 : 0;
   // a traced step: one record per stage; dense-batch plans have 7 per layer (two RMSNorm stages) and norm + head at the end
-  p.trace_stages = s.dense_batch ? 7 * s.layers + 2 : s.stages_per_layer(batch) * s.layers + 1;
+  p.trace_stages = s.dense_batch ? 7 * s.layers + 2 : s.stages_per_layer(rows) * s.layers + 1;
   // grid-wide arrivals of a step: one per stage except QKV (attention tasks wait per KV-head group)
   // plus the argmax hand-over; a dense-batch plan's RMSNorm stages arrive too
   // (with chunk_rows also the QKV stage and the append stage that follows it)
-  p.bars_per_step = s.dense_batch ? (s.chunk_rows ? 8 : 6) * s.layers + 2 : (s.stages_per_layer(batch) - 1) * s.layers + 1;
+  p.bars_per_step = s.dense_batch ? (s.chunk_rows ? 8 : 6) * s.layers + 2 : (s.stages_per_layer(rows) - 1) * s.layers + 1;
   for (int g = 0; g < tmb::kNumGemv; ++g) p.dgeo[g] = s.dgeo[g];
   p.eps = float(s.eps);
   p.qk_scale_log2 = float(1.4426950408889634 / std::sqrt(double(s.head_dim)));
@@ -345,13 +350,13 @@ void* tm_plan_create(int batch, void* const* external, int device) {
   // (rows are padded by 8 elements so that the batch rows of a k-chunk sit on distinct banks)
   // a normalised stage also parks its raw rows and the norm weights there: 2*batch + 1 hidden-wide rows
   // (batch > 4: the rows are normalised in a second pass over global memory instead: batch + 1 rows)
-  int xs = std::max({batch * (s.max_k() + 8) * 2, (batch > 4 ? batch + 1 : 2 * batch + 1) * (s.geo[tmb::kQkv].k + 8) * 2, attention_scratch,
+  int xs = std::max({rows * (s.max_k() + 8) * 2, (rows > 4 ? rows + 1 : 2 * rows + 1) * (s.geo[tmb::kQkv].k + 8) * 2, attention_scratch,
                      expert_rows});
   // dense-batch: the activation chunks of the GEMM stages (batch x 128 columns each) share the area
   // with the attention scratch; chunks must start on 1024-byte boundaries (128-byte swizzle)
   // (their attention tasks also hold the summed q, k, v rows of one KV head: gq + 2 more rows)
   if (s.dense_batch)
-    xs = std::max(attention_scratch + (gq + 2) * s.head_dim * 2, tmb::dense_x_slots(batch) * batch * tmb::kDenseTileK * 2);
+    xs = std::max(attention_scratch + (gq + 2) * s.head_dim * 2, tmb::dense_x_slots(rows) * rows * tmb::kDenseTileK * 2);
   xs = s.dense_batch ? (xs + 1023) & ~1023 : (xs + 127) & ~127;
   p.xs_bytes = xs;
   p.attn_min_spt = s.attn_min_slots;
@@ -380,8 +385,8 @@ void* tm_plan_create(int batch, void* const* external, int device) {
     // 16 rows: entry (b, j) = b*Hkv*capacity/16 + j, heads capacity*D apart
     // (python/tilemega/serving/state.py:86-98).
     const int per_head = s.capacity / tmb::kKvBlock;
-    std::vector<int> table(size_t(batch) * s.max_blocks);
-    for (int b = 0; b < batch; ++b)
+    std::vector<int> table(size_t(seqs) * s.max_blocks);
+    for (int b = 0; b < seqs; ++b)
       for (int j = 0; j < s.max_blocks; ++j) table[size_t(b) * s.max_blocks + j] = b * s.kv_heads * per_head + j;
     void* dev = nullptr;
     cudaError_t err = Alloc(*plan, &dev, table.size() * sizeof(int));
@@ -391,7 +396,7 @@ void* tm_plan_create(int batch, void* const* external, int device) {
     p.ctx_base = nullptr;
     p.kv_block_stride = (long long)(tmb::kKvBlock * D);
     p.kv_head_stride = (long long)(uint64_t(s.capacity) * D);
-    p.kv_max_entry = ((batch - 1) * s.kv_heads + 1) * per_head - 1;
+    p.kv_max_entry = ((seqs - 1) * s.kv_heads + 1) * per_head - 1;
   }
   p.embed = plan->buffer_ptr[s.embed];
   p.final_norm = plan->buffer_ptr[s.final_norm];
@@ -434,13 +439,13 @@ void* tm_plan_create(int batch, void* const* external, int device) {
   };
   void *down_partial = nullptr, *attn_part = nullptr, *argmax_val = nullptr, *argmax_idx = nullptr, *status = nullptr,
        *step_ns = nullptr, *past = nullptr;
-  const size_t attn_tasks = 2 * size_t(p.grid) + size_t(batch) * s.kv_heads + 2;
+  const size_t attn_tasks = 2 * size_t(p.grid) + size_t(rows) * s.kv_heads + 2;
   p.attn_part_tasks = int(attn_tasks);
   const Scratch scratch[] = {
-      {&down_partial, size_t(batch) * s.hidden * sizeof(float)},
+      {&down_partial, size_t(rows) * s.hidden * sizeof(float)},
       {&attn_part, attn_tasks * gq * (s.head_dim + 2) * sizeof(float)},
-      {&argmax_val, size_t(p.grid) * batch * sizeof(float)},
-      {&argmax_idx, size_t(p.grid) * batch * sizeof(int)},
+      {&argmax_val, size_t(p.grid) * rows * sizeof(float)},
+      {&argmax_idx, size_t(p.grid) * rows * sizeof(int)},
       {&status, tmb::kStWords * sizeof(unsigned long long)},
       {&step_ns, size_t(s.capacity + 2) * sizeof(unsigned long long)},
       {&past, size_t(s.capacity) * sizeof(int)},
@@ -450,9 +455,9 @@ void* tm_plan_create(int batch, void* const* external, int device) {
     if (err != cudaSuccess) return fail("scratch", err);
   }
   // barrier word, then the attention arrival counters: one block, rezeroed per launch
-  const size_t attn_cnt = size_t(batch) * s.kv_heads;
+  const size_t attn_cnt = size_t(rows) * s.kv_heads;
   // ... and the task claim counters of every stage instance of the longest possible launch
-  const size_t stage_cnt = size_t(s.capacity) * (size_t(s.stages_per_layer(batch)) * size_t(s.layers) + 1) + 2;   // + the two look-ahead claims past the last stage
+  const size_t stage_cnt = size_t(s.capacity) * (size_t(s.stages_per_layer(rows)) * size_t(s.layers) + 1) + 2;   // + the two look-ahead claims past the last stage
   const size_t ready_offset = (128 + attn_cnt * sizeof(unsigned) + 7) & ~size_t(7);
   plan->claim_offset = ready_offset + size_t(s.kv_heads) * sizeof(unsigned long long);
   plan->sync_bytes = plan->claim_offset + stage_cnt * sizeof(unsigned);
@@ -467,7 +472,7 @@ void* tm_plan_create(int batch, void* const* external, int device) {
   p.qkv_ready = reinterpret_cast<unsigned long long*>(plan->sync_block + ready_offset);
   p.stage_cnt = reinterpret_cast<unsigned*>(plan->sync_block + plan->claim_offset);
   if (s.dense_batch) {
-    if (const char* why = BindDense(*plan, s, batch)) {
+    if (const char* why = BindDense(*plan, s, rows)) {
       Fail(-1, std::string("tm_plan_create: ") + why);
       return nullptr;
     }
@@ -480,6 +485,34 @@ void* tm_plan_create(int batch, void* const* external, int device) {
   p.step_ns = static_cast<unsigned long long*>(step_ns);
   plan->past_dev = static_cast<int*>(past);
   p.past = plan->past_dev;
+  p.row_seq = p.row_pos = nullptr;
+  if (s.prefill) {
+    // The plan's one step covers seqs * seq (sequence, position) pairs: kernel step c takes pairs [c * rows,
+    // (c + 1) * rows), sequences in order and positions ascending, so that a position's predecessors lie in the
+    // same or an earlier kernel step; the last step's spare rows repeat the last pair (they recompute and
+    // rewrite exactly what that pair writes). `past` of kernel step c is c * rows, the offset of its pairs.
+    const int total = seqs * s.prefill_seq;
+    const int chunks = (total + rows - 1) / rows;
+    if (chunks > s.capacity) return fail("prefill plan", cudaErrorInvalidValue);
+    std::vector<int> map, first;
+    map.resize(size_t(2) * chunks * rows);
+    first.resize(size_t(chunks));
+    for (int r = 0; r < chunks * rows; ++r) {
+      const int pair = std::min(r, total - 1);
+      map[size_t(r)] = pair / s.prefill_seq;
+      map[size_t(chunks) * rows + r] = pair % s.prefill_seq;
+    }
+    for (int ck = 0; ck < chunks; ++ck) first[size_t(ck)] = ck * rows;
+    void* dev = nullptr;
+    cudaError_t err = Alloc(*plan, &dev, map.size() * sizeof(int));
+    if (err == cudaSuccess) err = cudaMemcpy(dev, map.data(), map.size() * sizeof(int), cudaMemcpyHostToDevice);
+    if (err == cudaSuccess) err = cudaMemcpy(plan->past_dev, first.data(), first.size() * sizeof(int), cudaMemcpyHostToDevice);
+    if (err != cudaSuccess) return fail("prefill row map", err);
+    p.row_seq = static_cast<const int*>(dev);
+    p.row_pos = p.row_seq + size_t(chunks) * rows;
+    plan->prefill_chunks = uint32_t(chunks);
+    plan->prompt_len = s.prefill_seq;   // positions before the prompt's end keep the caller's tokens
+  }
   {
     const int status = tmb_prepare_decode(&p);
     if (status != 0) return fail("the persistent grid does not fit the device", cudaError_t(status));
@@ -492,6 +525,12 @@ int tm_plan_set_steps(void* handle, const int32_t* past, uint32_t count) {
   Plan* plan = AsPlan(handle);
   if (!plan || !past || count == 0) return Fail(-1, "tm_plan_set_steps: bad argument");
   const tmb::MegaParams& p = plan->params;
+  if (plan->prefill_chunks) {
+    // a prefill plan has ONE step, at past 0 (python/tilemega/serving/engine.py:89-90 sets exactly that)
+    if (count != 1 || past[0] != 0) return Fail(-2, "tm_plan_set_steps: a prefill plan has one step, at past 0");
+    plan->step_count = 1;
+    return 0;
+  }
   if (count > uint32_t(p.capacity)) return Fail(-2, "tm_plan_set_steps: more steps than the plan's capacity");
   for (uint32_t i = 0; i < count; ++i)
     if (past[i] < 0 || past[i] >= p.capacity) return Fail(-2, "tm_plan_set_steps: position outside [0, capacity)");
@@ -506,6 +545,7 @@ int tm_plan_set_prompt_len(void* handle, int prompt_len) {
   Plan* plan = AsPlan(handle);
   if (!plan || prompt_len < 0 || prompt_len > plan->params.capacity)
     return Fail(-1, "tm_plan_set_prompt_len: bad argument");
+  if (plan->prefill_chunks) return Fail(-1, "tm_plan_set_prompt_len: a prefill plan's prompt length is its seq");
   plan->prompt_len = prompt_len;
   return 0;
 }
@@ -526,19 +566,21 @@ int PrepareLaunch(Plan* plan, const char* who, uint32_t first_step, uint32_t ste
     return Fail(-4, name + ": a bounded device wait gave up on this plan; read tm_plan_watchdog, then tm_plan_clear_watchdog");
   if (uint64_t(first_step) + steps > plan->step_count)
     return Fail(-2, name + ": steps outside the interval given to tm_plan_set_steps");
+  // a prefill plan's one step is prefill_chunks kernel steps
+  const uint32_t kernel_steps = plan->prefill_chunks ? plan->prefill_chunks : steps;
   if (base_iteration != plan->next_iteration[mode])
     return Fail(-2, name + ": iteration is not the number of previous launches of this mode");
   if (plan->params.tp_world > 1 && !plan->tp_bound)
     return Fail(-1, name + ": a tensor-parallel plan must be bound with tm_plan_bind_tp first");
   // only the claim counters this launch can touch are rezeroed
   const size_t used = plan->claim_offset +
-                      (size_t(steps) * (size_t(plan->params.stages_per_layer) * size_t(plan->params.layers) + 1) + 2) * sizeof(unsigned);
+                      (size_t(kernel_steps) * (size_t(plan->params.stages_per_layer) * size_t(plan->params.layers) + 1) + 2) * sizeof(unsigned);
   cudaError_t err = cudaMemsetAsync(plan->sync_block, 0, used, s);
   if (err != cudaSuccess) return Fail(int(err), name + ": " + cudaGetErrorString(err));
   *out = plan->params;
   out->tp_steps = plan->tp_steps;
   out->first_step = int(first_step);
-  out->nsteps = int(steps);
+  out->nsteps = int(kernel_steps);
   out->prompt_len = plan->prompt_len;
   out->trace = plan->trace_step >= 0 ? plan->trace_dev : nullptr;
   out->trace_step = plan->trace_step;

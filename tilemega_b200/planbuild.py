@@ -32,14 +32,20 @@ def plan_document(config: dict, *, batch_lo: int = 1, batch_hi: int | None = Non
                   grid: int = 0, slots: int = 0, write_logits: bool = True,
                   tp: int = 1,
                   attn_min_slots: int | None = None,
-                  weights: str = "bf16", chunk_rows: bool = False) -> dict:
+                  weights: str = "bf16", chunk_rows: bool = False, phase: str = "decode", seq: int = 0) -> dict:
     """The sidecar for one decode plan; raises ValueError on shapes the kernels do not cover."""
     model = {key: config[key] for key in MODEL_KEYS if key in config}
     model.setdefault("head_dim", config["hidden_size"] // config["num_attention_heads"])
     model.setdefault("rms_norm_eps", 1e-5)
     batch_hi = batch_lo if batch_hi is None else batch_hi
-    dense_batch = batch_hi > 8   # batch 16..64: the GEMM stages run on tcgen05 tiles, weight pages are 128 x 128
-    if dense_batch and (batch_lo <= 8 or batch_hi > 64 or batch_lo % 16 or batch_hi % 16 or batch_lo > batch_hi):
+    if phase not in ("decode", "prefill"):
+        raise ValueError("phase must be 'decode' or 'prefill'")
+    prefill = phase == "prefill"
+    if prefill and (not 1 <= batch_lo <= batch_hi <= 64 or not 1 <= seq < capacity):
+        raise ValueError("a prefill plan covers 1..64 sequences of seq positions, 1 <= seq < capacity")
+    # batch 16..64 (and every prefill plan): the GEMM stages run on tcgen05 tiles, weight pages are 128 x 128
+    dense_batch = batch_hi > 8 or prefill
+    if dense_batch and not prefill and (batch_lo <= 8 or batch_hi > 64 or batch_lo % 16 or batch_hi % 16 or batch_lo > batch_hi):
         raise ValueError("a dense-batch plan covers batch sizes 16, 32, 48, 64 (interval bounds multiples of 16)")
     if not dense_batch and not 1 <= batch_lo <= batch_hi:
         raise ValueError("batch interval must lie in [1, 8], or in [16, 64] in steps of 16")
@@ -57,7 +63,7 @@ def plan_document(config: dict, *, batch_lo: int = 1, batch_hi: int | None = Non
         if config[key] % tp:
             raise ValueError(f"{key}={config[key]} is not divisible by the tp degree {tp}")
     document = {
-        "execution": "megakernel", "pg": "ring", "arch": "sm_100a", "phase": "decode",
+        "execution": "megakernel", "pg": "ring", "arch": "sm_100a", "phase": phase,
         "model": model, "batch_lo": batch_lo, "batch_hi": batch_hi, "capacity": capacity,
         "kv": {"layout": kv_layout, "block": 16, "num_blocks": num_blocks},
         "geometry": geometry or {}, "grid": grid, "slots": slots, "write_logits": write_logits,
@@ -68,6 +74,9 @@ def plan_document(config: dict, *, batch_lo: int = 1, batch_hi: int | None = Non
         raise ValueError("weights must be 'bf16' or 'e4m3'")
     if weights == "e4m3":
         document["weights"] = "e4m3"   # GEMV matrices as e4m3 bytes + one fp32 scale per output row
+    if prefill:
+        # the plan's ONE step runs the prompts of batch sequences, seq positions each, as (sequence, position) rows
+        document["seq"] = seq
     if chunk_rows:
         if not dense_batch or kv_layout != "paged":
             raise ValueError("chunk_rows (rows of one sequence at consecutive positions) needs a paged dense-batch plan")

@@ -52,7 +52,8 @@ class ServingEngine:
                  decode_so: str | Path, batch: int, prompt_len: int = 64, max_new_tokens: int = 1024,
                  mode: str = "auto", device: int = 0, decode_loop: bool = True,
                  decode_chunk: int | None = None, step_events: bool = True,
-                 block_table: torch.Tensor | None = None, weights: dict[str, torch.Tensor] | None = None):
+                 block_table: torch.Tensor | None = None, weights: dict[str, torch.Tensor] | None = None,
+                 prefill_so: str | Path | None = None):
         if min(prompt_len, max_new_tokens) < 1:
             raise ValueError("prompt length and output length must be positive")
         if mode not in MODES:
@@ -75,8 +76,27 @@ class ServingEngine:
         bound = {name: tensor.data_ptr() for name, tensor in self.weights.items()} | self.state.pointers
         self.decode = self.decode_lib.create(batch, bound, device)
         self.loop_modes = self.decode.loop_modes()
-        self.decode.set_prompt_len(prompt_len)
-        self.decode.set_steps(list(range(prompt_len + max_new_tokens - 1)))
+        # With a prefill plan (phase 0, seq == prompt_len, same capacity and KV layout: the reference's
+        # engine.py:41-57,89-92) the prompt runs as ONE step of that plan over the shared state; the decode plan
+        # then starts behind the prompt. Without one the decode plan runs the prompt teacher-forced.
+        self.prefill = self.prefill_lib = None
+        if prefill_so is not None:
+            self.prefill_lib = PlanLibrary(prefill_so)
+            shape = self.prefill_lib.info
+            if shape.phase != 0 or shape.seq != prompt_len or shape.capacity != described.capacity:
+                raise ValueError("the prefill plan does not cover this prompt length and capacity")
+            self.prefill_weights = load_weights(checkpoint, self.prefill_lib, device=where)
+            both = bound | {name: tensor.data_ptr() for name, tensor in self.prefill_weights.items()}
+            try:
+                self.prefill = self.prefill_lib.create(batch, both, device)
+            except BaseException:
+                self.decode.close()
+                raise
+            self.prefill.set_steps([0])
+            self.decode.set_steps(list(range(prompt_len, prompt_len + max_new_tokens - 1)) or [prompt_len])
+        else:
+            self.decode.set_prompt_len(prompt_len)
+            self.decode.set_steps(list(range(prompt_len + max_new_tokens - 1)))
 
     def generate(self, prompt_ids: torch.Tensor, new_tokens: int | None = None) -> Generation:
         wanted = self.max_new_tokens if new_tokens is None else new_tokens
@@ -85,7 +105,9 @@ class ServingEngine:
         if tuple(prompt_ids.shape) != (self.batch, self.prompt_len):
             raise ValueError("prompt tensor shape disagrees with plan")
         looped = self.decode_loop and wanted > 1 and bool(self.loop_modes & self.decode_mode)
-        spans = [(0, self.prompt_len)] + decode_spans(self.prompt_len, wanted - 1, self.decode_chunk, looped)
+        # plan steps of the decode plan: with a prefill plan its step s decodes position prompt_len + s
+        first_decode = 0 if self.prefill is not None else self.prompt_len
+        spans = [(0, self.prompt_len)] + decode_spans(first_decode, wanted - 1, self.decode_chunk, looped)
         host_prompt = prompt_ids.to(device="cpu", dtype=torch.int32).contiguous()
         host_prompt = host_prompt if host_prompt.is_pinned() else host_prompt.pin_memory()
         host_tokens = torch.empty((self.batch, wanted), dtype=torch.int32, pin_memory=True)
@@ -96,7 +118,9 @@ class ServingEngine:
         for number, (first, count) in enumerate(spans):
             if number == 0:
                 marks[0].record(stream)
-            if count == 1 and not looped and number > 0:
+            if number == 0 and self.prefill is not None:
+                self.prefill.launch(0, self.decode_mode, stream.cuda_stream)
+            elif count == 1 and not looped and number > 0:
                 self.decode.launch(first, self.decode_mode, stream.cuda_stream)
             else:
                 self.decode.launch_steps(first, count, self.decode_mode, stream.cuda_stream)
@@ -105,17 +129,19 @@ class ServingEngine:
         host_tokens.copy_(self.state.tokens[:, self.prompt_len:self.prompt_len + wanted], non_blocking=True)
         stream.synchronize()
         e2e_ms = (time.perf_counter() - began) * 1e3
-        gave_up = self.decode.watchdog()
+        gave_up = self.decode.watchdog() or (self.prefill.watchdog() if self.prefill is not None else None)
         if gave_up is not None:
             raise RuntimeError(f"a bounded device wait gave up: {gave_up}")
         step_ms = [marks[0].elapsed_time(marks[1])]
         stamped = self.step_events and wanted > 1
         if stamped:
-            stamps = self.decode.read_step_ns(self.prompt_len, wanted)
+            stamps = self.decode.read_step_ns(first_decode, wanted)
             step_ms += [(later - earlier) / 1e6 for earlier, later in zip(stamps, stamps[1:])]
         return Generation(host_tokens, step_ms[0], step_ms, e2e_ms, looped, stamped)
 
     def close(self) -> None:
+        if self.prefill is not None:
+            self.prefill.close()
         self.decode.close()
 
     def __enter__(self) -> "ServingEngine":
