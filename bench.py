@@ -268,15 +268,18 @@ def run_reference(args) -> None:
 
 
 def run_prefill(args) -> None:
-    """Secondary workload: chunked prefill of one prompt of `--prefill` tokens through the dense-batch plan
-    with chunk_rows (64 positions per step, weights streamed once per chunk). One JSON line in the same
-    shape as the decode line; a step is one chunk."""
+    """Secondary workload: one prompt of `--prefill` tokens through a prefill plan (phase 0 of the plan ABI):
+    ONE launch whose kernel steps take 64 (sequence, position) rows each, weights streamed once per kernel
+    step, GEMM stages on tcgen05 tiles. One JSON line in the shape of the decode line; a step is one such
+    kernel step (64 prompt positions)."""
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the product path has no CPU implementation")
     import time
 
     from tilemega_b200.planbuild import PLAN_DIR, emit_plan, remove_plans
-    from tilemega_b200.serving.prefill import ChunkedPrefill
+    from tilemega_b200.serving.plan import L2, PlanLibrary
+    from tilemega_b200.serving.state import allocate_state, shuffled_block_table
+    from tilemega_b200.serving.weights import load_weights
     config = dict(MODELS[args.model or "llama-3.1-8b"])
     if args.layers:
         config["num_hidden_layers"] = args.layers
@@ -286,44 +289,64 @@ def run_prefill(args) -> None:
     capacity = (length + 32) // 16 * 16
     num_blocks = capacity // 16 + 2
     plan_dir = PLAN_DIR / "bench"
-    so = emit_plan(config, plan_dir, batch_lo=rows, batch_hi=rows, capacity=capacity, kv_layout="paged",
-                   num_blocks=num_blocks, write_logits=False, chunk_rows=True)
-    layers, hkv, dim = config["num_hidden_layers"], config["num_key_value_heads"], synthetic.head_dim_of(config)
-    pool = torch.zeros((layers, 2, num_blocks, hkv, 16, dim), dtype=torch.bfloat16, device=device)
-    prompt = synthetic.seeded_tokens(1, length, config["vocab_size"], seed=3)[0].tolist()
-    blocks = (torch.randperm(num_blocks - 1, generator=torch.Generator().manual_seed(7)) + 1)[:-(-(length + 1) // 16)].tolist()
-    prefill = ChunkedPrefill(synthetic.LazySeededCheckpoint(config, seed=0, device=device), config, so, rows, pool, 0)
-    prefill.run([prompt[:2 * rows]], [blocks])                  # warm-up: two chunks
+    layout = dict(capacity=capacity, kv_layout="paged", num_blocks=num_blocks, write_logits=False)
+    prefill_lib = PlanLibrary(emit_plan(config, plan_dir, batch_lo=1, batch_hi=1, phase="prefill", seq=length, **layout))
+    decode_lib = PlanLibrary(emit_plan(config, plan_dir, batch_lo=1, batch_hi=1, **layout))   # the state's description
+    weights = load_weights(synthetic.LazySeededCheckpoint(config, seed=0, device=device), prefill_lib, device=device)
+    table = shuffled_block_table(1, capacity // 16, num_blocks, seed=7)
+    state = allocate_state(config, 1, decode_lib, device, block_table=table)
+    pointers = {name: tensor.data_ptr() for name, tensor in weights.items()} | state.pointers
+    plan = prefill_lib.create(1, pointers, 0)
+    plan.set_steps([0])
+    prompt = synthetic.seeded_tokens(1, length, config["vocab_size"], seed=3).to(torch.int32)
+    host_prompt = prompt.pin_memory()
+    host_token = torch.zeros(1, dtype=torch.int32).pin_memory()
+    stream = torch.cuda.current_stream()
+    chunks = -(-length // rows)
+
+    def once() -> tuple[float, float]:
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        wall = time.perf_counter()
+        state.tokens[:, :length].copy_(host_prompt, non_blocking=True)
+        begin.record(stream)
+        plan.launch(0, L2, stream.cuda_stream)
+        end.record(stream)
+        host_token.copy_(state.tokens[:, length], non_blocking=True)
+        stream.synchronize()
+        wall = time.perf_counter() - wall
+        if plan.watchdog() is not None:
+            raise SystemExit(f"a bounded device wait gave up: {plan.watchdog()}")
+        return begin.elapsed_time(end) / 1e3, wall
+
+    for _ in range(max(args.warmup, 3) if length <= 1024 else 1):
+        once()
     peak, peak_kind = measured_peak_gbs()
     with ClockSampler(0) as clocks:
-        prefill.device_ms, prefill.chunks_run = 0.0, 0
-        torch.cuda.synchronize()
-        begin = time.perf_counter()
-        result = prefill.run([prompt], [blocks])[0]
-        torch.cuda.synchronize()
-        wall = time.perf_counter() - begin
-    chunks, device_s = prefill.chunks_run, prefill.device_ms / 1e3
-    # algorithmic bytes: every chunk streams the GEMM weights once; row i of a chunk reads the p0 + i cached positions
+        runs = [once() for _ in range(3)]
+    device_s, wall = sorted(runs)[1]
+    # algorithmic bytes: every kernel step streams the GEMM weights once; row i reads its p + 1 cached positions
+    layers, hkv, dim = config["num_hidden_layers"], config["num_key_value_heads"], synthetic.head_dim_of(config)
     hidden, inter, heads, vocab = config["hidden_size"], config["intermediate_size"], config["num_attention_heads"], config["vocab_size"]
     weight_bytes = 2 * (layers * (hidden * (heads + 2 * hkv) * dim + heads * dim * hidden + 3 * hidden * inter) + vocab * hidden)
     kv_bytes = sum(position + 1 for position in range(length)) * layers * 2 * hkv * dim * 2
     total_bytes = chunks * weight_bytes + kv_bytes
-    flops = 2.0 * length * weight_bytes / 2
+    flops = float(length) * weight_bytes          # 2 flops per weight element (2 bytes) and row
     line = {
-        "metric": "prefill_tokens_per_s", "value": length / device_s, "unit": UNIT, "n_gpus": 1, "steps": chunks, "warmup": 2,
-        "ms_per_step": prefill.device_ms / chunks, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"{args.model or 'llama-3.1-8b'}-shaped chunked prefill, one prompt of {length} tokens, "
-                               f"{rows} positions per step, paged KV block 16, scattered blocks", "layers": layers,
-                   "l2": "inputs (15 GB of weights per chunk) exceed L2", "first_token": result.first_token},
+        "metric": "prefill_tokens_per_s", "value": length / device_s, "unit": UNIT, "n_gpus": 1, "steps": chunks,
+        "warmup": 1 if length > 1024 else max(args.warmup, 3), "ms_per_step": device_s * 1e3 / chunks, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"{args.model or 'llama-3.1-8b'}-shaped prefill plan, one prompt of {length} tokens, "
+                               f"{rows} positions per kernel step, paged KV block 16, shuffled block table", "layers": layers,
+                   "l2": "inputs (15 GB of weights per kernel step) exceed L2", "first_token": int(host_token[0]),
+                   "time_to_first_token_ms": wall * 1e3},
         "roofline": {"bound": "hbm", "achieved": total_bytes / device_s / 1e9, "peak": peak, "unit": "GB/s",
                      "frac": total_bytes / device_s / 1e9 / peak, "traffic": None, "peak_kind": "of " + peak_kind,
-                     "bytes_per_launch": total_bytes / chunks, "tensor_tflops": flops / device_s / 1e12},
-        "e2e": {"value": length / wall, "unit": UNIT, "h2d_bytes_per_step": rows * (capacity // 16 + 2) * 4,
-                "d2h_bytes_per_step": 4},
-        "gpu_launches": chunks, "clocks": clocks.summary(),
+                     "bytes_per_launch": total_bytes, "tensor_tflops": flops / device_s / 1e12},
+        "e2e": {"value": length / wall, "unit": UNIT, "h2d_bytes_per_step": length * 4 / chunks, "d2h_bytes_per_step": 4 / chunks},
+        "gpu_launches": 1, "clocks": clocks.summary(),
     }
-    prefill.close()
+    plan.close()
     remove_plans(plan_dir)
     print(json.dumps(line), flush=True)
 

@@ -261,7 +261,7 @@ __device__ __forceinline__ int seq_of(const MegaParams& p, int past, int b) {
 __device__ __forceinline__ int seq_pos(const MegaParams& p, int past, int b) {
   int pos;
   if (p.row_pos) {
-    pos = __ldg(p.row_pos + past + b) + (p.ctx_base ? __ldg(p.ctx_base + __ldg(p.row_seq + past + b)) : 0);
+    pos = __ldg(p.row_pos + past + b);   // resolved by the host at launch: position in the prompt + context_base
   } else {
     pos = past + (p.ctx_base ? __ldg(p.ctx_base + b) : 0);
   }

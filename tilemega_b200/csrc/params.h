@@ -167,8 +167,9 @@ struct MegaParams {
   // dense-batch plans (dense != 0): GEMM stages on tcgen05 tiles
   int dense;
   int chunk_rows;              // rows may be consecutive positions of one sequence: append stage + barrier before attention
-  // prefill plans: row r of step s is position row_pos[s * batch + r] (plus the sequence's context_base) of sequence
-  // row_seq[s * batch + r]; the plan's `past` entry of step s is s * batch (null: row b is sequence b at position past)
+  // prefill plans: row r of step s is cache position row_pos[s * batch + r] (its position in the prompt plus the
+  // sequence's context_base, resolved at launch) of sequence row_seq[s * batch + r]; the plan's `past` entry of
+  // step s is s * batch (null: row b is sequence b at position past + context_base[b])
   const int* row_seq;
   const int* row_pos;
   DenseGeo dgeo[kNumGemv];     // indexed by StageKind (kRouter unused)

@@ -116,7 +116,18 @@ struct Plan {
   size_t sync_bytes = 0;
   size_t claim_offset = 0;
   uint32_t prefill_chunks = 0;          // prefill plan: kernel steps (64 rows each) behind its one plan step
+  const int* row_seq_dev = nullptr;     // ... its (sequence, position in the prompt) pairs, one per kernel row,
+  const int* row_rel_dev = nullptr;
+  int* row_abs_dev = nullptr;           // ... and the pairs' positions in the cache, resolved at every launch
 };
+
+// Position in the cache of every row of a prefill plan: its position in the prompt plus its sequence's
+// context_base (an external buffer the caller may change between launches), so that the kernel reads one word
+// per row where it would chase two.
+__global__ void ResolveRowPositions(const int* rel, const int* seq, const int* base, int* out, int count) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r < count) out[r] = rel[r] + (base ? base[seq[r]] : 0);
+}
 
 Plan* AsPlan(void* handle) {
   Plan* plan = static_cast<Plan*>(handle);
@@ -504,12 +515,17 @@ void* tm_plan_create(int batch, void* const* external, int device) {
     }
     for (int ck = 0; ck < chunks; ++ck) first[size_t(ck)] = ck * rows;
     void* dev = nullptr;
+    void* resolved = nullptr;
     cudaError_t err = Alloc(*plan, &dev, map.size() * sizeof(int));
+    if (err == cudaSuccess) err = Alloc(*plan, &resolved, size_t(chunks) * rows * sizeof(int));
     if (err == cudaSuccess) err = cudaMemcpy(dev, map.data(), map.size() * sizeof(int), cudaMemcpyHostToDevice);
     if (err == cudaSuccess) err = cudaMemcpy(plan->past_dev, first.data(), first.size() * sizeof(int), cudaMemcpyHostToDevice);
     if (err != cudaSuccess) return fail("prefill row map", err);
-    p.row_seq = static_cast<const int*>(dev);
-    p.row_pos = p.row_seq + size_t(chunks) * rows;
+    plan->row_seq_dev = static_cast<const int*>(dev);
+    plan->row_rel_dev = plan->row_seq_dev + size_t(chunks) * rows;
+    plan->row_abs_dev = static_cast<int*>(resolved);
+    p.row_seq = plan->row_seq_dev;
+    p.row_pos = plan->row_abs_dev;      // filled by ResolveRowPositions at every launch
     plan->prefill_chunks = uint32_t(chunks);
     plan->prompt_len = s.prefill_seq;   // positions before the prompt's end keep the caller's tokens
   }
@@ -577,6 +593,13 @@ int PrepareLaunch(Plan* plan, const char* who, uint32_t first_step, uint32_t ste
                       (size_t(kernel_steps) * (size_t(plan->params.stages_per_layer) * size_t(plan->params.layers) + 1) + 2) * sizeof(unsigned);
   cudaError_t err = cudaMemsetAsync(plan->sync_block, 0, used, s);
   if (err != cudaSuccess) return Fail(int(err), name + ": " + cudaGetErrorString(err));
+  if (plan->prefill_chunks) {
+    const int count = int(plan->prefill_chunks) * plan->params.batch;
+    ResolveRowPositions<<<(count + 255) / 256, 256, 0, s>>>(plan->row_rel_dev, plan->row_seq_dev, plan->params.ctx_base,
+                                                            plan->row_abs_dev, count);
+    err = cudaGetLastError();
+    if (err != cudaSuccess) return Fail(int(err), name + ": " + cudaGetErrorString(err));
+  }
   *out = plan->params;
   out->tp_steps = plan->tp_steps;
   out->first_step = int(first_step);
