@@ -36,7 +36,13 @@ enum { TM_DTYPE_BF16 = 0, TM_DTYPE_F32 = 1, TM_DTYPE_I32 = 2,
         * fp32 buffer "<name>.scale" of one scale per output row */
        TM_DTYPE_E4M3 = 4 };
 
-/* ServingAbi.h:17-23 */
+/* ServingAbi.h:17-23. Two phases are built. TM_SERVING_DECODE: seq = 1, one sequence position per plan step
+ * (past_lo..past_hi = 0..capacity-1). TM_SERVING_PREFILL: seq = the prompt length the plan was emitted for,
+ * ONE plan step (past 0) that runs positions 0..seq-1 of all `batch` sequences over the same request buffers
+ * a decode plan of the same model, capacity and KV layout names (tokens, RoPE tables, KV caches or pools,
+ * block table) and writes the token sampled after the prompt to serving.tokens[b][seq]; its GEMM weight
+ * buffers are named "prefill.<decode name>" (128 x 128 pages), so one driver-side table can hold both plans'
+ * buffers (python/tilemega/serving/engine.py:49-57). */
 typedef struct {
   uint32_t abi_version, phase;
   int32_t batch_lo, batch_hi, seq, past_lo, past_hi, capacity;
