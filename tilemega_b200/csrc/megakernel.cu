@@ -268,14 +268,40 @@ __device__ __forceinline__ int seq_pos(const MegaParams& p, int past, int b) {
   return min(max(pos, 0), p.capacity - 1);
 }
 
+// The rows' positions and sequences, fetched ONCE per stage by every warp that partitions the stage: lane l
+// holds rows l and l + 32 (a batch has at most 64 rows) and hands them out by shuffle. The partition below
+// walks over the rows one after another; with a global load per row and step (which misses the small L1 left
+// beside 227 KB of shared memory) that walk was tens of microseconds at batch 64, on the streaming warp
+// before its first copy and on the arithmetic warps before their first product. Every function that takes a
+// Rows must be called by all 32 lanes of a warp together.
+struct Rows {
+  int p0, p1, s0, s1;
+};
+
+__device__ __forceinline__ Rows load_rows(const MegaParams& p, int past) {
+  const int lane = threadIdx.x & 31;
+  Rows r;
+  r.p0 = lane < p.batch ? seq_pos(p, past, lane) : 0;
+  r.p1 = lane + 32 < p.batch ? seq_pos(p, past, lane + 32) : 0;
+  r.s0 = lane < p.batch ? seq_of(p, past, lane) : 0;
+  r.s1 = lane + 32 < p.batch ? seq_of(p, past, lane + 32) : 0;
+  return r;
+}
+__device__ __forceinline__ int row_pos(const Rows& r, int b) { return __shfl_sync(0xffffffffu, b < 32 ? r.p0 : r.p1, b & 31); }
+__device__ __forceinline__ int row_seq(const Rows& r, int b) { return __shfl_sync(0xffffffffu, b < 32 ? r.s0 : r.s1, b & 31); }
+__device__ __forceinline__ int warp_sum(int v) {
+#pragma unroll
+  for (int m = 16; m; m >>= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
+  return v;
+}
+
 // slots-per-task and task count for one attention stage
-__device__ __forceinline__ int attn_count(const MegaParams& p, int past, int nk, int spt) {
-  int ntasks = 0;
-  for (int b = 0; b < p.batch; ++b) {
-    const int ns = seq_pos(p, past, b) / nk + 1;
-    ntasks += p.kv_heads * ((ns + spt - 1) / spt);
-  }
-  return ntasks;
+__device__ __forceinline__ int attn_count(const MegaParams& p, const Rows& rw, int nk, int spt) {
+  const int lane = threadIdx.x & 31;
+  int mine = 0;
+  if (lane < p.batch) mine += (rw.p0 / nk + 1 + spt - 1) / spt;
+  if (lane + 32 < p.batch) mine += (rw.p1 / nk + 1 + spt - 1) / spt;
+  return p.kv_heads * warp_sum(mine);
 }
 
 // How one attention stage is cut into tasks. Two regimes:
@@ -288,10 +314,10 @@ struct AttnShape {
   int spt, ntasks, per, total;
 };
 
-__device__ __forceinline__ AttnShape attn_shape(const MegaParams& p, int past, int nk) {
+__device__ __forceinline__ AttnShape attn_shape(const MegaParams& p, const Rows& rw, int nk) {
+  const int lane = threadIdx.x & 31;
   AttnShape sh;
-  sh.total = 0;
-  for (int b = 0; b < p.batch; ++b) sh.total += (seq_pos(p, past, b) / nk + 1) * p.kv_heads;
+  sh.total = p.kv_heads * warp_sum((lane < p.batch ? rw.p0 / nk + 1 : 0) + (lane + 32 < p.batch ? rw.p1 / nk + 1 : 0));
   const int floor_spt = max(1, p.attn_min_spt);   // a task's fixed cost wants at least this many slots
   const int per_cta = (sh.total + p.grid - 1) / p.grid;
   if (per_cta >= 2 * floor_spt) {
@@ -302,27 +328,27 @@ __device__ __forceinline__ AttnShape attn_shape(const MegaParams& p, int past, i
   }
   sh.per = 0;
   sh.spt = max(floor_spt, per_cta);
-  sh.ntasks = attn_count(p, past, nk, sh.spt);
+  sh.ntasks = attn_count(p, rw, nk, sh.spt);
   // every task owns one record of partial results: never more tasks than records
   while (sh.ntasks > p.attn_part_tasks) {
     sh.spt += 1;
-    sh.ntasks = attn_count(p, past, nk, sh.spt);
+    sh.ntasks = attn_count(p, rw, nk, sh.spt);
   }
   return sh;
 }
 
-__device__ __forceinline__ AttnTask attn_task(const MegaParams& p, int past, int nk, int spt, int t) {
+__device__ __forceinline__ AttnTask attn_task(const MegaParams& p, const Rows& rw, int nk, int spt, int t) {
   AttnTask a;
   int base = 0;
   for (int b = 0;; ++b) {
-    const int pos = seq_pos(p, past, b);
+    const int pos = row_pos(rw, b);
     const int ns = pos / nk + 1;
     const int nch = (ns + spt - 1) / spt;
     const int n = p.kv_heads * nch;
     if (t < base + n || b == p.batch - 1) {
       const int r = t - base;
       a.b = b;
-      a.sq = seq_of(p, past, b);
+      a.sq = row_seq(rw, b);
       a.g = r / nch;
       a.c = r % nch;
       a.pos = pos;
@@ -345,7 +371,7 @@ struct AttnWalk {
   bool done;
 };
 
-__device__ __forceinline__ AttnWalk attn_walk(const MegaParams& p, int past, int nk, const AttnShape& sh, int t) {
+__device__ __forceinline__ AttnWalk attn_walk(const MegaParams& p, const Rows& rw, int nk, const AttnShape& sh, int t) {
   AttnWalk w;
   w.t = t;
   w.done = false;
@@ -353,7 +379,7 @@ __device__ __forceinline__ AttnWalk attn_walk(const MegaParams& p, int past, int
   w.x1 = min(sh.total, w.x + sh.per);
   w.b = 0;
   w.base = 0;
-  w.ns = seq_pos(p, past, 0) / nk + 1;
+  w.ns = row_pos(rw, 0) / nk + 1;
   return w;
 }
 
@@ -362,19 +388,19 @@ __device__ __forceinline__ AttnWalk attn_walk(const MegaParams& p, int past, int
 // and its partial records are consecutive from (first such range) + (unit index): along the
 // flattened axis every new segment advances the range, the unit or both, so no two segments
 // share a record and there are at most ntasks + B * Hkv of them.
-__device__ __forceinline__ bool attn_next(const MegaParams& p, int past, int nk, const AttnShape& sh, AttnWalk& w,
+__device__ __forceinline__ bool attn_next(const MegaParams& p, const Rows& rw, int nk, const AttnShape& sh, AttnWalk& w,
                                           AttnTask& a) {
   if (sh.per == 0) {
     if (w.done) return false;
     w.done = true;
-    a = attn_task(p, past, nk, sh.spt, w.t);
+    a = attn_task(p, rw, nk, sh.spt, w.t);
     return true;
   }
   if (w.x >= w.x1) return false;
   while (w.x >= w.base + w.ns * p.kv_heads && w.b < p.batch - 1) {
     w.base += w.ns * p.kv_heads;
     ++w.b;
-    w.ns = seq_pos(p, past, w.b) / nk + 1;
+    w.ns = row_pos(rw, w.b) / nk + 1;
   }
   const int rel = w.x - w.base;
   const int g = min(rel / w.ns, p.kv_heads - 1);
@@ -383,9 +409,9 @@ __device__ __forceinline__ bool attn_next(const MegaParams& p, int past, int nk,
   const int u0 = w.base + g * w.ns;
   const int first = u0 / sh.per, last = (u0 + w.ns - 1) / sh.per;
   a.b = w.b;
-  a.sq = seq_of(p, past, w.b);
+  a.sq = row_seq(rw, w.b);
   a.g = g;
-  a.pos = seq_pos(p, past, w.b);
+  a.pos = row_pos(rw, w.b);
   a.ns = w.ns;
   a.nch = last - first + 1;
   a.c = w.x / sh.per - first;
@@ -632,7 +658,8 @@ __device__ __forceinline__ void stream_attn(Ctx& c, const LayerPtrs& lp, int pas
   const int piece = c.lane % NB;                 // block of the slot this lane copies
   const bool is_v = c.lane >= NB;
   const unsigned char* pool = static_cast<const unsigned char*>(is_v ? lp.v_pool : lp.k_pool);
-  const AttnShape sh = attn_shape(c.p, past, NK);
+  const Rows rw = load_rows(c.p, past);
+  const AttnShape sh = attn_shape(c.p, rw, NK);
   int t = __shfl_sync(kAll, c.pending, 0);
   bool dead = __shfl_sync(kAll, c.dead ? 1 : 0, 0) != 0;
   while (t < sh.ntasks && !dead) {
@@ -641,9 +668,9 @@ __device__ __forceinline__ void stream_attn(Ctx& c, const LayerPtrs& lp, int pas
       upcoming = claim(c, c.inst);
       fifo_push(c, t);
     }
-    AttnWalk walk = attn_walk(c.p, past, NK, sh, t);
+    AttnWalk walk = attn_walk(c.p, rw, NK, sh, t);
     AttnTask a;
-    while (!dead && attn_next(c.p, past, NK, sh, walk, a)) {
+    while (!dead && attn_next(c.p, rw, NK, sh, walk, a)) {
       const int nblk = a.pos / kKvBlock + 1;
       for (int s = a.slot0; s < a.slot1; ++s) {
         const int nb = min(NB, nblk - s * NB);
@@ -1531,7 +1558,8 @@ __device__ void attn_stage(Ctx& c, const LayerPtrs& lp, int past, bool tr, int s
   const __nv_bfloat16* cosb = static_cast<const __nv_bfloat16*>(p.rope_cos);
   const __nv_bfloat16* sinb = static_cast<const __nv_bfloat16*>(p.rope_sin);
 
-  const AttnShape sh = attn_shape(p, past, NK);
+  const Rows rw = load_rows(p, past);
+  const AttnShape sh = attn_shape(p, rw, NK);
 #if TMB_DENSE
   // Dense-batch plans leave a QKV reduction that ran in parts unsummed: the tasks here add the
   // parts' fp32 tiles (ascending, then one rounding to bf16 -- what a summing epilogue would have
@@ -1548,9 +1576,9 @@ __device__ void attn_stage(Ctx& c, const LayerPtrs& lp, int past, bool tr, int s
   const bool appended = p.chunk_rows != 0;
   trace_mark(c, tr, stage, 2);
   for (int t = fifo_pop_uniform(c); t >= 0; t = fifo_pop_uniform(c)) {
-    AttnWalk walk = attn_walk(p, past, NK, sh, min(t, sh.ntasks - 1));
+    AttnWalk walk = attn_walk(p, rw, NK, sh, min(t, sh.ntasks - 1));
     AttnTask a;
-    while (attn_next(p, past, NK, sh, walk, a)) {
+    while (attn_next(p, rw, NK, sh, walk, a)) {
     const bool tail = a.slot1 == a.ns;   // this chunk holds the new token
     // the (GQ + 2) * D QKV rows of KV head a.g must be stored: their row tiles are counted per group
     if (c.tid == 0 && !c.dead) {
