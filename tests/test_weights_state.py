@@ -118,3 +118,31 @@ def test_scaled_rope_tables_match_the_hf_rotary_module(case):
         assert (ours == theirs).float().mean().item() >= 0.98
     with pytest.raises(ValueError):
         rotary_tables(dict(config, rope_scaling={"rope_type": "yarn", "factor": 2.0}), 16, "cpu")
+
+
+def test_safetensors_directory_loads_like_an_in_memory_checkpoint(tmp_path, plan_dir):
+    """A model directory of sharded *.safetensors files (the reference's input, python/tilemega/serving/
+    weights.py:17-49): tensors are read one at a time as the recipes ask for them, tied embeddings resolve
+    through config.json, and the packed buffers are those of the same tensors held in memory."""
+    import json
+    from safetensors.torch import save_file
+    from tilemega_b200 import synthetic
+    from tilemega_b200.planbuild import emit_plan
+    from tilemega_b200.serving.plan import PlanLibrary
+    from tilemega_b200.serving.weights import Checkpoint, TensorCheckpoint, load_weights
+    config = dict(synthetic.TINY, num_hidden_layers=1, tie_word_embeddings=True)
+    tensors = {name: tensor.to(torch.bfloat16).contiguous() for name, tensor in synthetic.seeded_weights(config, 0).items()}
+    tensors.pop("lm_head.weight", None)                       # tied: the head is the embedding table
+    names = sorted(tensors)
+    save_file({name: tensors[name] for name in names[::2]}, tmp_path / "model-00001-of-00002.safetensors")
+    save_file({name: tensors[name] for name in names[1::2]}, tmp_path / "model-00002-of-00002.safetensors")
+    (tmp_path / "config.json").write_text(json.dumps(config))
+    lib = PlanLibrary(emit_plan(config, plan_dir, batch_lo=1, batch_hi=1, capacity=32))
+    from_files = load_weights(tmp_path, lib, device="cpu")
+    in_memory = load_weights(TensorCheckpoint(tensors, True), lib, device="cpu")
+    assert set(from_files) == set(in_memory) and "lm_head.weight" in from_files
+    for name in in_memory:
+        assert torch.equal(from_files[name], in_memory[name]), name
+    assert Checkpoint(tmp_path).tie_word_embeddings
+    with pytest.raises(KeyError):
+        Checkpoint(tmp_path).tensor("model.layers.7.mlp.up_proj.weight")
