@@ -672,10 +672,20 @@ __device__ __forceinline__ void stream_attn(Ctx& c, const LayerPtrs& lp, int pas
     AttnTask a;
     while (!dead && attn_next(c.p, rw, NK, sh, walk, a)) {
       const int nblk = a.pos / kKvBlock + 1;
+      // Block-table entries in windows of 32 consecutive blocks, one per lane (one coalesced load), the
+      // NEXT window fetched while this one is used: a slot's entries then come out of registers by
+      // shuffle. Fetched per slot, right before the copies that need them, every slot waited for an
+      // L2 round trip (the small L1 beside 227 KB of shared memory does not keep the table).
+      int win0 = a.slot0 * NB;
+      int win = table_entry(c.p, a.sq, win0 + c.lane), ahead = table_entry(c.p, a.sq, win0 + 32 + c.lane);
       for (int s = a.slot0; s < a.slot1; ++s) {
         const int nb = min(NB, nblk - s * NB);
-        // this lane's block-table entry first (its load is in flight during the wait below)
-        const long long e = table_entry(c.p, a.sq, s * NB + min(piece, max(nb - 1, 0)));
+        if (s * NB >= win0 + 32) {   // (32 is a multiple of NB: a slot never straddles two windows)
+          win0 += 32;
+          win = ahead;
+          ahead = table_entry(c.p, a.sq, win0 + 32 + c.lane);
+        }
+        const long long e = __shfl_sync(kAll, win, s * NB - win0 + min(piece, max(nb - 1, 0)));
         const long long off = (e * c.p.kv_block_stride + (long long)a.g * c.p.kv_head_stride) * 2;
         int word = -1;                           // the slot to fill, or -1: the wait gave up
         if (lead && stream_wait_empty(c, false)) {
