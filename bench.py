@@ -52,7 +52,7 @@ NOMINAL_HBM_GBS = 8000.0
 # of the same kernel on 2-layer cases of the same shapes (traffic is proportional to the streamed
 # weights, so a full launch's traffic is this ratio times its algorithmic bytes). Keyed by
 # (model, batch): a workload without a capture reports no traffic.
-NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = {("llama-3.1-8b", 1): 0.9906, ("llama-3.1-8b", 64): 1.0142}
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = {("llama-3.1-8b", 1): 0.9922, ("llama-3.1-8b", 64): 1.0143}
 # roofline.frac of the one-GPU headline run (profiles/decode_megakernel_llama31_8b_b1.md): the
 # denominator of config.mbu_retained_vs_1gpu in a tensor-parallel line
 SINGLE_GPU_FRAC = 0.791
