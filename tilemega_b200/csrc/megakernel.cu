@@ -220,10 +220,19 @@ __device__ __forceinline__ bool grid_wait(Ctx& c) {
     unsigned long long t0 = 0;
     uint32_t polls = 0;
     unsigned long long seen;
+    // "has a wait given up anywhere" is read while the arrivals are polled for, not after them: as a
+    // dependent load behind the barrier it cost every stage boundary one more L2 round trip (a flag set
+    // during this wait is seen by the next one)
+    unsigned long long fired = ld_relaxed(c.p.status + kStFired);
     while ((seen = ld_acquire(c.p.bar)) < c.bar_target) {
-      if ((++polls & 63u) == 0 && wait_give_up(c.p, t0, kSiteGrid, c.bar_target, seen)) break;
+      if ((++polls & 63u) == 0) {
+        if (wait_give_up(c.p, t0, kSiteGrid, c.bar_target, seen)) {
+          fired = 1;
+          break;
+        }
+      }
     }
-    c.ctl()[0] = ld_relaxed(c.p.status + kStFired) != 0 ? 1 : 0;
+    c.ctl()[0] = fired != 0 ? 1 : 0;
   }
   consumer_sync();
   return c.ctl()[0] == 0;
