@@ -206,3 +206,44 @@ def test_prefill_plan_behind_the_abi_feeds_the_decode_plan(kv_layout, plan_dir):
         decided = (logits.topk(2).values[:, 0] - logits.topk(2).values[:, 1]) > 4 * LOGIT_TOLERANCE
         if decided.all():
             assert torch.equal(tokens[b], by_decode[b])
+
+
+def test_prefill_plan_continues_behind_cached_history(plan_dir):
+    """serving.context_base shifts a prefill plan's positions: a prompt prefilled in two pieces (32 positions,
+    then 21 more behind them) must leave the cache and sample the token of the same prompt prefilled at once,
+    bit for bit (both run the same rows through the same arithmetic, only cut into kernel steps differently)."""
+    from tilemega_b200.serving.plan import L2, PlanLibrary
+    from tilemega_b200.serving.state import allocate_state, shuffled_block_table
+    from tilemega_b200.serving.weights import load_weights
+    config = synthetic.TINY_D128
+    capacity, num_blocks, first, second = 96, 9, 32, 21
+    weights = bf16_weights(config)
+    checkpoint = TensorCheckpoint(weights, config.get("tie_word_embeddings", False))
+    prompt = synthetic.seeded_tokens(1, first + second, config["vocab_size"], seed=21).to(torch.int32)
+    layout = dict(batch_lo=1, batch_hi=1, capacity=capacity, kv_layout="paged", num_blocks=num_blocks)
+    decode_lib = PlanLibrary(emit_plan(config, plan_dir, **layout))
+    table = shuffled_block_table(1, capacity // 16, num_blocks, seed=5)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def prefill(pieces):
+        state = allocate_state(config, 1, decode_lib, "cuda:0", block_table=table)
+        done = 0
+        for length in pieces:
+            # (a piece writes the token it samples behind its last position; the driver knows the prompt goes on)
+            state.tokens[0, :first + second] = prompt[0].cuda()
+            lib = PlanLibrary(emit_plan(config, plan_dir, phase="prefill", seq=length, **layout))
+            packed = load_weights(checkpoint, lib, device="cuda:0")
+            plan = lib.create(1, {name: t.data_ptr() for name, t in packed.items()} | state.pointers, 0)
+            state.context_base.fill_(done)
+            plan.set_steps([0])
+            plan.launch(0, L2, stream)
+            torch.cuda.synchronize()
+            assert plan.watchdog() is None
+            plan.close()
+            done += length
+        return state.kv_storage.clone(), state.tokens[0, :first + second + 1].cpu()
+
+    cache_once, tokens_once = prefill([first + second])
+    cache_twice, tokens_twice = prefill([first, second])
+    assert torch.equal(tokens_twice[:first + second], prompt[0])          # the prompt itself is never overwritten
+    assert torch.equal(cache_twice, cache_once) and torch.equal(tokens_twice, tokens_once)

@@ -2762,10 +2762,12 @@ __device__ void consumer_main_dense(Ctx& c) {
         if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
       }
       if (c.lane == 0) {
-        const int pos = seq_pos(p, past, b);
-        int* slot = p.tokens + size_t(seq_of(p, past, b)) * p.capacity + min(pos + 1, p.capacity - 1);
+        const int pos = seq_pos(p, past, b), sq = seq_of(p, past, b);
+        int* slot = p.tokens + size_t(sq) * p.capacity + min(pos + 1, p.capacity - 1);
         int tok = min(max(bi, 0), p.vocab - 1);
-        if (pos + 1 < p.prompt_len) {
+        // a prefill plan's prompt starts at its sequence's context_base: its positions are forced up to there
+        const int forced_below = p.prompt_len + (p.row_pos && p.ctx_base ? __ldg(p.ctx_base + sq) : 0);
+        if (pos + 1 < forced_below) {
           tok = __ldcg(slot);   // teacher-forced prompt position: the token state wins
         } else if (c.cta == 0 && pos + 1 < p.capacity) {
           *slot = tok;
