@@ -2360,49 +2360,67 @@ __device__ void norm_stage_dense(Ctx& c, const void* src, const void* weight, bo
     const __nv_bfloat16* row = static_cast<const __nv_bfloat16*>(src) +
                                (embed ? size_t(min(max(dtok(c)[b], 0), p.vocab - 1)) : size_t(b)) * p.hidden;
     constexpr int kHold = 4;   // hidden <= 8192: at most four 16-byte chunks per thread
-    uint4 v[kHold];
+    uint4 v[kHold], wv[kHold];
     float ss = 0.f;
+    // Two chunks per thread at a time, and everything they need -- the row's values, the norm weights, the
+    // first four parts' partial sums -- requested before anything is used: one L2 round trip for the stage's
+    // loads where chunk after chunk, part group after part group and then the weights paid four or more.
 #pragma unroll
-    for (int j = 0; j < kHold; ++j) {
-      const int i = c.tid + j * kConsumerThreads;
-      v[j] = make_uint4(0u, 0u, 0u, 0u);
-      if (i < chunks) v[j] = embed ? __ldg(reinterpret_cast<const uint4*>(row) + i) : __ldcg(reinterpret_cast<const uint4*>(row) + i);
-      float f[8];
-      unpack8(v[j], f);
-      if (parts > 1 && i < chunks) {
-        // columns 8i .. 8i+7 lie in tile i / 16 at feature 8 * (i % 16): two 16-byte loads per part,
-        // four parts in flight together
-        const float4* tile0 = reinterpret_cast<const float4*>(p.gemm_part + (size_t(i >> 4) * parts * p.batch + b) * kDenseTileN + ((i & 15) << 3));
-        float sum[8];
+    for (int j0 = 0; j0 < kHold; j0 += 2) {
+      float4 x[2][4][2];
+      const float4* tile0[2];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) sum[e] = 0.f;
-        for (int part0 = 0; part0 < parts; part0 += 4) {
-          float4 x[4][2];
-#pragma unroll
-          for (int pp = 0; pp < 4; ++pp) {
-            const bool live = part0 + pp < parts;
-            const float4* at = tile0 + size_t(live ? part0 + pp : part0) * (tile_floats >> 2);
-            x[pp][0] = live ? __ldcg(at) : make_float4(0.f, 0.f, 0.f, 0.f);
-            x[pp][1] = live ? __ldcg(at + 1) : make_float4(0.f, 0.f, 0.f, 0.f);
-          }
-#pragma unroll
-          for (int pp = 0; pp < 4; ++pp) {
-            sum[0] += x[pp][0].x; sum[1] += x[pp][0].y; sum[2] += x[pp][0].z; sum[3] += x[pp][0].w;
-            sum[4] += x[pp][1].x; sum[5] += x[pp][1].y; sum[6] += x[pp][1].z; sum[7] += x[pp][1].w;
-          }
+      for (int jj = 0; jj < 2; ++jj) {
+        const int i = c.tid + (j0 + jj) * kConsumerThreads;
+        const bool live = i < chunks;
+        v[j0 + jj] = wv[j0 + jj] = make_uint4(0u, 0u, 0u, 0u);
+        if (live) {
+          v[j0 + jj] = embed ? __ldg(reinterpret_cast<const uint4*>(row) + i) : __ldcg(reinterpret_cast<const uint4*>(row) + i);
+          wv[j0 + jj] = __ldg(nw + i);
         }
-        uint32_t o[4];
+        // columns 8i .. 8i+7 lie in tile i / 16 at feature 8 * (i % 16): two 16-byte loads per part
+        tile0[jj] = reinterpret_cast<const float4*>(p.gemm_part + (size_t(i >> 4) * parts * p.batch + b) * kDenseTileN + ((i & 15) << 3));
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          f[2 * e] = bf16_round(bf16_round(sum[2 * e]) + f[2 * e]);
-          f[2 * e + 1] = bf16_round(bf16_round(sum[2 * e + 1]) + f[2 * e + 1]);
-          o[e] = uint32_t(bf16_bits(f[2 * e])) | (uint32_t(bf16_bits(f[2 * e + 1])) << 16);
+        for (int pp = 0; pp < 4; ++pp) {
+          const bool wanted = parts > 1 && live && pp < parts;
+          const float4* at = tile0[jj] + size_t(wanted ? pp : 0) * (tile_floats >> 2);
+          x[jj][pp][0] = wanted ? __ldcg(at) : make_float4(0.f, 0.f, 0.f, 0.f);
+          x[jj][pp][1] = wanted ? __ldcg(at + 1) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
-        v[j] = make_uint4(o[0], o[1], o[2], o[3]);
-        reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.x) + size_t(b) * p.hidden)[i] = v[j];
       }
 #pragma unroll
-      for (int e = 0; e < 8; ++e) ss = fmaf(f[e], f[e], ss);
+      for (int jj = 0; jj < 2; ++jj) {
+        const int i = c.tid + (j0 + jj) * kConsumerThreads;
+        float f[8];
+        unpack8(v[j0 + jj], f);
+        if (parts > 1 && i < chunks) {
+          float sum[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) sum[e] = 0.f;
+#pragma unroll
+          for (int pp = 0; pp < 4; ++pp) {   // ascending part order
+            sum[0] += x[jj][pp][0].x; sum[1] += x[jj][pp][0].y; sum[2] += x[jj][pp][0].z; sum[3] += x[jj][pp][0].w;
+            sum[4] += x[jj][pp][1].x; sum[5] += x[jj][pp][1].y; sum[6] += x[jj][pp][1].z; sum[7] += x[jj][pp][1].w;
+          }
+          for (int part = 4; part < parts; ++part) {   // (more than four parts: the rest, part by part)
+            const float4* at = tile0[jj] + size_t(part) * (tile_floats >> 2);
+            const float4 lo = __ldcg(at), hi = __ldcg(at + 1);
+            sum[0] += lo.x; sum[1] += lo.y; sum[2] += lo.z; sum[3] += lo.w;
+            sum[4] += hi.x; sum[5] += hi.y; sum[6] += hi.z; sum[7] += hi.w;
+          }
+          uint32_t o[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            f[2 * e] = bf16_round(bf16_round(sum[2 * e]) + f[2 * e]);
+            f[2 * e + 1] = bf16_round(bf16_round(sum[2 * e + 1]) + f[2 * e + 1]);
+            o[e] = uint32_t(bf16_bits(f[2 * e])) | (uint32_t(bf16_bits(f[2 * e + 1])) << 16);
+          }
+          v[j0 + jj] = make_uint4(o[0], o[1], o[2], o[3]);
+          reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.x) + size_t(b) * p.hidden)[i] = v[j0 + jj];
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss = fmaf(f[e], f[e], ss);
+      }
     }
 #pragma unroll
     for (int m = 16; m; m >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
@@ -2418,7 +2436,7 @@ __device__ void norm_stage_dense(Ctx& c, const void* src, const void* weight, bo
       if (i < chunks) {
         float f[8], w[8];
         unpack8(v[j], f);
-        unpack8(__ldg(nw + i), w);
+        unpack8(wv[j], w);
         uint32_t o[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e)
