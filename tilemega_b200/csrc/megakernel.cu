@@ -319,8 +319,13 @@ __device__ __forceinline__ int attn_count(const MegaParams& p, const Rows& rw, i
 //    (sequence, head, slot) order, are cut into `ntasks` <= grid RANGES of `per` slots, one claim
 //    each, so every CTA streams the same number of slots whatever the sequences' lengths; a range
 //    is worked through as the SEGMENTS where it meets the units, each segment a partial of its unit.
+//    A segment has a fixed cost (readiness, RoPE staging, merge: about four slots' worth of time), so
+//    the axis the ranges cut is slots PLUS that cost per unit: with sequences of very different
+//    lengths a range over many short units would otherwise take much longer than one inside a long unit
+//    (batch 64, contexts 512..8192: the slowest CTA took 242 us, the median one 195 us).
 struct AttnShape {
   int spt, ntasks, per, total;
+  int fixed;   // ranges are measured in slots plus `fixed` per unit: what a segment costs before its first slot
 };
 
 __device__ __forceinline__ AttnShape attn_shape(const MegaParams& p, const Rows& rw, int nk) {
@@ -329,10 +334,13 @@ __device__ __forceinline__ AttnShape attn_shape(const MegaParams& p, const Rows&
   sh.total = p.kv_heads * warp_sum((lane < p.batch ? rw.p0 / nk + 1 : 0) + (lane + 32 < p.batch ? rw.p1 / nk + 1 : 0));
   const int floor_spt = max(1, p.attn_min_spt);   // a task's fixed cost wants at least this many slots
   const int per_cta = (sh.total + p.grid - 1) / p.grid;
+  sh.fixed = 0;
   if (per_cta >= 2 * floor_spt) {
-    sh.per = per_cta;
-    sh.spt = per_cta;
-    sh.ntasks = (sh.total + per_cta - 1) / per_cta;
+    sh.fixed = floor_spt;
+    sh.total += p.batch * p.kv_heads * sh.fixed;       // slots plus the fixed cost of every unit
+    sh.per = (sh.total + p.grid - 1) / p.grid;
+    sh.spt = sh.per;
+    sh.ntasks = (sh.total + sh.per - 1) / sh.per;
     return sh;
   }
   sh.per = 0;
@@ -405,30 +413,34 @@ __device__ __forceinline__ bool attn_next(const MegaParams& p, const Rows& rw, i
     a = attn_task(p, rw, nk, sh.spt, w.t);
     return true;
   }
-  if (w.x >= w.x1) return false;
-  while (w.x >= w.base + w.ns * p.kv_heads && w.b < p.batch - 1) {
-    w.base += w.ns * p.kv_heads;
-    ++w.b;
-    w.ns = row_pos(rw, w.b) / nk + 1;
+  // a unit occupies [u0, u0 + fixed + ns) of the axis: its fixed cost first, then its slots; the part of the
+  // range inside the slots is a segment (a range that only touches a unit's fixed cost holds none of it)
+  for (;;) {
+    if (w.x >= w.x1) return false;
+    while (w.x >= w.base + (w.ns + sh.fixed) * p.kv_heads && w.b < p.batch - 1) {
+      w.base += (w.ns + sh.fixed) * p.kv_heads;
+      ++w.b;
+      w.ns = row_pos(rw, w.b) / nk + 1;
+    }
+    const int cost = w.ns + sh.fixed;
+    const int g = min((w.x - w.base) / cost, p.kv_heads - 1);
+    const int u0 = w.base + g * cost;
+    const int lo = max(w.x, u0 + sh.fixed), hi = min(w.x1, u0 + cost);
+    w.x = min(w.x1, u0 + cost);
+    if (lo >= hi) continue;
+    const int first = (u0 + sh.fixed) / sh.per, last = (u0 + cost - 1) / sh.per;
+    a.b = w.b;
+    a.sq = row_seq(rw, w.b);
+    a.g = g;
+    a.pos = row_pos(rw, w.b);
+    a.ns = w.ns;
+    a.nch = last - first + 1;
+    a.c = lo / sh.per - first;
+    a.slot0 = lo - (u0 + sh.fixed);
+    a.slot1 = hi - (u0 + sh.fixed);
+    a.task0 = first + w.b * p.kv_heads + g;
+    return true;
   }
-  const int rel = w.x - w.base;
-  const int g = min(rel / w.ns, p.kv_heads - 1);
-  const int s0 = rel - g * w.ns;
-  const int len = min(w.ns - s0, w.x1 - w.x);
-  const int u0 = w.base + g * w.ns;
-  const int first = u0 / sh.per, last = (u0 + w.ns - 1) / sh.per;
-  a.b = w.b;
-  a.sq = row_seq(rw, w.b);
-  a.g = g;
-  a.pos = row_pos(rw, w.b);
-  a.ns = w.ns;
-  a.nch = last - first + 1;
-  a.c = w.x / sh.per - first;
-  a.slot0 = s0;
-  a.slot1 = s0 + len;
-  a.task0 = first + w.b * p.kv_heads + g;
-  w.x += len;
-  return true;
 }
 
 __device__ __forceinline__ int table_entry(const MegaParams& p, int b, int blk) {
