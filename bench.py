@@ -67,7 +67,8 @@ def measured_peak_gbs() -> tuple[float, str]:
 
 
 MODELS = {"llama-3.1-8b": synthetic.LLAMA_3_1_8B, "llama-3.2-1b": synthetic.LLAMA_3_2_1B,
-          "llama-3.1-70b": synthetic.LLAMA_3_1_70B, "qwen3-30b-a3b": synthetic.QWEN3_30B_A3B}
+          "llama-3.1-70b": synthetic.LLAMA_3_1_70B, "qwen3-30b-a3b": synthetic.QWEN3_30B_A3B,
+          "bert-base": synthetic.BERT_BASE}   # bert-base: the encoder forward workload (run_forward)
 
 
 def workload(args) -> dict:
@@ -351,6 +352,94 @@ def run_prefill(args) -> None:
     print(json.dumps(line), flush=True)
 
 
+def run_forward(args) -> None:
+    """Secondary workload: the BERT-base-shaped encoder forward (`--model bert-base --batch B`, batch x 128 tokens)
+    through a forward plan (phase 2 of the plan ABI). A step is one forward pass = one graph launch of the
+    encoder's kernels; `--steps` passes are timed back to back between two CUDA events. The CPU baseline is the
+    oracle's fp32 forward on the host cores."""
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU implementation")
+    from tilemega_b200.planbuild import PLAN_DIR, emit_plan, remove_plans
+    from tilemega_b200.serving.encoder import EncoderEngine
+    from tilemega_b200.serving.weights import TensorCheckpoint
+    config = dict(synthetic.BERT_BASE)
+    if args.layers:
+        config["num_hidden_layers"] = args.layers
+    batch, seq, steps, warmup = args.batch, 128, args.steps, max(args.warmup, 3)
+    dtype_name = "bf16" if args.weights == "bf16" and os.environ.get("TMB_ENCODER_DTYPE") == "bf16" else "f16"
+    torch.cuda.set_device(0)
+    plan_dir = PLAN_DIR / "bench"
+    weights = synthetic.encoder_weights(config, seed=0)
+    ids, types = synthetic.encoder_inputs(config, batch, seed=1)
+    so = emit_plan(config, plan_dir, phase="forward", batch_lo=batch, dtype=dtype_name)
+    engine = EncoderEngine(TensorCheckpoint(weights), so, batch)
+    stream = engine.stream
+    host_ids, host_types = ids.pin_memory(), types.pin_memory()
+    hidden_out, pooled_out = engine.outputs()
+    host_pooled = torch.zeros_like(pooled_out, device="cpu").pin_memory()
+    engine(ids.cuda(), types.cuda())
+    for _ in range(warmup):
+        engine.launch()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    with ClockSampler(0) as clocks:
+        begin.record(stream)
+        for _ in range(steps):
+            engine.launch()
+        end.record(stream)
+        stream.synchronize()
+        device_s = begin.elapsed_time(end) / 1e3
+        # end to end: every pass copies its ids from pinned host memory and reads the pooled rows back
+        wall = time.perf_counter()
+        for _ in range(steps):
+            engine.tensors["input_ids"].copy_(host_ids.view(-1), non_blocking=True)
+            engine.tensors["token_type_ids"].copy_(host_types.view(-1), non_blocking=True)
+            engine.launch()
+            host_pooled.copy_(pooled_out, non_blocking=True)
+            stream.synchronize()
+        wall = time.perf_counter() - wall
+    if engine.plan.watchdog() is not None:
+        raise SystemExit(f"a bounded device wait gave up: {engine.plan.watchdog()}")
+    hidden, inter, layers = config["hidden_size"], config["intermediate_size"], config["num_hidden_layers"]
+    tokens = batch * seq
+    # products of the projections (2 flops per weight element and token) and of attention (QK^T and PV)
+    flops = 2.0 * tokens * layers * (4 * hidden * hidden + 2 * hidden * inter) + 4.0 * batch * layers * seq * seq * hidden
+    weight_bytes = 2 * layers * (4 * hidden * hidden + 2 * hidden * inter)
+    peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
+    peak_tf, peak_kind = (float(peaks["bf16_tflops"]), "measured") if peaks else (1590.0, "fallback")
+    line = {
+        "metric": "encoder_sequences_per_s", "value": batch * steps / device_s, "unit": "seq/s", "n_gpus": 1, "steps": steps,
+        "warmup": warmup, "ms_per_step": device_s * 1e3 / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": dtype_name, "data": "synthetic",
+        "config": {"workload": f"bert-base-shaped encoder forward, batch {batch} x {seq} tokens, all-ones attention mask", "layers": layers,
+                   "l2": f"weights ({weight_bytes / 1e6:.0f} MB) exceed L2" if weight_bytes > 126e6 else "weights fit L2 (small case)"},
+        "roofline": {"bound": "tensor", "achieved": flops / device_s * steps / 1e12, "peak": peak_tf, "unit": "TFLOP/s",
+                     "frac": flops / device_s * steps / 1e12 / peak_tf, "traffic": None, "peak_kind": "of " + peak_kind + " (cuBLAS bf16 burst)",
+                     "flops_per_launch": flops, "weight_gbs": weight_bytes * steps / device_s / 1e9},
+        "e2e": {"value": batch * steps / wall, "unit": "seq/s", "h2d_bytes_per_step": 2 * tokens * 8,
+                "d2h_bytes_per_step": pooled_out.numel() * pooled_out.element_size()},
+        # per pass: embedding, pooler, and per layer QKV, attention, O-proj, add + LayerNorm, FFN up, FFN down, add + LayerNorm
+        "gpu_launches": steps * (2 + 7 * layers),
+        "clocks": clocks.summary(),
+    }
+    if not args.no_cpu:
+        from oracle.encoder_oracle import encoder_forward
+        threads = min(os.cpu_count() or 1, 16)
+        torch.set_num_threads(threads)
+        sample = min(batch, 4)
+        encoder_forward(weights, config, ids[:1], types[:1])
+        started = time.perf_counter()
+        repeats = 3
+        for _ in range(repeats):
+            encoder_forward(weights, config, ids[:sample], types[:sample])
+        cpu_s = (time.perf_counter() - started) / repeats
+        line["cpu_baseline"] = {"value": sample / cpu_s, "unit": "seq/s", "cores": threads, "kind": "port",
+                                "sample": f"the oracle's fp32 forward of {sample} sequence(s) of {seq} tokens, mean of {repeats}"}
+    engine.close()
+    remove_plans(plan_dir)
+    print(json.dumps(line), flush=True)
+
+
 def run_ours(args) -> None:
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the product path has no CPU implementation")
@@ -565,6 +654,8 @@ def main() -> None:
     args = parser.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.model == "bert-base":
+        run_forward(args)
     elif args.prefill:
         run_prefill(args)
     else:

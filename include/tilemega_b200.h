@@ -31,6 +31,11 @@ enum { TM_SERVING_PREFILL = 0, TM_SERVING_DECODE = 1, TM_SERVING_FORWARD = 2 };
 enum { TM_SERVING_L1 = 1, TM_SERVING_L2 = 2 };
 enum { TM_BUFFER_INTERNAL = 0, TM_BUFFER_EXTERNAL = 1 };
 enum { TM_DTYPE_BF16 = 0, TM_DTYPE_F32 = 1, TM_DTYPE_I32 = 2,
+       /* the reference's forward runtime adds this code for token ids
+        * (include/tilemega/Codegen/tasks/Sm90F3Runtime.cuh:20-22) */
+       TM_DTYPE_I64 = 3,
+       /* addition: fp16 elements, in the buffers of a forward plan whose sidecar says "dtype": "f16" */
+       TM_DTYPE_F16 = 5,
        /* addition (the reference has no 8-bit weights): e4m3 bytes, one element per byte, in the
         * weight buffers of a plan whose sidecar says "weights": "e4m3"; each such buffer comes with an
         * fp32 buffer "<name>.scale" of one scale per output row */

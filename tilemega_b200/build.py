@@ -20,9 +20,13 @@ LIBRARY = LIB_DIR / "libtilemega_b200.so"
 UNITS = (("megakernel", "megakernel.cu", ()), ("megakernel_extended", "megakernel.cu", ("-DTMB_EXTENDED=1",)),
          ("megakernel_dense", "megakernel.cu", ("-DTMB_DENSE=1",)), ("megakernel_fp8", "megakernel.cu", ("-DTMB_FP8=1",)),
          ("runtime", "runtime.cu", ()), ("plan_spec", "plan_spec.cpp", ()), ("static_probe", "static_probe.cu", ()),
-         ("pack", "pack.cu", ()), ("calibrate", "calibrate.cu", ()))
+         ("pack", "pack.cu", ()), ("calibrate", "calibrate.cu", ()), ("encoder", "encoder.cu", ()))
+# headers a source includes (directly or through another header): a unit is rebuilt when one of ITS headers changed
+KERNEL_HEADERS = ("params.h", "ptx.cuh")
+UNIT_HEADERS = {"megakernel.cu": KERNEL_HEADERS, "static_probe.cu": KERNEL_HEADERS, "calibrate.cu": ("ptx.cuh",), "pack.cu": (),
+                "plan_spec.cpp": ("plan_spec.h", "json.h", "params.h")}
 SOURCES = tuple(sorted({unit[1] for unit in UNITS}))
-HEADERS = ("params.h", "ptx.cuh", "plan_spec.h", "json.h")
+HEADERS = ("params.h", "ptx.cuh", "plan_spec.h", "json.h", "encoder.h")
 
 
 def nvcc() -> str:
@@ -53,11 +57,10 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
     build_dir = ROOT / "build"
     build_dir.mkdir(exist_ok=True)
     running = []
-    headers = [CSRC / name for name in HEADERS] + [ROOT.parent / "include" / "tilemega_b200.h"]
     for stem, name, flags in UNITS:
         obj = build_dir / (stem + ".o")
         objects.append(str(obj))
-        inputs = [CSRC / name] + headers
+        inputs = [CSRC / name] + [CSRC / header for header in UNIT_HEADERS.get(name, HEADERS)] + [ROOT.parent / "include" / "tilemega_b200.h"]
         if not force and not verbose and obj.exists() and all(path.stat().st_mtime <= obj.stat().st_mtime for path in inputs):
             continue   # this unit's object is newer than its source and every header
         cmd = [nvcc(), *common, *flags, "-x", "cu" if name.endswith(".cu") else "c++", "-c", str(CSRC / name), "-o",

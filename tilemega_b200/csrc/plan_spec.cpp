@@ -110,6 +110,88 @@ GemvGeo MakeGeo(const char* what, int n, int k, const Json& overrides, int elem_
   return g;
 }
 
+// A forward plan's table (the reference's forward runtime exposes the exported module's parameters under their
+// qualified names, its int64 inputs and its outputs: include/tilemega/Codegen/tasks/Sm90F3Runtime.cuh:95-131,
+// python/tilemega/dnn/check.py:33-66): the BertModel parameters in nn.Linear layout as they are (no packing: the
+// GEMM kernel reads K-major rows through tensor maps), two int64 inputs, two outputs, four internal activations.
+PlanSpec ForwardSpec(const Json& plan) {
+  PlanSpec s;
+  s.forward = true;
+  const Json& model = plan.at("model");
+  s.hidden = int(model.integer("hidden_size", 0));
+  s.inter = int(model.integer("intermediate_size", 0));
+  s.heads = int(model.integer("num_attention_heads", 0));
+  s.layers = int(model.integer("num_hidden_layers", 0));
+  s.vocab = int(model.integer("vocab_size", 0));
+  s.max_position = int(model.integer("max_position_embeddings", 0));
+  s.type_vocab = int(model.integer("type_vocab_size", 0));
+  s.eps = model.num("layer_norm_eps", 1e-12);
+  s.kv_heads = s.heads;
+  s.head_dim = s.heads ? s.hidden / s.heads : 0;
+  s.forward_seq = int(plan.integer("seq", 0));
+  s.batch_lo = int(plan.integer("batch_lo", 1));
+  s.batch_hi = int(plan.integer("batch_hi", s.batch_lo));
+  s.grid = int(plan.integer("grid", 0));
+  const std::string dtype = plan.str("dtype", "f16");
+  if (dtype != "f16" && dtype != "bf16") throw std::invalid_argument("a forward plan computes in f16 or bf16 (dtype)");
+  s.f16 = dtype == "f16";
+  if (model.str("hidden_act", "gelu") != "gelu") throw std::invalid_argument("the encoder's feed-forward is built with the erf GELU only");
+  if (model.str("position_embedding_type", "absolute") != "absolute")
+    throw std::invalid_argument("the encoder is built with absolute position embeddings only");
+  if (s.hidden <= 0 || s.inter <= 0 || s.heads <= 0 || s.layers <= 0 || s.vocab <= 0 || s.type_vocab <= 0)
+    throw std::invalid_argument("model dimensions must be positive");
+  if (s.head_dim != 64 || s.heads * 64 != s.hidden) throw std::invalid_argument("encoder heads must be 64 wide");
+  if (s.hidden % 128 || s.hidden > 1024) throw std::invalid_argument("encoder hidden size must be a multiple of 128, at most 1024");
+  if (s.inter % 128) throw std::invalid_argument("encoder intermediate size must be a multiple of 128");
+  if (s.forward_seq != 128 || s.forward_seq > s.max_position) throw std::invalid_argument("forward plans run sequences of 128 positions (seq)");
+  if (s.batch_lo < 1 || s.batch_hi < s.batch_lo || s.batch_hi > 512) throw std::invalid_argument("forward batch interval must lie in [1, 512]");
+  const uint32_t elem = s.f16 ? 5u : 0u;
+  auto add = [&](const std::string& name, uint32_t role, uint32_t dtype, uint64_t constant, uint64_t per_batch, bool weight) {
+    BufferSpec b;
+    b.name = name;
+    b.role = role;
+    b.dtype = dtype;
+    b.elements_constant = constant;
+    b.elements_per_batch = per_batch;
+    if (weight) b.pack_json = Alias(name);
+    s.buffers.push_back(b);
+  };
+  const uint64_t H = uint64_t(s.hidden), I = uint64_t(s.inter), S = uint64_t(s.forward_seq);
+  add("embeddings.word_embeddings.weight", 1, elem, uint64_t(s.vocab) * H, 0, true);
+  add("embeddings.position_embeddings.weight", 1, elem, uint64_t(s.max_position) * H, 0, true);
+  add("embeddings.token_type_embeddings.weight", 1, elem, uint64_t(s.type_vocab) * H, 0, true);
+  add("embeddings.LayerNorm.weight", 1, elem, H, 0, true);
+  add("embeddings.LayerNorm.bias", 1, elem, H, 0, true);
+  for (int l = 0; l < s.layers; ++l) {
+    const std::string p = "encoder.layer." + std::to_string(l) + ".";
+    for (const char* part : {"query", "key", "value"}) {
+      add(p + "attention.self." + part + ".weight", 1, elem, H * H, 0, true);
+      add(p + "attention.self." + part + ".bias", 1, elem, H, 0, true);
+    }
+    add(p + "attention.output.dense.weight", 1, elem, H * H, 0, true);
+    add(p + "attention.output.dense.bias", 1, elem, H, 0, true);
+    add(p + "attention.output.LayerNorm.weight", 1, elem, H, 0, true);
+    add(p + "attention.output.LayerNorm.bias", 1, elem, H, 0, true);
+    add(p + "intermediate.dense.weight", 1, elem, I * H, 0, true);
+    add(p + "intermediate.dense.bias", 1, elem, I, 0, true);
+    add(p + "output.dense.weight", 1, elem, H * I, 0, true);
+    add(p + "output.dense.bias", 1, elem, H, 0, true);
+    add(p + "output.LayerNorm.weight", 1, elem, H, 0, true);
+    add(p + "output.LayerNorm.bias", 1, elem, H, 0, true);
+  }
+  add("pooler.dense.weight", 1, elem, H * H, 0, true);
+  add("pooler.dense.bias", 1, elem, H, 0, true);
+  add("input_ids", 1, 3, 0, S, false);
+  add("token_type_ids", 1, 3, 0, S, false);
+  add("last_hidden_state", 1, elem, 0, S * H, false);
+  add("pooler_output", 1, elem, 0, H, false);
+  add("forward.hidden", 0, elem, 0, S * H, false);
+  add("forward.qkv", 0, elem, 0, S * 3 * H, false);
+  add("forward.context", 0, elem, 0, S * H, false);
+  add("forward.ffn", 0, elem, 0, S * I, false);
+  return s;
+}
+
 }  // namespace
 
 int PlanSpec::max_k() const {
@@ -133,7 +215,8 @@ uint64_t PlanSpec::weight_bytes() const {
 PlanSpec PlanSpec::FromJson(const Json& plan) {
   PlanSpec s;
   const std::string phase = plan.str("phase", "decode");
-  if (phase != "decode" && phase != "prefill") throw std::invalid_argument("decode and prefill plans are built (phase)");
+  if (phase == "forward") return ForwardSpec(plan);
+  if (phase != "decode" && phase != "prefill") throw std::invalid_argument("decode, prefill and forward plans are built (phase)");
   s.prefill = phase == "prefill";
   const Json& model = plan.at("model");
   s.hidden = int(model.integer("hidden_size", 0));

@@ -17,7 +17,7 @@ namespace tmb {
 struct BufferSpec {
   std::string name;
   uint32_t role = 0;   // 0 internal, 1 external
-  uint32_t dtype = 0;  // 0 bf16, 1 f32, 2 i32
+  uint32_t dtype = 0;  // 0 bf16, 1 f32, 2 i32, 3 i64, 4 e4m3, 5 f16
   uint64_t elements_constant = 0, elements_per_batch = 0;
   std::string pack_json;
 };
@@ -59,6 +59,11 @@ struct PlanSpec {
   // runs kDenseMaxBatch rows per step, (sequence, position) pairs in order, ceil(batch * seq / rows) steps per launch
   bool prefill = false;
   int prefill_seq = 0;
+  // forward plans (phase 2): a stateless encoder pass over batch x forward_seq tokens (csrc/encoder.cu); hidden,
+  // inter, heads, layers, vocab and eps describe the encoder, none of the decode fields above applies
+  bool forward = false;
+  bool f16 = false;             // activations and weights in fp16 (else bf16)
+  int forward_seq = 0, max_position = 0, type_vocab = 0;
   DenseGeo dgeo[kNumGemv] = {};
   int normed_buf = -1;
   // buffer table

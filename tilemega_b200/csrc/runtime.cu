@@ -20,6 +20,7 @@
 
 #include "../../include/tilemega_b200.h"
 #include "params.h"
+#include "encoder.h"
 #include "plan_spec.h"
 
 extern "C" int tmb_smem_bytes(const tmb::MegaParams* p);
@@ -119,6 +120,7 @@ struct Plan {
   const int* row_seq_dev = nullptr;     // ... its (sequence, position in the prompt) pairs, one per kernel row,
   const int* row_rel_dev = nullptr;
   int* row_abs_dev = nullptr;           // ... and the pairs' positions in the cache, resolved at every launch
+  tmb::EncoderPlan* encoder = nullptr;  // forward plan: the encoder's launch graph (none of the decode state above is used)
 };
 
 // Position in the cache of every row of a prefill plan: its position in the prompt plus its sequence's
@@ -134,7 +136,9 @@ Plan* AsPlan(void* handle) {
   return plan && plan->magic == kMagic ? plan : nullptr;
 }
 
-uint64_t ElementBytes(uint32_t dtype) { return dtype == TM_DTYPE_BF16 ? 2 : dtype == TM_DTYPE_E4M3 ? 1 : 4; }
+uint64_t ElementBytes(uint32_t dtype) {
+  return dtype == TM_DTYPE_BF16 || dtype == TM_DTYPE_F16 ? 2 : dtype == TM_DTYPE_E4M3 ? 1 : dtype == TM_DTYPE_I64 ? 8 : 4;
+}
 
 cudaError_t Alloc(Plan& plan, void** out, size_t bytes) {
   cudaError_t err = cudaMalloc(out, bytes ? bytes : 16);
@@ -145,6 +149,7 @@ cudaError_t Alloc(Plan& plan, void** out, size_t bytes) {
 
 void Destroy(Plan* plan) {
   DeviceScope scope(plan->device);
+  tmb::EncoderDestroy(plan->encoder);
   for (void* p : plan->owned) cudaFree(p);
   plan->magic = 0;
   delete plan;
@@ -220,12 +225,12 @@ int tm_plan_query(tm_plan_info* out) {
   const tmb::PlanSpec& s = lib.spec;
   std::memset(out, 0, sizeof(*out));
   out->abi_version = TM_SERVING_ABI_VERSION;
-  out->phase = s.prefill ? TM_SERVING_PREFILL : TM_SERVING_DECODE;
+  out->phase = s.forward ? TM_SERVING_FORWARD : s.prefill ? TM_SERVING_PREFILL : TM_SERVING_DECODE;
   out->batch_lo = s.batch_lo;
   out->batch_hi = s.batch_hi;
-  out->seq = s.prefill ? s.prefill_seq : 1;
+  out->seq = s.forward ? s.forward_seq : s.prefill ? s.prefill_seq : 1;
   out->past_lo = 0;
-  out->past_hi = s.prefill ? 0 : s.capacity - 1;
+  out->past_hi = s.prefill || s.forward ? 0 : s.capacity - 1;
   out->capacity = s.capacity;
   out->grid = s.grid;  // 0: one CTA per SM of the device the plan is created on
   out->residency = 1;
@@ -307,6 +312,17 @@ void* tm_plan_create(int batch, void* const* external, int device) {
       cudaError_t err = Alloc(*plan, &plan->buffer_ptr[i], plan->buffer_bytes[i]);
       if (err != cudaSuccess) return fail("allocating " + b.name, err);
     }
+  }
+  if (s.forward) {
+    // a stateless encoder pass: the launch graph over the table's buffers is all the plan holds
+    std::string why;
+    plan->encoder = tmb::EncoderCreate(s, batch, plan->buffer_ptr, prop.multiProcessorCount, &why);
+    if (!plan->encoder) {
+      Fail(-1, "tm_plan_create: " + why);
+      return nullptr;
+    }
+    plan->step_count = 1;
+    return plan.release();
   }
   tmb::MegaParams& p = plan->params;
   p.batch = rows;
@@ -541,6 +557,11 @@ int tm_plan_set_steps(void* handle, const int32_t* past, uint32_t count) {
   Plan* plan = AsPlan(handle);
   if (!plan || !past || count == 0) return Fail(-1, "tm_plan_set_steps: bad argument");
   const tmb::MegaParams& p = plan->params;
+  if (plan->encoder) {
+    // a forward plan has ONE step, at past 0 (include/tilemega/Codegen/tasks/Sm90F3Runtime.cuh:121-123)
+    if (count != 1 || past[0] != 0) return Fail(-2, "tm_plan_set_steps: a forward plan has one step, at past 0");
+    return 0;
+  }
   if (plan->prefill_chunks) {
     // a prefill plan has ONE step, at past 0 (python/tilemega/serving/engine.py:89-90 sets exactly that)
     if (count != 1 || past[0] != 0) return Fail(-2, "tm_plan_set_steps: a prefill plan has one step, at past 0");
@@ -562,6 +583,7 @@ int tm_plan_set_prompt_len(void* handle, int prompt_len) {
   if (!plan || prompt_len < 0 || prompt_len > plan->params.capacity)
     return Fail(-1, "tm_plan_set_prompt_len: bad argument");
   if (plan->prefill_chunks) return Fail(-1, "tm_plan_set_prompt_len: a prefill plan's prompt length is its seq");
+  if (plan->encoder) return Fail(-1, "tm_plan_set_prompt_len: a forward plan has no prompt");
   plan->prompt_len = prompt_len;
   return 0;
 }
@@ -624,6 +646,14 @@ int tm_plan_launch_steps(void* handle, uint32_t first_step, uint32_t steps, uint
   Plan* plan = AsPlan(handle);
   if (!plan) return Fail(-1, "tm_plan_launch_steps: bad argument");
   DeviceScope scope(plan->device);
+  if (plan->encoder) {
+    // one stateless pass; both executor modes run the same graph (their outputs are bit-identical by construction)
+    if (first_step != 0 || steps != 1) return Fail(-2, "tm_plan_launch_steps: a forward plan has one step");
+    if (mode != TM_SERVING_L1 && mode != TM_SERVING_L2) return Fail(-3, "tm_plan_launch_steps: unknown mode");
+    if (plan->abandoned) return Fail(-4, "tm_plan_launch_steps: the plan was abandoned by a bounded wait; clear the watchdog first");
+    const int status = tmb::EncoderLaunch(plan->encoder, static_cast<cudaStream_t>(stream));
+    return status == 0 ? 0 : Fail(status, std::string("tm_plan_launch_steps: ") + cudaGetErrorString(cudaError_t(status)));
+  }
   tmb::MegaParams p;
   const int ready = PrepareLaunch(plan, "tm_plan_launch_steps", first_step, steps, mode, base_iteration,
                                   static_cast<cudaStream_t>(stream), &p);
@@ -689,7 +719,7 @@ unsigned tm_plan_loop_modes(void* handle) { return AsPlan(handle) ? (TM_SERVING_
 
 int tm_plan_read_step_ns(void* handle, uint32_t first, uint32_t count, uint64_t* host) {
   Plan* plan = AsPlan(handle);
-  if (!plan || !host || uint64_t(first) + count > uint64_t(plan->params.capacity) + 2)
+  if (!plan || !host || plan->encoder || uint64_t(first) + count > uint64_t(plan->params.capacity) + 2)
     return Fail(-1, "tm_plan_read_step_ns: bad argument");
   DeviceScope scope(plan->device);
   cudaError_t err =
@@ -710,6 +740,11 @@ int tm_plan_watchdog(void* handle, uint64_t* record12) {
   Plan* plan = AsPlan(handle);
   if (!plan || !record12) return 0;
   DeviceScope scope(plan->device);
+  if (plan->encoder) {
+    const int fired = tmb::EncoderStatus(plan->encoder, record12);
+    if (fired > 0) plan->abandoned = true;
+    return fired > 0 ? 1 : 0;
+  }
   unsigned long long words[tmb::kStWords] = {};
   if (cudaMemcpy(words, plan->params.status, sizeof(words), cudaMemcpyDeviceToHost) != cudaSuccess) return 0;
   for (int i = 0; i < 12; ++i) record12[i] = words[i];
@@ -721,6 +756,11 @@ int tm_plan_clear_watchdog(void* handle) {
   Plan* plan = AsPlan(handle);
   if (!plan) return Fail(-1, "tm_plan_clear_watchdog: bad plan");
   DeviceScope scope(plan->device);
+  if (plan->encoder) {
+    tmb::EncoderClear(plan->encoder);
+    plan->abandoned = false;
+    return 0;
+  }
   cudaError_t err = cudaMemset(plan->params.status, 0, tmb::kStWords * sizeof(unsigned long long));
   if (err == cudaSuccess) plan->abandoned = false;
   return err == cudaSuccess ? 0 : Fail(int(err), cudaGetErrorString(err));
@@ -728,7 +768,7 @@ int tm_plan_clear_watchdog(void* handle) {
 
 int tm_plan_watchdog_probe(void* handle, int withhold, uint32_t limit_us, void* stream) {
   Plan* plan = AsPlan(handle);
-  if (!plan || limit_us == 0 || limit_us > 1000000u) return Fail(-1, "tm_plan_watchdog_probe: bad argument");
+  if (!plan || plan->encoder || limit_us == 0 || limit_us > 1000000u) return Fail(-1, "tm_plan_watchdog_probe: bad argument");
   DeviceScope scope(plan->device);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   cudaError_t err = cudaMemsetAsync(plan->sync_block, 0, plan->sync_bytes, s);
@@ -748,7 +788,7 @@ int tm_plan_watchdog_probe(void* handle, int withhold, uint32_t limit_us, void* 
 
 int tm_plan_trace_step(void* handle, int step) {
   Plan* plan = AsPlan(handle);
-  if (!plan) return Fail(-1, "tm_plan_trace_step: bad plan");
+  if (!plan || plan->encoder) return Fail(-1, "tm_plan_trace_step: bad plan");
   DeviceScope scope(plan->device);
   if (step >= 0 && !plan->trace_dev) {
     plan->trace_bytes = size_t(plan->params.grid) * size_t(plan->params.trace_stages) * 4 * sizeof(unsigned long long);

@@ -27,6 +27,29 @@ MODEL_KEYS = ("hidden_size", "intermediate_size", "num_attention_heads", "num_ke
               "norm_topk_prob")
 
 
+ENCODER_KEYS = ("hidden_size", "intermediate_size", "num_attention_heads", "num_hidden_layers", "vocab_size",
+                "max_position_embeddings", "type_vocab_size", "layer_norm_eps", "hidden_act", "position_embedding_type")
+
+
+def forward_document(config: dict, *, batch_lo: int = 1, batch_hi: int | None = None, seq: int = 128,
+                     dtype: str = "f16") -> dict:
+    """The sidecar of a forward plan (phase 2): a stateless BERT-shaped encoder pass over batch x seq tokens."""
+    model = {key: config[key] for key in ENCODER_KEYS if key in config}
+    batch_hi = batch_lo if batch_hi is None else batch_hi
+    if not 1 <= batch_lo <= batch_hi <= 512:
+        raise ValueError("forward batch interval must lie in [1, 512]")
+    if seq != 128:
+        raise ValueError("forward plans run sequences of 128 positions")
+    if dtype not in ("f16", "bf16"):
+        raise ValueError("dtype must be 'f16' or 'bf16'")
+    if config["hidden_size"] != 64 * config["num_attention_heads"] or config["hidden_size"] % 128 or config["hidden_size"] > 1024:
+        raise ValueError("encoder heads must be 64 wide, the hidden size a multiple of 128 up to 1024")
+    if config["intermediate_size"] % 128:
+        raise ValueError("encoder intermediate size must be a multiple of 128")
+    return {"execution": "graph", "arch": "sm_100a", "phase": "forward", "model": model, "batch_lo": batch_lo,
+            "batch_hi": batch_hi, "seq": seq, "dtype": dtype}
+
+
 def plan_document(config: dict, *, batch_lo: int = 1, batch_hi: int | None = None, capacity: int,
                   kv_layout: str = "contiguous", num_blocks: int = 0, geometry: dict | None = None,
                   grid: int = 0, slots: int = 0, write_logits: bool = True,
@@ -90,7 +113,10 @@ def emit_plan(config: dict, out_dir: str | Path | None = None, **options) -> Pat
     """Write `<out_dir>/<digest>.so` + `.so.plan.json` and return the library path
     (`out_dir` defaults to PLAN_DIR, inside the package tree)."""
     out_dir = PLAN_DIR if out_dir is None else out_dir
-    document = plan_document(config, **options)
+    if options.get("phase") == "forward":
+        document = forward_document(config, **{key: value for key, value in options.items() if key != "phase"})
+    else:
+        document = plan_document(config, **options)
     text = json.dumps(document, indent=1, sort_keys=True) + "\n"
     digest = hashlib.sha256(text.encode()).hexdigest()[:16]
     out_dir = Path(out_dir)
@@ -122,4 +148,4 @@ def remove_plans(out_dir: str | Path) -> None:
             out_dir.rmdir()
 
 
-__all__ = ["emit_plan", "plan_document", "remove_plans", "LIBRARY", "PLAN_DIR"]
+__all__ = ["emit_plan", "forward_document", "plan_document", "remove_plans", "LIBRARY", "PLAN_DIR"]

@@ -15,7 +15,8 @@ import torch
 
 from .plan import Buffer, PlanLibrary
 
-DTYPES = {0: torch.bfloat16, 1: torch.float32, 2: torch.int32, 4: torch.uint8}   # 4: e4m3 bytes (an addition of this library)
+DTYPES = {0: torch.bfloat16, 1: torch.float32, 2: torch.int32, 3: torch.int64, 4: torch.uint8,   # 4: e4m3 bytes, 5: fp16 (additions
+          5: torch.float16}                                                                     # of this library)
 E4M3_MAX = 448.0
 
 

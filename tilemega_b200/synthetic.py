@@ -151,3 +151,50 @@ def seeded_contexts(batch: int, low: int, high: int, seed: int = 2) -> torch.Ten
     """Per-sequence context lengths uniform in [low, high]."""
     generator = torch.Generator().manual_seed(seed)
     return torch.randint(low, high + 1, (batch,), generator=generator, dtype=torch.int64).to(torch.int32)
+
+
+# BERT-base-shaped encoder (the forward workload) and a two-layer model with the same structure for tests.
+BERT_BASE = dict(architectures=["BertModel"], hidden_size=768, intermediate_size=3072, num_attention_heads=12,
+                 num_hidden_layers=12, vocab_size=30522, max_position_embeddings=512, type_vocab_size=2,
+                 layer_norm_eps=1e-12, hidden_act="gelu", position_embedding_type="absolute")
+TINY_BERT = dict(architectures=["BertModel"], hidden_size=256, intermediate_size=512, num_attention_heads=4,
+                 num_hidden_layers=2, vocab_size=1000, max_position_embeddings=128, type_vocab_size=2,
+                 layer_norm_eps=1e-12, hidden_act="gelu", position_embedding_type="absolute")
+
+
+def encoder_parameter_shapes(config: dict) -> list[tuple[str, tuple[int, ...]]]:
+    """BertModel tensor names and shapes in state-dict order (the draw order)."""
+    hidden, inter = config["hidden_size"], config["intermediate_size"]
+    shapes = [("embeddings.word_embeddings.weight", (config["vocab_size"], hidden)),
+              ("embeddings.position_embeddings.weight", (config["max_position_embeddings"], hidden)),
+              ("embeddings.token_type_embeddings.weight", (config["type_vocab_size"], hidden)),
+              ("embeddings.LayerNorm.weight", (hidden,)), ("embeddings.LayerNorm.bias", (hidden,))]
+    for layer in range(config["num_hidden_layers"]):
+        p = f"encoder.layer.{layer}."
+        for part in ("query", "key", "value"):
+            shapes += [(p + f"attention.self.{part}.weight", (hidden, hidden)), (p + f"attention.self.{part}.bias", (hidden,))]
+        shapes += [(p + "attention.output.dense.weight", (hidden, hidden)), (p + "attention.output.dense.bias", (hidden,)),
+                   (p + "attention.output.LayerNorm.weight", (hidden,)), (p + "attention.output.LayerNorm.bias", (hidden,)),
+                   (p + "intermediate.dense.weight", (inter, hidden)), (p + "intermediate.dense.bias", (inter,)),
+                   (p + "output.dense.weight", (hidden, inter)), (p + "output.dense.bias", (hidden,)),
+                   (p + "output.LayerNorm.weight", (hidden,)), (p + "output.LayerNorm.bias", (hidden,))]
+    return shapes + [("pooler.dense.weight", (hidden, hidden)), ("pooler.dense.bias", (hidden,))]
+
+
+def encoder_weights(config: dict, seed: int = 0) -> dict[str, torch.Tensor]:
+    """Seeded N(0, 0.02) draws for every tensor (LayerNorm weights 1 + the draw, so that every scale and bias of
+    the forward pass is exercised), fp32."""
+    generator = torch.Generator().manual_seed(seed)
+    tensors = {}
+    for name, shape in encoder_parameter_shapes(config):
+        draw = torch.randn(shape, generator=generator, dtype=torch.float32) * 0.02
+        tensors[name] = 1.0 + draw if name.endswith("LayerNorm.weight") else draw
+    return tensors
+
+
+def encoder_inputs(config: dict, batch: int, seq: int = 128, seed: int = 1) -> tuple[torch.Tensor, torch.Tensor]:
+    """Token ids uniform in [0, vocab) and segment ids in [0, type_vocab), int64 [batch, seq]."""
+    generator = torch.Generator().manual_seed(seed)
+    ids = torch.randint(0, config["vocab_size"], (batch, seq), generator=generator, dtype=torch.int64)
+    types = torch.randint(0, config["type_vocab_size"], (batch, seq), generator=generator, dtype=torch.int64)
+    return ids, types
