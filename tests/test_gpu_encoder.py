@@ -68,7 +68,7 @@ def test_tiny_encoder_matches_the_module_fixture(plan_dir):
 @pytest.mark.parametrize("batch,dtype_name", [(1, "f16"), (8, "f16"), (8, "bf16")])
 def test_bert_base_shape_matches_the_oracle(batch, dtype_name, plan_dir):
     """The benchmark's shapes: 12 layers, hidden 768, 12 heads, FFN 3072, vocabulary 30522, batch x 128 tokens
-    (batch 1: 32-row weight tiles and K split in up to 6; batch 8: 128-row tiles)."""
+    (batch 1: 32-row weight tiles and K split in 4; batch 8: 128-row tiles, K split in 2)."""
     run_case(synthetic.BERT_BASE, batch, dtype_name, plan_dir, seed=20)
 
 

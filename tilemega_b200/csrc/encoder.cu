@@ -16,6 +16,7 @@
 #include <stdint.h>
 
 #include <algorithm>
+#include <cstdlib>
 #include <string>
 #include <vector>
 
@@ -69,6 +70,17 @@ template <typename T> __device__ __forceinline__ void unpack4(const uint2& v, fl
   f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
 }
 
+// ---- programmatic dependent launch ---------------------------------------------------------------------------
+// Every kernel of the pass is launched as a programmatic dependent of the one before it: it may start (and run its
+// prologue: barriers, tensor-memory allocation, descriptor prefetch) while its predecessor drains, and reads or writes
+// global memory only after dependency_wait(), which returns once the predecessor grid has completed and its writes
+// are visible. allow_dependents() lets the successor start as soon as every CTA of this grid has issued it.
+__device__ __forceinline__ void allow_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void prefetch_map(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
+
 // ---- bounded waits -------------------------------------------------------------------------------------------
 // Wait for a phase of an mbarrier, but not for ever: after kWaitLimitNs (or once another wait of the launch
 // has given up) the caller gets `false`, leaves its loop and the kernel runs to its end. status[0] keeps the
@@ -110,9 +122,10 @@ template <int BN> struct GemmShape {
 
 // C[128 x BN tile] = A[rows x K] (tokens, K-major) * W[N x K]^T (nn.Linear layout, K-major), fp32 in tensor memory.
 // blockIdx = (n tile, m tile, K split). Warp 0: TMA producer. Warp 1: tensor-memory owner and MMA issuer.
-// Warps 2..5: epilogue, each on the 32 lanes its warp id modulo 4 may read.
+// Warps 2..9: epilogue, each on the 32 lanes its warp id modulo 4 may read and on one half of the tile's columns.
+constexpr int kGemmThreads = 320;
 template <typename T, int BN, int EPI>
-__global__ void __launch_bounds__(192) encoder_gemm(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap wmap0,
+__global__ void __launch_bounds__(kGemmThreads) encoder_gemm(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap wmap0,
                                                     const __grid_constant__ CUtensorMap wmap1, const __grid_constant__ CUtensorMap wmap2,
                                                     const GemmArgs g) {
   using Shape = GemmShape<BN>;
@@ -129,7 +142,10 @@ __global__ void __launch_bounds__(192) encoder_gemm(const __grid_constant__ CUte
   const int which = n0 / g.n_per_map, nm = n0 - which * g.n_per_map;   // weight map and the row inside it
   const CUtensorMap* wmap = which == 0 ? &wmap0 : which == 1 ? &wmap1 : &wmap2;
 
+  allow_dependents();
   if (threadIdx.x == 0) {
+    prefetch_map(&amap);
+    prefetch_map(wmap);
     for (int s = 0; s < S; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
@@ -142,6 +158,7 @@ __global__ void __launch_bounds__(192) encoder_gemm(const __grid_constant__ CUte
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem = *tmem_slot;
+  dependency_wait();   // from here on the activations of the kernel before this one may be read, and outputs written
 
   if (warp == 0) {
     if (lane == 0) {
@@ -180,11 +197,11 @@ __global__ void __launch_bounds__(192) encoder_gemm(const __grid_constant__ CUte
   } else {
     const bool ok = wait_bounded(accum, 0, g.status, 4);
     tcgen05_fence_after();
-    const int quarter = warp & 3;
+    const int quarter = warp & 3, column_half = (warp - 2) >> 2;
     const int row = m0 + 32 * quarter + lane;
     if (ok) {
 #pragma unroll 1
-      for (int c = 0; c < BN / 16; ++c) {
+      for (int c = column_half * (BN / 32); c < (column_half + 1) * (BN / 32); ++c) {
         float v[16];
         tmem_load_16(tmem + (uint32_t(32 * quarter) << 16) + uint32_t(c * 16), v);
         if (EPI == kEpiPartial) {
@@ -222,6 +239,7 @@ __global__ void __launch_bounds__(192) encoder_gemm(const __grid_constant__ CUte
 
 // ---- LayerNorm stages ----------------------------------------------------------------------------------------
 constexpr int kMaxGroups = 8;   // hidden <= 32 lanes x 4 columns x 8 groups = 1024
+constexpr int kMaxSplits = 4;   // partial slabs of a projection whose K is split
 
 // LayerNorm of one row held as groups of 4 columns per lane: v[g][i] = column (g * 32 + lane) * 4 + i.
 template <typename T>
@@ -266,6 +284,8 @@ __global__ void __launch_bounds__(256) encoder_embed(const long long* ids, const
                                                      const T* segment, const T* gamma, const T* beta, T* out, int rows, int seq,
                                                      int hidden, int vocab, int segments, float eps) {
   const int row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  allow_dependents();
+  dependency_wait();
   if (row >= rows) return;
   long long id = ids[row], ty = types[row];
   id = id < 0 ? 0 : id >= vocab ? vocab - 1 : id;          // an id outside the table reads its nearest row
@@ -289,10 +309,12 @@ __global__ void __launch_bounds__(256) encoder_embed(const long long* ids, const
 // Sum of a projection's partial slabs (in slab order: the result does not depend on the schedule) + bias + the
 // residual row, then LayerNorm (BertSelfOutput / BertOutput). One warp per token.
 template <typename T>
-__global__ void __launch_bounds__(256) encoder_add_norm(const float* parts, int nparts, unsigned long long part_stride, const T* bias,
+__global__ void __launch_bounds__(128) encoder_add_norm(const float* parts, int nparts, unsigned long long part_stride, const T* bias,
                                                         const T* residual, const T* gamma, const T* beta, T* out, int rows, int hidden,
                                                         float eps) {
-  const int row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  allow_dependents();
+  dependency_wait();
   if (row >= rows) return;
   const int groups = hidden / 128;
   float v[kMaxGroups][4];
@@ -300,11 +322,17 @@ __global__ void __launch_bounds__(256) encoder_add_norm(const float* parts, int 
   for (int g = 0; g < kMaxGroups; ++g)
     if (g < groups) {
       const int col = (g * 32 + lane) * 4;
-      float4 acc = *reinterpret_cast<const float4*>(parts + size_t(row) * hidden + col);
-      for (int s = 1; s < nparts; ++s) {
-        const float4 more = *reinterpret_cast<const float4*>(parts + size_t(s) * part_stride + size_t(row) * hidden + col);
-        acc.x += more.x; acc.y += more.y; acc.z += more.z; acc.w += more.w;
-      }
+      // every slab's load goes out before the first sum (the slabs are added in slab order)
+      float4 slab[kMaxSplits];
+#pragma unroll
+      for (int s = 0; s < kMaxSplits; ++s)
+        if (s < nparts) slab[s] = __ldcs(reinterpret_cast<const float4*>(parts + size_t(s) * part_stride + size_t(row) * hidden + col));
+      float4 acc = slab[0];
+#pragma unroll
+      for (int s = 1; s < kMaxSplits; ++s)
+        if (s < nparts) {
+          acc.x += slab[s].x; acc.y += slab[s].y; acc.z += slab[s].z; acc.w += slab[s].w;
+        }
       float b[4], r[4];
       unpack4<T>(__ldg(reinterpret_cast<const uint2*>(bias + col)), b);
       unpack4<T>(*reinterpret_cast<const uint2*>(residual + size_t(row) * hidden + col), r);
@@ -334,23 +362,34 @@ template <> __device__ __forceinline__ void mma_16816<__nv_bfloat16>(float (&d)[
 __device__ __forceinline__ uint32_t tile_addr(uint32_t base, int row, int chunk) { return base + row * 128 + ((chunk ^ (row & 7)) << 4); }
 
 // Bidirectional attention of one (sequence, head) over 128 positions, no mask (the all-ones mask of the workload):
-// softmax(Q K^T / sqrt(64)) V. A CTA takes 64 query rows (4 warps x 16) against all 128 keys; scores, softmax and
-// the probability operand stay in registers.
+// softmax(Q K^T / sqrt(64)) V. A CTA takes the 128 query rows (8 warps x 16) against the 128 keys; scores, softmax
+// and the probability operand stay in registers.
 template <typename T>
-__global__ void __launch_bounds__(128) encoder_attention(const T* qkv, T* ctx, int heads, int hidden, float scale_log2) {
-  __shared__ __align__(128) unsigned char ks[kSeq * 128], vs[kSeq * 128], qs[64 * 128];
-  const int half = blockIdx.x & 1, bh = blockIdx.x >> 1, head = bh % heads, seq = bh / heads;
+__global__ void __launch_bounds__(256) encoder_attention(const T* qkv, T* ctx, int heads, int hidden, float scale_log2) {
+  __shared__ __align__(128) unsigned char ks[kSeq * 128], vs[kSeq * 128], qs[kSeq * 128];
+  const int head = blockIdx.x % heads, seq = blockIdx.x / heads;
   const int ld = 3 * hidden, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const T* base = qkv + size_t(seq) * kSeq * ld + head * kHeadDim;
-  for (int i = threadIdx.x; i < kSeq * 8; i += 128) {
-    const int r = i >> 3, ch = i & 7, at = r * 128 + ((ch ^ (r & 7)) << 4);
-    *reinterpret_cast<uint4*>(ks + at) = *reinterpret_cast<const uint4*>(base + size_t(r) * ld + hidden + ch * 8);
-    *reinterpret_cast<uint4*>(vs + at) = *reinterpret_cast<const uint4*>(base + size_t(r) * ld + 2 * hidden + ch * 8);
-  }
-  for (int i = threadIdx.x; i < 64 * 8; i += 128) {
-    const int r = i >> 3, ch = i & 7;
-    *reinterpret_cast<uint4*>(qs + r * 128 + ((ch ^ (r & 7)) << 4)) =
-        *reinterpret_cast<const uint4*>(base + size_t(half * 64 + r) * ld + ch * 8);
+  allow_dependents();
+  dependency_wait();
+  {
+    // 128 rows x 8 sixteen-byte chunks of q, k and v: four chunks of each per thread, all twelve loads in flight
+    uint4 qv[4], kv[4], vv[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int i = threadIdx.x + j * 256, r = i >> 3, ch = i & 7;
+      const T* row = base + size_t(r) * ld + ch * 8;
+      qv[j] = *reinterpret_cast<const uint4*>(row);
+      kv[j] = *reinterpret_cast<const uint4*>(row + hidden);
+      vv[j] = *reinterpret_cast<const uint4*>(row + 2 * hidden);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int i = threadIdx.x + j * 256, r = i >> 3, ch = i & 7, at = r * 128 + ((ch ^ (r & 7)) << 4);
+      *reinterpret_cast<uint4*>(qs + at) = qv[j];
+      *reinterpret_cast<uint4*>(ks + at) = kv[j];
+      *reinterpret_cast<uint4*>(vs + at) = vv[j];
+    }
   }
   __syncthreads();
   const uint32_t kbase = smem_u32(ks), vbase = smem_u32(vs), qbase = smem_u32(qs);
@@ -418,7 +457,7 @@ __global__ void __launch_bounds__(128) encoder_attention(const T* qkv, T* ctx, i
     }
   }
   const float inv_lo = 1.0f / sum_lo, inv_hi = 1.0f / sum_hi;
-  T* out = ctx + (size_t(seq) * kSeq + half * 64 + warp * 16 + (lane >> 2)) * hidden + head * kHeadDim + 2 * (lane & 3);
+  T* out = ctx + (size_t(seq) * kSeq + warp * 16 + (lane >> 2)) * hidden + head * kHeadDim + 2 * (lane & 3);
 #pragma unroll
   for (int t = 0; t < 8; ++t) {
     *reinterpret_cast<uint32_t*>(out + t * 8) = Num<T>::pack(o[t][0] * inv_lo, o[t][1] * inv_lo);
@@ -431,6 +470,8 @@ __global__ void __launch_bounds__(128) encoder_attention(const T* qkv, T* ctx, i
 template <typename T>
 __global__ void __launch_bounds__(256) encoder_pooler(const T* hidden_out, const T* weight, const T* bias, T* out, int seq, int hidden) {
   const int n = blockIdx.x * 8 + (threadIdx.x >> 5), b = blockIdx.y, lane = threadIdx.x & 31;
+  allow_dependents();
+  dependency_wait();
   if (n >= hidden) return;
   const T* x = hidden_out + size_t(b) * seq * hidden;
   const T* w = weight + size_t(n) * hidden;
@@ -454,6 +495,7 @@ struct GemmLaunch {
   GemmArgs args;
   dim3 grid;
   int bn, epilogue;
+  bool dependent;
 };
 
 struct EncoderPlan {
@@ -465,6 +507,7 @@ struct EncoderPlan {
   cudaGraph_t graph = nullptr;
   cudaGraphExec_t exec = nullptr;
   int kernels = 0;
+  bool chained = true;   // kernels recorded as programmatic dependents of one another
 };
 
 namespace {
@@ -500,12 +543,27 @@ bool EncodeMatrix(CUtensorMap* map, bool f16, const void* base, uint64_t rows, u
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// One kernel launch; `dependent`: as a programmatic dependent of the launch before it on the stream.
+template <typename... Params, typename... Args>
+cudaError_t Launch(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, bool dependent, Args&&... args) {
+  cudaLaunchConfig_t config{};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute{};
+  attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute.val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = dependent ? &attribute : nullptr;
+  config.numAttrs = dependent ? 1 : 0;
+  return cudaLaunchKernelEx(&config, kernel, std::forward<Args>(args)...);
+}
+
 template <typename T, int BN, int EPI> cudaError_t LaunchGemmAs(const GemmLaunch& l, cudaStream_t stream) {
   auto kernel = encoder_gemm<T, BN, EPI>;
   if (!stream)   // preparation pass (before the recording starts): only raise the kernel's shared-memory limit
     return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmShape<BN>::kSmem);
-  kernel<<<l.grid, 192, GemmShape<BN>::kSmem, stream>>>(l.amap, l.wmap[0], l.wmap[1], l.wmap[2], l.args);
-  return cudaGetLastError();
+  return Launch(kernel, l.grid, dim3(kGemmThreads), GemmShape<BN>::kSmem, stream, l.dependent, l.amap, l.wmap[0], l.wmap[1], l.wmap[2], l.args);
 }
 
 template <typename T, int BN> cudaError_t LaunchGemmTile(const GemmLaunch& l, cudaStream_t stream) {
@@ -524,24 +582,28 @@ template <typename T> cudaError_t LaunchGemm(const GemmLaunch& l, cudaStream_t s
   }
 }
 
-// Tile width and K split of one projection: the widest weight tile that still gives every SM a CTA; a projection
-// that ends in the add + LayerNorm stage may also split K (its partial slabs are summed there, in slab order).
+// Tile width and K split of one projection. Wide weight tiles re-read the token tile less often from L2, so the
+// widest tile that still gives three quarters of the SMs a CTA wins; a projection that ends in the add + LayerNorm
+// stage may instead split K in up to kMaxSplits parts (its partial slabs are summed there, in slab order), and
+// takes the fewest parts that occupy half of the SMs.
 void ChooseTiling(int rows, int n, int k, int sm_count, bool may_split, int* bn, int* splits) {
-  const int mtiles = rows / kTileM;
+  const int mtiles = rows / kTileM, chunks = k / kTileK;
+  int widest_split = 1;
+  if (may_split)
+    for (int candidate = 1; candidate <= kMaxSplits; ++candidate)
+      if (chunks % candidate == 0) widest_split = candidate;
+  const int wanted = may_split ? sm_count / 2 : sm_count * 3 / 4;
   *bn = 32;
   for (int candidate : {128, 64, 32})
-    if (mtiles * (n / candidate) >= sm_count) {
+    if (mtiles * (n / candidate) * widest_split >= wanted) {
       *bn = candidate;
       break;
     }
   *splits = 1;
-  if (may_split) {
-    const int chunks = k / kTileK;
-    for (int candidate : {1, 2, 3, 4, 6}) {
-      if (chunks % candidate) continue;
-      *splits = candidate;
-      if (mtiles * (n / *bn) * candidate >= sm_count) break;
-    }
+  for (int candidate = 1; candidate <= widest_split; ++candidate) {
+    if (chunks % candidate) continue;
+    *splits = candidate;
+    if (mtiles * (n / *bn) * candidate >= wanted) break;
   }
 }
 
@@ -552,7 +614,7 @@ template <typename T> cudaError_t PrepareGemms() {
     for (int epilogue : {int(kEpiBias), int(kEpiBiasGelu), int(kEpiPartial)}) {
       l.bn = bn;
       l.epilogue = epilogue;
-      const cudaError_t err = LaunchGemm<T>(l, nullptr);
+      const cudaError_t err = LaunchGemm<T>(l, nullptr);   // a null stream means: prepare only
       if (err != cudaSuccess) return err;
     }
   return cudaSuccess;
@@ -565,7 +627,7 @@ int Find(const PlanSpec& spec, const std::string& name) {
 }
 
 template <typename T> cudaError_t Enqueue(EncoderPlan& plan, const PlanSpec& spec, const std::vector<void*>& buffers, int sm_count,
-                                         float* parts, cudaStream_t stream, std::string* error) {
+                                         float* parts, cudaStream_t stream, bool chained, std::string* error) {
   auto at = [&](const std::string& name) -> void* {
     const int index = Find(spec, name);
     if (index < 0) {
@@ -595,13 +657,13 @@ template <typename T> cudaError_t Enqueue(EncoderPlan& plan, const PlanSpec& spe
   TMB_AT(pool_b, "pooler.dense.bias")
   cudaError_t err = cudaSuccess;
   plan.kernels = 0;
-  encoder_embed<T><<<(rows + 7) / 8, 256, 0, stream>>>(static_cast<const long long*>(ids), static_cast<const long long*>(types),
-                                                      static_cast<const T*>(word), static_cast<const T*>(position),
-                                                      static_cast<const T*>(segment), static_cast<const T*>(embed_gamma),
-                                                      static_cast<const T*>(embed_beta), static_cast<T*>(x), rows, plan.seq, hidden,
-                                                      plan.vocab, plan.segments, plan.eps);
+  // the first kernel of the pass is an ordinary launch: it follows whatever the caller's stream ran before
+  err = Launch(encoder_embed<T>, dim3(unsigned((rows + 7) / 8)), dim3(256), 0, stream, false, static_cast<const long long*>(ids),
+               static_cast<const long long*>(types), static_cast<const T*>(word), static_cast<const T*>(position),
+               static_cast<const T*>(segment), static_cast<const T*>(embed_gamma), static_cast<const T*>(embed_beta), static_cast<T*>(x),
+               rows, plan.seq, hidden, plan.vocab, plan.segments, plan.eps);
   ++plan.kernels;
-  if ((err = cudaGetLastError()) != cudaSuccess) return err;
+  if (err != cudaSuccess) return err;
 
   // one projection: A = activation [rows][k], up to three weight matrices of n_per_map rows each
   auto gemm = [&](const void* a, int k, const void* const (&w)[3], const void* const (&bias)[3], int n, int n_per_map, int epilogue,
@@ -627,17 +689,17 @@ template <typename T> cudaError_t Enqueue(EncoderPlan& plan, const PlanSpec& spe
     l.args.status = plan.status;
     l.grid = dim3(unsigned(n / l.bn), unsigned(rows / kTileM), unsigned(splits));
     l.epilogue = epilogue;
+    l.dependent = chained;
     ++plan.kernels;
     return LaunchGemm<T>(l, stream);
   };
   auto add_norm = [&](int k, const void* bias, const void* gamma, const void* beta, void* out) -> cudaError_t {
     int bn = 0, splits = 1;
     ChooseTiling(rows, hidden, k, sm_count, true, &bn, &splits);   // the slab count the projection before it wrote
-    encoder_add_norm<T><<<(rows + 7) / 8, 256, 0, stream>>>(parts, splits, (unsigned long long)(rows) * hidden, static_cast<const T*>(bias),
-                                                           static_cast<const T*>(x), static_cast<const T*>(gamma),
-                                                           static_cast<const T*>(beta), static_cast<T*>(out), rows, hidden, plan.eps);
     ++plan.kernels;
-    return cudaGetLastError();
+    return Launch(encoder_add_norm<T>, dim3(unsigned((rows + 3) / 4)), dim3(128), 0, stream, chained, static_cast<const float*>(parts), splits,
+                  (unsigned long long)(rows) * hidden, static_cast<const T*>(bias), static_cast<const T*>(x), static_cast<const T*>(gamma),
+                  static_cast<const T*>(beta), static_cast<T*>(out), rows, hidden, plan.eps);
   };
   const float scale_log2 = 1.4426950408889634f / 8.0f;   // log2(e) / sqrt(64)
   for (int layer = 0; layer < plan.layers; ++layer) {
@@ -663,10 +725,10 @@ template <typename T> cudaError_t Enqueue(EncoderPlan& plan, const PlanSpec& spe
       const void* const b[3] = {bq, bk, bv};
       if ((err = gemm(x, hidden, w, b, 3 * hidden, hidden, kEpiBias, qkv)) != cudaSuccess) return err;
     }
-    encoder_attention<T><<<plan.batch * plan.heads * 2, 128, 0, stream>>>(static_cast<const T*>(qkv), static_cast<T*>(ctx), plan.heads,
-                                                                         hidden, scale_log2);
+    err = Launch(encoder_attention<T>, dim3(unsigned(plan.batch * plan.heads)), dim3(256), 0, stream, chained, static_cast<const T*>(qkv),
+                 static_cast<T*>(ctx), plan.heads, hidden, scale_log2);
     ++plan.kernels;
-    if ((err = cudaGetLastError()) != cudaSuccess) return err;
+    if (err != cudaSuccess) return err;
     {
       const void* const w[3] = {wo, wo, wo};
       const void* const b[3] = {bo, bo, bo};
@@ -686,12 +748,11 @@ template <typename T> cudaError_t Enqueue(EncoderPlan& plan, const PlanSpec& spe
     // the last layer's LayerNorm writes the caller's output buffer
     if ((err = add_norm(inter, bd, g2, b2, layer + 1 == plan.layers ? last_hidden : x)) != cudaSuccess) return err;
   }
-  encoder_pooler<T><<<dim3(unsigned((hidden + 7) / 8), unsigned(plan.batch)), 256, 0, stream>>>(
-      static_cast<const T*>(last_hidden), static_cast<const T*>(pool_w), static_cast<const T*>(pool_b), static_cast<T*>(pooled), plan.seq,
-      hidden);
   ++plan.kernels;
 #undef TMB_AT
-  return cudaGetLastError();
+  return Launch(encoder_pooler<T>, dim3(unsigned((hidden + 7) / 8), unsigned(plan.batch)), dim3(256), 0, stream, chained,
+                static_cast<const T*>(last_hidden), static_cast<const T*>(pool_w), static_cast<const T*>(pool_b), static_cast<T*>(pooled),
+                plan.seq, hidden);
 }
 
 }  // namespace
@@ -715,9 +776,9 @@ EncoderPlan* EncoderCreate(const PlanSpec& spec, int batch, const std::vector<vo
     return nullptr;
   };
   if (!TensorMapEncoder()) return fail("the driver does not offer cuTensorMapEncodeTiled");
-  // partial slabs of the two projections that end in add + LayerNorm: at most 6 slabs of rows x hidden fp32
+  // partial slabs of the two projections that end in add + LayerNorm: at most kMaxSplits slabs of rows x hidden fp32
   void* parts = nullptr;
-  if (cudaMalloc(&parts, size_t(6) * plan->rows * plan->hidden * sizeof(float)) != cudaSuccess) return fail("no device memory for the partial sums");
+  if (cudaMalloc(&parts, size_t(kMaxSplits) * plan->rows * plan->hidden * sizeof(float)) != cudaSuccess) return fail("no device memory for the partial sums");
   plan->owned.push_back(parts);
   void* status = nullptr;
   if (cudaMalloc(&status, 64) != cudaSuccess || cudaMemset(status, 0, 64) != cudaSuccess) return fail("no device memory for the status words");
@@ -727,10 +788,13 @@ EncoderPlan* EncoderCreate(const PlanSpec& spec, int batch, const std::vector<vo
   if ((spec.f16 ? PrepareGemms<__half>() : PrepareGemms<__nv_bfloat16>()) != cudaSuccess) return fail("cannot raise the GEMM kernels' shared-memory limit");
   cudaStream_t recorder = nullptr;
   if (cudaStreamCreateWithFlags(&recorder, cudaStreamNonBlocking) != cudaSuccess) return fail("cannot create the recording stream");
+  // TILEMEGA_ENCODER_CHAIN=0 records plain launches (each kernel starts when the one before it has ended)
+  const char* chain = std::getenv("TILEMEGA_ENCODER_CHAIN");
+  plan->chained = !(chain && chain[0] == '0');
   cudaError_t err = cudaStreamBeginCapture(recorder, cudaStreamCaptureModeThreadLocal);
   if (err == cudaSuccess) {
-    err = spec.f16 ? Enqueue<__half>(*plan, spec, buffers, sm_count, static_cast<float*>(parts), recorder, error)
-                   : Enqueue<__nv_bfloat16>(*plan, spec, buffers, sm_count, static_cast<float*>(parts), recorder, error);
+    err = spec.f16 ? Enqueue<__half>(*plan, spec, buffers, sm_count, static_cast<float*>(parts), recorder, plan->chained, error)
+                   : Enqueue<__nv_bfloat16>(*plan, spec, buffers, sm_count, static_cast<float*>(parts), recorder, plan->chained, error);
     const cudaError_t ended = cudaStreamEndCapture(recorder, &plan->graph);
     if (err == cudaSuccess) err = ended;
   }
