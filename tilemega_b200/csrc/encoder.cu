@@ -112,8 +112,10 @@ struct GemmArgs {
   unsigned* status;
 };
 
-template <int BN> struct GemmShape {
-  static constexpr int kStages = BN >= 128 ? 3 : BN == 64 ? 4 : 5;     // about 100 KB: two CTAs share an SM
+template <int BN, bool DEEP = false> struct GemmShape {
+  // about 100 KB of stages, so that two CTAs share an SM; the deep form (32-row weight tiles in a grid of at most one
+  // CTA per SM) has ten stages, which puts nearly a whole K = 768 reduction in flight at once
+  static constexpr int kStages = DEEP ? 10 : BN >= 128 ? 3 : BN == 64 ? 4 : 5;
   static constexpr int kBBytes = BN * kTileK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kSmem = kStages * kStageBytes + 1024 /* alignment */ + 256 /* barriers */;
@@ -124,11 +126,11 @@ template <int BN> struct GemmShape {
 // blockIdx = (n tile, m tile, K split). Warp 0: TMA producer. Warp 1: tensor-memory owner and MMA issuer.
 // Warps 2..9: epilogue, each on the 32 lanes its warp id modulo 4 may read and on one half of the tile's columns.
 constexpr int kGemmThreads = 320;
-template <typename T, int BN, int EPI>
+template <typename T, int BN, int EPI, bool DEEP>
 __global__ void __launch_bounds__(kGemmThreads) encoder_gemm(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap wmap0,
                                                     const __grid_constant__ CUtensorMap wmap1, const __grid_constant__ CUtensorMap wmap2,
                                                     const GemmArgs g) {
-  using Shape = GemmShape<BN>;
+  using Shape = GemmShape<BN, DEEP>;
   constexpr int S = Shape::kStages;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -158,6 +160,13 @@ __global__ void __launch_bounds__(kGemmThreads) encoder_gemm(const __grid_consta
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem = *tmem_slot;
+  // weights do not depend on the kernel before this one: the first stages' weight tiles are requested at once
+  const int early = g.kchunks < S ? g.kchunks : S;
+  if (threadIdx.x == 0)
+    for (int c = 0; c < early; ++c) {
+      mbar_expect_tx(&full[c], Shape::kStageBytes);
+      tma_load_2d(tiles + c * Shape::kStageBytes + kABytes, wmap, (k0 + c) * kTileK, nm, &full[c]);
+    }
   dependency_wait();   // from here on the activations of the kernel before this one may be read, and outputs written
 
   if (warp == 0) {
@@ -169,9 +178,11 @@ __global__ void __launch_bounds__(kGemmThreads) encoder_gemm(const __grid_consta
         if (c >= S) ok = wait_bounded(&empty[s], uint32_t((c / S) - 1) & 1u, g.status, 1);
         if (!ok) break;
         unsigned char* a = tiles + s * Shape::kStageBytes;
-        mbar_expect_tx(&full[s], Shape::kStageBytes);
+        if (c >= early) {   // (the first stages' barriers were armed, and their weight tiles requested, above)
+          mbar_expect_tx(&full[s], Shape::kStageBytes);
+          tma_load_2d(a + kABytes, wmap, (k0 + c) * kTileK, nm, &full[s]);
+        }
         tma_load_2d(a, &amap, (k0 + c) * kTileK, m0, &full[s]);
-        tma_load_2d(a + kABytes, wmap, (k0 + c) * kTileK, nm, &full[s]);
         issued = c + 1;
       }
       if (!ok)   // leaving early: first let the copies already issued land in this CTA's shared memory
@@ -495,7 +506,7 @@ struct GemmLaunch {
   GemmArgs args;
   dim3 grid;
   int bn, epilogue;
-  bool dependent;
+  bool dependent, deep;
 };
 
 struct EncoderPlan {
@@ -559,18 +570,18 @@ cudaError_t Launch(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem
   return cudaLaunchKernelEx(&config, kernel, std::forward<Args>(args)...);
 }
 
-template <typename T, int BN, int EPI> cudaError_t LaunchGemmAs(const GemmLaunch& l, cudaStream_t stream) {
-  auto kernel = encoder_gemm<T, BN, EPI>;
+template <typename T, int BN, int EPI, bool DEEP = false> cudaError_t LaunchGemmAs(const GemmLaunch& l, cudaStream_t stream) {
+  auto kernel = encoder_gemm<T, BN, EPI, DEEP>;
   if (!stream)   // preparation pass (before the recording starts): only raise the kernel's shared-memory limit
-    return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmShape<BN>::kSmem);
-  return Launch(kernel, l.grid, dim3(kGemmThreads), GemmShape<BN>::kSmem, stream, l.dependent, l.amap, l.wmap[0], l.wmap[1], l.wmap[2], l.args);
+    return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmShape<BN, DEEP>::kSmem);
+  return Launch(kernel, l.grid, dim3(kGemmThreads), GemmShape<BN, DEEP>::kSmem, stream, l.dependent, l.amap, l.wmap[0], l.wmap[1], l.wmap[2], l.args);
 }
 
-template <typename T, int BN> cudaError_t LaunchGemmTile(const GemmLaunch& l, cudaStream_t stream) {
+template <typename T, int BN, bool DEEP = false> cudaError_t LaunchGemmTile(const GemmLaunch& l, cudaStream_t stream) {
   switch (l.epilogue) {
-    case kEpiBias: return LaunchGemmAs<T, BN, kEpiBias>(l, stream);
-    case kEpiBiasGelu: return LaunchGemmAs<T, BN, kEpiBiasGelu>(l, stream);
-    default: return LaunchGemmAs<T, BN, kEpiPartial>(l, stream);
+    case kEpiBias: return LaunchGemmAs<T, BN, kEpiBias, DEEP>(l, stream);
+    case kEpiBiasGelu: return LaunchGemmAs<T, BN, kEpiBiasGelu, DEEP>(l, stream);
+    default: return LaunchGemmAs<T, BN, kEpiPartial, DEEP>(l, stream);
   }
 }
 
@@ -578,7 +589,7 @@ template <typename T> cudaError_t LaunchGemm(const GemmLaunch& l, cudaStream_t s
   switch (l.bn) {
     case 128: return LaunchGemmTile<T, 128>(l, stream);
     case 64: return LaunchGemmTile<T, 64>(l, stream);
-    default: return LaunchGemmTile<T, 32>(l, stream);
+    default: return l.deep ? LaunchGemmTile<T, 32, true>(l, stream) : LaunchGemmTile<T, 32>(l, stream);
   }
 }
 
@@ -586,13 +597,21 @@ template <typename T> cudaError_t LaunchGemm(const GemmLaunch& l, cudaStream_t s
 // widest tile that still gives three quarters of the SMs a CTA wins; a projection that ends in the add + LayerNorm
 // stage may instead split K in up to kMaxSplits parts (its partial slabs are summed there, in slab order), and
 // takes the fewest parts that occupy half of the SMs.
+#ifndef TMB_ENCODER_WANTED_PLAIN
+#define TMB_ENCODER_WANTED_PLAIN 100
+#endif
+#ifndef TMB_ENCODER_WANTED_SPLIT
+#define TMB_ENCODER_WANTED_SPLIT 100
+#endif
+constexpr int kWantedPlainPercent = TMB_ENCODER_WANTED_PLAIN, kWantedSplitPercent = TMB_ENCODER_WANTED_SPLIT;
+
 void ChooseTiling(int rows, int n, int k, int sm_count, bool may_split, int* bn, int* splits) {
   const int mtiles = rows / kTileM, chunks = k / kTileK;
   int widest_split = 1;
   if (may_split)
     for (int candidate = 1; candidate <= kMaxSplits; ++candidate)
       if (chunks % candidate == 0) widest_split = candidate;
-  const int wanted = may_split ? sm_count / 2 : sm_count * 3 / 4;
+  const int wanted = sm_count * (may_split ? kWantedSplitPercent : kWantedPlainPercent) / 100;
   *bn = 32;
   for (int candidate : {128, 64, 32})
     if (mtiles * (n / candidate) * widest_split >= wanted) {
@@ -610,9 +629,10 @@ void ChooseTiling(int rows, int n, int k, int sm_count, bool may_split, int* bn,
 // Every instantiation a plan of this element type may launch gets its dynamic shared-memory limit raised.
 template <typename T> cudaError_t PrepareGemms() {
   GemmLaunch l{};
-  for (int bn : {128, 64, 32})
+  for (int form = 0; form < 4; ++form)
     for (int epilogue : {int(kEpiBias), int(kEpiBiasGelu), int(kEpiPartial)}) {
-      l.bn = bn;
+      l.bn = form == 0 ? 128 : form == 1 ? 64 : 32;
+      l.deep = form == 3;
       l.epilogue = epilogue;
       const cudaError_t err = LaunchGemm<T>(l, nullptr);   // a null stream means: prepare only
       if (err != cudaSuccess) return err;
@@ -689,6 +709,7 @@ template <typename T> cudaError_t Enqueue(EncoderPlan& plan, const PlanSpec& spe
     l.args.status = plan.status;
     l.grid = dim3(unsigned(n / l.bn), unsigned(rows / kTileM), unsigned(splits));
     l.epilogue = epilogue;
+    l.deep = l.bn == 32 && int(l.grid.x * l.grid.y * l.grid.z) <= sm_count;
     l.dependent = chained;
     ++plan.kernels;
     return LaunchGemm<T>(l, stream);
