@@ -2,8 +2,9 @@
 // attention over 128 positions, output projection + residual + LayerNorm, GELU FFN + residual + LayerNorm, and the
 // pooler) over batch x 128 tokens. The four projections of a layer are one GEMM kernel on the 5th-generation
 // tensor cores: token tiles (128 rows) and weight tiles (32..128 rows) arrive in shared memory through TMA tensor
-// maps with the 128-byte swizzle, one thread issues tcgen05.mma into a tensor-memory accumulator, four warps read
-// it back with tcgen05.ld for the epilogue. A forward pass is ONE CUDA graph of these kernels.
+// maps with the 128-byte swizzle, one thread issues tcgen05.mma into a tensor-memory accumulator, eight warps read
+// it back with tcgen05.ld for the epilogue. A forward pass is ONE CUDA graph of these kernels, each recorded as a
+// programmatic dependent of the one before it.
 //
 // What the reference does for this path: include/tilemega/Codegen/tasks/Sm90F3Program.cuh:690-732 (one persistent
 // wgmma kernel over a compile-time stage list), Backend/Sm90F3Gemm.cuh, Sm90F3Attention.cuh, tasks/LayerNormTaskBody.h,
