@@ -102,6 +102,30 @@ __device__ __forceinline__ bool wait_bounded(uint64_t* bar, uint32_t parity, uns
   return true;
 }
 
+// 32 consecutive fp32 columns of this thread's tensor-memory lane in one instruction.
+__device__ __forceinline__ void tmem_load_32(uint32_t address, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, "
+      "%20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+      "tcgen05.wait::ld.sync.aligned;"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+        "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(address)
+      : "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// One 32-byte store (a whole sector) to a 32-byte aligned global address.
+__device__ __forceinline__ void store_32_bytes(void* dst, const uint4& lo, const uint4& hi) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst), "r"(lo.x), "r"(lo.y), "r"(lo.z), "r"(lo.w),
+               "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w)
+               : "memory");
+}
+
 // ---- GEMM on tcgen05 -----------------------------------------------------------------------------------------
 struct GemmArgs {
   const void* bias[3];     // one per weight map (QKV: query, key, value; otherwise the same three times)
@@ -119,7 +143,7 @@ template <int BN, bool DEEP = false> struct GemmShape {
   static constexpr int kStages = DEEP ? 10 : BN >= 128 ? 3 : BN == 64 ? 4 : 5;
   static constexpr int kBBytes = BN * kTileK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kSmem = kStages * kStageBytes + 1024 /* alignment */ + 256 /* barriers */;
+  static constexpr int kSmem = kStages * kStageBytes + 1024 /* alignment */ + 256 /* barriers */ + 512 /* the tile's bias */;
   static constexpr int kTmemCols = BN < 32 ? 32 : BN;
 };
 
@@ -139,6 +163,7 @@ __global__ void __launch_bounds__(kGemmThreads) encoder_gemm(const __grid_consta
   uint64_t* empty = full + S;
   uint64_t* accum = empty + S;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
+  unsigned char* bias_tile = tiles + S * Shape::kStageBytes + 256;   // BN elements of T, staged by the epilogue warps
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * BN, m0 = blockIdx.y * kTileM, k0 = blockIdx.z * g.kchunks;
@@ -207,36 +232,51 @@ __global__ void __launch_bounds__(kGemmThreads) encoder_gemm(const __grid_consta
       umma_commit(accum);   // arrives once everything issued above is done (at once if nothing was)
     }
   } else {
+    // while the main loop runs: this tile's bias into shared memory (weights: no need to wait for the kernel before)
+    if (EPI != kEpiPartial) {
+      const int e = threadIdx.x - 64;
+      if (e < BN / 8) reinterpret_cast<uint4*>(bias_tile)[e] = __ldg(reinterpret_cast<const uint4*>(static_cast<const T*>(g.bias[which]) + nm) + e);
+      asm volatile("bar.sync 1, 256;" ::: "memory");   // the eight epilogue warps
+    }
     const bool ok = wait_bounded(accum, 0, g.status, 4);
     tcgen05_fence_after();
     const int quarter = warp & 3, column_half = (warp - 2) >> 2;
     const int row = m0 + 32 * quarter + lane;
+    constexpr int W = BN >= 64 ? 32 : 16;          // columns per tensor-memory load
     if (ok) {
-#pragma unroll 1
-      for (int c = column_half * (BN / 32); c < (column_half + 1) * (BN / 32); ++c) {
-        float v[16];
-        tmem_load_16(tmem + (uint32_t(32 * quarter) << 16) + uint32_t(c * 16), v);
-        if (EPI == kEpiPartial) {
-          float* dst = static_cast<float*>(g.out) + size_t(blockIdx.z) * g.part_stride + size_t(row) * g.ldc + n0 + c * 16;
 #pragma unroll
-          for (int i = 0; i < 4; ++i) reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+      for (int c = column_half * (BN / 2); c < (column_half + 1) * (BN / 2); c += W) {
+        float v[W];
+        if constexpr (W == 32) {
+          tmem_load_32(tmem + (uint32_t(32 * quarter) << 16) + uint32_t(c), v);
         } else {
-          const T* bias = static_cast<const T*>(g.bias[which]) + nm + c * 16;
-          float lo[8], hi[8];
-          unpack8<T>(__ldg(reinterpret_cast<const uint4*>(bias)), lo);
-          unpack8<T>(__ldg(reinterpret_cast<const uint4*>(bias) + 1), hi);
+          tmem_load_16(tmem + (uint32_t(32 * quarter) << 16) + uint32_t(c), v);
+        }
+        if (EPI == kEpiPartial) {
+          float* dst = static_cast<float*>(g.out) + size_t(blockIdx.z) * g.part_stride + size_t(row) * g.ldc + n0 + c;
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            lo[i] += v[i];
-            hi[i] += v[8 + i];
-            if (EPI == kEpiBiasGelu) {   // the exact (erf) GELU of the BERT feed-forward
-              lo[i] = 0.5f * lo[i] * (1.0f + erff(lo[i] * 0.70710678118654752f));
-              hi[i] = 0.5f * hi[i] * (1.0f + erff(hi[i] * 0.70710678118654752f));
+          for (int i = 0; i < W / 8; ++i)
+            store_32_bytes(dst + 8 * i,
+                           make_uint4(__float_as_uint(v[8 * i]), __float_as_uint(v[8 * i + 1]), __float_as_uint(v[8 * i + 2]), __float_as_uint(v[8 * i + 3])),
+                           make_uint4(__float_as_uint(v[8 * i + 4]), __float_as_uint(v[8 * i + 5]), __float_as_uint(v[8 * i + 6]), __float_as_uint(v[8 * i + 7])));
+        } else {
+          T* dst = static_cast<T*>(g.out) + size_t(row) * g.ldc + n0 + c;
+#pragma unroll
+          for (int i = 0; i < W / 16; ++i) {
+            float lo[8], hi[8];
+            unpack8<T>(reinterpret_cast<const uint4*>(bias_tile)[(c + 16 * i) / 8], lo);
+            unpack8<T>(reinterpret_cast<const uint4*>(bias_tile)[(c + 16 * i) / 8 + 1], hi);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              lo[j] += v[16 * i + j];
+              hi[j] += v[16 * i + 8 + j];
+              if (EPI == kEpiBiasGelu) {   // the exact (erf) GELU of the BERT feed-forward
+                lo[j] = 0.5f * lo[j] * (1.0f + erff(lo[j] * 0.70710678118654752f));
+                hi[j] = 0.5f * hi[j] * (1.0f + erff(hi[j] * 0.70710678118654752f));
+              }
             }
+            store_32_bytes(dst + 16 * i, pack8<T>(lo), pack8<T>(hi));
           }
-          T* dst = static_cast<T*>(g.out) + size_t(row) * g.ldc + n0 + c * 16;
-          reinterpret_cast<uint4*>(dst)[0] = pack8<T>(lo);
-          reinterpret_cast<uint4*>(dst)[1] = pack8<T>(hi);
         }
       }
     }
