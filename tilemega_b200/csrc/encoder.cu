@@ -82,6 +82,20 @@ __device__ __forceinline__ void prefetch_map(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
 
+// erf(x) by the rational approximation 7.1.26 of Abramowitz and Stegun (absolute error below 1e-6 in fp32
+// arithmetic, far inside a 16-bit output's resolution): two special-function instructions and six multiply-adds, where the library's erff
+// costs the GELU epilogue about as much as the tile's whole main loop.
+__device__ __forceinline__ float erf_fast(float x) {
+  const float a = fabsf(x);
+  const float t = __fdividef(1.0f, fmaf(0.3275911f, a, 1.0f));
+  float poly = fmaf(t, 1.061405429f, -1.453152027f);
+  poly = fmaf(poly, t, 1.421413741f);
+  poly = fmaf(poly, t, -0.284496736f);
+  poly = fmaf(poly, t, 0.254829592f);
+  const float tail = poly * t * ex2(-1.4426950408889634f * a * a);
+  return copysignf(1.0f - tail, x);
+}
+
 // ---- bounded waits -------------------------------------------------------------------------------------------
 // Wait for a phase of an mbarrier, but not for ever: after kWaitLimitNs (or once another wait of the launch
 // has given up) the caller gets `false`, leaves its loop and the kernel runs to its end. status[0] keeps the
@@ -170,7 +184,6 @@ __global__ void __launch_bounds__(kGemmThreads) encoder_gemm(const __grid_consta
   const int which = n0 / g.n_per_map, nm = n0 - which * g.n_per_map;   // weight map and the row inside it
   const CUtensorMap* wmap = which == 0 ? &wmap0 : which == 1 ? &wmap1 : &wmap2;
 
-  allow_dependents();
   if (threadIdx.x == 0) {
     prefetch_map(&amap);
     prefetch_map(wmap);
@@ -240,6 +253,9 @@ __global__ void __launch_bounds__(kGemmThreads) encoder_gemm(const __grid_consta
     }
     const bool ok = wait_bounded(accum, 0, g.status, 4);
     tcgen05_fence_after();
+    // the main loop is over: the next kernel may start (its CTAs then find the SMs this grid is about to leave,
+    // and its prologue and first weight tiles run under this epilogue)
+    allow_dependents();
     const int quarter = warp & 3, column_half = (warp - 2) >> 2;
     const int row = m0 + 32 * quarter + lane;
     constexpr int W = BN >= 64 ? 32 : 16;          // columns per tensor-memory load
@@ -271,8 +287,8 @@ __global__ void __launch_bounds__(kGemmThreads) encoder_gemm(const __grid_consta
               lo[j] += v[16 * i + j];
               hi[j] += v[16 * i + 8 + j];
               if (EPI == kEpiBiasGelu) {   // the exact (erf) GELU of the BERT feed-forward
-                lo[j] = 0.5f * lo[j] * (1.0f + erff(lo[j] * 0.70710678118654752f));
-                hi[j] = 0.5f * hi[j] * (1.0f + erff(hi[j] * 0.70710678118654752f));
+                lo[j] = 0.5f * lo[j] * (1.0f + erf_fast(lo[j] * 0.70710678118654752f));
+                hi[j] = 0.5f * hi[j] * (1.0f + erf_fast(hi[j] * 0.70710678118654752f));
               }
             }
             store_32_bytes(dst + 16 * i, pack8<T>(lo), pack8<T>(hi));
