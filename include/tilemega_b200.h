@@ -44,7 +44,8 @@ enum { TM_DTYPE_BF16 = 0, TM_DTYPE_F32 = 1, TM_DTYPE_I32 = 2,
 /* ServingAbi.h:17-23. All three phases are built. TM_SERVING_FORWARD (a stateless encoder pass; the reference's
  * forward runtime behind the same entry points is include/tilemega/Codegen/tasks/Sm90F3Runtime.cuh:95-200): seq =
  * the positions per sequence (128), capacity 0, ONE plan step at past 0; external buffers are the module's
- * parameters under their qualified names, "input_ids" and "token_type_ids" (TM_DTYPE_I64, [batch][seq]) and the
+ * parameters under their qualified names, "input_ids" and "token_type_ids" (TM_DTYPE_I64, [batch][seq]; with
+ * "mask": true in the sidecar also "attention_mask", 0 = hidden key position) and the
  * outputs "last_hidden_state" ([batch][seq][hidden]) and "pooler_output" ([batch][hidden]); tm_plan_set_prompt_len,
  * the tracing, probe and tensor-parallel entry points refuse such a plan. TM_SERVING_DECODE: seq = 1, one sequence position per plan step
  * (past_lo..past_hi = 0..capacity-1). TM_SERVING_PREFILL: seq = the prompt length the plan was emitted for,

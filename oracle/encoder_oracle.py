@@ -24,9 +24,10 @@ import torch.nn.functional as F
 
 
 def encoder_forward(weights: dict[str, torch.Tensor], config: dict, input_ids: torch.Tensor, token_type_ids: torch.Tensor,
-                    dtype: torch.dtype = torch.float32) -> tuple[torch.Tensor, torch.Tensor]:
+                    dtype: torch.dtype = torch.float32, attention_mask: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor]:
     """(last_hidden_state [B, S, H], pooler_output [B, H]) in `dtype` arithmetic (every module output rounded to it,
-    as a module cast to that dtype does)."""
+    as a module cast to that dtype does). `attention_mask` [B, S] (0 = hidden key position) becomes the module's
+    additive mask: the most negative finite number of the score type on hidden keys, for every query."""
     w = {name: tensor.to(dtype) for name, tensor in weights.items()}
     hidden, heads, eps = config["hidden_size"], config["num_attention_heads"], float(config.get("layer_norm_eps", 1e-12))
     dim = hidden // heads
@@ -43,6 +44,9 @@ def encoder_forward(weights: dict[str, torch.Tensor], config: dict, input_ids: t
         k = split(F.linear(x, w[p + "attention.self.key.weight"], w[p + "attention.self.key.bias"]))
         v = split(F.linear(x, w[p + "attention.self.value.weight"], w[p + "attention.self.value.bias"]))
         scores = torch.matmul(q, k.transpose(-1, -2)) / math.sqrt(dim)
+        if attention_mask is not None:
+            hidden_keys = (attention_mask == 0)[:, None, None, :]
+            scores = scores.masked_fill(hidden_keys, torch.finfo(scores.dtype).min)
         context = torch.matmul(torch.softmax(scores.float(), dim=-1).to(dtype), v)
         context = context.transpose(1, 2).reshape(batch, seq, hidden)
         attended = F.linear(context, w[p + "attention.output.dense.weight"], w[p + "attention.output.dense.bias"])

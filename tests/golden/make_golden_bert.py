@@ -12,7 +12,7 @@ sys.path.insert(0, str(Path(__file__).resolve().parents[2]))
 from tilemega_b200.synthetic import TINY_BERT, encoder_inputs, encoder_weights   # noqa: E402
 
 
-def module_outputs(config: dict, weights: dict, ids: torch.Tensor, types: torch.Tensor):
+def module_outputs(config: dict, weights: dict, ids: torch.Tensor, types: torch.Tensor, mask: torch.Tensor | None = None):
     from transformers import BertConfig, BertModel
     keys = ("hidden_size", "intermediate_size", "num_attention_heads", "num_hidden_layers", "vocab_size",
             "max_position_embeddings", "type_vocab_size", "layer_norm_eps", "hidden_act")
@@ -23,7 +23,7 @@ def module_outputs(config: dict, weights: dict, ids: torch.Tensor, types: torch.
     if unexpected or any("position_ids" not in name for name in missing):
         raise RuntimeError(f"state dict mismatch: missing {missing}, unexpected {unexpected}")
     with torch.inference_mode():
-        out = module(input_ids=ids, token_type_ids=types)
+        out = module(input_ids=ids, token_type_ids=types) if mask is None else module(input_ids=ids, token_type_ids=types, attention_mask=mask)
     return out.last_hidden_state.clone(), out.pooler_output.clone()
 
 
@@ -32,7 +32,11 @@ if __name__ == "__main__":
     weights = encoder_weights(TINY_BERT, seed=0)
     ids, types = encoder_inputs(TINY_BERT, batch=2, seed=1)
     hidden, pooled = module_outputs(TINY_BERT, weights, ids, types)
+    # the same inputs with padded tails (the reference's masked check: python/tilemega/dnn/check.py:151-171, 251-253)
+    mask = (torch.arange(ids.shape[1])[None, :] < torch.tensor([[77], [128 - 19]])).to(torch.int64)
+    masked_hidden, masked_pooled = module_outputs(TINY_BERT, weights, ids, types, mask)
     target = Path(__file__).with_name("tiny_bert.pt")
     torch.save({"config": TINY_BERT, "input_ids": ids, "token_type_ids": types, "last_hidden_state": hidden,
-                "pooler_output": pooled}, target)
+                "pooler_output": pooled, "attention_mask": mask, "masked_last_hidden_state": masked_hidden,
+                "masked_pooler_output": masked_pooled}, target)
     print(target, hidden.shape, float(hidden.abs().max()))

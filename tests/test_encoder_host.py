@@ -21,6 +21,12 @@ def test_oracle_matches_the_module_fixture():
     # fp32 against fp32: only the order of summation differs
     assert (hidden - golden["last_hidden_state"]).abs().max() < 2e-5
     assert (pooled - golden["pooler_output"]).abs().max() < 2e-5
+    # padded tails: every position of the module's output, the padded ones included
+    hidden, pooled = encoder_forward(weights, golden["config"], golden["input_ids"], golden["token_type_ids"],
+                                     attention_mask=golden["attention_mask"])
+    assert (hidden - golden["masked_last_hidden_state"]).abs().max() < 2e-5
+    assert (pooled - golden["masked_pooler_output"]).abs().max() < 2e-5
+    assert (golden["masked_last_hidden_state"] - golden["last_hidden_state"]).abs().max() > 1e-2   # the mask matters
 
 
 def test_oracle_matches_the_module_run_here():
@@ -61,6 +67,9 @@ def test_forward_plan_tables(plan_dir):
     assert {name for name, buffer in table.items() if buffer.role == 0} == {"forward.hidden", "forward.qkv", "forward.context", "forward.ffn"}
     bf16 = PlanLibrary(emit_plan(config, plan_dir, phase="forward", batch_lo=8, dtype="bf16"))
     assert {buffer.dtype for buffer in bf16.buffers} == {0, 3}
+    assert "attention_mask" not in table
+    masked = {buffer.name: buffer for buffer in PlanLibrary(emit_plan(config, plan_dir, phase="forward", batch_lo=8, mask=True)).buffers}
+    assert (masked["attention_mask"].role, masked["attention_mask"].dtype, masked["attention_mask"].elements_per_batch) == (1, 3, 128)
     # without a CUDA device the plan refuses loudly
     if not torch.cuda.is_available():
         with pytest.raises(RuntimeError):

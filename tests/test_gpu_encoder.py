@@ -29,8 +29,8 @@ def run_case(config, batch, dtype_name, plan_dir, seed):
     ids, types = synthetic.encoder_inputs(config, batch, seed=seed + 1)
     so = emit_plan(config, plan_dir, phase="forward", batch_lo=batch, dtype=dtype_name)
     with EncoderEngine(TensorCheckpoint(weights), so, batch) as engine:
-        hidden, pooled = engine(ids.cuda(), types.cuda(), L2)
-        again, pooled_again = engine(ids.cuda(), types.cuda(), L1)
+        hidden, pooled = engine(ids.cuda(), types.cuda(), mode=L2)
+        again, pooled_again = engine(ids.cuda(), types.cuda(), mode=L1)
         # both executor modes, and a repeated launch, give the same bits (check.py:96-98)
         assert torch.equal(hidden, again) and torch.equal(pooled, pooled_again)
     truth, truth_pooled = encoder_forward(weights, config, ids, types)
@@ -63,6 +63,34 @@ def test_tiny_encoder_matches_the_module_fixture(plan_dir):
     assert token_cosine(hidden.float().cpu(), golden["last_hidden_state"]).min() >= COSINE
     assert (hidden.float().cpu() - golden["last_hidden_state"]).abs().max() < 3e-2
     assert (pooled.float().cpu() - golden["pooler_output"]).abs().max() < 1e-2
+
+
+def test_padded_sequences_match_the_oracle_and_the_module_fixture(plan_dir):
+    """A plan with the attention_mask input: the module's own outputs on padded inputs (every position, the padded
+    ones included), then BERT-base shapes with a different visible length per sequence, one of them a single token."""
+    golden = torch.load(Path(__file__).parent / "golden" / "tiny_bert.pt")
+    config = golden["config"]
+    weights = synthetic.encoder_weights(config, seed=0)
+    so = emit_plan(config, plan_dir, phase="forward", batch_lo=2, dtype="f16", mask=True)
+    with EncoderEngine(TensorCheckpoint(weights), so, 2) as engine:
+        hidden, pooled = engine(golden["input_ids"].cuda(), golden["token_type_ids"].cuda(), golden["attention_mask"].cuda())
+        plain, _ = engine(golden["input_ids"].cuda(), golden["token_type_ids"].cuda())   # no mask given: all visible
+    assert token_cosine(hidden.float().cpu(), golden["masked_last_hidden_state"]).min() >= COSINE
+    assert (hidden.float().cpu() - golden["masked_last_hidden_state"]).abs().max() < 3e-2
+    assert (pooled.float().cpu() - golden["masked_pooler_output"]).abs().max() < 1e-2
+    assert (plain.float().cpu() - golden["last_hidden_state"]).abs().max() < 3e-2
+    config, batch = synthetic.BERT_BASE, 4
+    weights = {name: tensor.half().float() for name, tensor in synthetic.encoder_weights(config, seed=40).items()}
+    ids, types = synthetic.encoder_inputs(config, batch, seed=41)
+    mask = (torch.arange(128)[None, :] < torch.tensor([[128], [1], [64], [97]])).to(torch.int64)
+    so = emit_plan(config, plan_dir, phase="forward", batch_lo=batch, dtype="f16", mask=True)
+    with EncoderEngine(TensorCheckpoint(weights), so, batch) as engine:
+        hidden, pooled = engine(ids.cuda(), types.cuda(), mask.cuda())
+    truth, truth_pooled = encoder_forward(weights, config, ids, types, attention_mask=mask)
+    yard, _ = encoder_forward(weights, config, ids, types, torch.float16, attention_mask=mask)
+    hidden, pooled = hidden.float().cpu(), pooled.float().cpu()
+    assert token_cosine(hidden, truth).min() >= COSINE and token_cosine(pooled, truth_pooled).min() >= COSINE
+    assert (hidden - truth).abs().max().item() <= NOISE_FACTOR * (yard.float() - truth).abs().max().item() + 1e-3
 
 
 @pytest.mark.parametrize("batch,dtype_name", [(1, "f16"), (8, "f16"), (8, "bf16")])

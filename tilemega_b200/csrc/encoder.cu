@@ -429,11 +429,14 @@ template <> __device__ __forceinline__ void mma_16816<__nv_bfloat16>(float (&d)[
 // XOR-swizzled by the row (eight rows of one chunk column then sit in eight different bank groups).
 __device__ __forceinline__ uint32_t tile_addr(uint32_t base, int row, int chunk) { return base + row * 128 + ((chunk ^ (row & 7)) << 4); }
 
-// Bidirectional attention of one (sequence, head) over 128 positions, no mask (the all-ones mask of the workload):
-// softmax(Q K^T / sqrt(64)) V. A CTA takes the 128 query rows (8 warps x 16) against the 128 keys; scores, softmax
+// Bidirectional attention of one (sequence, head) over 128 positions: softmax(Q K^T / sqrt(64) + mask) V, where a
+// key position whose `mask` entry is 0 gets the most negative finite score (the additive mask the module builds from
+// its attention_mask input; every query row still attends, a row with no visible key attends uniformly). `mask` may
+// be null: every position visible. A CTA takes the 128 query rows (8 warps x 16) against the 128 keys; scores, softmax
 // and the probability operand stay in registers.
 template <typename T>
-__global__ void __launch_bounds__(256) encoder_attention(const T* qkv, T* ctx, int heads, int hidden, float scale_log2) {
+__global__ void __launch_bounds__(256) encoder_attention(const T* qkv, T* ctx, const long long* mask, int heads, int hidden,
+                                                         float scale_log2) {
   __shared__ __align__(128) unsigned char ks[kSeq * 128], vs[kSeq * 128], qs[kSeq * 128];
   const int head = blockIdx.x % heads, seq = blockIdx.x / heads;
   const int ld = 3 * hidden, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -476,6 +479,15 @@ __global__ void __launch_bounds__(256) encoder_attention(const T* qkv, T* ctx, i
       ldmatrix_x4(b, tile_addr(kbase, tp * 16 + (lane & 7) + (lane >> 4) * 8, 2 * kk + ((lane >> 3) & 1)));
       mma_16816<T>(s[2 * tp], a, b[0], b[1]);
       mma_16816<T>(s[2 * tp + 1], a, b[2], b[3]);
+    }
+  }
+  if (mask) {   // this thread's key columns of tile t: 8 t + 2 (lane % 4) and the next one
+    const long long* visible = mask + size_t(seq) * kSeq + 2 * (lane & 3);
+#pragma unroll
+    for (int t = 0; t < 16; ++t) {
+      const longlong2 m = *reinterpret_cast<const longlong2*>(visible + 8 * t);
+      if (m.x == 0) s[t][0] = s[t][2] = -3.0e38f;
+      if (m.y == 0) s[t][1] = s[t][3] = -3.0e38f;
     }
   }
   // softmax over the 128 keys of rows lane / 4 (values 0, 1 of a tile) and lane / 4 + 8 (values 2, 3)
@@ -732,6 +744,11 @@ template <typename T> cudaError_t Enqueue(EncoderPlan& plan, const PlanSpec& spe
   TMB_AT(pooled, "pooler_output")
   TMB_AT(pool_w, "pooler.dense.weight")
   TMB_AT(pool_b, "pooler.dense.bias")
+  void* mask = nullptr;
+  if (spec.forward_mask) {
+    TMB_AT(bound_mask, "attention_mask")
+    mask = bound_mask;
+  }
   cudaError_t err = cudaSuccess;
   plan.kernels = 0;
   // the first kernel of the pass is an ordinary launch: it follows whatever the caller's stream ran before
@@ -804,7 +821,7 @@ template <typename T> cudaError_t Enqueue(EncoderPlan& plan, const PlanSpec& spe
       if ((err = gemm(x, hidden, w, b, 3 * hidden, hidden, kEpiBias, qkv)) != cudaSuccess) return err;
     }
     err = Launch(encoder_attention<T>, dim3(unsigned(plan.batch * plan.heads)), dim3(256), 0, stream, chained, static_cast<const T*>(qkv),
-                 static_cast<T*>(ctx), plan.heads, hidden, scale_log2);
+                 static_cast<T*>(ctx), static_cast<const long long*>(mask), plan.heads, hidden, scale_log2);
     ++plan.kernels;
     if (err != cudaSuccess) return err;
     {

@@ -135,6 +135,7 @@ PlanSpec ForwardSpec(const Json& plan) {
   const std::string dtype = plan.str("dtype", "f16");
   if (dtype != "f16" && dtype != "bf16") throw std::invalid_argument("a forward plan computes in f16 or bf16 (dtype)");
   s.f16 = dtype == "f16";
+  s.forward_mask = plan.flag("mask", false);
   if (model.str("hidden_act", "gelu") != "gelu") throw std::invalid_argument("the encoder's feed-forward is built with the erf GELU only");
   if (model.str("position_embedding_type", "absolute") != "absolute")
     throw std::invalid_argument("the encoder is built with absolute position embeddings only");
@@ -183,6 +184,7 @@ PlanSpec ForwardSpec(const Json& plan) {
   add("pooler.dense.bias", 1, elem, H, 0, true);
   add("input_ids", 1, 3, 0, S, false);
   add("token_type_ids", 1, 3, 0, S, false);
+  if (s.forward_mask) add("attention_mask", 1, 3, 0, S, false);
   add("last_hidden_state", 1, elem, 0, S * H, false);
   add("pooler_output", 1, elem, 0, H, false);
   add("forward.hidden", 0, elem, 0, S * H, false);

@@ -64,6 +64,7 @@ struct PlanSpec {
   bool forward = false;
   bool f16 = false;             // activations and weights in fp16 (else bf16)
   int forward_seq = 0, max_position = 0, type_vocab = 0;
+  bool forward_mask = false;    // the plan takes an "attention_mask" input (int64 [batch][seq], 0 = key position hidden)
   DenseGeo dgeo[kNumGemv] = {};
   int normed_buf = -1;
   // buffer table

@@ -32,7 +32,7 @@ ENCODER_KEYS = ("hidden_size", "intermediate_size", "num_attention_heads", "num_
 
 
 def forward_document(config: dict, *, batch_lo: int = 1, batch_hi: int | None = None, seq: int = 128,
-                     dtype: str = "f16") -> dict:
+                     dtype: str = "f16", mask: bool = False) -> dict:
     """The sidecar of a forward plan (phase 2): a stateless BERT-shaped encoder pass over batch x seq tokens."""
     model = {key: config[key] for key in ENCODER_KEYS if key in config}
     batch_hi = batch_lo if batch_hi is None else batch_hi
@@ -46,8 +46,11 @@ def forward_document(config: dict, *, batch_lo: int = 1, batch_hi: int | None = 
         raise ValueError("encoder heads must be 64 wide, the hidden size a multiple of 128 up to 1024")
     if config["intermediate_size"] % 128:
         raise ValueError("encoder intermediate size must be a multiple of 128")
-    return {"execution": "graph", "arch": "sm_100a", "phase": "forward", "model": model, "batch_lo": batch_lo,
-            "batch_hi": batch_hi, "seq": seq, "dtype": dtype}
+    document = {"execution": "graph", "arch": "sm_100a", "phase": "forward", "model": model, "batch_lo": batch_lo,
+                "batch_hi": batch_hi, "seq": seq, "dtype": dtype}
+    if mask:
+        document["mask"] = True   # a third input, "attention_mask" (int64 [batch, seq]; 0 hides a key position)
+    return document
 
 
 def plan_document(config: dict, *, batch_lo: int = 1, batch_hi: int | None = None, capacity: int,

@@ -13,7 +13,7 @@ import torch
 from .plan import FORWARD, L2, PlanLibrary
 from .weights import DTYPES, load_weights
 
-INPUTS = ("input_ids", "token_type_ids")
+INPUTS = ("input_ids", "token_type_ids", "attention_mask")   # the third only in a plan emitted with mask=True
 OUTPUTS = ("last_hidden_state", "pooler_output")
 
 
@@ -38,6 +38,7 @@ class EncoderEngine:
             raise ValueError("the bound tensors differ from the plan's external buffers")
         self.plan = self.library.create(batch, {name: tensor.data_ptr() for name, tensor in self.tensors.items()}, device)
         self.plan.set_steps([0])
+        self.masked = "attention_mask" in self.tensors
         self.hidden = self.tensors["pooler_output"].numel() // batch
         self.stream = torch.cuda.current_stream()
 
@@ -49,8 +50,14 @@ class EncoderEngine:
         return (self.tensors["last_hidden_state"].view(self.batch, self.seq, self.hidden),
                 self.tensors["pooler_output"].view(self.batch, self.hidden))
 
-    def __call__(self, input_ids: torch.Tensor, token_type_ids: torch.Tensor, mode: int = L2) -> tuple[torch.Tensor, torch.Tensor]:
-        for name, value in zip(INPUTS, (input_ids, token_type_ids)):
+    def __call__(self, input_ids: torch.Tensor, token_type_ids: torch.Tensor, attention_mask: torch.Tensor | None = None,
+                 mode: int = L2) -> tuple[torch.Tensor, torch.Tensor]:
+        if attention_mask is not None and not self.masked:
+            raise ValueError("this plan was emitted without an attention_mask input")
+        if self.masked and attention_mask is None:
+            attention_mask = torch.ones_like(input_ids)
+        given = (input_ids, token_type_ids) + ((attention_mask,) if self.masked else ())
+        for name, value in zip(INPUTS, given):
             if tuple(value.shape) != (self.batch, self.seq) or value.dtype != torch.int64:
                 raise ValueError(f"{name} must be int64 [{self.batch}, {self.seq}]")
             self.tensors[name].copy_(value.reshape(-1), non_blocking=True)
