@@ -366,7 +366,7 @@ def run_forward(args) -> None:
     if args.layers:
         config["num_hidden_layers"] = args.layers
     batch, seq, steps, warmup = args.batch, 128, args.steps, max(args.warmup, 3)
-    dtype_name = "bf16" if args.weights == "bf16" and os.environ.get("TMB_ENCODER_DTYPE") == "bf16" else "f16"
+    dtype_name = args.encoder_dtype
     torch.cuda.set_device(0)
     plan_dir = PLAN_DIR / "bench"
     weights = synthetic.encoder_weights(config, seed=0)
@@ -643,6 +643,8 @@ def main() -> None:
     parser.add_argument("--layers", type=int, default=0, help="override the depth (profiling a small case)")
     parser.add_argument("--weights", choices=("bf16", "e4m3"), default="bf16",
                         help="e4m3: GEMV matrices as 8-bit codes with one fp32 scale per output row")
+    parser.add_argument("--encoder-dtype", choices=("f16", "bf16"), default="f16",
+                        help="--model bert-base: element type of the forward plan (f16: the benchmark configuration; bf16: what the reference's export runs)")
     parser.add_argument("--prefill", type=int, default=0,
                         help="secondary workload: chunked prefill of one prompt of this many tokens (one GPU)")
     parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
