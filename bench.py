@@ -268,6 +268,59 @@ def run_reference(args) -> None:
     print(json.dumps(line), flush=True)
 
 
+def run_forward_reference(args) -> None:
+    """Reference arm of the encoder workload: the module the reference exports for it (transformers.BertModel, fp32,
+    python/tilemega/dnn/export.py:50-59) on the host cores where that package is importable, else the oracle's
+    restatement of it; same metric and configuration as run_forward, a bounded sample of sequences per step."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    from oracle.encoder_oracle import encoder_forward
+    config = dict(synthetic.BERT_BASE)
+    if args.layers:
+        config["num_hidden_layers"] = args.layers
+    batch, seq = args.batch, 128
+    threads = min(os.cpu_count() or 1, 16)
+    torch.set_num_threads(threads)
+    weights = synthetic.encoder_weights(config, seed=0)
+    sample = min(batch, 8)
+    ids, types = synthetic.encoder_inputs(config, sample, seed=1)
+    kind, forward = "port", (lambda: encoder_forward(weights, config, ids, types))
+    try:
+        from transformers import BertConfig, BertModel
+        keys = ("hidden_size", "intermediate_size", "num_attention_heads", "num_hidden_layers", "vocab_size",
+                "max_position_embeddings", "type_vocab_size", "layer_norm_eps", "hidden_act")
+        bert_config = BertConfig(**{key: config[key] for key in keys})
+        bert_config._attn_implementation = "sdpa"
+        module = BertModel(bert_config).eval()
+        module.load_state_dict(weights, strict=False)
+        kind = "reference"
+
+        def forward():
+            with torch.inference_mode():
+                return module(input_ids=ids, token_type_ids=types)
+    except ImportError:
+        pass
+    steps = max(3, min(args.steps, 16))
+    forward()
+    started = time.perf_counter()
+    for _ in range(steps):
+        forward()
+    seconds = (time.perf_counter() - started) / steps
+    value = sample / seconds
+    what = "transformers.BertModel" if kind == "reference" else "the oracle's restatement of BertModel"
+    line = {
+        "impl": "reference", "metric": "encoder_sequences_per_s", "value": value, "unit": "seq/s", "n_gpus": args.gpus,
+        "steps": steps, "steps_requested": args.steps, "warmup": 1, "ms_per_step": seconds * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"bert-base-shaped encoder forward, batch {batch} x {seq} tokens, all-ones attention mask",
+                   "layers": config["num_hidden_layers"], "parallelism": "host cores", "arm": what + ", fp32, CPU"},
+        "cpu_baseline": {"value": value, "unit": "seq/s", "cores": threads, "kind": kind,
+                         "sample": f"{what}: {sample} sequence(s) of {seq} tokens per step, mean of {steps} steps"},
+        "e2e": {"value": value, "unit": "seq/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
 def run_prefill(args) -> None:
     """Secondary workload: one prompt of `--prefill` tokens through a prefill plan (phase 0 of the plan ABI):
     ONE launch whose kernel steps take 64 (sequence, position) rows each, weights streamed once per kernel
@@ -654,7 +707,9 @@ def main() -> None:
                         help="several GPUs: independent copies of the one-GPU workload instead of one sharded model")
     parser.add_argument("--tp", action="store_true", help="accepted for compatibility: several GPUs shard one model by default")
     args = parser.parse_args()
-    if args.impl == "reference":
+    if args.impl == "reference" and args.model == "bert-base":
+        run_forward_reference(args)
+    elif args.impl == "reference":
         run_reference(args)
     elif args.model == "bert-base":
         run_forward(args)
