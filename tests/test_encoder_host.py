@@ -76,6 +76,47 @@ def test_forward_plan_tables(plan_dir):
             lib.create(1, {name: 16 for name, buffer in table.items() if buffer.role == 1}, 0)
 
 
+def test_forward_plan_bridge_file(plan_dir):
+    """The export bridge the reference's forward driver reads (python/tilemega/dnn/check.py:40, 45-59): its user
+    inputs and outputs are exactly the external buffers that carry no packing recipe, and its dtypes are the ones
+    that driver maps (a bf16 plan). No identity file is written (it is the reference compiler's build record, and the
+    reference's PlanLibrary verifies one when it finds one)."""
+    import json
+    so = emit_plan(synthetic.TINY_BERT, plan_dir, phase="forward", batch_lo=2, dtype="bf16", mask=True)
+    assert not Path(str(so) + ".identity.json").exists()
+    bridge = json.loads(Path(str(so) + ".bridge.json").read_text())
+    nodes = {node["name"]: node for node in bridge["nodes"]}
+    inputs = [item["name"] for item in bridge["signature"]["inputs"] if item["kind"] == "USER_INPUT"]
+    outputs = [item["name"] for item in bridge["signature"]["outputs"] if item["kind"] == "USER_OUTPUT"]
+    lib = PlanLibrary(so)
+    unpacked = {buffer.name for buffer in lib.buffers if buffer.role == 1 and not buffer.pack_json}
+    assert set(inputs) | set(outputs) == unpacked and inputs == ["input_ids", "token_type_ids", "attention_mask"]
+    assert all(nodes[name]["dtype"] == "torch.int64" and nodes[name]["shape"] == [2, 128] for name in inputs)
+    assert {nodes[name]["dtype"] for name in outputs} == {"torch.bfloat16"}
+    assert nodes["last_hidden_state"]["shape"] == [2, 128, 256] and nodes["pooler_output"]["shape"] == [2, 256]
+
+
+def test_reference_driver_classes_accept_a_forward_plan(plan_dir):
+    """Where the reference tree is at hand: its own PlanLibrary loads a forward plan emitted here and sees a stateless
+    forward library, and its recipe table lists exactly the module's parameters."""
+    import sys
+    reference = Path("/root/reference/python")
+    if not (reference / "tilemega" / "serving" / "plan.py").is_file():
+        pytest.skip("the reference tree is not present")
+    sys.path.insert(0, str(reference))
+    try:
+        from tilemega.serving.plan import FORWARD as THEIR_FORWARD, PlanLibrary as TheirLibrary
+        from tilemega.serving.weights import weight_recipes
+    except Exception as error:   # a dependency of the reference's package that is not installed here
+        pytest.skip(f"the reference's driver does not import here: {error}")
+    finally:
+        sys.path.remove(str(reference))
+    so = emit_plan(synthetic.TINY_BERT, plan_dir, phase="forward", batch_lo=2, dtype="bf16")
+    theirs = TheirLibrary(so)
+    assert theirs.info.phase == THEIR_FORWARD and not theirs.info.capacity and theirs.info.batch_lo <= 2 <= theirs.info.batch_hi
+    assert set(weight_recipes(theirs)) == {name for name, _ in synthetic.encoder_parameter_shapes(synthetic.TINY_BERT)}
+
+
 def test_forward_plan_rejects_shapes_it_does_not_cover():
     with pytest.raises(ValueError):
         forward_document(synthetic.BERT_BASE, seq=64)

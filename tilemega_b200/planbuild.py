@@ -138,7 +138,31 @@ def emit_plan(config: dict, out_dir: str | Path | None = None, **options) -> Pat
         tmp = Path(str(sidecar) + unique)
         tmp.write_text(text)
         os.replace(tmp, sidecar)
+    if document.get("phase") == "forward":
+        _write_bridge(target, document, unique)
     return target
+
+
+def _write_bridge(target: Path, document: dict, unique: str) -> None:
+    """The export bridge the reference's forward driver reads (python/tilemega/dnn/check.py:40, 45-49), as
+    `<so>.bridge.json`: the graph's user inputs and outputs with shape and dtype. No `<so>.identity.json` is written:
+    that file is the reference compiler's build record (hashes of its generated source and ptxas log, checked by
+    python/tilemega/build/identity.py:99-130), and the reference's PlanLibrary loads a library without one."""
+    model, seq, batch = document["model"], document["seq"], document["batch_lo"]
+    element = "torch.float16" if document["dtype"] == "f16" else "torch.bfloat16"
+    inputs = ["input_ids", "token_type_ids"] + (["attention_mask"] if document.get("mask") else [])
+    nodes = [{"name": name, "shape": [batch, seq], "dtype": "torch.int64"} for name in inputs]
+    nodes += [{"name": "last_hidden_state", "shape": [batch, seq, model["hidden_size"]], "dtype": element},
+              {"name": "pooler_output", "shape": [batch, model["hidden_size"]], "dtype": element}]
+    bridge = {"nodes": nodes,
+              "signature": {"inputs": [{"name": name, "kind": "USER_INPUT"} for name in inputs],
+                            "outputs": [{"name": name, "kind": "USER_OUTPUT"} for name in ("last_hidden_state", "pooler_output")]}}
+    path = Path(str(target) + ".bridge.json")
+    text = json.dumps(bridge, indent=1, sort_keys=True) + "\n"
+    if not path.exists() or path.read_text() != text:
+        tmp = Path(str(path) + unique)
+        tmp.write_text(text)
+        os.replace(tmp, path)
 
 
 def remove_plans(out_dir: str | Path) -> None:
