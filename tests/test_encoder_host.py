@@ -100,9 +100,12 @@ def test_reference_driver_classes_accept_a_forward_plan(plan_dir):
     """Where the reference tree is at hand: its own PlanLibrary loads a forward plan emitted here and sees a stateless
     forward library, and its recipe table lists exactly the module's parameters."""
     import sys
-    reference = Path("/root/reference/python")
-    if not (reference / "tilemega" / "serving" / "plan.py").is_file():
-        pytest.skip("the reference tree is not present")
+    sys.path.insert(0, str(Path(__file__).resolve().parents[1] / "oracle"))
+    from build_ref import reference_tree
+    tree = reference_tree()
+    if tree is None or not (tree / "python" / "tilemega" / "serving" / "plan.py").is_file():
+        pytest.skip("no reference tree on this machine")
+    reference = tree / "python"
     sys.path.insert(0, str(reference))
     try:
         from tilemega.serving.plan import FORWARD as THEIR_FORWARD, PlanLibrary as TheirLibrary
