@@ -410,6 +410,8 @@ def run_forward(args) -> None:
     through a forward plan (phase 2 of the plan ABI). A step is one forward pass = one graph launch of the
     encoder's kernels; `--steps` passes are timed back to back between two CUDA events. The CPU baseline is the
     oracle's fp32 forward on the host cores."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return   # the encoder forward does not shard: one GPU is measured, other ranks of a launcher have nothing to do
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the product path has no CPU implementation")
     from tilemega_b200.planbuild import PLAN_DIR, emit_plan, remove_plans
